@@ -1,0 +1,104 @@
+"""ctypes view of libchromofold_b200.so (the C ABI declared under include/chromofold_b200/).
+
+There is no fallback: if the shared library is missing or does not load, importing the symbols raises.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libchromofold_b200.so")
+
+CF_OK, CF_ERR_INVALID_ARGUMENT, CF_ERR_UNSUPPORTED, CF_ERR_CUDA = 0, 1, 2, 3
+ABI_VERSION = 1
+F16, BF16, F32 = 1, 2, 3
+CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES = 0, 1, 2
+DEVSTAT_BAD_RECORD, DEVSTAT_WAIT_EXPIRED, DEVSTAT_WORKSPACE, DEVSTAT_NONFINITE, DEVSTAT_ARENA_FULL = 1, 2, 4, 8, 16
+
+_u32, _u64, _vp, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_float
+
+
+class CodebookTables(C.Structure):
+    _fields_ = [("rans_slot", _u32 * 4096), ("rans_freq", C.c_uint16 * 256), ("rans_cum", C.c_uint16 * 256),
+                ("huff_lut", C.c_uint16 * 4096), ("huff_code", _u32 * 256)]
+
+
+class SealedAttentionDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", _u32), ("abi_version", _u32),
+        ("kv_head_count", _u32), ("query_head_count", _u32), ("head_dim", _u32), ("page_tokens", _u32),
+        ("block_size", _u32), ("kv_head_begin", _u32), ("kv_head_span", _u32), ("codebook_id", _u32),
+        ("arena", _vp), ("page_dir", _vp), ("page_table", _vp), ("seq_sealed_tokens", _vp), ("seq_slots", _vp),
+        ("page_table_stride", _u32), ("seq_count", _u32),
+        ("k_tables", _vp), ("v_tables", _vp),
+        ("tail_k", _vp), ("tail_v", _vp), ("tail_tokens", _vp),
+        ("queries", _vp), ("output", _vp), ("query_type", _u32), ("output_type", _u32),
+        ("softmax_scale", _f32), ("causal_window", _u32),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("min_pages_per_unit", _u32), ("kernel", _u32),
+        ("status", _vp), ("reserved", _u32),
+    ]
+
+
+class SealDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", _u32), ("abi_version", _u32),
+        ("kv_head_count", _u32), ("head_dim", _u32), ("page_tokens", _u32), ("block_size", _u32),
+        ("coder", _u32), ("codebook_id", _u32),
+        ("k_tables", _vp), ("v_tables", _vp), ("tail_k", _vp), ("tail_v", _vp),
+        ("job_slots", _vp), ("job_pages", _vp), ("job_tokens", _vp),
+        ("job_count", _u32), ("reserved", _u32),
+        ("arena", _vp), ("arena_units", _u64), ("arena_cursor_units", _vp), ("page_dir", _vp), ("status", _vp),
+    ]
+
+
+class DenseAttentionDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", _u32), ("abi_version", _u32),
+        ("kv_head_count", _u32), ("query_head_count", _u32), ("head_dim", _u32), ("page_tokens", _u32),
+        ("pool_k", _vp), ("pool_v", _vp), ("page_table", _vp), ("seq_sealed_tokens", _vp), ("seq_slots", _vp),
+        ("page_table_stride", _u32), ("seq_count", _u32),
+        ("queries", _vp), ("output", _vp), ("softmax_scale", _f32), ("causal_window", _u32),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("min_pages_per_unit", _u32), ("reserved", _u32),
+    ]
+
+
+# Every symbol the headers under include/chromofold_b200 declare; the symbol test walks this list.
+EXPORTS = {
+    "sealed_kv.h": [
+        "cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
+        "cf_b200_sealed_attention_async", "cf_b200_codebook_build", "cf_b200_seal_validate",
+        "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
+        "cf_b200_dense_attention_async", "cf_b200_build_info",
+    ],
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library. Raises if it was not built (run `python -m chromofold_b200.build`)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m chromofold_b200.build`; "
+                               "this package has no CPU or PyTorch fallback")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.cf_b200_build_info.restype = C.c_char_p
+        for name in ("cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
+                     "cf_b200_sealed_attention_async", "cf_b200_codebook_build", "cf_b200_seal_validate",
+                     "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
+                     "cf_b200_dense_attention_async"):
+            getattr(_lib, name).restype = C.c_int
+    return _lib
+
+
+class CfError(RuntimeError):
+    def __init__(self, what, status):
+        names = {1: "CF_ERR_INVALID_ARGUMENT", 2: "CF_ERR_UNSUPPORTED", 3: "CF_ERR_CUDA"}
+        super().__init__(f"{what}: {names.get(status, status)}")
+        self.status = status
+
+
+def check(what, status):
+    if status != CF_OK:
+        raise CfError(what, status)

@@ -1,0 +1,246 @@
+"""Host-side mirror of the reference's single-layer compressed cache for the sealed-KV path.
+
+The reference's CompressedKvCache (src/runtime/compressed_kv_cache.cu:66-178) keeps an appendable active tail,
+seals full pages and hands an attention view to the kernel. This class keeps the same life cycle —
+append -> seal_full_pages -> attention — for a batch of sequence slots, but every buffer lives on the GPU and
+sealing and attention are the library's CUDA entry points (include/chromofold_b200/sealed_kv.h). PyTorch is
+used for device memory and streams only.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _native as N
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream_ptr():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class SealedKvLayer:
+    """One layer of sealed KV pages for up to `max_sequences` sequence slots on one GPU."""
+
+    def __init__(self, *, kv_heads, query_heads, head_dim=128, page_tokens=16, block_size=64, coder=N.CODER_RANS,
+                 max_sequences, max_pages_per_sequence, max_pages, arena_bytes, workspace_bytes=None,
+                 codebook_id=0, device="cuda:0"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("chromofold_b200 needs a CUDA device; there is no CPU path")
+        self.lib = N.lib()
+        self.device = torch.device(device)
+        self.kv_heads, self.query_heads, self.head_dim = kv_heads, query_heads, head_dim
+        self.page_tokens, self.block_size, self.coder, self.codebook_id = page_tokens, block_size, coder, codebook_id
+        self.max_sequences, self.max_pages_per_sequence, self.max_pages = max_sequences, max_pages_per_sequence, max_pages
+        dev = self.device
+        self.arena_units = arena_bytes // 16
+        self.arena = torch.zeros(self.arena_units * 16 + 64, dtype=torch.uint8, device=dev)
+        self.page_dir = torch.zeros(max_pages * kv_heads, dtype=torch.int64, device=dev)
+        self.page_table = torch.zeros((max_sequences, max_pages_per_sequence), dtype=torch.int32, device=dev)
+        self.sealed_tokens = torch.zeros(max_sequences, dtype=torch.int32, device=dev)
+        self.tail_tokens = torch.zeros(max_sequences, dtype=torch.int32, device=dev)
+        self.tail_k = torch.zeros((max_sequences, kv_heads, page_tokens, head_dim), dtype=torch.float16, device=dev)
+        self.tail_v = torch.zeros_like(self.tail_k)
+        self.cursor = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.k_tables = torch.zeros(C.sizeof(N.CodebookTables), dtype=torch.uint8, device=dev)
+        self.v_tables = torch.zeros_like(self.k_tables)
+        if workspace_bytes is None:
+            d = self._attention_desc(None, None, max_sequences, None)
+            need = C.c_uint64(0)
+            N.check("workspace_bytes", self.lib.cf_b200_sealed_attention_workspace_bytes(
+                C.byref(d), C.c_uint64(max_sequences * max_pages_per_sequence), C.byref(need)))
+            workspace_bytes = need.value
+        self.workspace = torch.zeros(workspace_bytes + 256, dtype=torch.uint8, device=dev)
+        # host bookkeeping (authoritative for page ids and lengths)
+        self.h_page_table = np.zeros((max_sequences, max_pages_per_sequence), np.int32)
+        self.h_sealed = np.zeros(max_sequences, np.int64)
+        self.h_tail = np.zeros(max_sequences, np.int64)
+        self.next_page_id = 1  # page id 0 stays unpublished so a zeroed table entry is detectable
+        self.host_tables = (N.CodebookTables(), N.CodebookTables())
+
+    # -- codebooks ---------------------------------------------------------------------------------
+    def set_codebooks(self, hist_k, hist_v):
+        for hist, host, dev in ((hist_k, self.host_tables[0], self.k_tables), (hist_v, self.host_tables[1], self.v_tables)):
+            h = np.ascontiguousarray(hist, np.uint64)
+            N.check("codebook_build", self.lib.cf_b200_codebook_build(h.ctypes.data_as(C.c_void_p), C.byref(host)))
+            dev.copy_(torch.frombuffer(bytearray(bytes(host)), dtype=torch.uint8))
+
+    def histograms(self, slots=None):
+        """Symbol histograms of the quantised streams of the current tails (GPU)."""
+        slots = self._slots_tensor(slots)
+        hk = torch.zeros(256, dtype=torch.int64, device=self.device)
+        hv = torch.zeros_like(hk)
+        d = self._seal_desc(slots, None, self.tail_tokens[slots.long()].contiguous())
+        N.check("histogram", self.lib.cf_b200_histogram_async(C.byref(d), _ptr(hk), _ptr(hv), _stream_ptr()))
+        return hk.cpu().numpy().astype(np.uint64), hv.cpu().numpy().astype(np.uint64)
+
+    # -- append / seal -------------------------------------------------------------------------------
+    def append(self, slots, k, v):
+        """Append one token per listed slot. k, v: float16 device tensors [len(slots), kv_heads, head_dim]."""
+        slots = np.asarray(slots, np.int64)
+        if np.any(self.h_tail[slots] >= self.page_tokens):
+            raise ValueError("active tail is full: seal_full_pages() first")
+        idx = torch.as_tensor(slots, device=self.device)
+        pos = torch.as_tensor(self.h_tail[slots], device=self.device)
+        self.tail_k[idx, :, pos, :] = k.to(torch.float16)
+        self.tail_v[idx, :, pos, :] = v.to(torch.float16)
+        self.h_tail[slots] += 1
+        self.tail_tokens[idx] += 1
+
+    def fill_tails(self, slots, k, v, tokens):
+        """Set whole tails at once. k, v: float16 [len(slots), kv_heads, page_tokens, head_dim]."""
+        slots = np.asarray(slots, np.int64)
+        idx = torch.as_tensor(slots, device=self.device)
+        self.tail_k[idx] = k.to(torch.float16)
+        self.tail_v[idx] = v.to(torch.float16)
+        self.h_tail[slots] = tokens
+        self.tail_tokens[idx] = int(tokens)
+
+    def seal_full_pages(self, slots=None, force=False):
+        """Seal the tails that hold page_tokens rows (all non-empty tails with force=True, the reference's flush)."""
+        cand = np.arange(self.max_sequences) if slots is None else np.asarray(slots, np.int64)
+        full = cand[(self.h_tail[cand] >= self.page_tokens) | (force & (self.h_tail[cand] > 0))]
+        if full.size == 0:
+            return 0
+        if np.any(self.h_sealed[full] % self.page_tokens):
+            raise ValueError("a sequence with a partly filled sealed page cannot grow")
+        page_index = self.h_sealed[full] // self.page_tokens
+        if np.any(page_index >= self.max_pages_per_sequence) or self.next_page_id + full.size > self.max_pages:
+            raise ValueError("page table or page directory is full")
+        ids = np.arange(self.next_page_id, self.next_page_id + full.size, dtype=np.int32)
+        self.next_page_id += full.size
+        rows = self.h_tail[full].astype(np.int32)
+        d_slots = torch.as_tensor(full.astype(np.int32), device=self.device)
+        d_ids = torch.as_tensor(ids, device=self.device)
+        d_rows = torch.as_tensor(rows, device=self.device)
+        d = self._seal_desc(d_slots, d_ids, d_rows)
+        N.check("seal_pages", self.lib.cf_b200_seal_pages_async(C.byref(d), _stream_ptr()))
+        self.h_page_table[full, page_index] = ids
+        self.page_table[d_slots.long(), torch.as_tensor(page_index, device=self.device)] = d_ids
+        self.h_sealed[full] += rows
+        self.h_tail[full] = 0
+        self.sealed_tokens[d_slots.long()] += d_rows
+        self.tail_tokens[d_slots.long()] = 0
+        return int(full.size)
+
+    # -- import of records sealed elsewhere ------------------------------------------------------------
+    def import_records(self, slot, records, tokens_per_page=None):
+        """Append already sealed pages to `slot`. records[p][h] is the record (bytes-like) of page p, kv head h."""
+        blobs, entries = [], []
+        cursor = int(self.cursor.item())
+        for page in records:
+            for rec in page:
+                rec = np.frombuffer(bytes(rec), np.uint8)
+                assert rec.size % 16 == 0
+                entries.append(cursor | ((rec.size // 16) << 40))
+                blobs.append(rec)
+                cursor += rec.size // 16
+        if cursor > self.arena_units:
+            raise ValueError("arena is full")
+        blob = np.concatenate(blobs)
+        start = int(self.cursor.item()) * 16
+        self.arena[start:start + blob.size] = torch.from_numpy(blob).to(self.device)
+        self.cursor.fill_(cursor)
+        n = len(records)
+        ids = np.arange(self.next_page_id, self.next_page_id + n, dtype=np.int32)
+        self.next_page_id += n
+        first = int(self.h_sealed[slot] // self.page_tokens)
+        e = torch.from_numpy(np.array(entries, np.int64)).to(self.device)
+        self.page_dir[int(ids[0]) * self.kv_heads:(int(ids[-1]) + 1) * self.kv_heads] = e
+        self.h_page_table[slot, first:first + n] = ids
+        self.page_table[slot, first:first + n] = torch.from_numpy(ids).to(self.device)
+        added = n * self.page_tokens if tokens_per_page is None else int(np.sum(tokens_per_page))
+        self.h_sealed[slot] += added
+        self.sealed_tokens[slot] += added
+
+    # -- attention -----------------------------------------------------------------------------------
+    def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
+                  kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0):
+        """Decode-step attention: queries [n, query_heads, head_dim] (float16 or float32) -> float32 output."""
+        n = queries.shape[0]
+        if out is None:
+            out = torch.zeros((n, self.query_heads, self.head_dim), dtype=torch.float32, device=self.device)
+        d = self._attention_desc(queries, out, n, slots)
+        d.softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / float(np.sqrt(self.head_dim))
+        d.causal_window = causal_window
+        d.kernel = kernel
+        d.kv_head_begin, d.kv_head_span = kv_head_begin, kv_head_span
+        d.min_pages_per_unit = min_pages_per_unit
+        N.check("sealed_attention", self.lib.cf_b200_sealed_attention_async(C.byref(d), _stream_ptr()))
+        return out
+
+    def decode_pages(self, page_ids):
+        """Decode whole records to symbols on the GPU: returns (k, v) uint8 [pages, kv_heads, page_tokens*head_dim]."""
+        ids = torch.as_tensor(np.asarray(page_ids, np.int32), device=self.device)
+        n = self.page_tokens * self.head_dim
+        ks = torch.zeros((ids.numel(), self.kv_heads, n), dtype=torch.uint8, device=self.device)
+        vs = torch.zeros_like(ks)
+        d = self._attention_desc(None, None, 1, None)
+        N.check("decode_pages", self.lib.cf_b200_decode_pages_async(C.byref(d), _ptr(ids), C.c_uint32(ids.numel()),
+                                                                      _ptr(ks), _ptr(vs), _stream_ptr()))
+        return ks, vs
+
+    def record_bytes(self, page_id, kv_head):
+        """Copy one record back to the host (for byte-exactness checks and statistics)."""
+        e = int(self.page_dir[page_id * self.kv_heads + kv_head].item())
+        off, units = e & 0xFFFFFFFFFF, (e >> 40) & 0xFFFF
+        return self.arena[off * 16:(off + units) * 16].cpu().numpy()
+
+    def sealed_bytes(self):
+        return int(self.cursor.item()) * 16
+
+    def device_status(self):
+        return int(self.status.item())
+
+    # -- descriptors ---------------------------------------------------------------------------------
+    def _slots_tensor(self, slots):
+        if slots is None:
+            slots = np.arange(self.max_sequences)
+        if isinstance(slots, torch.Tensor):
+            return slots.to(device=self.device, dtype=torch.int32)
+        return torch.as_tensor(np.asarray(slots, np.int32), device=self.device)
+
+    def _attention_desc(self, queries, out, n, slots):
+        d = N.SealedAttentionDesc()
+        d.struct_size, d.abi_version = C.sizeof(N.SealedAttentionDesc), N.ABI_VERSION
+        d.kv_head_count, d.query_head_count, d.head_dim = self.kv_heads, self.query_heads, self.head_dim
+        d.page_tokens, d.block_size, d.codebook_id = self.page_tokens, self.block_size, self.codebook_id
+        d.arena, d.page_dir = self.arena.data_ptr(), self.page_dir.data_ptr()
+        d.page_table, d.seq_sealed_tokens = self.page_table.data_ptr(), self.sealed_tokens.data_ptr()
+        if slots is not None:
+            self._slots_keepalive = self._slots_tensor(slots)
+            d.seq_slots = self._slots_keepalive.data_ptr()
+        d.page_table_stride, d.seq_count = self.max_pages_per_sequence, n
+        d.k_tables, d.v_tables = self.k_tables.data_ptr(), self.v_tables.data_ptr()
+        d.tail_k, d.tail_v, d.tail_tokens = self.tail_k.data_ptr(), self.tail_v.data_ptr(), self.tail_tokens.data_ptr()
+        if queries is not None:
+            d.queries = queries.data_ptr()
+            d.query_type = N.F16 if queries.dtype == torch.float16 else N.F32
+            d.output = out.data_ptr()
+            d.output_type = N.F16 if out.dtype == torch.float16 else N.F32
+        ws = self.workspace.data_ptr() if hasattr(self, "workspace") else 0
+        aligned = (ws + 255) // 256 * 256
+        d.workspace = aligned
+        d.workspace_bytes = (self.workspace.numel() - (aligned - ws)) if hasattr(self, "workspace") else 0
+        d.status = self.status.data_ptr()
+        return d
+
+    def _seal_desc(self, d_slots, d_ids, d_rows):
+        d = N.SealDesc()
+        d.struct_size, d.abi_version = C.sizeof(N.SealDesc), N.ABI_VERSION
+        d.kv_head_count, d.head_dim, d.page_tokens, d.block_size = self.kv_heads, self.head_dim, self.page_tokens, self.block_size
+        d.coder, d.codebook_id = self.coder, self.codebook_id
+        d.k_tables, d.v_tables = self.k_tables.data_ptr(), self.v_tables.data_ptr()
+        d.tail_k, d.tail_v = self.tail_k.data_ptr(), self.tail_v.data_ptr()
+        self._seal_keepalive = (d_slots, d_ids, d_rows)
+        d.job_slots = d_slots.data_ptr()
+        d.job_pages = d_ids.data_ptr() if d_ids is not None else None
+        d.job_tokens = d_rows.data_ptr() if d_rows is not None else None
+        d.job_count = d_slots.numel()
+        d.arena, d.arena_units = self.arena.data_ptr(), self.arena_units
+        d.arena_cursor_units, d.page_dir, d.status = self.cursor.data_ptr(), self.page_dir.data_ptr(), self.status.data_ptr()
+        return d

@@ -1,0 +1,138 @@
+// cf_device_common.cuh — small device/host helpers shared by the kernels of this library.
+#ifndef CHROMOFOLD_B200_DEVICE_COMMON_CUH
+#define CHROMOFOLD_B200_DEVICE_COMMON_CUH
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "chromofold_b200/sealed_kv.h"
+
+namespace cfb {
+
+constexpr uint32_t kRansL = CF_B200_RANS_L;
+constexpr int kZero = CF_B200_ZERO_POINT;
+
+__host__ __device__ inline uint32_t align_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Split-KV workspace. One chunk = `pages_per_unit` consecutive pages of one sequence; one unit = (chunk, kv head).
+//   [0, 64)                       PlanHeader
+//   [64, 64 + 4*(seq_count+1))    chunk_prefix: number of chunks before each sequence
+//   [partials_offset, ...)        per chunk and local query head: float m, float l, float acc[head_dim]
+struct PlanHeader {
+    uint32_t chunk_count;
+    uint32_t pages_per_unit;
+    uint32_t next_unit;      // work counter for the attention kernel; the plan kernel clears it
+    uint32_t chunk_capacity;
+    uint32_t overflow;
+    uint32_t pad[11];
+};
+
+struct WorkspaceLayout {
+    uint64_t prefix_offset;
+    uint64_t partials_offset;
+    uint64_t partial_stride_floats;  // per (chunk, local query head)
+    uint64_t chunk_capacity;
+};
+
+__host__ __device__ inline WorkspaceLayout workspace_layout(uint32_t seq_count, uint32_t local_q_heads,
+                                                            uint32_t head_dim, uint64_t workspace_bytes) {
+    WorkspaceLayout w;
+    w.prefix_offset = sizeof(PlanHeader);
+    w.partials_offset = (w.prefix_offset + 4ull * (seq_count + 1) + 255ull) / 256ull * 256ull;
+    w.partial_stride_floats = head_dim + 2ull;
+    const uint64_t per_chunk = w.partial_stride_floats * 4ull * local_q_heads;
+    w.chunk_capacity = workspace_bytes > w.partials_offset ? (workspace_bytes - w.partials_offset) / per_chunk : 0;
+    return w;
+}
+
+// First token a query at `query_token` may see (src/cuda/paged_kv_attention.cu:50-52).
+__host__ __device__ inline uint32_t window_begin(uint32_t query_token, uint32_t causal_window) {
+    return causal_window == 0 || query_token + 1u <= causal_window ? 0u : query_token + 1u - causal_window;
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---- scalar block decoders: one thread walks one block ----------------------------------------------
+
+// One rANS symbol: src/cuda/rans.cu:20-23 with the three table reads folded into one packed word
+// (sym | freq << 8 | (slot - cum) << 20).
+template <class Emit>
+__device__ __forceinline__ void rans_decode_block(const uint8_t *payload, uint32_t pos, uint32_t state,
+                                                  const uint32_t *slot_table, int count, Emit emit) {
+    for (int j = 0; j < count; ++j) {
+        const uint32_t e = slot_table[state & (CF_B200_RANS_M - 1u)];
+        state = ((e >> 8) & 0xfffu) * (state >> CF_B200_RANS_PROB_BITS) + (e >> 20);
+        while (state < kRansL) {
+            state = (state << 8) | payload[pos];
+            ++pos;
+        }
+        emit(j, e & 0xffu);
+    }
+}
+
+// One Huffman symbol per step: the next 12 bits MSB-first index the LUT
+// (include/chromofold/detail/block_huffman_device.cuh:12-19), read here from two words at once.
+template <class Emit>
+__device__ __forceinline__ void huffman_decode_block(const uint32_t *words, uint32_t bit, const uint16_t *lut,
+                                                     int count, Emit emit) {
+    for (int j = 0; j < count; ++j) {
+        const uint32_t w = bit >> 5;
+        const uint64_t two = (static_cast<uint64_t>(words[w]) << 32) | words[w + 1];
+        const uint32_t look = static_cast<uint32_t>(two >> (64u - CF_B200_HUFF_MAXLEN - (bit & 31u))) &
+                              (CF_B200_HUFF_LUT_SIZE - 1u);
+        const uint32_t sl = lut[look];
+        emit(j, sl & 0xffu);
+        bit += sl >> 8;
+    }
+}
+
+// Fixed 8-bit symbols, MSB-first in u32 words (src/runtime/kv_gpu_fixture.cpp:110-116).
+template <class Emit>
+__device__ __forceinline__ void fixed8_decode_block(const uint32_t *words, uint32_t first_symbol, int count,
+                                                    Emit emit) {
+    for (int j = 0; j < count; ++j) {
+        const uint32_t i = first_symbol + j;
+        emit(j, (words[i >> 2] >> (24u - 8u * (i & 3u))) & 0xffu);
+    }
+}
+
+// Decode block `b` of one stream part (layout in sealed_page_format.h). `part` must be 16-byte aligned and readable
+// 8 bytes past its end.
+template <class Emit>
+__device__ __forceinline__ void decode_part_block(const uint8_t *part, uint32_t coder, uint32_t nblocks, uint32_t b,
+                                                  uint32_t block_size, uint32_t symbols,
+                                                  const cf_b200_codebook_tables *tables, Emit emit) {
+    const uint32_t base = b * block_size;
+    const int count = static_cast<int>(min(block_size, symbols - base));
+    if (coder == CF_B200_CODER_RANS) {
+        const uint32_t *state0 = reinterpret_cast<const uint32_t *>(part);
+        const uint16_t *off = reinterpret_cast<const uint16_t *>(part + 4u * nblocks);
+        const uint8_t *payload = part + align_up_u32(6u * nblocks, 4u);
+        rans_decode_block(payload, off[b], state0[b], tables->rans_slot, count, emit);
+    } else if (coder == CF_B200_CODER_HUFFMAN) {
+        const uint16_t *off = reinterpret_cast<const uint16_t *>(part);
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(part + align_up_u32(2u * nblocks, 4u));
+        huffman_decode_block(words, off[b], tables->huff_lut, count, emit);
+    } else {
+        fixed8_decode_block(reinterpret_cast<const uint32_t *>(part), base, count, emit);
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace cfb
+
+#endif

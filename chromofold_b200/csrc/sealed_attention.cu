@@ -1,0 +1,521 @@
+// sealed_attention.cu — decode-step attention over sealed pages: planning, the any-geometry kernel, the split-KV
+// combine, the decode probe, and the C entry points.
+//
+// The arithmetic follows the reference's paged attention (src/cuda/paged_kv_attention.cu:41-176): dequantise inside
+// the dot product, one online softmax over every page and the tail, output = weighted / sum. What differs is the
+// execution: sequences are cut into chunks of pages, each (chunk, kv head) unit is processed independently for all
+// query heads of the group at once (a K/V code is decoded once, not once per query head), and the partial
+// (max, sum, weighted) triples are merged with the rule of cf_online_softmax_merge (src/runtime/kv_runtime.cpp:219-243).
+
+#include <math_constants.h>
+
+#include "attention_params.cuh"
+
+namespace cfb {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kPlanThreads = 1024;
+constexpr int kGenericThreads = 128;
+constexpr uint32_t kGenericMaxGroup = 16;
+
+// ---------------------------------------------------------------------------------------------------------------
+// Plan: how many chunks each sequence gets. One block.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint32_t seq, uint32_t *first_page) {
+    const uint32_t slot = slot_of(p, seq);
+    const uint32_t sealed = p.seq_sealed_tokens[slot];
+    const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
+    const uint32_t pages = (sealed + p.page_tokens - 1u) / p.page_tokens;
+    const uint32_t first = min(window_begin(sealed + tail, p.causal_window) / p.page_tokens, pages);
+    if (first_page) *first_page = first;
+    return pages - first;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
+    __shared__ uint32_t scan[kPlanThreads];
+    __shared__ uint32_t s_total;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t per_thread = (p.seq_count + kPlanThreads - 1) / kPlanThreads;
+    const uint32_t begin = min(tid * per_thread, p.seq_count);
+    const uint32_t end = min(begin + per_thread, p.seq_count);
+    PlanHeader *hdr = plan_header(p);
+    uint32_t *prefix = chunk_prefix(p);
+
+    uint32_t pages_per_unit = max(p.min_pages_per_unit, 1u);
+    uint32_t overflow = 0;
+    uint32_t local = 0;  // chunks of this thread's sequences at the current pages_per_unit
+    for (int attempt = 0; attempt < 32; ++attempt) {
+        local = 0;
+        for (uint32_t s = begin; s < end; ++s) local += (visible_pages(p, s, nullptr) + pages_per_unit - 1u) / pages_per_unit;
+        __syncthreads();
+        scan[tid] = local;
+        __syncthreads();
+        for (uint32_t off = 1; off < kPlanThreads; off <<= 1) {  // inclusive scan
+            const uint32_t add = tid >= off ? scan[tid - off] : 0u;
+            __syncthreads();
+            scan[tid] += add;
+            __syncthreads();
+        }
+        if (tid == kPlanThreads - 1) s_total = scan[tid];
+        __syncthreads();
+        if (s_total <= p.layout.chunk_capacity) break;
+        if (attempt == 31 || pages_per_unit >= (1u << 30)) { overflow = 1; break; }
+        pages_per_unit <<= 1;
+    }
+    uint32_t running = scan[tid] - local;
+    for (uint32_t s = begin; s < end; ++s) {
+        prefix[s] = overflow ? 0u : running;
+        running += (visible_pages(p, s, nullptr) + pages_per_unit - 1u) / pages_per_unit;
+    }
+    if (tid == 0) {
+        prefix[p.seq_count] = overflow ? 0u : s_total;
+        hdr->chunk_count = overflow ? 0u : s_total;
+        hdr->pages_per_unit = pages_per_unit;
+        hdr->next_unit = 0;
+        hdr->chunk_capacity = static_cast<uint32_t>(min(p.layout.chunk_capacity, static_cast<uint64_t>(0xffffffffu)));
+        hdr->overflow = overflow;
+        if (overflow) raise_status(p, CF_B200_DEVSTAT_WORKSPACE);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Query load helper.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_query(const AttentionParams &p, uint32_t seq, uint32_t q_head, uint32_t d) {
+    const uint64_t i = (static_cast<uint64_t>(seq) * p.query_head_count + q_head) * p.head_dim + d;
+    return p.query_type == CF_B200_F16 ? __half2float(reinterpret_cast<const __half *>(p.queries)[i])
+                                       : reinterpret_cast<const float *>(p.queries)[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Any-geometry attention kernel: one CTA per (chunk, kv head) unit. Each page record is copied to shared memory,
+// both streams are decoded to symbols there (one thread per block), then scores and the online-softmax update
+// are computed from shared memory. Built for coverage of every legal geometry, not for speed.
+// ---------------------------------------------------------------------------------------------------------------
+struct GenericSmem {
+    uint32_t record_bytes, sym_bytes;
+    uint32_t off_record, off_ksym, off_vsym, off_q, off_acc, off_scores, off_ml, total;
+};
+
+__host__ __device__ inline GenericSmem generic_smem(uint32_t symbols, uint32_t group, uint32_t head_dim,
+                                                    uint32_t page_tokens) {
+    GenericSmem s;
+    s.record_bytes = 16u + 2u * align_up_u32(symbols, 16u) + 32u;
+    s.sym_bytes = align_up_u32(symbols, 16u);
+    s.off_record = 0;
+    s.off_ksym = s.off_record + s.record_bytes;
+    s.off_vsym = s.off_ksym + s.sym_bytes;
+    s.off_q = s.off_vsym + s.sym_bytes;
+    s.off_acc = s.off_q + group * head_dim * 4u;
+    s.off_scores = s.off_acc + group * head_dim * 4u;
+    s.off_ml = s.off_scores + group * page_tokens * 4u;
+    s.total = s.off_ml + group * 8u + 16u;
+    return s;
+}
+
+__global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(AttentionParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ uint32_t s_unit;
+    const GenericSmem lay = generic_smem(p.symbols, p.group, p.head_dim, p.page_tokens);
+    uint8_t *record = smem + lay.off_record;
+    uint8_t *ksym = smem + lay.off_ksym;
+    uint8_t *vsym = smem + lay.off_vsym;
+    float *q = reinterpret_cast<float *>(smem + lay.off_q);
+    float *acc = reinterpret_cast<float *>(smem + lay.off_acc);
+    float *scores = reinterpret_cast<float *>(smem + lay.off_scores);
+    float *ml = reinterpret_cast<float *>(smem + lay.off_ml);  // [group][2]: running max, running sum
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t D = p.head_dim, T = p.page_tokens, G = p.group;
+    PlanHeader *hdr = plan_header(p);
+    const uint32_t *prefix = chunk_prefix(p);
+    const uint32_t unit_count = hdr->chunk_count * p.kv_head_span;
+    const uint32_t pages_per_unit = hdr->pages_per_unit;
+    const uint32_t max_part_units = align_up_u32(p.symbols, 16u) / 16u;
+
+    for (;;) {
+        __syncthreads();
+        if (tid == 0) s_unit = atomicAdd(&hdr->next_unit, 1u);
+        __syncthreads();
+        const uint32_t unit = s_unit;
+        if (unit >= unit_count) break;
+        const uint32_t chunk = unit / p.kv_head_span;
+        const uint32_t head_local = unit % p.kv_head_span;
+        const uint32_t kv_head = p.kv_head_begin + head_local;
+        const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
+        const uint32_t slot = slot_of(p, seq);
+        const uint32_t sealed = p.seq_sealed_tokens[slot];
+        const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
+        const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
+        uint32_t first_page;
+        const uint32_t vis = visible_pages(p, seq, &first_page);
+        const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
+        const uint32_t page_end = min(page_begin + pages_per_unit, first_page + vis);
+
+        for (uint32_t i = tid; i < G * D; i += kGenericThreads) {
+            q[i] = load_query(p, seq, kv_head * G + i / D, i % D) * (p.softmax_scale * kLog2e);
+            acc[i] = 0.0f;
+        }
+        if (tid < G) {
+            ml[2 * tid] = -CUDART_INF_F;
+            ml[2 * tid + 1] = 0.0f;
+        }
+
+        for (uint32_t page = page_begin; page < page_end; ++page) {
+            __syncthreads();
+            const uint32_t page_id = p.page_table[static_cast<uint64_t>(slot) * p.page_table_stride + page];
+            const uint64_t entry = p.page_dir[static_cast<uint64_t>(page_id) * p.kv_head_count + kv_head];
+            const uint32_t units = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
+            if (units == 0 || units > 1u + 2u * max_part_units) {
+                if (tid == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                continue;
+            }
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry));
+            for (uint32_t i = tid; i < units; i += kGenericThreads) reinterpret_cast<uint4 *>(record)[i] = src[i];
+            __syncthreads();
+            const cf_b200_record_header h = *reinterpret_cast<const cf_b200_record_header *>(record);
+            if (h.version != CF_B200_FORMAT_VERSION || h.codebook_id != p.codebook_id ||
+                1u + h.k_part_units + h.v_part_units != units || h.k_part_units > max_part_units ||
+                h.v_part_units > max_part_units || h.token_count == 0 || h.token_count > T || h.k_coder > 2 ||
+                h.v_coder > 2) {
+                if (tid == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                continue;
+            }
+            const uint8_t *k_part = record + 16;
+            const uint8_t *v_part = record + 16 + 16u * h.k_part_units;
+            for (uint32_t b = tid; b < 2u * p.nblocks; b += kGenericThreads) {
+                if (b < p.nblocks) {
+                    uint8_t *dst = ksym + b * p.block_size;
+                    decode_part_block(k_part, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
+                                      [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
+                } else {
+                    const uint32_t vb = b - p.nblocks;
+                    uint8_t *dst = vsym + vb * p.block_size;
+                    decode_part_block(v_part, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
+                                      [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
+                }
+            }
+            __syncthreads();
+            const float k_scale = __half2float(__ushort_as_half(h.k_scale_f16));
+            const float v_scale = __half2float(__ushort_as_half(h.v_scale_f16));
+            // scores[g][t], one warp per (g, t)
+            for (uint32_t pair = warp; pair < G * T; pair += kGenericThreads / 32) {
+                const uint32_t g = pair / T, t = pair % T;
+                const uint32_t token = page * T + t;
+                float s = -CUDART_INF_F;
+                if (t < h.token_count && token >= first_token && token < sealed) {
+                    float dot = 0.0f;
+                    for (uint32_t d = lane; d < D; d += 32)
+                        dot += q[g * D + d] * static_cast<float>(static_cast<int>(ksym[t * D + d]) - kZero);
+                    s = warp_sum(dot) * k_scale;
+                }
+                if (lane == 0) scores[g * T + t] = s;
+            }
+            __syncthreads();
+            // online softmax update: thread d owns channel d of every group member
+            float new_m[kGenericMaxGroup], new_l[kGenericMaxGroup];
+            for (uint32_t g = 0; g < G; ++g) {
+                const float m_old = ml[2 * g], l_old = ml[2 * g + 1];
+                float pm = -CUDART_INF_F;
+                for (uint32_t t = 0; t < T; ++t) pm = fmaxf(pm, scores[g * T + t]);
+                const float m_new = fmaxf(m_old, pm);
+                new_m[g] = m_new;
+                new_l[g] = l_old;
+                if (m_new == -CUDART_INF_F) continue;
+                const float alpha = m_old == -CUDART_INF_F ? 0.0f : exp2f(m_old - m_new);
+                float lsum = 0.0f, a = 0.0f;
+                for (uint32_t t = 0; t < T; ++t) {
+                    const float s = scores[g * T + t];
+                    const float w = s == -CUDART_INF_F ? 0.0f : exp2f(s - m_new);
+                    lsum += w;
+                    if (tid < D) a += w * static_cast<float>(static_cast<int>(vsym[tid * T + t]) - kZero);
+                }
+                new_l[g] = l_old * alpha + lsum;
+                if (tid < D) acc[g * D + tid] = acc[g * D + tid] * alpha + a * v_scale;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                for (uint32_t g = 0; g < G; ++g) {
+                    ml[2 * g] = new_m[g];
+                    ml[2 * g + 1] = new_l[g];
+                }
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < G * D; i += kGenericThreads) {
+            const uint32_t g = i / D, d = i % D;
+            float *dst = partial_ptr(p, chunk, head_local * G + g);
+            dst[2 + d] = acc[i];
+            if (d == 0) {
+                dst[0] = ml[2 * g];
+                dst[1] = ml[2 * g + 1];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Combine: merge the chunk partials of one (sequence, query head) with the unsealed tail and write the output.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kCombineThreads = 128;
+
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParams p) {
+    extern __shared__ float tail_scores[];  // [page_tokens]
+    __shared__ float s_red[kCombineThreads / 32];
+    const uint32_t seq = blockIdx.x;
+    const uint32_t local_q = blockIdx.y;
+    const uint32_t G = p.group, D = p.head_dim, T = p.page_tokens;
+    const uint32_t kv_head = p.kv_head_begin + local_q / G;
+    const uint32_t q_head = kv_head * G + local_q % G;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t slot = slot_of(p, seq);
+    const uint32_t sealed = p.seq_sealed_tokens[slot];
+    const uint32_t tail = p.tail_tokens ? min(p.tail_tokens[slot], T) : 0u;
+    const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
+    const uint32_t *prefix = chunk_prefix(p);
+    const uint32_t c0 = prefix[seq], c1 = prefix[seq + 1];
+
+    // tail scores (binary16 rows, one warp per token)
+    for (uint32_t t = warp; t < tail; t += kCombineThreads / 32) {
+        const __half *row = p.tail_k + ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D;
+        float dot = 0.0f;
+        for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, seq, q_head, d) * __half2float(row[d]);
+        dot = warp_sum(dot);
+        if (lane == 0) tail_scores[t] = (sealed + t >= first_token) ? dot * p.softmax_scale * kLog2e : -CUDART_INF_F;
+    }
+    __syncthreads();
+
+    float m = -CUDART_INF_F;
+    for (uint32_t c = c0 + tid; c < c1; c += kCombineThreads) m = fmaxf(m, partial_ptr(p, c, local_q)[0]);
+    for (uint32_t t = tid; t < tail; t += kCombineThreads) m = fmaxf(m, tail_scores[t]);
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = s_red[0];
+    for (int w = 1; w < kCombineThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+
+    float l = 0.0f, a = 0.0f;
+    if (m != -CUDART_INF_F) {
+        for (uint32_t c = c0; c < c1; ++c) {
+            const float *part = partial_ptr(p, c, local_q);
+            const float pm = part[0];
+            if (pm == -CUDART_INF_F) continue;
+            const float w = exp2f(pm - m);
+            l += part[1] * w;
+            if (tid < D) a += part[2 + tid] * w;
+        }
+        for (uint32_t t = 0; t < tail; ++t) {
+            const float s = tail_scores[t];
+            if (s == -CUDART_INF_F) continue;
+            const float w = exp2f(s - m);
+            l += w;
+            if (tid < D)
+                a += w * __half2float(p.tail_v[((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D + tid]);
+        }
+    }
+    if (tid < D) {
+        const float out = l > 0.0f ? a / l : 0.0f;  // no visible token: zeros (paged_kv_attention.cu:170-173)
+        const uint64_t i = (static_cast<uint64_t>(seq) * p.query_head_count + q_head) * D + tid;
+        if (p.output_type == CF_B200_F16) reinterpret_cast<__half *>(p.output)[i] = __float2half_rn(out);
+        else reinterpret_cast<float *>(p.output)[i] = out;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Decode probe: write the symbols of whole records to global memory.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void decode_pages_kernel(AttentionParams p, const uint32_t *page_ids, uint8_t *k_out, uint8_t *v_out) {
+    const uint32_t page = blockIdx.x, kv_head = blockIdx.y;
+    const uint64_t entry = p.page_dir[static_cast<uint64_t>(page_ids[page]) * p.kv_head_count + kv_head];
+    if (CF_B200_DIR_LENGTH_UNITS(entry) == 0) {
+        if (threadIdx.x == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+        return;
+    }
+    const uint8_t *record = p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry);
+    const cf_b200_record_header h = *reinterpret_cast<const cf_b200_record_header *>(record);
+    if (h.version != CF_B200_FORMAT_VERSION || h.k_coder > 2 || h.v_coder > 2) {
+        if (threadIdx.x == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+        return;
+    }
+    const uint8_t *k_part = record + 16;
+    const uint8_t *v_part = record + 16 + 16u * h.k_part_units;
+    const uint64_t base = (static_cast<uint64_t>(page) * p.kv_head_count + kv_head) * p.symbols;
+    for (uint32_t b = threadIdx.x; b < 2u * p.nblocks; b += blockDim.x) {
+        if (b < p.nblocks) {
+            uint8_t *dst = k_out + base + b * p.block_size;
+            decode_part_block(k_part, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
+                              [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
+        } else {
+            const uint32_t vb = b - p.nblocks;
+            uint8_t *dst = v_out + base + vb * p.block_size;
+            decode_part_block(v_part, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
+                              [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
+        }
+    }
+}
+
+bool finite_float(float v) { return v == v && v - v == 0.0f; }
+
+bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
+    p->kv_head_count = d->kv_head_count;
+    p->query_head_count = d->query_head_count;
+    p->head_dim = d->head_dim;
+    p->page_tokens = d->page_tokens;
+    p->block_size = d->block_size;
+    p->kv_head_begin = d->kv_head_begin;
+    p->kv_head_span = d->kv_head_span ? d->kv_head_span : d->kv_head_count - d->kv_head_begin;
+    p->group = d->query_head_count / d->kv_head_count;
+    p->symbols = d->head_dim * d->page_tokens;
+    p->nblocks = (p->symbols + d->block_size - 1) / d->block_size;
+    p->codebook_id = d->codebook_id;
+    p->arena = d->arena;
+    p->page_dir = d->page_dir;
+    p->page_table = d->page_table;
+    p->seq_sealed_tokens = d->seq_sealed_tokens;
+    p->seq_slots = d->seq_slots;
+    p->page_table_stride = d->page_table_stride;
+    p->seq_count = d->seq_count;
+    p->k_tables = d->k_tables;
+    p->v_tables = d->v_tables;
+    p->tail_k = static_cast<const __half *>(d->tail_k);
+    p->tail_v = static_cast<const __half *>(d->tail_v);
+    p->tail_tokens = d->tail_tokens;
+    p->queries = d->queries;
+    p->output = d->output;
+    p->query_type = d->query_type;
+    p->output_type = d->output_type;
+    p->softmax_scale = d->softmax_scale;
+    p->causal_window = d->causal_window;
+    p->workspace = static_cast<uint8_t *>(d->workspace);
+    p->layout = workspace_layout(d->seq_count, p->kv_head_span * p->group, d->head_dim, d->workspace_bytes);
+    p->min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    p->status = d->status;
+    p->pool_k = nullptr;
+    p->pool_v = nullptr;
+    return true;
+}
+
+}  // namespace
+
+cudaError_t launch_plan(const AttentionParams &p, cudaStream_t stream) {
+    plan_kernel<<<1, kPlanThreads, 0, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_combine(const AttentionParams &p, cudaStream_t stream) {
+    const dim3 grid(p.seq_count, p.kv_head_span * p.group);
+    combine_kernel<<<grid, kCombineThreads, p.page_tokens * sizeof(float), stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_generic_attention(const AttentionParams &p, cudaStream_t stream) {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return e;
+    }
+    const GenericSmem lay = generic_smem(p.symbols, p.group, p.head_dim, p.page_tokens);
+    cudaError_t e = cudaFuncSetAttribute(generic_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(lay.total));
+    if (e != cudaSuccess) return e;
+    generic_attention_kernel<<<sm_count * 4, kGenericThreads, lay.total, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace cfb
+
+using cfb::AttentionParams;
+
+extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_attention_desc *d) {
+    if (d == nullptr || d->struct_size != sizeof(cf_b200_sealed_attention_desc) || d->abi_version != CF_B200_ABI_VERSION)
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->kv_head_count == 0 || d->query_head_count == 0 || d->head_dim == 0 || d->page_tokens == 0 ||
+        d->block_size == 0 || d->query_head_count % d->kv_head_count != 0 || !cfb::finite_float(d->softmax_scale))
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->kv_head_begin >= d->kv_head_count || d->kv_head_span > d->kv_head_count - d->kv_head_begin)
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->queries == nullptr || d->output == nullptr || d->workspace == nullptr || d->seq_sealed_tokens == nullptr ||
+        d->k_tables == nullptr || d->v_tables == nullptr)
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->seq_count == 0) return CF_ERR_INVALID_ARGUMENT;
+    if (d->page_table_stride != 0 && (d->page_table == nullptr || d->page_dir == nullptr || d->arena == nullptr))
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->tail_tokens != nullptr && (d->tail_k == nullptr || d->tail_v == nullptr)) return CF_ERR_INVALID_ARGUMENT;
+    if ((d->query_type != CF_B200_F16 && d->query_type != CF_B200_F32) ||
+        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_LANES)
+        return CF_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(d->arena) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->workspace) & 255u) != 0)
+        return CF_ERR_INVALID_ARGUMENT;
+    // format limits
+    if (d->head_dim > CF_KV_MAX_HEAD_DIM || d->head_dim * d->page_tokens > CF_B200_MAX_STREAM_SYMBOLS ||
+        d->block_size < 16 || d->block_size > 1024 || d->query_head_count / d->kv_head_count > cfb::kGenericMaxGroup)
+        return CF_ERR_UNSUPPORTED;
+    const uint32_t span = d->kv_head_span ? d->kv_head_span : d->kv_head_count - d->kv_head_begin;
+    const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, span * (d->query_head_count / d->kv_head_count),
+                                                         d->head_dim, d->workspace_bytes);
+    if (w.chunk_capacity < d->seq_count) return CF_ERR_INVALID_ARGUMENT;  // at least one chunk per sequence
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_sealed_attention_desc *d,
+                                                              uint64_t total_pages, uint64_t *out_bytes) {
+    if (d == nullptr || out_bytes == nullptr || d->kv_head_count == 0 || d->query_head_count == 0 ||
+        d->query_head_count % d->kv_head_count != 0 || d->head_dim == 0)
+        return CF_ERR_INVALID_ARGUMENT;
+    const uint32_t span = d->kv_head_span ? d->kv_head_span : d->kv_head_count - d->kv_head_begin;
+    const uint32_t local_q = span * (d->query_head_count / d->kv_head_count);
+    const uint32_t ppu = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    const uint64_t chunks = total_pages / ppu + d->seq_count + 1;  // each sequence may round up once
+    const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, local_q, d->head_dim, 0);
+    *out_bytes = w.partials_offset + chunks * w.partial_stride_floats * 4ull * local_q;
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *d, void *stream) {
+    const cf_status valid = cf_b200_sealed_attention_validate(d);
+    if (valid != CF_OK) return valid;
+    AttentionParams p;
+    cfb::fill_params(d, &p);
+    const bool lanes_ok = cfb::lanes_kernel_supports(p);
+    if (d->kernel == CF_B200_KERNEL_LANES && !lanes_ok) return CF_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
+    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
+    const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
+    if (e != cudaSuccess) return CF_ERR_CUDA;
+    if (cfb::launch_combine(p, s) != cudaSuccess) return CF_ERR_CUDA;
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_decode_pages_async(const cf_b200_sealed_attention_desc *d, const uint32_t *page_ids,
+                                                uint32_t page_count, uint8_t *k_symbols, uint8_t *v_symbols,
+                                                void *stream) {
+    if (d == nullptr || d->struct_size != sizeof(cf_b200_sealed_attention_desc) ||
+        d->abi_version != CF_B200_ABI_VERSION || page_ids == nullptr || k_symbols == nullptr || v_symbols == nullptr ||
+        d->arena == nullptr || d->page_dir == nullptr || d->k_tables == nullptr || d->v_tables == nullptr ||
+        d->kv_head_count == 0 || d->head_dim == 0 || d->page_tokens == 0 || d->block_size == 0)
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->head_dim * d->page_tokens > CF_B200_MAX_STREAM_SYMBOLS || d->block_size < 16 || d->block_size > 1024)
+        return CF_ERR_UNSUPPORTED;
+    if (page_count == 0) return CF_OK;
+    AttentionParams p{};
+    p.kv_head_count = d->kv_head_count;
+    p.head_dim = d->head_dim;
+    p.page_tokens = d->page_tokens;
+    p.block_size = d->block_size;
+    p.symbols = d->head_dim * d->page_tokens;
+    p.nblocks = (p.symbols + d->block_size - 1) / d->block_size;
+    p.arena = d->arena;
+    p.page_dir = d->page_dir;
+    p.k_tables = d->k_tables;
+    p.v_tables = d->v_tables;
+    p.status = d->status;
+    cfb::decode_pages_kernel<<<dim3(page_count, d->kv_head_count), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        p, page_ids, k_symbols, v_symbols);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}

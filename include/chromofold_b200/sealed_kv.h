@@ -1,0 +1,221 @@
+/* sealed_kv.h — C ABI of the B200 sealed-KV decode-attention path.
+ *
+ * These entry points sit beside the reference's symbols (compat_kv.h). They exist because the reference
+ * descriptors cannot express the target workloads: its launch takes at most 4096 page descriptors of 104
+ * bytes each by value (include/chromofold/kv_cuda.h:13,21-41), has fp32-only queries (:68-69), keeps LUTs
+ * and scale vectors per page, and has no rANS page at all (src/cuda/rans.cu is a flat stream decoder).
+ *
+ * Conventions are the reference's (include/chromofold/chromofold.h:25-30,48-50; specs/00-constitution.md):
+ *   - every function returns cf_status; CF_OK means "launch accepted", not "finished";
+ *   - `stream` is a cudaStream_t passed as void*, NULL is the default stream;
+ *   - a required pointer that is NULL gives CF_ERR_INVALID_ARGUMENT before any CUDA call;
+ *   - versioned structs carry struct_size and abi_version and are rejected when they do not match;
+ *   - the *_async query-path calls allocate nothing, never synchronise and copy nothing between host and
+ *     device; the caller owns stream ordering;
+ *   - there is no CPU or dense fallback: when no CUDA device is usable the calls fail with CF_ERR_CUDA.
+ */
+#ifndef CHROMOFOLD_B200_SEALED_KV_H
+#define CHROMOFOLD_B200_SEALED_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "chromofold_b200/cf_status.h"
+#include "chromofold_b200/sealed_page_format.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CF_B200_ABI_VERSION 1u
+
+/* Scalar types of query / output / appended K,V tensors; values of the reference's cf_device_scalar_type
+ * (include/chromofold/device_kv_dataplane.h:11-15). */
+#define CF_B200_F16 1u
+#define CF_B200_BF16 2u
+#define CF_B200_F32 3u
+
+/* Page directory entry: where the record of (page_id, kv_head) lies in the arena.
+ *   bits  0..39 : byte offset / 16
+ *   bits 40..55 : record length / 16
+ *   bits 56..63 : 0 (reserved) */
+#define CF_B200_DIR_ENTRY(offset_units, length_units) \
+    (((uint64_t)(offset_units) & 0xFFFFFFFFFFull) | ((uint64_t)(length_units) << 40))
+#define CF_B200_DIR_OFFSET_UNITS(e) ((e) & 0xFFFFFFFFFFull)
+#define CF_B200_DIR_LENGTH_UNITS(e) (((e) >> 40) & 0xFFFFull)
+
+/* --------------------------------------------------------------------------------------------------
+ * Raw launch: decode-step attention of a batch of sequences over sealed pages. The caller owns all
+ * memory. Replaces, for sealed pages, cf_kv_paged_attention_async (include/chromofold/kv_cuda.h:86,
+ * src/cuda/paged_kv_attention.cu:301-327) and the per-item launches of cf_ms_cuda_execute_batch_async
+ * (src/cuda/multisequence_cuda_resolver.cu:376-419) and cf_attention_execute_async
+ * (src/cuda/production_attention.cu:170-211).
+ *
+ * Semantics (src/cuda/paged_kv_attention.cu:41-176, src/runtime/kv_reference.cpp:164-243):
+ *   one query token per sequence at position sealed_tokens + tail_tokens; visible tokens are
+ *   window_begin <= t <= query position with window_begin as in paged_kv_attention.cu:50-52;
+ *   score = (sum_d q[d] * (sym-128) * k_scale) * softmax_scale; one online softmax over all pages and the
+ *   tail; output = weighted / sum; query head h reads kv head h / (Hq / Hkv); a sequence with no visible
+ *   token gets zeros (paged_kv_attention.cu:170-173).
+ * All pointers are DEVICE pointers. */
+typedef struct cf_b200_sealed_attention_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+
+    uint32_t kv_head_count;     /* kv heads present in page_dir and in the tails */
+    uint32_t query_head_count;  /* Hq of the whole layer; Hq % kv_head_count == 0 */
+    uint32_t head_dim;
+    uint32_t page_tokens;
+    uint32_t block_size;
+    uint32_t kv_head_begin;     /* this launch serves kv heads [kv_head_begin, kv_head_begin+kv_head_span) */
+    uint32_t kv_head_span;      /* and the query heads that map to them; 0 means all */
+    uint32_t codebook_id;
+
+    const uint8_t *arena;
+    const uint64_t *page_dir;            /* [page_id * kv_head_count + kv_head] */
+    const uint32_t *page_table;          /* [slot][page_table_stride] page ids */
+    const uint32_t *seq_sealed_tokens;   /* [slot] */
+    const uint32_t *seq_slots;           /* [seq_count] batch index -> slot; NULL = identity */
+    uint32_t page_table_stride;
+    uint32_t seq_count;
+
+    const cf_b200_codebook_tables *k_tables;
+    const cf_b200_codebook_tables *v_tables;
+
+    const void *tail_k;                  /* binary16 [slot][kv_head_count][page_tokens][head_dim], may be NULL */
+    const void *tail_v;
+    const uint32_t *tail_tokens;         /* [slot], NULL = no tails */
+
+    const void *queries;                 /* [seq_count][query_head_count][head_dim] */
+    void *output;                        /* same shape */
+    uint32_t query_type;                 /* CF_B200_F16 or CF_B200_F32 */
+    uint32_t output_type;                /* CF_B200_F16 or CF_B200_F32 */
+    float softmax_scale;
+    uint32_t causal_window;              /* 0 = all history */
+
+    void *workspace;                     /* split-KV partials; see cf_b200_sealed_attention_workspace_bytes */
+    uint64_t workspace_bytes;
+    uint32_t min_pages_per_unit;         /* 0 = default (16) */
+    uint32_t kernel;                     /* CF_B200_KERNEL_* */
+    uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
+    uint32_t reserved;
+} cf_b200_sealed_attention_desc;
+
+#define CF_B200_KERNEL_AUTO 0u     /* lane-per-block tensor-core kernel when the geometry allows, else generic */
+#define CF_B200_KERNEL_GENERIC 1u  /* any geometry within the format limits */
+#define CF_B200_KERNEL_LANES 2u    /* head_dim 128, page_tokens 16, block_size 64, group <= 8; else UNSUPPORTED */
+
+#define CF_B200_DEVSTAT_BAD_RECORD 0x1u      /* version / codebook id / size mismatch in a record header */
+#define CF_B200_DEVSTAT_WAIT_EXPIRED 0x2u    /* a bounded wait on a bulk copy ran out */
+#define CF_B200_DEVSTAT_WORKSPACE 0x4u       /* workspace too small for the planned units */
+#define CF_B200_DEVSTAT_NONFINITE 0x8u       /* the sealer met NaN or Inf; the page was not published */
+#define CF_B200_DEVSTAT_ARENA_FULL 0x10u     /* the sealer found no room in the arena */
+
+/* Host-side structural validation; dereferences nothing on the device
+ * (cf_kv_validate_paged_attention_desc, src/cuda/paged_kv_attention.cu:280-299). */
+cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_attention_desc *desc);
+
+/* Workspace needed so that a batch with at most total_pages sealed pages (summed over sequences) never
+ * has to grow its units beyond min_pages_per_unit. A smaller workspace is legal: units grow to fit. */
+cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_sealed_attention_desc *desc,
+                                                   uint64_t total_pages, uint64_t *out_bytes);
+
+cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *desc, void *stream);
+
+/* --------------------------------------------------------------------------------------------------
+ * Codebooks. Built on the host from symbol histograms (set-up work, not query path).
+ * Normalisation rule for rANS (M = 4096, every symbol codable):
+ *   f_i = 1 + floor(h_i * 3840 / N), the left-over slots go to the largest remainders (ties: lower symbol).
+ * Huffman: weights 2*h_i + 1, lengths limited to 12, canonical codes in (length, symbol) order.
+ * The reference has no codebook builder in-tree (tools/export_rans.py:27-29 imports it from elsewhere). */
+cf_status cf_b200_codebook_build(const uint64_t histogram[256], cf_b200_codebook_tables *out_tables);
+
+/* --------------------------------------------------------------------------------------------------
+ * Raw launch: seal full active pages on the GPU. Replaces cf_device_seal_full_page_async
+ * (src/cuda/device_kv_seal_attention.cu:244-334: finite scan, quantise, pack, publish — six launches, a
+ * host synchronisation and nine allocations per page) with one launch and no host round trip.
+ *
+ * For every job j: reads the binary16 rows of slot job_slots[j] from tail_k / tail_v
+ * ([slot][kv_head_count][page_tokens][head_dim], first job_tokens[j] rows valid), quantises each
+ * (kv_head, K|V) stream with its own absmax/127 binary16 scale (round-half-even, clamp [-128,127],
+ * src/runtime/kv_gpu_fixture.cpp:12-16), codes it with `coder` (a stream that would not shrink is stored
+ * fixed-width), takes room in the arena with one atomic add on *arena_cursor_units, writes the record and
+ * then the directory entry of (job_pages[j], kv_head). A page with a non-finite value is not published: its
+ * directory entries stay 0 and CF_B200_DEVSTAT_NONFINITE is set (device_kv_seal_attention.cu:255-267). */
+typedef struct cf_b200_seal_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t kv_head_count;
+    uint32_t head_dim;
+    uint32_t page_tokens;
+    uint32_t block_size;
+    uint32_t coder;               /* CF_B200_CODER_* */
+    uint32_t codebook_id;
+    const cf_b200_codebook_tables *k_tables;
+    const cf_b200_codebook_tables *v_tables;
+    const void *tail_k;
+    const void *tail_v;
+    const uint32_t *job_slots;    /* [job_count] */
+    const uint32_t *job_pages;    /* [job_count] page ids to publish */
+    const uint32_t *job_tokens;   /* [job_count] valid rows, NULL = page_tokens */
+    uint32_t job_count;
+    uint32_t reserved;
+    uint8_t *arena;
+    uint64_t arena_units;                     /* capacity in 16-byte units */
+    unsigned long long *arena_cursor_units;   /* device counter, next free unit */
+    uint64_t *page_dir;
+    uint32_t *status;
+} cf_b200_seal_desc;
+
+cf_status cf_b200_seal_validate(const cf_b200_seal_desc *desc);
+cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *desc, void *stream);
+
+/* Symbol histograms of quantised K and V streams of the same tails (for codebook calibration).
+ * hist_k / hist_v: device uint64[256], accumulated into (not cleared). */
+cf_status cf_b200_histogram_async(const cf_b200_seal_desc *desc, unsigned long long *hist_k,
+                                  unsigned long long *hist_v, void *stream);
+
+/* Decode records back to symbols on the GPU (no attention): k_symbols / v_symbols are device uint8
+ * [job][kv_head_count][page_tokens*head_dim] in stream order. This is the bit-exactness probe: the same
+ * decode routines the attention kernels use, with the codes written out instead of consumed. */
+cf_status cf_b200_decode_pages_async(const cf_b200_sealed_attention_desc *desc, const uint32_t *page_ids,
+                                     uint32_t page_count, uint8_t *k_symbols, uint8_t *v_symbols, void *stream);
+
+/* --------------------------------------------------------------------------------------------------
+ * Comparison kernel: the same attention over UNCOMPRESSED binary16 pages, same page table and split-KV
+ * skeleton, only the read differs (the reference's fairness rule for its dense comparison,
+ * tests/latency_bench.cu). pool_k / pool_v: binary16 [page_id][kv_head_count][page_tokens][head_dim]. */
+typedef struct cf_b200_dense_attention_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t kv_head_count;
+    uint32_t query_head_count;
+    uint32_t head_dim;
+    uint32_t page_tokens;
+    const void *pool_k;
+    const void *pool_v;
+    const uint32_t *page_table;
+    const uint32_t *seq_sealed_tokens;
+    const uint32_t *seq_slots;
+    uint32_t page_table_stride;
+    uint32_t seq_count;
+    const void *queries;     /* binary16 */
+    void *output;            /* float */
+    float softmax_scale;
+    uint32_t causal_window;
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t min_pages_per_unit;
+    uint32_t reserved;
+} cf_b200_dense_attention_desc;
+
+cf_status cf_b200_dense_attention_async(const cf_b200_dense_attention_desc *desc, void *stream);
+
+/* Build identification; also what a loader calls to check that the library carries device code. */
+const char *cf_b200_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

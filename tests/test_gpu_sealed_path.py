@@ -1,0 +1,168 @@
+"""GPU parity tests of the sealed-KV path, through the C ABI, against the CPU oracle."""
+import numpy as np
+import pytest
+
+from helpers import HostCache, attention_close, hist_of, laplace_codes
+
+pytestmark = pytest.mark.gpu
+
+CODERS = {"fixed8": 0, "huffman": 1, "rans": 2}
+
+
+def _layer(native, **kw):
+    from chromofold_b200.cache import SealedKvLayer
+    args = dict(kv_heads=2, query_heads=4, head_dim=128, page_tokens=16, block_size=64, coder=2, max_sequences=4,
+                max_pages_per_sequence=16, max_pages=256, arena_bytes=2 << 20)
+    args.update(kw)
+    return SealedKvLayer(**args)
+
+
+def _random_kv(rng, hkv, tokens, d, b=12.0, scale=0.01):
+    k = (laplace_codes(rng, (hkv, tokens, d), b).astype(np.float32) * scale).astype(np.float16).astype(np.float32)
+    v = (laplace_codes(rng, (hkv, tokens, d), b).astype(np.float32) * scale).astype(np.float16).astype(np.float32)
+    return k, v
+
+
+def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails, b=12.0):
+    """A GPU layer and a CPU HostCache holding the same sealed pages (sealed by the ORACLE and imported)."""
+    import torch
+    n = len(contexts)
+    stride = max(1, max((c + t - 1) // t for c in contexts))
+    calib = laplace_codes(rng, 1 << 16, b)
+    hist = hist_of(calib.astype(np.int16) + 128)
+    kcb = oracle.codebook_from_hist(hist)
+    vcb = oracle.codebook_from_hist(hist[::-1].copy())
+    layer = _layer(native, kv_heads=hkv, query_heads=hq, head_dim=d, page_tokens=t, block_size=block, coder=coder,
+                   max_sequences=n, max_pages_per_sequence=stride, max_pages=n * stride + 2,
+                   arena_bytes=max(1 << 16, n * stride * hkv * (2 * d * t + 64)))
+    layer.set_codebooks(hist, hist[::-1].copy())
+    host = HostCache(hkv, d, t, block, coder, kcb, vcb)
+    tail_k = np.zeros((n, hkv, t, d), np.float16)
+    tail_v = np.zeros((n, hkv, t, d), np.float16)
+    for s, ctx in enumerate(contexts):
+        done = 0
+        while done < ctx:
+            tokens = min(t, ctx - done)
+            k, v = _random_kv(rng, hkv, tokens, d, b)
+            host.seal_page(s, k, v)
+            done += tokens
+        if s in host.records:
+            layer.import_records(s, host.records[s], host.tokens[s])
+        if tails[s]:
+            k, v = _random_kv(rng, hkv, tails[s], d, b)
+            tail_k[s, :, :tails[s]] = k
+            tail_v[s, :, :tails[s]] = v
+            layer.fill_tails([s], torch.from_numpy(tail_k[s:s + 1]).cuda(), torch.from_numpy(tail_v[s:s + 1]).cuda(), tails[s])
+    return layer, host, kcb, vcb, tail_k, tail_v, stride
+
+
+def _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q16, hq, stride, window=0):
+    arena, offsets, table, sealed = host.flat(list(range(len(contexts))), stride)
+    return oracle.sealed_decode_attention(arena, offsets, table, sealed, q16, hq, host.hkv, host.d, host.t, host.block,
+                                          window, 1.0 / np.sqrt(host.d), kcb, vcb, tail_k=tail_k, tail_v=tail_v,
+                                          tail_count=np.array(tails, np.uint32))
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_gpu_decode_is_bit_exact(native, oracle, coder):
+    """Codes decoded on the GPU == codes the CPU quantiser produced == codes the restated reference decoders
+    recover from the same bytes."""
+    rng = np.random.default_rng(11)
+    contexts = [48, 16, 37]
+    layer, host, kcb, vcb, *_ = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=CODERS[coder],
+                                       contexts=contexts, tails=[0, 0, 0])
+    pid = 1
+    for s in range(len(contexts)):
+        ids = list(range(pid, pid + len(host.records[s])))
+        pid += len(ids)
+        ks, vs = layer.decode_pages(ids)
+        ks, vs = ks.cpu().numpy(), vs.cpu().numpy()
+        for p in range(len(ids)):
+            for h in range(2):
+                want_k, want_v = host.symbols[s][p][h]
+                assert np.array_equal(ks[p, h], want_k)
+                assert np.array_equal(vs[p, h], want_v)
+                back_k, back_v = oracle.open_record(host.records[s][p][h], 128, 16, 64, kcb, vcb)
+                assert np.array_equal(back_k, want_k) and np.array_equal(back_v, want_v)
+    assert layer.device_status() == 0
+
+
+GEOMETRIES = [
+    # hq, hkv, d, t, block, contexts, tails, window
+    (4, 2, 128, 16, 64, [64, 16, 40, 0], [0, 3, 5, 2], 0),
+    (32, 8, 128, 16, 64, [128, 96], [7, 0], 0),
+    (8, 8, 128, 16, 64, [80], [1], 0),
+    (14, 2, 64, 32, 64, [96, 50], [0, 4], 0),
+    (4, 4, 32, 16, 32, [33, 64], [2, 0], 0),
+    (8, 2, 96, 16, 128, [48, 70], [3, 9], 0),
+    (4, 2, 128, 16, 64, [160, 75], [5, 0], 50),
+]
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+@pytest.mark.parametrize("geo", GEOMETRIES, ids=lambda g: f"hq{g[0]}kv{g[1]}d{g[2]}t{g[3]}b{g[4]}w{g[7]}")
+def test_generic_attention_matches_oracle(native, oracle, coder, geo):
+    import torch
+    hq, hkv, d, t, block, contexts, tails, window = geo
+    rng = np.random.default_rng(5)
+    layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=hq, hkv=hkv, d=d, t=t, block=block,
+                                                           coder=CODERS[coder], contexts=contexts, tails=tails)
+    q = rng.standard_normal((len(contexts), hq, d)).astype(np.float16)
+    want = _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q, hq, stride, window)
+    got = layer.attention(torch.from_numpy(q).cuda(), causal_window=window, kernel=native.KERNEL_GENERIC).cpu().numpy()
+    ok, err = attention_close(got, want)
+    assert layer.device_status() == 0
+    assert ok, f"max abs error {err}"
+    # sequences with no visible token give zeros (src/cuda/paged_kv_attention.cu:170-173)
+    for s, (c, tl) in enumerate(zip(contexts, tails)):
+        if c + tl == 0:
+            assert np.all(got[s] == 0)
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_gpu_sealer_is_byte_exact(native, oracle, coder):
+    """Records written by the GPU sealer equal the oracle's records byte for byte (same quantiser rounding, same
+    block streams, same fallback rule, zero padding)."""
+    import torch
+    rng = np.random.default_rng(23)
+    hkv, d, t = 2, 128, 16
+    hist = hist_of(laplace_codes(rng, 1 << 16, 4.0).astype(np.int16) + 128)
+    kcb = oracle.codebook_from_hist(hist)
+    vcb = oracle.codebook_from_hist(hist)
+    layer = _layer(native, kv_heads=hkv, query_heads=4, coder=CODERS[coder], max_sequences=5)
+    layer.set_codebooks(hist, hist)
+    cases = []
+    for s, (b, rows) in enumerate([(4.0, 16), (12.0, 16), (40.0, 16), (4.0, 9), (0.0, 16)]):
+        k, v = _random_kv(rng, hkv, rows, d, b) if b else (np.zeros((hkv, rows, d), np.float32),) * 2
+        tk = np.zeros((1, hkv, t, d), np.float16)
+        tv = np.zeros((1, hkv, t, d), np.float16)
+        tk[0, :, :rows] = k
+        tv[0, :, :rows] = v
+        layer.fill_tails([s], torch.from_numpy(tk).cuda(), torch.from_numpy(tv).cuda(), rows)
+        cases.append((k, v, rows))
+    assert layer.seal_full_pages(force=True) == 5
+    assert layer.device_status() == 0
+    for s, (k, v, rows) in enumerate(cases):
+        pid = int(layer.h_page_table[s, 0])
+        for h in range(hkv):
+            want = oracle.seal_record(k[h], v[h], rows, d, t, 64, CODERS[coder], 0, kcb, vcb)[0]
+            got = layer.record_bytes(pid, h)
+            assert got.size == want.size, (s, h, got.size, want.size)
+            assert np.array_equal(got, want), (s, h)
+
+
+def test_gpu_sealer_rejects_non_finite(native, oracle):
+    import torch
+    layer = _layer(native, max_sequences=2)
+    hist = np.ones(256, np.uint64)
+    layer.set_codebooks(hist, hist)
+    k = torch.zeros((2, 2, 16, 128), dtype=torch.float16, device="cuda")
+    v = torch.zeros_like(k)
+    k[1, 0, 3, 7] = float("inf")
+    layer.fill_tails([0, 1], k, v, 16)
+    layer.seal_full_pages()
+    assert layer.device_status() & native.DEVSTAT_NONFINITE
+    pid_bad = int(layer.h_page_table[1, 0])
+    assert int(layer.page_dir[pid_bad * 2].item()) == 0          # not published
+    pid_ok = int(layer.h_page_table[0, 0])
+    assert int(layer.page_dir[pid_ok * 2].item()) != 0
