@@ -1,6 +1,505 @@
-// placeholder until the lane-per-block kernel lands
+// sealed_attention_lanes.cu — the hot kernel: decode-step attention over sealed pages for the geometry
+// head_dim 128, page_tokens 16, block_size 64 (32 blocks per stream), up to 4 query heads per kv head.
+//
+// What it computes is what src/cuda/paged_kv_attention.cu:183-276 computes for one query token; how it runs is new:
+//
+//   * One WARP owns one (chunk, kv head) unit. A page record arrives in shared memory as ONE bulk async copy
+//     (cp.async.bulk + mbarrier), double buffered per warp. Coding tables (rANS slot table, Huffman LUT) are loaded
+//     once per CTA. No thread ever reads page bytes from global memory directly.
+//   * Lane l decodes block l of the K stream and block l of the V stream, interleaved so that the two independent
+//     decoder chains overlap. Symbols never leave registers: four symbols are packed into one register, turned
+//     into two fp16 pairs with byte permutes (bias 1024, exact), and fed straight into mma.sync fragments.
+//       K block l = token l/2, channels 64*(l&1)..+63  -> A operand of S = K * Q^T   (16 mma per page)
+//       V block l = channels 4l..4l+3, all 16 tokens   -> B operand of O^T = P' * V  (16 mma per page)
+//     The query group is the other operand, laid out with zeros so that every lane's private slice of the
+//     contraction lands in its own output column/row. Tensor cores do the whole contraction for the group;
+//     a code is decoded once for all query heads (the reference re-decodes per query head,
+//     paged_kv_attention.cu:205-207).
+//   * Online softmax per page in fp32; partial (max, sum, weighted) per unit goes to the split-KV workspace and is
+//     merged by the combine kernel (cf_online_softmax_merge rule, src/runtime/kv_runtime.cpp:219-243).
+//   * Every wait on a copy is bounded; on expiry the warp raises CF_B200_DEVSTAT_WAIT_EXPIRED and leaves.
+
+#include <math_constants.h>
+
 #include "attention_params.cuh"
+
 namespace cfb {
-bool lanes_kernel_supports(const AttentionParams &) { return false; }
-cudaError_t launch_lanes_attention(const AttentionParams &, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
+constexpr uint32_t kStageBytes = 4224;   // 16 header + 2 * 2048 payload max + slack, multiple of 128
+constexpr uint32_t kScratchBytes = 256;  // P rows (4 heads x 16 tokens x 2 B) + alpha[4]
+constexpr uint32_t kWarpBytes = 2 * kStageBytes + kScratchBytes + 128;  // + 2 mbarriers (padded)
+constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
+constexpr uint32_t kSmemBytes = kTableBytes + kWarps * kWarpBytes;
+constexpr uint32_t kWaitSpins = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr uint32_t kMagic = 0x64646464u;       // fp16 1024.0 high byte, for the byte-permute conversion
+constexpr uint32_t kBias2 = 0x64806480u;       // half2(1152, 1152) = 1024 + zero point
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the copy did not land within kWaitSpins polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitSpins; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// One bulk async copy global -> this CTA's shared memory (16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// Four packed symbols (byte i = symbol i) -> two half2 of codes (symbol - 128), exact.
+__device__ __forceinline__ void quad_to_half2(uint32_t quad, uint32_t &lo, uint32_t &hi) {
+    lo = hsub2_u32(__byte_perm(quad, kMagic, 0x4140), kBias2);  // (s0, s1)
+    hi = hsub2_u32(__byte_perm(quad, kMagic, 0x4342), kBias2);  // (s2, s3)
+}
+
+// ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
+struct RansLane {
+    uint32_t x;
+    const uint8_t *bytes;
+    const uint32_t *table;
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint32_t *slot_table) {
+        x = reinterpret_cast<const uint32_t *>(part)[lane];
+        bytes = part + 192 + reinterpret_cast<const uint16_t *>(part + 128)[lane];
+        table = slot_table;
+    }
+    // src/cuda/rans.cu:20-23; the state stays >= 2^11 after the update, so at most two bytes come in.
+    __device__ __forceinline__ uint32_t symbol() {
+        const uint32_t e = table[x & (CF_B200_RANS_M - 1u)];
+        x = ((e >> 8) & 0xfffu) * (x >> CF_B200_RANS_PROB_BITS) + (e >> 20);
+        if (x < kRansL) {
+            x = (x << 8) | *bytes++;
+            if (x < kRansL) x = (x << 8) | *bytes++;
+        }
+        return e;
+    }
+    __device__ __forceinline__ uint32_t quad() {
+        uint32_t q = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
+        return q;
+    }
+};
+
+struct HuffLane {
+    uint32_t w0, w1, off;
+    const uint32_t *next;
+    const uint16_t *lut;
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint16_t *table) {
+        const uint32_t bit = reinterpret_cast<const uint16_t *>(part)[lane];
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(part + 64) + (bit >> 5);
+        w0 = words[0];
+        w1 = words[1];
+        next = words + 2;
+        off = bit & 31u;
+        lut = table;
+    }
+    // include/chromofold/detail/block_huffman_device.cuh:12-19: the next 12 bits, MSB-first, index the LUT.
+    __device__ __forceinline__ uint32_t symbol() {
+        const uint32_t look = __funnelshift_l(w1, w0, off) >> (32u - CF_B200_HUFF_MAXLEN);
+        const uint32_t e = lut[look];
+        off += e >> 8;
+        if (off >= 32u) {
+            off -= 32u;
+            w0 = w1;
+            w1 = *next++;
+        }
+        return e;
+    }
+    __device__ __forceinline__ uint32_t quad() {
+        uint32_t q = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
+        return q;
+    }
+};
+
+struct FixedLane {
+    const uint32_t *words;
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane) {
+        words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
+    }
+    // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
+    __device__ __forceinline__ uint32_t quad() { return __byte_perm(*words++, 0u, 0x0123); }
+};
+
+// Per-warp running state of one unit.
+struct UnitState {
+    float score[4];      // S fragment of the current page
+    float acc[4][4];     // O fragments: [channel of the lane's V block][fragment register]
+    uint32_t vq[16];     // V symbols of the current page, [channel*4 + token quad]
+    float m0, m1, l0, l1;  // running max / partial sum of the lane's two heads
+};
+
+template <class KLane, class VLane>
+__device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, const uint32_t (&bq)[16][2]) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+        uint32_t kq = 0, vv = 0;
+        if constexpr (sizeof(KLane) == sizeof(FixedLane)) {
+            kq = k.quad();
+            vv = v.quad();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {  // two independent decoder chains, interleaved symbol by symbol
+                kq = __funnelshift_r(kq, k.symbol(), 8);
+                vv = __funnelshift_r(vv, v.symbol(), 8);
+            }
+        }
+        u.vq[q] = vv;
+        uint32_t lo, hi;
+        quad_to_half2(kq, lo, hi);
+        mma_16816(u.score, lo, 0u, hi, 0u, bq[q][0], bq[q][1]);
+    }
+}
+
+template <class KLane>
+__device__ __forceinline__ void decode_k_only(KLane &k, UnitState &u, const uint32_t (&bq)[16][2]) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+        uint32_t lo, hi;
+        quad_to_half2(k.quad(), lo, hi);
+        mma_16816(u.score, lo, 0u, hi, 0u, bq[q][0], bq[q][1]);
+    }
+}
+
+template <class VLane>
+__device__ __forceinline__ void decode_v_only(VLane &v, UnitState &u) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) u.vq[q] = v.quad();
+}
+
+__global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint32_t *k_slot = reinterpret_cast<uint32_t *>(smem);
+    uint32_t *v_slot = k_slot + 4096;
+    uint16_t *k_lut = reinterpret_cast<uint16_t *>(v_slot + 4096);
+    uint16_t *v_lut = k_lut + 4096;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint8_t *warp_mem = smem + kTableBytes + warp * kWarpBytes;
+    uint8_t *stage[2] = {warp_mem, warp_mem + kStageBytes};
+    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);         // [4][16]
+    float *alpha_s = reinterpret_cast<float *>(warp_mem + 2 * kStageBytes + 128);    // [4]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + 2 * kStageBytes + kScratchBytes);
+
+    // coding tables: once per CTA
+    {
+        const uint4 *src;
+        uint4 *dst;
+        src = reinterpret_cast<const uint4 *>(p.k_tables->rans_slot);
+        dst = reinterpret_cast<uint4 *>(k_slot);
+        for (uint32_t i = tid; i < 1024; i += kThreads) dst[i] = src[i];
+        src = reinterpret_cast<const uint4 *>(p.v_tables->rans_slot);
+        dst = reinterpret_cast<uint4 *>(v_slot);
+        for (uint32_t i = tid; i < 1024; i += kThreads) dst[i] = src[i];
+        src = reinterpret_cast<const uint4 *>(p.k_tables->huff_lut);
+        dst = reinterpret_cast<uint4 *>(k_lut);
+        for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
+        src = reinterpret_cast<const uint4 *>(p.v_tables->huff_lut);
+        dst = reinterpret_cast<uint4 *>(v_lut);
+        for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
+    }
+    if (lane == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    PlanHeader *hdr = plan_header(p);
+    const uint32_t *prefix = chunk_prefix(p);
+    const uint32_t unit_count = hdr->chunk_count * p.kv_head_span;
+    const uint32_t pages_per_unit = hdr->pages_per_unit;
+    const uint32_t G = p.group;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    uint32_t phase[2] = {0u, 0u};
+
+    // fixed lane roles
+    const uint32_t q_head_of_col = g & 3u;                 // S columns: n = parity*4 + head
+    const bool q_col_live = ((t >> 1) == (g >> 2)) && q_head_of_col < G;
+    const uint32_t my_token = 2u * g + (t >> 1);           // S fragment: row g, this lane's token
+    const uint32_t my_head0 = 2u * (t & 1u);               // S fragment: this lane's two heads
+    const uint32_t o_head = g & 3u;                        // O fragments: all of this lane's outputs are one head
+    const uint32_t mask_lo = (t == (g >> 2)) ? 0xffffffffu : 0u;       // P rows with lane tag t
+    const uint32_t mask_hi = (t == (g >> 2) + 2u) ? 0xffffffffu : 0u;
+
+    for (;;) {
+        uint32_t unit = 0;
+        if (lane == 0) unit = atomicAdd(&hdr->next_unit, 1u);
+        unit = __shfl_sync(0xffffffffu, unit, 0);
+        if (unit >= unit_count) break;
+        const uint32_t chunk = unit / p.kv_head_span;
+        const uint32_t head_local = unit % p.kv_head_span;
+        const uint32_t kv_head = p.kv_head_begin + head_local;
+        const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
+        const uint32_t slot = slot_of(p, seq);
+        const uint32_t sealed = p.seq_sealed_tokens[slot];
+        const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
+        const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
+        const uint32_t pages = (sealed + 15u) / 16u;
+        const uint32_t first_page = min(first_token / 16u, pages);
+        const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
+        const uint32_t page_end = min(page_begin + pages_per_unit, pages);
+        const uint32_t n_pages = page_end > page_begin ? page_end - page_begin : 0u;
+        const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot) * p.page_table_stride;
+
+        // query fragments: B operand of S = K * Q^T, column n = parity*4 + head, zero where the lane's slice of
+        // the contraction belongs to the other token of the pair
+        uint32_t bq[16][2];
+        {
+            const __half *qrow = reinterpret_cast<const __half *>(p.queries) +
+                                 (static_cast<uint64_t>(seq) * p.query_head_count + kv_head * G + q_head_of_col) * 128u +
+                                 64u * (t & 1u);
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                uint2 v = make_uint2(0u, 0u);
+                if (q_col_live) v = *reinterpret_cast<const uint2 *>(qrow + 4 * s);
+                bq[s][0] = v.x;
+                bq[s][1] = v.y;
+            }
+        }
+
+        UnitState u;
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) u.acc[a][b] = 0.0f;
+        u.m0 = u.m1 = -CUDART_INF_F;
+        u.l0 = u.l1 = 0.0f;
+        float v_scale_prev = 1.0f;
+
+        auto load_entry = [&](uint32_t page) -> uint64_t {
+            const uint32_t page_id = table_row[page];
+            return p.page_dir[static_cast<uint64_t>(page_id) * p.kv_head_count + kv_head];
+        };
+        auto issue = [&](uint32_t st, uint64_t entry) {
+            const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
+            if (lane == 0 && units16 != 0 && units16 * 16u <= kStageBytes - 64u) {
+                mbar_expect_tx(&bars[st], units16 * 16u);
+                bulk_load(stage[st], p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
+            }
+        };
+        auto entry_ok = [&](uint64_t entry) {
+            const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
+            return units16 != 0 && units16 * 16u <= kStageBytes - 64u;
+        };
+
+        uint64_t entry_cur = n_pages ? load_entry(page_begin) : 0ull;
+        uint64_t entry_next = n_pages > 1 ? load_entry(page_begin + 1) : 0ull;
+        __syncwarp();
+        issue(0, entry_cur);
+        bool alive = true;
+
+        for (uint32_t i = 0; i < n_pages; ++i) {
+            const uint32_t st = i & 1u;
+            uint64_t entry_after = 0ull;
+            if (i + 1 < n_pages) {
+                __syncwarp();  // every lane is done with the other stage (page i-1)
+                issue(st ^ 1u, entry_next);
+                if (i + 2 < n_pages) entry_after = load_entry(page_begin + i + 2);
+            }
+            if (!entry_ok(entry_cur)) {
+                if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+            } else {
+                if (!mbar_wait(&bars[st], phase[st])) {
+                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                    alive = false;
+                    break;
+                }
+                phase[st] ^= 1u;
+                const uint8_t *rec = stage[st];
+                const uint4 hv = *reinterpret_cast<const uint4 *>(rec);
+                const uint32_t k_units = hv.x & 0xffffu, v_units = hv.x >> 16;
+                const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu, token_count = hv.y >> 16;
+                const uint32_t codebook = hv.w & 0xffffu, version = hv.w >> 24;
+                const bool good = version == CF_B200_FORMAT_VERSION && codebook == p.codebook_id &&
+                                  1u + k_units + v_units == CF_B200_DIR_LENGTH_UNITS(entry_cur) && k_units <= 128u &&
+                                  v_units <= 128u && k_coder <= 2u && v_coder <= 2u && token_count >= 1u &&
+                                  token_count <= 16u;
+                if (!good) {
+                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                } else {
+                    const uint8_t *k_part = rec + 16;
+                    const uint8_t *v_part = k_part + 16u * k_units;
+                    const float k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) *
+                                          (p.softmax_scale * kLog2e);
+                    const float v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
+                    u.score[0] = u.score[1] = u.score[2] = u.score[3] = 0.0f;
+
+                    if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
+                        RansLane k, v;
+                        k.open(k_part, lane, k_slot);
+                        v.open(v_part, lane, v_slot);
+                        decode_fused(k, v, u, bq);
+                    } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
+                        HuffLane k, v;
+                        k.open(k_part, lane, k_lut);
+                        v.open(v_part, lane, v_lut);
+                        decode_fused(k, v, u, bq);
+                    } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
+                        FixedLane k, v;
+                        k.open(k_part, lane);
+                        v.open(v_part, lane);
+                        decode_fused(k, v, u, bq);
+                    } else {  // mixed coders (one stream fell back to fixed width): one stream after the other
+                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_only(k, u, bq); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_only(k, u, bq); }
+                        else { FixedLane k; k.open(k_part, lane); decode_k_only(k, u, bq); }
+                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_only(v, u); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_only(v, u); }
+                        else { FixedLane v; v.open(v_part, lane); decode_v_only(v, u); }
+                    }
+
+                    // ---- online softmax for this page (fp32) ----
+                    const uint32_t token = (page_begin + i) * 16u + my_token;
+                    const bool visible = my_token < token_count && token >= first_token && token < sealed;
+                    const float s0 = visible ? u.score[0] * k_scale : -CUDART_INF_F;
+                    const float s1 = visible ? u.score[1] * k_scale : -CUDART_INF_F;
+                    float r0 = s0, r1 = s1;
+#pragma unroll
+                    for (int o = 2; o <= 16; o <<= 1) {  // lanes that hold the same two heads
+                        r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
+                        r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
+                    }
+                    const float n0 = fmaxf(u.m0, r0), n1 = fmaxf(u.m1, r1);
+                    const float z0 = n0 == -CUDART_INF_F ? 0.0f : n0, z1 = n1 == -CUDART_INF_F ? 0.0f : n1;
+                    const float p0 = exp2f(s0 - z0), p1 = exp2f(s1 - z1);
+                    const float a0 = exp2f(u.m0 - z0), a1 = exp2f(u.m1 - z1);
+                    u.l0 = u.l0 * a0 + p0;
+                    u.l1 = u.l1 * a1 + p1;
+                    u.m0 = n0;
+                    u.m1 = n1;
+                    __syncwarp();  // the previous page's readers of the scratch are done
+                    p_rows[my_head0 * 16u + my_token] = __float2half_rn(p0);
+                    p_rows[(my_head0 + 1u) * 16u + my_token] = __float2half_rn(p1);
+                    if (g == 0 && t < 2) {
+                        alpha_s[my_head0] = a0;
+                        alpha_s[my_head0 + 1u] = a1;
+                    }
+                    __syncwarp();
+                    // O = O * alpha, kept in units of the current page's V scale
+                    const float beta = alpha_s[o_head] * (v_scale_prev / v_scale);
+                    v_scale_prev = v_scale;
+                    const uint4 pr0 = *reinterpret_cast<const uint4 *>(p_rows + o_head * 16u);
+                    const uint4 pr1 = *reinterpret_cast<const uint4 *>(p_rows + o_head * 16u + 8u);
+                    const uint32_t prow[8] = {pr0.x, pr0.y, pr0.z, pr0.w, pr1.x, pr1.y, pr1.z, pr1.w};
+#pragma unroll
+                    for (int dd = 0; dd < 4; ++dd) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) u.acc[dd][c] *= beta;
+#pragma unroll
+                        for (int tq = 0; tq < 4; ++tq) {
+                            uint32_t lo, hi;
+                            quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
+                            mma_16816(u.acc[dd], prow[2 * tq] & mask_lo, prow[2 * tq] & mask_hi,
+                                      prow[2 * tq + 1] & mask_lo, prow[2 * tq + 1] & mask_hi, lo, hi);
+                        }
+                    }
+                }
+            }
+            entry_cur = entry_next;
+            entry_next = entry_after;
+        }
+        if (!alive) {
+            // give the copies still in flight a bounded chance to land before this warp's buffers go away
+            mbar_wait(&bars[0], phase[0]);
+            mbar_wait(&bars[1], phase[1]);
+            return;
+        }
+
+        // ---- unit partials ----
+        float l0 = u.l0, l1 = u.l1;
+#pragma unroll
+        for (int o = 2; o <= 16; o <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+        }
+        if (g == 0 && t < 2) {
+            if (my_head0 < G) {
+                float *dst = partial_ptr(p, chunk, head_local * G + my_head0);
+                dst[0] = u.m0;
+                dst[1] = l0;
+            }
+            if (my_head0 + 1u < G) {
+                float *dst = partial_ptr(p, chunk, head_local * G + my_head0 + 1u);
+                dst[0] = u.m1;
+                dst[1] = l1;
+            }
+        }
+        if (o_head < G) {
+            float *dst = partial_ptr(p, chunk, head_local * G + o_head) + 2;
+#pragma unroll
+            for (int dd = 0; dd < 4; ++dd) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t owner = 4u * (2u * t + (c & 1)) + (g >> 2) + 2u * (c >> 1);  // lane whose V block it is
+                    dst[4u * owner + dd] = u.acc[dd][c] * v_scale_prev;
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace
+
+bool lanes_kernel_supports(const AttentionParams &p) {
+    return p.head_dim == 128 && p.page_tokens == 16 && p.block_size == 64 && p.group >= 1 && p.group <= 4 &&
+           p.query_type == CF_B200_F16;
+}
+
+cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream) {
+    static int sm_count = 0;
+    static bool configured = false;
+    if (!configured) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lanes_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemBytes));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    lanes_attention_kernel<<<sm_count, kThreads, kSmemBytes, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
 }  // namespace cfb
