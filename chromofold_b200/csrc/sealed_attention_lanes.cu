@@ -90,6 +90,7 @@ __device__ __forceinline__ void quad_to_half2(uint32_t quad, uint32_t &lo, uint3
 
 // ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
 struct RansLane {
+    static constexpr bool kWholeQuads = false;
     uint32_t x;
     const uint8_t *bytes;
     const uint32_t *table;
@@ -117,6 +118,7 @@ struct RansLane {
 };
 
 struct HuffLane {
+    static constexpr bool kWholeQuads = false;
     uint32_t w0, w1, off;
     const uint32_t *next;
     const uint16_t *lut;
@@ -150,6 +152,7 @@ struct HuffLane {
 };
 
 struct FixedLane {
+    static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
     const uint32_t *words;
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane) {
         words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
@@ -171,7 +174,7 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, c
 #pragma unroll
     for (int q = 0; q < 16; ++q) {
         uint32_t kq = 0, vv = 0;
-        if constexpr (sizeof(KLane) == sizeof(FixedLane)) {
+        if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
             kq = k.quad();
             vv = v.quad();
         } else {
@@ -213,7 +216,6 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint8_t *warp_mem = smem + kTableBytes + warp * kWarpBytes;
-    uint8_t *stage[2] = {warp_mem, warp_mem + kStageBytes};
     __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);         // [4][16]
     float *alpha_s = reinterpret_cast<float *>(warp_mem + 2 * kStageBytes + 128);    // [4]
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + 2 * kStageBytes + kScratchBytes);
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     const uint32_t pages_per_unit = hdr->pages_per_unit;
     const uint32_t G = p.group;
     const uint32_t g = lane >> 2, t = lane & 3u;
-    uint32_t phase[2] = {0u, 0u};
+    uint32_t phase_bits = 0u;  // bit s: parity the next wait on stage s expects
 
     // fixed lane roles
     const uint32_t q_head_of_col = g & 3u;                 // S columns: n = parity*4 + head
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
             const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
             if (lane == 0 && units16 != 0 && units16 * 16u <= kStageBytes - 64u) {
                 mbar_expect_tx(&bars[st], units16 * 16u);
-                bulk_load(stage[st], p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
+                bulk_load(warp_mem + st * kStageBytes, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
             }
         };
         auto entry_ok = [&](uint64_t entry) {
@@ -337,13 +339,13 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
             if (!entry_ok(entry_cur)) {
                 if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
             } else {
-                if (!mbar_wait(&bars[st], phase[st])) {
+                if (!mbar_wait(&bars[st], (phase_bits >> st) & 1u)) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
                     alive = false;
                     break;
                 }
-                phase[st] ^= 1u;
-                const uint8_t *rec = stage[st];
+                phase_bits ^= 1u << st;
+                const uint8_t *rec = warp_mem + st * kStageBytes;
                 const uint4 hv = *reinterpret_cast<const uint4 *>(rec);
                 const uint32_t k_units = hv.x & 0xffffu, v_units = hv.x >> 16;
                 const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu, token_count = hv.y >> 16;
@@ -438,8 +440,8 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         }
         if (!alive) {
             // give the copies still in flight a bounded chance to land before this warp's buffers go away
-            mbar_wait(&bars[0], phase[0]);
-            mbar_wait(&bars[1], phase[1]);
+            mbar_wait(&bars[0], phase_bits & 1u);
+            mbar_wait(&bars[1], (phase_bits >> 1) & 1u);
             return;
         }
 

@@ -166,3 +166,88 @@ def test_gpu_sealer_rejects_non_finite(native, oracle):
     assert int(layer.page_dir[pid_bad * 2].item()) == 0          # not published
     pid_ok = int(layer.h_page_table[0, 0])
     assert int(layer.page_dir[pid_ok * 2].item()) != 0
+
+
+LANES_CASES = [
+    # hq, hkv, contexts, tails, window, min_pages_per_unit
+    (32, 8, [128, 96], [7, 0], 0, 0),
+    (8, 8, [80, 16], [1, 0], 0, 0),
+    (4, 2, [64, 16, 40, 0], [0, 3, 5, 2], 0, 0),
+    (8, 4, [330, 75, 16], [5, 0, 15], 0, 2),      # several chunks per sequence: split-KV + combine
+    (4, 2, [160, 75], [5, 0], 50, 1),              # causal window cuts inside a page, one page per unit
+    (12, 4, [100, 37], [0, 9], 0, 3),              # group of 3, ragged last page
+]
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+@pytest.mark.parametrize("case", LANES_CASES, ids=lambda c: f"hq{c[0]}kv{c[1]}w{c[4]}u{c[5]}")
+def test_lanes_kernel_matches_oracle(native, oracle, coder, case):
+    """The tensor-core lane-per-block kernel (head_dim 128, 16-token pages, 64-symbol blocks)."""
+    import torch
+    hq, hkv, contexts, tails, window, ppu = case
+    rng = np.random.default_rng(17)
+    layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=hq, hkv=hkv, d=128, t=16, block=64,
+                                                           coder=CODERS[coder], contexts=contexts, tails=tails)
+    q = rng.standard_normal((len(contexts), hq, 128)).astype(np.float16)
+    want = _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q, hq, stride, window)
+    got = layer.attention(torch.from_numpy(q).cuda(), causal_window=window, kernel=native.KERNEL_LANES,
+                          min_pages_per_unit=ppu).cpu().numpy()
+    assert layer.device_status() == 0
+    ok, err = attention_close(got, want)
+    assert ok, f"max abs error {err}"
+    generic = layer.attention(torch.from_numpy(q).cuda(), causal_window=window, kernel=native.KERNEL_GENERIC,
+                              min_pages_per_unit=ppu).cpu().numpy()
+    assert attention_close(got, generic, rel=1e-3, abs_=5e-4)[0]
+
+
+def test_lanes_kernel_mixed_coders_and_scales(native, oracle):
+    """Pages whose streams fell back to fixed width (model mismatch), all-zero pages and wildly different page scales
+    in one sequence."""
+    import torch
+    rng = np.random.default_rng(29)
+    hq, hkv, d, t = 8, 2, 128, 16
+    hist = hist_of(laplace_codes(rng, 1 << 16, 2.0).astype(np.int16) + 128)   # narrow model
+    kcb = oracle.codebook_from_hist(hist)
+    vcb = oracle.codebook_from_hist(hist)
+    layer = _layer(native, kv_heads=hkv, query_heads=hq, coder=2, max_sequences=1, max_pages_per_sequence=8,
+                   max_pages=16)
+    layer.set_codebooks(hist, hist)
+    host = HostCache(hkv, d, t, 64, 2, kcb, vcb)
+    for b, scale in [(2.0, 0.01), (60.0, 0.01), (2.0, 3.0), (0.0, 1.0), (60.0, 1e-4), (2.0, 0.5)]:
+        if b:
+            kc = laplace_codes(rng, (hkv, t, d), b).astype(np.float32)
+            vc = laplace_codes(rng, (hkv, t, d), 2.0 if b > 10 else 60.0).astype(np.float32)
+            kc[:, 0, 0] = 127.0   # pins absmax so that the codes keep their spread: narrow streams stay narrow
+            vc[:, 0, 0] = 127.0
+            k = (kc * scale).astype(np.float16).astype(np.float32)
+            v = (vc * scale).astype(np.float16).astype(np.float32)
+        else:
+            k = np.zeros((hkv, t, d), np.float32)
+            v = np.zeros((hkv, t, d), np.float32)
+        host.seal_page(0, k, v)
+    coders = {(int(r[4]), int(r[5])) for page in host.records[0] for r in page}
+    assert (0, 2) in coders or (2, 0) in coders, coders      # mixed pages are present
+    layer.import_records(0, host.records[0], host.tokens[0])
+    q = (rng.standard_normal((1, hq, d)) * 0.3).astype(np.float16)
+    arena, offsets, table, sealed = host.flat([0], 8)
+    want = oracle.sealed_decode_attention(arena, offsets, table, sealed, q, hq, hkv, d, t, 64, 0, 1.0 / np.sqrt(d), kcb, vcb)
+    for kernel in (native.KERNEL_GENERIC, native.KERNEL_LANES):
+        got = layer.attention(torch.from_numpy(q).cuda(), kernel=kernel).cpu().numpy()
+        ok, err = attention_close(got, want)
+        assert ok, (kernel, err)
+    assert layer.device_status() == 0
+
+
+def test_bad_records_are_reported_not_faulted(native, oracle):
+    """A directory entry that points at garbage raises the device status word; the launch completes."""
+    import torch
+    rng = np.random.default_rng(31)
+    layer, host, kcb, vcb, *_ = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=2,
+                                       contexts=[48], tails=[0])
+    layer.arena[15] = 9            # version byte of the first record
+    q = torch.zeros((1, 4, 128), dtype=torch.float16, device="cuda")
+    for kernel in (native.KERNEL_GENERIC, native.KERNEL_LANES):
+        layer.status.zero_()
+        layer.attention(q, kernel=kernel)
+        torch.cuda.synchronize()
+        assert layer.device_status() & native.DEVSTAT_BAD_RECORD
