@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the sealed-KV decode-attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--coder rans|huffman|fixed8]
+
+One "step" is one decode-step attention of the whole batch over one layer: plan + attention + combine launched
+through the C ABI. The workload at N = 1 is the Llama-3-8B-shaped GQA decode step the metric is quoted on:
+32 query heads, 8 kv heads, head_dim 128, 64 sequences with context lengths uniform in [2048, 32768] (whole
+16-token pages), int8 codes from a discretised Laplace(b=12), one binary16 scale per (page, kv head, K|V), pages
+sealed with rANS by the GPU sealer. At N > 1 every rank holds its own batch of 64 sequences (weak scaling, no
+collective on the data path). One JSON line is printed by rank 0.
+
+  value      seq-tokens/s of the whole job, inputs resident in HBM, CUDA events around K steps, max over ranks
+  e2e        the same with the step's host inputs copied in (queries, pinned) and its result copied out
+  roofline   the page-reading kernel alone: sealed bytes it must read / its mean duration (events between stages)
+  cpu_baseline  the CPU oracle (restated reference decoders + double online softmax) on all host cores, on a sample
+  dense      the same attention over uncompressed binary16 pages on the same GPU (memory / speed comparison)
+
+--impl reference times the reference's own CPU code (reference::paged_attention over its int4 sealed pages, built
+into oracle/_ref) on the host cores, on a bounded sample of the same shapes.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sealed-KV decode attn seq-tokens/s"
+UNIT = "seq-tokens/s"
+HQ, HKV, D, T, BLOCK = 32, 8, 128, 16, 64
+BATCH, CTX_LO, CTX_HI = 64, 2048, 32768
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"])
+    ap.add_argument("--laplace-b", type=float, default=12.0)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--ctx-lo", type=int, default=CTX_LO)
+    ap.add_argument("--ctx-hi", type=int, default=CTX_HI)
+    ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "lanes"])
+    ap.add_argument("--min-pages-per-unit", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed comparison kernel")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return (f"llama3-8b-gqa-decode: {HQ}q/{HKV}kv heads, head_dim {D}, batch {a.batch}, ctx U[{a.ctx_lo},{a.ctx_hi}], "
+            f"{T}-token pages, int8 Laplace(b={a.laplace_b:g}) codes, fp16 scale per page-head, {a.coder}-sealed, 1 layer")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        inside = [r for (t, r) in self.rows if t0 <= t <= t1 + 0.25] or [r for (_, r) in self.rows]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no sample"]}
+        sm = sorted(float(r[0]) for r in inside)
+        reasons = set()
+        for r in inside:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(inside[0][1]), "samples": len(inside),
+                "power_w_max": max(float(r[2]) for r in inside), "reasons": sorted(reasons)}
+
+
+def run_reference(a, rank):
+    """The reference's CPU implementation of the path (reference::paged_attention over pages sealed by its own
+    seal_int4_page), all host threads, on a bounded sample of the workload's sequences."""
+    if rank != 0:
+        return
+    from oracle import binding as ob
+    from chromofold_b200.workloads import uniform_contexts
+    ref = ob.ref_cpu()
+    line = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": workload_name(a)}}
+    if ref is None:
+        line = {"impl": "reference", "unavailable": "oracle/_ref/libcfref_cpu.so was not built (reference tree absent at build time)"}
+        print(json.dumps(line))
+        return
+    ref.ref_cache_create.restype = C.c_void_p
+    ref.ref_cache_bytes.restype = C.c_uint64
+    cores = os.cpu_count() or 1
+    contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3)
+    # bounded sample: the first sequences of the batch, at most one per host thread, at most ~400k tokens
+    sample, tokens = [], 0
+    for c in contexts:
+        if len(sample) >= cores or tokens + c > 400_000:
+            break
+        sample.append(int(c))
+        tokens += int(c)
+    rng = np.random.default_rng(7)
+    caches, queries = [], []
+    for c in sample:
+        k = rng.standard_normal((HKV, c, D), dtype=np.float32)
+        v = rng.standard_normal((HKV, c, D), dtype=np.float32)
+        h = ref.ref_cache_create(k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p), C.c_uint32(c),
+                                 C.c_uint32(T), C.c_uint32(HKV), C.c_uint32(D))
+        assert h, "reference sealing failed"
+        caches.append(C.c_void_p(h))
+        queries.append(rng.standard_normal((HQ, D), dtype=np.float32))
+    outs = [np.zeros((HQ, D), np.float32) for _ in sample]
+    scale = C.c_float(1.0 / np.sqrt(D))
+
+    def one(i):
+        rc = ref.ref_cache_attention(caches[i], queries[i].ctypes.data_as(C.c_void_p), C.c_uint32(HQ), C.c_uint32(0),
+                                     scale, outs[i].ctypes.data_as(C.c_void_p))
+        assert rc == 0
+
+    def step():
+        threads = [threading.Thread(target=one, args=(i,)) for i in range(len(sample))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+
+    for _ in range(a.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = tokens * a.steps / dt
+    for h in caches:
+        ref.ref_cache_destroy(h)
+    desc = (f"first {len(sample)} of {a.batch} sequences ({tokens} seq-tokens), reference int4 pages (K per-channel, "
+            f"V per-token fp32 scales), fp32 queries, one thread per sequence")
+    line.update({"value": value, "ms_per_step": dt / a.steps * 1e3,
+                 "cpu_baseline": {"value": value, "unit": UNIT, "cores": min(cores, len(sample)), "kind": "reference",
+                                  "sample": desc},
+                 "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 "gpu_launches": 0})
+    print(json.dumps(line))
+
+
+def cpu_baseline(a, layer, contexts, q_host, out_gpu):
+    """The CPU oracle on the same sealed records: restated reference decoders, dequantise, double online softmax,
+    all host threads. Also the full-size parity check of the GPU result on the sampled sequences."""
+    from oracle import binding as ob
+    import torch
+    cores = os.cpu_count() or 1
+    kcb = ob.codebook_from_hist(np.ones(256, np.uint64))
+    vcb = ob.codebook_from_hist(np.ones(256, np.uint64))
+    for cb, host in ((kcb, layer.host_tables[0]), (vcb, layer.host_tables[1])):  # same tables as the device uses
+        slot = np.ctypeslib.as_array(host.rans_slot)
+        cb.slot2sym[:] = (slot & 0xFF).astype(np.int32).tolist()
+        cb.freq[:] = np.ctypeslib.as_array(host.rans_freq).astype(np.int32).tolist()
+        cb.cum[:] = np.ctypeslib.as_array(host.rans_cum).astype(np.int32).tolist()
+        cb.lut[:] = np.ctypeslib.as_array(host.huff_lut).astype(np.int32).tolist()
+    arena = layer.arena[:layer.sealed_bytes() + 64].cpu().numpy()
+    entries = layer.page_dir.cpu().numpy().astype(np.uint64)
+    offsets = (entries & np.uint64(0xFFFFFFFFFF)) * np.uint64(16)
+    table = layer.h_page_table.astype(np.uint32)
+    scale = 1.0 / np.sqrt(D)
+
+    def run(n):
+        t0 = time.perf_counter()
+        out = ob.sealed_decode_attention(arena, offsets, table[:n], contexts[:n].astype(np.uint32), q_host[:n], HQ, HKV,
+                                         D, T, BLOCK, 0, scale, kcb, vcb, threads=cores)
+        return time.perf_counter() - t0, out
+
+    n = min(2, len(contexts))
+    dt, out = run(n)
+    rate = contexts[:n].sum() / dt
+    budget_tokens = rate * a.cpu_seconds
+    n_full = int(np.searchsorted(np.cumsum(contexts), budget_tokens)) + 1
+    n_full = max(n, min(len(contexts), n_full))
+    if n_full > n:
+        dt, out = run(n_full)
+        n = n_full
+    tokens = int(contexts[:n].sum())
+    got = out_gpu[:n].cpu().numpy()
+    err = np.abs(got - out)
+    ok = bool(np.all(err <= 1e-3 + 2e-3 * np.abs(out)))
+    return ({"value": tokens / dt, "unit": UNIT, "cores": cores, "kind": "port",
+             "sample": f"first {n} of {len(contexts)} sequences ({tokens} seq-tokens), same sealed records, all host threads"},
+            {"sequences_checked": n, "max_abs_err": float(err.max()), "within_2e-3_rel_1e-3_abs": ok})
+
+
+def main():
+    a = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.impl == "reference":
+        run_reference(a, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from chromofold_b200 import _native as N
+    from chromofold_b200.workloads import build_sealed_layer, uniform_contexts
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = f"cuda:{local_rank}"
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(device))
+
+    contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3 + 1000 * rank)
+    layer, info = build_sealed_layer(contexts, query_heads=HQ, kv_heads=HKV, head_dim=D, page_tokens=T, block_size=BLOCK,
+                                     coder=a.coder, dist=("laplace", a.laplace_b), seed=4 + 1000 * rank, device=device,
+                                     keep_dense=not a.no_dense)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(5 + 1000 * rank)
+    q = torch.randn((a.batch, HQ, D), generator=gen, device=device, dtype=torch.float32).half()
+    out = torch.zeros((a.batch, HQ, D), dtype=torch.float32, device=device)
+    kernel = {"auto": N.KERNEL_AUTO, "generic": N.KERNEL_GENERIC, "lanes": N.KERNEL_LANES}[a.kernel]
+    kw = dict(kernel=kernel, min_pages_per_unit=a.min_pages_per_unit)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    step = lambda: layer.attention(q, out=out, **kw)
+    for _ in range(max(a.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t0 = time.time()
+    ms = timed(step, a.steps)
+
+    # end to end: queries come from pinned host memory, the result goes back to pinned host memory, every step
+    q_pin = q.cpu().pin_memory()
+    out_pin = torch.zeros((a.batch, HQ, D), dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step():
+        q_dev.copy_(q_pin, non_blocking=True)
+        layer.attention(q_dev, out=out, **kw)
+        out_pin.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller needs the result before the next step
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, a.steps)
+
+    # the page-reading kernel alone: events between the three stages
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(a.steps)]
+    torch.cuda.synchronize()
+    for s in range(a.steps):
+        ev[s][0].record()
+        layer.attention(q, out=out, stages=N.STAGE_PLAN, **kw)
+        ev[s][1].record()
+        layer.attention(q, out=out, stages=N.STAGE_ATTENTION, **kw)
+        ev[s][2].record()
+        layer.attention(q, out=out, stages=N.STAGE_COMBINE, **kw)
+        ev[s][3].record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    stage_ms = [float(np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(a.steps)])) for i in range(3)]
+    clocks = sampler.stop(t0, t1) if sampler else None
+    status = layer.device_status()
+
+    tokens_rank = int(contexts.sum())
+    tokens_all = torch.tensor([tokens_rank], device=device, dtype=torch.float64)
+    bytes_all = torch.tensor([float(info["sealed_bytes"])], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tokens_all)
+        dist.all_reduce(bytes_all)
+    tokens_total = float(tokens_all.item())
+
+    dense = None
+    if not a.no_dense:
+        from chromofold_b200.cache import dense_attention
+        try:
+            out_d = torch.zeros_like(out)
+            dfn = lambda: dense_attention(layer, info["dense_k"], info["dense_v"], q, out_d)
+            for _ in range(3):
+                dfn()
+            ms_d = timed(dfn, a.steps)
+            err = float((out_d - out).abs().max().item())
+            dense_bytes = tokens_rank * info["fp16_bytes_per_seq_token"]
+            dense = {"value": tokens_total * a.steps / (ms_d * 1e-3), "unit": UNIT, "ms_per_step": ms_d / a.steps,
+                     "hbm_gbs": dense_bytes * a.steps / (ms_d * 1e-3) / 1e9, "bytes_per_seq_token": info["fp16_bytes_per_seq_token"],
+                     "max_abs_diff_vs_sealed": err}
+        except N.CfError as e:
+            dense = {"unavailable": str(e)}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+    # algorithmic bytes of one attention launch on this rank: every sealed record once, the page table, Q in, partials out
+    algo_bytes = info["sealed_bytes"] + 4 * info["pages"] + a.batch * HQ * D * 2
+    att_s = stage_ms[1] * 1e-3
+    achieved = algo_bytes / att_s / 1e9
+    line = {
+        "metric": METRIC, "value": tokens_total * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
+        "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8 codes, f16 mma operands, f32 accumulate", "data": "synthetic",
+        "config": {"workload": workload_name(a), "global_batch": a.batch * world, "seq_tokens_per_step": tokens_total,
+                   "sharding": f"sequences, {a.batch} per GPU, no collective", "l2": "inputs larger than L2 (sealed bytes per GPU "
+                   f"{info['sealed_bytes'] / 1e9:.2f} GB vs 126 MB)", "kernel": a.kernel,
+                   "h0_bits_per_code": {"k": info["h0_bits_k"], "v": info["h0_bits_v"]},
+                   "sealed_bytes_per_seq_token": info["bytes_per_seq_token"],
+                   "fp16_bytes_per_seq_token": info["fp16_bytes_per_seq_token"],
+                   "kv_memory_reduction_vs_fp16": info["fp16_bytes_per_seq_token"] / info["bytes_per_seq_token"],
+                   "whole_model_32_layers_seq_tokens_per_s": tokens_total * a.steps / (ms * 1e-3) / 32},
+        "e2e": {"value": tokens_total * a.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / a.steps,
+                "h2d_bytes_per_step": int(q_pin.numel() * 2), "d2h_bytes_per_step": int(out_pin.numel() * 4)},
+        "gpu_launches": 3 * a.steps,
+        "roofline": {"bound": "hbm", "kernel": "lanes_attention_kernel" if a.kernel != "generic" else "generic_attention_kernel",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
+                     "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": stage_ms[1],
+                     "plan_ms": stage_ms[0], "combine_ms": stage_ms[2],
+                     "decompressed_equivalent_gbs": tokens_rank * info["fp16_bytes_per_seq_token"] / att_s / 1e9},
+        "clocks": clocks, "device_status": status, "dense_fp16": dense,
+    }
+    if world == 1 and not a.no_cpu:
+        base, parity = cpu_baseline(a, layer, contexts, q.cpu().numpy(), out)
+        line["cpu_baseline"] = base
+        line["parity_full_size"] = parity
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -13,6 +13,7 @@ ABI_VERSION = 1
 F16, BF16, F32 = 1, 2, 3
 CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES = 0, 1, 2
+STAGE_PLAN, STAGE_ATTENTION, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 7
 DEVSTAT_BAD_RECORD, DEVSTAT_WAIT_EXPIRED, DEVSTAT_WORKSPACE, DEVSTAT_NONFINITE, DEVSTAT_ARENA_FULL = 1, 2, 4, 8, 16
 
 _u32, _u64, _vp, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_float
@@ -66,8 +67,8 @@ class DenseAttentionDesc(C.Structure):
 EXPORTS = {
     "sealed_kv.h": [
         "cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
-        "cf_b200_sealed_attention_async", "cf_b200_codebook_build", "cf_b200_seal_validate",
-        "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
+        "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async", "cf_b200_codebook_build",
+        "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
         "cf_b200_dense_attention_async", "cf_b200_build_info",
     ],
 }
@@ -85,7 +86,8 @@ def lib():
         _lib = C.CDLL(LIB_PATH)
         _lib.cf_b200_build_info.restype = C.c_char_p
         for name in ("cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
-                     "cf_b200_sealed_attention_async", "cf_b200_codebook_build", "cf_b200_seal_validate",
+                     "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async",
+                     "cf_b200_codebook_build", "cf_b200_seal_validate",
                      "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
                      "cf_b200_dense_attention_async"):
             getattr(_lib, name).restype = C.c_int

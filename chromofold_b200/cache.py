@@ -127,6 +127,35 @@ class SealedKvLayer:
         self.tail_tokens[d_slots.long()] = 0
         return int(full.size)
 
+    def seal_tiles(self, slots, k_tiles, v_tiles):
+        """Append one full page to every listed slot straight from tile tensors (bulk loading).
+        k_tiles, v_tiles: float16 device tensors [len(slots), kv_heads, page_tokens, head_dim]; a slot may appear
+        several times, its pages are appended in list order."""
+        slots = np.asarray(slots, np.int64)
+        n = slots.size
+        if self.next_page_id + n > self.max_pages:
+            raise ValueError("page directory is full")
+        ids = np.arange(self.next_page_id, self.next_page_id + n, dtype=np.int32)
+        self.next_page_id += n
+        order = np.zeros(n, np.int64)      # position of each job among the jobs of its slot
+        seen = {}
+        for j, s in enumerate(slots):
+            order[j] = seen.get(int(s), 0)
+            seen[int(s)] = order[j] + 1
+        page_index = self.h_sealed[slots] // self.page_tokens + order
+        if np.any(self.h_sealed[slots] % self.page_tokens) or np.any(page_index >= self.max_pages_per_sequence):
+            raise ValueError("slot cannot take another full page")
+        d_tiles = torch.arange(n, dtype=torch.int32, device=self.device)
+        d_ids = torch.as_tensor(ids, device=self.device)
+        d = self._seal_desc(d_tiles, d_ids, None)
+        d.tail_k, d.tail_v = k_tiles.data_ptr(), v_tiles.data_ptr()
+        N.check("seal_pages", self.lib.cf_b200_seal_pages_async(C.byref(d), _stream_ptr()))
+        self.h_page_table[slots, page_index] = ids
+        self.page_table[torch.as_tensor(slots, device=self.device), torch.as_tensor(page_index, device=self.device)] = d_ids
+        for s, c in seen.items():
+            self.h_sealed[s] += c * self.page_tokens
+        self.sealed_tokens.copy_(torch.as_tensor(self.h_sealed.astype(np.int32)))
+
     # -- import of records sealed elsewhere ------------------------------------------------------------
     def import_records(self, slot, records, tokens_per_page=None):
         """Append already sealed pages to `slot`. records[p][h] is the record (bytes-like) of page p, kv head h."""
@@ -159,7 +188,7 @@ class SealedKvLayer:
 
     # -- attention -----------------------------------------------------------------------------------
     def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
-                  kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0):
+                  kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL):
         """Decode-step attention: queries [n, query_heads, head_dim] (float16 or float32) -> float32 output."""
         n = queries.shape[0]
         if out is None:
@@ -170,7 +199,8 @@ class SealedKvLayer:
         d.kernel = kernel
         d.kv_head_begin, d.kv_head_span = kv_head_begin, kv_head_span
         d.min_pages_per_unit = min_pages_per_unit
-        N.check("sealed_attention", self.lib.cf_b200_sealed_attention_async(C.byref(d), _stream_ptr()))
+        N.check("sealed_attention", self.lib.cf_b200_sealed_attention_stages_async(C.byref(d), C.c_uint32(stages),
+                                                                                      _stream_ptr()))
         return out
 
     def decode_pages(self, page_ids):
@@ -244,3 +274,36 @@ class SealedKvLayer:
         d.arena, d.arena_units = self.arena.data_ptr(), self.arena_units
         d.arena_cursor_units, d.page_dir, d.status = self.cursor.data_ptr(), self.page_dir.data_ptr(), self.status.data_ptr()
         return d
+
+
+def swizzle_dense_tiles(tiles):
+    """Binary16 tiles [..., 16 tokens, 128 channels] -> the chunk-swizzled row layout the dense comparison kernel reads:
+    inside a token row, 16-byte chunk c is stored at position c ^ f(token),
+    f(token) = (((token ^ (token >> 2)) & 1) << 2) | ((token >> 1) & 1)."""
+    tok = torch.arange(16, device=tiles.device)
+    f = (((tok ^ (tok >> 2)) & 1) << 2) | ((tok >> 1) & 1)
+    src = torch.arange(16, device=tiles.device)[None, :] ^ f[:, None]          # [token][physical chunk] -> logical chunk
+    v = tiles.reshape(*tiles.shape[:-2], 16, 16, 8)
+    return v[..., tok[:, None], src, :].reshape(tiles.shape).contiguous()
+
+
+def dense_attention(layer, pool_k, pool_v, queries, out, *, softmax_scale=None, causal_window=0, slots=None):
+    """The comparison kernel: attention over uncompressed binary16 pages addressed by `layer`'s page table.
+    pool_k / pool_v: swizzled tiles [page_id][kv_heads][16][128] (see swizzle_dense_tiles)."""
+    d = N.DenseAttentionDesc()
+    d.struct_size, d.abi_version = C.sizeof(N.DenseAttentionDesc), N.ABI_VERSION
+    d.kv_head_count, d.query_head_count, d.head_dim, d.page_tokens = layer.kv_heads, layer.query_heads, layer.head_dim, layer.page_tokens
+    d.pool_k, d.pool_v = pool_k.data_ptr(), pool_v.data_ptr()
+    d.page_table, d.seq_sealed_tokens = layer.page_table.data_ptr(), layer.sealed_tokens.data_ptr()
+    if slots is not None:
+        layer._slots_keepalive = layer._slots_tensor(slots)
+        d.seq_slots = layer._slots_keepalive.data_ptr()
+    d.page_table_stride, d.seq_count = layer.max_pages_per_sequence, queries.shape[0]
+    d.queries, d.output = queries.data_ptr(), out.data_ptr()
+    d.softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / float(np.sqrt(layer.head_dim))
+    d.causal_window = causal_window
+    ws = layer.workspace.data_ptr()
+    aligned = (ws + 255) // 256 * 256
+    d.workspace, d.workspace_bytes = aligned, layer.workspace.numel() - (aligned - ws)
+    N.check("dense_attention", layer.lib.cf_b200_dense_attention_async(C.byref(d), _stream_ptr()))
+    return out

@@ -476,20 +476,29 @@ extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_seal
     return CF_OK;
 }
 
-extern "C" cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *d, void *stream) {
+extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_attention_desc *d, uint32_t stages,
+                                                           void *stream) {
     const cf_status valid = cf_b200_sealed_attention_validate(d);
     if (valid != CF_OK) return valid;
+    if (stages == 0 || stages > 7u) return CF_ERR_INVALID_ARGUMENT;
     AttentionParams p;
     cfb::fill_params(d, &p);
     const bool lanes_ok = cfb::lanes_kernel_supports(p);
     if (d->kernel == CF_B200_KERNEL_LANES && !lanes_ok) return CF_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
-    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
-    const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
-    if (e != cudaSuccess) return CF_ERR_CUDA;
-    if (cfb::launch_combine(p, s) != cudaSuccess) return CF_ERR_CUDA;
+    if ((stages & CF_B200_STAGE_PLAN) && cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
+    if (stages & CF_B200_STAGE_ATTENTION) {
+        const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
+        const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
+        if (e != cudaSuccess) return CF_ERR_CUDA;
+    }
+    if ((stages & CF_B200_STAGE_COMBINE) && cfb::launch_combine(p, s) != cudaSuccess) return CF_ERR_CUDA;
     return CF_OK;
+}
+
+extern "C" cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *d, void *stream) {
+    return cf_b200_sealed_attention_stages_async(
+        d, CF_B200_STAGE_PLAN | CF_B200_STAGE_ATTENTION | CF_B200_STAGE_COMBINE, stream);
 }
 
 extern "C" cf_status cf_b200_decode_pages_async(const cf_b200_sealed_attention_desc *d, const uint32_t *page_ids,

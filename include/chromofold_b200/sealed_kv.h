@@ -122,6 +122,15 @@ cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_sealed_attentio
 
 cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *desc, void *stream);
 
+/* The same launch cut into its three kernels, so that a profiler or a benchmark can put events between them:
+ * plan (chunk layout, one block), attention (the kernel that reads the pages), combine (merge + tail + output).
+ * `stages` is a mask; running all three in order equals cf_b200_sealed_attention_async. */
+#define CF_B200_STAGE_PLAN 1u
+#define CF_B200_STAGE_ATTENTION 2u
+#define CF_B200_STAGE_COMBINE 4u
+cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_attention_desc *desc, uint32_t stages,
+                                                void *stream);
+
 /* --------------------------------------------------------------------------------------------------
  * Codebooks. Built on the host from symbol histograms (set-up work, not query path).
  * Normalisation rule for rANS (M = 4096, every symbol codable):

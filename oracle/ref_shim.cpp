@@ -3,6 +3,7 @@
 // compiled together with the reference's src/runtime/{kv_reference,kv_gpu_fixture,kv_runtime}.cpp, taken from
 // where they lie, into oracle/_ref/libcfref_cpu.so (see oracle/Makefile).
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <stdexcept>
@@ -140,5 +141,53 @@ int ref_paged_attention_int4(const float *keys, const float *values, uint32_t se
         return 2;
     }
 }
+
+// A sequence sealed once with reference::seal_int4_page, attended many times with reference::paged_attention
+// (the timed part of the CPU baseline). keys/values: [kv_head_count][tokens][head_dim], cut into page_tokens pages.
+struct RefCache {
+    std::vector<ref::SealedKvPage> pages;
+    uint32_t kv_head_count, head_dim, tokens;
+};
+
+void *ref_cache_create(const float *keys, const float *values, uint32_t tokens, uint32_t page_tokens,
+                       uint32_t kv_head_count, uint32_t head_dim) {
+    try {
+        auto *c = new RefCache{{}, kv_head_count, head_dim, tokens};
+        for (uint32_t h = 0; h < kv_head_count; ++h) {
+            for (uint32_t begin = 0; begin < tokens; begin += page_tokens) {
+                const uint32_t count = std::min(page_tokens, tokens - begin);
+                const size_t off = (static_cast<size_t>(h) * tokens + begin) * head_dim;
+                c->pages.push_back(ref::seal_int4_page(keys + off, values + off, begin, count, 0, h, head_dim));
+            }
+        }
+        return c;
+    } catch (const std::exception &) {
+        return nullptr;
+    }
+}
+
+int ref_cache_attention(const void *cache, const float *queries, uint32_t query_head_count, uint32_t causal_window,
+                        float score_scale, float *output) {
+    try {
+        const auto *c = static_cast<const RefCache *>(cache);
+        ref::AttentionShape shape{1, query_head_count, c->kv_head_count, c->head_dim, c->tokens, causal_window, score_scale};
+        std::vector<float> out;
+        ref::paged_attention(c->pages, {}, queries, shape, &out);
+        std::memcpy(output, out.data(), out.size() * 4);
+        return 0;
+    } catch (const std::invalid_argument &) {
+        return 1;
+    } catch (const std::exception &) {
+        return 2;
+    }
+}
+
+uint64_t ref_cache_bytes(const void *cache) {
+    uint64_t total = 0;
+    for (const auto &p : static_cast<const RefCache *>(cache)->pages) total += p.resident_bytes();
+    return total;
+}
+
+void ref_cache_destroy(void *cache) { delete static_cast<RefCache *>(cache); }
 
 }  // extern "C"

@@ -251,3 +251,39 @@ def test_bad_records_are_reported_not_faulted(native, oracle):
         layer.attention(q, kernel=kernel)
         torch.cuda.synchronize()
         assert layer.device_status() & native.DEVSTAT_BAD_RECORD
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 8), (16, 2), (6, 2)])
+def test_dense_comparison_kernel_matches_oracle(native, oracle, hq, hkv):
+    """The uncompressed binary16 paged-attention kernel against the oracle's dense attention on the same values."""
+    import torch
+    from chromofold_b200.cache import dense_attention, swizzle_dense_tiles
+    rng = np.random.default_rng(41)
+    contexts = [16 * 21, 16 * 3, 16 * 40]
+    pages = [c // 16 for c in contexts]
+    layer = _layer(native, kv_heads=hkv, query_heads=hq, max_sequences=3, max_pages_per_sequence=max(pages),
+                   max_pages=sum(pages) + 2)
+    pool_k = torch.zeros((sum(pages) + 2, hkv, 16, 128), dtype=torch.float16, device="cuda")
+    pool_v = torch.zeros_like(pool_k)
+    q = rng.standard_normal((3, hq, 128)).astype(np.float16)
+    pid = 1
+    want = []
+    for s, n in enumerate(pages):
+        k = rng.standard_normal((hkv, n * 16, 128)).astype(np.float16)
+        v = rng.standard_normal((hkv, n * 16, 128)).astype(np.float16)
+        tiles_k = torch.from_numpy(k.reshape(hkv, n, 16, 128).transpose(1, 0, 2, 3).copy()).cuda()
+        tiles_v = torch.from_numpy(v.reshape(hkv, n, 16, 128).transpose(1, 0, 2, 3).copy()).cuda()
+        pool_k[pid:pid + n] = swizzle_dense_tiles(tiles_k)
+        pool_v[pid:pid + n] = swizzle_dense_tiles(tiles_v)
+        layer.h_page_table[s, :n] = np.arange(pid, pid + n)
+        pid += n
+        rc, o = oracle.dense_attention(k.astype(np.float32), v.astype(np.float32), 0, q[s:s + 1].astype(np.float32),
+                                       n * 16, 0, 1.0 / np.sqrt(128.0))
+        assert rc == 0
+        want.append(o[0])
+    layer.page_table.copy_(torch.from_numpy(layer.h_page_table))
+    layer.sealed_tokens.copy_(torch.tensor(contexts, dtype=torch.int32))
+    out = torch.zeros((3, hq, 128), dtype=torch.float32, device="cuda")
+    dense_attention(layer, pool_k, pool_v, torch.from_numpy(q).cuda(), out)
+    ok, err = attention_close(out.cpu().numpy(), np.stack(want))
+    assert ok, err
