@@ -213,14 +213,17 @@ def test_lanes_kernel_mixed_coders_and_scales(native, oracle):
                    max_pages=16)
     layer.set_codebooks(hist, hist)
     host = HostCache(hkv, d, t, 64, 2, kcb, vcb)
-    for b, scale in [(2.0, 0.01), (60.0, 0.01), (2.0, 3.0), (0.0, 1.0), (60.0, 1e-4), (2.0, 0.5)]:
+    # (K spread, K scale, V scale): V scales differ by 4 orders of magnitude between neighbouring pages; K scales
+    # stay where attention logits are O(10), as trained models have them
+    for b, k_scale, v_scale in [(2.0, 0.01, 0.01), (60.0, 0.004, 0.01), (2.0, 0.02, 3.0), (0.0, 1.0, 1.0),
+                                (60.0, 0.005, 1e-4), (2.0, 0.015, 0.5)]:
         if b:
             kc = laplace_codes(rng, (hkv, t, d), b).astype(np.float32)
             vc = laplace_codes(rng, (hkv, t, d), 2.0 if b > 10 else 60.0).astype(np.float32)
             kc[:, 0, 0] = 127.0   # pins absmax so that the codes keep their spread: narrow streams stay narrow
             vc[:, 0, 0] = 127.0
-            k = (kc * scale).astype(np.float16).astype(np.float32)
-            v = (vc * scale).astype(np.float16).astype(np.float32)
+            k = (kc * k_scale).astype(np.float16).astype(np.float32)
+            v = (vc * v_scale).astype(np.float16).astype(np.float32)
         else:
             k = np.zeros((hkv, t, d), np.float32)
             v = np.zeros((hkv, t, d), np.float32)
