@@ -29,7 +29,7 @@ namespace {
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kStageBytes = 4224;   // 16 header + 2 * 2048 payload max + slack, multiple of 128
-constexpr uint32_t kScratchBytes = 256;  // P rows (4 heads x 16 tokens x 2 B) + alpha[4]
+constexpr uint32_t kScratchBytes = 512;  // P rows, high and low halves (2 x 4 heads x 16 tokens x 2 B) + alpha[4]
 constexpr uint32_t kWarpBytes = 2 * kStageBytes + kScratchBytes + 128;  // + 2 mbarriers (padded)
 constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
 constexpr uint32_t kSmemBytes = kTableBytes + kWarps * kWarpBytes;
@@ -89,27 +89,47 @@ __device__ __forceinline__ void quad_to_half2(uint32_t quad, uint32_t &lo, uint3
 }
 
 // ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
+// Both entropy decoders are written without branches so that the K chain and the V chain of a lane interleave in
+// one straight instruction stream. A 64-bit window holds the upcoming stream bits, top aligned; it is reloaded from
+// shared memory once per quad (four symbols), which is as often as it can run dry.
 struct RansLane {
     static constexpr bool kWholeQuads = false;
-    uint32_t x;
-    const uint8_t *bytes;
-    const uint32_t *table;
+    uint32_t x, whi, wlo, used;   // state; window (next byte = top byte of whi); bits taken since the reload
+    uint32_t pos;                 // shared-memory byte address of the first byte not yet taken at the last reload
+    uint32_t table;               // shared-memory byte address of the slot table
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint32_t *slot_table) {
         x = reinterpret_cast<const uint32_t *>(part)[lane];
-        bytes = part + 192 + reinterpret_cast<const uint16_t *>(part + 128)[lane];
-        table = slot_table;
+        pos = smem_addr(part) + 192u + reinterpret_cast<const uint16_t *>(part + 128)[lane];
+        table = smem_addr(slot_table);
+        used = 0;
     }
-    // src/cuda/rans.cu:20-23; the state stays >= 2^11 after the update, so at most two bytes come in.
+    // Eight bytes starting at `pos`, in stream order, most significant first (the order rans.cu:23 shifts them in).
+    __device__ __forceinline__ void reload() {
+        pos += used >> 3;
+        used = 0;
+        const uint32_t base = pos & ~3u, sel = 0x0123u + 0x1111u * (pos & 3u);
+        uint32_t w0, w1, w2;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
+        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
+        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(w2) : "r"(base));
+        whi = __byte_perm(w0, w1, sel);
+        wlo = __byte_perm(w1, w2, sel);
+    }
+    // src/cuda/rans.cu:20-23. After the update the state is >= 2^11, so the `while (state < L)` loop of the
+    // reference runs 0, 1 or 2 times: exactly (clz(state) - 1) / 8 times. The bytes come out of the window.
     __device__ __forceinline__ uint32_t symbol() {
-        const uint32_t e = table[x & (CF_B200_RANS_M - 1u)];
+        uint32_t e;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(table + ((x & (CF_B200_RANS_M - 1u)) << 2)));
         x = ((e >> 8) & 0xfffu) * (x >> CF_B200_RANS_PROB_BITS) + (e >> 20);
-        if (x < kRansL) {
-            x = (x << 8) | *bytes++;
-            if (x < kRansL) x = (x << 8) | *bytes++;
-        }
+        const uint32_t shift = (static_cast<uint32_t>(__clz(x)) - 1u) & 24u;
+        x = __funnelshift_l(whi, x, shift);
+        whi = __funnelshift_l(wlo, whi, shift);
+        wlo <<= shift;
+        used += shift;
         return e;
     }
     __device__ __forceinline__ uint32_t quad() {
+        reload();
         uint32_t q = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
@@ -119,31 +139,38 @@ struct RansLane {
 
 struct HuffLane {
     static constexpr bool kWholeQuads = false;
-    uint32_t w0, w1, off;
-    const uint32_t *next;
-    const uint16_t *lut;
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint16_t *table) {
-        const uint32_t bit = reinterpret_cast<const uint16_t *>(part)[lane];
-        const uint32_t *words = reinterpret_cast<const uint32_t *>(part + 64) + (bit >> 5);
-        w0 = words[0];
-        w1 = words[1];
-        next = words + 2;
-        off = bit & 31u;
-        lut = table;
+    uint32_t whi, wlo, used;   // window of upcoming bits, MSB first; bits taken since the reload
+    uint32_t words, bit;       // shared-memory address of the payload words; bit position at the last reload
+    uint32_t table;
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint16_t *lut) {
+        bit = reinterpret_cast<const uint16_t *>(part)[lane];
+        words = smem_addr(part) + 64u;
+        table = smem_addr(lut);
+        used = 0;
+    }
+    __device__ __forceinline__ void reload() {  // four codes take at most 48 bits; the window holds 64
+        bit += used;
+        used = 0;
+        const uint32_t base = words + ((bit >> 5) << 2), off = bit & 31u;
+        uint32_t w0, w1, w2;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
+        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
+        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(w2) : "r"(base));
+        whi = __funnelshift_l(w1, w0, off);
+        wlo = __funnelshift_l(w2, w1, off);
     }
     // include/chromofold/detail/block_huffman_device.cuh:12-19: the next 12 bits, MSB-first, index the LUT.
     __device__ __forceinline__ uint32_t symbol() {
-        const uint32_t look = __funnelshift_l(w1, w0, off) >> (32u - CF_B200_HUFF_MAXLEN);
-        const uint32_t e = lut[look];
-        off += e >> 8;
-        if (off >= 32u) {
-            off -= 32u;
-            w0 = w1;
-            w1 = *next++;
-        }
+        uint32_t e;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e) : "r"(table + ((whi >> (32u - CF_B200_HUFF_MAXLEN)) << 1)));
+        const uint32_t len = e >> 8;
+        whi = __funnelshift_l(wlo, whi, len);
+        wlo <<= len;
+        used += len;
         return e;
     }
     __device__ __forceinline__ uint32_t quad() {
+        reload();
         uint32_t q = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
@@ -178,6 +205,8 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, c
             kq = k.quad();
             vv = v.quad();
         } else {
+            k.reload();
+            v.reload();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // two independent decoder chains, interleaved symbol by symbol
                 kq = __funnelshift_r(kq, k.symbol(), 8);
@@ -216,8 +245,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint8_t *warp_mem = smem + kTableBytes + warp * kWarpBytes;
-    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);         // [4][16]
-    float *alpha_s = reinterpret_cast<float *>(warp_mem + 2 * kStageBytes + 128);    // [4]
+    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);         // [4][16] fp16(p)
+    __half *p_rows_lo = p_rows + 64;                                                 // [4][16] fp16(p - fp16(p))
+    float *alpha_s = reinterpret_cast<float *>(warp_mem + 2 * kStageBytes + 448);    // [4]; bytes 256..447 stay zero
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + 2 * kStageBytes + kScratchBytes);
 
     // coding tables: once per CTA
@@ -236,6 +266,11 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         src = reinterpret_cast<const uint4 *>(p.v_tables->huff_lut);
         dst = reinterpret_cast<uint4 *>(v_lut);
         for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
+    }
+    {   // the zero row that inactive lanes read their P fragments from
+        uint32_t *zero = reinterpret_cast<uint32_t *>(warp_mem + 2 * kStageBytes + 256);
+        zero[lane] = 0u;
+        if (lane < 16) zero[32 + lane] = 0u;
     }
     if (lane == 0) {
         mbar_init(&bars[0], 1);
@@ -408,8 +443,13 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     u.m0 = n0;
                     u.m1 = n1;
                     __syncwarp();  // the previous page's readers of the scratch are done
-                    p_rows[my_head0 * 16u + my_token] = __float2half_rn(p0);
-                    p_rows[(my_head0 + 1u) * 16u + my_token] = __float2half_rn(p1);
+                    // P goes to the tensor cores as fp16; the rounding residue is fed as a second operand so that
+                    // P V is accurate to fp32 level whatever the magnitude of V
+                    const __half p0h = __float2half_rn(p0), p1h = __float2half_rn(p1);
+                    p_rows[my_head0 * 16u + my_token] = p0h;
+                    p_rows[(my_head0 + 1u) * 16u + my_token] = p1h;
+                    p_rows_lo[my_head0 * 16u + my_token] = __float2half_rn(p0 - __half2float(p0h));
+                    p_rows_lo[(my_head0 + 1u) * 16u + my_token] = __float2half_rn(p1 - __half2float(p1h));
                     if (g == 0 && t < 2) {
                         alpha_s[my_head0] = a0;
                         alpha_s[my_head0 + 1u] = a1;
@@ -418,19 +458,30 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     // O = O * alpha, kept in units of the current page's V scale
                     const float beta = alpha_s[o_head] * (v_scale_prev / v_scale);
                     v_scale_prev = v_scale;
-                    const uint4 pr0 = *reinterpret_cast<const uint4 *>(p_rows + o_head * 16u);
-                    const uint4 pr1 = *reinterpret_cast<const uint4 *>(p_rows + o_head * 16u + 8u);
-                    const uint32_t prow[8] = {pr0.x, pr0.y, pr0.z, pr0.w, pr1.x, pr1.y, pr1.z, pr1.w};
+                    // P rows as A fragments. Rows g / g+8 of the fragment belong to lane tags g>>2 / (g>>2)+2; a lane
+                    // feeds the row whose tag is its own t and zeros (read from a zero row) otherwise.
+                    const __half *row_a = p_rows + (mask_lo ? o_head * 16u : 128u);
+                    const __half *row_b = p_rows + (mask_hi ? o_head * 16u : 128u);
 #pragma unroll
-                    for (int dd = 0; dd < 4; ++dd) {
+                    for (int dd = 0; dd < 4; ++dd)
 #pragma unroll
                         for (int c = 0; c < 4; ++c) u.acc[dd][c] *= beta;
 #pragma unroll
-                        for (int tq = 0; tq < 4; ++tq) {
-                            uint32_t lo, hi;
-                            quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
-                            mma_16816(u.acc[dd], prow[2 * tq] & mask_lo, prow[2 * tq] & mask_hi,
-                                      prow[2 * tq + 1] & mask_lo, prow[2 * tq + 1] & mask_hi, lo, hi);
+                    for (int part = 0; part < 2; ++part) {  // fp16(p), then the rounding residue
+                        const uint4 a_lo = *reinterpret_cast<const uint4 *>(row_a + part * 64);
+                        const uint4 a_hi = *reinterpret_cast<const uint4 *>(row_a + part * 64 + 8);
+                        const uint4 b_lo = *reinterpret_cast<const uint4 *>(row_b + part * 64);
+                        const uint4 b_hi = *reinterpret_cast<const uint4 *>(row_b + part * 64 + 8);
+                        const uint32_t ra[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+                        const uint32_t rb[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+#pragma unroll
+                        for (int dd = 0; dd < 4; ++dd) {
+#pragma unroll
+                            for (int tq = 0; tq < 4; ++tq) {
+                                uint32_t lo, hi;
+                                quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
+                                mma_16816(u.acc[dd], ra[2 * tq], rb[2 * tq], ra[2 * tq + 1], rb[2 * tq + 1], lo, hi);
+                            }
                         }
                     }
                 }
