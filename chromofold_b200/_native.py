@@ -13,6 +13,7 @@ ABI_VERSION = 1
 F16, BF16, F32 = 1, 2, 3
 CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES = 0, 1, 2
+STATIC_WORKSPACE_BYTES = 8 << 20
 STAGE_PLAN, STAGE_ATTENTION, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 7
 DEVSTAT_BAD_RECORD, DEVSTAT_WAIT_EXPIRED, DEVSTAT_WORKSPACE, DEVSTAT_NONFINITE, DEVSTAT_ARENA_FULL = 1, 2, 4, 8, 16
 
@@ -69,7 +70,8 @@ EXPORTS = {
         "cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
         "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async", "cf_b200_codebook_build",
         "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
-        "cf_b200_dense_attention_async", "cf_b200_build_info",
+        "cf_b200_dense_attention_async", "cf_b200_build_info", "cf_b200_sealed_attention_static_async",
+        "cf_b200_sealed_attention_static_error",
     ],
 }
 
@@ -89,8 +91,9 @@ def lib():
                      "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async",
                      "cf_b200_codebook_build", "cf_b200_seal_validate",
                      "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
-                     "cf_b200_dense_attention_async"):
+                     "cf_b200_dense_attention_async", "cf_b200_sealed_attention_static_async"):
             getattr(_lib, name).restype = C.c_int
+        _lib.cf_b200_sealed_attention_static_error.restype = C.c_char_p
     return _lib
 
 

@@ -203,6 +203,24 @@ class SealedKvLayer:
                                                                                       _stream_ptr()))
         return out
 
+    def attention_no_alloc(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0,
+                           kernel=N.KERNEL_AUTO):
+        """The same decode-step attention through the entry point that uses the library's built-in workspace
+        (for callers that cannot allocate device memory). `out` must be given by such a caller; it is created here
+        only as a convenience for tests."""
+        n = queries.shape[0]
+        if out is None:
+            out = torch.zeros((n, self.query_heads, self.head_dim), dtype=torch.float32, device=self.device)
+        d = self._attention_desc(queries, out, n, slots)
+        d.workspace, d.workspace_bytes = None, 0
+        d.softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / float(np.sqrt(self.head_dim))
+        d.causal_window = causal_window
+        d.kernel = kernel
+        status = self.lib.cf_b200_sealed_attention_static_async(C.byref(d), _stream_ptr())
+        if status != N.CF_OK:
+            raise N.CfError(self.lib.cf_b200_sealed_attention_static_error().decode(), status)
+        return out
+
     def decode_pages(self, page_ids):
         """Decode whole records to symbols on the GPU: returns (k, v) uint8 [pages, kv_heads, page_tokens*head_dim]."""
         ids = torch.as_tensor(np.asarray(page_ids, np.int32), device=self.device)

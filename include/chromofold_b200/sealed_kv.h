@@ -131,6 +131,22 @@ cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *de
 cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_attention_desc *desc, uint32_t stages,
                                                 void *stream);
 
+/* The same attention for callers that cannot allocate device memory (an engine that gave the whole heap to its
+ * own arena, a plugin inside another framework's budget, a serving thread where allocator calls are banned).
+ * This entry point has no counterpart in the reference. It takes the descriptor of
+ * cf_b200_sealed_attention_async, ignores `workspace` / `workspace_bytes`, and uses a fixed array inside the
+ * library image instead: CF_B200_STATIC_WORKSPACE_BYTES per GPU that loads the library, held until exit.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine.
+ *   - A batch whose partials cannot fit (seq_count x local query heads x (head_dim + 2) floats, one chunk per
+ *     sequence at least) is rejected with CF_ERR_UNSUPPORTED; cf_b200_sealed_attention_static_error() says why.
+ *     Larger contexts are fine: chunks grow to fit the array.
+ *   - The first call on a device looks up the array's device address; make that call outside any stream capture.
+ *   - All calls on a device share the array. Calls that overlap on the GPU race; order them on one stream or with
+ *     events. Nothing has to be cleared between calls: each call rewrites what it reads. */
+#define CF_B200_STATIC_WORKSPACE_BYTES (8u << 20)
+cf_status cf_b200_sealed_attention_static_async(const cf_b200_sealed_attention_desc *desc, void *stream);
+const char *cf_b200_sealed_attention_static_error(void);
+
 /* --------------------------------------------------------------------------------------------------
  * Codebooks. Built on the host from symbol histograms (set-up work, not query path).
  * Normalisation rule for rANS (M = 4096, every symbol codable):
