@@ -32,6 +32,7 @@ def build(force=False, verbose=False):
            "-Xlinker", "-Bsymbolic", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(HERE, "csrc")]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("CFB_NVCC_FLAGS", "").split()  # extra -D switches for tuning experiments
     cmd += sources() + ["-o", LIB]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:

@@ -20,8 +20,10 @@ struct AttentionParams {
     uint32_t page_table_stride, seq_count;
     const cf_b200_codebook_tables *k_tables, *v_tables;
     // tails
-    const __half *tail_k, *tail_v;
+    const void *tail_k, *tail_v;
     const uint32_t *tail_tokens;
+    uint32_t tail_type;
+    const uint32_t *query_positions;
     // io
     const void *queries;
     void *output;
@@ -50,6 +52,13 @@ __device__ __forceinline__ float *partial_ptr(const AttentionParams &p, uint32_t
 }
 __device__ __forceinline__ uint32_t slot_of(const AttentionParams &p, uint32_t seq) {
     return p.seq_slots ? p.seq_slots[seq] : seq;
+}
+// Position of the query token of batch entry `seq`: given, or right after everything cached (a decode step).
+__device__ __forceinline__ uint32_t query_position(const AttentionParams &p, uint32_t seq, uint32_t sealed, uint32_t tail) {
+    return p.query_positions ? p.query_positions[seq] : sealed + tail;
+}
+__device__ __forceinline__ float load_tail(const void *base, uint32_t type, uint64_t i) {
+    return type == CF_B200_F32 ? static_cast<const float *>(base)[i] : __half2float(static_cast<const __half *>(base)[i]);
 }
 __device__ __forceinline__ void raise_status(const AttentionParams &p, uint32_t bits) {
     if (p.status) atomicOr(p.status, bits);

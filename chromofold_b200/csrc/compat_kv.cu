@@ -1,0 +1,260 @@
+// compat_kv.cu — the reference's CUDA entry points for this path, re-implemented for sm_100a
+// (declared in include/chromofold_b200/compat_kv.h):
+//   cf_kv_validate_paged_attention_desc / cf_kv_paged_attention_async   (src/cuda/paged_kv_attention.cu:280-327)
+//   cf_rans_decode_async                                                (src/cuda/rans.cu:38-50)
+// The descriptors are the reference's (one 104-byte descriptor per page and kv head, per-page LUTs, K per-channel and
+// V per-token fp32 scales), so this path keeps their cost; the sealed-KV entry points are the fast path.
+
+#include <math_constants.h>
+
+#include "cf_device_common.cuh"
+#include "chromofold_b200/compat_kv.h"
+
+namespace cfb {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr uint32_t kBatchSymbols = 4096;   // symbols of one stream decoded to shared memory at a time
+constexpr uint32_t kMaxGroup = 16;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Decode coded block `b` of a page stream and hand every symbol whose flat index lies in [lo, hi) to `emit`.
+template <class Emit>
+__device__ void decode_block_range(const uint32_t *words, const int32_t *offsets, const int32_t *lut, uint32_t maxlen,
+                                   uint32_t fixed_bits, uint32_t block_size, uint32_t b, uint32_t total, uint32_t lo,
+                                   uint32_t hi, Emit emit) {
+    const uint32_t first = b * block_size;
+    const uint32_t last = min(first + block_size, total);
+    if (fixed_bits) {  // symbol i sits at bit i * fixed_bits, never crossing a word (kv_gpu_fixture.cpp:36-40)
+        const uint32_t mask = (1u << fixed_bits) - 1u;
+        for (uint32_t i = max(first, lo); i < min(last, hi); ++i) {
+            const uint32_t bit = i * fixed_bits;
+            emit(i, (words[bit >> 5] >> ((32u - fixed_bits) - (bit & 31u))) & mask);
+        }
+        return;
+    }
+    uint32_t bit = static_cast<uint32_t>(offsets[b]);
+    for (uint32_t i = first; i < min(last, hi); ++i) {  // block_huffman_device.cuh:12-19, two words at a time
+        const uint32_t w = bit >> 5, off = bit & 31u;
+        uint32_t window = words[w] << off;
+        if (off + maxlen > 32u) window |= words[w + 1] >> (32u - off);
+        const uint32_t entry = static_cast<uint32_t>(lut[window >> (32u - maxlen)]);
+        if (i >= lo) emit(i, entry & 0xffu);
+        bit += entry >> 8;
+    }
+}
+
+struct Smem {
+    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, total;
+};
+__host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, uint32_t batch_tokens) {
+    Smem s;
+    s.off_ksym = 0;
+    s.off_vsym = kBatchSymbols;
+    s.off_q = 2 * kBatchSymbols;
+    s.off_qk = s.off_q + group * head_dim * 4;
+    s.off_acc = s.off_qk + group * head_dim * 4;
+    s.off_scores = s.off_acc + group * head_dim * 4;
+    s.off_ml = s.off_scores + group * batch_tokens * 4;
+    s.total = s.off_ml + group * 8 + 16;
+    return s;
+}
+
+// One block per (query row, kv head): all query heads of the group share every decoded symbol.
+__global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_paged_attention_desc desc,
+                                                                          uint32_t batch_tokens) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t G = desc.gqa_group_size, D = desc.head_dim;
+    const Smem lay = smem_layout(G, D, batch_tokens);
+    uint8_t *ksym = smem + lay.off_ksym;
+    uint8_t *vsym = smem + lay.off_vsym;
+    float *q = reinterpret_cast<float *>(smem + lay.off_q);        // q * softmax_scale * log2(e)
+    float *qk = reinterpret_cast<float *>(smem + lay.off_qk);      // q scaled by the page's per-channel K scales
+    float *acc = reinterpret_cast<float *>(smem + lay.off_acc);
+    float *scores = reinterpret_cast<float *>(smem + lay.off_scores);
+    float *ml = reinterpret_cast<float *>(smem + lay.off_ml);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t query_row = blockIdx.x, kv_head = blockIdx.y;
+    const uint32_t query_token = desc.query_token_begin + query_row;
+    const uint32_t first_token = window_begin(query_token, desc.causal_window);
+
+    for (uint32_t i = tid; i < G * D; i += kThreads) {
+        const uint32_t head = kv_head * G + i / D;
+        q[i] = desc.queries[(static_cast<uint64_t>(query_row) * desc.query_head_count + head) * D + i % D] *
+               (desc.softmax_scale * kLog2e);
+        acc[i] = 0.0f;
+    }
+    if (tid < G) {
+        ml[2 * tid] = -CUDART_INF_F;
+        ml[2 * tid + 1] = 0.0f;
+    }
+    __syncthreads();
+
+    // Online-softmax update from scores[g][0..count) and a value getter; every thread owns channel `tid`.
+    auto update = [&](uint32_t count, auto value_of) {
+        float new_m[kMaxGroup], new_l[kMaxGroup];
+        for (uint32_t g = 0; g < G; ++g) {
+            const float m_old = ml[2 * g], l_old = ml[2 * g + 1];
+            float pm = -CUDART_INF_F;
+            for (uint32_t t = 0; t < count; ++t) pm = fmaxf(pm, scores[g * batch_tokens + t]);
+            const float m_new = fmaxf(m_old, pm);
+            new_m[g] = m_new;
+            new_l[g] = l_old;
+            if (m_new == -CUDART_INF_F) continue;
+            const float alpha = m_old == -CUDART_INF_F ? 0.0f : exp2f(m_old - m_new);
+            float lsum = 0.0f, a = 0.0f;
+            for (uint32_t t = 0; t < count; ++t) {
+                const float s = scores[g * batch_tokens + t];
+                if (s == -CUDART_INF_F) continue;
+                const float w = exp2f(s - m_new);
+                lsum += w;
+                if (tid < D) a += w * value_of(t, tid);
+            }
+            new_l[g] = l_old * alpha + lsum;
+            if (tid < D) acc[g * D + tid] = acc[g * D + tid] * alpha + a;
+        }
+        __syncthreads();
+        if (tid == 0)
+            for (uint32_t g = 0; g < G; ++g) {
+                ml[2 * g] = new_m[g];
+                ml[2 * g + 1] = new_l[g];
+            }
+        __syncthreads();
+    };
+
+    for (uint32_t pi = 0; pi < desc.page_count; ++pi) {
+        const cf_kv_device_page page = desc.pages[pi];
+        if (page.kv_head != kv_head || page.head_dim != D) continue;
+        if (page.token_begin > query_token || page.token_begin + page.token_count <= first_token) continue;
+        const uint32_t total = page.token_count * D;
+        const int zp = static_cast<int>(page.zero_point);
+        for (uint32_t i = tid; i < G * D; i += kThreads) qk[i] = q[i] * page.k_scales[i % D];
+        for (uint32_t t0 = 0; t0 < page.token_count; t0 += batch_tokens) {
+            const uint32_t count = min(batch_tokens, page.token_count - t0);
+            const uint32_t lo = t0 * D, hi = (t0 + count) * D;
+            const uint32_t b_first = lo / page.block_size, b_last = (hi - 1) / page.block_size;
+            __syncthreads();
+            for (uint32_t job = tid; job < 2 * (b_last - b_first + 1); job += kThreads) {
+                const uint32_t b = b_first + (job >> 1);
+                if (job & 1)
+                    decode_block_range(page.v_words, page.v_block_offsets, page.v_lut, page.v_max_code_length,
+                                       page.fixed_code_length, page.block_size, b, total, lo, hi,
+                                       [&](uint32_t i, uint32_t s) { vsym[i - lo] = static_cast<uint8_t>(s); });
+                else
+                    decode_block_range(page.k_words, page.k_block_offsets, page.k_lut, page.k_max_code_length,
+                                       page.fixed_code_length, page.block_size, b, total, lo, hi,
+                                       [&](uint32_t i, uint32_t s) { ksym[i - lo] = static_cast<uint8_t>(s); });
+            }
+            __syncthreads();
+            for (uint32_t pair = warp; pair < G * count; pair += kThreads / 32) {
+                const uint32_t g = pair / count, t = pair % count;
+                const uint32_t token = page.token_begin + t0 + t;
+                float s = -CUDART_INF_F;
+                if (token >= first_token && token <= query_token) {
+                    float dot = 0.0f;
+                    for (uint32_t d = lane; d < D; d += 32)
+                        dot += qk[g * D + d] * static_cast<float>(static_cast<int>(ksym[t * D + d]) - zp);
+                    s = warp_sum(dot);
+                }
+                if (lane == 0) scores[g * batch_tokens + t] = s;
+            }
+            __syncthreads();
+            update(count, [&](uint32_t t, uint32_t d) {
+                return static_cast<float>(static_cast<int>(vsym[t * D + d]) - zp) * page.v_scales[t0 + t];
+            });
+        }
+    }
+
+    // dense fp32 tail [active_token_count][kv_head_count][head_dim] (paged_kv_attention.cu:154-166)
+    for (uint32_t t0 = 0; t0 < desc.active_token_count; t0 += batch_tokens) {
+        const uint32_t count = min(batch_tokens, desc.active_token_count - t0);
+        __syncthreads();
+        for (uint32_t pair = warp; pair < G * count; pair += kThreads / 32) {
+            const uint32_t g = pair / count, t = pair % count;
+            const uint32_t token = desc.active_token_begin + t0 + t;
+            float s = -CUDART_INF_F;
+            if (token >= first_token && token <= query_token) {
+                const float *row = desc.active_k + (static_cast<uint64_t>(t0 + t) * desc.kv_head_count + kv_head) * D;
+                float dot = 0.0f;
+                for (uint32_t d = lane; d < D; d += 32) dot += q[g * D + d] * row[d];
+                s = warp_sum(dot);
+            }
+            if (lane == 0) scores[g * batch_tokens + t] = s;
+        }
+        __syncthreads();
+        update(count, [&](uint32_t t, uint32_t d) {
+            return desc.active_v[(static_cast<uint64_t>(t0 + t) * desc.kv_head_count + kv_head) * D + d];
+        });
+    }
+
+    for (uint32_t i = tid; i < G * D; i += kThreads) {
+        const uint32_t g = i / D;
+        const float l = ml[2 * g + 1];
+        desc.output[(static_cast<uint64_t>(query_row) * desc.query_head_count + kv_head * G + g) * D + i % D] =
+            l > 0.0f ? acc[i] / l : 0.0f;  // no visible token: zeros (paged_kv_attention.cu:170-173)
+    }
+}
+
+// One thread per coded block (rans.cu:28-36), recurrence of rans.cu:20-23.
+__global__ void compat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint32_t *state0,
+                                          const int32_t *slot2sym, const int32_t *freq, const int32_t *cum, int block,
+                                          int n, int32_t *out) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    const long long base = static_cast<long long>(b) * block;
+    if (base >= n) return;
+    const int count = static_cast<int>(min(static_cast<long long>(block), n - base));
+    uint32_t x = state0[b];
+    const uint8_t *bytes = data + byte_off[b];
+    for (int j = 0; j < count; ++j) {
+        const uint32_t slot = x & (CF_B200_RANS_M - 1u);
+        const int s = __ldg(slot2sym + slot);
+        x = static_cast<uint32_t>(__ldg(freq + s)) * (x >> CF_B200_RANS_PROB_BITS) + slot - static_cast<uint32_t>(__ldg(cum + s));
+        while (x < kRansL) x = (x << 8) | *bytes++;
+        out[base + j] = s;
+    }
+}
+
+bool finite_float(float v) { return v == v && v - v == 0.0f; }
+
+}  // namespace
+}  // namespace cfb
+
+extern "C" cf_status cf_kv_validate_paged_attention_desc(const cf_kv_paged_attention_desc *d) {
+    if (!d || d->struct_size != sizeof(cf_kv_paged_attention_desc) || d->abi_version != CF_KV_CUDA_ABI_VERSION ||
+        !d->queries || !d->output || d->query_count == 0 || d->query_head_count == 0 || d->kv_head_count == 0 ||
+        d->gqa_group_size == 0 || d->head_dim == 0 || d->head_dim > CF_KV_MAX_HEAD_DIM || !cfb::finite_float(d->softmax_scale))
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->query_head_count != d->kv_head_count * d->gqa_group_size || d->page_count > CF_KV_CUDA_MAX_PAGES_PER_LAUNCH ||
+        (d->page_count != 0 && !d->pages) || (d->active_token_count != 0 && (!d->active_k || !d->active_v)))
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->query_token_begin > UINT32_MAX - d->query_count || d->active_token_begin > UINT32_MAX - d->active_token_count)
+        return CF_ERR_INVALID_ARGUMENT;
+    return CF_OK;
+}
+
+extern "C" cf_status cf_kv_paged_attention_async(const cf_kv_paged_attention_desc *d, void *stream) {
+    const cf_status valid = cf_kv_validate_paged_attention_desc(d);
+    if (valid != CF_OK) return valid;
+    if (d->gqa_group_size > cfb::kMaxGroup) return CF_ERR_UNSUPPORTED;
+    const uint32_t batch_tokens = cfb::kBatchSymbols / d->head_dim;
+    const cfb::Smem lay = cfb::smem_layout(d->gqa_group_size, d->head_dim, batch_tokens);
+    if (cudaFuncSetAttribute(cfb::compat_paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(lay.total)) != cudaSuccess)
+        return CF_ERR_CUDA;
+    cfb::compat_paged_attention_kernel<<<dim3(d->query_count, d->kv_head_count), cfb::kThreads, lay.total,
+                                         static_cast<cudaStream_t>(stream)>>>(*d, batch_tokens);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}
+
+extern "C" cf_status cf_rans_decode_async(const uint8_t *data, const int32_t *byte_off, const uint32_t *state0,
+                                          const int32_t *slot2sym, const int32_t *freq, const int32_t *cum, int block,
+                                          int n, int32_t *out, void *stream) {
+    if (!data || !byte_off || !state0 || !slot2sym || !freq || !cum || !out) return CF_ERR_INVALID_ARGUMENT;
+    if (block <= 0 || n < 0) return CF_ERR_INVALID_ARGUMENT;
+    if (n == 0) return CF_OK;
+    const int blocks = (n + block - 1) / block;
+    cfb::compat_rans_decode_kernel<<<(blocks + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        data, byte_off, state0, slot2sym, freq, cum, block, n, out);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}

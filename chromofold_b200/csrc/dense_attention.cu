@@ -98,8 +98,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_attention_kernel(AttentionP
         const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
         const uint32_t slot = slot_of(p, seq);
         const uint32_t sealed = p.seq_sealed_tokens[slot];
-        const uint32_t first_token = window_begin(sealed, p.causal_window);
-        const uint32_t pages = (sealed + 15u) / 16u;
+        const uint32_t qpos = query_position(p, seq, sealed, 0u);
+        const uint32_t first_token = window_begin(qpos, p.causal_window);
+        const uint32_t pages = min((sealed + 15u) / 16u, qpos / 16u + 1u);
         const uint32_t first_page = min(first_token / 16u, pages);
         const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
         const uint32_t page_end = min(page_begin + pages_per_unit, pages);
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_attention_kernel(AttentionP
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const uint32_t token = (page_begin + i) * 16u + 8u * (e >> 1) + 2u * t + (e & 1);
-                const bool visible = token >= first_token && token < sealed;
+                const bool visible = token >= first_token && token < sealed && token <= qpos;
                 sv[e] = visible ? s[e >> 1][e & 1] * scale : -CUDART_INF_F;
                 mx = fmaxf(mx, sv[e]);
             }

@@ -35,8 +35,9 @@ __host__ __device__ inline SealSmem seal_smem(uint32_t symbols, uint32_t nblocks
 struct SealParams {
     uint32_t kv_head_count, head_dim, page_tokens, block_size, coder, codebook_id, symbols, nblocks;
     const cf_b200_codebook_tables *k_tables, *v_tables;
-    const __half *tail_k, *tail_v;
-    const uint32_t *job_slots, *job_pages, *job_tokens;
+    const void *tail_k, *tail_v;
+    uint32_t tail_type;
+    const uint32_t *job_slots, *job_pages, *job_tokens, *job_heads;
     uint8_t *arena;
     uint64_t arena_units;
     unsigned long long *cursor;
@@ -59,11 +60,15 @@ __device__ __forceinline__ uint32_t quantise_symbol(float x, float scale) {
 }
 
 // Block-wide absmax and non-finite flag over `count` binary16 values.
-__device__ float tile_absmax(const __half *tile, uint32_t count, int *nonfinite, float *red) {
+__device__ __forceinline__ float tile_value(const void *base, uint32_t type, uint64_t i) {
+    return type == CF_B200_F32 ? static_cast<const float *>(base)[i] : __half2float(static_cast<const __half *>(base)[i]);
+}
+
+__device__ float tile_absmax(const void *base, uint32_t type, uint64_t tile, uint32_t count, int *nonfinite, float *red) {
     float m = 0.0f;
     int bad = 0;
     for (uint32_t i = threadIdx.x; i < count; i += kSealThreads) {
-        const float x = __half2float(tile[i]);
+        const float x = tile_value(base, type, tile + i);
         if (!isfinite(x)) bad = 1;
         else m = fmaxf(m, fabsf(x));
     }
@@ -196,16 +201,15 @@ __device__ uint32_t encode_stream(const SealParams &p, const SealSmem &lay, cons
     return part_bytes;
 }
 
-__device__ __forceinline__ void quantise_tiles(const SealParams &p, const __half *k_tile, const __half *v_tile,
-                                               uint32_t rows, float k_scale, float v_scale, uint8_t *ksym,
-                                               uint8_t *vsym) {
+__device__ __forceinline__ void quantise_tiles(const SealParams &p, uint64_t tile, uint32_t rows, float k_scale,
+                                               float v_scale, uint8_t *ksym, uint8_t *vsym) {
     const uint32_t D = p.head_dim, T = p.page_tokens;
     for (uint32_t i = threadIdx.x; i < p.symbols; i += kSealThreads) {
         const uint32_t t = i / D, d = i % D;
         uint32_t ks = kZero, vs = kZero;
         if (t < rows) {
-            ks = quantise_symbol(__half2float(k_tile[i]), k_scale);
-            vs = quantise_symbol(__half2float(v_tile[i]), v_scale);
+            ks = quantise_symbol(tile_value(p.tail_k, p.tail_type, tile + i), k_scale);
+            vs = quantise_symbol(tile_value(p.tail_v, p.tail_type, tile + i), v_scale);
         }
         ksym[i] = static_cast<uint8_t>(ks);          // K order: token-major
         vsym[d * T + t] = static_cast<uint8_t>(vs);  // V order: token-minor
@@ -227,23 +231,22 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     uint32_t *blk_off = blk_len + p.nblocks;
     uint32_t *blk_state = blk_off + p.nblocks;
 
-    const uint32_t job = blockIdx.x, kv_head = blockIdx.y, tid = threadIdx.x;
+    const uint32_t job = blockIdx.x, tid = threadIdx.x;
+    const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
     const uint32_t slot = p.job_slots[job];
     const uint32_t rows = p.job_tokens ? min(p.job_tokens[job], p.page_tokens) : p.page_tokens;
     const uint64_t tile = (static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.symbols;
-    const __half *k_tile = p.tail_k + tile;
-    const __half *v_tile = p.tail_v + tile;
 
     int k_bad, v_bad;
-    const float k_max = tile_absmax(k_tile, rows * p.head_dim, &k_bad, red);
-    const float v_max = tile_absmax(v_tile, rows * p.head_dim, &v_bad, red);
+    const float k_max = tile_absmax(p.tail_k, p.tail_type, tile, rows * p.head_dim, &k_bad, red);
+    const float v_max = tile_absmax(p.tail_v, p.tail_type, tile, rows * p.head_dim, &v_bad, red);
     if (rows == 0 || k_bad || v_bad) {  // finite validation failed: nothing is published
         if (tid == 0 && p.status) atomicOr(p.status, CF_B200_DEVSTAT_NONFINITE);
         return;
     }
     const uint16_t k_bits = scale_bits_from_absmax(k_max), v_bits = scale_bits_from_absmax(v_max);
-    quantise_tiles(p, k_tile, v_tile, rows, __half2float(__ushort_as_half(k_bits)),
-                   __half2float(__ushort_as_half(v_bits)), ksym, vsym);
+    quantise_tiles(p, tile, rows, __half2float(__ushort_as_half(k_bits)), __half2float(__ushort_as_half(v_bits)), ksym,
+                   vsym);
     for (uint32_t i = tid; i < 2u * lay.part_capacity / 4u; i += kSealThreads) reinterpret_cast<uint32_t *>(k_part)[i] = 0u;
     __syncthreads();
 
@@ -290,22 +293,21 @@ __global__ void __launch_bounds__(kSealThreads) histogram_kernel(SealParams p, u
                                                                  unsigned long long *hist_v) {
     __shared__ float red[8];
     __shared__ uint32_t hk[256], hv[256];
-    const uint32_t job = blockIdx.x, kv_head = blockIdx.y, tid = threadIdx.x;
+    const uint32_t job = blockIdx.x, tid = threadIdx.x;
+    const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
     const uint32_t slot = p.job_slots[job];
     const uint32_t rows = p.job_tokens ? min(p.job_tokens[job], p.page_tokens) : p.page_tokens;
     const uint64_t tile = (static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.symbols;
-    const __half *k_tile = p.tail_k + tile;
-    const __half *v_tile = p.tail_v + tile;
     for (uint32_t i = tid; i < 256; i += kSealThreads) hk[i] = hv[i] = 0;
     int k_bad, v_bad;
-    const float k_max = tile_absmax(k_tile, rows * p.head_dim, &k_bad, red);
-    const float v_max = tile_absmax(v_tile, rows * p.head_dim, &v_bad, red);
+    const float k_max = tile_absmax(p.tail_k, p.tail_type, tile, rows * p.head_dim, &k_bad, red);
+    const float v_max = tile_absmax(p.tail_v, p.tail_type, tile, rows * p.head_dim, &v_bad, red);
     if (rows == 0 || k_bad || v_bad) return;
     const float ks = __half2float(__ushort_as_half(scale_bits_from_absmax(k_max)));
     const float vs = __half2float(__ushort_as_half(scale_bits_from_absmax(v_max)));
     for (uint32_t i = tid; i < rows * p.head_dim; i += kSealThreads) {
-        atomicAdd(&hk[quantise_symbol(__half2float(k_tile[i]), ks)], 1u);
-        atomicAdd(&hv[quantise_symbol(__half2float(v_tile[i]), vs)], 1u);
+        atomicAdd(&hk[quantise_symbol(tile_value(p.tail_k, p.tail_type, tile + i), ks)], 1u);
+        atomicAdd(&hv[quantise_symbol(tile_value(p.tail_v, p.tail_type, tile + i), vs)], 1u);
     }
     __syncthreads();
     for (uint32_t i = tid; i < 256; i += kSealThreads) {
@@ -325,11 +327,13 @@ void fill(const cf_b200_seal_desc *d, SealParams *p) {
     p->nblocks = (p->symbols + d->block_size - 1) / d->block_size;
     p->k_tables = d->k_tables;
     p->v_tables = d->v_tables;
-    p->tail_k = static_cast<const __half *>(d->tail_k);
-    p->tail_v = static_cast<const __half *>(d->tail_v);
+    p->tail_k = d->tail_k;
+    p->tail_v = d->tail_v;
+    p->tail_type = d->tail_type == CF_B200_F32 ? CF_B200_F32 : CF_B200_F16;
     p->job_slots = d->job_slots;
     p->job_pages = d->job_pages;
     p->job_tokens = d->job_tokens;
+    p->job_heads = d->job_heads;
     p->arena = d->arena;
     p->arena_units = d->arena_units;
     p->cursor = d->arena_cursor_units;
@@ -373,7 +377,7 @@ extern "C" cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *d, void *
     if (cudaFuncSetAttribute(cfb::seal_pages_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(lay.total)) != cudaSuccess)
         return CF_ERR_CUDA;
-    cfb::seal_pages_kernel<<<dim3(d->job_count, d->kv_head_count), cfb::kSealThreads, lay.total,
+    cfb::seal_pages_kernel<<<dim3(d->job_count, d->job_heads ? 1u : d->kv_head_count), cfb::kSealThreads, lay.total,
                              static_cast<cudaStream_t>(stream)>>>(p);
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }
@@ -386,7 +390,7 @@ extern "C" cf_status cf_b200_histogram_async(const cf_b200_seal_desc *d, unsigne
     if (d->job_count == 0) return CF_OK;
     cfb::SealParams p;
     cfb::fill(d, &p);
-    cfb::histogram_kernel<<<dim3(d->job_count, d->kv_head_count), cfb::kSealThreads, 0,
+    cfb::histogram_kernel<<<dim3(d->job_count, d->job_heads ? 1u : d->kv_head_count), cfb::kSealThreads, 0,
                             static_cast<cudaStream_t>(stream)>>>(p, hist_k, hist_v);
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }

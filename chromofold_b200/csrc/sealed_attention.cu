@@ -27,8 +27,9 @@ __device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint
     const uint32_t slot = slot_of(p, seq);
     const uint32_t sealed = p.seq_sealed_tokens[slot];
     const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
-    const uint32_t pages = (sealed + p.page_tokens - 1u) / p.page_tokens;
-    const uint32_t first = min(window_begin(sealed + tail, p.causal_window) / p.page_tokens, pages);
+    const uint32_t qpos = query_position(p, seq, sealed, tail);
+    const uint32_t pages = min((sealed + p.page_tokens - 1u) / p.page_tokens, qpos / p.page_tokens + 1u);
+    const uint32_t first = min(window_begin(qpos, p.causal_window) / p.page_tokens, pages);
     if (first_page) *first_page = first;
     return pages - first;
 }
@@ -148,7 +149,8 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
         const uint32_t slot = slot_of(p, seq);
         const uint32_t sealed = p.seq_sealed_tokens[slot];
         const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
-        const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
+        const uint32_t qpos = query_position(p, seq, sealed, tail);
+        const uint32_t first_token = window_begin(qpos, p.causal_window);
         uint32_t first_page;
         const uint32_t vis = visible_pages(p, seq, &first_page);
         const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
                 const uint32_t g = pair / T, t = pair % T;
                 const uint32_t token = page * T + t;
                 float s = -CUDART_INF_F;
-                if (t < h.token_count && token >= first_token && token < sealed) {
+                if (t < h.token_count && token >= first_token && token < sealed && token <= qpos) {
                     float dot = 0.0f;
                     for (uint32_t d = lane; d < D; d += 32)
                         dot += q[g * D + d] * static_cast<float>(static_cast<int>(ksym[t * D + d]) - kZero);
@@ -273,17 +275,19 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
     const uint32_t slot = slot_of(p, seq);
     const uint32_t sealed = p.seq_sealed_tokens[slot];
     const uint32_t tail = p.tail_tokens ? min(p.tail_tokens[slot], T) : 0u;
-    const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
+    const uint32_t qpos = query_position(p, seq, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
+    const uint32_t first_token = window_begin(qpos, p.causal_window);
     const uint32_t *prefix = chunk_prefix(p);
     const uint32_t c0 = prefix[seq], c1 = prefix[seq + 1];
 
     // tail scores (binary16 rows, one warp per token)
     for (uint32_t t = warp; t < tail; t += kCombineThreads / 32) {
-        const __half *row = p.tail_k + ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D;
+        const uint64_t row = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D;
         float dot = 0.0f;
-        for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, seq, q_head, d) * __half2float(row[d]);
+        for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, seq, q_head, d) * load_tail(p.tail_k, p.tail_type, row + d);
         dot = warp_sum(dot);
-        if (lane == 0) tail_scores[t] = (sealed + t >= first_token) ? dot * p.softmax_scale * kLog2e : -CUDART_INF_F;
+        if (lane == 0)
+            tail_scores[t] = (sealed + t >= first_token && sealed + t <= qpos) ? dot * p.softmax_scale * kLog2e : -CUDART_INF_F;
     }
     __syncthreads();
 
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
             const float w = exp2f(s - m);
             l += w;
             if (tid < D)
-                a += w * __half2float(p.tail_v[((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D + tid]);
+                a += w * load_tail(p.tail_v, p.tail_type, ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D + tid);
         }
     }
     if (tid < D) {
@@ -379,9 +383,11 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->seq_count = d->seq_count;
     p->k_tables = d->k_tables;
     p->v_tables = d->v_tables;
-    p->tail_k = static_cast<const __half *>(d->tail_k);
-    p->tail_v = static_cast<const __half *>(d->tail_v);
+    p->tail_k = d->tail_k;
+    p->tail_v = d->tail_v;
     p->tail_tokens = d->tail_tokens;
+    p->tail_type = d->tail_type == CF_B200_F32 ? CF_B200_F32 : CF_B200_F16;
+    p->query_positions = d->query_positions;
     p->queries = d->queries;
     p->output = d->output;
     p->query_type = d->query_type;
@@ -447,7 +453,8 @@ extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_atte
         return CF_ERR_INVALID_ARGUMENT;
     if (d->tail_tokens != nullptr && (d->tail_k == nullptr || d->tail_v == nullptr)) return CF_ERR_INVALID_ARGUMENT;
     if ((d->query_type != CF_B200_F16 && d->query_type != CF_B200_F32) ||
-        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_LANES)
+        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_LANES ||
+        (d->tail_type != 0 && d->tail_type != CF_B200_F16 && d->tail_type != CF_B200_F32))
         return CF_ERR_INVALID_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(d->arena) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->workspace) & 255u) != 0)
         return CF_ERR_INVALID_ARGUMENT;

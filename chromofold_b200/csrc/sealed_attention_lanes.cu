@@ -26,9 +26,12 @@
 namespace cfb {
 namespace {
 
-constexpr int kWarps = 16;
+#ifndef CFB_LANES_WARPS
+#define CFB_LANES_WARPS 16
+#endif
+constexpr int kWarps = CFB_LANES_WARPS;
 constexpr int kThreads = kWarps * 32;
-constexpr uint32_t kStageBytes = 4224;   // 16 header + 2 * 2048 payload max + slack, multiple of 128
+constexpr uint32_t kStageBytes = 4160;   // 16 header + 2 * 2048 payload max + 48 slack (decoders read ahead)
 constexpr uint32_t kScratchBytes = 512;  // P rows, high and low halves (2 x 4 heads x 16 tokens x 2 B) + alpha[4]
 constexpr uint32_t kWarpBytes = 2 * kStageBytes + kScratchBytes + 128;  // + 2 mbarriers (padded)
 constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
@@ -308,8 +311,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         const uint32_t slot = slot_of(p, seq);
         const uint32_t sealed = p.seq_sealed_tokens[slot];
         const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
-        const uint32_t first_token = window_begin(sealed + tail, p.causal_window);
-        const uint32_t pages = (sealed + 15u) / 16u;
+        const uint32_t qpos = query_position(p, seq, sealed, tail);
+        const uint32_t first_token = window_begin(qpos, p.causal_window);
+        const uint32_t pages = min((sealed + 15u) / 16u, qpos / 16u + 1u);
         const uint32_t first_page = min(first_token / 16u, pages);
         const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
         const uint32_t page_end = min(page_begin + pages_per_unit, pages);
@@ -347,14 +351,14 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         };
         auto issue = [&](uint32_t st, uint64_t entry) {
             const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
-            if (lane == 0 && units16 != 0 && units16 * 16u <= kStageBytes - 64u) {
+            if (lane == 0 && units16 != 0 && units16 * 16u <= kStageBytes - 32u) {
                 mbar_expect_tx(&bars[st], units16 * 16u);
                 bulk_load(warp_mem + st * kStageBytes, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
             }
         };
         auto entry_ok = [&](uint64_t entry) {
             const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
-            return units16 != 0 && units16 * 16u <= kStageBytes - 64u;
+            return units16 != 0 && units16 * 16u <= kStageBytes - 32u;
         };
 
         uint64_t entry_cur = n_pages ? load_entry(page_begin) : 0ull;
@@ -425,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
                     // ---- online softmax for this page (fp32) ----
                     const uint32_t token = (page_begin + i) * 16u + my_token;
-                    const bool visible = my_token < token_count && token >= first_token && token < sealed;
+                    const bool visible = my_token < token_count && token >= first_token && token < sealed && token <= qpos;
                     const float s0 = visible ? u.score[0] * k_scale : -CUDART_INF_F;
                     const float s1 = visible ? u.score[1] * k_scale : -CUDART_INF_F;
                     float r0 = s0, r1 = s1;

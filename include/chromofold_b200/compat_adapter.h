@@ -1,0 +1,85 @@
+/* compat_adapter.h — the llama.cpp-facing KV adapter, same symbols and struct layouts as the reference's
+ * integrations/llama.cpp/chromofold_kv_adapter.h:13-89, served by the sealed-KV path of this library.
+ *
+ * A caller compiled against the reference header links against this library unchanged: every function below has
+ * the reference's name, argument list and return convention (0 / -1 and a last_error string owned by the handle,
+ * exceptions never cross the boundary — chromofold_kv_adapter.cpp:35-49).
+ *
+ * What is kept: one sequence (id 0) per adapter (src/runtime/compressed_kv_cache.cu:180-193); append takes HOST fp32
+ * rows per (layer, kv head) and must be logically contiguous (:78-80); full pages seal on append (:87), flush seals
+ * the partial tail (:111-125); attention takes DEVICE fp32 queries [query_count][Hq][head_dim], query row i sits at
+ * token query_token_begin + i and sees tokens <= its position inside the causal window
+ * (src/cuda/paged_kv_attention.cu:48-52,67-69); all kv heads must hold the same tokens when attention runs
+ * (compressed_kv_cache.cu:152-154).
+ * What differs: pages are quantised to int8 with one fp16 scale per stream and entropy coded (format v1) on the GPU,
+ * whatever kv_bits says (kv_bits selects 4-/8-bit fixed-width pages in the reference, chromofold_kv_adapter.cpp:30-31);
+ * physically a reference page of page_size tokens is stored as page_size / T records of T tokens with
+ * T * head_dim <= 4096; statistics are reported in the reference's units.
+ * Environment: CHROMOFOLD_B200_CODER = rans (default) | huffman | fixed8. */
+#ifndef CHROMOFOLD_B200_COMPAT_ADAPTER_H
+#define CHROMOFOLD_B200_COMPAT_ADAPTER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef CHROMOFOLD_LLAMA_KV_ADAPTER_H /* the reference header declares the same types */
+typedef enum cf_llama_kv_backend {
+    CF_LLAMA_KV_BACKEND_DENSE = 0,
+    CF_LLAMA_KV_BACKEND_CHROMOFOLD = 1,
+} cf_llama_kv_backend;
+
+typedef struct cf_llama_kv_options { /* chromofold_kv_adapter.h:18-28 */
+    uint32_t struct_size;
+    cf_llama_kv_backend backend;
+    uint32_t layer_count;
+    uint32_t kv_head_count;
+    uint32_t query_head_count;
+    uint32_t head_dim;
+    uint32_t page_size;
+    uint32_t gqa_group_size;
+    uint32_t kv_bits;
+} cf_llama_kv_options;
+
+typedef struct cf_llama_kv_stats { /* chromofold_kv_adapter.h:30-38 */
+    uint64_t appended_tokens;
+    uint64_t sealed_tokens;
+    uint64_t sealed_pages;
+    uint64_t active_tokens;
+    uint64_t dense_active_bytes;
+    uint64_t compressed_bytes;
+    uint64_t descriptor_bytes;
+} cf_llama_kv_stats;
+
+typedef struct cf_llama_kv_adapter cf_llama_kv_adapter;
+#endif
+
+int cf_llama_kv_options_validate(const cf_llama_kv_options *options);                 /* :42 */
+cf_llama_kv_adapter *cf_llama_kv_create(const cf_llama_kv_options *options);          /* :43 */
+void cf_llama_kv_destroy(cf_llama_kv_adapter *adapter);                               /* :44 */
+int cf_llama_kv_append(cf_llama_kv_adapter *adapter, uint32_t layer, uint32_t kv_head, uint32_t token_begin,
+                       const float *keys, const float *values, uint32_t token_count, void *stream); /* :46-53 */
+int cf_llama_kv_attention(cf_llama_kv_adapter *adapter, uint32_t layer, const float *queries_device,
+                          float *output_device, uint32_t query_count, uint32_t query_head_count,
+                          uint32_t gqa_group_size, uint32_t query_token_begin, float softmax_scale,
+                          uint32_t causal_window, void *stream);                       /* :58-68 */
+int cf_llama_kv_attention_host(cf_llama_kv_adapter *adapter, uint32_t layer, const float *queries_host,
+                               float *output_host, uint32_t query_count, uint32_t query_head_count,
+                               uint32_t gqa_group_size, uint32_t query_token_begin, float softmax_scale,
+                               uint32_t causal_window, void *stream);                  /* :72-82 */
+int cf_llama_kv_flush(cf_llama_kv_adapter *adapter, void *stream);                    /* :84 */
+int cf_llama_kv_seq_rm(cf_llama_kv_adapter *adapter, uint64_t sequence_id);           /* :85 */
+int cf_llama_kv_seq_cp(cf_llama_kv_adapter *adapter, uint64_t source_id, uint64_t destination_id); /* :86 */
+int cf_llama_kv_seq_shift(cf_llama_kv_adapter *adapter, uint64_t sequence_id, int32_t delta);      /* :87 */
+int cf_llama_kv_clear(cf_llama_kv_adapter *adapter);                                  /* :88 */
+int cf_llama_kv_get_stats(const cf_llama_kv_adapter *adapter, cf_llama_kv_stats *stats); /* :89 */
+const char *cf_llama_kv_last_error(const cf_llama_kv_adapter *adapter);               /* :91 */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

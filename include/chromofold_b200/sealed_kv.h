@@ -82,7 +82,7 @@ typedef struct cf_b200_sealed_attention_desc {
     const cf_b200_codebook_tables *k_tables;
     const cf_b200_codebook_tables *v_tables;
 
-    const void *tail_k;                  /* binary16 [slot][kv_head_count][page_tokens][head_dim], may be NULL */
+    const void *tail_k;                  /* [slot][kv_head_count][page_tokens][head_dim] of tail_type, may be NULL */
     const void *tail_v;
     const uint32_t *tail_tokens;         /* [slot], NULL = no tails */
 
@@ -98,7 +98,12 @@ typedef struct cf_b200_sealed_attention_desc {
     uint32_t min_pages_per_unit;         /* 0 = default (16) */
     uint32_t kernel;                     /* CF_B200_KERNEL_* */
     uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
+    uint32_t tail_type;                  /* CF_B200_F16 (0 means F16 too) or CF_B200_F32: element type of the tails */
     uint32_t reserved;
+    /* Optional [seq_count]: position of each batch entry's query token. NULL = sealed + tail tokens (a decode
+     * step). A smaller position hides the tokens after it (paged_kv_attention.cu:67-69), so several entries may
+     * name the same slot with different positions: that is multi-query (prefill) attention over one sequence. */
+    const uint32_t *query_positions;
 } cf_b200_sealed_attention_desc;
 
 #define CF_B200_KERNEL_AUTO 0u     /* lane-per-block tensor-core kernel when the geometry allows, else generic */
@@ -183,8 +188,9 @@ typedef struct cf_b200_seal_desc {
     const uint32_t *job_slots;    /* [job_count] */
     const uint32_t *job_pages;    /* [job_count] page ids to publish */
     const uint32_t *job_tokens;   /* [job_count] valid rows, NULL = page_tokens */
+    const uint32_t *job_heads;    /* [job_count] kv head of each job; NULL = every job seals all kv heads */
     uint32_t job_count;
-    uint32_t reserved;
+    uint32_t tail_type;           /* CF_B200_F16 (0 means F16 too) or CF_B200_F32 */
     uint8_t *arena;
     uint64_t arena_units;                     /* capacity in 16-byte units */
     unsigned long long *arena_cursor_units;   /* device counter, next free unit */

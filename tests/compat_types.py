@@ -1,0 +1,59 @@
+"""ctypes mirrors of the reference structs this library is layout-compatible with (include/chromofold_b200/compat_*.h)."""
+import ctypes as C
+
+_u32, _u64, _vp, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_float
+
+
+class SoftmaxState(C.Structure):
+    _fields_ = [("max_score", C.c_double), ("exp_sum", C.c_double), ("weighted_values", C.POINTER(C.c_double)),
+                ("dim", _u32), ("initialized", _u32)]
+
+
+class PageView(C.Structure):
+    _fields_ = [(n, _u32) for n in ("struct_size", "abi_version", "flags", "layer", "kv_head", "token_begin", "token_count",
+                                    "head_dim", "block_size", "zero_point")] + [
+        ("k_words", _vp), ("k_word_count", _u64), ("k_block_offsets", _vp), ("k_block_count", _u64),
+        ("k_lut", _vp), ("k_lut_count", _u64), ("k_scales", _vp), ("k_scale_count", _u64),
+        ("v_words", _vp), ("v_word_count", _u64), ("v_block_offsets", _vp), ("v_block_count", _u64),
+        ("v_lut", _vp), ("v_lut_count", _u64), ("v_scales", _vp), ("v_scale_count", _u64)]
+
+
+class CacheLayout(C.Structure):
+    _fields_ = [(n, _u32) for n in ("struct_size", "abi_version", "layer_count", "kv_head_count", "head_dim",
+                                    "page_capacity_tokens", "active_token_begin", "active_token_count",
+                                    "active_element_bytes", "reserved")] + [
+        ("pages", C.POINTER(PageView)), ("page_count", _u64), ("active_k_bytes", _u64), ("active_v_bytes", _u64)]
+
+
+class MemoryStats(C.Structure):
+    _fields_ = [(n, _u64) for n in ("sealed_payload_bytes", "sealed_descriptor_bytes", "active_payload_bytes",
+                                    "total_resident_bytes", "sealed_tokens", "active_tokens", "page_count")]
+
+
+class DevicePage(C.Structure):
+    _fields_ = [(n, _vp) for n in ("k_words", "k_block_offsets", "k_lut", "k_scales", "v_words", "v_block_offsets",
+                                   "v_lut", "v_scales")] + [
+        (n, _u32) for n in ("token_begin", "token_count", "head_dim", "block_size", "k_max_code_length",
+                            "v_max_code_length", "zero_point", "kv_head", "fixed_code_length")]
+
+
+class PagedAttentionDesc(C.Structure):
+    _fields_ = [("struct_size", _u32), ("abi_version", _u32), ("pages", _vp), ("page_count", _u32),
+                ("kv_head_count", _u32), ("query_head_count", _u32), ("gqa_group_size", _u32), ("active_k", _vp),
+                ("active_v", _vp), ("active_token_begin", _u32), ("active_token_count", _u32), ("queries", _vp),
+                ("output", _vp), ("query_token_begin", _u32), ("query_count", _u32), ("head_dim", _u32),
+                ("causal_window", _u32), ("softmax_scale", _f32)]
+
+
+class LlamaKvOptions(C.Structure):
+    _fields_ = [(n, _u32) for n in ("struct_size", "backend", "layer_count", "kv_head_count", "query_head_count",
+                                    "head_dim", "page_size", "gqa_group_size", "kv_bits")]
+
+
+class LlamaKvStats(C.Structure):
+    _fields_ = [(n, _u64) for n in ("appended_tokens", "sealed_tokens", "sealed_pages", "active_tokens",
+                                    "dense_active_bytes", "compressed_bytes", "descriptor_bytes")]
+
+
+assert C.sizeof(PageView) == 168 and C.sizeof(CacheLayout) == 72 and C.sizeof(DevicePage) == 104
+assert C.sizeof(PagedAttentionDesc) == 96 and C.sizeof(SoftmaxState) == 32

@@ -1,0 +1,137 @@
+"""Host-side functions of the reference ABI re-implemented by this library (compat_kv.h, compat_adapter.h): the cases
+of the reference's tests/kv_runtime_test.cpp and tests/llama_kv_adapter_seam.cpp, plus the golden vectors made from the
+reference's own cf_online_softmax_* (tests/golden/online_softmax.npz). No GPU is touched."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from compat_types import CacheLayout, LlamaKvOptions, MemoryStats, PageView, SoftmaxState
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FAKE = [0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 0x7000, 0x8000]   # never dereferenced (kv_runtime_test.cpp:12-17)
+
+
+def _page(token_begin=0, tokens=4, dim=8, layer=0, head=0):
+    p = PageView()
+    p.struct_size, p.abi_version, p.flags = C.sizeof(PageView), 0, 0x3
+    p.layer, p.kv_head, p.token_begin, p.token_count, p.head_dim, p.block_size, p.zero_point = layer, head, token_begin, tokens, dim, 64, 8
+    p.k_words, p.k_word_count, p.v_words, p.v_word_count = FAKE[0], 5, FAKE[1], 6
+    p.k_block_offsets, p.k_block_count, p.v_block_offsets, p.v_block_count = FAKE[2], 1, FAKE[3], 1
+    p.k_lut, p.k_lut_count, p.v_lut, p.v_lut_count = FAKE[4], 16, FAKE[5], 16
+    p.k_scales, p.k_scale_count, p.v_scales, p.v_scale_count = FAKE[6], dim, FAKE[7], tokens
+    return p
+
+
+def test_page_validation_and_exact_byte_accounting(native):
+    lib = native.lib()
+    p = _page()
+    assert lib.cf_kv_validate_page(C.byref(p)) == 0
+    n = C.c_uint64(0)
+    assert lib.cf_kv_page_resident_bytes(C.byref(p), C.byref(n)) == 0
+    assert n.value == (5 + 6) * 4 + (1 + 1 + 16 + 16) * 4 + (8 + 4) * 4       # kv_runtime_test.cpp:49-68
+    assert lib.cf_kv_validate_page(None) == 1
+    for field, value in [("struct_size", 4), ("abi_version", 9), ("flags", 0x2), ("token_count", 0), ("head_dim", 129),
+                         ("block_size", 0), ("k_words", None), ("k_word_count", 0), ("k_scale_count", 7),
+                         ("v_scale_count", 5), ("k_block_count", 0)]:
+        bad = _page()
+        setattr(bad, field, value)
+        assert lib.cf_kv_validate_page(C.byref(bad)) == 1, field
+    bad = _page(token_begin=0xFFFFFFFE, tokens=4)
+    assert lib.cf_kv_validate_page(C.byref(bad)) == 1
+    big = _page(tokens=4096, dim=128)
+    big.block_size = 1
+    big.k_block_count = big.v_block_count = 10          # fewer blocks than tokens*dim needs
+    assert lib.cf_kv_validate_page(C.byref(big)) == 1
+    assert lib.cf_kv_page_resident_bytes(C.byref(p), None) == 1
+    over = _page()
+    over.k_word_count = 0x7FFFFFFFFFFFFFFF                  # byte count overflows 64 bits: unsupported, not invalid
+    assert lib.cf_kv_page_resident_bytes(C.byref(over), C.byref(n)) == 2
+
+
+def test_layout_validation_and_memory_stats(native):
+    lib = native.lib()
+    pages = (PageView * 2)(_page(0, 4), _page(4, 4))
+    lay = CacheLayout()
+    lay.struct_size, lay.abi_version = C.sizeof(CacheLayout), 0
+    lay.layer_count, lay.kv_head_count, lay.head_dim, lay.page_capacity_tokens = 1, 1, 8, 4
+    lay.active_token_begin, lay.active_token_count, lay.active_element_bytes = 8, 2, 4
+    lay.pages, lay.page_count = pages, 2
+    lay.active_k_bytes = lay.active_v_bytes = 2 * 8 * 4
+    assert lib.cf_kv_validate_layout(C.byref(lay)) == 0
+    st = MemoryStats()
+    assert lib.cf_kv_cache_memory_stats(C.byref(lay), C.byref(st)) == 0
+    one = (5 + 6) * 4 + 34 * 4 + 12 * 4
+    assert (st.page_count, st.sealed_tokens, st.active_tokens) == (2, 8, 2)
+    assert st.sealed_payload_bytes == 2 * one and st.sealed_descriptor_bytes == 2 * 168
+    assert st.active_payload_bytes == 128 and st.total_resident_bytes == 2 * one + 336 + 128
+    pages[1].token_begin = 3                                  # overlap (kv_runtime_test.cpp:70-104)
+    assert lib.cf_kv_validate_layout(C.byref(lay)) == 1
+    pages[1].token_begin = 4
+    lay.active_k_bytes = 1                                    # tail under-accounted
+    assert lib.cf_kv_validate_layout(C.byref(lay)) == 1
+    lay.active_k_bytes = 64
+    lay.active_token_begin = 7                                # a sealed page reaches into the tail
+    assert lib.cf_kv_validate_layout(C.byref(lay)) == 1
+    lay.active_token_begin = 8
+    lay.active_token_count = 5                                # tail longer than a page
+    assert lib.cf_kv_validate_layout(C.byref(lay)) == 1
+    assert lib.cf_kv_cache_memory_stats(C.byref(lay), None) == 1
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def test_online_softmax_matches_reference_golden(native):
+    """Same inputs, same split into partial states, same merges as the golden file made with the reference's
+    cf_online_softmax_* — every intermediate state must agree to the last bit of the double."""
+    lib = native.lib()
+    z = np.load(os.path.join(GOLD, "online_softmax.npz"))
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        scores, values, cuts = z[f"{name}.scores"], z[f"{name}.values"], z[f"{name}.cuts"]
+        dim = values.shape[1]
+        merged, mbuf = SoftmaxState(), (C.c_double * dim)()
+        assert lib.cf_online_softmax_init(C.byref(merged), mbuf, dim) == 0
+        begin = 0
+        for i, end in enumerate(cuts):
+            st, buf = SoftmaxState(), (C.c_double * dim)()
+            assert lib.cf_online_softmax_init(C.byref(st), buf, dim) == 0
+            for j in range(begin, int(end)):
+                assert lib.cf_online_softmax_accumulate(C.byref(st), C.c_double(scores[j]), _p(np.ascontiguousarray(values[j]))) == 0
+            assert st.max_score == z[f"{name}.partial_max"][i] and st.exp_sum == z[f"{name}.partial_sum"][i]
+            assert np.array_equal(np.array(buf[:]), z[f"{name}.partial_weighted"][i])
+            assert lib.cf_online_softmax_merge(C.byref(merged), C.byref(st)) == 0
+            begin = int(end)
+        out = np.zeros(dim, np.float32)
+        assert lib.cf_online_softmax_finalize(C.byref(merged), _p(out)) == 0
+        assert merged.max_score == float(z[f"{name}.merged_max"]) and merged.exp_sum == float(z[f"{name}.merged_sum"])
+        assert np.array_equal(out, z[f"{name}.output"])
+    empty, ebuf = SoftmaxState(), (C.c_double * 4)()
+    assert lib.cf_online_softmax_init(C.byref(empty), ebuf, 4) == 0
+    assert lib.cf_online_softmax_finalize(C.byref(empty), _p(np.zeros(4, np.float32))) == 1     # kv_runtime_test.cpp:152-157
+    assert lib.cf_online_softmax_init(C.byref(empty), ebuf, 129) == 1
+    assert lib.cf_online_softmax_accumulate(C.byref(empty), C.c_double(float("nan")), _p(np.zeros(4, np.float32))) == 1
+
+
+def test_adapter_options_and_null_handles(native):
+    """integrations/llama.cpp/chromofold_kv_adapter.cpp:53-63 and tests/llama_kv_adapter_seam.cpp."""
+    lib = native.lib()
+    lib.cf_llama_kv_last_error.restype = C.c_char_p
+    lib.cf_llama_kv_create.restype = C.c_void_p
+    o = LlamaKvOptions()
+    o.struct_size, o.backend = C.sizeof(LlamaKvOptions), 1
+    o.layer_count, o.kv_head_count, o.query_head_count, o.head_dim, o.page_size, o.gqa_group_size = 2, 2, 8, 64, 32, 4
+    assert lib.cf_llama_kv_options_validate(C.byref(o)) == 0
+    assert lib.cf_llama_kv_options_validate(None) == -1
+    o.query_head_count = 7
+    assert lib.cf_llama_kv_options_validate(C.byref(o)) == -1      # Hq != Hkv * group
+    assert lib.cf_llama_kv_create(C.byref(o)) is None
+    o.backend = 0
+    assert lib.cf_llama_kv_options_validate(C.byref(o)) == 0       # dense backend: nothing to check
+    assert lib.cf_llama_kv_create(C.byref(o)) is None              # but no adapter is made for it
+    o.struct_size = 8
+    assert lib.cf_llama_kv_options_validate(C.byref(o)) == -1
+    assert lib.cf_llama_kv_append(None, 0, 0, 0, None, None, 0, None) == -1
+    assert lib.cf_llama_kv_flush(None, None) == -1 and lib.cf_llama_kv_get_stats(None, None) == -1
+    assert lib.cf_llama_kv_last_error(None) == b"invalid ChromoFold KV adapter"
