@@ -56,6 +56,8 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed comparison kernel")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank has its own batch; strong: one batch sharded over the ranks by the scheduler")
     return ap.parse_args()
 
 
@@ -242,14 +244,20 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
 
-    contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3 + 1000 * rank)
+    if a.scaling == "strong" and world > 1:
+        from chromofold_b200.scheduler import shard_sequences
+        everyone = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3)
+        contexts = everyone[shard_sequences(everyone, world)[rank]]
+    else:
+        contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3 + 1000 * rank)
+    n_local = len(contexts)
     layer, info = build_sealed_layer(contexts, query_heads=HQ, kv_heads=HKV, head_dim=D, page_tokens=T, block_size=BLOCK,
                                      coder=a.coder, dist=("laplace", a.laplace_b), seed=4 + 1000 * rank, device=device,
                                      keep_dense=not a.no_dense)
     gen = torch.Generator(device=device)
     gen.manual_seed(5 + 1000 * rank)
-    q = torch.randn((a.batch, HQ, D), generator=gen, device=device, dtype=torch.float32).half()
-    out = torch.zeros((a.batch, HQ, D), dtype=torch.float32, device=device)
+    q = torch.randn((n_local, HQ, D), generator=gen, device=device, dtype=torch.float32).half()
+    out = torch.zeros((n_local, HQ, D), dtype=torch.float32, device=device)
     kernel = {"auto": N.KERNEL_AUTO, "generic": N.KERNEL_GENERIC, "lanes": N.KERNEL_LANES}[a.kernel]
     kw = dict(kernel=kernel, min_pages_per_unit=a.min_pages_per_unit)
 
@@ -281,7 +289,7 @@ def main():
 
     # end to end: queries come from pinned host memory, the result goes back to pinned host memory, every step
     q_pin = q.cpu().pin_memory()
-    out_pin = torch.zeros((a.batch, HQ, D), dtype=torch.float32).pin_memory()
+    out_pin = torch.zeros((n_local, HQ, D), dtype=torch.float32).pin_memory()
     q_dev = torch.empty_like(q)
 
     def e2e_step():
@@ -349,15 +357,17 @@ def main():
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
     # algorithmic bytes of one attention launch on this rank: every sealed record once, the page table, Q in, partials out
-    algo_bytes = info["sealed_bytes"] + 4 * info["pages"] + a.batch * HQ * D * 2
+    algo_bytes = info["sealed_bytes"] + 4 * info["pages"] + n_local * HQ * D * 2
     att_s = stage_ms[1] * 1e-3
     achieved = algo_bytes / att_s / 1e9
     line = {
         "metric": METRIC, "value": tokens_total * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": a.steps,
-        "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": a.scaling,
         "vs_baseline": None, "dtype": "u8 codes, f16 mma operands, f32 accumulate", "data": "synthetic",
-        "config": {"workload": workload_name(a), "global_batch": a.batch * world, "seq_tokens_per_step": tokens_total,
-                   "sharding": f"sequences, {a.batch} per GPU, no collective", "l2": "inputs larger than L2 (sealed bytes per GPU "
+        "config": {"workload": workload_name(a), "global_batch": a.batch * world if a.scaling == "weak" else a.batch,
+                   "seq_tokens_per_step": tokens_total,
+                   "sharding": (f"sequences, {a.batch} per GPU, no collective" if a.scaling == "weak" else
+                                f"{a.batch} sequences bin-packed over {world} GPUs by context length, no collective"), "l2": "inputs larger than L2 (sealed bytes per GPU "
                    f"{info['sealed_bytes'] / 1e9:.2f} GB vs 126 MB)", "kernel": a.kernel,
                    "h0_bits_per_code": {"k": info["h0_bits_k"], "v": info["h0_bits_v"]},
                    "sealed_bytes_per_seq_token": info["bytes_per_seq_token"],
