@@ -156,6 +156,18 @@ class SealedKvLayer:
             self.h_sealed[s] += c * self.page_tokens
         self.sealed_tokens.copy_(torch.as_tensor(self.h_sealed.astype(np.int32)))
 
+    def copy_sequence(self, src, dst):
+        """Give slot `dst` the history of slot `src` without copying a sealed byte: the sealed pages are shared by page
+        id (the reference's shared-page semantics, src/multisequence_cache.cpp:235-292); the unsealed tail is copied."""
+        n = int((self.h_sealed[src] + self.page_tokens - 1) // self.page_tokens)
+        self.h_page_table[dst, :n] = self.h_page_table[src, :n]
+        self.page_table[dst, :n] = self.page_table[src, :n]
+        self.h_sealed[dst], self.h_tail[dst] = self.h_sealed[src], self.h_tail[src]
+        self.sealed_tokens[dst] = int(self.h_sealed[src])
+        self.tail_tokens[dst] = int(self.h_tail[src])
+        self.tail_k[dst] = self.tail_k[src]
+        self.tail_v[dst] = self.tail_v[src]
+
     # -- import of records sealed elsewhere ------------------------------------------------------------
     def import_records(self, slot, records, tokens_per_page=None):
         """Append already sealed pages to `slot`. records[p][h] is the record (bytes-like) of page p, kv head h."""

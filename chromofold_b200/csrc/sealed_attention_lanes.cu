@@ -1,5 +1,6 @@
 // sealed_attention_lanes.cu — the hot kernel: decode-step attention over sealed pages for the geometry
-// head_dim 128, page_tokens 16, block_size 64 (32 blocks per stream), up to 4 query heads per kv head.
+// head_dim 128, page_tokens 16, block_size 64 (32 blocks per stream). Query groups larger than 4 heads per kv head are
+// served four heads at a time (the unit is then decoded once per sub-group).
 //
 // What it computes is what src/cuda/paged_kv_attention.cu:183-276 computes for one query token; how it runs is new:
 //
@@ -284,15 +285,15 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
     PlanHeader *hdr = plan_header(p);
     const uint32_t *prefix = chunk_prefix(p);
-    const uint32_t unit_count = hdr->chunk_count * p.kv_head_span;
+    const uint32_t subgroups = (p.group + 3u) / 4u;   // four query heads per pass
+    const uint32_t unit_count = hdr->chunk_count * p.kv_head_span * subgroups;
     const uint32_t pages_per_unit = hdr->pages_per_unit;
-    const uint32_t G = p.group;
     const uint32_t g = lane >> 2, t = lane & 3u;
     uint32_t phase_bits = 0u;  // bit s: parity the next wait on stage s expects
 
     // fixed lane roles
     const uint32_t q_head_of_col = g & 3u;                 // S columns: n = parity*4 + head
-    const bool q_col_live = ((t >> 1) == (g >> 2)) && q_head_of_col < G;
+    const bool q_col_mine = (t >> 1) == (g >> 2);
     const uint32_t my_token = 2u * g + (t >> 1);           // S fragment: row g, this lane's token
     const uint32_t my_head0 = 2u * (t & 1u);               // S fragment: this lane's two heads
     const uint32_t o_head = g & 3u;                        // O fragments: all of this lane's outputs are one head
@@ -304,9 +305,14 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         if (lane == 0) unit = atomicAdd(&hdr->next_unit, 1u);
         unit = __shfl_sync(0xffffffffu, unit, 0);
         if (unit >= unit_count) break;
-        const uint32_t chunk = unit / p.kv_head_span;
-        const uint32_t head_local = unit % p.kv_head_span;
+        const uint32_t sub = unit % subgroups;
+        const uint32_t chunk = (unit / subgroups) / p.kv_head_span;
+        const uint32_t head_local = (unit / subgroups) % p.kv_head_span;
         const uint32_t kv_head = p.kv_head_begin + head_local;
+        const uint32_t G = min(4u, p.group - 4u * sub);                 // query heads served by this pass
+        const uint32_t q_head_base = kv_head * p.group + 4u * sub;     // first of them
+        const uint32_t out_head_base = head_local * p.group + 4u * sub;
+        const bool q_col_live = q_col_mine && q_head_of_col < G;
         const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
         const uint32_t slot = slot_of(p, seq);
         const uint32_t sealed = p.seq_sealed_tokens[slot];
@@ -325,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         uint32_t bq[16][2];
         {
             const __half *qrow = reinterpret_cast<const __half *>(p.queries) +
-                                 (static_cast<uint64_t>(seq) * p.query_head_count + kv_head * G + q_head_of_col) * 128u +
+                                 (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base + q_head_of_col) * 128u +
                                  64u * (t & 1u);
 #pragma unroll
             for (int s = 0; s < 16; ++s) {
@@ -509,18 +515,18 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         }
         if (g == 0 && t < 2) {
             if (my_head0 < G) {
-                float *dst = partial_ptr(p, chunk, head_local * G + my_head0);
+                float *dst = partial_ptr(p, chunk, out_head_base + my_head0);
                 dst[0] = u.m0;
                 dst[1] = l0;
             }
             if (my_head0 + 1u < G) {
-                float *dst = partial_ptr(p, chunk, head_local * G + my_head0 + 1u);
+                float *dst = partial_ptr(p, chunk, out_head_base + my_head0 + 1u);
                 dst[0] = u.m1;
                 dst[1] = l1;
             }
         }
         if (o_head < G) {
-            float *dst = partial_ptr(p, chunk, head_local * G + o_head) + 2;
+            float *dst = partial_ptr(p, chunk, out_head_base + o_head) + 2;
 #pragma unroll
             for (int dd = 0; dd < 4; ++dd) {
 #pragma unroll
@@ -537,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 }  // namespace
 
 bool lanes_kernel_supports(const AttentionParams &p) {
-    return p.head_dim == 128 && p.page_tokens == 16 && p.block_size == 64 && p.group >= 1 && p.group <= 4 &&
+    return p.head_dim == 128 && p.page_tokens == 16 && p.block_size == 64 && p.group >= 1 && p.group <= 16 &&
            p.query_type == CF_B200_F16;
 }
 

@@ -75,3 +75,27 @@ def attention_close(actual, expected, rel=2e-3, abs_=1e-3):
     expected = np.asarray(expected, np.float64)
     err = np.abs(actual - expected)
     return bool(np.all(err <= abs_ + rel * np.abs(expected))), float(err.max())
+
+
+def oracle_from_layer(layer, q16, causal_window=0, slots=None, threads=None):
+    """CPU oracle attention over the very records a SealedKvLayer holds on the GPU (arena, directory, page table and
+    tails are copied back): restated reference decoders -> dequantise -> double online softmax."""
+    kcb = ob.codebook_from_hist(np.ones(256, np.uint64))
+    vcb = ob.codebook_from_hist(np.ones(256, np.uint64))
+    for cb, host in ((kcb, layer.host_tables[0]), (vcb, layer.host_tables[1])):
+        slot = np.ctypeslib.as_array(host.rans_slot)
+        cb.slot2sym[:] = (slot & 0xFF).astype(np.int32).tolist()
+        cb.freq[:] = np.ctypeslib.as_array(host.rans_freq).astype(np.int32).tolist()
+        cb.cum[:] = np.ctypeslib.as_array(host.rans_cum).astype(np.int32).tolist()
+        cb.lut[:] = np.ctypeslib.as_array(host.huff_lut).astype(np.int32).tolist()
+    arena = layer.arena[:layer.sealed_bytes() + 64].cpu().numpy()
+    offsets = (layer.page_dir.cpu().numpy().astype(np.uint64) & np.uint64(0xFFFFFFFFFF)) * np.uint64(16)
+    sel = np.arange(layer.max_sequences) if slots is None else np.asarray(slots)
+    table = layer.page_table.cpu().numpy().astype(np.uint32)[sel]
+    sealed = layer.sealed_tokens.cpu().numpy().astype(np.uint32)[sel]
+    tails = layer.tail_tokens.cpu().numpy().astype(np.uint32)[sel]
+    tk = layer.tail_k.cpu().numpy()[sel]
+    tv = layer.tail_v.cpu().numpy()[sel]
+    return ob.sealed_decode_attention(arena, offsets, table, sealed, q16, layer.query_heads, layer.kv_heads, layer.head_dim,
+                                      layer.page_tokens, layer.block_size, causal_window, 1.0 / np.sqrt(layer.head_dim),
+                                      kcb, vcb, tail_k=tk, tail_v=tv, tail_count=tails, threads=threads)

@@ -1,0 +1,131 @@
+"""The benchmark configurations as parity cases (seeded synthetic inputs with their shapes and distributions), through
+the C ABI, against the CPU oracle reading the same sealed bytes. Config 2 runs at its full size."""
+import numpy as np
+import pytest
+
+from helpers import attention_close, oracle_from_layer
+
+pytestmark = pytest.mark.gpu
+
+
+def _q(n, hq, seed):
+    import torch
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    return torch.randn((n, hq, 128), generator=g, device="cuda", dtype=torch.float32).half()
+
+
+def test_config1_plumbing_single_sequence_mha(native, oracle):
+    """1 sequence, 8 = 8 heads, head_dim 128, 4096 tokens, K/V fp16 N(0,1) quantised with per-page-per-head fp16 absmax
+    scales, rANS pages. Codes decoded on the GPU equal the CPU quantiser's codes; outputs match the oracle."""
+    import torch
+    from chromofold_b200.cache import SealedKvLayer
+    rng = np.random.default_rng(1)
+    layer = SealedKvLayer(kv_heads=8, query_heads=8, max_sequences=1, max_pages_per_sequence=258, max_pages=260,
+                          arena_bytes=260 * 8 * 4200, coder=native.CODER_RANS)
+    k = rng.standard_normal((256, 8, 16, 128)).astype(np.float16)
+    v = rng.standard_normal((256, 8, 16, 128)).astype(np.float16)
+    rc, bits, codes = oracle.quantize_stream(k[0, 0].astype(np.float32))
+    hist = np.bincount(codes.astype(np.int64) + 128, minlength=256).astype(np.uint64) + 1
+    layer.set_codebooks(hist, hist)
+    layer.seal_tiles([0] * 256, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+    assert layer.device_status() == 0
+    ks, vs = layer.decode_pages([1, 100, 256])
+    for i, p in enumerate((0, 99, 255)):
+        for h in (0, 7):
+            rc, bits, codes = oracle.quantize_stream(k[p, h].astype(np.float32))
+            assert np.array_equal(ks[i, h].cpu().numpy(), (codes.astype(np.int16) + 128).astype(np.uint8))
+            rc, bits, codes = oracle.quantize_stream(v[p, h].astype(np.float32))
+            assert np.array_equal(vs[i, h].cpu().numpy().reshape(128, 16).T.ravel(), (codes.astype(np.int16) + 128).astype(np.uint8))
+    q = _q(1, 8, 2)
+    want = oracle_from_layer(layer, q.cpu().numpy())
+    for kernel in (native.KERNEL_LANES, native.KERNEL_GENERIC):
+        ok, err = attention_close(layer.attention(q, kernel=kernel).cpu().numpy(), want)
+        assert ok, (kernel, err)
+    # N(0,1) scaled by absmax/127 has H0 ~ 7.2 bits: entropy coding buys little, as the reference found
+    assert 0.80 < layer.sealed_bytes() / (4096 * 8 * 2 * 128) < 1.01
+
+
+def test_config2_llama8b_full_size(native, oracle):
+    """64 sequences, contexts U[2048, 32768], 32/8 heads, Laplace(b=12) codes, rANS pages — the benchmark workload at
+    full size (1.8 GB of sealed pages); every sequence checked against the oracle."""
+    from chromofold_b200.workloads import build_sealed_layer, uniform_contexts
+    contexts = uniform_contexts(64, 2048, 32768, 16, 3)
+    layer, info = build_sealed_layer(contexts, coder="rans", dist=("laplace", 12.0), seed=4)
+    assert 5.9 < info["h0_bits_k"] < 6.2 and 1650 < info["bytes_per_seq_token"] < 1850
+    q = _q(64, 32, 5)
+    got = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    assert layer.device_status() == 0
+    want = oracle_from_layer(layer, q.cpu().numpy())
+    ok, err = attention_close(got, want)
+    assert ok, err
+
+
+@pytest.mark.parametrize("p", [0.05, 0.1, 0.2, 0.4, 0.7])
+def test_config3_coder_crossover(native, oracle, p):
+    """Two-sided geometric codes at five entropies, each sealed with rANS and with Huffman: parity for both, and both
+    stay below the fixed-width size."""
+    from chromofold_b200.workloads import build_sealed_layer
+    sizes = {}
+    for coder in ("rans", "huffman"):
+        layer, info = build_sealed_layer(np.array([512, 1024, 256]), coder=coder, dist=("geometric", p), seed=6)
+        q = _q(3, 32, 7)
+        got = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+        ok, err = attention_close(got, oracle_from_layer(layer, q.cpu().numpy()))
+        assert ok and layer.device_status() == 0, (coder, err)
+        sizes[coder] = info["bytes_per_seq_token"]
+    assert sizes["rans"] < 2056 and sizes["huffman"] < 2056
+    if p >= 0.4:
+        assert sizes["huffman"] < sizes["rans"] * 1.25    # block-64 state overhead keeps rANS from winning big
+
+
+def test_config4_gqa8_kv_head_sharding(native, oracle):
+    """70B shape (64 query / 8 kv heads): kv heads sharded 1, 2, 4 and 8 ways, each shard a separate launch over its
+    kv_head_begin / kv_head_span; the union of the shards' head blocks equals the unsharded result."""
+    import torch
+    from chromofold_b200.scheduler import shard_kv_heads
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, _ = build_sealed_layer(np.array([2048, 1536]), query_heads=64, kv_heads=8, coder="rans", seed=8)
+    q = _q(2, 64, 9)
+    want = oracle_from_layer(layer, q.cpu().numpy())
+    whole = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    ok, err = attention_close(whole, want)
+    assert ok, err
+    for ways in (2, 4, 8):
+        merged = torch.zeros((2, 64, 128), device="cuda")
+        for begin, span in shard_kv_heads(8, ways):
+            part = layer.attention(q, kernel=native.KERNEL_LANES, kv_head_begin=begin, kv_head_span=span)
+            merged[:, begin * 8:(begin + span) * 8] = part[:, begin * 8:(begin + span) * 8]
+        assert np.array_equal(merged.cpu().numpy(), whole)       # sharding changes nothing, bit for bit
+    assert layer.device_status() == 0
+
+
+def test_config5_shared_prefix_with_gpu_sealed_suffixes(native, oracle):
+    """Sequences sharing one sealed prefix (one copy of its pages, referenced from every page table) plus private
+    suffixes that grow by one token per step and are sealed on the GPU whenever 16 tokens have accumulated."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    n, prefix = 12, 1024
+    layer, info = build_sealed_layer(np.array([prefix] + [0] * (n - 1)), coder="rans", seed=10, extra_pages_per_sequence=8)
+    bytes_one_copy = layer.sealed_bytes()
+    for s in range(1, n):
+        layer.copy_sequence(0, s)
+    assert layer.sealed_bytes() == bytes_one_copy                # sharing copies no page
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    slots = list(range(n))
+    for step in range(37):
+        k = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append(slots, k, v)
+        if step in (4, 15, 36):
+            q = _q(n, 32, 100 + step)
+            got = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+            ok, err = attention_close(got, oracle_from_layer(layer, q.cpu().numpy()))
+            assert ok, (step, err)
+            assert not np.allclose(got[0], got[1])               # private suffixes differ
+        layer.seal_full_pages()
+    assert layer.device_status() == 0
+    assert int(layer.h_sealed[3]) == prefix + 32 and int(layer.h_tail[3]) == 5
+    assert np.array_equal(layer.h_page_table[0, :prefix // 16], layer.h_page_table[7, :prefix // 16])
+    assert layer.h_page_table[0, prefix // 16] != layer.h_page_table[7, prefix // 16]
