@@ -92,6 +92,14 @@ __device__ __forceinline__ void quad_to_half2(uint32_t quad, uint32_t &lo, uint3
     hi = hsub2_u32(__byte_perm(quad, kMagic, 0x4342), kBias2);  // (s2, s3)
 }
 
+// a * b + c on the multiply-add pipe. Plain adds and constant shifts written this way leave the integer ALU pipe,
+// which is the busiest one in the decoders, to the operations that have no other home (logic, funnel shifts).
+__device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
 // ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
 // Both entropy decoders are written without branches so that the K chain and the V chain of a lane interleave in
 // one straight instruction stream. A 64-bit window holds the upcoming stream bits, top aligned; it is reloaded from
@@ -123,13 +131,13 @@ struct RansLane {
     // reference runs 0, 1 or 2 times: exactly (clz(state) - 1) / 8 times. The bytes come out of the window.
     __device__ __forceinline__ uint32_t symbol() {
         uint32_t e;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(table + ((x & (CF_B200_RANS_M - 1u)) << 2)));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(imad(x & (CF_B200_RANS_M - 1u), 4u, table)));
         x = ((e >> 8) & 0xfffu) * (x >> CF_B200_RANS_PROB_BITS) + (e >> 20);
-        const uint32_t shift = (static_cast<uint32_t>(__clz(x)) - 1u) & 24u;
+        const uint32_t shift = imad(static_cast<uint32_t>(__clz(x)), 1u, 0xffffffffu) & 24u;
         x = __funnelshift_l(whi, x, shift);
         whi = __funnelshift_l(wlo, whi, shift);
         wlo <<= shift;
-        used += shift;
+        used = imad(shift, 1u, used);
         return e;
     }
     __device__ __forceinline__ uint32_t quad() {
@@ -166,11 +174,11 @@ struct HuffLane {
     // include/chromofold/detail/block_huffman_device.cuh:12-19: the next 12 bits, MSB-first, index the LUT.
     __device__ __forceinline__ uint32_t symbol() {
         uint32_t e;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e) : "r"(table + ((whi >> (32u - CF_B200_HUFF_MAXLEN)) << 1)));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e) : "r"(imad(whi >> (32u - CF_B200_HUFF_MAXLEN), 2u, table)));
         const uint32_t len = e >> 8;
         whi = __funnelshift_l(wlo, whi, len);
         wlo <<= len;
-        used += len;
+        used = imad(len, 1u, used);
         return e;
     }
     __device__ __forceinline__ uint32_t quad() {
