@@ -37,7 +37,7 @@ class SealedAttentionDesc(C.Structure):
         ("queries", _vp), ("output", _vp), ("query_type", _u32), ("output_type", _u32),
         ("softmax_scale", _f32), ("causal_window", _u32),
         ("workspace", _vp), ("workspace_bytes", _u64), ("min_pages_per_unit", _u32), ("kernel", _u32),
-        ("status", _vp), ("tail_type", _u32), ("reserved", _u32), ("query_positions", _vp),
+        ("status", _vp), ("tail_type", _u32), ("tail_capacity", _u32), ("query_positions", _vp),
     ]
 
 
@@ -47,8 +47,8 @@ class SealDesc(C.Structure):
         ("kv_head_count", _u32), ("head_dim", _u32), ("page_tokens", _u32), ("block_size", _u32),
         ("coder", _u32), ("codebook_id", _u32),
         ("k_tables", _vp), ("v_tables", _vp), ("tail_k", _vp), ("tail_v", _vp),
-        ("job_slots", _vp), ("job_pages", _vp), ("job_tokens", _vp), ("job_heads", _vp),
-        ("job_count", _u32), ("tail_type", _u32),
+        ("job_slots", _vp), ("job_pages", _vp), ("job_tokens", _vp), ("job_heads", _vp), ("job_rows", _vp),
+        ("job_count", _u32), ("tail_type", _u32), ("tail_capacity", _u32), ("reserved", _u32),
         ("arena", _vp), ("arena_units", _u64), ("arena_cursor_units", _vp), ("page_dir", _vp), ("status", _vp),
     ]
 
@@ -77,6 +77,14 @@ EXPORTS = {
         "cf_kv_validate_page", "cf_kv_validate_layout", "cf_kv_page_resident_bytes", "cf_kv_cache_memory_stats",
         "cf_online_softmax_init", "cf_online_softmax_accumulate", "cf_online_softmax_merge", "cf_online_softmax_finalize",
         "cf_kv_validate_paged_attention_desc", "cf_kv_paged_attention_async", "cf_rans_decode_async",
+    ],
+    "compat_device.h": [
+        "cf_device_tensor_validate", "cf_device_kv_create", "cf_device_kv_destroy", "cf_device_kv_append_async",
+        "cf_device_kv_seal_full_pages_async", "cf_device_kv_attention_async", "cf_device_kv_clear_async",
+        "cf_device_kv_get_counters", "cf_device_kv_last_error", "cf_device_seal_create", "cf_device_seal_destroy",
+        "cf_device_seal_stage_active_page", "cf_device_seal_full_page_async", "cf_device_seal_attention_async",
+        "cf_device_seal_clear_async", "cf_device_seal_set_fault", "cf_device_seal_get_state",
+        "cf_device_seal_get_counters", "cf_device_seal_last_error",
     ],
     "compat_adapter.h": [
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",

@@ -22,7 +22,7 @@ struct AttentionParams {
     // tails
     const void *tail_k, *tail_v;
     const uint32_t *tail_tokens;
-    uint32_t tail_type;
+    uint32_t tail_type, tail_capacity;
     const uint32_t *query_positions;
     // io
     const void *queries;

@@ -289,6 +289,7 @@ extern "C" cf_status cf_b200_dense_attention_async(const cf_b200_dense_attention
     p.workspace = static_cast<uint8_t *>(d->workspace);
     p.layout = cfb::workspace_layout(d->seq_count, d->query_head_count, d->head_dim, d->workspace_bytes);
     p.min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    p.tail_capacity = d->page_tokens;
     p.pool_k = static_cast<const __half *>(d->pool_k);
     p.pool_v = static_cast<const __half *>(d->pool_v);
     if (p.layout.chunk_capacity < d->seq_count) return CF_ERR_INVALID_ARGUMENT;

@@ -36,8 +36,8 @@ struct SealParams {
     uint32_t kv_head_count, head_dim, page_tokens, block_size, coder, codebook_id, symbols, nblocks;
     const cf_b200_codebook_tables *k_tables, *v_tables;
     const void *tail_k, *tail_v;
-    uint32_t tail_type;
-    const uint32_t *job_slots, *job_pages, *job_tokens, *job_heads;
+    uint32_t tail_type, tail_capacity;
+    const uint32_t *job_slots, *job_pages, *job_tokens, *job_heads, *job_rows;
     uint8_t *arena;
     uint64_t arena_units;
     unsigned long long *cursor;
@@ -235,7 +235,8 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
     const uint32_t slot = p.job_slots[job];
     const uint32_t rows = p.job_tokens ? min(p.job_tokens[job], p.page_tokens) : p.page_tokens;
-    const uint64_t tile = (static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.symbols;
+    const uint64_t tile = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.tail_capacity +
+                           (p.job_rows ? p.job_rows[job] : 0u)) * p.head_dim;
 
     int k_bad, v_bad;
     const float k_max = tile_absmax(p.tail_k, p.tail_type, tile, rows * p.head_dim, &k_bad, red);
@@ -297,7 +298,8 @@ __global__ void __launch_bounds__(kSealThreads) histogram_kernel(SealParams p, u
     const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
     const uint32_t slot = p.job_slots[job];
     const uint32_t rows = p.job_tokens ? min(p.job_tokens[job], p.page_tokens) : p.page_tokens;
-    const uint64_t tile = (static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.symbols;
+    const uint64_t tile = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.tail_capacity +
+                           (p.job_rows ? p.job_rows[job] : 0u)) * p.head_dim;
     for (uint32_t i = tid; i < 256; i += kSealThreads) hk[i] = hv[i] = 0;
     int k_bad, v_bad;
     const float k_max = tile_absmax(p.tail_k, p.tail_type, tile, rows * p.head_dim, &k_bad, red);
@@ -334,6 +336,8 @@ void fill(const cf_b200_seal_desc *d, SealParams *p) {
     p->job_pages = d->job_pages;
     p->job_tokens = d->job_tokens;
     p->job_heads = d->job_heads;
+    p->job_rows = d->job_rows;
+    p->tail_capacity = d->tail_capacity ? d->tail_capacity : d->page_tokens;
     p->arena = d->arena;
     p->arena_units = d->arena_units;
     p->cursor = d->arena_cursor_units;

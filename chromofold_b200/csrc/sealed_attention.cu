@@ -264,17 +264,18 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
 constexpr int kCombineThreads = 128;
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParams p) {
-    extern __shared__ float tail_scores[];  // [page_tokens]
+    extern __shared__ float tail_scores[];  // [tail_capacity]
     __shared__ float s_red[kCombineThreads / 32];
     const uint32_t seq = blockIdx.x;
     const uint32_t local_q = blockIdx.y;
-    const uint32_t G = p.group, D = p.head_dim, T = p.page_tokens;
+    const uint32_t G = p.group, D = p.head_dim;
     const uint32_t kv_head = p.kv_head_begin + local_q / G;
     const uint32_t q_head = kv_head * G + local_q % G;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t slot = slot_of(p, seq);
     const uint32_t sealed = p.seq_sealed_tokens[slot];
-    const uint32_t tail = p.tail_tokens ? min(p.tail_tokens[slot], T) : 0u;
+    const uint32_t C = p.tail_capacity;  // rows per (slot, kv head) in the tails
+    const uint32_t tail = p.tail_tokens ? min(p.tail_tokens[slot], C) : 0u;
     const uint32_t qpos = query_position(p, seq, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
     const uint32_t first_token = window_begin(qpos, p.causal_window);
     const uint32_t *prefix = chunk_prefix(p);
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
 
     // tail scores (binary16 rows, one warp per token)
     for (uint32_t t = warp; t < tail; t += kCombineThreads / 32) {
-        const uint64_t row = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D;
+        const uint64_t row = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * C + t) * D;
         float dot = 0.0f;
         for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, seq, q_head, d) * load_tail(p.tail_k, p.tail_type, row + d);
         dot = warp_sum(dot);
@@ -316,7 +317,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
             const float w = exp2f(s - m);
             l += w;
             if (tid < D)
-                a += w * load_tail(p.tail_v, p.tail_type, ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * T + t) * D + tid);
+                a += w * load_tail(p.tail_v, p.tail_type, ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * C + t) * D + tid);
         }
     }
     if (tid < D) {
@@ -388,6 +389,7 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->tail_tokens = d->tail_tokens;
     p->tail_type = d->tail_type == CF_B200_F32 ? CF_B200_F32 : CF_B200_F16;
     p->query_positions = d->query_positions;
+    p->tail_capacity = d->tail_capacity ? d->tail_capacity : d->page_tokens;
     p->queries = d->queries;
     p->output = d->output;
     p->query_type = d->query_type;
@@ -412,7 +414,7 @@ cudaError_t launch_plan(const AttentionParams &p, cudaStream_t stream) {
 
 cudaError_t launch_combine(const AttentionParams &p, cudaStream_t stream) {
     const dim3 grid(p.seq_count, p.kv_head_span * p.group);
-    combine_kernel<<<grid, kCombineThreads, p.page_tokens * sizeof(float), stream>>>(p);
+    combine_kernel<<<grid, kCombineThreads, max(p.tail_capacity, 1u) * sizeof(float), stream>>>(p);
     return cudaPeekAtLastError();
 }
 

@@ -82,7 +82,7 @@ typedef struct cf_b200_sealed_attention_desc {
     const cf_b200_codebook_tables *k_tables;
     const cf_b200_codebook_tables *v_tables;
 
-    const void *tail_k;                  /* [slot][kv_head_count][page_tokens][head_dim] of tail_type, may be NULL */
+    const void *tail_k;                  /* [slot][kv_head_count][tail_capacity][head_dim] of tail_type, may be NULL */
     const void *tail_v;
     const uint32_t *tail_tokens;         /* [slot], NULL = no tails */
 
@@ -99,7 +99,7 @@ typedef struct cf_b200_sealed_attention_desc {
     uint32_t kernel;                     /* CF_B200_KERNEL_* */
     uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
     uint32_t tail_type;                  /* CF_B200_F16 (0 means F16 too) or CF_B200_F32: element type of the tails */
-    uint32_t reserved;
+    uint32_t tail_capacity;              /* rows per (slot, kv head) in tail_k / tail_v; 0 = page_tokens */
     /* Optional [seq_count]: position of each batch entry's query token. NULL = sealed + tail tokens (a decode
      * step). A smaller position hides the tokens after it (paged_kv_attention.cu:67-69), so several entries may
      * name the same slot with different positions: that is multi-query (prefill) attention over one sequence. */
@@ -165,8 +165,8 @@ cf_status cf_b200_codebook_build(const uint64_t histogram[256], cf_b200_codebook
  * (src/cuda/device_kv_seal_attention.cu:244-334: finite scan, quantise, pack, publish — six launches, a
  * host synchronisation and nine allocations per page) with one launch and no host round trip.
  *
- * For every job j: reads the binary16 rows of slot job_slots[j] from tail_k / tail_v
- * ([slot][kv_head_count][page_tokens][head_dim], first job_tokens[j] rows valid), quantises each
+ * For every job j: reads rows job_rows[j] .. job_rows[j] + job_tokens[j] of slot job_slots[j] from tail_k / tail_v
+ * ([slot][kv_head_count][tail_capacity][head_dim] of tail_type), quantises each
  * (kv_head, K|V) stream with its own absmax/127 binary16 scale (round-half-even, clamp [-128,127],
  * src/runtime/kv_gpu_fixture.cpp:12-16), codes it with `coder` (a stream that would not shrink is stored
  * fixed-width), takes room in the arena with one atomic add on *arena_cursor_units, writes the record and
@@ -189,8 +189,11 @@ typedef struct cf_b200_seal_desc {
     const uint32_t *job_pages;    /* [job_count] page ids to publish */
     const uint32_t *job_tokens;   /* [job_count] valid rows, NULL = page_tokens */
     const uint32_t *job_heads;    /* [job_count] kv head of each job; NULL = every job seals all kv heads */
+    const uint32_t *job_rows;     /* [job_count] first tail row of the tile to seal; NULL = 0 */
     uint32_t job_count;
     uint32_t tail_type;           /* CF_B200_F16 (0 means F16 too) or CF_B200_F32 */
+    uint32_t tail_capacity;       /* rows per (slot, kv head) in tail_k / tail_v; 0 = page_tokens */
+    uint32_t reserved;
     uint8_t *arena;
     uint64_t arena_units;                     /* capacity in 16-byte units */
     unsigned long long *arena_cursor_units;   /* device counter, next free unit */

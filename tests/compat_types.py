@@ -55,5 +55,43 @@ class LlamaKvStats(C.Structure):
                                     "dense_active_bytes", "compressed_bytes", "descriptor_bytes")]
 
 
+class TensorView(C.Structure):
+    _fields_ = [("data", _vp), ("scalar_type", _u32), ("token_count", _u32), ("head_count", _u32), ("head_dim", _u32),
+                ("token_stride_bytes", _u64), ("head_stride_bytes", _u64), ("element_stride_bytes", _u64),
+                ("device_ordinal", C.c_int32)]
+
+
+class DeviceKvConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "kv_head_count", "query_head_count", "head_dim", "page_size",
+                                    "gqa_group_size", "use_async_allocator")]
+
+
+class DeviceKvCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in (
+        "device_append_calls", "device_values_appended", "fp16_values_converted", "bf16_values_converted",
+        "fp32_values_copied", "quantization_launches", "huffman_pack_launches", "seal_attempts", "seal_successes",
+        "seal_failures", "descriptor_publications", "compressed_attention_launches", "sealed_values_consumed",
+        "active_values_consumed", "query_conversion_launches", "output_conversion_launches", "dense_fallback_launches",
+        "cuda_errors", "active_bytes", "compressed_bytes", "descriptor_bytes", "workspace_bytes", "retired_pending_bytes",
+        "peak_owned_bytes")]
+
+
+class DeviceSealConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "kv_head_count", "query_head_count", "head_dim", "page_size",
+                                    "gqa_group_size", "block_size", "use_async_allocator")]
+
+
+class DeviceSealCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in (
+        "seal_attempts", "seal_successes", "seal_failures", "finite_validation_launches", "values_scanned", "nan_values",
+        "inf_values", "invalid_pages_rejected", "quantization_launches", "values_quantized", "saturation_count",
+        "packing_launches", "symbols_packed", "payload_bytes_written", "descriptor_validations",
+        "descriptor_publications", "page_table_reallocations", "page_table_generation", "compressed_attention_launches",
+        "sealed_pages_consumed", "sealed_values_consumed", "active_values_consumed", "query_conversion_launches",
+        "output_conversion_launches", "cuda_errors", "compressed_bytes", "descriptor_bytes", "workspace_bytes",
+        "peak_owned_bytes")]
+
+
+assert C.sizeof(TensorView) == 56 and C.sizeof(DeviceSealCounters) == 29 * 8 and C.sizeof(DeviceKvCounters) == 24 * 8
 assert C.sizeof(PageView) == 168 and C.sizeof(CacheLayout) == 72 and C.sizeof(DevicePage) == 104
 assert C.sizeof(PagedAttentionDesc) == 96 and C.sizeof(SoftmaxState) == 32

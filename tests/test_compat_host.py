@@ -135,3 +135,51 @@ def test_adapter_options_and_null_handles(native):
     assert lib.cf_llama_kv_append(None, 0, 0, 0, None, None, 0, None) == -1
     assert lib.cf_llama_kv_flush(None, None) == -1 and lib.cf_llama_kv_get_stats(None, None) == -1
     assert lib.cf_llama_kv_last_error(None) == b"invalid ChromoFold KV adapter"
+
+
+def test_device_engine_contracts_without_a_gpu(native):
+    """The reference's no-GPU contracts: tests/m9_device_seal_contract.cpp and tests/device_kv_dataplane_contract.cpp.
+    Handles are created, queried and destroyed without any CUDA call."""
+    from compat_types import DeviceKvConfig, DeviceKvCounters, DeviceSealConfig, DeviceSealCounters, TensorView
+    lib = native.lib()
+    lib.cf_device_seal_create.restype = C.c_void_p
+    lib.cf_device_kv_create.restype = C.c_void_p
+    lib.cf_device_seal_last_error.restype = C.c_char_p
+    cfg = DeviceSealConfig(2, 4, 8, 64, 64, 2, 32, 1)
+    e = C.c_void_p(lib.cf_device_seal_create(C.byref(cfg)))
+    assert e.value
+    state = C.c_uint32(99)
+    assert lib.cf_device_seal_get_state(e, 0, C.byref(state)) == 0 and state.value == 0      # CF_SEAL_ACTIVE_FILLING
+    for fault in range(0, 11):
+        assert lib.cf_device_seal_set_fault(e, fault) == 0
+    assert lib.cf_device_seal_set_fault(e, 11) != 0
+    n = DeviceSealCounters()
+    assert lib.cf_device_seal_get_counters(e, C.byref(n)) == 0
+    assert (n.seal_attempts, n.seal_successes, n.descriptor_publications, n.compressed_attention_launches) == (0, 0, 0, 0)
+    assert lib.cf_device_seal_full_page_async(e, 0, None) == -1                                # nothing staged
+    assert b"full active page" in lib.cf_device_seal_last_error(e)
+    assert lib.cf_device_seal_get_state(e, 5, C.byref(state)) == -1
+    lib.cf_device_seal_destroy(e, None)
+    bad = DeviceSealConfig(2, 4, 7, 64, 64, 2, 32, 1)
+    assert lib.cf_device_seal_create(C.byref(bad)) is None
+    bad = DeviceSealConfig(2, 4, 8, 64, 64, 2, 0, 1)
+    assert lib.cf_device_seal_create(C.byref(bad)) is None
+    assert lib.cf_device_seal_last_error(None) == b"null seal engine"
+
+    fake = (C.c_float * 1)()
+    v = TensorView(C.addressof(fake), 3, 2, 4, 8, 4 * 8 * 4, 8 * 4, 4, 0)
+    assert lib.cf_device_tensor_validate(C.byref(v)) == 0
+    for field, value in [("scalar_type", 999), ("element_stride_bytes", 1), ("head_stride_bytes", 1),
+                         ("token_stride_bytes", 1), ("data", None), ("token_count", 0)]:
+        w = TensorView(C.addressof(fake), 3, 2, 4, 8, 4 * 8 * 4, 8 * 4, 4, 0)
+        setattr(w, field, value)
+        assert lib.cf_device_tensor_validate(C.byref(w)) != 0, field
+    kc = DeviceKvConfig(2, 4, 8, 8, 64, 2, 1)
+    d = C.c_void_p(lib.cf_device_kv_create(C.byref(kc)))
+    assert d.value
+    kn = DeviceKvCounters()
+    assert lib.cf_device_kv_get_counters(d, C.byref(kn)) == 0
+    assert kn.device_append_calls == 0 and kn.dense_fallback_launches == 0
+    lib.cf_device_kv_destroy(d, None)
+    kc.query_head_count = 7
+    assert lib.cf_device_kv_create(C.byref(kc)) is None
