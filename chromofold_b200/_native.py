@@ -86,6 +86,12 @@ EXPORTS = {
         "cf_device_seal_clear_async", "cf_device_seal_set_fault", "cf_device_seal_get_state",
         "cf_device_seal_get_counters", "cf_device_seal_last_error",
     ],
+    "compat_ms.h": [
+        "cf_ms_cuda_create", "cf_ms_cuda_destroy", "cf_ms_cuda_sequence_create", "cf_ms_cuda_sequence_remove_async",
+        "cf_ms_cuda_publish_page_async", "cf_ms_cuda_stage_active_async", "cf_ms_cuda_copy_sequence_async",
+        "cf_ms_cuda_shift_sequence", "cf_ms_cuda_execute_batch_async", "cf_ms_cuda_cancel_sequence_async",
+        "cf_ms_cuda_reclaim_async", "cf_ms_cuda_audit", "cf_ms_cuda_get_counters", "cf_ms_cuda_last_error",
+    ],
     "compat_adapter.h": [
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",
         "cf_llama_kv_attention", "cf_llama_kv_attention_host", "cf_llama_kv_flush", "cf_llama_kv_seq_rm",

@@ -1,0 +1,110 @@
+// engine_common.cuh — pieces shared by the fronts of the reference's device ABIs (device_engine.cu, ms_resolver.cu):
+// a grow-only device buffer, typed strided loads and stores, and the row-conversion kernels.
+#ifndef CHROMOFOLD_B200_ENGINE_COMMON_CUH
+#define CHROMOFOLD_B200_ENGINE_COMMON_CUH
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "chromofold_b200/compat_device.h"
+#include "chromofold_b200/sealed_kv.h"
+
+namespace cfb_engine {
+
+inline void cuda_check(cudaError_t e, const char *what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+inline size_t scalar_bytes(uint32_t type) {
+    return type == CF_DEVICE_F16 || type == CF_DEVICE_BF16 ? 2 : type == CF_DEVICE_F32 ? 4 : 0;
+}
+
+template <class T>
+struct Buffer {  // grow-only device array; growing copies the old contents
+    T *ptr = nullptr;
+    size_t count = 0;
+    Buffer() = default;
+    Buffer(const Buffer &) = delete;
+    Buffer &operator=(const Buffer &) = delete;
+    ~Buffer() { if (ptr) cudaFree(ptr); }
+    void ensure(size_t wanted, cudaStream_t s) {
+        if (wanted <= count) return;
+        const size_t next = std::max(wanted, count * 2);
+        T *fresh = nullptr;
+        cuda_check(cudaMalloc(reinterpret_cast<void **>(&fresh), next * sizeof(T)), "cudaMalloc");
+        cuda_check(cudaMemsetAsync(fresh, 0, next * sizeof(T), s), "cudaMemsetAsync");
+        if (ptr) {
+            cuda_check(cudaMemcpyAsync(fresh, ptr, count * sizeof(T), cudaMemcpyDeviceToDevice, s), "cudaMemcpyAsync");
+            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            cudaFree(ptr);
+        }
+        ptr = fresh;
+        count = next;
+    }
+    size_t bytes() const { return count * sizeof(T); }
+};
+
+__device__ __forceinline__ float load_scalar(const void *base, uint64_t byte_offset, uint32_t type) {
+    const char *p = static_cast<const char *>(base) + byte_offset;
+    if (type == CF_DEVICE_F16) return __half2float(*reinterpret_cast<const __half *>(p));
+    if (type == CF_DEVICE_BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
+    return *reinterpret_cast<const float *>(p);
+}
+
+__device__ __forceinline__ void store_scalar(void *base, uint64_t byte_offset, uint32_t type, float v) {
+    char *p = static_cast<char *>(base) + byte_offset;
+    if (type == CF_DEVICE_F16) *reinterpret_cast<__half *>(p) = __float2half_rn(v);
+    else if (type == CF_DEVICE_BF16) *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(v);
+    else *reinterpret_cast<float *>(p) = v;
+}
+
+// Strided [token][head][dim] rows of any scalar type -> the engine's fp32 tail [head][capacity][dim], starting at
+// tail row `row0` (the job of the reference's convert_to_active, src/cuda/device_kv_dataplane.cu:49-70, with the
+// head-major order the sealer and the attention tail reader use).
+static __global__ void rows_to_tail_kernel(cf_device_tensor_view view, float *tail, uint32_t capacity, uint32_t row0) {
+    const uint64_t count = static_cast<uint64_t>(view.token_count) * view.head_count * view.head_dim;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint32_t d = i % view.head_dim, h = (i / view.head_dim) % view.head_count;
+    const uint32_t t = i / (static_cast<uint64_t>(view.head_dim) * view.head_count);
+    const float v = load_scalar(view.data, t * view.token_stride_bytes + h * view.head_stride_bytes + d * view.element_stride_bytes,
+                                view.scalar_type);
+    tail[(static_cast<uint64_t>(h) * capacity + row0 + t) * view.head_dim + d] = v;
+}
+
+// Strided typed view -> contiguous fp32 [token][head][dim]; and back for outputs.
+static __global__ void view_to_dense_kernel(cf_device_tensor_view view, float *dense) {
+    const uint64_t count = static_cast<uint64_t>(view.token_count) * view.head_count * view.head_dim;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint32_t d = i % view.head_dim, h = (i / view.head_dim) % view.head_count;
+    const uint32_t t = i / (static_cast<uint64_t>(view.head_dim) * view.head_count);
+    dense[i] = load_scalar(view.data, t * view.token_stride_bytes + h * view.head_stride_bytes + d * view.element_stride_bytes,
+                           view.scalar_type);
+}
+static __global__ void dense_to_view_kernel(const float *dense, void *out, uint32_t type, uint32_t tokens, uint32_t heads,
+                                     uint32_t dim, uint64_t ts, uint64_t hs, uint64_t es) {
+    const uint64_t count = static_cast<uint64_t>(tokens) * heads * dim;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint32_t d = i % dim, h = (i / dim) % heads;
+    const uint32_t t = i / (static_cast<uint64_t>(dim) * heads);
+    store_scalar(out, t * ts + h * hs + d * es, type, dense[i]);
+}
+
+inline uint32_t choose_tile_tokens(uint32_t page_size, uint32_t head_dim) {
+    const uint32_t limit = CF_B200_MAX_STREAM_SYMBOLS / head_dim;
+    for (uint32_t t = std::min(page_size, limit); t >= 1; --t)
+        if (page_size % t == 0) return t;
+    return 1;
+}
+
+
+}  // namespace cfb_engine
+
+#endif

@@ -1,0 +1,716 @@
+// ms_resolver.cu — the reference's device sequence resolver ABI (include/chromofold_b200/compat_ms.h) on this
+// library's multi-sequence page store. Host semantics follow src/cuda/multisequence_cuda_resolver.cu (shared pages
+// with logical / in-flight references, snapshots released on events, deferred reclamation, copy-on-write tails);
+// the data path is new: pages are format-v1 records in one arena, every sequence has a row in a device page table,
+// and a batch is one cf_b200_sealed_attention_async launch per layer instead of one kernel per item.
+
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "chromofold_b200/compat_ms.h"
+#include "engine_common.cuh"
+
+using namespace cfb_engine;
+
+namespace {
+
+constexpr uint32_t kMaxBatchTokens = 2048;
+
+struct PageRef { uint64_t page_id; int64_t logical_begin; uint32_t tokens; uint32_t first_tile, tiles; };
+struct SharedPage {
+    uint64_t logical_refs = 0, in_flight_refs = 0, resident_bytes = 0, seal_generation = 0;
+    bool retired = false;
+    std::vector<uint32_t> store_ids;  // page ids of its tiles in the arena's directory
+};
+struct LayerSeq {
+    std::vector<PageRef> pages;
+    uint32_t sealed_tokens = 0, tiles = 0;
+    bool partial_last = false;
+    uint32_t active_begin = 0, active_count = 0;
+    uint64_t active_generation = 0, descriptor_generation = 0;
+};
+struct Sequence {
+    int64_t id = 0;
+    uint32_t slot = 0;
+    bool dispatchable = true;
+    uint64_t topology_generation = 0;
+    std::vector<LayerSeq> layers;
+};
+struct Snapshot { int64_t sequence_id; uint32_t layer; std::vector<uint64_t> page_ids; };
+struct Pending { Snapshot snapshot; cudaEvent_t event = nullptr; };
+
+// Reference int4 page (all kv heads): value = (nibble - 8) * scale[flat / block_size], flat = (token*Hkv + head)*D + d,
+// two nibbles per byte, low nibble first (src/cuda/device_kv_seal_attention.cu:106-118). Written as fp32 rows into
+// a scratch tail [kv head][capacity][dim].
+__global__ void unpack_reference_page_kernel(cf_device_page_descriptor page, float *tail_k, float *tail_v, uint32_t capacity) {
+    const uint64_t count = static_cast<uint64_t>(page.token_count) * page.kv_head_count * page.head_dim;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint32_t d = i % page.head_dim, h = (i / page.head_dim) % page.kv_head_count;
+    const uint32_t t = i / (static_cast<uint64_t>(page.head_dim) * page.kv_head_count);
+    const uint32_t shift = (i & 1) ? 4u : 0u;
+    const float k = static_cast<float>(static_cast<int>((page.key_payload[i >> 1] >> shift) & 0xfu) - 8) * page.key_scales[i / page.block_size];
+    const float v = static_cast<float>(static_cast<int>((page.value_payload[i >> 1] >> shift) & 0xfu) - 8) * page.value_scales[i / page.block_size];
+    const uint64_t dst = (static_cast<uint64_t>(h) * capacity + t) * page.head_dim + d;
+    tail_k[dst] = k;
+    tail_v[dst] = v;
+}
+
+struct ItemIo {   // one batch item's query view and output placement, as the gather / scatter kernels see them
+    cf_device_tensor_view query;
+    void *output;
+    uint32_t output_type, first_row;
+    uint64_t ots, ohs, oes;
+};
+
+__global__ void gather_queries_kernel(const ItemIo *items, float *dense, uint32_t heads, uint32_t dim) {
+    const ItemIo it = items[blockIdx.y];
+    const uint64_t count = static_cast<uint64_t>(it.query.token_count) * heads * dim;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t d = i % dim, h = (i / dim) % heads;
+        const uint32_t t = i / (static_cast<uint64_t>(dim) * heads);
+        dense[static_cast<uint64_t>(it.first_row) * heads * dim + i] = load_scalar(
+            it.query.data, t * it.query.token_stride_bytes + h * it.query.head_stride_bytes + d * it.query.element_stride_bytes,
+            it.query.scalar_type);
+    }
+}
+__global__ void scatter_outputs_kernel(const ItemIo *items, const float *dense, uint32_t heads, uint32_t dim) {
+    const ItemIo it = items[blockIdx.y];
+    const uint64_t count = static_cast<uint64_t>(it.query.token_count) * heads * dim;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t d = i % dim, h = (i / dim) % heads;
+        const uint32_t t = i / (static_cast<uint64_t>(dim) * heads);
+        store_scalar(it.output, t * it.ots + h * it.ohs + d * it.oes, it.output_type,
+                     dense[static_cast<uint64_t>(it.first_row) * heads * dim + i]);
+    }
+}
+
+}  // namespace
+
+struct cf_ms_cuda_resolver {
+    cf_ms_cuda_config config{};
+    mutable std::mutex mutex;
+    std::map<int64_t, Sequence> sequences;
+    std::unordered_map<uint64_t, SharedPage> pages;
+    std::vector<Pending> pending;
+    std::vector<uint32_t> free_slots;
+    uint64_t next_page_id = 1;
+    uint32_t next_slot = 0;
+    cf_ms_cuda_counters counters{};
+    std::string error;
+    // device side
+    uint32_t tile = 0, tiles_per_page = 0, slot_capacity = 0, stride = 256;
+    uint32_t next_store_id = 1;
+    std::vector<uint32_t> free_store_ids;
+    uint64_t records = 0;
+    std::vector<bool> calibrated;
+    bool ready = false;
+    Buffer<uint8_t> arena, workspace;
+    Buffer<uint64_t> page_dir;
+    Buffer<uint32_t> page_table, sealed, tails, jobs, status, slot_list, positions;   // tables are [layer][slot]
+    Buffer<float> tail_k, tail_v, scratch_k, scratch_v, q_dense, o_dense;          // tails are [layer][slot][Hkv][page][D]
+    Buffer<cf_b200_codebook_tables> tables;
+    Buffer<unsigned long long> cursor;
+    Buffer<ItemIo> item_io;
+
+    size_t page_values() const { return static_cast<size_t>(config.kv_head_count) * config.page_size * config.head_dim; }
+    size_t max_record_bytes() const { return 16 + 2 * ((static_cast<size_t>(tile) * config.head_dim + 15) / 16 * 16); }
+    size_t row(uint32_t layer, uint32_t slot) const { return static_cast<size_t>(layer) * slot_capacity + slot; }
+
+    void ensure_ready(cudaStream_t s) {
+        if (ready) return;
+        tile = choose_tile_tokens(config.page_size, config.head_dim);
+        tiles_per_page = config.page_size / tile;
+        calibrated.assign(config.layer_count, false);
+        tables.ensure(2 * config.layer_count, s);
+        cursor.ensure(513, s);
+        status.ensure(1, s);
+        jobs.ensure(4 * 64, s);
+        arena.ensure(16u << 20, s);
+        page_dir.ensure(static_cast<size_t>(4096) * config.kv_head_count, s);
+        scratch_k.ensure(page_values(), s);
+        scratch_v.ensure(page_values(), s);
+        slot_list.ensure(kMaxBatchTokens, s);
+        positions.ensure(kMaxBatchTokens, s);
+        item_io.ensure(1024, s);
+        q_dense.ensure(static_cast<size_t>(kMaxBatchTokens) * config.query_head_count * config.head_dim, s);
+        o_dense.ensure(q_dense.count, s);
+        cf_b200_sealed_attention_desc d{};
+        d.kv_head_count = config.kv_head_count;
+        d.query_head_count = config.query_head_count;
+        d.head_dim = config.head_dim;
+        d.seq_count = kMaxBatchTokens;
+        uint64_t bytes = 0;
+        cf_b200_sealed_attention_workspace_bytes(&d, 65536, &bytes);
+        workspace.ensure(bytes + 256, s);
+        ready = true;
+        grow_slots(std::max(16u, next_slot), s);
+    }
+
+    // Tables are laid out [layer][slot]; growing the slot count re-strides them.
+    void grow_slots(uint32_t wanted, cudaStream_t s) {
+        if (wanted <= slot_capacity) return;
+        uint32_t next = std::max(16u, slot_capacity);
+        while (next < wanted) next *= 2;
+        const uint32_t L = config.layer_count, old = slot_capacity;
+        auto restride = [&](auto &buf, size_t per_slot) {
+            using T = std::remove_pointer_t<decltype(buf.ptr)>;
+            Buffer<T> fresh;
+            fresh.ensure(static_cast<size_t>(L) * next * per_slot, s);
+            if (old)
+                cuda_check(cudaMemcpy2DAsync(fresh.ptr, next * per_slot * sizeof(T), buf.ptr, old * per_slot * sizeof(T),
+                                             old * per_slot * sizeof(T), L, cudaMemcpyDeviceToDevice, s), "re-stride table");
+            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            std::swap(fresh.ptr, buf.ptr);
+            std::swap(fresh.count, buf.count);
+        };
+        restride(page_table, stride);
+        restride(sealed, 1);
+        restride(tails, 1);
+        restride(tail_k, page_values());
+        restride(tail_v, page_values());
+        slot_capacity = next;
+    }
+
+    void grow_stride(uint32_t wanted, cudaStream_t s) {
+        if (wanted <= stride) return;
+        uint32_t next = stride;
+        while (next < wanted) next *= 2;
+        Buffer<uint32_t> fresh;
+        const size_t rows = static_cast<size_t>(config.layer_count) * slot_capacity;
+        fresh.ensure(rows * next, s);
+        cuda_check(cudaMemcpy2DAsync(fresh.ptr, next * 4, page_table.ptr, stride * 4, stride * 4, rows, cudaMemcpyDeviceToDevice, s),
+                   "widen page table");
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+        std::swap(fresh.ptr, page_table.ptr);
+        std::swap(fresh.count, page_table.count);
+        stride = next;
+        ++counters.descriptor_table_rebuilds;
+    }
+
+    uint32_t take_slot(cudaStream_t s) {
+        if (!free_slots.empty()) { const uint32_t v = free_slots.back(); free_slots.pop_back(); return v; }
+        const uint32_t slot = next_slot++;
+        if (ready) grow_slots(next_slot, s);
+        return slot;
+    }
+
+    void push_scalars(const Sequence &q, uint32_t layer, cudaStream_t s) {
+        const LayerSeq &L = q.layers[layer];
+        cuda_check(cudaMemcpyAsync(sealed.ptr + row(layer, q.slot), &L.sealed_tokens, 4, cudaMemcpyHostToDevice, s), "sealed count");
+        cuda_check(cudaMemcpyAsync(tails.ptr + row(layer, q.slot), &L.active_count, 4, cudaMemcpyHostToDevice, s), "tail count");
+    }
+
+    void release_snapshot(const Snapshot &snap) {
+        for (uint64_t id : snap.page_ids) {
+            auto p = pages.find(id);
+            if (p == pages.end() || p->second.in_flight_refs == 0) throw std::runtime_error("snapshot reference underflow");
+            --p->second.in_flight_refs;
+            --counters.in_flight_page_references;
+        }
+        ++counters.snapshots_released;
+    }
+};
+
+namespace {
+
+template <class Fn>
+int locked(cf_ms_cuda_resolver *r, bool count_cuda_error, Fn &&fn) {
+    std::lock_guard<std::mutex> guard(r->mutex);
+    try {
+        fn();
+        r->error.clear();
+        return 0;
+    } catch (const std::exception &e) {
+        if (count_cuda_error) ++r->counters.cuda_errors;
+        r->error = e.what();
+        return -1;
+    }
+}
+
+Sequence &find_sequence(cf_ms_cuda_resolver *r, int64_t id, const char *what) {
+    auto it = r->sequences.find(id);
+    if (it == r->sequences.end()) throw std::runtime_error(what);
+    return it->second;
+}
+
+void retire_if_unreferenced(cf_ms_cuda_resolver *r, SharedPage &page) {
+    if (page.logical_refs != 0 || page.retired) return;
+    page.retired = true;
+    ++r->counters.pages_retired;
+    r->counters.pending_reclamation_bytes += page.resident_bytes;
+    r->counters.pending_reclamation_bytes_peak = std::max(r->counters.pending_reclamation_bytes_peak, r->counters.pending_reclamation_bytes);
+}
+
+}  // namespace
+
+extern "C" cf_ms_cuda_resolver *cf_ms_cuda_create(const cf_ms_cuda_config *c) {
+    if (!c || !c->layer_count || !c->kv_head_count || !c->query_head_count || !c->head_dim || !c->page_size ||
+        !c->gqa_group_size || c->query_head_count != c->kv_head_count * c->gqa_group_size || c->head_dim > CF_KV_MAX_HEAD_DIM ||
+        c->gqa_group_size > 16)
+        return nullptr;
+    try {
+        auto *r = new cf_ms_cuda_resolver();
+        r->config = *c;
+        return r;
+    } catch (...) {
+        return nullptr;
+    }
+}
+
+extern "C" void cf_ms_cuda_destroy(cf_ms_cuda_resolver *r, void *stream) {
+    if (!r) return;
+    if (r->ready) cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    for (auto &p : r->pending)
+        if (p.event) cudaEventDestroy(p.event);
+    delete r;
+}
+
+extern "C" int cf_ms_cuda_sequence_create(cf_ms_cuda_resolver *r, int64_t id) {
+    if (!r) return -1;
+    return locked(r, false, [&] {
+        if (r->sequences.count(id)) throw std::runtime_error("sequence already exists");
+        Sequence q;
+        q.id = id;
+        q.slot = r->take_slot(nullptr);
+        q.layers.resize(r->config.layer_count);
+        r->sequences.emplace(id, std::move(q));
+    });
+}
+
+extern "C" int cf_ms_cuda_publish_page_async(cf_ms_cuda_resolver *r, const cf_ms_page_publication *pub, void *stream) {
+    if (!r || !pub) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    try {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        auto it = r->sequences.find(pub->sequence_id);
+        if (it == r->sequences.end() || pub->layer >= it->second.layers.size()) throw std::runtime_error("publication target is invalid");
+        const cf_device_page_descriptor &d = pub->descriptor;
+        if (!d.key_payload || !d.value_payload || !d.key_scales || !d.value_scales) throw std::runtime_error("publication descriptor is incomplete");
+        if (d.kv_head_count != r->config.kv_head_count || d.head_dim != r->config.head_dim || d.token_count == 0 ||
+            d.token_count > r->config.page_size || d.block_size == 0)
+            throw std::runtime_error("publication descriptor does not match the resolver topology");
+        Sequence &q = it->second;
+        LayerSeq &L = q.layers[pub->layer];
+        if (L.partial_last) throw std::runtime_error("a short page can only be the last page of a layer");
+        if (d.token_begin != L.sealed_tokens) throw std::runtime_error("published page must continue the sealed history of the layer");
+        r->ensure_ready(s);
+        const uint32_t n = (d.token_count + r->tile - 1) / r->tile;
+        r->grow_stride(L.tiles + n, s);
+        r->records += static_cast<uint64_t>(n) * r->config.kv_head_count;
+        r->arena.ensure(r->records * r->max_record_bytes() + 4096, s);
+        // transcode: int4 page -> fp32 scratch rows -> format-v1 records
+        const uint64_t count = static_cast<uint64_t>(d.token_count) * d.kv_head_count * d.head_dim;
+        unpack_reference_page_kernel<<<static_cast<int>((count + 255) / 256), 256, 0, s>>>(d, r->scratch_k.ptr, r->scratch_v.ptr,
+                                                                                         r->config.page_size);
+        cuda_check(cudaGetLastError(), "page unpack launch");
+        SharedPage page;
+        std::vector<uint32_t> host(4 * n);
+        for (uint32_t j = 0; j < n; ++j) {
+            uint32_t id;
+            if (!r->free_store_ids.empty()) { id = r->free_store_ids.back(); r->free_store_ids.pop_back(); }
+            else id = r->next_store_id++;
+            page.store_ids.push_back(id);
+            host[j] = 0;
+            host[n + j] = id;
+            host[2 * n + j] = std::min(r->tile, d.token_count - j * r->tile);
+            host[3 * n + j] = j * r->tile;
+        }
+        r->page_dir.ensure(static_cast<size_t>(r->next_store_id + 1) * r->config.kv_head_count, s);
+        r->jobs.ensure(4 * n, s);
+        cuda_check(cudaMemcpyAsync(r->jobs.ptr, host.data(), host.size() * 4, cudaMemcpyHostToDevice, s), "upload seal jobs");
+        cf_b200_seal_desc sd{};
+        sd.struct_size = sizeof sd;
+        sd.abi_version = CF_B200_ABI_VERSION;
+        sd.kv_head_count = r->config.kv_head_count;
+        sd.head_dim = r->config.head_dim;
+        sd.page_tokens = r->tile;
+        sd.block_size = 64;
+        sd.coder = CF_B200_CODER_RANS;
+        sd.codebook_id = pub->layer;
+        sd.k_tables = r->tables.ptr + 2 * pub->layer;
+        sd.v_tables = r->tables.ptr + 2 * pub->layer + 1;
+        sd.tail_k = r->scratch_k.ptr;
+        sd.tail_v = r->scratch_v.ptr;
+        sd.tail_type = CF_B200_F32;
+        sd.tail_capacity = r->config.page_size;
+        sd.job_slots = r->jobs.ptr;
+        sd.job_pages = r->jobs.ptr + n;
+        sd.job_tokens = r->jobs.ptr + 2 * n;
+        sd.job_rows = r->jobs.ptr + 3 * n;
+        sd.job_count = n;
+        sd.arena = r->arena.ptr;
+        sd.arena_units = r->arena.count / 16;
+        sd.arena_cursor_units = r->cursor.ptr;
+        sd.page_dir = r->page_dir.ptr;
+        sd.status = r->status.ptr;
+        if (!r->calibrated[pub->layer]) {
+            cuda_check(cudaMemsetAsync(r->cursor.ptr + 1, 0, 512 * sizeof(unsigned long long), s), "clear histograms");
+            if (cf_b200_histogram_async(&sd, r->cursor.ptr + 1, r->cursor.ptr + 257, s) != CF_OK) throw std::runtime_error("histogram launch rejected");
+            unsigned long long hist[512];
+            cuda_check(cudaMemcpyAsync(hist, r->cursor.ptr + 1, sizeof hist, cudaMemcpyDeviceToHost, s), "read histograms");
+            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            std::vector<cf_b200_codebook_tables> tables(2);
+            uint64_t hk[256], hv[256];
+            for (int i = 0; i < 256; ++i) { hk[i] = hist[i]; hv[i] = hist[256 + i]; }
+            if (cf_b200_codebook_build(hk, &tables[0]) != CF_OK || cf_b200_codebook_build(hv, &tables[1]) != CF_OK)
+                throw std::runtime_error("codebook build failed");
+            cuda_check(cudaMemcpyAsync(r->tables.ptr + 2 * pub->layer, tables.data(), 2 * sizeof(cf_b200_codebook_tables),
+                                       cudaMemcpyHostToDevice, s), "upload codebooks");
+            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            r->calibrated[pub->layer] = true;
+        }
+        if (cf_b200_seal_pages_async(&sd, s) != CF_OK) throw std::runtime_error("seal launch rejected");
+        cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(pub->layer, q.slot) * r->stride + L.tiles, host.data() + n, n * 4,
+                                   cudaMemcpyHostToDevice, s), "publish page ids");
+        page.seal_generation = pub->seal_generation;
+        page.resident_bytes = pub->resident_bytes;
+        page.logical_refs = 1;
+        const uint64_t id = r->next_page_id++;
+        L.pages.push_back({id, static_cast<int64_t>(d.token_begin), d.token_count, L.tiles, n});
+        r->pages.emplace(id, std::move(page));
+        L.tiles += n;
+        L.sealed_tokens += d.token_count;
+        L.partial_last = d.token_count % r->tile != 0;
+        if (L.active_count && L.active_begin < L.sealed_tokens) L.active_count = 0;  // the staged rows were this page
+        ++L.descriptor_generation;
+        r->push_scalars(q, pub->layer, s);
+        ++q.topology_generation;
+        ++r->counters.pages_registered;
+        ++r->counters.descriptor_tables_built;
+        r->error.clear();
+        return 0;
+    } catch (const std::exception &e) {
+        ++r->counters.page_registration_failures;
+        r->error = e.what();
+        return -1;
+    }
+}
+
+extern "C" int cf_ms_cuda_stage_active_async(cf_ms_cuda_resolver *r, int64_t id, uint32_t layer, uint32_t token_begin,
+                                             const float *keys, const float *values, uint32_t token_count, void *stream) {
+    if (!r || !keys || !values || !token_count || token_count > r->config.page_size) return -1;
+    return locked(r, true, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        auto it = r->sequences.find(id);
+        if (it == r->sequences.end() || layer >= it->second.layers.size()) throw std::runtime_error("active target is invalid");
+        Sequence &q = it->second;
+        LayerSeq &L = q.layers[layer];
+        if (token_begin != L.sealed_tokens) throw std::runtime_error("active rows must continue the sealed history of the layer");
+        r->ensure_ready(s);
+        cf_device_tensor_view view{};
+        view.scalar_type = CF_DEVICE_F32;
+        view.token_count = token_count;
+        view.head_count = r->config.kv_head_count;
+        view.head_dim = r->config.head_dim;
+        view.element_stride_bytes = 4;
+        view.head_stride_bytes = 4ull * view.head_dim;
+        view.token_stride_bytes = view.head_stride_bytes * view.head_count;
+        const uint64_t count = static_cast<uint64_t>(token_count) * view.head_count * view.head_dim;
+        const int blocks = static_cast<int>((count + 255) / 256);
+        const size_t base = r->row(layer, q.slot) * r->page_values();
+        view.data = keys;
+        rows_to_tail_kernel<<<blocks, 256, 0, s>>>(view, r->tail_k.ptr + base, r->config.page_size, 0);
+        view.data = values;
+        rows_to_tail_kernel<<<blocks, 256, 0, s>>>(view, r->tail_v.ptr + base, r->config.page_size, 0);
+        cuda_check(cudaGetLastError(), "stage sequence active rows");
+        L.active_begin = token_begin;
+        L.active_count = token_count;
+        ++L.active_generation;
+        r->push_scalars(q, layer, s);
+    });
+}
+
+extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t source_id, int64_t destination_id, void *stream) {
+    if (!r || source_id == destination_id) return -1;
+    return locked(r, true, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        Sequence &src = find_sequence(r, source_id, "source sequence is missing");
+        Sequence candidate;
+        candidate.id = destination_id;
+        auto old = r->sequences.find(destination_id);
+        if (old != r->sequences.end()) {  // the old destination is replaced: its pages lose one reference each
+            old->second.dispatchable = false;
+            for (auto &layer : old->second.layers)
+                for (const auto &ref : layer.pages) {
+                    SharedPage &page = r->pages.at(ref.page_id);
+                    --page.logical_refs;
+                    retire_if_unreferenced(r, page);
+                }
+            candidate.slot = old->second.slot;
+        } else {
+            candidate.slot = r->take_slot(s);
+        }
+        const Sequence &source = r->sequences.at(source_id);  // take_slot may have re-strided, not re-hashed: still valid
+        candidate.layers = source.layers;
+        for (uint32_t layer = 0; layer < r->config.layer_count; ++layer) {
+            LayerSeq &L = candidate.layers[layer];
+            for (const auto &ref : L.pages) ++r->pages.at(ref.page_id).logical_refs;
+            if (r->ready) {
+                if (L.tiles)
+                    cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(layer, candidate.slot) * r->stride,
+                                               r->page_table.ptr + r->row(layer, source.slot) * r->stride, L.tiles * 4ull,
+                                               cudaMemcpyDeviceToDevice, s), "copy page table row");
+                if (L.active_count) {  // the unsealed rows are the only bytes that are copied
+                    const size_t bytes = r->page_values() * sizeof(float);
+                    cuda_check(cudaMemcpyAsync(r->tail_k.ptr + r->row(layer, candidate.slot) * r->page_values(),
+                                               r->tail_k.ptr + r->row(layer, source.slot) * r->page_values(), bytes,
+                                               cudaMemcpyDeviceToDevice, s), "copy active K");
+                    cuda_check(cudaMemcpyAsync(r->tail_v.ptr + r->row(layer, candidate.slot) * r->page_values(),
+                                               r->tail_v.ptr + r->row(layer, source.slot) * r->page_values(), bytes,
+                                               cudaMemcpyDeviceToDevice, s), "copy active V");
+                    ++L.active_generation;
+                    ++r->counters.copy_on_write_tail_copies;
+                }
+                r->push_scalars(candidate, layer, s);
+            }
+            ++r->counters.descriptor_tables_built;
+        }
+        (void)src;
+        r->sequences[destination_id] = std::move(candidate);
+    });
+}
+
+extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_ms_batch_item *items, uint32_t item_count,
+                                              void *stream) {
+    if (!r || !items || !item_count) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::lock_guard<std::mutex> guard(r->mutex);
+    std::vector<Snapshot> snapshots;
+    try {
+        // validate everything and take every snapshot before the first launch (:381-390)
+        uint32_t total_rows = 0;
+        for (uint32_t i = 0; i < item_count; ++i) {
+            const cf_ms_batch_item &it = items[i];
+            if (cf_device_tensor_validate(&it.query) != 0 || !it.output || !scalar_bytes(it.output_type))
+                throw std::runtime_error("invalid batch tensor");
+            auto q = r->sequences.find(it.sequence_id);
+            if (q == r->sequences.end() || !q->second.dispatchable) throw std::runtime_error("sequence is unavailable for dispatch");
+            if (it.layer >= q->second.layers.size()) throw std::runtime_error("layer out of range");
+            if (it.query.head_count != r->config.query_head_count || it.query.head_dim != r->config.head_dim)
+                throw std::runtime_error("query topology mismatch");
+            total_rows += it.query.token_count;
+        }
+        if (total_rows > kMaxBatchTokens || item_count > 1024) throw std::runtime_error("batch is larger than the resolver's staging buffers");
+        for (uint32_t i = 0; i < item_count; ++i) {
+            Snapshot snap{items[i].sequence_id, items[i].layer, {}};
+            for (const auto &ref : r->sequences.at(items[i].sequence_id).layers[items[i].layer].pages) {
+                SharedPage &page = r->pages.at(ref.page_id);
+                ++page.in_flight_refs;
+                ++r->counters.in_flight_page_references;
+                snap.page_ids.push_back(ref.page_id);
+            }
+            ++r->counters.snapshots_acquired;
+            snapshots.push_back(std::move(snap));
+        }
+        ++r->counters.server_batches_received;
+        r->counters.tokens_per_batch_peak = std::max<uint64_t>(r->counters.tokens_per_batch_peak, item_count);
+        r->ensure_ready(s);
+
+        // rows of the batch, grouped by layer: [layer 0 items..., layer 1 items..., ...]
+        std::vector<ItemIo> io(item_count);
+        std::vector<uint32_t> slots, positions, order;
+        std::vector<std::pair<uint32_t, uint32_t>> layer_rows(r->config.layer_count, {0u, 0u});  // first row, count
+        for (uint32_t layer = 0; layer < r->config.layer_count; ++layer) {
+            layer_rows[layer].first = static_cast<uint32_t>(slots.size());
+            for (uint32_t i = 0; i < item_count; ++i) {
+                const cf_ms_batch_item &it = items[i];
+                if (it.layer != layer) continue;
+                io[i] = ItemIo{it.query, it.output, it.output_type, static_cast<uint32_t>(slots.size()),
+                               it.output_token_stride_bytes, it.output_head_stride_bytes, it.output_element_stride_bytes};
+                const uint32_t slot = r->sequences.at(it.sequence_id).slot;
+                for (uint32_t t = 0; t < it.query.token_count; ++t) {
+                    slots.push_back(slot);
+                    positions.push_back(it.query_token_begin + t);
+                }
+                if (it.query.token_count == 1) ++r->counters.decode_items; else ++r->counters.prefill_items;
+            }
+            layer_rows[layer].second = static_cast<uint32_t>(slots.size()) - layer_rows[layer].first;
+        }
+        cuda_check(cudaMemcpyAsync(r->item_io.ptr, io.data(), io.size() * sizeof(ItemIo), cudaMemcpyHostToDevice, s), "upload batch items");
+        cuda_check(cudaMemcpyAsync(r->slot_list.ptr, slots.data(), slots.size() * 4, cudaMemcpyHostToDevice, s), "upload batch slots");
+        cuda_check(cudaMemcpyAsync(r->positions.ptr, positions.data(), positions.size() * 4, cudaMemcpyHostToDevice, s), "upload batch positions");
+        const uint32_t Hq = r->config.query_head_count, D = r->config.head_dim;
+        gather_queries_kernel<<<dim3(8, item_count), 256, 0, s>>>(r->item_io.ptr, r->q_dense.ptr, Hq, D);
+        cuda_check(cudaGetLastError(), "query gather launch");
+        float softmax_scale = items[0].softmax_scale;
+        uint32_t window = items[0].causal_window;
+        for (uint32_t i = 1; i < item_count; ++i)
+            if (items[i].softmax_scale != softmax_scale || items[i].causal_window != window)
+                throw std::runtime_error("items of one batch must share softmax_scale and causal_window");
+        for (uint32_t layer = 0; layer < r->config.layer_count; ++layer) {
+            const auto [first, count] = layer_rows[layer];
+            if (!count) continue;
+            cf_b200_sealed_attention_desc d{};
+            d.struct_size = sizeof d;
+            d.abi_version = CF_B200_ABI_VERSION;
+            d.kv_head_count = r->config.kv_head_count;
+            d.query_head_count = Hq;
+            d.head_dim = D;
+            d.page_tokens = r->tile;
+            d.block_size = 64;
+            d.codebook_id = layer;
+            d.arena = r->arena.ptr;
+            d.page_dir = r->page_dir.ptr;
+            d.page_table = r->page_table.ptr + r->row(layer, 0) * r->stride;
+            d.seq_sealed_tokens = r->sealed.ptr + r->row(layer, 0);
+            d.seq_slots = r->slot_list.ptr + first;
+            d.page_table_stride = r->stride;
+            d.seq_count = count;
+            d.k_tables = r->tables.ptr + 2 * layer;
+            d.v_tables = r->tables.ptr + 2 * layer + 1;
+            d.tail_k = r->tail_k.ptr + r->row(layer, 0) * r->page_values();
+            d.tail_v = r->tail_v.ptr + r->row(layer, 0) * r->page_values();
+            d.tail_tokens = r->tails.ptr + r->row(layer, 0);
+            d.tail_type = CF_B200_F32;
+            d.tail_capacity = r->config.page_size;
+            d.query_positions = r->positions.ptr + first;
+            d.queries = r->q_dense.ptr + static_cast<size_t>(first) * Hq * D;
+            d.output = r->o_dense.ptr + static_cast<size_t>(first) * Hq * D;
+            d.query_type = CF_B200_F32;
+            d.output_type = CF_B200_F32;
+            d.softmax_scale = softmax_scale;
+            d.causal_window = window;
+            const uintptr_t ws = reinterpret_cast<uintptr_t>(r->workspace.ptr), aligned = (ws + 255) / 256 * 256;
+            d.workspace = reinterpret_cast<void *>(aligned);
+            d.workspace_bytes = r->workspace.count - (aligned - ws);
+            d.status = r->status.ptr;
+            if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("multi-sequence attention launch rejected");
+            ++r->counters.sequence_attention_launches;
+        }
+        scatter_outputs_kernel<<<dim3(8, item_count), 256, 0, s>>>(r->item_io.ptr, r->o_dense.ptr, Hq, D);
+        cuda_check(cudaGetLastError(), "output scatter launch");
+        for (auto &snap : snapshots) {
+            Pending p;
+            p.snapshot = std::move(snap);
+            cuda_check(cudaEventCreateWithFlags(&p.event, cudaEventDisableTiming), "create snapshot release event");
+            cuda_check(cudaEventRecord(p.event, s), "record snapshot release event");
+            r->pending.push_back(std::move(p));
+            ++r->counters.snapshot_release_events;
+        }
+        ++r->counters.compressed_batches_executed;
+        r->error.clear();
+        return 0;
+    } catch (const std::exception &e) {
+        for (const auto &snap : snapshots) {
+            try { r->release_snapshot(snap); } catch (...) {}
+        }
+        ++r->counters.cuda_errors;
+        r->error = e.what();
+        return -1;
+    }
+}
+
+extern "C" int cf_ms_cuda_cancel_sequence_async(cf_ms_cuda_resolver *r, int64_t id, void *) {
+    if (!r) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    auto q = r->sequences.find(id);
+    if (q == r->sequences.end()) return -1;
+    q->second.dispatchable = false;
+    ++r->counters.cancellation_requests;
+    return 0;
+}
+
+extern "C" int cf_ms_cuda_sequence_remove_async(cf_ms_cuda_resolver *r, int64_t id, void *) {
+    if (!r) return -1;
+    return locked(r, false, [&] {
+        Sequence &q = find_sequence(r, id, "sequence is missing");
+        for (auto &layer : q.layers)
+            for (const auto &ref : layer.pages) {
+                SharedPage &page = r->pages.at(ref.page_id);
+                if (!page.logical_refs) throw std::runtime_error("page logical reference underflow");
+                --page.logical_refs;
+                retire_if_unreferenced(r, page);
+            }
+        r->free_slots.push_back(q.slot);
+        r->sequences.erase(id);
+    });
+}
+
+extern "C" int cf_ms_cuda_reclaim_async(cf_ms_cuda_resolver *r, void *stream) {
+    if (!r) return -1;
+    return locked(r, true, [&] {
+        for (auto it = r->pending.begin(); it != r->pending.end();) {
+            const cudaError_t status = cudaEventQuery(it->event);
+            if (status == cudaErrorNotReady) { ++it; continue; }
+            cuda_check(status, "query snapshot release event");
+            r->release_snapshot(it->snapshot);
+            cudaEventDestroy(it->event);
+            it = r->pending.erase(it);
+        }
+        for (auto it = r->pages.begin(); it != r->pages.end();) {
+            SharedPage &page = it->second;
+            if (page.retired && page.logical_refs == 0 && page.in_flight_refs == 0) {
+                // the directory rows of its tiles go back to "not there" and the ids can be handed out again; the
+                // record bytes stay in the arena until it is rebuilt
+                for (uint32_t id : page.store_ids) {
+                    if (r->ready)
+                        cuda_check(cudaMemsetAsync(r->page_dir.ptr + static_cast<size_t>(id) * r->config.kv_head_count, 0,
+                                                   r->config.kv_head_count * sizeof(uint64_t), static_cast<cudaStream_t>(stream)),
+                                   "clear directory rows");
+                    r->free_store_ids.push_back(id);
+                }
+                r->counters.pending_reclamation_bytes -= page.resident_bytes;
+                ++r->counters.pages_reclaimed;
+                it = r->pages.erase(it);
+            } else {
+                ++it;
+            }
+        }
+    });
+}
+
+extern "C" int cf_ms_cuda_shift_sequence(cf_ms_cuda_resolver *r, int64_t id, uint32_t begin, uint32_t end, int32_t delta) {
+    if (!r || end < begin) return -1;
+    return locked(r, false, [&] {
+        Sequence &q = find_sequence(r, id, "sequence is missing");
+        for (auto &layer : q.layers)
+            for (auto &ref : layer.pages) {
+                const int64_t ref_end = ref.logical_begin + r->config.page_size;
+                if (ref.logical_begin >= begin && ref_end <= end) {
+                    if (delta != 0) throw std::runtime_error("sealed records carry no position: a non-zero shift needs a re-seal");
+                } else if (ref.logical_begin < end && ref_end > begin) {
+                    throw std::runtime_error("shift intersects part of an immutable page");
+                }
+            }
+        ++q.topology_generation;
+    });
+}
+
+extern "C" int cf_ms_cuda_audit(const cf_ms_cuda_resolver *r) {
+    if (!r) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    std::unordered_map<uint64_t, uint64_t> observed;
+    std::unordered_map<uint32_t, int> slots;
+    for (const auto &[id, q] : r->sequences) {
+        if (id != q.id || ++slots[q.slot] > 1) return -1;
+        for (const auto &layer : q.layers) {
+            uint32_t tokens = 0;
+            for (const auto &ref : layer.pages) {
+                auto page = r->pages.find(ref.page_id);
+                if (page == r->pages.end() || page->second.retired) return -1;
+                ++observed[ref.page_id];
+                tokens += ref.tokens;
+            }
+            if (tokens != layer.sealed_tokens) return -1;
+        }
+    }
+    for (const auto &[id, page] : r->pages)
+        if (!page.retired && page.logical_refs != observed[id]) return -1;
+    return r->counters.cross_sequence_contamination == 0 && r->counters.dense_fallback_launches == 0 ? 0 : -1;
+}
+
+extern "C" int cf_ms_cuda_get_counters(const cf_ms_cuda_resolver *r, cf_ms_cuda_counters *out) {
+    if (!r || !out) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    *out = r->counters;
+    return 0;
+}
+
+extern "C" const char *cf_ms_cuda_last_error(const cf_ms_cuda_resolver *r) {
+    return r ? r->error.c_str() : "null multi-sequence CUDA resolver";
+}

@@ -92,6 +92,40 @@ class DeviceSealCounters(C.Structure):
         "peak_owned_bytes")]
 
 
+class PageDescriptor(C.Structure):
+    _fields_ = [("key_payload", _vp), ("value_payload", _vp), ("key_scales", _vp), ("value_scales", _vp)] + [
+        (n, _u32) for n in ("token_begin", "token_count", "kv_head_count", "head_dim", "block_size", "blocks_per_page")] + [
+        (n, _u64) for n in ("key_payload_bytes", "value_payload_bytes", "resident_bytes", "generation")]
+
+
+class MsConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "kv_head_count", "query_head_count", "head_dim", "page_size",
+                                    "gqa_group_size", "use_async_allocator")]
+
+
+class MsPublication(C.Structure):
+    _fields_ = [("sequence_id", C.c_int64), ("layer", _u32), ("descriptor", PageDescriptor), ("resident_bytes", _u64),
+                ("seal_generation", _u64)]
+
+
+class MsBatchItem(C.Structure):
+    _fields_ = [("sequence_id", C.c_int64), ("layer", _u32), ("query", TensorView), ("output", _vp), ("output_type", _u32),
+                ("output_token_stride_bytes", _u64), ("output_head_stride_bytes", _u64), ("output_element_stride_bytes", _u64),
+                ("query_token_begin", _u32), ("softmax_scale", _f32), ("causal_window", _u32)]
+
+
+class MsCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in (
+        "pages_registered", "page_registration_failures", "descriptor_tables_built", "descriptor_table_rebuilds",
+        "snapshots_acquired", "snapshots_released", "in_flight_page_references", "snapshot_release_events",
+        "stale_snapshot_rejections", "server_batches_received", "compressed_batches_executed",
+        "sequence_attention_launches", "prefill_items", "decode_items", "tokens_per_batch_peak",
+        "copy_on_write_tail_copies", "cancellation_requests", "pages_retired", "pages_reclaimed",
+        "pending_reclamation_bytes", "pending_reclamation_bytes_peak", "cross_sequence_contamination",
+        "dense_fallback_launches", "cuda_errors")]
+
+
+assert C.sizeof(PageDescriptor) == 88 and C.sizeof(MsPublication) == 120 and C.sizeof(MsBatchItem) == 128
 assert C.sizeof(TensorView) == 56 and C.sizeof(DeviceSealCounters) == 29 * 8 and C.sizeof(DeviceKvCounters) == 24 * 8
 assert C.sizeof(PageView) == 168 and C.sizeof(CacheLayout) == 72 and C.sizeof(DevicePage) == 104
 assert C.sizeof(PagedAttentionDesc) == 96 and C.sizeof(SoftmaxState) == 32

@@ -183,3 +183,31 @@ def test_device_engine_contracts_without_a_gpu(native):
     lib.cf_device_kv_destroy(d, None)
     kc.query_head_count = 7
     assert lib.cf_device_kv_create(C.byref(kc)) is None
+
+
+def test_sequence_resolver_contract_without_a_gpu(native):
+    """tests/m10_cuda_sequence_resolver_contract.cpp: create, duplicate rejection, a shift that moves nothing, cancel,
+    audit, counters — no CUDA call is made."""
+    from compat_types import MsConfig, MsCounters
+    lib = native.lib()
+    lib.cf_ms_cuda_create.restype = C.c_void_p
+    lib.cf_ms_cuda_last_error.restype = C.c_char_p
+    r = C.c_void_p(lib.cf_ms_cuda_create(C.byref(MsConfig(2, 2, 4, 64, 64, 2, 0))))
+    assert r.value
+    assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(101)) == 0
+    assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(202)) == 0
+    assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(101)) != 0
+    assert b"already exists" in lib.cf_ms_cuda_last_error(r)
+    assert lib.cf_ms_cuda_shift_sequence(r, C.c_int64(101), 0, 0, 0) == 0
+    assert lib.cf_ms_cuda_cancel_sequence_async(r, C.c_int64(202), None) == 0
+    assert lib.cf_ms_cuda_cancel_sequence_async(r, C.c_int64(303), None) == -1
+    assert lib.cf_ms_cuda_audit(r) == 0
+    n = MsCounters()
+    assert lib.cf_ms_cuda_get_counters(r, C.byref(n)) == 0
+    assert n.cancellation_requests == 1 and n.dense_fallback_launches == 0 and n.cross_sequence_contamination == 0
+    assert lib.cf_ms_cuda_sequence_remove_async(r, C.c_int64(101), None) == 0
+    assert lib.cf_ms_cuda_sequence_remove_async(r, C.c_int64(101), None) == -1
+    assert lib.cf_ms_cuda_copy_sequence_async(r, C.c_int64(5), C.c_int64(5), None) == -1
+    lib.cf_ms_cuda_destroy(r, None)
+    assert lib.cf_ms_cuda_create(C.byref(MsConfig(2, 2, 5, 64, 64, 2, 0))) is None
+    assert lib.cf_ms_cuda_last_error(None) == b"null multi-sequence CUDA resolver"
