@@ -215,6 +215,128 @@ __global__ void compat_rans_decode_kernel(const uint8_t *data, const int32_t *by
     }
 }
 
+// ---- flat (non-paged) windowed attention over block-Huffman K / V: the reference's M6 entry points -------------------
+// (src/cuda/fused_kv_attention.cu:26-161). One block per query row. Both entry points run the SAME arithmetic in the
+// same order — scores by one thread per window row, serial over channels; output by one thread per channel, serial
+// over window rows — so the fused result equals the decode-then-dense result bit for bit, as the reference promises
+// for its own pair. The fused kernel decodes the window's rows to symbols in shared memory (never to global memory).
+constexpr int kFlatThreads = 128;
+
+// Bit position of flat element `flat`: its block's offset plus a skip-decode inside the block (fused_kv_attention.cu:16-23).
+__device__ uint32_t flat_row_position(const uint32_t *words, const int32_t *boff, const int32_t *lut, int maxlen, int block,
+                                      long flat) {
+    const int b = static_cast<int>(flat / block);
+    uint32_t bit = static_cast<uint32_t>(boff[b]);
+    const int skip = static_cast<int>(flat - static_cast<long>(b) * block);
+    for (int i = 0; i < skip; ++i) {
+        const uint32_t w = bit >> 5, off = bit & 31u;
+        uint32_t window = words[w] << off;
+        if (off + maxlen > 32u) window |= words[w + 1] >> (32u - off);
+        bit += static_cast<uint32_t>(lut[window >> (32u - maxlen)]) >> 8;
+    }
+    return bit;
+}
+
+template <class Emit>
+__device__ void flat_decode_row(const uint32_t *words, const int32_t *lut, int maxlen, uint32_t bit, int dim, Emit emit) {
+    for (int c = 0; c < dim; ++c) {
+        const uint32_t w = bit >> 5, off = bit & 31u;
+        uint32_t window = words[w] << off;
+        if (off + maxlen > 32u) window |= words[w + 1] >> (32u - off);
+        const uint32_t e = static_cast<uint32_t>(lut[window >> (32u - maxlen)]);
+        emit(c, static_cast<int>(e & 0xffu));
+        bit += e >> 8;
+    }
+}
+
+struct FlatArgs {
+    const uint32_t *kw, *vw;
+    const int32_t *kb, *kl, *vb, *vl;
+    int kmax, vmax;
+    const float *kscale, *vscale, *Q, *Kd, *Vd;
+    float *out;
+    int seq, dim, nq, window, block, zero;
+    float sscale;
+};
+
+template <bool kFused>
+__global__ void __launch_bounds__(kFlatThreads) flat_attention_kernel(FlatArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float *q = reinterpret_cast<float *>(smem);                        // [dim]
+    float *sc = q + CF_KV_MAX_HEAD_DIM;                                 // [window]
+    uint8_t *ksym = reinterpret_cast<uint8_t *>(sc + CF_KV_MAX_WINDOW); // [window][dim]   (fused only)
+    uint8_t *vsym = ksym + static_cast<size_t>(a.window) * a.dim;
+    __shared__ float s_inv;
+    const int i = blockIdx.x, tid = threadIdx.x;
+    const int lo = max(0, i - a.window + 1), nk = i - lo + 1;
+    for (int c = tid; c < a.dim; c += kFlatThreads) q[c] = a.Q[static_cast<long>(i) * a.dim + c];
+    if (kFused) {
+        for (int job = tid; job < 2 * nk; job += kFlatThreads) {
+            const int jj = job >> 1, j = lo + jj;
+            if (job & 1) {
+                const uint32_t bit = flat_row_position(a.vw, a.vb, a.vl, a.vmax, a.block, static_cast<long>(j) * a.dim);
+                flat_decode_row(a.vw, a.vl, a.vmax, bit, a.dim, [&](int c, int s) { vsym[jj * a.dim + c] = static_cast<uint8_t>(s); });
+            } else {
+                const uint32_t bit = flat_row_position(a.kw, a.kb, a.kl, a.kmax, a.block, static_cast<long>(j) * a.dim);
+                flat_decode_row(a.kw, a.kl, a.kmax, bit, a.dim, [&](int c, int s) { ksym[jj * a.dim + c] = static_cast<uint8_t>(s); });
+            }
+        }
+    }
+    __syncthreads();
+    auto k_at = [&](int jj, int c) {
+        return kFused ? static_cast<float>(static_cast<int>(ksym[jj * a.dim + c]) - a.zero) * a.kscale[c]
+                      : a.Kd[static_cast<long>(lo + jj) * a.dim + c];
+    };
+    auto v_at = [&](int jj, int c) {
+        return kFused ? static_cast<float>(static_cast<int>(vsym[jj * a.dim + c]) - a.zero) * a.vscale[lo + jj]
+                      : a.Vd[static_cast<long>(lo + jj) * a.dim + c];
+    };
+    for (int jj = tid; jj < nk; jj += kFlatThreads) {
+        float s = 0.0f;
+        for (int c = 0; c < a.dim; ++c) s += q[c] * k_at(jj, c);
+        sc[jj] = s * a.sscale;
+    }
+    __syncthreads();
+    if (tid == 0) {  // serial max and sum: the order is part of the bit-identity contract
+        float mx = -1e30f;
+        for (int jj = 0; jj < nk; ++jj) mx = fmaxf(mx, sc[jj]);
+        float sum = 0.0f;
+        for (int jj = 0; jj < nk; ++jj) {
+            sc[jj] = expf(sc[jj] - mx);
+            sum += sc[jj];
+        }
+        s_inv = 1.0f / sum;
+    }
+    __syncthreads();
+    for (int c = tid; c < a.dim; c += kFlatThreads) {
+        float acc = 0.0f;
+        for (int jj = 0; jj < nk; ++jj) acc += (sc[jj] * s_inv) * v_at(jj, c);
+        a.out[static_cast<long>(i) * a.dim + c] = acc;
+    }
+}
+
+// Decode-then-dense stage 1: one thread per row writes dequantised fp32 rows (fused_kv_attention.cu:69-81).
+__global__ void flat_decode_dense_kernel(const uint32_t *words, const int32_t *boff, const int32_t *lut, int maxlen, int block,
+                                         int seq, int dim, int zero, const float *scale, int per_token, float *dense) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= seq) return;
+    const uint32_t bit = flat_row_position(words, boff, lut, maxlen, block, static_cast<long>(j) * dim);
+    flat_decode_row(words, lut, maxlen, bit, dim, [&](int c, int s) {
+        dense[static_cast<long>(j) * dim + c] = static_cast<float>(s - zero) * (per_token ? scale[j] : scale[c]);
+    });
+}
+
+cf_status flat_validate(const void *kw, const void *kb, const void *kl, int kmax, const void *vw, const void *vb,
+                        const void *vl, int vmax, const void *kscale, const void *vscale, const void *Q, const void *out,
+                        int seq, int dim, int nq, int window, int block, float sscale) {  // fused_kv_attention.cu:115-126
+    if (!kw || !kb || !kl || !vw || !vb || !vl || !kscale || !vscale || !Q || !out) return CF_ERR_INVALID_ARGUMENT;
+    if (seq <= 0 || dim <= 0 || nq < 0 || nq > seq || window <= 0 || block <= 0 || kmax <= 0 || vmax <= 0)
+        return CF_ERR_INVALID_ARGUMENT;
+    if (!(sscale == sscale) || sscale - sscale != 0.0f) return CF_ERR_INVALID_ARGUMENT;
+    if (dim > CF_KV_MAX_HEAD_DIM || window > CF_KV_MAX_WINDOW || kmax > 24 || vmax > 24) return CF_ERR_UNSUPPORTED;
+    return CF_OK;
+}
+
 bool finite_float(float v) { return v == v && v - v == 0.0f; }
 
 }  // namespace
@@ -256,5 +378,43 @@ extern "C" cf_status cf_rans_decode_async(const uint8_t *data, const int32_t *by
     const int blocks = (n + block - 1) / block;
     cfb::compat_rans_decode_kernel<<<(blocks + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         data, byte_off, state0, slot2sym, freq, cum, block, n, out);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}
+
+extern "C" cf_status cf_kv_attn_fused_async(const uint32_t *kw, const int32_t *kb, const int32_t *kl, int kmax,
+                                            const uint32_t *vw, const int32_t *vb, const int32_t *vl, int vmax,
+                                            const float *kscale, const float *vscale, const float *Q, float *out, int seq,
+                                            int dim, int nq, int window, int block, int zero, float sscale, void *stream) {
+    const cf_status valid = cfb::flat_validate(kw, kb, kl, kmax, vw, vb, vl, vmax, kscale, vscale, Q, out, seq, dim, nq, window,
+                                               block, sscale);
+    if (valid != CF_OK) return valid;
+    if (nq == 0) return CF_OK;
+    const cfb::FlatArgs a{kw, vw, kb, kl, vb, vl, kmax, vmax, kscale, vscale, Q, nullptr, nullptr, out,
+                          seq, dim, nq, window, block, zero, sscale};
+    const size_t smem = (CF_KV_MAX_HEAD_DIM + CF_KV_MAX_WINDOW) * sizeof(float) + 2 * static_cast<size_t>(window) * dim;
+    if (cudaFuncSetAttribute(cfb::flat_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+        return CF_ERR_CUDA;
+    cfb::flat_attention_kernel<true><<<nq, cfb::kFlatThreads, smem, static_cast<cudaStream_t>(stream)>>>(a);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}
+
+extern "C" cf_status cf_kv_attn_dense_async(const uint32_t *kw, const int32_t *kb, const int32_t *kl, int kmax,
+                                            const uint32_t *vw, const int32_t *vb, const int32_t *vl, int vmax,
+                                            const float *kscale, const float *vscale, const float *Q, float *Kd, float *Vd,
+                                            float *out, int seq, int dim, int nq, int window, int block, int zero,
+                                            float sscale, void *stream) {
+    const cf_status valid = cfb::flat_validate(kw, kb, kl, kmax, vw, vb, vl, vmax, kscale, vscale, Q, out, seq, dim, nq, window,
+                                               block, sscale);
+    if (valid != CF_OK) return valid;
+    if (!Kd || !Vd) return CF_ERR_INVALID_ARGUMENT;
+    if (nq == 0) return CF_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cfb::flat_decode_dense_kernel<<<(seq + 63) / 64, 64, 0, s>>>(kw, kb, kl, kmax, block, seq, dim, zero, kscale, 0, Kd);
+    cfb::flat_decode_dense_kernel<<<(seq + 63) / 64, 64, 0, s>>>(vw, vb, vl, vmax, block, seq, dim, zero, vscale, 1, Vd);
+    const cfb::FlatArgs a{kw, vw, kb, kl, vb, vl, kmax, vmax, kscale, vscale, Q, Kd, Vd, out,
+                          seq, dim, nq, window, block, zero, sscale};
+    const size_t smem = (CF_KV_MAX_HEAD_DIM + CF_KV_MAX_WINDOW) * sizeof(float);
+    cfb::flat_attention_kernel<false><<<nq, cfb::kFlatThreads, smem, s>>>(a);
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }

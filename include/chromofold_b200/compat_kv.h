@@ -100,6 +100,20 @@ cf_status cf_rans_decode_async(const uint8_t *data, const int32_t *byte_off, con
                                const int32_t *slot2sym, const int32_t *freq, const int32_t *cum, int block, int n,
                                int32_t *out, void *stream);
 
+/* ---- include/chromofold/chromofold.h:81-98 ------------------------------------------------------------ */
+/* Flat (non-paged) causal windowed attention over block-Huffman coded K / V (K per-channel, V per-token scales):
+ * query row i attends rows max(0, i-window+1) .. i. The fused call decodes inside the consumer; the dense call first
+ * writes fp32 K / V to the caller's scratch and runs the same arithmetic — both give bit-identical outputs
+ * (src/cuda/fused_kv_attention.cu:1-8). Bounds as in the reference: dim <= 128, window <= 512, nq <= seq. */
+cf_status cf_kv_attn_fused_async(const uint32_t *kw, const int32_t *kb, const int32_t *kl, int kmax, const uint32_t *vw,
+                                 const int32_t *vb, const int32_t *vl, int vmax, const float *kscale, const float *vscale,
+                                 const float *Q, float *out, int seq, int dim, int nq, int window, int block, int zero,
+                                 float sscale, void *stream);
+cf_status cf_kv_attn_dense_async(const uint32_t *kw, const int32_t *kb, const int32_t *kl, int kmax, const uint32_t *vw,
+                                 const int32_t *vb, const int32_t *vl, int vmax, const float *kscale, const float *vscale,
+                                 const float *Q, float *Kd, float *Vd, float *out, int seq, int dim, int nq, int window,
+                                 int block, int zero, float sscale, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -259,3 +259,64 @@ def test_adapter_round_trip(native, oracle, head_dim, coder, monkeypatch):
     assert lib.cf_llama_kv_get_stats(a, C.byref(st)) == 0 and st.appended_tokens == 0 and st.sealed_pages == 0
     assert lib.cf_llama_kv_append(a, 0, 0, 0, p(k[0, 0, :4]), p(v[0, 0, :4]), 4, None) == 0      # usable after clear
     lib.cf_llama_kv_destroy(a)
+
+
+@pytest.mark.parametrize("shape", [(64, 32, 64, 16, 64), (300, 128, 40, 512, 64), (97, 80, 97, 33, 100)], ids=str)
+def test_flat_fused_and_dense_attention(native, oracle, shape):
+    """cf_kv_attn_fused_async / cf_kv_attn_dense_async (include/chromofold/chromofold.h:81-98) on block-Huffman K / V
+    with per-channel K and per-token V scales: fused == dense bit for bit (src/cuda/fused_kv_attention.cu:1-8), both
+    match fp64 softmax attention, and match the reference's own kernels where oracle/_ref holds them."""
+    import torch
+    seq, dim, nq, window, block = shape
+    rng = np.random.default_rng(seq * 7 + dim)
+    ksym = (laplace_codes(rng, seq * dim, 9.0).astype(np.int16) + 128).astype(np.uint8)
+    vsym = (laplace_codes(rng, seq * dim, 14.0).astype(np.int16) + 128).astype(np.uint8)
+    kcb, vcb = oracle.codebook_from_hist(hist_of(ksym)), oracle.codebook_from_hist(hist_of(vsym))
+    kw, kb = oracle.huff_encode(ksym, block, kcb)
+    vw, vb = oracle.huff_encode(vsym, block, vcb)
+    kscale = rng.uniform(0.005, 0.02, dim).astype(np.float32)
+    vscale = rng.uniform(0.005, 0.02, seq).astype(np.float32)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    sscale = 1.0 / np.sqrt(dim)
+    kd = (ksym.astype(np.float32).reshape(seq, dim) - 128.0) * kscale[None, :]
+    vd = (vsym.astype(np.float32).reshape(seq, dim) - 128.0) * vscale[:, None]
+    positions = np.arange(nq)
+    firsts = np.maximum(0, positions - window + 1)
+    expect = _softmax_attention(kd[None], vd[None], q[:, None, :], positions, firsts, sscale, 1)[:, 0]
+
+    pad = np.zeros(2, np.uint32)
+    dev = [_dev(np.concatenate([kw, pad])), _dev(kb), _dev(kcb.np("lut")), _dev(np.concatenate([vw, pad])), _dev(vb),
+           _dev(vcb.np("lut")), _dev(kscale), _dev(vscale), _dev(q)]
+    p = [C.c_void_p(t.data_ptr()) for t in dev]
+    libs = [native.lib()] + ([oracle.ref_cuda()] if oracle.ref_cuda() is not None else [])
+    results = []
+    for lib in libs:
+        fused = torch.zeros((nq, dim), dtype=torch.float32, device="cuda")
+        dense = torch.zeros_like(fused)
+        kdd = torch.zeros((seq, dim), dtype=torch.float32, device="cuda")
+        vdd = torch.zeros_like(kdd)
+        tail = (C.c_int(seq), C.c_int(dim), C.c_int(nq), C.c_int(window), C.c_int(block), C.c_int(128), C.c_float(sscale),
+                None)
+        head = (p[0], p[1], p[2], C.c_int(12), p[3], p[4], p[5], C.c_int(12), p[6], p[7], p[8])
+        assert lib.cf_kv_attn_fused_async(*head, C.c_void_p(fused.data_ptr()), *tail) == 0
+        assert lib.cf_kv_attn_dense_async(*head, C.c_void_p(kdd.data_ptr()), C.c_void_p(vdd.data_ptr()),
+                                          C.c_void_p(dense.data_ptr()), *tail) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(fused, dense)
+        assert np.array_equal(kdd.cpu().numpy(), kd) and np.array_equal(vdd.cpu().numpy(), vd)
+        results.append(fused.cpu().numpy())
+        assert np.allclose(results[-1], expect, rtol=1e-4, atol=1e-5)
+    for r in results[1:]:
+        assert np.allclose(r, results[0], rtol=1e-5, atol=1e-6)
+
+    mine = native.lib()
+    out = torch.zeros((nq, dim), dtype=torch.float32, device="cuda")
+    head = (p[0], p[1], p[2], C.c_int(12), p[3], p[4], p[5], C.c_int(12), p[6], p[7], p[8], C.c_void_p(out.data_ptr()))
+
+    def call(seq_=seq, dim_=dim, nq_=nq, window_=window, block_=block, scale_=sscale, head_=head):
+        return mine.cf_kv_attn_fused_async(*head_, C.c_int(seq_), C.c_int(dim_), C.c_int(nq_), C.c_int(window_),
+                                           C.c_int(block_), C.c_int(128), C.c_float(scale_), None)
+    assert call(nq_=0) == 0
+    assert call(nq_=seq + 1) == 1 and call(window_=0) == 1 and call(block_=0) == 1 and call(scale_=float("nan")) == 1
+    assert call(head_=(None,) + head[1:]) == 1
+    assert call(dim_=129) == 2 and call(window_=513) == 2
