@@ -100,6 +100,11 @@ __device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
     return r;
 }
 
+// The low bytes of four table entries as one register, first symbol in byte 0: three byte permutes.
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3) {
+    return __byte_perm(__byte_perm(e0, e1, 0x0040), __byte_perm(e2, e3, 0x0040), 0x5410);
+}
+
 // ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
 // Both entropy decoders are written without branches so that the K chain and the V chain of a lane interleave in
 // one straight instruction stream. A 64-bit window holds the upcoming stream bits, top aligned; it is reloaded from
@@ -119,7 +124,7 @@ struct RansLane {
     __device__ __forceinline__ void reload() {
         pos += used >> 3;
         used = 0;
-        const uint32_t base = pos & ~3u, sel = 0x0123u + 0x1111u * (pos & 3u);
+        const uint32_t base = pos & ~3u, sel = imad(pos & 3u, 0x1111u, 0x0123u);
         uint32_t w0, w1, w2;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
         asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
@@ -127,12 +132,14 @@ struct RansLane {
         whi = __byte_perm(w0, w1, sel);
         wlo = __byte_perm(w1, w2, sel);
     }
-    // src/cuda/rans.cu:20-23. After the update the state is >= 2^11, so the `while (state < L)` loop of the
-    // reference runs 0, 1 or 2 times: exactly (clz(state) - 1) / 8 times. The bytes come out of the window.
+    // src/cuda/rans.cu:20-23: x = freq * (x >> 12) + (x & 4095) - cum, then bytes are shifted in while x < 2^23.
+    // The shared-memory table holds e = sym | (slot - cum) << 8 | freq << 20, so e >> 8 = (slot - cum) + freq * 4096
+    // and the update is freq * ((x >> 12) - 4096) + (e >> 8): no field of the entry needs masking.
+    // After the update the state is >= 2^11, so the reference's loop runs 0, 1 or 2 times: (clz(state) - 1) / 8.
     __device__ __forceinline__ uint32_t symbol() {
         uint32_t e;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(imad(x & (CF_B200_RANS_M - 1u), 4u, table)));
-        x = ((e >> 8) & 0xfffu) * (x >> CF_B200_RANS_PROB_BITS) + (e >> 20);
+        x = imad(e >> 20, imad(x >> CF_B200_RANS_PROB_BITS, 1u, 0u - CF_B200_RANS_M), e >> 8);
         const uint32_t shift = imad(static_cast<uint32_t>(__clz(x)), 1u, 0xffffffffu) & 24u;
         x = __funnelshift_l(whi, x, shift);
         whi = __funnelshift_l(wlo, whi, shift);
@@ -142,10 +149,8 @@ struct RansLane {
     }
     __device__ __forceinline__ uint32_t quad() {
         reload();
-        uint32_t q = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
-        return q;
+        const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
+        return pack_low_bytes(e0, e1, e2, e3);
     }
 };
 
@@ -183,10 +188,8 @@ struct HuffLane {
     }
     __device__ __forceinline__ uint32_t quad() {
         reload();
-        uint32_t q = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) q = __funnelshift_r(q, symbol(), 8);
-        return q;
+        const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
+        return pack_low_bytes(e0, e1, e2, e3);
     }
 };
 
@@ -219,11 +222,14 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, c
         } else {
             k.reload();
             v.reload();
+            uint32_t ke[4], ve[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {  // two independent decoder chains, interleaved symbol by symbol
-                kq = __funnelshift_r(kq, k.symbol(), 8);
-                vv = __funnelshift_r(vv, v.symbol(), 8);
+                ke[i] = k.symbol();
+                ve[i] = v.symbol();
             }
+            kq = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+            vv = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
         }
         u.vq[q] = vv;
         uint32_t lo, hi;
@@ -266,12 +272,12 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     {
         const uint4 *src;
         uint4 *dst;
-        src = reinterpret_cast<const uint4 *>(p.k_tables->rans_slot);
-        dst = reinterpret_cast<uint4 *>(k_slot);
-        for (uint32_t i = tid; i < 1024; i += kThreads) dst[i] = src[i];
-        src = reinterpret_cast<const uint4 *>(p.v_tables->rans_slot);
-        dst = reinterpret_cast<uint4 *>(v_slot);
-        for (uint32_t i = tid; i < 1024; i += kThreads) dst[i] = src[i];
+        // slot entries are re-packed for RansLane::symbol(): sym | (slot - cum) << 8 | freq << 20
+        auto repack = [](uint32_t e) { return (e & 0xffu) | ((e >> 20) << 8) | (((e >> 8) & 0xfffu) << 20); };
+        for (uint32_t i = tid; i < 4096; i += kThreads) {
+            k_slot[i] = repack(p.k_tables->rans_slot[i]);
+            v_slot[i] = repack(p.v_tables->rans_slot[i]);
+        }
         src = reinterpret_cast<const uint4 *>(p.k_tables->huff_lut);
         dst = reinterpret_cast<uint4 *>(k_lut);
         for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
