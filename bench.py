@@ -249,7 +249,8 @@ def main():
         everyone = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3)
         contexts = everyone[shard_sequences(everyone, world)[rank]]
     else:
-        contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3 + 1000 * rank)
+        # weak scaling: the same context-length multiset on every rank (fixed work per GPU), different codes and queries
+        contexts = uniform_contexts(a.batch, a.ctx_lo, a.ctx_hi, T, 3)
     n_local = len(contexts)
     layer, info = build_sealed_layer(contexts, query_heads=HQ, kv_heads=HKV, head_dim=D, page_tokens=T, block_size=BLOCK,
                                      coder=a.coder, dist=("laplace", a.laplace_b), seed=4 + 1000 * rank, device=device,
@@ -366,7 +367,7 @@ def main():
         "vs_baseline": None, "dtype": "u8 codes, f16 mma operands, f32 accumulate", "data": "synthetic",
         "config": {"workload": workload_name(a), "global_batch": a.batch * world if a.scaling == "weak" else a.batch,
                    "seq_tokens_per_step": tokens_total,
-                   "sharding": (f"sequences, {a.batch} per GPU, no collective" if a.scaling == "weak" else
+                   "sharding": (f"sequences, {a.batch} per GPU, same context lengths on every GPU, no collective" if a.scaling == "weak" else
                                 f"{a.batch} sequences bin-packed over {world} GPUs by context length, no collective"), "l2": "inputs larger than L2 (sealed bytes per GPU "
                    f"{info['sealed_bytes'] / 1e9:.2f} GB vs 126 MB)", "kernel": a.kernel,
                    "h0_bits_per_code": {"k": info["h0_bits_k"], "v": info["h0_bits_v"]},

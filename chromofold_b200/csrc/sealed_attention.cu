@@ -261,11 +261,13 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
 // ---------------------------------------------------------------------------------------------------------------
 // Combine: merge the chunk partials of one (sequence, query head) with the unsealed tail and write the output.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kCombineThreads = 128;
+constexpr int kCombineThreads = 256;
+constexpr int kCombineWarps = kCombineThreads / 32;
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParams p) {
     extern __shared__ float tail_scores[];  // [tail_capacity]
-    __shared__ float s_red[kCombineThreads / 32];
+    __shared__ float s_m[kCombineWarps], s_l[kCombineWarps];
+    __shared__ float s_acc[kCombineWarps][128];
     const uint32_t seq = blockIdx.x;
     const uint32_t local_q = blockIdx.y;
     const uint32_t G = p.group, D = p.head_dim;
@@ -292,24 +294,43 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
     }
     __syncthreads();
 
-    float m = -CUDART_INF_F;
-    for (uint32_t c = c0 + tid; c < c1; c += kCombineThreads) m = fmaxf(m, partial_ptr(p, c, local_q)[0]);
-    for (uint32_t t = tid; t < tail; t += kCombineThreads) m = fmaxf(m, tail_scores[t]);
-    m = warp_max(m);
-    if (lane == 0) s_red[warp] = m;
+    // Chunk partials: every warp merges its share of the chunks in one pass (running max, rescale on the way), four
+    // channels per lane, so that many independent loads are in flight; the warps' results meet in shared memory.
+    {
+        float wm = -CUDART_INF_F, wl = 0.0f, wa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t c = c0 + warp; c < c1; c += kCombineWarps) {
+            const float *part = partial_ptr(p, c, local_q);
+            const float pm = part[0], pl = part[1];
+            float pa[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pa[j] = lane + 32u * j < D ? part[2 + lane + 32u * j] : 0.0f;
+            if (pm == -CUDART_INF_F) continue;
+            const float nm = fmaxf(wm, pm);
+            const float so = exp2f(wm - nm), sn = exp2f(pm - nm);  // wm = -inf gives so = 0
+            wl = wl * so + pl * sn;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wa[j] = wa[j] * so + pa[j] * sn;
+            wm = nm;
+        }
+        if (lane == 0) {
+            s_m[warp] = wm;
+            s_l[warp] = wl;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s_acc[warp][lane + 32 * j] = wa[j];
+    }
     __syncthreads();
-    m = s_red[0];
-    for (int w = 1; w < kCombineThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+    float m = -CUDART_INF_F;
+    for (int w = 0; w < kCombineWarps; ++w) m = fmaxf(m, s_m[w]);
+    for (uint32_t t = 0; t < tail; ++t) m = fmaxf(m, tail_scores[t]);
 
     float l = 0.0f, a = 0.0f;
     if (m != -CUDART_INF_F) {
-        for (uint32_t c = c0; c < c1; ++c) {
-            const float *part = partial_ptr(p, c, local_q);
-            const float pm = part[0];
-            if (pm == -CUDART_INF_F) continue;
-            const float w = exp2f(pm - m);
-            l += part[1] * w;
-            if (tid < D) a += part[2 + tid] * w;
+        for (int w = 0; w < kCombineWarps; ++w) {
+            if (s_m[w] == -CUDART_INF_F) continue;
+            const float sw = exp2f(s_m[w] - m);
+            l += s_l[w] * sw;
+            if (tid < D) a += s_acc[w][tid] * sw;
         }
         for (uint32_t t = 0; t < tail; ++t) {
             const float s = tail_scores[t];
