@@ -93,6 +93,11 @@ EXPORTS = {
         "cf_ms_cuda_shift_sequence", "cf_ms_cuda_execute_batch_async", "cf_ms_cuda_cancel_sequence_async",
         "cf_ms_cuda_reclaim_async", "cf_ms_cuda_audit", "cf_ms_cuda_get_counters", "cf_ms_cuda_last_error",
     ],
+    "compat_production.h": [
+        "cf_attention_runtime_create", "cf_attention_runtime_destroy", "cf_attention_execute_async",
+        "cf_attention_compare_async", "cf_attention_invalidate_graphs", "cf_attention_get_counters",
+        "cf_attention_last_error",
+    ],
     "compat_adapter.h": [
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",
         "cf_llama_kv_attention", "cf_llama_kv_attention_host", "cf_llama_kv_flush", "cf_llama_kv_seq_rm",

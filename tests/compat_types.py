@@ -129,3 +129,34 @@ assert C.sizeof(PageDescriptor) == 88 and C.sizeof(MsPublication) == 120 and C.s
 assert C.sizeof(TensorView) == 56 and C.sizeof(DeviceSealCounters) == 29 * 8 and C.sizeof(DeviceKvCounters) == 24 * 8
 assert C.sizeof(PageView) == 168 and C.sizeof(CacheLayout) == 72 and C.sizeof(DevicePage) == 104
 assert C.sizeof(PagedAttentionDesc) == 96 and C.sizeof(SoftmaxState) == 32
+
+
+class AttentionTuning(C.Structure):
+    _fields_ = [(n, _u32) for n in ("threads_per_block", "warps_per_block", "heads_per_block", "pages_per_work_unit",
+                                    "vector_width", "enable_cuda_graphs", "enable_async_sealing")]
+
+
+class AttentionRuntimeConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "query_head_count", "kv_head_count", "head_dim", "page_size",
+                                    "block_size", "gqa_group_size", "cuda_device", "use_async_allocator", "mode")] + [
+        ("tuning", AttentionTuning)]
+
+
+class AttentionBatchItem(C.Structure):
+    _fields_ = [("sequence_id", C.c_int64), ("layer", _u32), ("query", TensorView), ("output", _vp), ("output_type", _u32),
+                ("output_token_stride_bytes", _u64), ("output_head_stride_bytes", _u64),
+                ("output_element_stride_bytes", _u64), ("query_token_begin", _u32), ("softmax_scale", C.c_float),
+                ("causal_window", _u32), ("sealed_pages", _vp), ("sealed_page_count", _u32), ("active_keys", _vp),
+                ("active_values", _vp), ("active_token_begin", _u32), ("active_token_count", _u32)]
+
+
+ATTENTION_COUNTER_NAMES = (
+    "reference_launches", "optimized_launches", "decode_launches", "prefill_launches", "grouped_batches", "grouped_items",
+    "kernel_launches_avoided", "graph_captures", "graph_replays", "graph_invalidations", "graph_replay_failures",
+    "async_seal_submissions", "async_seal_overlaps", "descriptor_bytes_read", "compressed_payload_bytes_read",
+    "scale_bytes_read", "allocation_count", "pool_hits", "pool_misses", "peak_reserved_bytes", "peak_live_bytes",
+    "numerical_failures", "cross_sequence_contamination", "dense_fallback_launches", "cuda_errors")
+
+
+class AttentionCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in ATTENTION_COUNTER_NAMES]

@@ -211,3 +211,43 @@ def test_sequence_resolver_contract_without_a_gpu(native):
     lib.cf_ms_cuda_destroy(r, None)
     assert lib.cf_ms_cuda_create(C.byref(MsConfig(2, 2, 5, 64, 64, 2, 0))) is None
     assert lib.cf_ms_cuda_last_error(None) == b"null multi-sequence CUDA resolver"
+
+
+def test_production_runtime_contract_without_a_gpu(native):
+    """The cases of the reference's tests/m12_production_attention_contract.cpp: create / counters / invalidate /
+    destroy, plus the argument checks that come before any CUDA call."""
+    from compat_types import AttentionBatchItem, AttentionCounters, AttentionRuntimeConfig
+    lib = native.lib()
+    lib.cf_attention_runtime_create.restype = C.c_void_p
+    lib.cf_attention_last_error.restype = C.c_char_p
+    assert C.sizeof(AttentionBatchItem) == 168
+    cfg = AttentionRuntimeConfig()
+    cfg.layer_count, cfg.query_head_count, cfg.kv_head_count, cfg.head_dim = 2, 8, 2, 64
+    cfg.page_size, cfg.block_size, cfg.gqa_group_size, cfg.mode = 16, 64, 4, 1
+    assert lib.cf_attention_runtime_create(None) is None
+    bad = AttentionRuntimeConfig.from_buffer_copy(cfg)
+    bad.gqa_group_size = 3
+    assert lib.cf_attention_runtime_create(C.byref(bad)) is None   # query heads != kv heads * group
+    bad = AttentionRuntimeConfig.from_buffer_copy(cfg)
+    bad.head_dim = 0
+    assert lib.cf_attention_runtime_create(C.byref(bad)) is None
+    rt = C.c_void_p(lib.cf_attention_runtime_create(C.byref(cfg)))
+    assert rt.value
+    counters = AttentionCounters()
+    assert lib.cf_attention_get_counters(rt, C.byref(counters)) == 0
+    assert all(getattr(counters, n) == 0 for n, _ in AttentionCounters._fields_)
+    assert lib.cf_attention_invalidate_graphs(rt) == 0
+    assert lib.cf_attention_get_counters(rt, C.byref(counters)) == 0
+    assert counters.graph_invalidations == 1
+    assert lib.cf_attention_get_counters(rt, None) == -1 and lib.cf_attention_get_counters(None, C.byref(counters)) == -1
+    item = AttentionBatchItem()
+    assert lib.cf_attention_execute_async(rt, None, 1, None) == -1
+    assert lib.cf_attention_execute_async(rt, C.byref(item), 0, None) == -1
+    assert lib.cf_attention_execute_async(None, C.byref(item), 1, None) == -1
+    item.layer = 5
+    assert lib.cf_attention_execute_async(rt, C.byref(item), 1, None) == -1
+    assert b"layer" in lib.cf_attention_last_error(rt)
+    assert lib.cf_attention_compare_async(rt, C.byref(item), 1, C.c_float(0.0), C.c_float(1.0), None) == -1
+    assert lib.cf_attention_last_error(None) == b"runtime is null"
+    lib.cf_attention_runtime_destroy(rt, None)
+    lib.cf_attention_runtime_destroy(None, None)
