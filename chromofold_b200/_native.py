@@ -77,7 +77,7 @@ EXPORTS = {
         "cf_kv_validate_page", "cf_kv_validate_layout", "cf_kv_page_resident_bytes", "cf_kv_cache_memory_stats",
         "cf_online_softmax_init", "cf_online_softmax_accumulate", "cf_online_softmax_merge", "cf_online_softmax_finalize",
         "cf_kv_validate_paged_attention_desc", "cf_kv_paged_attention_async", "cf_rans_decode_async",
-        "cf_kv_attn_fused_async", "cf_kv_attn_dense_async",
+        "cf_kv_attn_fused_async", "cf_kv_attn_dense_async", "cf_delta_fetch_async",
     ],
     "compat_device.h": [
         "cf_device_tensor_validate", "cf_device_kv_create", "cf_device_kv_destroy", "cf_device_kv_append_async",

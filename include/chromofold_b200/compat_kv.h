@@ -114,6 +114,14 @@ cf_status cf_kv_attn_dense_async(const uint32_t *kw, const int32_t *kb, const in
                                  const float *Q, float *Kd, float *Vd, float *out, int seq, int dim, int nq, int window,
                                  int block, int zero, float sscale, void *stream);
 
+/* Token-id fetch from a reference/delta cluster (src/cuda/delta_apply.cu:30-44; cluster layout of
+ * tools/export_delta.py:13-17): out[i] = the override of leaf device_leaf[i] at position device_pos[i] if it has one
+ * (its dpos[dstart[leaf] .. +dlen[leaf]) is sorted ascending), else base[pos], else -1 when pos is past the base.
+ * All pointers are device pointers; dpos / dval may be NULL when every dlen is 0. */
+cf_status cf_delta_fetch_async(const int32_t *base, int nbase, const int32_t *dpos, const int32_t *dval,
+                               const int32_t *dstart, const int32_t *dlen, const int32_t *device_leaf,
+                               const int32_t *device_pos, int32_t *out, size_t count, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -172,6 +172,16 @@ def huffman_decode(ref, rng):
     np.savez_compressed(os.path.join(HERE, "huffman_decode.npz"), **out)
 
 
+def delta_cluster():
+    """A small reference/delta cluster frozen by the reference's own exporter (tools/export_delta.py, numpy only):
+    base + sparse per-member overrides + the original sequences the fetch must reproduce."""
+    import subprocess
+    ref_root = os.environ.get("CF_REFERENCE_ROOT", "/root/reference")
+    subprocess.run([sys.executable, os.path.join(ref_root, "tools", "export_delta.py"), os.path.join(HERE, "delta_cluster.cfdc"),
+                    "--members", "12", "--base", "600", "--divergence", "0.02", "--suffix", "24", "--vocab", "50000",
+                    "--seed", "7"], check=True)
+
+
 def main():
     ob.build(with_ref=True)
     ref = ob.ref_cpu()
@@ -181,8 +191,9 @@ def main():
     paged_attention(ref, rng)
     online_softmax(ref, rng)
     huffman_decode(ref, rng)
+    delta_cluster()
     for f in sorted(os.listdir(HERE)):
-        if f.endswith(".npz"):
+        if f.endswith(".npz") or f.endswith(".cfdc"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
