@@ -50,9 +50,10 @@ def entropy_bits(hist):
 
 def build_sealed_layer(contexts, *, query_heads=32, kv_heads=8, head_dim=128, page_tokens=16, block_size=64,
                        coder="rans", dist=("laplace", 12.0), seed=4, device="cuda:0", tiles_per_launch=2048,
-                       extra_pages_per_sequence=2, keep_dense=False):
+                       extra_pages_per_sequence=2, keep_dense=False, reserve_pages=0):
     """Seal `contexts[i]` tokens for slot i. Returns (layer, info). With keep_dense=True the binary16 tiles are also
-    kept as an uncompressed pool [page_id][kv_heads][page_tokens][head_dim] for the comparison kernel."""
+    kept as an uncompressed pool [page_id][kv_heads][page_tokens][head_dim] for the comparison kernel.
+    `reserve_pages` more pages (directory entries and arena room) are set aside for pages sealed later."""
     contexts = np.asarray(contexts, np.int64)
     assert np.all(contexts % page_tokens == 0)
     pages = contexts // page_tokens
@@ -61,8 +62,8 @@ def build_sealed_layer(contexts, *, query_heads=32, kv_heads=8, head_dim=128, pa
     max_record = 16 + 2 * ((head_dim * page_tokens + 15) // 16 * 16)
     layer = SealedKvLayer(kv_heads=kv_heads, query_heads=query_heads, head_dim=head_dim, page_tokens=page_tokens,
                           block_size=block_size, coder=CODERS[coder], max_sequences=len(contexts),
-                          max_pages_per_sequence=stride, max_pages=total + 2 + 2 * len(contexts),
-                          arena_bytes=(total + 2 * len(contexts)) * kv_heads * max_record + 4096, device=device)
+                          max_pages_per_sequence=stride, max_pages=total + 2 + 2 * len(contexts) + reserve_pages,
+                          arena_bytes=(total + 2 * len(contexts) + reserve_pages) * kv_heads * max_record + 4096, device=device)
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     draw = (lambda shape: laplace_codes(shape, dist[1], gen, device)) if dist[0] == "laplace" else (
