@@ -22,6 +22,8 @@
 
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "attention_params.cuh"
 
 namespace cfb {
@@ -33,10 +35,7 @@ namespace {
 constexpr int kWarps = CFB_LANES_WARPS;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kStageBytes = 4160;   // 16 header + 2 * 2048 payload max + 48 slack (decoders read ahead)
-constexpr uint32_t kScratchBytes = 512;  // P rows, high and low halves (2 x 4 heads x 16 tokens x 2 B) + alpha[4]
-constexpr uint32_t kWarpBytes = 2 * kStageBytes + kScratchBytes + 128;  // + 2 mbarriers (padded)
 constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
-constexpr uint32_t kSmemBytes = kTableBytes + kWarps * kWarpBytes;
 constexpr uint32_t kWaitSpins = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kMagic = 0x64646464u;       // fp16 1024.0 high byte, for the byte-permute conversion
@@ -203,16 +202,51 @@ struct FixedLane {
     __device__ __forceinline__ uint32_t quad() { return __byte_perm(*words++, 0u, 0x0123); }
 };
 
-// Per-warp running state of one unit.
+// Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
+template <int NG>
 struct UnitState {
-    float score[4];      // S fragment of the current page
-    float acc[4][4];     // O fragments: [channel of the lane's V block][fragment register]
-    uint32_t vq[16];     // V symbols of the current page, [channel*4 + token quad]
-    float m0, m1, l0, l1;  // running max / partial sum of the lane's two heads
+    float score[NG][4];      // S fragments of the current page
+    float acc[NG][4][4];     // O fragments: [group][channel of the lane's V block][fragment register]
+    uint32_t vq[16];         // V symbols of the current page, [channel*4 + token quad]
+    float m0[NG], m1[NG], l0[NG], l1[NG];  // running max / partial sum of the lane's two heads of each group
 };
 
-template <class KLane, class VLane>
-__device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, const uint32_t (&bq)[16][2]) {
+// Where a lane finds its B fragments of S = K * Q^T (column n = parity*4 + head; zero where the lane's slice of the
+// contraction belongs to the other token of the pair).
+//   QRegs: held in registers, one group of four heads.
+//   QSmem: the query rows of up to eight heads sit in the warp's shared memory as [head][half][64 channels] with a
+//   row stride of 36 words, which puts the eight rows one load touches into different banks; a lane reads two words
+//   of row (head g&3 of the group, half t&1), or of a zero row when the column is not its own.
+struct QRegs {
+    uint32_t bq[16][2];
+    template <int GRP>
+    __device__ __forceinline__ void get(int q, uint32_t &b0, uint32_t &b1) const {
+        b0 = bq[q][0];
+        b1 = bq[q][1];
+    }
+};
+struct QSmem {
+    uint32_t addr, group_stride;  // byte address of the lane's row for group 0; distance to the row for group 1 (0 on the zero row)
+    template <int GRP>
+    __device__ __forceinline__ void get(int q, uint32_t &b0, uint32_t &b1) const {
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr + GRP * group_stride + 8u * q));
+    }
+};
+
+template <int NG, class QSrc>
+__device__ __forceinline__ void score_quad(UnitState<NG> &u, const QSrc &qs, int q, uint32_t kq) {
+    uint32_t lo, hi, b0, b1;
+    quad_to_half2(kq, lo, hi);
+    qs.template get<0>(q, b0, b1);
+    mma_16816(u.score[0], lo, 0u, hi, 0u, b0, b1);
+    if constexpr (NG == 2) {
+        qs.template get<1>(q, b0, b1);
+        mma_16816(u.score[1], lo, 0u, hi, 0u, b0, b1);
+    }
+}
+
+template <class KLane, class VLane, int NG, class QSrc>
+__device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &u, const QSrc &qs) {
 #pragma unroll
     for (int q = 0; q < 16; ++q) {
         uint32_t kq = 0, vv = 0;
@@ -232,29 +266,43 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState &u, c
             vv = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
         }
         u.vq[q] = vv;
-        uint32_t lo, hi;
-        quad_to_half2(kq, lo, hi);
-        mma_16816(u.score, lo, 0u, hi, 0u, bq[q][0], bq[q][1]);
+        score_quad(u, qs, q, kq);
     }
 }
 
-template <class KLane>
-__device__ __forceinline__ void decode_k_only(KLane &k, UnitState &u, const uint32_t (&bq)[16][2]) {
+template <class KLane, int NG, class QSrc>
+__device__ __forceinline__ void decode_k_only(KLane &k, UnitState<NG> &u, const QSrc &qs) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-        uint32_t lo, hi;
-        quad_to_half2(k.quad(), lo, hi);
-        mma_16816(u.score, lo, 0u, hi, 0u, bq[q][0], bq[q][1]);
-    }
+    for (int q = 0; q < 16; ++q) score_quad(u, qs, q, k.quad());
 }
 
-template <class VLane>
-__device__ __forceinline__ void decode_v_only(VLane &v, UnitState &u) {
+template <class VLane, int NG>
+__device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
 #pragma unroll
     for (int q = 0; q < 16; ++q) u.vq[q] = v.quad();
 }
 
+// Shared memory of one warp: two record stages, the softmax scratch, two mbarriers and (NG = 2) the query rows.
+//   scratch: P rows fp16 high halves [4 NG][16] | low halves [4 NG][16] | 128 zero bytes | alpha[4 NG]
+template <int NG>
+struct WarpLayout {
+    static constexpr uint32_t kPBytes = 4 * NG * 16 * 2;
+    static constexpr uint32_t kPLo = 2 * kStageBytes + kPBytes;
+    static constexpr uint32_t kZero = kPLo + kPBytes;
+    static constexpr uint32_t kAlpha = kZero + 128;
+    static constexpr uint32_t kBars = kAlpha + 4 * NG * 4;
+    static constexpr uint32_t kQRows = kBars + 32;
+    static constexpr uint32_t kQRowWords = 36;
+    static constexpr uint32_t kBytes = (kQRows + (NG == 2 ? 16 * kQRowWords * 4 : 0) + 15u) / 16u * 16u;
+    static constexpr uint32_t kSmem = kTableBytes + kWarps * kBytes;
+};
+static_assert(WarpLayout<2>::kSmem <= 232448, "the eight-head kernel must fit the 227 KB of one CTA");
+
+template <int NG>
 __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
+    using L = WarpLayout<NG>;
+    using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
+    constexpr uint32_t kPassHeads = 4u * NG;
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t *k_slot = reinterpret_cast<uint32_t *>(smem);
     uint32_t *v_slot = k_slot + 4096;
@@ -262,34 +310,30 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     uint16_t *v_lut = k_lut + 4096;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    uint8_t *warp_mem = smem + kTableBytes + warp * kWarpBytes;
-    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);         // [4][16] fp16(p)
-    __half *p_rows_lo = p_rows + 64;                                                 // [4][16] fp16(p - fp16(p))
-    float *alpha_s = reinterpret_cast<float *>(warp_mem + 2 * kStageBytes + 448);    // [4]; bytes 256..447 stay zero
-    uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + 2 * kStageBytes + kScratchBytes);
+    uint8_t *warp_mem = smem + kTableBytes + warp * L::kBytes;
+    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);   // [4 NG][16] fp16(p)
+    __half *p_rows_lo = reinterpret_cast<__half *>(warp_mem + L::kPLo);        // [4 NG][16] fp16(p - fp16(p))
+    const __half *zero_row = reinterpret_cast<const __half *>(warp_mem + L::kZero);
+    float *alpha_s = reinterpret_cast<float *>(warp_mem + L::kAlpha);          // [4 NG]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + L::kBars);
+    uint32_t *q_rows = reinterpret_cast<uint32_t *>(warp_mem + L::kQRows);     // NG == 2 only
 
     // coding tables: once per CTA
     {
-        const uint4 *src;
-        uint4 *dst;
         // slot entries are re-packed for RansLane::symbol(): sym | (slot - cum) << 8 | freq << 20
         auto repack = [](uint32_t e) { return (e & 0xffu) | ((e >> 20) << 8) | (((e >> 8) & 0xfffu) << 20); };
         for (uint32_t i = tid; i < 4096; i += kThreads) {
             k_slot[i] = repack(p.k_tables->rans_slot[i]);
             v_slot[i] = repack(p.v_tables->rans_slot[i]);
         }
-        src = reinterpret_cast<const uint4 *>(p.k_tables->huff_lut);
-        dst = reinterpret_cast<uint4 *>(k_lut);
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.k_tables->huff_lut);
+        uint4 *dst = reinterpret_cast<uint4 *>(k_lut);
         for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
         src = reinterpret_cast<const uint4 *>(p.v_tables->huff_lut);
         dst = reinterpret_cast<uint4 *>(v_lut);
         for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
     }
-    {   // the zero row that inactive lanes read their P fragments from
-        uint32_t *zero = reinterpret_cast<uint32_t *>(warp_mem + 2 * kStageBytes + 256);
-        zero[lane] = 0u;
-        if (lane < 16) zero[32 + lane] = 0u;
-    }
+    reinterpret_cast<uint32_t *>(warp_mem + L::kZero)[lane] = 0u;   // the zero row inactive lanes read their fragments from
     if (lane == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
@@ -299,7 +343,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
     PlanHeader *hdr = plan_header(p);
     const uint32_t *prefix = chunk_prefix(p);
-    const uint32_t subgroups = (p.group + 3u) / 4u;   // four query heads per pass
+    const uint32_t subgroups = (p.group + kPassHeads - 1u) / kPassHeads;   // 4 NG query heads per pass
     const uint32_t unit_count = hdr->chunk_count * p.kv_head_span * subgroups;
     const uint32_t pages_per_unit = hdr->pages_per_unit;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -309,10 +353,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     const uint32_t q_head_of_col = g & 3u;                 // S columns: n = parity*4 + head
     const bool q_col_mine = (t >> 1) == (g >> 2);
     const uint32_t my_token = 2u * g + (t >> 1);           // S fragment: row g, this lane's token
-    const uint32_t my_head0 = 2u * (t & 1u);               // S fragment: this lane's two heads
-    const uint32_t o_head = g & 3u;                        // O fragments: all of this lane's outputs are one head
-    const uint32_t mask_lo = (t == (g >> 2)) ? 0xffffffffu : 0u;       // P rows with lane tag t
-    const uint32_t mask_hi = (t == (g >> 2) + 2u) ? 0xffffffffu : 0u;
+    const uint32_t my_head0 = 2u * (t & 1u);               // S fragment: this lane's two heads (of each group)
+    const uint32_t o_head = g & 3u;                        // O fragments: all of this lane's outputs are one head per group
+    const bool row_lo_mine = t == (g >> 2), row_hi_mine = t == (g >> 2) + 2u;   // P rows with lane tag t
 
     for (;;) {
         uint32_t unit = 0;
@@ -323,10 +366,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         const uint32_t chunk = (unit / subgroups) / p.kv_head_span;
         const uint32_t head_local = (unit / subgroups) % p.kv_head_span;
         const uint32_t kv_head = p.kv_head_begin + head_local;
-        const uint32_t G = min(4u, p.group - 4u * sub);                 // query heads served by this pass
-        const uint32_t q_head_base = kv_head * p.group + 4u * sub;     // first of them
-        const uint32_t out_head_base = head_local * p.group + 4u * sub;
-        const bool q_col_live = q_col_mine && q_head_of_col < G;
+        const uint32_t G = min(kPassHeads, p.group - kPassHeads * sub);       // query heads served by this pass
+        const uint32_t q_head_base = kv_head * p.group + kPassHeads * sub;    // first of them
+        const uint32_t out_head_base = head_local * p.group + kPassHeads * sub;
         const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
         const uint32_t slot = slot_of(p, seq);
         const uint32_t sealed = p.seq_sealed_tokens[slot];
@@ -340,29 +382,43 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         const uint32_t n_pages = page_end > page_begin ? page_end - page_begin : 0u;
         const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot) * p.page_table_stride;
 
-        // query fragments: B operand of S = K * Q^T, column n = parity*4 + head, zero where the lane's slice of
-        // the contraction belongs to the other token of the pair
-        uint32_t bq[16][2];
-        {
+        QSrc qs;
+        if constexpr (NG == 1) {
+            const bool live = q_col_mine && q_head_of_col < G;
             const __half *qrow = reinterpret_cast<const __half *>(p.queries) +
                                  (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base + q_head_of_col) * 128u +
                                  64u * (t & 1u);
 #pragma unroll
             for (int s = 0; s < 16; ++s) {
                 uint2 v = make_uint2(0u, 0u);
-                if (q_col_live) v = *reinterpret_cast<const uint2 *>(qrow + 4 * s);
-                bq[s][0] = v.x;
-                bq[s][1] = v.y;
+                if (live) v = *reinterpret_cast<const uint2 *>(qrow + 4 * s);
+                qs.bq[s][0] = v.x;
+                qs.bq[s][1] = v.y;
             }
+        } else {
+            const uint32_t *qsrc = reinterpret_cast<const uint32_t *>(
+                reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * 128u);
+            __syncwarp();  // the previous unit's readers are done
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {   // 8 heads x 64 words; row = head*2 + half
+                const uint32_t i = lane + 32u * j, head = i >> 6;
+                q_rows[(i >> 5) * L::kQRowWords + (i & 31u)] = head < G ? qsrc[i] : 0u;
+            }
+            __syncwarp();
+            qs.addr = q_col_mine ? smem_addr(q_rows + (q_head_of_col * 2u + (t & 1u)) * L::kQRowWords) : smem_addr(zero_row);
+            qs.group_stride = q_col_mine ? 8u * L::kQRowWords * 4u : 0u;
         }
 
-        UnitState u;
+        UnitState<NG> u;
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int n = 0; n < NG; ++n) {
 #pragma unroll
-            for (int b = 0; b < 4; ++b) u.acc[a][b] = 0.0f;
-        u.m0 = u.m1 = -CUDART_INF_F;
-        u.l0 = u.l1 = 0.0f;
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) u.acc[n][a][b] = 0.0f;
+            u.m0[n] = u.m1[n] = -CUDART_INF_F;
+            u.l0[n] = u.l1[n] = 0.0f;
+        }
         float v_scale_prev = 1.0f;
 
         auto load_entry = [&](uint32_t page) -> uint64_t {
@@ -421,90 +477,107 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     const float k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) *
                                           (p.softmax_scale * kLog2e);
                     const float v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
-                    u.score[0] = u.score[1] = u.score[2] = u.score[3] = 0.0f;
+#pragma unroll
+                    for (int n = 0; n < NG; ++n) u.score[n][0] = u.score[n][1] = u.score[n][2] = u.score[n][3] = 0.0f;
 
                     if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
                         RansLane k, v;
                         k.open(k_part, lane, k_slot);
                         v.open(v_part, lane, v_slot);
-                        decode_fused(k, v, u, bq);
+                        decode_fused(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
                         HuffLane k, v;
                         k.open(k_part, lane, k_lut);
                         v.open(v_part, lane, v_lut);
-                        decode_fused(k, v, u, bq);
+                        decode_fused(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
                         FixedLane k, v;
                         k.open(k_part, lane);
                         v.open(v_part, lane);
-                        decode_fused(k, v, u, bq);
+                        decode_fused(k, v, u, qs);
                     } else {  // mixed coders (one stream fell back to fixed width): one stream after the other
-                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_only(k, u, bq); }
-                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_only(k, u, bq); }
-                        else { FixedLane k; k.open(k_part, lane); decode_k_only(k, u, bq); }
+                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_only(k, u, qs); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_only(k, u, qs); }
+                        else { FixedLane k; k.open(k_part, lane); decode_k_only(k, u, qs); }
                         if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_only(v, u); }
                         else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_only(v, u); }
                         else { FixedLane v; v.open(v_part, lane); decode_v_only(v, u); }
                     }
 
-                    // ---- online softmax for this page (fp32) ----
+                    // ---- online softmax for this page (fp32), per group of four heads ----
                     const uint32_t token = (page_begin + i) * 16u + my_token;
                     const bool visible = my_token < token_count && token >= first_token && token < sealed && token <= qpos;
-                    const float s0 = visible ? u.score[0] * k_scale : -CUDART_INF_F;
-                    const float s1 = visible ? u.score[1] * k_scale : -CUDART_INF_F;
-                    float r0 = s0, r1 = s1;
-#pragma unroll
-                    for (int o = 2; o <= 16; o <<= 1) {  // lanes that hold the same two heads
-                        r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
-                        r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
-                    }
-                    const float n0 = fmaxf(u.m0, r0), n1 = fmaxf(u.m1, r1);
-                    const float z0 = n0 == -CUDART_INF_F ? 0.0f : n0, z1 = n1 == -CUDART_INF_F ? 0.0f : n1;
-                    const float p0 = exp2f(s0 - z0), p1 = exp2f(s1 - z1);
-                    const float a0 = exp2f(u.m0 - z0), a1 = exp2f(u.m1 - z1);
-                    u.l0 = u.l0 * a0 + p0;
-                    u.l1 = u.l1 * a1 + p1;
-                    u.m0 = n0;
-                    u.m1 = n1;
                     __syncwarp();  // the previous page's readers of the scratch are done
-                    // P goes to the tensor cores as fp16; the rounding residue is fed as a second operand so that
-                    // P V is accurate to fp32 level whatever the magnitude of V
-                    const __half p0h = __float2half_rn(p0), p1h = __float2half_rn(p1);
-                    p_rows[my_head0 * 16u + my_token] = p0h;
-                    p_rows[(my_head0 + 1u) * 16u + my_token] = p1h;
-                    p_rows_lo[my_head0 * 16u + my_token] = __float2half_rn(p0 - __half2float(p0h));
-                    p_rows_lo[(my_head0 + 1u) * 16u + my_token] = __float2half_rn(p1 - __half2float(p1h));
-                    if (g == 0 && t < 2) {
-                        alpha_s[my_head0] = a0;
-                        alpha_s[my_head0 + 1u] = a1;
+#pragma unroll
+                    for (int n = 0; n < NG; ++n) {
+                        const float s0 = visible ? u.score[n][0] * k_scale : -CUDART_INF_F;
+                        const float s1 = visible ? u.score[n][1] * k_scale : -CUDART_INF_F;
+                        float r0 = s0, r1 = s1;
+#pragma unroll
+                        for (int o = 2; o <= 16; o <<= 1) {  // lanes that hold the same two heads
+                            r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
+                            r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, o));
+                        }
+                        const float n0 = fmaxf(u.m0[n], r0), n1 = fmaxf(u.m1[n], r1);
+                        const float z0 = n0 == -CUDART_INF_F ? 0.0f : n0, z1 = n1 == -CUDART_INF_F ? 0.0f : n1;
+                        const float p0 = exp2f(s0 - z0), p1 = exp2f(s1 - z1);
+                        const float a0 = exp2f(u.m0[n] - z0), a1 = exp2f(u.m1[n] - z1);
+                        u.l0[n] = u.l0[n] * a0 + p0;
+                        u.l1[n] = u.l1[n] * a1 + p1;
+                        u.m0[n] = n0;
+                        u.m1[n] = n1;
+                        // P goes to the tensor cores as fp16; the rounding residue is fed as a second operand so that
+                        // P V is accurate to fp32 level whatever the magnitude of V
+                        const uint32_t h0 = 4u * n + my_head0;
+                        const __half p0h = __float2half_rn(p0), p1h = __float2half_rn(p1);
+                        p_rows[h0 * 16u + my_token] = p0h;
+                        p_rows[(h0 + 1u) * 16u + my_token] = p1h;
+                        p_rows_lo[h0 * 16u + my_token] = __float2half_rn(p0 - __half2float(p0h));
+                        p_rows_lo[(h0 + 1u) * 16u + my_token] = __float2half_rn(p1 - __half2float(p1h));
+                        if (g == 0 && t < 2) {
+                            alpha_s[h0] = a0;
+                            alpha_s[h0 + 1u] = a1;
+                        }
                     }
                     __syncwarp();
-                    // O = O * alpha, kept in units of the current page's V scale
-                    const float beta = alpha_s[o_head] * (v_scale_prev / v_scale);
+                    const float v_ratio = v_scale_prev / v_scale;   // O is kept in units of the current page's V scale
                     v_scale_prev = v_scale;
+#pragma unroll
+                    for (int n = 0; n < NG; ++n) {
+                        const float beta = alpha_s[4u * n + o_head] * v_ratio;
+#pragma unroll
+                        for (int dd = 0; dd < 4; ++dd)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) u.acc[n][dd][c] *= beta;
+                    }
                     // P rows as A fragments. Rows g / g+8 of the fragment belong to lane tags g>>2 / (g>>2)+2; a lane
-                    // feeds the row whose tag is its own t and zeros (read from a zero row) otherwise.
-                    const __half *row_a = p_rows + (mask_lo ? o_head * 16u : 128u);
-                    const __half *row_b = p_rows + (mask_hi ? o_head * 16u : 128u);
-#pragma unroll
-                    for (int dd = 0; dd < 4; ++dd)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) u.acc[dd][c] *= beta;
+                    // feeds the row whose tag is its own t and zeros (read from the zero row) otherwise.
 #pragma unroll
                     for (int part = 0; part < 2; ++part) {  // fp16(p), then the rounding residue
-                        const uint4 a_lo = *reinterpret_cast<const uint4 *>(row_a + part * 64);
-                        const uint4 a_hi = *reinterpret_cast<const uint4 *>(row_a + part * 64 + 8);
-                        const uint4 b_lo = *reinterpret_cast<const uint4 *>(row_b + part * 64);
-                        const uint4 b_hi = *reinterpret_cast<const uint4 *>(row_b + part * 64 + 8);
-                        const uint32_t ra[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-                        const uint32_t rb[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
+                        uint32_t ra[NG][8], rb[NG][8];
+#pragma unroll
+                        for (int n = 0; n < NG; ++n) {
+                            const __half *rows = (part ? p_rows_lo : p_rows) + (4u * n + o_head) * 16u;
+                            const __half *row_a = row_lo_mine ? rows : zero_row;
+                            const __half *row_b = row_hi_mine ? rows : zero_row;
+                            const uint4 a_lo = *reinterpret_cast<const uint4 *>(row_a);
+                            const uint4 a_hi = *reinterpret_cast<const uint4 *>(row_a + 8);
+                            const uint4 b_lo = *reinterpret_cast<const uint4 *>(row_b);
+                            const uint4 b_hi = *reinterpret_cast<const uint4 *>(row_b + 8);
+                            ra[n][0] = a_lo.x; ra[n][1] = a_lo.y; ra[n][2] = a_lo.z; ra[n][3] = a_lo.w;
+                            ra[n][4] = a_hi.x; ra[n][5] = a_hi.y; ra[n][6] = a_hi.z; ra[n][7] = a_hi.w;
+                            rb[n][0] = b_lo.x; rb[n][1] = b_lo.y; rb[n][2] = b_lo.z; rb[n][3] = b_lo.w;
+                            rb[n][4] = b_hi.x; rb[n][5] = b_hi.y; rb[n][6] = b_hi.z; rb[n][7] = b_hi.w;
+                        }
 #pragma unroll
                         for (int dd = 0; dd < 4; ++dd) {
 #pragma unroll
                             for (int tq = 0; tq < 4; ++tq) {
                                 uint32_t lo, hi;
                                 quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
-                                mma_16816(u.acc[dd], ra[2 * tq], rb[2 * tq], ra[2 * tq + 1], rb[2 * tq + 1], lo, hi);
+#pragma unroll
+                                for (int n = 0; n < NG; ++n)
+                                    mma_16816(u.acc[n][dd], ra[n][2 * tq], rb[n][2 * tq], ra[n][2 * tq + 1], rb[n][2 * tq + 1], lo, hi);
                             }
                         }
                     }
@@ -521,32 +594,36 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         }
 
         // ---- unit partials ----
-        float l0 = u.l0, l1 = u.l1;
 #pragma unroll
-        for (int o = 2; o <= 16; o <<= 1) {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, o);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, o);
-        }
-        if (g == 0 && t < 2) {
-            if (my_head0 < G) {
-                float *dst = partial_ptr(p, chunk, out_head_base + my_head0);
-                dst[0] = u.m0;
-                dst[1] = l0;
+        for (int n = 0; n < NG; ++n) {
+            float l0 = u.l0[n], l1 = u.l1[n];
+#pragma unroll
+            for (int o = 2; o <= 16; o <<= 1) {
+                l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+                l1 += __shfl_xor_sync(0xffffffffu, l1, o);
             }
-            if (my_head0 + 1u < G) {
-                float *dst = partial_ptr(p, chunk, out_head_base + my_head0 + 1u);
-                dst[0] = u.m1;
-                dst[1] = l1;
+            const uint32_t h0 = 4u * n + my_head0;
+            if (g == 0 && t < 2) {
+                if (h0 < G) {
+                    float *dst = partial_ptr(p, chunk, out_head_base + h0);
+                    dst[0] = u.m0[n];
+                    dst[1] = l0;
+                }
+                if (h0 + 1u < G) {
+                    float *dst = partial_ptr(p, chunk, out_head_base + h0 + 1u);
+                    dst[0] = u.m1[n];
+                    dst[1] = l1;
+                }
             }
-        }
-        if (o_head < G) {
-            float *dst = partial_ptr(p, chunk, out_head_base + o_head) + 2;
+            if (4u * n + o_head < G) {
+                float *dst = partial_ptr(p, chunk, out_head_base + 4u * n + o_head) + 2;
 #pragma unroll
-            for (int dd = 0; dd < 4; ++dd) {
+                for (int dd = 0; dd < 4; ++dd) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t owner = 4u * (2u * t + (c & 1)) + (g >> 2) + 2u * (c >> 1);  // lane whose V block it is
-                    dst[4u * owner + dd] = u.acc[dd][c] * v_scale_prev;
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t owner = 4u * (2u * t + (c & 1)) + (g >> 2) + 2u * (c >> 1);  // lane whose V block it is
+                        dst[4u * owner + dd] = u.acc[n][dd][c] * v_scale_prev;
+                    }
                 }
             }
         }
@@ -561,6 +638,8 @@ bool lanes_kernel_supports(const AttentionParams &p) {
            p.query_type == CF_B200_F16;
 }
 
+// Query groups of up to four heads per kv head run the four-head kernel; larger groups run the eight-head one, which
+// decodes a page once for eight query heads (its query operands live in shared memory instead of registers).
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream) {
     static int sm_count = 0;
     static bool configured = false;
@@ -570,12 +649,16 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         if (e != cudaSuccess) return e;
         e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(kSmemBytes));
+        e = cudaFuncSetAttribute(lanes_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<1>::kSmem));
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lanes_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    lanes_attention_kernel<<<sm_count, kThreads, kSmemBytes, stream>>>(p);
+    if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    else lanes_attention_kernel<2><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 
