@@ -38,6 +38,7 @@ class SealedAttentionDesc(C.Structure):
         ("softmax_scale", _f32), ("causal_window", _u32),
         ("workspace", _vp), ("workspace_bytes", _u64), ("min_pages_per_unit", _u32), ("kernel", _u32),
         ("status", _vp), ("tail_type", _u32), ("tail_capacity", _u32), ("query_positions", _vp),
+        ("shared_prefix_pages", _u32), ("reserved0", _u32),
     ]
 
 

@@ -50,6 +50,7 @@ class SealedKvLayer:
         self.v_tables = torch.zeros_like(self.k_tables)
         if workspace_bytes is None:
             d = self._attention_desc(None, None, max_sequences, None)
+            d.shared_prefix_pages = 1   # also set room aside for the partials of a shared prefix
             need = C.c_uint64(0)
             N.check("workspace_bytes", self.lib.cf_b200_sealed_attention_workspace_bytes(
                 C.byref(d), C.c_uint64(max_sequences * max_pages_per_sequence), C.byref(need)))
@@ -200,8 +201,10 @@ class SealedKvLayer:
 
     # -- attention -----------------------------------------------------------------------------------
     def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
-                  kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL):
-        """Decode-step attention: queries [n, query_heads, head_dim] (float16 or float32) -> float32 output."""
+                  kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL, shared_prefix_pages=0):
+        """Decode-step attention: queries [n, query_heads, head_dim] (float16 or float32) -> float32 output.
+        shared_prefix_pages = P states that the first P pages of every listed sequence are the same pages (as after
+        copy_sequence): they are then decoded once for all the sequences instead of once per sequence."""
         n = queries.shape[0]
         if out is None:
             out = torch.zeros((n, self.query_heads, self.head_dim), dtype=torch.float32, device=self.device)
@@ -211,6 +214,7 @@ class SealedKvLayer:
         d.kernel = kernel
         d.kv_head_begin, d.kv_head_span = kv_head_begin, kv_head_span
         d.min_pages_per_unit = min_pages_per_unit
+        d.shared_prefix_pages = shared_prefix_pages
         N.check("sealed_attention", self.lib.cf_b200_sealed_attention_stages_async(C.byref(d), C.c_uint32(stages),
                                                                                       _stream_ptr()))
         return out

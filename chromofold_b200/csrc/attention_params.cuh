@@ -34,6 +34,8 @@ struct AttentionParams {
     uint8_t *workspace;
     WorkspaceLayout layout;
     uint32_t min_pages_per_unit;
+    uint32_t shared_prefix_pages;   // the caller's hint, already zeroed when the launch cannot use it
+    uint32_t sm_count;
     uint32_t *status;
     // uncompressed comparison pools (dense kernel only)
     const __half *pool_k, *pool_v;
@@ -49,6 +51,12 @@ __device__ __forceinline__ uint32_t *chunk_prefix(const AttentionParams &p) {
 __device__ __forceinline__ float *partial_ptr(const AttentionParams &p, uint32_t chunk, uint32_t local_q_head) {
     return reinterpret_cast<float *>(p.workspace + p.layout.partials_offset) +
            (static_cast<uint64_t>(chunk) * (p.kv_head_span * p.group) + local_q_head) * p.layout.partial_stride_floats;
+}
+// Shared-prefix partial of (shared chunk, batch entry, local query head).
+__device__ __forceinline__ float *shared_partial_ptr(const AttentionParams &p, uint32_t chunk, uint32_t seq, uint32_t local_q_head) {
+    return reinterpret_cast<float *>(p.workspace + p.layout.shared_offset) +
+           ((static_cast<uint64_t>(chunk) * p.seq_count + seq) * (p.kv_head_span * p.group) + local_q_head) *
+               p.layout.partial_stride_floats;
 }
 __device__ __forceinline__ uint32_t slot_of(const AttentionParams &p, uint32_t seq) {
     return p.seq_slots ? p.seq_slots[seq] : seq;
@@ -81,6 +89,8 @@ cudaError_t launch_generic_attention(const AttentionParams &p, cudaStream_t stre
 // Implemented in sealed_attention_lanes.cu
 bool lanes_kernel_supports(const AttentionParams &p);
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream);
+// Implemented in sealed_attention_prefix.cu
+cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t stream);
 // Implemented in dense_attention.cu
 cudaError_t launch_dense_attention(const AttentionParams &p, cudaStream_t stream);
 

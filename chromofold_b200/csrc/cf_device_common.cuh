@@ -18,6 +18,7 @@ __host__ __device__ inline uint32_t align_up_u32(uint32_t v, uint32_t a) { retur
 // Split-KV workspace. One chunk = `pages_per_unit` consecutive pages of one sequence; one unit = (chunk, kv head).
 //   [0, 64)                       PlanHeader
 //   [64, 64 + 4*(seq_count+1))    chunk_prefix: number of chunks before each sequence
+//   [shared_offset, ...)          shared-prefix partials, per (shared chunk, sequence, local query head), when asked for
 //   [partials_offset, ...)        per chunk and local query head: float m, float l, float acc[head_dim]
 struct PlanHeader {
     uint32_t chunk_count;
@@ -25,22 +26,33 @@ struct PlanHeader {
     uint32_t next_unit;      // work counter for the attention kernel; the plan kernel clears it
     uint32_t chunk_capacity;
     uint32_t overflow;
-    uint32_t pad[11];
+    uint32_t shared_pages;            // pages at the head of every sequence that the shared-prefix kernel handles (0 = none)
+    uint32_t shared_chunks;           // the shared prefix is cut into this many chunks of
+    uint32_t shared_pages_per_chunk;  // this many pages
+    uint32_t pad[8];
 };
 
 struct WorkspaceLayout {
     uint64_t prefix_offset;
+    uint64_t shared_offset;          // 0 = no room was set aside for shared-prefix partials
     uint64_t partials_offset;
     uint64_t partial_stride_floats;  // per (chunk, local query head)
     uint64_t chunk_capacity;
 };
 
 __host__ __device__ inline WorkspaceLayout workspace_layout(uint32_t seq_count, uint32_t local_q_heads,
-                                                            uint32_t head_dim, uint64_t workspace_bytes) {
+                                                            uint32_t head_dim, uint64_t workspace_bytes,
+                                                            bool shared_prefix = false) {
     WorkspaceLayout w;
     w.prefix_offset = sizeof(PlanHeader);
     w.partials_offset = (w.prefix_offset + 4ull * (seq_count + 1) + 255ull) / 256ull * 256ull;
     w.partial_stride_floats = head_dim + 2ull;
+    w.shared_offset = 0;
+    if (shared_prefix) {
+        w.shared_offset = w.partials_offset;
+        w.partials_offset += (static_cast<uint64_t>(CF_B200_SHARED_CHUNKS_MAX) * seq_count * local_q_heads *
+                              w.partial_stride_floats * 4ull + 255ull) / 256ull * 256ull;
+    }
     const uint64_t per_chunk = w.partial_stride_floats * 4ull * local_q_heads;
     w.chunk_capacity = workspace_bytes > w.partials_offset ? (workspace_bytes - w.partials_offset) / per_chunk : 0;
     return w;

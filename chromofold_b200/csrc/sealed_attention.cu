@@ -23,13 +23,14 @@ constexpr uint32_t kGenericMaxGroup = 16;
 // ---------------------------------------------------------------------------------------------------------------
 // Plan: how many chunks each sequence gets. One block.
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint32_t seq, uint32_t *first_page) {
+__device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint32_t seq, uint32_t *first_page,
+                                                  uint32_t shared_pages = 0) {
     const uint32_t slot = slot_of(p, seq);
     const uint32_t sealed = p.seq_sealed_tokens[slot];
     const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
     const uint32_t qpos = query_position(p, seq, sealed, tail);
     const uint32_t pages = min((sealed + p.page_tokens - 1u) / p.page_tokens, qpos / p.page_tokens + 1u);
-    const uint32_t first = min(window_begin(qpos, p.causal_window) / p.page_tokens, pages);
+    const uint32_t first = min(max(window_begin(qpos, p.causal_window) / p.page_tokens, shared_pages), pages);
     if (first_page) *first_page = first;
     return pages - first;
 }
@@ -44,12 +45,40 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     PlanHeader *hdr = plan_header(p);
     uint32_t *prefix = chunk_prefix(p);
 
+    // Shared prefix: taken only if every listed sequence has the pages sealed and its page-table row starts with the
+    // same ids as the first sequence's. The pages are then cut into chunks for the shared-prefix kernel and left out
+    // of the per-sequence chunks below.
+    uint32_t shared = p.shared_prefix_pages;
+    if (shared) {
+        const uint32_t *row0 = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
+        int bad = 0;
+        for (uint32_t s = begin; s < end; ++s)
+            if (p.seq_sealed_tokens[slot_of(p, s)] / p.page_tokens < shared) bad = 1;
+        const uint64_t cells = static_cast<uint64_t>(p.seq_count) * shared;
+        for (uint64_t i = tid; i < cells && !bad; i += kPlanThreads) {
+            const uint32_t s = static_cast<uint32_t>(i / shared), pg = static_cast<uint32_t>(i % shared);
+            if (p.page_table[static_cast<uint64_t>(slot_of(p, s)) * p.page_table_stride + pg] != row0[pg]) bad = 1;
+        }
+        if (__syncthreads_or(bad)) {
+            shared = 0;
+            if (tid == 0) raise_status(p, CF_B200_DEVSTAT_PREFIX_MISMATCH);
+        }
+    }
+    uint32_t shared_chunks = 0, shared_per_chunk = 0;
+    if (shared) {
+        const uint32_t row_tiles = (p.seq_count * p.group + 127u) / 128u;
+        const uint32_t wanted = (2u * p.sm_count + p.kv_head_span * row_tiles - 1u) / (p.kv_head_span * row_tiles);
+        shared_chunks = min(max(wanted, 1u), min(CF_B200_SHARED_CHUNKS_MAX, (shared + 15u) / 16u));
+        shared_per_chunk = ((shared + shared_chunks - 1u) / shared_chunks + 7u) / 8u * 8u;   // whole rounds of eight pages
+        shared_chunks = (shared + shared_per_chunk - 1u) / shared_per_chunk;
+    }
+
     uint32_t pages_per_unit = max(p.min_pages_per_unit, 1u);
     uint32_t overflow = 0;
     uint32_t local = 0;  // chunks of this thread's sequences at the current pages_per_unit
     for (int attempt = 0; attempt < 32; ++attempt) {
         local = 0;
-        for (uint32_t s = begin; s < end; ++s) local += (visible_pages(p, s, nullptr) + pages_per_unit - 1u) / pages_per_unit;
+        for (uint32_t s = begin; s < end; ++s) local += (visible_pages(p, s, nullptr, shared) + pages_per_unit - 1u) / pages_per_unit;
         __syncthreads();
         scan[tid] = local;
         __syncthreads();
@@ -68,7 +97,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     uint32_t running = scan[tid] - local;
     for (uint32_t s = begin; s < end; ++s) {
         prefix[s] = overflow ? 0u : running;
-        running += (visible_pages(p, s, nullptr) + pages_per_unit - 1u) / pages_per_unit;
+        running += (visible_pages(p, s, nullptr, shared) + pages_per_unit - 1u) / pages_per_unit;
     }
     if (tid == 0) {
         prefix[p.seq_count] = overflow ? 0u : s_total;
@@ -77,6 +106,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         hdr->next_unit = 0;
         hdr->chunk_capacity = static_cast<uint32_t>(min(p.layout.chunk_capacity, static_cast<uint64_t>(0xffffffffu)));
         hdr->overflow = overflow;
+        hdr->shared_pages = overflow ? 0u : shared;
+        hdr->shared_chunks = overflow ? 0u : shared_chunks;
+        hdr->shared_pages_per_chunk = shared_per_chunk;
         if (overflow) raise_status(p, CF_B200_DEVSTAT_WORKSPACE);
     }
 }
@@ -312,6 +344,21 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
             for (int j = 0; j < 4; ++j) wa[j] = wa[j] * so + pa[j] * sn;
             wm = nm;
         }
+        const uint32_t shared_chunks = plan_header(p)->shared_chunks;
+        for (uint32_t c = warp; c < shared_chunks; c += kCombineWarps) {   // the shared prefix's chunks, same rule
+            const float *part = shared_partial_ptr(p, c, seq, local_q);
+            const float pm = part[0], pl = part[1];
+            float pa[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pa[j] = lane + 32u * j < D ? part[2 + lane + 32u * j] : 0.0f;
+            if (pm == -CUDART_INF_F) continue;
+            const float nm = fmaxf(wm, pm);
+            const float so = exp2f(wm - nm), sn = exp2f(pm - nm);
+            wl = wl * so + pl * sn;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wa[j] = wa[j] * so + pa[j] * sn;
+            wm = nm;
+        }
         if (lane == 0) {
             s_m[warp] = wm;
             s_l[warp] = wl;
@@ -418,8 +465,11 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->softmax_scale = d->softmax_scale;
     p->causal_window = d->causal_window;
     p->workspace = static_cast<uint8_t *>(d->workspace);
-    p->layout = workspace_layout(d->seq_count, p->kv_head_span * p->group, d->head_dim, d->workspace_bytes);
+    p->layout = workspace_layout(d->seq_count, p->kv_head_span * p->group, d->head_dim, d->workspace_bytes,
+                                 d->shared_prefix_pages != 0);
     p->min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    p->shared_prefix_pages = 0;   // the launch code sets it when the lanes kernels serve the call
+    p->sm_count = 0;
     p->status = d->status;
     p->pool_k = nullptr;
     p->pool_v = nullptr;
@@ -487,8 +537,9 @@ extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_atte
         return CF_ERR_UNSUPPORTED;
     const uint32_t span = d->kv_head_span ? d->kv_head_span : d->kv_head_count - d->kv_head_begin;
     const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, span * (d->query_head_count / d->kv_head_count),
-                                                         d->head_dim, d->workspace_bytes);
+                                                         d->head_dim, d->workspace_bytes, d->shared_prefix_pages != 0);
     if (w.chunk_capacity < d->seq_count) return CF_ERR_INVALID_ARGUMENT;  // at least one chunk per sequence
+    if (d->shared_prefix_pages > d->page_table_stride || d->reserved0 != 0) return CF_ERR_INVALID_ARGUMENT;
     return CF_OK;
 }
 
@@ -501,7 +552,7 @@ extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_seal
     const uint32_t local_q = span * (d->query_head_count / d->kv_head_count);
     const uint32_t ppu = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
     const uint64_t chunks = total_pages / ppu + d->seq_count + 1;  // each sequence may round up once
-    const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, local_q, d->head_dim, 0);
+    const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, local_q, d->head_dim, 0, d->shared_prefix_pages != 0);
     *out_bytes = w.partials_offset + chunks * w.partial_stride_floats * 4ull * local_q;
     return CF_OK;
 }
@@ -516,9 +567,22 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     const bool lanes_ok = cfb::lanes_kernel_supports(p);
     if (d->kernel == CF_B200_KERNEL_LANES && !lanes_ok) return CF_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
+    // the shared-prefix kernel works on rows of 128 = whole query groups, full history, decode-step positions
+    if (use_lanes && d->shared_prefix_pages && d->causal_window == 0 && d->query_positions == nullptr && 128u % p.group == 0) {
+        static int sm_count = 0;
+        if (sm_count == 0) {
+            int device = 0;
+            if (cudaGetDevice(&device) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+                return CF_ERR_CUDA;
+        }
+        p.shared_prefix_pages = d->shared_prefix_pages;
+        p.sm_count = static_cast<uint32_t>(sm_count);
+    }
     if ((stages & CF_B200_STAGE_PLAN) && cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
     if (stages & CF_B200_STAGE_ATTENTION) {
-        const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
+        if (p.shared_prefix_pages && cfb::launch_prefix_attention(p, s) != cudaSuccess) return CF_ERR_CUDA;
         const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
         if (e != cudaSuccess) return CF_ERR_CUDA;
     }

@@ -24,184 +24,18 @@
 
 #include <type_traits>
 
-#include "attention_params.cuh"
+#include "lanes_decoders.cuh"
 
 namespace cfb {
 namespace {
+
+using namespace lanes;
 
 #ifndef CFB_LANES_WARPS
 #define CFB_LANES_WARPS 16
 #endif
 constexpr int kWarps = CFB_LANES_WARPS;
 constexpr int kThreads = kWarps * 32;
-constexpr uint32_t kStageBytes = 4160;   // 16 header + 2 * 2048 payload max + 48 slack (decoders read ahead)
-constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
-constexpr uint32_t kWaitSpins = 1u << 22;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr uint32_t kMagic = 0x64646464u;       // fp16 1024.0 high byte, for the byte-permute conversion
-constexpr uint32_t kBias2 = 0x64806480u;       // half2(1152, 1152) = 1024 + zero point
-
-// ---- PTX wrappers ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false if the copy did not land within kWaitSpins polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitSpins; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// One bulk async copy global -> this CTA's shared memory (16-byte aligned, size a multiple of 16).
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-// Four packed symbols (byte i = symbol i) -> two half2 of codes (symbol - 128), exact.
-__device__ __forceinline__ void quad_to_half2(uint32_t quad, uint32_t &lo, uint32_t &hi) {
-    lo = hsub2_u32(__byte_perm(quad, kMagic, 0x4140), kBias2);  // (s0, s1)
-    hi = hsub2_u32(__byte_perm(quad, kMagic, 0x4342), kBias2);  // (s2, s3)
-}
-
-// a * b + c on the multiply-add pipe. Plain adds and constant shifts written this way leave the integer ALU pipe,
-// which is the busiest one in the decoders, to the operations that have no other home (logic, funnel shifts).
-__device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-
-// The low bytes of four table entries as one register, first symbol in byte 0: three byte permutes.
-__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3) {
-    return __byte_perm(__byte_perm(e0, e1, 0x0040), __byte_perm(e2, e3, 0x0040), 0x5410);
-}
-
-// ---- per-lane block decoders: each yields four symbols packed in one register -----------------------------------
-// Both entropy decoders are written without branches so that the K chain and the V chain of a lane interleave in
-// one straight instruction stream. A 64-bit window holds the upcoming stream bits, top aligned; it is reloaded from
-// shared memory once per quad (four symbols), which is as often as it can run dry.
-struct RansLane {
-    static constexpr bool kWholeQuads = false;
-    uint32_t x, whi, wlo, used;   // state; window (next byte = top byte of whi); bits taken since the reload
-    uint32_t pos;                 // shared-memory byte address of the first byte not yet taken at the last reload
-    uint32_t table;               // shared-memory byte address of the slot table
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint32_t *slot_table) {
-        x = reinterpret_cast<const uint32_t *>(part)[lane];
-        pos = smem_addr(part) + 192u + reinterpret_cast<const uint16_t *>(part + 128)[lane];
-        table = smem_addr(slot_table);
-        used = 0;
-    }
-    // Eight bytes starting at `pos`, in stream order, most significant first (the order rans.cu:23 shifts them in).
-    __device__ __forceinline__ void reload() {
-        pos += used >> 3;
-        used = 0;
-        const uint32_t base = pos & ~3u, sel = imad(pos & 3u, 0x1111u, 0x0123u);
-        uint32_t w0, w1, w2;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
-        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
-        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(w2) : "r"(base));
-        whi = __byte_perm(w0, w1, sel);
-        wlo = __byte_perm(w1, w2, sel);
-    }
-    // src/cuda/rans.cu:20-23: x = freq * (x >> 12) + (x & 4095) - cum, then bytes are shifted in while x < 2^23.
-    // The shared-memory table holds e = sym | (slot - cum) << 8 | freq << 20, so e >> 8 = (slot - cum) + freq * 4096
-    // and the update is freq * ((x >> 12) - 4096) + (e >> 8): no field of the entry needs masking.
-    // After the update the state is >= 2^11, so the reference's loop runs 0, 1 or 2 times: (clz(state) - 1) / 8.
-    __device__ __forceinline__ uint32_t symbol() {
-        uint32_t e;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(imad(x & (CF_B200_RANS_M - 1u), 4u, table)));
-        x = imad(e >> 20, imad(x >> CF_B200_RANS_PROB_BITS, 1u, 0u - CF_B200_RANS_M), e >> 8);
-        const uint32_t shift = imad(static_cast<uint32_t>(__clz(x)), 1u, 0xffffffffu) & 24u;
-        x = __funnelshift_l(whi, x, shift);
-        whi = __funnelshift_l(wlo, whi, shift);
-        wlo <<= shift;
-        used = imad(shift, 1u, used);
-        return e;
-    }
-    __device__ __forceinline__ uint32_t quad() {
-        reload();
-        const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
-        return pack_low_bytes(e0, e1, e2, e3);
-    }
-};
-
-struct HuffLane {
-    static constexpr bool kWholeQuads = false;
-    uint32_t whi, wlo, used;   // window of upcoming bits, MSB first; bits taken since the reload
-    uint32_t words, bit;       // shared-memory address of the payload words; bit position at the last reload
-    uint32_t table;
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint16_t *lut) {
-        bit = reinterpret_cast<const uint16_t *>(part)[lane];
-        words = smem_addr(part) + 64u;
-        table = smem_addr(lut);
-        used = 0;
-    }
-    __device__ __forceinline__ void reload() {  // four codes take at most 48 bits; the window holds 64
-        bit += used;
-        used = 0;
-        const uint32_t base = words + ((bit >> 5) << 2), off = bit & 31u;
-        uint32_t w0, w1, w2;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
-        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
-        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(w2) : "r"(base));
-        whi = __funnelshift_l(w1, w0, off);
-        wlo = __funnelshift_l(w2, w1, off);
-    }
-    // include/chromofold/detail/block_huffman_device.cuh:12-19: the next 12 bits, MSB-first, index the LUT.
-    __device__ __forceinline__ uint32_t symbol() {
-        uint32_t e;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(e) : "r"(imad(whi >> (32u - CF_B200_HUFF_MAXLEN), 2u, table)));
-        const uint32_t len = e >> 8;
-        whi = __funnelshift_l(wlo, whi, len);
-        wlo <<= len;
-        used = imad(len, 1u, used);
-        return e;
-    }
-    __device__ __forceinline__ uint32_t quad() {
-        reload();
-        const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
-        return pack_low_bytes(e0, e1, e2, e3);
-    }
-};
-
-struct FixedLane {
-    static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
-    const uint32_t *words;
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane) {
-        words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
-    }
-    // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
-    __device__ __forceinline__ uint32_t quad() { return __byte_perm(*words++, 0u, 0x0123); }
-};
-
 // Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
 template <int NG>
 struct UnitState {
@@ -318,21 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + L::kBars);
     uint32_t *q_rows = reinterpret_cast<uint32_t *>(warp_mem + L::kQRows);     // NG == 2 only
 
-    // coding tables: once per CTA
-    {
-        // slot entries are re-packed for RansLane::symbol(): sym | (slot - cum) << 8 | freq << 20
-        auto repack = [](uint32_t e) { return (e & 0xffu) | ((e >> 20) << 8) | (((e >> 8) & 0xfffu) << 20); };
-        for (uint32_t i = tid; i < 4096; i += kThreads) {
-            k_slot[i] = repack(p.k_tables->rans_slot[i]);
-            v_slot[i] = repack(p.v_tables->rans_slot[i]);
-        }
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.k_tables->huff_lut);
-        uint4 *dst = reinterpret_cast<uint4 *>(k_lut);
-        for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
-        src = reinterpret_cast<const uint4 *>(p.v_tables->huff_lut);
-        dst = reinterpret_cast<uint4 *>(v_lut);
-        for (uint32_t i = tid; i < 512; i += kThreads) dst[i] = src[i];
-    }
+    load_tables(smem, p, tid, kThreads);   // coding tables: once per CTA
     reinterpret_cast<uint32_t *>(warp_mem + L::kZero)[lane] = 0u;   // the zero row inactive lanes read their fragments from
     if (lane == 0) {
         mbar_init(&bars[0], 1);
@@ -376,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         const uint32_t qpos = query_position(p, seq, sealed, tail);
         const uint32_t first_token = window_begin(qpos, p.causal_window);
         const uint32_t pages = min((sealed + 15u) / 16u, qpos / 16u + 1u);
-        const uint32_t first_page = min(first_token / 16u, pages);
+        const uint32_t first_page = min(max(first_token / 16u, hdr->shared_pages), pages);   // shared pages are not this kernel's
         const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
         const uint32_t page_end = min(page_begin + pages_per_unit, pages);
         const uint32_t n_pages = page_end > page_begin ? page_end - page_begin : 0u;
@@ -462,13 +282,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                 phase_bits ^= 1u << st;
                 const uint8_t *rec = warp_mem + st * kStageBytes;
                 const uint4 hv = *reinterpret_cast<const uint4 *>(rec);
-                const uint32_t k_units = hv.x & 0xffffu, v_units = hv.x >> 16;
+                const uint32_t k_units = hv.x & 0xffffu;
                 const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu, token_count = hv.y >> 16;
-                const uint32_t codebook = hv.w & 0xffffu, version = hv.w >> 24;
-                const bool good = version == CF_B200_FORMAT_VERSION && codebook == p.codebook_id &&
-                                  1u + k_units + v_units == CF_B200_DIR_LENGTH_UNITS(entry_cur) && k_units <= 128u &&
-                                  v_units <= 128u && k_coder <= 2u && v_coder <= 2u && token_count >= 1u &&
-                                  token_count <= 16u;
+                const bool good = record_header_ok(hv, entry_cur, p.codebook_id);
                 if (!good) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
                 } else {

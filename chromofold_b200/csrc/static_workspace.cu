@@ -49,7 +49,8 @@ extern "C" cf_status cf_b200_sealed_attention_static_async(const cf_b200_sealed_
     const uint32_t span = desc->kv_head_span ? desc->kv_head_span : desc->kv_head_count - desc->kv_head_begin;
     const uint32_t local_q = span * (desc->query_head_count / desc->kv_head_count);
     const cfb::WorkspaceLayout layout =
-        cfb::workspace_layout(desc->seq_count, local_q, desc->head_dim, CF_B200_STATIC_WORKSPACE_BYTES);
+        cfb::workspace_layout(desc->seq_count, local_q, desc->head_dim, CF_B200_STATIC_WORKSPACE_BYTES,
+                              desc->shared_prefix_pages != 0);
     if (layout.partials_offset >= CF_B200_STATIC_WORKSPACE_BYTES || layout.chunk_capacity < desc->seq_count) {
         std::snprintf(g_error, sizeof g_error,
                       "batch too large for the built-in workspace: %u sequences x %u query heads x head_dim %u needs "

@@ -104,6 +104,15 @@ typedef struct cf_b200_sealed_attention_desc {
      * step). A smaller position hides the tokens after it (paged_kv_attention.cu:67-69), so several entries may
      * name the same slot with different positions: that is multi-query (prefill) attention over one sequence. */
     const uint32_t *query_positions;
+    /* Shared prefix: the caller states that the first shared_prefix_pages entries of the page-table row of EVERY
+     * listed sequence name the same pages (one sealed copy referenced by all, src/multisequence_cache.cpp:235-292).
+     * Such pages are then decoded once per 128 query rows instead of once per sequence, and the contraction with all
+     * the rows that share them runs on the tensor cores. It is a hint: the plan kernel checks the rows; if they
+     * differ, or the geometry is not the lanes kernel's, or causal_window / query_positions are in use, every page
+     * is handled per sequence as if the field were 0 (a mismatch also raises CF_B200_DEVSTAT_PREFIX_MISMATCH).
+     * The workspace must have been sized with the field set (cf_b200_sealed_attention_workspace_bytes). */
+    uint32_t shared_prefix_pages;
+    uint32_t reserved0;
 } cf_b200_sealed_attention_desc;
 
 #define CF_B200_KERNEL_AUTO 0u     /* lane-per-block tensor-core kernel when the geometry allows, else generic */
@@ -115,6 +124,8 @@ typedef struct cf_b200_sealed_attention_desc {
 #define CF_B200_DEVSTAT_WORKSPACE 0x4u       /* workspace too small for the planned units */
 #define CF_B200_DEVSTAT_NONFINITE 0x8u       /* the sealer met NaN or Inf; the page was not published */
 #define CF_B200_DEVSTAT_ARENA_FULL 0x10u     /* the sealer found no room in the arena */
+#define CF_B200_DEVSTAT_PREFIX_MISMATCH 0x20u /* shared_prefix_pages was set but the page-table rows differ */
+#define CF_B200_SHARED_CHUNKS_MAX 8u         /* a shared prefix is cut into at most this many chunks */
 
 /* Host-side structural validation; dereferences nothing on the device
  * (cf_kv_validate_paged_attention_desc, src/cuda/paged_kv_attention.cu:280-299). */

@@ -129,3 +129,59 @@ def test_config5_shared_prefix_with_gpu_sealed_suffixes(native, oracle):
     assert int(layer.h_sealed[3]) == prefix + 32 and int(layer.h_tail[3]) == 5
     assert np.array_equal(layer.h_page_table[0, :prefix // 16], layer.h_page_table[7, :prefix // 16])
     assert layer.h_page_table[0, prefix // 16] != layer.h_page_table[7, prefix // 16]
+
+
+@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8"])
+@pytest.mark.parametrize("heads", [(32, 8), (64, 8), (8, 8)], ids=str)
+def test_shared_prefix_is_decoded_once_for_all_sequences(native, oracle, coder, heads):
+    """The shared-prefix kernel: with the hint the sealed prefix pages are decoded once per 128 query rows and
+    contracted with every sequence's queries on the tensor cores; results must equal the per-sequence path within
+    the attention tolerance and the oracle's."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    hq, hkv = heads
+    n, prefix = 21, 1616                      # 101 shared pages: not a multiple of the 8-page round
+    layer, info = build_sealed_layer(np.array([prefix] + [0] * (n - 1)), query_heads=hq, kv_heads=hkv, coder=coder,
+                                     seed=70, extra_pages_per_sequence=8, reserve_pages=4 * n)
+    for s in range(1, n):
+        layer.copy_sequence(0, s)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(71)
+    slots = list(range(n))
+    for step in range(21):                    # one sealed private page and a 5-token tail per sequence
+        k = (torch.randn((n, hkv, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((n, hkv, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append(slots, k, v)
+        layer.seal_full_pages()
+    q = _q(n, hq, 72)
+    plain = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    shared = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=prefix // 16).cpu().numpy()
+    assert layer.device_status() == 0
+    ok, err = attention_close(shared, plain)
+    assert ok, err
+    ok, err = attention_close(shared, oracle_from_layer(layer, q.cpu().numpy()))
+    assert ok, err
+    # a shorter claim is fine too (the rest of the prefix is then handled per sequence)
+    part = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=40).cpu().numpy()
+    ok, err = attention_close(part, plain)
+    assert ok, err
+    # a subset of the sequences, in another order
+    some = [5, 0, 17, 9]
+    sub = layer.attention(q[:4].contiguous(), slots=some, kernel=native.KERNEL_LANES, shared_prefix_pages=prefix // 16).cpu().numpy()
+    ref = layer.attention(q[:4].contiguous(), slots=some, kernel=native.KERNEL_LANES).cpu().numpy()
+    ok, err = attention_close(sub, ref)
+    assert ok, err
+    assert layer.device_status() == 0
+
+
+def test_shared_prefix_claim_that_does_not_hold_falls_back(native, oracle):
+    """A claim the page tables do not bear out is refused by the plan kernel: the status word says so and the
+    result is the per-sequence one."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, info = build_sealed_layer(np.array([512, 512, 512]), coder="rans", seed=73)   # three unrelated sequences
+    q = _q(3, 32, 74)
+    plain = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    claimed = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=16).cpu().numpy()
+    assert np.array_equal(claimed, plain)
+    assert layer.device_status() == 0x20
