@@ -64,7 +64,7 @@ def config4(a, device, rank, world):
     """Long context, 70B shape: 64 query / 8 kv heads, 8 sequences x 131072 tokens, kv heads sharded."""
     import torch.distributed as dist
     contexts = np.full(a.batch4, a.ctx4)
-    layer, info = build_sealed_layer(contexts, query_heads=64, kv_heads=8, coder="rans", seed=50, device=device)
+    layer, info = build_sealed_layer(contexts, query_heads=64, kv_heads=8, coder=a.coder, seed=50, device=device)
     q = _queries(len(contexts), 64, 51, device)
     out = torch.zeros((len(contexts), 64, 128), dtype=torch.float32, device=device)
     tokens = int(contexts.sum())
@@ -111,7 +111,7 @@ def config5(a, device):
     step appends one token to every sequence, seals the pages that filled up, and runs the decode attention."""
     n, prefix, suffix = a.seqs5, a.prefix5, a.suffix5
     contexts = np.array([prefix] + [0] * (n - 1))
-    layer, info = build_sealed_layer(contexts, coder="rans", seed=60, device=device,
+    layer, info = build_sealed_layer(contexts, coder=a.coder, seed=60, device=device,
                                      extra_pages_per_sequence=suffix // 16 + 8, reserve_pages=n * (suffix // 16 + 8))
     one_copy = layer.sealed_bytes()
     for s in range(1, n):
@@ -143,7 +143,7 @@ def config5(a, device):
     logical_tokens = n * (prefix + suffix)
     unique_bytes = layer.sealed_bytes()
     flops = 4 * 128 * 32 * logical_tokens
-    print(json.dumps({"config": 5, "sequences": n, "shared_prefix_tokens": prefix, "private_suffix_tokens": suffix,
+    print(json.dumps({"config": 5, "coder": a.coder, "sequences": n, "shared_prefix_tokens": prefix, "private_suffix_tokens": suffix,
                       "unique_sealed_bytes": unique_bytes, "logical_sealed_bytes": int(one_copy * n + (unique_bytes - one_copy)),
                       "ms_per_step_append_seal_attention": round(ms, 4), "ms_attention_only": round(ms_attn, 4),
                       "ms_attention_without_the_shared_prefix_kernel": round(ms_per_sequence, 4),
@@ -158,6 +158,7 @@ def main():
     ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5])
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"], help="configurations 4 and 5")
     ap.add_argument("--batch4", type=int, default=8)
     ap.add_argument("--ctx4", type=int, default=131072)
     ap.add_argument("--seqs5", type=int, default=256)

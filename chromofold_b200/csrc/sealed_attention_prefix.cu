@@ -117,7 +117,8 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
     float *meta = reinterpret_cast<float *>(smem + kOffMeta);   // [page of the round][4]: k scale, v scale, tokens, -
     uint64_t *bar = reinterpret_cast<uint64_t *>(smem + kOffBars) + warp;
 
-    const PlanHeader *hdr = plan_header(p);
+    PlanHeader *hdr = plan_header(p);
+    __shared__ uint32_t s_unit;
     const uint32_t shared_pages = hdr->shared_pages, chunks = hdr->shared_chunks, per_chunk = hdr->shared_pages_per_chunk;
     if (shared_pages == 0 || chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
 
@@ -136,7 +137,12 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
     const uint32_t unit_count = chunks * p.kv_head_span * row_tiles;
     const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
 
-    for (uint32_t unit = blockIdx.x; unit < unit_count; unit += gridDim.x) {
+    for (;;) {
+        __syncthreads();   // everyone has read the previous s_unit
+        if (tid == 0) s_unit = atomicAdd(&hdr->next_shared_unit, 1u);
+        __syncthreads();
+        const uint32_t unit = s_unit;
+        if (unit >= unit_count) break;
         const uint32_t tile_index = unit % row_tiles;
         const uint32_t head_local = (unit / row_tiles) % p.kv_head_span;
         const uint32_t chunk = unit / (row_tiles * p.kv_head_span);
@@ -398,7 +404,7 @@ cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t strea
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    prefix_attention_kernel<<<sm_count * 2, kPThreads, kPrefixSmem, stream>>>(p);
+    prefix_attention_kernel<<<sm_count, kPThreads, kPrefixSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

@@ -125,7 +125,7 @@ typedef struct cf_b200_sealed_attention_desc {
 #define CF_B200_DEVSTAT_NONFINITE 0x8u       /* the sealer met NaN or Inf; the page was not published */
 #define CF_B200_DEVSTAT_ARENA_FULL 0x10u     /* the sealer found no room in the arena */
 #define CF_B200_DEVSTAT_PREFIX_MISMATCH 0x20u /* shared_prefix_pages was set but the page-table rows differ */
-#define CF_B200_SHARED_CHUNKS_MAX 8u         /* a shared prefix is cut into at most this many chunks */
+#define CF_B200_SHARED_CHUNKS_MAX 16u        /* a shared prefix is cut into at most this many chunks */
 
 /* Host-side structural validation; dereferences nothing on the device
  * (cf_kv_validate_paged_attention_desc, src/cuda/paged_kv_attention.cu:280-299). */
