@@ -386,9 +386,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                             rb[n][4] = b_hi.x; rb[n][5] = b_hi.y; rb[n][6] = b_hi.z; rb[n][7] = b_hi.w;
                         }
 #pragma unroll
-                        for (int dd = 0; dd < 4; ++dd) {
+                        for (int tq = 0; tq < 4; ++tq) {   // token quads outside: consecutive mma feed different accumulators
 #pragma unroll
-                            for (int tq = 0; tq < 4; ++tq) {
+                            for (int dd = 0; dd < 4; ++dd) {
                                 uint32_t lo, hi;
                                 quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
 #pragma unroll

@@ -261,28 +261,34 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
                 uint32_t tc[2];
                 if (__float_as_uint(meta[4 * pg + 2]) == 0u && (pg + 1 >= in_round || __float_as_uint(meta[4 * pg + 6]) == 0u))
                     continue;   // neither page of the pair is present (uniform across the block)
+                const uint32_t *krow[2][2];
+                uint32_t krot[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const bool present = pg + h < in_round;
                     ks[h] = present ? meta[4 * (pg + h)] : 0.0f;
                     vs[h] = present ? meta[4 * (pg + h) + 1] : 0.0f;
                     tc[h] = present ? __float_as_uint(meta[4 * (pg + h) + 2]) : 0u;
-                    const uint8_t *kt = tiles + (pg + h) * kTileBytes;
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt) {
                         s[h][nt][0] = s[h][nt][1] = s[h][nt][2] = s[h][nt][3] = 0.0f;
-                        if (tc[h] == 0u) continue;   // uniform across the warp
                         const uint32_t tok = 4u * (g >> 1) + (g & 1u) + 2u * nt;   // the token of column n = g
-                        const uint32_t *row = reinterpret_cast<const uint32_t *>(kt + tok * 128u);
-                        const uint32_t rot = k_rotation(tok);
+                        krow[h][nt] = reinterpret_cast<const uint32_t *>(tiles + (pg + h) * kTileBytes + tok * 128u) + t;
+                        krot[nt] = k_rotation(tok);
+                    }
+                }
 #pragma unroll
-                        for (int ss = 0; ss < 8; ++ss) {
+                for (int ss = 0; ss < 8; ++ss)   // k-steps outside: consecutive mma feed different accumulators
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (tc[h] == 0u) continue;   // uniform across the warp
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt) {
                             uint32_t b0, b1;
-                            quad_to_half2(row[4u * ((ss + rot) & 7u) + t], b0, b1);
+                            quad_to_half2(krow[h][nt][4u * ((ss + krot[nt]) & 7u)], b0, b1);
                             mma_16816(s[h][nt], qa[ss][0], qa[ss][1], qa[ss][2], qa[ss][3], b0, b1);
                         }
                     }
-                }
                 // scores, masks, row maxima (row g: fragments 0,1; row g+8: fragments 2,3; columns 2t+e)
                 float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
 #pragma unroll
@@ -354,11 +360,14 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
                     if (tc[h] == 0u) continue;
                     const uint32_t *vt = reinterpret_cast<const uint32_t *>(tiles + (pg + h) * kTileBytes + 2048u);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {   // channels 8j + g, tokens 4t..4t+3
-                        uint32_t b0, b1;
-                        quad_to_half2(vt[(8u * j + g) * 4u + t], b0, b1);
-                        mma_16816(o[j], pa[h][0][0], pa[h][0][1], pa[h][0][2], pa[h][0][3], b0, b1);
-                        mma_16816(o[j], pa[h][1][0], pa[h][1][1], pa[h][1][2], pa[h][1][3], b0, b1);
+                    for (int j0 = 0; j0 < 16; j0 += 4) {   // channels 8j + g, tokens 4t..4t+3; four accumulators in flight
+                        uint32_t b0[4], b1[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) quad_to_half2(vt[(8u * (j0 + j) + g) * 4u + t], b0[j], b1[j]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) mma_16816(o[j0 + j], pa[h][0][0], pa[h][0][1], pa[h][0][2], pa[h][0][3], b0[j], b1[j]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) mma_16816(o[j0 + j], pa[h][1][0], pa[h][1][1], pa[h][1][2], pa[h][1][3], b0[j], b1[j]);
                     }
                 }
             }
