@@ -34,6 +34,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + write) of one attention launch over its algorithmic bytes, from the ncu captures of the batch-16
+# case of the same workload (profiles/lanes_attention_kernel_batch16.md); traffic grows in proportion to the pages read.
+DRAM_TRAFFIC_RATIO = {"rans": 410.8 / 387.9, "huffman": 388.5 / 365.6, "fixed8": 481.9 / 457.0}
 METRIC = "sealed-KV decode attn seq-tokens/s"
 UNIT = "seq-tokens/s"
 HQ, HKV, D, T, BLOCK = 32, 8, 128, 16, 64
@@ -380,7 +383,9 @@ def main():
         "gpu_launches": 3 * a.steps,
         "roofline": {"bound": "hbm", "kernel": "lanes_attention_kernel" if a.kernel != "generic" else "generic_attention_kernel",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
+                     "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": (int(algo_bytes * DRAM_TRAFFIC_RATIO[a.coder]) if a.kernel != "generic" else None),
+                     "traffic_source": "ncu dram bytes of the batch-16 capture scaled by algorithmic bytes",
                      "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": stage_ms[1],
                      "plan_ms": stage_ms[0], "combine_ms": stage_ms[2],
                      "decompressed_equivalent_gbs": tokens_rank * info["fp16_bytes_per_seq_token"] / att_s / 1e9},
