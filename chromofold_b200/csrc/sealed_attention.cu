@@ -52,8 +52,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     if (shared) {
         const uint32_t *row0 = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
         int bad = 0;
-        for (uint32_t s = begin; s < end; ++s)
-            if (p.seq_sealed_tokens[slot_of(p, s)] / p.page_tokens < shared) bad = 1;
+        for (uint32_t s = begin; s < end; ++s) {   // the pages must be sealed and wholly visible to the entry's query token
+            const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
+            const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
+            if (sealed / p.page_tokens < shared || qpos + 1u < shared * p.page_tokens) bad = 1;
+        }
         const uint64_t cells = static_cast<uint64_t>(p.seq_count) * shared;
         for (uint64_t i = tid; i < cells && !bad; i += kPlanThreads) {
             const uint32_t s = static_cast<uint32_t>(i / shared), pg = static_cast<uint32_t>(i % shared);
@@ -570,8 +573,8 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     if (d->kernel == CF_B200_KERNEL_LANES && !lanes_ok) return CF_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
-    // the shared-prefix kernel works on rows of 128 = whole query groups, full history, decode-step positions
-    if (use_lanes && d->shared_prefix_pages && d->causal_window == 0 && d->query_positions == nullptr && 128u % p.group == 0) {
+    // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
+    if (use_lanes && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static int sm_count = 0;
         if (sm_count == 0) {
             int device = 0;

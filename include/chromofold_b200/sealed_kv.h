@@ -107,9 +107,11 @@ typedef struct cf_b200_sealed_attention_desc {
     /* Shared prefix: the caller states that the first shared_prefix_pages entries of the page-table row of EVERY
      * listed sequence name the same pages (one sealed copy referenced by all, src/multisequence_cache.cpp:235-292).
      * Such pages are then decoded once per 128 query rows instead of once per sequence, and the contraction with all
-     * the rows that share them runs on the tensor cores. It is a hint: the plan kernel checks the rows; if they
-     * differ, or the geometry is not the lanes kernel's, or causal_window / query_positions are in use, every page
-     * is handled per sequence as if the field were 0 (a mismatch also raises CF_B200_DEVSTAT_PREFIX_MISMATCH).
+     * the rows that share them runs on the tensor cores. Entries that name the SAME slot with different
+     * query_positions (multi-query / prefill attention) share all of that slot's sealed pages this way. It is a
+     * hint: the plan kernel checks the rows and that every entry's query position lies at or after the last shared
+     * token; if not, or the geometry is not the lanes kernel's, or causal_window is in use, every page is handled
+     * per entry as if the field were 0 (a failed check also raises CF_B200_DEVSTAT_PREFIX_MISMATCH).
      * The workspace must have been sized with the field set (cf_b200_sealed_attention_workspace_bytes). */
     uint32_t shared_prefix_pages;
     uint32_t reserved0;

@@ -185,3 +185,41 @@ def test_shared_prefix_claim_that_does_not_hold_falls_back(native, oracle):
     claimed = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=16).cpu().numpy()
     assert np.array_equal(claimed, plain)
     assert layer.device_status() == 0x20
+
+
+def test_prefill_query_tokens_share_the_sealed_history(native, oracle):
+    """Multi-query (prefill) attention over sealed pages: several entries name the same slot at consecutive query
+    positions (src/cuda/paged_kv_attention.cu:67-69). With the shared-prefix hint the slot's sealed pages are decoded
+    once for all the query tokens; the result equals the per-entry path, and the last position equals a decode step."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    # the empty slots only make the layer's workspace large enough for eleven entries
+    layer, info = build_sealed_layer(np.array([2048, 1024] + [0] * 10), coder="rans", seed=80, extra_pages_per_sequence=4)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(81)
+    for step in range(11):                     # an unsealed tail of 11 tokens on both sequences
+        k = (torch.randn((2, 8, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((2, 8, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append([0, 1], k, v)
+    n = 11
+    q = _q(n, 32, 82)
+    slots = [0] * n
+    positions = torch.arange(2048, 2048 + n, dtype=torch.int32, device="cuda")   # token j of the tail asks as itself
+    per_entry = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=positions).cpu().numpy()
+    shared = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=positions,
+                             shared_prefix_pages=2048 // 16).cpu().numpy()
+    assert layer.device_status() == 0
+    ok, err = attention_close(shared, per_entry)
+    assert ok, err
+    assert not np.allclose(shared[0], shared[5])
+    # the last query token sees every cached token except none after it: position 2058 = sealed + tail - 1
+    decode = layer.attention(q[n - 1:].contiguous(), slots=[0], kernel=native.KERNEL_LANES,
+                             query_positions=positions[n - 1:].contiguous()).cpu().numpy()
+    ok, err = attention_close(shared[n - 1:], decode)
+    assert ok, err
+    # a position inside the shared pages makes the claim false for that entry: refused, per-entry result
+    early = positions.clone()
+    early[3] = 1000
+    a = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=early, shared_prefix_pages=128).cpu().numpy()
+    b = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=early).cpu().numpy()
+    assert np.array_equal(a, b) and layer.device_status() == 0x20
