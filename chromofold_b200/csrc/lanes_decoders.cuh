@@ -88,6 +88,7 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t e0, uint32_t e1, uin
 // shared memory once per quad (four symbols), which is as often as it can run dry.
 struct RansLane {
     static constexpr bool kWholeQuads = false;
+    static constexpr int kSymbolsPerReload = 4;   // a symbol takes at most two bytes; the window holds eight
     uint32_t x, whi, wlo, used;   // state; window (next byte = top byte of whi); bits taken since the reload
     uint32_t pos;                 // shared-memory byte address of the first byte not yet taken at the last reload
     uint32_t table;               // shared-memory byte address of the slot table
@@ -133,6 +134,7 @@ struct RansLane {
 
 struct HuffLane {
     static constexpr bool kWholeQuads = false;
+    static constexpr int kSymbolsPerReload = 5;   // a code takes at most 12 bits; the window holds 64
     uint32_t whi, wlo, used;   // window of upcoming bits, MSB first; bits taken since the reload
     uint32_t words, bit;       // shared-memory address of the payload words; bit position at the last reload
     uint32_t table;
@@ -142,7 +144,7 @@ struct HuffLane {
         table = smem_addr(lut);
         used = 0;
     }
-    __device__ __forceinline__ void reload() {  // four codes take at most 48 bits; the window holds 64
+    __device__ __forceinline__ void reload() {
         bit += used;
         used = 0;
         const uint32_t base = words + ((bit >> 5) << 2), off = bit & 31u;
@@ -172,6 +174,7 @@ struct HuffLane {
 
 struct FixedLane {
     static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
+    static constexpr int kSymbolsPerReload = 4;
     const uint32_t *words;
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane) {
         words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;

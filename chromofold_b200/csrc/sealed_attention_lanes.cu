@@ -81,26 +81,28 @@ __device__ __forceinline__ void score_quad(UnitState<NG> &u, const QSrc &qs, int
 
 template <class KLane, class VLane, int NG, class QSrc>
 __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &u, const QSrc &qs) {
+    if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-        uint32_t kq = 0, vv = 0;
-        if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
-            kq = k.quad();
-            vv = v.quad();
-        } else {
-            k.reload();
-            v.reload();
-            uint32_t ke[4], ve[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {  // two independent decoder chains, interleaved symbol by symbol
-                ke[i] = k.symbol();
-                ve[i] = v.symbol();
-            }
-            kq = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
-            vv = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
+        for (int q = 0; q < 16; ++q) {
+            const uint32_t kq = k.quad();
+            u.vq[q] = v.quad();
+            score_quad(u, qs, q, kq);
         }
-        u.vq[q] = vv;
-        score_quad(u, qs, q, kq);
+    } else {
+        // two independent decoder chains, interleaved symbol by symbol; each window is refilled as rarely as its
+        // coder's worst case allows, four symbols make one packed register
+        uint32_t ke[4], ve[4];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            if (i % KLane::kSymbolsPerReload == 0) k.reload();
+            if (i % VLane::kSymbolsPerReload == 0) v.reload();
+            ke[i & 3] = k.symbol();
+            ve[i & 3] = v.symbol();
+            if ((i & 3) == 3) {
+                u.vq[i >> 2] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
+                score_quad(u, qs, i >> 2, pack_low_bytes(ke[0], ke[1], ke[2], ke[3]));
+            }
+        }
     }
 }
 
