@@ -29,6 +29,10 @@ namespace {
 
 using namespace lanes;
 
+#ifndef CFB_PV_IN_FLIGHT
+#define CFB_PV_IN_FLIGHT 4
+#endif
+constexpr int kPvInFlight = CFB_PV_IN_FLIGHT;   // independent accumulators between an mma and the next one on the same accumulator
 constexpr int kPWarps = 8;
 constexpr int kPThreads = kPWarps * 32;
 constexpr uint32_t kTileBytes = 4096;                       // K int8 [16][128] + V int8 [128][16]
@@ -360,14 +364,14 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
                     if (tc[h] == 0u) continue;
                     const uint32_t *vt = reinterpret_cast<const uint32_t *>(tiles + (pg + h) * kTileBytes + 2048u);
 #pragma unroll
-                    for (int j0 = 0; j0 < 16; j0 += 4) {   // channels 8j + g, tokens 4t..4t+3; four accumulators in flight
-                        uint32_t b0[4], b1[4];
+                    for (int j0 = 0; j0 < 16; j0 += kPvInFlight) {   // channels 8j + g, tokens 4t..4t+3
+                        uint32_t b0[kPvInFlight], b1[kPvInFlight];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) quad_to_half2(vt[(8u * (j0 + j) + g) * 4u + t], b0[j], b1[j]);
+                        for (int j = 0; j < kPvInFlight; ++j) quad_to_half2(vt[(8u * (j0 + j) + g) * 4u + t], b0[j], b1[j]);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) mma_16816(o[j0 + j], pa[h][0][0], pa[h][0][1], pa[h][0][2], pa[h][0][3], b0[j], b1[j]);
+                        for (int j = 0; j < kPvInFlight; ++j) mma_16816(o[j0 + j], pa[h][0][0], pa[h][0][1], pa[h][0][2], pa[h][0][3], b0[j], b1[j]);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) mma_16816(o[j0 + j], pa[h][1][0], pa[h][1][1], pa[h][1][2], pa[h][1][3], b0[j], b1[j]);
+                        for (int j = 0; j < kPvInFlight; ++j) mma_16816(o[j0 + j], pa[h][1][0], pa[h][1][1], pa[h][1][2], pa[h][1][3], b0[j], b1[j]);
                     }
                 }
             }
