@@ -58,6 +58,7 @@ def parse():
     ap.add_argument("--min-pages-per-unit", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed comparison kernel")
+    ap.add_argument("--no-others", action="store_true", help="skip the legs that time the same workload sealed with the other coders")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every rank has its own batch; strong: one batch sharded over the ranks by the scheduler")
@@ -395,6 +396,32 @@ def main():
         base, parity = cpu_baseline(a, layer, contexts, q.cpu().numpy(), out)
         line["cpu_baseline"] = base
         line["parity_full_size"] = parity
+    if world == 1 and not a.no_others:
+        # the same codes sealed with the other coders of the format, timed the same way (device-resident inputs)
+        others = {}
+        info.pop("dense_k", None)
+        info.pop("dense_v", None)
+        del layer
+        torch.cuda.empty_cache()
+        for coder in ("rans", "huffman", "fixed8"):
+            if coder == a.coder:
+                continue
+            other, oinfo = build_sealed_layer(contexts, query_heads=HQ, kv_heads=HKV, head_dim=D, page_tokens=T,
+                                              block_size=BLOCK, coder=coder, dist=("laplace", a.laplace_b), seed=4,
+                                              device=device)
+            ostep = lambda: other.attention(q, out=out, **kw)
+            for _ in range(5):
+                ostep()
+            oms = timed(ostep, a.steps)
+            others[coder] = {"value": tokens_total * a.steps / (oms * 1e-3), "unit": UNIT, "ms_per_step": oms / a.steps,
+                             "sealed_bytes_per_seq_token": oinfo["bytes_per_seq_token"],
+                             "kv_memory_reduction_vs_fp16": oinfo["fp16_bytes_per_seq_token"] / oinfo["bytes_per_seq_token"],
+                             "sealed_gbs": oinfo["sealed_bytes"] * a.steps / (oms * 1e-3) / 1e9,
+                             "frac_of_peak": oinfo["sealed_bytes"] * a.steps / (oms * 1e-3) / 1e9 / peak,
+                             "device_status": other.device_status()}
+            del other, oinfo
+            torch.cuda.empty_cache()
+        line["other_coders"] = others
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
