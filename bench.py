@@ -321,6 +321,7 @@ def main():
     torch.cuda.synchronize()
     t1 = time.time()
     stage_ms = [float(np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(a.steps)])) for i in range(3)]
+    per_launch = np.array([ev[s][1].elapsed_time(ev[s][2]) for s in range(a.steps)])   # the attention kernel, launch by launch
     clocks = sampler.stop(t0, t1) if sampler else None
     status = layer.device_status()
 
@@ -389,6 +390,9 @@ def main():
                      "traffic_source": "ncu dram bytes of the batch-16 capture scaled by algorithmic bytes",
                      "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": stage_ms[1],
                      "plan_ms": stage_ms[0], "combine_ms": stage_ms[2],
+                     "kernel_ms_median": float(np.median(per_launch)), "kernel_ms_p5": float(np.percentile(per_launch, 5)),
+                     "kernel_ms_p95": float(np.percentile(per_launch, 95)),
+                     "kernel_ms_cv": float(per_launch.std() / per_launch.mean()),
                      "decompressed_equivalent_gbs": tokens_rank * info["fp16_bytes_per_seq_token"] / att_s / 1e9},
         "clocks": clocks, "device_status": status, "dense_fp16": dense,
     }

@@ -60,6 +60,30 @@ def config3(a, device):
             torch.cuda.empty_cache()
 
 
+def config3_blocks(a, device):
+    """Block-size dial of the coder crossover: what 128- and 256-symbol blocks save in bytes (fewer per-block states
+    and offsets) and what they cost (they run on the any-geometry kernel; the lane-per-block kernel is built for
+    32 blocks of 64 symbols per stream)."""
+    contexts = np.full(8, 8192)
+    for p in (0.1, 0.4):
+        for coder in ("rans", "huffman"):
+            for block in (64, 128, 256):
+                layer, info = build_sealed_layer(contexts, coder=coder, dist=("geometric", p), seed=40, device=device,
+                                                 block_size=block)
+                q = _queries(8, 32, 41, device)
+                out = torch.zeros((8, 32, 128), dtype=torch.float32, device=device)
+                ms = _time(lambda: layer.attention(q, out=out), max(a.steps // 3, 3), 2)
+                print(json.dumps({"config": 3, "p": p, "coder": coder, "block_size": block,
+                                  "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
+                                  "bits_per_code_stored": round(info["bytes_per_seq_token"] * 8 / 2048, 3),
+                                  "h0_bits_per_code": round(info["h0_bits_k"], 3),
+                                  "kernel": "lanes" if block == 64 else "generic", "ms_per_step": round(ms, 4),
+                                  "seq_tokens_per_s": round(int(contexts.sum()) / ms * 1e3),
+                                  "device_status": layer.device_status()}))
+                del layer, info
+                torch.cuda.empty_cache()
+
+
 def config4(a, device, rank, world):
     """Long context, 70B shape: 64 query / 8 kv heads, 8 sequences x 131072 tokens, kv heads sharded."""
     import torch.distributed as dist
@@ -160,6 +184,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"], help="configurations 4 and 5")
+    ap.add_argument("--blocks", action="store_true", help="configuration 3: the block-size dial instead of the p sweep")
     ap.add_argument("--batch4", type=int, default=8)
     ap.add_argument("--ctx4", type=int, default=131072)
     ap.add_argument("--seqs5", type=int, default=256)
@@ -176,7 +201,9 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
-    if a.config == 3:
+    if a.config == 3 and a.blocks:
+        config3_blocks(a, device)
+    elif a.config == 3:
         config3(a, device)
     elif a.config == 4:
         config4(a, device, rank, world)
