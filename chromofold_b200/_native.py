@@ -93,6 +93,20 @@ EXPORTS = {
         "cf_ms_cuda_publish_page_async", "cf_ms_cuda_stage_active_async", "cf_ms_cuda_copy_sequence_async",
         "cf_ms_cuda_shift_sequence", "cf_ms_cuda_execute_batch_async", "cf_ms_cuda_cancel_sequence_async",
         "cf_ms_cuda_reclaim_async", "cf_ms_cuda_audit", "cf_ms_cuda_get_counters", "cf_ms_cuda_last_error",
+        "cf_b200_ms_append_active_async", "cf_b200_ms_seal_active_async", "cf_b200_ms_truncate_async",
+        "cf_b200_ms_sequence_tokens", "cf_b200_ms_page_sharing",
+    ],
+    "compat_mscache.h": [
+        "cf_multisequence_create", "cf_multisequence_destroy", "cf_sequence_create", "cf_sequence_copy_async",
+        "cf_sequence_remove_async", "cf_sequence_shift_async", "cf_sequence_append_async",
+        "cf_multisequence_attention_async", "cf_sequence_speculation_begin", "cf_sequence_speculation_commit",
+        "cf_sequence_speculation_rollback", "cf_multisequence_reclaim_async", "cf_multisequence_audit",
+        "cf_multisequence_get_counters", "cf_multisequence_last_error",
+        "cf_llama_server_runtime_create", "cf_llama_server_runtime_destroy", "cf_llama_server_slot_create",
+        "cf_llama_server_slot_reset_async", "cf_llama_server_cancel_async", "cf_llama_server_sequence_copy_async",
+        "cf_llama_server_sequence_remove_async", "cf_llama_server_sequence_shift_async",
+        "cf_llama_server_append_layer_async", "cf_llama_server_execute_batch_async", "cf_llama_server_shutdown_async",
+        "cf_llama_server_get_stats", "cf_llama_server_last_error",
     ],
     "compat_production.h": [
         "cf_attention_runtime_create", "cf_attention_runtime_destroy", "cf_attention_execute_async",

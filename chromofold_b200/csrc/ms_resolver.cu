@@ -100,6 +100,7 @@ struct cf_ms_cuda_resolver {
     std::vector<uint32_t> free_slots;
     uint64_t next_page_id = 1;
     uint32_t next_slot = 0;
+    uint64_t ref_increments = 0, ref_decrements = 0;   // page references taken / dropped by sequences
     cf_ms_cuda_counters counters{};
     std::string error;
     // device side
@@ -246,6 +247,77 @@ void retire_if_unreferenced(cf_ms_cuda_resolver *r, SharedPage &page) {
     r->counters.pending_reclamation_bytes_peak = std::max(r->counters.pending_reclamation_bytes_peak, r->counters.pending_reclamation_bytes);
 }
 
+// Seal `token_count` fp32 rows laid out [kv head][page_size][dim] at src_k / src_v into format-v1 records (one launch),
+// append their ids to the sequence's page-table row of `layer` and return the number of tiles. The first page of a
+// layer also calibrates the layer's shared codebooks from its own codes.
+uint32_t seal_rows(cf_ms_cuda_resolver *r, Sequence &q, uint32_t layer, const float *src_k, const float *src_v,
+                   uint32_t token_count, SharedPage &page, cudaStream_t s) {
+    LayerSeq &L = q.layers[layer];
+    const uint32_t n = (token_count + r->tile - 1) / r->tile;
+    r->grow_stride(L.tiles + n, s);
+    r->records += static_cast<uint64_t>(n) * r->config.kv_head_count;
+    r->arena.ensure(r->records * r->max_record_bytes() + 4096, s);
+    std::vector<uint32_t> host(4 * n);
+    for (uint32_t j = 0; j < n; ++j) {
+        uint32_t id;
+        if (!r->free_store_ids.empty()) { id = r->free_store_ids.back(); r->free_store_ids.pop_back(); }
+        else id = r->next_store_id++;
+        page.store_ids.push_back(id);
+        host[j] = 0;
+        host[n + j] = id;
+        host[2 * n + j] = std::min(r->tile, token_count - j * r->tile);
+        host[3 * n + j] = j * r->tile;
+    }
+    r->page_dir.ensure(static_cast<size_t>(r->next_store_id + 1) * r->config.kv_head_count, s);
+    r->jobs.ensure(4 * n, s);
+    cuda_check(cudaMemcpyAsync(r->jobs.ptr, host.data(), host.size() * 4, cudaMemcpyHostToDevice, s), "upload seal jobs");
+    cf_b200_seal_desc sd{};
+    sd.struct_size = sizeof sd;
+    sd.abi_version = CF_B200_ABI_VERSION;
+    sd.kv_head_count = r->config.kv_head_count;
+    sd.head_dim = r->config.head_dim;
+    sd.page_tokens = r->tile;
+    sd.block_size = 64;
+    sd.coder = CF_B200_CODER_RANS;
+    sd.codebook_id = layer;
+    sd.k_tables = r->tables.ptr + 2 * layer;
+    sd.v_tables = r->tables.ptr + 2 * layer + 1;
+    sd.tail_k = src_k;
+    sd.tail_v = src_v;
+    sd.tail_type = CF_B200_F32;
+    sd.tail_capacity = r->config.page_size;
+    sd.job_slots = r->jobs.ptr;
+    sd.job_pages = r->jobs.ptr + n;
+    sd.job_tokens = r->jobs.ptr + 2 * n;
+    sd.job_rows = r->jobs.ptr + 3 * n;
+    sd.job_count = n;
+    sd.arena = r->arena.ptr;
+    sd.arena_units = r->arena.count / 16;
+    sd.arena_cursor_units = r->cursor.ptr;
+    sd.page_dir = r->page_dir.ptr;
+    sd.status = r->status.ptr;
+    if (!r->calibrated[layer]) {
+        cuda_check(cudaMemsetAsync(r->cursor.ptr + 1, 0, 512 * sizeof(unsigned long long), s), "clear histograms");
+        if (cf_b200_histogram_async(&sd, r->cursor.ptr + 1, r->cursor.ptr + 257, s) != CF_OK) throw std::runtime_error("histogram launch rejected");
+        unsigned long long hist[512];
+        cuda_check(cudaMemcpyAsync(hist, r->cursor.ptr + 1, sizeof hist, cudaMemcpyDeviceToHost, s), "read histograms");
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+        std::vector<cf_b200_codebook_tables> tables(2);
+        uint64_t hk[256], hv[256];
+        for (int i = 0; i < 256; ++i) { hk[i] = hist[i]; hv[i] = hist[256 + i]; }
+        if (cf_b200_codebook_build(hk, &tables[0]) != CF_OK || cf_b200_codebook_build(hv, &tables[1]) != CF_OK)
+            throw std::runtime_error("codebook build failed");
+        cuda_check(cudaMemcpyAsync(r->tables.ptr + 2 * layer, tables.data(), 2 * sizeof(cf_b200_codebook_tables),
+                                   cudaMemcpyHostToDevice, s), "upload codebooks");
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+        r->calibrated[layer] = true;
+    }
+    if (cf_b200_seal_pages_async(&sd, s) != CF_OK) throw std::runtime_error("seal launch rejected");
+    cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(layer, q.slot) * r->stride + L.tiles, host.data() + n, n * 4,
+                               cudaMemcpyHostToDevice, s), "publish page ids");
+    return n;
+}
+
 }  // namespace
 
 extern "C" cf_ms_cuda_resolver *cf_ms_cuda_create(const cf_ms_cuda_config *c) {
@@ -299,77 +371,17 @@ extern "C" int cf_ms_cuda_publish_page_async(cf_ms_cuda_resolver *r, const cf_ms
         if (L.partial_last) throw std::runtime_error("a short page can only be the last page of a layer");
         if (d.token_begin != L.sealed_tokens) throw std::runtime_error("published page must continue the sealed history of the layer");
         r->ensure_ready(s);
-        const uint32_t n = (d.token_count + r->tile - 1) / r->tile;
-        r->grow_stride(L.tiles + n, s);
-        r->records += static_cast<uint64_t>(n) * r->config.kv_head_count;
-        r->arena.ensure(r->records * r->max_record_bytes() + 4096, s);
         // transcode: int4 page -> fp32 scratch rows -> format-v1 records
         const uint64_t count = static_cast<uint64_t>(d.token_count) * d.kv_head_count * d.head_dim;
         unpack_reference_page_kernel<<<static_cast<int>((count + 255) / 256), 256, 0, s>>>(d, r->scratch_k.ptr, r->scratch_v.ptr,
                                                                                          r->config.page_size);
         cuda_check(cudaGetLastError(), "page unpack launch");
         SharedPage page;
-        std::vector<uint32_t> host(4 * n);
-        for (uint32_t j = 0; j < n; ++j) {
-            uint32_t id;
-            if (!r->free_store_ids.empty()) { id = r->free_store_ids.back(); r->free_store_ids.pop_back(); }
-            else id = r->next_store_id++;
-            page.store_ids.push_back(id);
-            host[j] = 0;
-            host[n + j] = id;
-            host[2 * n + j] = std::min(r->tile, d.token_count - j * r->tile);
-            host[3 * n + j] = j * r->tile;
-        }
-        r->page_dir.ensure(static_cast<size_t>(r->next_store_id + 1) * r->config.kv_head_count, s);
-        r->jobs.ensure(4 * n, s);
-        cuda_check(cudaMemcpyAsync(r->jobs.ptr, host.data(), host.size() * 4, cudaMemcpyHostToDevice, s), "upload seal jobs");
-        cf_b200_seal_desc sd{};
-        sd.struct_size = sizeof sd;
-        sd.abi_version = CF_B200_ABI_VERSION;
-        sd.kv_head_count = r->config.kv_head_count;
-        sd.head_dim = r->config.head_dim;
-        sd.page_tokens = r->tile;
-        sd.block_size = 64;
-        sd.coder = CF_B200_CODER_RANS;
-        sd.codebook_id = pub->layer;
-        sd.k_tables = r->tables.ptr + 2 * pub->layer;
-        sd.v_tables = r->tables.ptr + 2 * pub->layer + 1;
-        sd.tail_k = r->scratch_k.ptr;
-        sd.tail_v = r->scratch_v.ptr;
-        sd.tail_type = CF_B200_F32;
-        sd.tail_capacity = r->config.page_size;
-        sd.job_slots = r->jobs.ptr;
-        sd.job_pages = r->jobs.ptr + n;
-        sd.job_tokens = r->jobs.ptr + 2 * n;
-        sd.job_rows = r->jobs.ptr + 3 * n;
-        sd.job_count = n;
-        sd.arena = r->arena.ptr;
-        sd.arena_units = r->arena.count / 16;
-        sd.arena_cursor_units = r->cursor.ptr;
-        sd.page_dir = r->page_dir.ptr;
-        sd.status = r->status.ptr;
-        if (!r->calibrated[pub->layer]) {
-            cuda_check(cudaMemsetAsync(r->cursor.ptr + 1, 0, 512 * sizeof(unsigned long long), s), "clear histograms");
-            if (cf_b200_histogram_async(&sd, r->cursor.ptr + 1, r->cursor.ptr + 257, s) != CF_OK) throw std::runtime_error("histogram launch rejected");
-            unsigned long long hist[512];
-            cuda_check(cudaMemcpyAsync(hist, r->cursor.ptr + 1, sizeof hist, cudaMemcpyDeviceToHost, s), "read histograms");
-            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
-            std::vector<cf_b200_codebook_tables> tables(2);
-            uint64_t hk[256], hv[256];
-            for (int i = 0; i < 256; ++i) { hk[i] = hist[i]; hv[i] = hist[256 + i]; }
-            if (cf_b200_codebook_build(hk, &tables[0]) != CF_OK || cf_b200_codebook_build(hv, &tables[1]) != CF_OK)
-                throw std::runtime_error("codebook build failed");
-            cuda_check(cudaMemcpyAsync(r->tables.ptr + 2 * pub->layer, tables.data(), 2 * sizeof(cf_b200_codebook_tables),
-                                       cudaMemcpyHostToDevice, s), "upload codebooks");
-            cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
-            r->calibrated[pub->layer] = true;
-        }
-        if (cf_b200_seal_pages_async(&sd, s) != CF_OK) throw std::runtime_error("seal launch rejected");
-        cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(pub->layer, q.slot) * r->stride + L.tiles, host.data() + n, n * 4,
-                                   cudaMemcpyHostToDevice, s), "publish page ids");
+        const uint32_t n = seal_rows(r, q, pub->layer, r->scratch_k.ptr, r->scratch_v.ptr, d.token_count, page, s);
         page.seal_generation = pub->seal_generation;
         page.resident_bytes = pub->resident_bytes;
         page.logical_refs = 1;
+        ++r->ref_increments;
         const uint64_t id = r->next_page_id++;
         L.pages.push_back({id, static_cast<int64_t>(d.token_begin), d.token_count, L.tiles, n});
         r->pages.emplace(id, std::move(page));
@@ -425,6 +437,148 @@ extern "C" int cf_ms_cuda_stage_active_async(cf_ms_cuda_resolver *r, int64_t id,
     });
 }
 
+// ---- additive entry points: the append / seal / truncate seam of a data-bearing sequence cache ---------------------
+// (what cf_sequence_append_async + the device seal engine + cf_ms_cuda_publish_page_async do together in the
+// reference, without the int4 detour: rows are appended to the active tail and the tail is sealed in one launch)
+
+extern "C" int cf_b200_ms_append_active_async(cf_ms_cuda_resolver *r, int64_t id, uint32_t layer, uint32_t token_begin,
+                                              const cf_device_tensor_view *keys, const cf_device_tensor_view *values, void *stream) {
+    if (!r || !keys || !values) return -1;
+    if (cf_device_tensor_validate(keys) != 0 || cf_device_tensor_validate(values) != 0) return -1;
+    return locked(r, true, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        auto it = r->sequences.find(id);
+        if (it == r->sequences.end() || layer >= it->second.layers.size()) throw std::invalid_argument("append target is invalid");
+        if (keys->token_count != values->token_count || keys->head_count != r->config.kv_head_count ||
+            values->head_count != r->config.kv_head_count || keys->head_dim != r->config.head_dim ||
+            values->head_dim != r->config.head_dim || keys->token_count == 0)
+            throw std::invalid_argument("append tensor topology mismatch");
+        Sequence &q = it->second;
+        LayerSeq &L = q.layers[layer];
+        if (L.partial_last) throw std::invalid_argument("a layer whose last page is short cannot grow");
+        if (token_begin != L.sealed_tokens + L.active_count) throw std::invalid_argument("non-contiguous sequence append");
+        if (L.active_count + keys->token_count > r->config.page_size)
+            throw std::invalid_argument("append crosses sequence active-page boundary");
+        r->ensure_ready(s);
+        const uint64_t count = static_cast<uint64_t>(keys->token_count) * keys->head_count * keys->head_dim;
+        const int blocks = static_cast<int>((count + 255) / 256);
+        const size_t base = r->row(layer, q.slot) * r->page_values();
+        rows_to_tail_kernel<<<blocks, 256, 0, s>>>(*keys, r->tail_k.ptr + base, r->config.page_size, L.active_count);
+        rows_to_tail_kernel<<<blocks, 256, 0, s>>>(*values, r->tail_v.ptr + base, r->config.page_size, L.active_count);
+        cuda_check(cudaGetLastError(), "append sequence rows");
+        if (!L.active_count) L.active_begin = L.sealed_tokens;
+        L.active_count += keys->token_count;
+        ++L.active_generation;
+        r->push_scalars(q, layer, s);
+    });
+}
+
+extern "C" int cf_b200_ms_seal_active_async(cf_ms_cuda_resolver *r, int64_t id, uint32_t layer, void *stream) {
+    if (!r) return -1;
+    return locked(r, true, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        auto it = r->sequences.find(id);
+        if (it == r->sequences.end() || layer >= it->second.layers.size()) throw std::invalid_argument("seal target is invalid");
+        Sequence &q = it->second;
+        LayerSeq &L = q.layers[layer];
+        if (!L.active_count) throw std::invalid_argument("no active rows to seal");
+        if (L.partial_last) throw std::invalid_argument("a short page can only be the last page of a layer");
+        r->ensure_ready(s);
+        const size_t base = r->row(layer, q.slot) * r->page_values();
+        SharedPage page;
+        const uint32_t n = seal_rows(r, q, layer, r->tail_k.ptr + base, r->tail_v.ptr + base, L.active_count, page, s);
+        page.logical_refs = 1;
+        ++r->ref_increments;
+        page.resident_bytes = static_cast<uint64_t>(n) * r->config.kv_head_count * r->max_record_bytes();
+        const uint64_t page_id = r->next_page_id++;
+        L.pages.push_back({page_id, static_cast<int64_t>(L.sealed_tokens), L.active_count, L.tiles, n});
+        r->pages.emplace(page_id, std::move(page));
+        L.tiles += n;
+        L.sealed_tokens += L.active_count;
+        L.partial_last = L.active_count % r->tile != 0;
+        L.active_count = 0;
+        L.active_begin = L.sealed_tokens;
+        ++L.descriptor_generation;
+        r->push_scalars(q, layer, s);
+        ++q.topology_generation;
+        ++r->counters.pages_registered;
+        ++r->counters.descriptor_tables_built;
+    });
+}
+
+// Keep the first `token_count` tokens of every layer of the sequence: later whole pages lose this sequence's
+// reference, the active tail is shortened; a cut inside a sealed page is refused (pages are immutable,
+// src/multisequence_cache.cpp:318-321).
+extern "C" int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *r, int64_t id, uint32_t token_count, void *stream) {
+    if (!r) return -1;
+    return locked(r, false, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        Sequence &q = find_sequence(r, id, "sequence is missing");
+        for (const LayerSeq &L : q.layers) {   // validate every layer before changing any
+            if (token_count >= L.sealed_tokens) continue;
+            uint32_t end = 0;
+            bool boundary = token_count == 0;
+            for (const PageRef &ref : L.pages) {
+                end += ref.tokens;
+                if (end == token_count) boundary = true;
+            }
+            if (!boundary) throw std::invalid_argument("removal inside immutable page is not supported");
+        }
+        for (uint32_t layer = 0; layer < q.layers.size(); ++layer) {
+            LayerSeq &L = q.layers[layer];
+            if (token_count >= L.sealed_tokens + L.active_count) continue;
+            if (token_count >= L.sealed_tokens) {
+                L.active_count = token_count - L.sealed_tokens;
+            } else {
+                L.active_count = 0;
+                while (!L.pages.empty() && L.sealed_tokens > token_count) {
+                    const PageRef ref = L.pages.back();
+                    L.pages.pop_back();
+                    L.sealed_tokens -= ref.tokens;
+                    L.tiles -= ref.tiles;
+                    SharedPage &page = r->pages.at(ref.page_id);
+                    --page.logical_refs;
+                ++r->ref_decrements;
+                    ++r->ref_decrements;
+                    retire_if_unreferenced(r, page);
+                }
+                L.partial_last = !L.pages.empty() && L.pages.back().tokens % (r->tile ? r->tile : 1u) != 0;
+                L.active_begin = L.sealed_tokens;
+                ++L.descriptor_generation;
+            }
+            ++L.active_generation;
+            if (r->ready) r->push_scalars(q, layer, s);
+        }
+        ++q.topology_generation;
+    });
+}
+
+extern "C" int cf_b200_ms_page_sharing(const cf_ms_cuda_resolver *r, uint64_t *shared_pages, uint64_t *shared_references,
+                                       uint64_t *reference_increments, uint64_t *reference_decrements) {
+    if (!r || !shared_pages || !shared_references || !reference_increments || !reference_decrements) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    *shared_pages = *shared_references = 0;
+    for (const auto &entry : r->pages)
+        if (entry.second.logical_refs >= 2) {
+            ++*shared_pages;
+            *shared_references += entry.second.logical_refs;
+        }
+    *reference_increments = r->ref_increments;
+    *reference_decrements = r->ref_decrements;
+    return 0;
+}
+
+extern "C" int cf_b200_ms_sequence_tokens(const cf_ms_cuda_resolver *r, int64_t id, uint32_t layer, uint32_t *sealed_tokens,
+                                          uint32_t *active_tokens) {
+    if (!r || !sealed_tokens || !active_tokens) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    auto it = r->sequences.find(id);
+    if (it == r->sequences.end() || layer >= it->second.layers.size()) return -1;
+    *sealed_tokens = it->second.layers[layer].sealed_tokens;
+    *active_tokens = it->second.layers[layer].active_count;
+    return 0;
+}
+
 extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t source_id, int64_t destination_id, void *stream) {
     if (!r || source_id == destination_id) return -1;
     return locked(r, true, [&] {
@@ -439,6 +593,8 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
                 for (const auto &ref : layer.pages) {
                     SharedPage &page = r->pages.at(ref.page_id);
                     --page.logical_refs;
+                ++r->ref_decrements;
+                    ++r->ref_decrements;
                     retire_if_unreferenced(r, page);
                 }
             candidate.slot = old->second.slot;
@@ -449,7 +605,10 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
         candidate.layers = source.layers;
         for (uint32_t layer = 0; layer < r->config.layer_count; ++layer) {
             LayerSeq &L = candidate.layers[layer];
-            for (const auto &ref : L.pages) ++r->pages.at(ref.page_id).logical_refs;
+            for (const auto &ref : L.pages) {
+                ++r->pages.at(ref.page_id).logical_refs;
+                ++r->ref_increments;
+            }
             if (r->ready) {
                 if (L.tiles)
                     cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(layer, candidate.slot) * r->stride,
@@ -624,6 +783,7 @@ extern "C" int cf_ms_cuda_sequence_remove_async(cf_ms_cuda_resolver *r, int64_t 
                 SharedPage &page = r->pages.at(ref.page_id);
                 if (!page.logical_refs) throw std::runtime_error("page logical reference underflow");
                 --page.logical_refs;
+                ++r->ref_decrements;
                 retire_if_unreferenced(r, page);
             }
         r->free_slots.push_back(q.slot);

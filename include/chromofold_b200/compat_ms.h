@@ -81,6 +81,23 @@ int cf_ms_cuda_audit(const cf_ms_cuda_resolver *resolver);                      
 int cf_ms_cuda_get_counters(const cf_ms_cuda_resolver *resolver, cf_ms_cuda_counters *counters);            /* :92 */
 const char *cf_ms_cuda_last_error(const cf_ms_cuda_resolver *resolver);                                     /* :93 */
 
+/* ---- additive, beside the reference's symbols: the append / seal / truncate seam of a data-bearing sequence cache.
+ * In the reference a page reaches the resolver as an int4 descriptor made elsewhere (the seal engine) and rows reach
+ * it only as a whole staged tail; here rows are appended to the active tail as strided typed views (the rules of
+ * cf_device_kv_append_async: contiguous, never across a page boundary) and the tail is sealed in one launch into
+ * format-v1 records and published in the same call. */
+int cf_b200_ms_append_active_async(cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t layer, uint32_t token_begin,
+                                   const cf_device_tensor_view *keys, const cf_device_tensor_view *values, void *stream);
+int cf_b200_ms_seal_active_async(cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t layer, void *stream);
+/* Keep the first token_count tokens of every layer: drops later whole pages (this sequence's reference to them) and
+ * shortens the active tail; a cut inside a sealed page is refused. */
+int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t token_count, void *stream);
+int cf_b200_ms_sequence_tokens(const cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t layer,
+                               uint32_t *sealed_tokens, uint32_t *active_tokens);
+/* Pages referenced by two or more sequences, the references they hold, and the references taken / dropped so far. */
+int cf_b200_ms_page_sharing(const cf_ms_cuda_resolver *resolver, uint64_t *shared_pages, uint64_t *shared_references,
+                            uint64_t *reference_increments, uint64_t *reference_decrements);
+
 #ifdef __cplusplus
 }
 #endif

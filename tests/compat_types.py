@@ -160,3 +160,37 @@ ATTENTION_COUNTER_NAMES = (
 
 class AttentionCounters(C.Structure):
     _fields_ = [(n, _u64) for n in ATTENTION_COUNTER_NAMES]
+
+
+class MultisequenceConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "kv_head_count", "query_head_count", "head_dim", "page_size",
+                                    "gqa_group_size", "use_async_allocator", "enable_invariant_auditor")]
+
+
+MULTISEQUENCE_COUNTER_NAMES = (
+    "sequences_created", "sequences_copied", "sequences_removed", "sequences_shifted", "active_sequences",
+    "active_sequences_peak", "shared_pages", "shared_page_references", "page_ref_increments", "page_ref_decrements",
+    "pages_reclaimed", "pages_pending_reclamation", "pending_reclamation_bytes", "pending_reclamation_bytes_peak",
+    "speculative_transactions_started", "speculative_transactions_committed", "speculative_transactions_rolled_back",
+    "batches_dispatched", "sequences_per_batch_peak", "invariant_audits", "invariant_failures", "unsupported_operations",
+    "dense_fallback_launches")
+
+
+class MultisequenceCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in MULTISEQUENCE_COUNTER_NAMES]
+
+
+class LlamaServerConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "query_head_count", "kv_head_count", "head_dim", "page_size",
+                                    "block_size", "context_window", "gqa_group_size", "cuda_device", "strict_mode")] + [
+        ("evidence_path", C.c_char_p), ("llama_commit", C.c_char_p), ("model_sha256", C.c_char_p)]
+
+
+class LlamaServerBatch(C.Structure):
+    _fields_ = [("tokens", _vp), ("token_item_count", _u32), ("attention_items", _vp), ("attention_item_count", _u32)]
+
+
+class LlamaServerStats(C.Structure):
+    _fields_ = [(n, _u64) for n in ("http_requests", "interleaved_batches", "slot_reuses", "cancelled_requests",
+                                    "context_shifts", "speculative_rollbacks", "dense_nodes_scheduled", "shutdown_audits",
+                                    "shutdown_failures")]

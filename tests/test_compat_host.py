@@ -251,3 +251,70 @@ def test_production_runtime_contract_without_a_gpu(native):
     assert lib.cf_attention_last_error(None) == b"runtime is null"
     lib.cf_attention_runtime_destroy(rt, None)
     lib.cf_attention_runtime_destroy(None, None)
+
+
+def test_multisequence_cache_and_server_contracts_without_a_gpu(native):
+    """The host-only cases of the reference's tests/m10_multisequence_host_contract.cpp and
+    tests/m11_pinned_server_contract.cpp: create / duplicate-reject / copy / speculation / remove / reclaim / audit /
+    counters, and the server runtime's config rules and shutdown audit. No row is appended, so no CUDA call is made."""
+    from compat_types import (LlamaServerConfig, LlamaServerStats, MultisequenceConfig, MultisequenceCounters, TensorView)
+    lib = native.lib()
+    lib.cf_multisequence_create.restype = C.c_void_p
+    lib.cf_multisequence_last_error.restype = C.c_char_p
+    lib.cf_sequence_speculation_begin.restype = C.c_uint64
+    lib.cf_llama_server_runtime_create.restype = C.c_void_p
+    lib.cf_llama_server_last_error.restype = C.c_char_p
+    assert lib.cf_multisequence_create(None) is None
+    assert lib.cf_multisequence_create(C.byref(MultisequenceConfig(2, 2, 8, 64, 16, 3, 0, 1))) is None   # 8 != 2 * 3
+    c = C.c_void_p(lib.cf_multisequence_create(C.byref(MultisequenceConfig(2, 2, 8, 64, 16, 4, 0, 1))))
+    assert c.value
+    i64 = C.c_int64
+    assert lib.cf_sequence_create(c, i64(1)) == 0
+    assert lib.cf_sequence_create(c, i64(1)) == -1 and b"already exists" in lib.cf_multisequence_last_error(c)
+    assert lib.cf_sequence_copy_async(c, i64(1), i64(1), 0, 10, None) == -1          # onto itself
+    assert lib.cf_sequence_copy_async(c, i64(1), i64(2), 5, 1, None) == -1           # end < begin
+    assert lib.cf_sequence_copy_async(c, i64(9), i64(2), 0, 10, None) == -1          # unknown source
+    assert lib.cf_sequence_copy_async(c, i64(1), i64(2), 0, 1 << 30, None) == 0
+    assert lib.cf_sequence_copy_async(c, i64(1), i64(3), 4, 1 << 30, None) == -1     # must start at token 0
+    spec = lib.cf_sequence_speculation_begin(c, i64(2))
+    assert spec != 0 and lib.cf_sequence_speculation_begin(c, i64(2)) == 0           # one at a time
+    assert lib.cf_sequence_speculation_commit(c, i64(2), C.c_uint64(spec + 5), 0, None) == -1
+    assert lib.cf_sequence_speculation_commit(c, i64(2), C.c_uint64(spec), 3, None) == -1    # nothing provisional
+    assert lib.cf_sequence_speculation_rollback(c, i64(2), C.c_uint64(spec), None) == 0
+    spec = lib.cf_sequence_speculation_begin(c, i64(2))
+    assert lib.cf_sequence_speculation_commit(c, i64(2), C.c_uint64(spec), 0, None) == 0
+    view = TensorView()
+    assert lib.cf_sequence_append_async(c, i64(1), 0, 0, None, C.byref(view), None) == -1
+    assert lib.cf_sequence_append_async(c, i64(1), 7, 0, C.byref(view), C.byref(view), None) == -1   # layer out of range
+    assert lib.cf_multisequence_attention_async(c, None, 1, None) == -1
+    assert lib.cf_sequence_shift_async(c, i64(1), 0, 0, 0, None) == 0                # a shift that moves nothing
+    assert lib.cf_sequence_remove_async(c, i64(2), i64(5), i64(1), None) == -1
+    assert lib.cf_sequence_remove_async(c, i64(2), i64(-1), i64(-1), None) == 0
+    assert lib.cf_sequence_remove_async(c, i64(2), i64(-1), i64(-1), None) == -1
+    assert lib.cf_multisequence_reclaim_async(c, None) == 0 and lib.cf_multisequence_audit(c) == 0
+    k = MultisequenceCounters()
+    assert lib.cf_multisequence_get_counters(c, C.byref(k)) == 0
+    assert (k.sequences_created, k.sequences_copied, k.sequences_removed, k.active_sequences, k.active_sequences_peak) == (1, 1, 1, 1, 2)
+    assert (k.speculative_transactions_started, k.speculative_transactions_committed, k.speculative_transactions_rolled_back) == (2, 1, 1)
+    assert k.unsupported_operations == 1 and k.invariant_audits > 0 and k.invariant_failures == 0 and k.dense_fallback_launches == 0
+    assert lib.cf_multisequence_last_error(None) == b"null multisequence cache"
+    lib.cf_multisequence_destroy(c, None)
+
+    cfg = LlamaServerConfig(2, 8, 2, 64, 16, 64, 4096, 4, 0, 1, None, b"76f46ad2", None)
+    assert lib.cf_llama_server_runtime_create(C.byref(cfg)) is None                   # model_sha256 is required
+    cfg.model_sha256 = b"0" * 64
+    s = C.c_void_p(lib.cf_llama_server_runtime_create(C.byref(cfg)))
+    assert s.value
+    assert lib.cf_llama_server_slot_create(s, i64(11)) == 0 and lib.cf_llama_server_slot_create(s, i64(11)) == -1
+    assert lib.cf_llama_server_slot_create(s, i64(12)) == 0
+    assert lib.cf_llama_server_sequence_copy_async(s, i64(11), i64(13), 0, 1 << 30, None) == 0
+    assert lib.cf_llama_server_cancel_async(s, i64(12), None) == 0
+    assert lib.cf_llama_server_slot_reset_async(s, i64(12), None) == 0
+    assert lib.cf_llama_server_slot_reset_async(s, i64(12), None) == -1
+    assert lib.cf_llama_server_execute_batch_async(s, None, None) == -1
+    assert lib.cf_llama_server_shutdown_async(s, None) == 0
+    assert lib.cf_llama_server_slot_create(s, i64(14)) == -1 and b"shutting down" in lib.cf_llama_server_last_error(s)
+    st = LlamaServerStats()
+    assert lib.cf_llama_server_get_stats(s, C.byref(st)) == 0
+    assert (st.http_requests, st.slot_reuses, st.cancelled_requests, st.shutdown_audits, st.shutdown_failures) == (2, 1, 1, 1, 0)
+    lib.cf_llama_server_runtime_destroy(s, None)
