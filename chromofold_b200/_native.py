@@ -108,6 +108,12 @@ EXPORTS = {
         "cf_llama_server_append_layer_async", "cf_llama_server_execute_batch_async", "cf_llama_server_shutdown_async",
         "cf_llama_server_get_stats", "cf_llama_server_last_error",
     ],
+    "compat_multigpu.h": [
+        "cf_multigpu_cuda_create", "cf_multigpu_cuda_destroy", "cf_multigpu_cuda_validate_topology",
+        "cf_multigpu_cuda_execute_async", "cf_multigpu_cuda_migrate_sequence_async",
+        "cf_multigpu_cuda_inject_device_failure", "cf_multigpu_cuda_shutdown", "cf_multigpu_cuda_get_counters",
+        "cf_multigpu_cuda_last_error",
+    ],
     "compat_production.h": [
         "cf_attention_runtime_create", "cf_attention_runtime_destroy", "cf_attention_execute_async",
         "cf_attention_compare_async", "cf_attention_invalidate_graphs", "cf_attention_get_counters",

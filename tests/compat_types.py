@@ -194,3 +194,33 @@ class LlamaServerStats(C.Structure):
     _fields_ = [(n, _u64) for n in ("http_requests", "interleaved_batches", "slot_reuses", "cancelled_requests",
                                     "context_shifts", "speculative_rollbacks", "dense_nodes_scheduled", "shutdown_audits",
                                     "shutdown_failures")]
+
+
+class MultigpuDeviceConfig(C.Structure):
+    _fields_ = [("device_ordinal", C.c_int32), ("memory_budget_bytes", _u64), ("peer_group", _u32)]
+
+
+class MultigpuRuntimeConfig(C.Structure):
+    _fields_ = [("devices", _vp)] + [(n, _u32) for n in ("device_count", "layer_count", "tensor_parallel_size",
+                                                          "allow_host_staging", "require_peer_access", "collective")]
+
+
+class MultigpuPageView(C.Structure):
+    _fields_ = [("key_payload", _vp), ("value_payload", _vp), ("key_scales", _vp), ("value_scales", _vp),
+                ("key_payload_bytes", _u64), ("value_payload_bytes", _u64)] + [
+        (n, _u32) for n in ("key_codec", "value_codec", "token_count", "kv_head_count", "head_dim", "block_size")] + [
+        ("source_device", C.c_int32), ("generation", _u64)]
+
+
+class MultigpuShard(C.Structure):
+    _fields_ = [("sequence_id", _u64), ("layer", _u32), ("query_head_begin", _u32), ("query_head_count", _u32),
+                ("execution_device", C.c_int32), ("query", _vp), ("output", _vp), ("query_type", _u32),
+                ("output_type", _u32), ("head_dim", _u32), ("page_count", _u32), ("pages", _vp)]
+
+
+class MultigpuCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in (
+        "batches_submitted", "shards_dispatched", "p2p_copy_calls", "p2p_bytes", "host_staged_copy_calls",
+        "host_staged_bytes", "collective_calls", "collective_bytes", "mixed_codec_pages_consumed", "remote_pages_loaded",
+        "migrations_completed", "device_failures_detected", "fail_closed_rejections", "cross_device_contamination",
+        "dense_fallback_launches", "cuda_errors", "transfer_errors", "page_refs_at_shutdown", "snapshot_refs_at_shutdown")]

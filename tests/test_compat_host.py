@@ -318,3 +318,49 @@ def test_multisequence_cache_and_server_contracts_without_a_gpu(native):
     assert lib.cf_llama_server_get_stats(s, C.byref(st)) == 0
     assert (st.http_requests, st.slot_reuses, st.cancelled_requests, st.shutdown_audits, st.shutdown_failures) == (2, 1, 1, 1, 0)
     lib.cf_llama_server_runtime_destroy(s, None)
+
+
+def test_multigpu_runtime_contract_without_a_gpu(native):
+    """The cases of the reference's tests/m15_multigpu_cuda_contract.cpp (two-device config, injected failure) plus
+    the admission rules of src/cuda/multigpu_cuda_runtime.cu:34-55,103-134. Local pages only, so no CUDA call is made."""
+    from compat_types import MultigpuCounters, MultigpuDeviceConfig, MultigpuPageView, MultigpuRuntimeConfig, MultigpuShard
+    lib = native.lib()
+    lib.cf_multigpu_cuda_create.restype = C.c_void_p
+    lib.cf_multigpu_cuda_last_error.restype = C.c_char_p
+    devs = (MultigpuDeviceConfig * 2)(MultigpuDeviceConfig(0, 1 << 30, 0), MultigpuDeviceConfig(1, 1 << 30, 0))
+    mk = lambda **kw: MultigpuRuntimeConfig(**{**dict(devices=C.cast(devs, C.c_void_p), device_count=2, layer_count=4,
+                                                      tensor_parallel_size=2, allow_host_staging=0, require_peer_access=1,
+                                                      collective=0), **kw})
+    assert lib.cf_multigpu_cuda_create(None) is None
+    assert lib.cf_multigpu_cuda_create(C.byref(mk(device_count=1))) is None
+    assert lib.cf_multigpu_cuda_create(C.byref(mk(tensor_parallel_size=3))) is None
+    same = (MultigpuDeviceConfig * 2)(MultigpuDeviceConfig(0, 1 << 30, 0), MultigpuDeviceConfig(0, 1 << 30, 0))
+    assert lib.cf_multigpu_cuda_create(C.byref(mk(devices=C.cast(same, C.c_void_p)))) is None   # ordinals must be unique
+    r = C.c_void_p(lib.cf_multigpu_cuda_create(C.byref(mk(collective=1))))
+    assert r.value
+    page = MultigpuPageView(0x1000, 0x2000, 0x3000, 0x4000, 512, 512, 4, 4, 16, 2, 64, 32, 0, 1)
+    shard = MultigpuShard(7, 0, 0, 4, 0, 0x5000, 0x6000, 1, 3, 64, 1, C.cast(C.pointer(page), C.c_void_p))
+    assert lib.cf_multigpu_cuda_execute_async(r, C.byref(shard), 1, None) == 0
+    bad = MultigpuShard.from_buffer_copy(shard)
+    bad.layer = 9
+    assert lib.cf_multigpu_cuda_execute_async(r, C.byref(bad), 1, None) == -1
+    odd = MultigpuPageView.from_buffer_copy(page)
+    odd.key_codec = 3
+    bad = MultigpuShard.from_buffer_copy(shard)
+    bad.pages = C.cast(C.pointer(odd), C.c_void_p)
+    assert lib.cf_multigpu_cuda_execute_async(r, C.byref(bad), 1, None) == -1
+    assert b"page descriptor" in lib.cf_multigpu_cuda_last_error(r)
+    assert lib.cf_multigpu_cuda_migrate_sequence_async(r, C.c_uint64(7), 0, 1, C.byref(page), 1, None) == 0
+    assert lib.cf_multigpu_cuda_migrate_sequence_async(r, C.c_uint64(7), 1, 0, C.byref(page), 1, None) == -1   # not the owner
+    assert lib.cf_multigpu_cuda_inject_device_failure(r, 5) == -1 and lib.cf_multigpu_cuda_inject_device_failure(r, 0) == 0
+    assert lib.cf_multigpu_cuda_execute_async(r, C.byref(shard), 1, None) == -1
+    assert b"unknown or failed" in lib.cf_multigpu_cuda_last_error(r)
+    assert lib.cf_multigpu_cuda_shutdown(r) == 0
+    other = MultigpuShard.from_buffer_copy(shard)
+    other.execution_device = 1
+    assert lib.cf_multigpu_cuda_execute_async(r, C.byref(other), 1, None) == -1
+    k = MultigpuCounters()
+    assert lib.cf_multigpu_cuda_get_counters(r, C.byref(k)) == 0
+    assert (k.batches_submitted, k.shards_dispatched, k.collective_calls, k.migrations_completed) == (1, 1, 1, 1)
+    assert (k.device_failures_detected, k.fail_closed_rejections, k.remote_pages_loaded, k.dense_fallback_launches) == (1, 5, 0, 0)
+    lib.cf_multigpu_cuda_destroy(r)
