@@ -108,6 +108,8 @@ EXPORTS = {
         "cf_llama_server_append_layer_async", "cf_llama_server_execute_batch_async", "cf_llama_server_shutdown_async",
         "cf_llama_server_get_stats", "cf_llama_server_last_error",
     ],
+    "page_transfer.h": ["cf_b200_pages_pack_async", "cf_b200_pages_unpack_async", "cf_b200_fnv1a",
+                        "cf_b200_record_checksum"],
     "compat_multigpu.h": [
         "cf_multigpu_cuda_create", "cf_multigpu_cuda_destroy", "cf_multigpu_cuda_validate_topology",
         "cf_multigpu_cuda_execute_async", "cf_multigpu_cuda_migrate_sequence_async",
@@ -126,6 +128,16 @@ EXPORTS = {
         "cf_llama_kv_last_error",
     ],
 }
+
+class TransferHeader(C.Structure):
+    _fields_ = [("magic", _u64), ("version", _u32), ("format_version", _u32), ("kv_head_count", _u32), ("head_dim", _u32),
+                ("page_tokens", _u32), ("block_size", _u32), ("codebook_id", _u32), ("page_count", _u32),
+                ("payload_bytes", _u64), ("manifest_checksum", _u64), ("reserved", _u64)]
+
+
+FORMAT_VERSION = 1   # CF_B200_FORMAT_VERSION of include/chromofold_b200/sealed_page_format.h
+TRANSFER_MAGIC = 0x3147504643
+DEVSTAT_CHECKSUM = 0x40
 
 _lib = None
 

@@ -199,6 +199,72 @@ class SealedKvLayer:
         self.h_sealed[slot] += added
         self.sealed_tokens[slot] += added
 
+    # -- transfer images (warm-start file / hand-over to another GPU) -------------------------------------
+    def export_pages(self, slot):
+        """The sealed pages of `slot` as one transfer image (bytes): header, manifest, packed records
+        (include/chromofold_b200/page_transfer.h). Packed and checksummed on the GPU."""
+        n = int((self.h_sealed[slot] + self.page_tokens - 1) // self.page_tokens)
+        ids = torch.as_tensor(self.h_page_table[slot, :n].astype(np.int32), device=self.device)
+        manifest = torch.zeros(n * self.kv_heads * 16, dtype=torch.uint8, device=self.device)
+        capacity = n * self.kv_heads * (16 + 2 * ((self.head_dim * self.page_tokens + 15) // 16 * 16))
+        payload = torch.zeros(capacity + 16, dtype=torch.uint8, device=self.device)
+        cursor = torch.zeros(1, dtype=torch.int64, device=self.device)
+        N.check("pages_pack", self.lib.cf_b200_pages_pack_async(
+            C.c_void_p(self.arena.data_ptr()), C.c_void_p(self.page_dir.data_ptr()), C.c_uint32(self.kv_heads),
+            C.c_void_p(ids.data_ptr()), C.c_uint32(n), C.c_void_p(manifest.data_ptr()), C.c_void_p(payload.data_ptr()),
+            C.c_uint64(capacity), C.c_void_p(cursor.data_ptr()), C.c_void_p(self.status.data_ptr()), _stream_ptr()))
+        used = int(cursor.item()) * 16
+        man = manifest.cpu().numpy().tobytes()
+        header = N.TransferHeader()
+        header.magic, header.version, header.format_version = N.TRANSFER_MAGIC, 1, N.FORMAT_VERSION
+        header.kv_head_count, header.head_dim, header.page_tokens = self.kv_heads, self.head_dim, self.page_tokens
+        header.block_size, header.codebook_id, header.page_count = self.block_size, self.codebook_id, n
+        header.payload_bytes = used
+        self.lib.cf_b200_fnv1a.restype = C.c_uint64
+        header.manifest_checksum = self.lib.cf_b200_fnv1a(man, C.c_uint64(len(man)))
+        tokens = np.minimum(self.page_tokens, self.h_sealed[slot] - np.arange(n) * self.page_tokens).astype(np.uint32)
+        return bytes(header) + man + payload[:used].cpu().numpy().tobytes() + tokens.tobytes()
+
+    def import_pages(self, slot, image):
+        """Append the pages of a transfer image to `slot`. The image must match this layer's geometry and codebook
+        id; every record is verified against its checksum on the GPU (a bad one is not published and raises
+        CF_B200_DEVSTAT_CHECKSUM in the status word). Returns the number of pages."""
+        header = N.TransferHeader.from_buffer_copy(image[:C.sizeof(N.TransferHeader)])
+        if header.magic != N.TRANSFER_MAGIC or header.version != 1 or header.format_version != N.FORMAT_VERSION:
+            raise ValueError("not a transfer image of this format version")
+        if (header.kv_head_count, header.head_dim, header.page_tokens, header.block_size, header.codebook_id) != (
+                self.kv_heads, self.head_dim, self.page_tokens, self.block_size, self.codebook_id):
+            raise ValueError("transfer image geometry or codebook id does not match this layer")
+        n, hs = header.page_count, C.sizeof(N.TransferHeader)
+        man = image[hs:hs + 16 * n * self.kv_heads]
+        self.lib.cf_b200_fnv1a.restype = C.c_uint64
+        if self.lib.cf_b200_fnv1a(man, C.c_uint64(len(man))) != header.manifest_checksum:
+            raise ValueError("transfer image manifest is corrupt")
+        body = image[hs + len(man):hs + len(man) + header.payload_bytes]
+        tokens = np.frombuffer(image[hs + len(man) + header.payload_bytes:], np.uint32)
+        if len(body) != header.payload_bytes or tokens.size != n or self.h_sealed[slot] % self.page_tokens:
+            raise ValueError("transfer image is truncated, or the sequence ends in a short page")
+        first = int(self.h_sealed[slot] // self.page_tokens)
+        if first + n > self.max_pages_per_sequence or self.next_page_id + n > self.max_pages:
+            raise ValueError("page table or page directory is full")
+        ids = np.arange(self.next_page_id, self.next_page_id + n, dtype=np.int32)
+        self.next_page_id += n
+        d_ids = torch.as_tensor(ids, device=self.device)
+        d_man = torch.frombuffer(bytearray(man), dtype=torch.uint8).to(self.device)
+        d_body = torch.zeros(len(body) + 16, dtype=torch.uint8, device=self.device)
+        d_body[:len(body)] = torch.frombuffer(bytearray(body), dtype=torch.uint8).to(self.device)
+        N.check("pages_unpack", self.lib.cf_b200_pages_unpack_async(
+            C.c_void_p(d_man.data_ptr()), C.c_void_p(d_body.data_ptr()), C.c_uint64(len(body)), C.c_uint32(self.kv_heads),
+            C.c_void_p(d_ids.data_ptr()), C.c_uint32(n), C.c_void_p(self.arena.data_ptr()), C.c_uint64(self.arena_units),
+            C.c_void_p(self.cursor.data_ptr()), C.c_void_p(self.page_dir.data_ptr()), C.c_void_p(self.status.data_ptr()),
+            _stream_ptr()))
+        torch.cuda.current_stream().synchronize()   # the staging tensors above go away with this frame
+        self.h_page_table[slot, first:first + n] = ids
+        self.page_table[slot, first:first + n] = d_ids
+        self.h_sealed[slot] += int(tokens.sum())
+        self.sealed_tokens[slot] += int(tokens.sum())
+        return n
+
     # -- attention -----------------------------------------------------------------------------------
     def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
                   kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL, shared_prefix_pages=0,
