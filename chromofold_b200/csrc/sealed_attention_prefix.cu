@@ -29,10 +29,7 @@ namespace {
 
 using namespace lanes;
 
-#ifndef CFB_PV_IN_FLIGHT
-#define CFB_PV_IN_FLIGHT 4
-#endif
-constexpr int kPvInFlight = CFB_PV_IN_FLIGHT;   // independent accumulators between an mma and the next one on the same accumulator
+constexpr int kPvInFlight = 4;   // independent accumulators between an mma and the next one on the same accumulator
 constexpr int kPWarps = 8;
 constexpr int kPThreads = kPWarps * 32;
 constexpr uint32_t kTileBytes = 4096;                       // K int8 [16][128] + V int8 [128][16]

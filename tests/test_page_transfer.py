@@ -49,7 +49,7 @@ def test_pages_travel_between_stores_and_tampering_is_caught(native, oracle):
     assert int(man["len"].sum()) * 16 == header.payload_bytes
 
     # a second store with the same codebooks (same histogram -> same tables)
-    dst, _ = build_sealed_layer(np.array([0, 32]), coder="rans", seed=96)
+    dst, _ = build_sealed_layer(np.array([0, 32]), coder="rans", seed=96, extra_pages_per_sequence=70, reserve_pages=80)
     dst.k_tables.copy_(src.k_tables)
     dst.v_tables.copy_(src.v_tables)
     dst.codebook_id = src.codebook_id
@@ -65,7 +65,7 @@ def test_pages_travel_between_stores_and_tampering_is_caught(native, oracle):
     # one flipped payload bit: that record is refused, the status word says so
     bad = bytearray(image)
     bad[64 + man.nbytes + 16 * int(man[5]["off"]) + 40] ^= 0x10
-    dst2, _ = build_sealed_layer(np.array([0, 32]), coder="rans", seed=96)
+    dst2, _ = build_sealed_layer(np.array([0, 32]), coder="rans", seed=96, extra_pages_per_sequence=70, reserve_pages=80)
     dst2.k_tables.copy_(src.k_tables)
     dst2.v_tables.copy_(src.v_tables)
     dst2.import_pages(0, bytes(bad))
@@ -75,6 +75,6 @@ def test_pages_travel_between_stores_and_tampering_is_caught(native, oracle):
     bad[64 + 3] ^= 1
     with pytest.raises(ValueError):
         dst2.import_pages(1, bytes(bad))
-    other, _ = build_sealed_layer(np.array([0]), kv_heads=4, query_heads=16, coder="rans", seed=98)
+    other, _ = build_sealed_layer(np.array([16]), kv_heads=4, query_heads=16, coder="rans", seed=98, extra_pages_per_sequence=70, reserve_pages=80)
     with pytest.raises(ValueError):
         other.import_pages(0, image)
