@@ -16,7 +16,7 @@ namespace {
 constexpr int kSealThreads = 128;
 
 struct SealSmem {
-    uint32_t off_ksym, off_vsym, off_scratch, off_part, off_blk, part_capacity, slot_bytes, total;
+    uint32_t off_ksym, off_vsym, off_scratch, off_part, off_blk, off_enc, part_capacity, slot_bytes, total;
 };
 
 __host__ __device__ inline SealSmem seal_smem(uint32_t symbols, uint32_t nblocks, uint32_t block_size) {
@@ -26,9 +26,10 @@ __host__ __device__ inline SealSmem seal_smem(uint32_t symbols, uint32_t nblocks
     s.off_ksym = 0;
     s.off_vsym = s.off_ksym + align_up_u32(symbols, 16u);
     s.off_scratch = s.off_vsym + align_up_u32(symbols, 16u);
-    s.off_part = s.off_scratch + nblocks * s.slot_bytes;
+    s.off_part = s.off_scratch + 2u * nblocks * s.slot_bytes;   // one scratch area per stream
     s.off_blk = s.off_part + 2u * s.part_capacity;
-    s.total = s.off_blk + 3u * nblocks * 4u + 64u;
+    s.off_enc = align_up_u32(s.off_blk + 6u * nblocks * 4u, 8u);
+    s.total = s.off_enc + 2u * 256u * 8u + 64u;
     return s;
 }
 
@@ -89,20 +90,30 @@ __device__ float tile_absmax(const void *base, uint32_t type, uint64_t tile, uin
     return r;
 }
 
+// Per-symbol encoder entry in shared memory: x = freq | cum << 12 | shift << 24, y = ceil(2^(31 + shift) / freq) with
+// shift = ceil(log2 freq). Then floor(v / freq) = (v * y) >> (31 + shift) exactly for every v < 2^31, so the encoder
+// needs no division.
+__device__ __forceinline__ uint2 encoder_entry(uint32_t freq, uint32_t cum) {
+    const uint32_t shift = freq > 1u ? 32u - static_cast<uint32_t>(__clz(freq - 1u)) : 0u;
+    const unsigned long long rcp = ((1ull << (31u + shift)) + freq - 1u) / freq;
+    return make_uint2(freq | (cum << 12) | (shift << 24), static_cast<uint32_t>(rcp));
+}
+
 // Inverse of rans_decode_block: symbols pushed last to first from state L; bytes leave the low end of the state
 // and are written backwards so that they read forwards. Returns the byte count; *state0 gets the final state.
-__device__ uint32_t rans_encode_block(const uint8_t *sym, int count, const cf_b200_codebook_tables *t,
-                                      uint8_t *slot_end, uint32_t *state0) {
+__device__ uint32_t rans_encode_block(const uint8_t *sym, int count, const uint2 *enc, uint8_t *slot_end, uint32_t *state0) {
     uint32_t x = kRansL;
     uint8_t *p = slot_end;
     for (int j = count - 1; j >= 0; --j) {
-        const uint32_t f = t->rans_freq[sym[j]];
+        const uint2 e = enc[sym[j]];
+        const uint32_t f = e.x & 0xfffu, cum = (e.x >> 12) & 0xfffu, shift = e.x >> 24;
         const uint32_t x_max = f << 19;  // ((L >> 12) << 8) * f
         while (x >= x_max) {
             *--p = static_cast<uint8_t>(x & 0xffu);
             x >>= 8;
         }
-        x = ((x / f) << CF_B200_RANS_PROB_BITS) + (x % f) + t->rans_cum[sym[j]];
+        const uint32_t q = static_cast<uint32_t>((static_cast<unsigned long long>(x) * e.y) >> (31u + shift));
+        x = (q << CF_B200_RANS_PROB_BITS) + (x - q * f) + cum;
     }
     *state0 = x;
     return static_cast<uint32_t>(slot_end - p);
@@ -119,86 +130,93 @@ __device__ __forceinline__ void put_bits(uint32_t *words, uint32_t bit, uint32_t
     }
 }
 
-// Encode one stream into `part` (shared memory, zeroed by the caller). Whole-CTA call. Returns the part size in
-// bytes (a multiple of 16); *coder_used is the coder actually stored.
-__device__ uint32_t encode_stream(const SealParams &p, const SealSmem &lay, const uint8_t *sym,
-                                  const cf_b200_codebook_tables *tables, uint8_t *scratch, uint8_t *part,
-                                  uint32_t *blk_len, uint32_t *blk_off, uint32_t *blk_state, uint32_t *coder_used,
-                                  volatile uint32_t *s_flag) {
+// Encode the K stream (which = 0) and the V stream (which = 1) into their parts (shared memory, zeroed by the caller),
+// both at once: block b of stream w is the job of thread w * nblocks + b. Whole-CTA call. bytes_out[w] gets the part
+// size (a multiple of 16), coder_out[w] the coder actually stored.
+struct StreamJob {
+    const uint8_t *sym;
+    const cf_b200_codebook_tables *tables;
+    const uint2 *enc;
+    uint8_t *part;
+};
+
+__device__ void encode_streams(const SealParams &p, const SealSmem &lay, const StreamJob (&job)[2], uint8_t *scratch,
+                               uint32_t *blk_len, uint32_t *blk_off, uint32_t *blk_state, volatile uint32_t *s_flag,
+                               uint32_t (&coder_out)[2], uint32_t (&bytes_out)[2]) {
     const uint32_t tid = threadIdx.x, nb = p.nblocks, n = p.symbols;
     const uint32_t fixed_bytes = align_up_u32(n, 16u);
-    uint32_t coder = p.coder;
-    uint32_t part_bytes = fixed_bytes;
-    if (coder != CF_B200_CODER_FIXED8) {
-        for (uint32_t b = tid; b < nb; b += kSealThreads) {  // pass 1: coded length of every block
-            const uint32_t base = b * p.block_size;
+    uint32_t coder[2] = {p.coder, p.coder};
+    bytes_out[0] = bytes_out[1] = fixed_bytes;
+    if (p.coder != CF_B200_CODER_FIXED8) {
+        for (uint32_t j = tid; j < 2u * nb; j += kSealThreads) {  // pass 1: coded length of every block
+            const uint32_t w = j / nb, b = j % nb, base = b * p.block_size;
             const int count = static_cast<int>(min(p.block_size, n - base));
-            if (coder == CF_B200_CODER_RANS) {
+            if (p.coder == CF_B200_CODER_RANS) {
                 uint32_t st;
-                blk_len[b] = rans_encode_block(sym + base, count, tables, scratch + (b + 1) * lay.slot_bytes, &st);
-                blk_state[b] = st;
+                blk_len[j] = rans_encode_block(job[w].sym + base, count, job[w].enc, scratch + (j + 1) * lay.slot_bytes, &st);
+                blk_state[j] = st;
             } else {
                 uint32_t bits = 0;
-                for (int j = 0; j < count; ++j) bits += tables->huff_code[sym[base + j]] >> 16;
-                blk_len[b] = bits;
+                for (int i = 0; i < count; ++i) bits += job[w].tables->huff_code[job[w].sym[base + i]] >> 16;
+                blk_len[j] = bits;
             }
         }
         __syncthreads();
-        if (tid == 0) {
+        if (tid < 2) {
             uint32_t run = 0;
             for (uint32_t b = 0; b < nb; ++b) {
-                blk_off[b] = run;
-                run += blk_len[b];
+                blk_off[tid * nb + b] = run;
+                run += blk_len[tid * nb + b];
             }
-            const uint32_t bytes = coder == CF_B200_CODER_RANS
+            const uint32_t bytes = p.coder == CF_B200_CODER_RANS
                                        ? align_up_u32(align_up_u32(6u * nb, 4u) + run, 16u)
                                        : align_up_u32(align_up_u32(2u * nb, 4u) + 4u * ((run + 31u) / 32u), 16u);
-            s_flag[0] = bytes > fixed_bytes ? 1u : 0u;  // would not shrink: store fixed-width instead
-            s_flag[1] = bytes;
+            s_flag[2 * tid] = bytes > fixed_bytes ? 1u : 0u;  // would not shrink: store fixed-width instead
+            s_flag[2 * tid + 1] = bytes;
         }
         __syncthreads();
-        if (s_flag[0]) coder = CF_B200_CODER_FIXED8;
-        else part_bytes = s_flag[1];
-    }
-    if (coder == CF_B200_CODER_RANS) {
-        uint32_t *state_tbl = reinterpret_cast<uint32_t *>(part);
-        uint16_t *off_tbl = reinterpret_cast<uint16_t *>(part + 4u * nb);
-        uint8_t *payload = part + align_up_u32(6u * nb, 4u);
-        for (uint32_t b = tid; b < nb; b += kSealThreads) {
-            state_tbl[b] = blk_state[b];
-            off_tbl[b] = static_cast<uint16_t>(blk_off[b]);
-            const uint8_t *src = scratch + (b + 1) * lay.slot_bytes - blk_len[b];
-            uint8_t *dst = payload + blk_off[b];
-            for (uint32_t i = 0; i < blk_len[b]; ++i) dst[i] = src[i];
+        for (int w = 0; w < 2; ++w) {
+            if (s_flag[2 * w]) coder[w] = CF_B200_CODER_FIXED8;
+            else bytes_out[w] = s_flag[2 * w + 1];
         }
-    } else if (coder == CF_B200_CODER_HUFFMAN) {
-        uint16_t *off_tbl = reinterpret_cast<uint16_t *>(part);
-        uint32_t *words = reinterpret_cast<uint32_t *>(part + align_up_u32(2u * nb, 4u));
-        for (uint32_t b = tid; b < nb; b += kSealThreads) {
+    }
+    for (uint32_t j = tid; j < 2u * nb; j += kSealThreads) {   // pass 2: tables and payload of the coded streams
+        const uint32_t w = j / nb, b = j % nb;
+        uint8_t *part = job[w].part;
+        if (coder[w] == CF_B200_CODER_RANS) {
+            reinterpret_cast<uint32_t *>(part)[b] = blk_state[j];
+            reinterpret_cast<uint16_t *>(part + 4u * nb)[b] = static_cast<uint16_t>(blk_off[j]);
+            const uint8_t *src = scratch + (j + 1) * lay.slot_bytes - blk_len[j];
+            uint8_t *dst = part + align_up_u32(6u * nb, 4u) + blk_off[j];
+            for (uint32_t i = 0; i < blk_len[j]; ++i) dst[i] = src[i];
+        } else if (coder[w] == CF_B200_CODER_HUFFMAN) {
+            uint32_t *words = reinterpret_cast<uint32_t *>(part + align_up_u32(2u * nb, 4u));
             const uint32_t base = b * p.block_size;
             const int count = static_cast<int>(min(p.block_size, n - base));
-            uint32_t bit = blk_off[b];
-            off_tbl[b] = static_cast<uint16_t>(bit);
-            for (int j = 0; j < count; ++j) {
-                const uint32_t cl = tables->huff_code[sym[base + j]];
+            uint32_t bit = blk_off[j];
+            reinterpret_cast<uint16_t *>(part)[b] = static_cast<uint16_t>(bit);
+            for (int i = 0; i < count; ++i) {
+                const uint32_t cl = job[w].tables->huff_code[job[w].sym[base + i]];
                 put_bits(words, bit, cl & 0xffffu, cl >> 16);
                 bit += cl >> 16;
             }
         }
-    } else {
-        uint32_t *words = reinterpret_cast<uint32_t *>(part);
-        for (uint32_t w = tid; w < (n + 3u) / 4u; w += kSealThreads) {
+    }
+    for (int w = 0; w < 2; ++w) {
+        if (coder[w] != CF_B200_CODER_FIXED8) continue;
+        uint32_t *words = reinterpret_cast<uint32_t *>(job[w].part);
+        for (uint32_t i = tid; i < (n + 3u) / 4u; i += kSealThreads) {
             uint32_t v = 0;
             for (uint32_t k = 0; k < 4; ++k) {
-                const uint32_t i = 4u * w + k;
-                if (i < n) v |= static_cast<uint32_t>(sym[i]) << (24u - 8u * k);
+                const uint32_t at = 4u * i + k;
+                if (at < n) v |= static_cast<uint32_t>(job[w].sym[at]) << (24u - 8u * k);
             }
-            words[w] = v;
+            words[i] = v;
         }
     }
     __syncthreads();
-    *coder_used = coder;
-    return part_bytes;
+    coder_out[0] = coder[0];
+    coder_out[1] = coder[1];
 }
 
 __device__ __forceinline__ void quantise_tiles(const SealParams &p, uint64_t tile, uint32_t rows, float k_scale,
@@ -219,7 +237,7 @@ __device__ __forceinline__ void quantise_tiles(const SealParams &p, uint64_t til
 __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ float red[8];
-    __shared__ uint32_t s_flag[2];
+    __shared__ uint32_t s_flag[4];
     __shared__ unsigned long long s_offset;
     const SealSmem lay = seal_smem(p.symbols, p.nblocks, p.block_size);
     uint8_t *ksym = smem + lay.off_ksym;
@@ -227,9 +245,10 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     uint8_t *scratch = smem + lay.off_scratch;
     uint8_t *k_part = smem + lay.off_part;
     uint8_t *v_part = k_part + lay.part_capacity;
-    uint32_t *blk_len = reinterpret_cast<uint32_t *>(smem + lay.off_blk);
-    uint32_t *blk_off = blk_len + p.nblocks;
-    uint32_t *blk_state = blk_off + p.nblocks;
+    uint32_t *blk_len = reinterpret_cast<uint32_t *>(smem + lay.off_blk);   // [2 streams][nblocks] each
+    uint32_t *blk_off = blk_len + 2u * p.nblocks;
+    uint32_t *blk_state = blk_off + 2u * p.nblocks;
+    uint2 *enc = reinterpret_cast<uint2 *>(smem + lay.off_enc);               // [2 streams][256 symbols]
 
     const uint32_t job = blockIdx.x, tid = threadIdx.x;
     const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
@@ -249,13 +268,17 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     quantise_tiles(p, tile, rows, __half2float(__ushort_as_half(k_bits)), __half2float(__ushort_as_half(v_bits)), ksym,
                    vsym);
     for (uint32_t i = tid; i < 2u * lay.part_capacity / 4u; i += kSealThreads) reinterpret_cast<uint32_t *>(k_part)[i] = 0u;
+    if (p.coder == CF_B200_CODER_RANS)
+        for (uint32_t i = tid; i < 512u; i += kSealThreads) {
+            const cf_b200_codebook_tables *t = i < 256u ? p.k_tables : p.v_tables;
+            enc[i] = encoder_entry(t->rans_freq[i & 255u], t->rans_cum[i & 255u]);
+        }
     __syncthreads();
 
-    uint32_t k_coder, v_coder;
-    const uint32_t k_bytes = encode_stream(p, lay, ksym, p.k_tables, scratch, k_part, blk_len, blk_off, blk_state,
-                                           &k_coder, s_flag);
-    const uint32_t v_bytes = encode_stream(p, lay, vsym, p.v_tables, scratch, v_part, blk_len, blk_off, blk_state,
-                                           &v_coder, s_flag);
+    const StreamJob jobs[2] = {{ksym, p.k_tables, enc, k_part}, {vsym, p.v_tables, enc + 256, v_part}};
+    uint32_t coders[2], bytes[2];
+    encode_streams(p, lay, jobs, scratch, blk_len, blk_off, blk_state, s_flag, coders, bytes);
+    const uint32_t k_coder = coders[0], v_coder = coders[1], k_bytes = bytes[0], v_bytes = bytes[1];
 
     const uint32_t units = 1u + k_bytes / 16u + v_bytes / 16u;
     if (tid == 0) s_offset = atomicAdd(p.cursor, static_cast<unsigned long long>(units));
