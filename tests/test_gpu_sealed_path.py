@@ -238,6 +238,10 @@ def test_lanes_kernel_mixed_coders_and_scales(native, oracle):
         got = layer.attention(torch.from_numpy(q).cuda(), kernel=kernel).cpu().numpy()
         ok, err = attention_close(got, want)
         assert ok, (kernel, err)
+    # the same pages through the shared-prefix kernel (its mixed-coder, all-zero-page and scale handling)
+    got = layer.attention(torch.from_numpy(q).cuda(), kernel=native.KERNEL_LANES, shared_prefix_pages=6).cpu().numpy()
+    ok, err = attention_close(got, want)
+    assert ok, ("prefix", err)
     assert layer.device_status() == 0
 
 
@@ -254,6 +258,10 @@ def test_bad_records_are_reported_not_faulted(native, oracle):
         layer.attention(q, kernel=kernel)
         torch.cuda.synchronize()
         assert layer.device_status() & native.DEVSTAT_BAD_RECORD
+    layer.status.zero_()
+    layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=3)   # the shared-prefix kernel skips it too
+    torch.cuda.synchronize()
+    assert layer.device_status() & native.DEVSTAT_BAD_RECORD
 
 
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 8), (16, 2), (6, 2)])
