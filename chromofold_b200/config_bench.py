@@ -178,9 +178,49 @@ def config5(a, device):
                       "attention_tflops": round(flops / ms_attn / 1e9, 2), "device_status": layer.device_status()}))
 
 
+def transfer(a, device):
+    """Pack / verify-unpack rate of transfer images: one 32768-token sequence (2048 pages x 8 kv heads) moved from one
+    store into another on the same GPU, device buffers only."""
+    import ctypes as C
+    contexts = np.array([32768])
+    src, info = build_sealed_layer(contexts, coder="rans", seed=70, device=device)
+    dst, _ = build_sealed_layer(np.array([0]), coder="rans", seed=71, device=device, extra_pages_per_sequence=2100,
+                                reserve_pages=2100 * (a.steps + a.warmup + 2))
+    n = 2048
+    ids = torch.as_tensor(src.h_page_table[0, :n].astype(np.int32), device=device)
+    manifest = torch.zeros(n * 8 * 16, dtype=torch.uint8, device=device)
+    payload = torch.zeros(info["sealed_bytes"] + 4096, dtype=torch.uint8, device=device)
+    cursor = torch.zeros(1, dtype=torch.int64, device=device)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())
+
+    def pack():
+        cursor.zero_()
+        N.check("pack", src.lib.cf_b200_pages_pack_async(p(src.arena), p(src.page_dir), C.c_uint32(8), p(ids), C.c_uint32(n),
+                                                         p(manifest), p(payload), C.c_uint64(payload.numel()), p(cursor),
+                                                         p(src.status), stream))
+    next_id = [1]
+
+    def unpack():
+        d_ids = torch.arange(next_id[0], next_id[0] + n, dtype=torch.int32, device=device)
+        next_id[0] += n
+        N.check("unpack", dst.lib.cf_b200_pages_unpack_async(p(manifest), p(payload), C.c_uint64(info["sealed_bytes"]),
+                                                             C.c_uint32(8), p(d_ids), C.c_uint32(n), p(dst.arena),
+                                                             C.c_uint64(dst.arena_units), p(dst.cursor), p(dst.page_dir),
+                                                             p(dst.status), stream))
+    ms_pack = _time(pack, a.steps, a.warmup)
+    ms_unpack = _time(unpack, a.steps, a.warmup)
+    gb = info["sealed_bytes"] / 1e9
+    print(json.dumps({"transfer": "2048 pages x 8 kv heads", "sealed_bytes": info["sealed_bytes"],
+                      "pack_ms": round(ms_pack, 4), "pack_gbs_read_plus_write": round(2 * gb / ms_pack * 1e3, 1),
+                      "unpack_ms": round(ms_unpack, 4), "unpack_gbs_read_plus_write": round(2 * gb / ms_unpack * 1e3, 1),
+                      "status": [src.device_status(), dst.device_status()]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=[3, 4, 5])
+    ap.add_argument("--config", type=int, default=0, choices=[0, 3, 4, 5])
+    ap.add_argument("--transfer", action="store_true", help="time the pack / unpack kernels of transfer images instead")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"], help="configurations 4 and 5")
@@ -201,7 +241,9 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
-    if a.config == 3 and a.blocks:
+    if a.transfer:
+        transfer(a, device)
+    elif a.config == 3 and a.blocks:
         config3_blocks(a, device)
     elif a.config == 3:
         config3(a, device)
