@@ -318,6 +318,19 @@ def main():
         ev[s][2].record()
         layer.attention(q, out=out, stages=N.STAGE_COMBINE, **kw)
         ev[s][3].record()
+    # the decode floor: the same launch without its attention (page fetch + entropy decode only)
+    probe_kw = dict(kw, kernel=N.KERNEL_DECODE_PROBE)
+    for _ in range(3):
+        layer.attention(q, out=out, stages=N.STAGE_PLAN | N.STAGE_ATTENTION, **probe_kw)
+    pe = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(a.steps)]
+    for s_ in range(a.steps):   # the plan stage re-arms the kernel's work counter, so it runs before every launch
+        layer.attention(q, out=out, stages=N.STAGE_PLAN, **probe_kw)
+        pe[s_][0].record()
+        layer.attention(q, out=out, stages=N.STAGE_ATTENTION, **probe_kw)
+        pe[s_][1].record()
+    torch.cuda.synchronize()
+    decode_only_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in pe])) if a.kernel != "generic" else None
+    layer.attention(q, out=out, **kw)   # leave a real result in `out`
     torch.cuda.synchronize()
     t1 = time.time()
     stage_ms = [float(np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(a.steps)])) for i in range(3)]
@@ -389,7 +402,7 @@ def main():
                      "traffic": (int(algo_bytes * DRAM_TRAFFIC_RATIO[a.coder]) if a.kernel != "generic" else None),
                      "traffic_source": "ncu dram bytes of the batch-16 capture scaled by algorithmic bytes",
                      "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": stage_ms[1],
-                     "plan_ms": stage_ms[0], "combine_ms": stage_ms[2],
+                     "plan_ms": stage_ms[0], "combine_ms": stage_ms[2], "decode_only_ms": decode_only_ms,
                      "kernel_ms_median": float(np.median(per_launch)), "kernel_ms_p5": float(np.percentile(per_launch, 5)),
                      "kernel_ms_p95": float(np.percentile(per_launch, 95)),
                      "kernel_ms_cv": float(per_launch.std() / per_launch.mean()),

@@ -36,6 +36,7 @@ struct AttentionParams {
     uint32_t min_pages_per_unit;
     uint32_t shared_prefix_pages;   // the caller's hint, already zeroed when the launch cannot use it
     uint32_t sm_count;
+    uint32_t decode_probe;          // measurement: decode every page, fold the symbols into a checksum, no attention
     uint32_t *status;
     // uncompressed comparison pools (dense kernel only)
     const __half *pool_k, *pool_v;

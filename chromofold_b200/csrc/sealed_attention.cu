@@ -475,6 +475,7 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
     p->shared_prefix_pages = 0;   // the launch code sets it when the lanes kernels serve the call
     p->sm_count = 0;
+    p->decode_probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE ? 1u : 0u;
     p->status = d->status;
     p->pool_k = nullptr;
     p->pool_v = nullptr;
@@ -531,7 +532,7 @@ extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_atte
         return CF_ERR_INVALID_ARGUMENT;
     if (d->tail_tokens != nullptr && (d->tail_k == nullptr || d->tail_v == nullptr)) return CF_ERR_INVALID_ARGUMENT;
     if ((d->query_type != CF_B200_F16 && d->query_type != CF_B200_F32) ||
-        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_LANES ||
+        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_DECODE_PROBE ||
         (d->tail_type != 0 && d->tail_type != CF_B200_F16 && d->tail_type != CF_B200_F32))
         return CF_ERR_INVALID_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(d->arena) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->workspace) & 255u) != 0)
@@ -570,11 +571,12 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     AttentionParams p;
     cfb::fill_params(d, &p);
     const bool lanes_ok = cfb::lanes_kernel_supports(p);
-    if (d->kernel == CF_B200_KERNEL_LANES && !lanes_ok) return CF_ERR_UNSUPPORTED;
+    if ((d->kernel == CF_B200_KERNEL_LANES || d->kernel == CF_B200_KERNEL_DECODE_PROBE) && !lanes_ok) return CF_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
+    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || d->kernel == CF_B200_KERNEL_DECODE_PROBE ||
+                           (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
-    if (use_lanes && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
+    if (use_lanes && !p.decode_probe && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static int sm_count = 0;
         if (sm_count == 0) {
             int device = 0;

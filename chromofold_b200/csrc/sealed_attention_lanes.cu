@@ -79,14 +79,19 @@ __device__ __forceinline__ void score_quad(UnitState<NG> &u, const QSrc &qs, int
     }
 }
 
-template <class KLane, class VLane, int NG, class QSrc>
+// kProbe: the symbols are only folded into a checksum (u.vq[0]) — the decode work of the kernel without its attention.
+template <bool kProbe = false, class KLane, class VLane, int NG, class QSrc>
 __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &u, const QSrc &qs) {
     if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
             const uint32_t kq = k.quad();
-            u.vq[q] = v.quad();
-            score_quad(u, qs, q, kq);
+            if constexpr (kProbe) {
+                u.vq[0] ^= kq ^ v.quad();
+            } else {
+                u.vq[q] = v.quad();
+                score_quad(u, qs, q, kq);
+            }
         }
     } else {
         // two independent decoder chains, interleaved symbol by symbol; each window is refilled as rarely as its
@@ -99,8 +104,12 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &
             ke[i & 3] = k.symbol();
             ve[i & 3] = v.symbol();
             if ((i & 3) == 3) {
-                u.vq[i >> 2] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
-                score_quad(u, qs, i >> 2, pack_low_bytes(ke[0], ke[1], ke[2], ke[3]));
+                if constexpr (kProbe) {
+                    u.vq[0] ^= pack_low_bytes(ve[0], ve[1], ve[2], ve[3]) ^ pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+                } else {
+                    u.vq[i >> 2] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
+                    score_quad(u, qs, i >> 2, pack_low_bytes(ke[0], ke[1], ke[2], ke[3]));
+                }
             }
         }
     }
@@ -134,7 +143,7 @@ struct WarpLayout {
 };
 static_assert(WarpLayout<2>::kSmem <= 232448, "the eight-head kernel must fit the 227 KB of one CTA");
 
-template <int NG>
+template <int NG, bool kProbe = false>
 __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
     using L = WarpLayout<NG>;
     using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
@@ -232,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         }
 
         UnitState<NG> u;
+        if constexpr (kProbe) u.vq[0] = 0u;
 #pragma unroll
         for (int n = 0; n < NG; ++n) {
 #pragma unroll
@@ -302,17 +312,17 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                         RansLane k, v;
                         k.open(k_part, lane, k_slot);
                         v.open(v_part, lane, v_slot);
-                        decode_fused(k, v, u, qs);
+                        decode_fused<kProbe>(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
                         HuffLane k, v;
                         k.open(k_part, lane, k_lut);
                         v.open(v_part, lane, v_lut);
-                        decode_fused(k, v, u, qs);
+                        decode_fused<kProbe>(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
                         FixedLane k, v;
                         k.open(k_part, lane);
                         v.open(v_part, lane);
-                        decode_fused(k, v, u, qs);
+                        decode_fused<kProbe>(k, v, u, qs);
                     } else {  // mixed coders (one stream fell back to fixed width): one stream after the other
                         if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_only(k, u, qs); }
                         else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_only(k, u, qs); }
@@ -322,6 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                         else { FixedLane v; v.open(v_part, lane); decode_v_only(v, u); }
                     }
 
+                    if constexpr (!kProbe) {
                     // ---- online softmax for this page (fp32), per group of four heads ----
                     const uint32_t token = (page_begin + i) * 16u + my_token;
                     const bool visible = my_token < token_count && token >= first_token && token < sealed && token <= qpos;
@@ -399,6 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                             }
                         }
                     }
+                    }   // !kProbe
                 }
             }
             entry_cur = entry_next;
@@ -411,6 +423,12 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
             return;
         }
 
+        if constexpr (kProbe) {   // the checksum of everything the unit decoded, so that the work cannot be dropped
+            uint32_t x = u.vq[0];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) x ^= __shfl_xor_sync(0xffffffffu, x, o);
+            if (lane == 0) partial_ptr(p, chunk, out_head_base)[0] = __uint_as_float(x);
+        } else {
         // ---- unit partials ----
 #pragma unroll
         for (int n = 0; n < NG; ++n) {
@@ -445,6 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                 }
             }
         }
+        }   // !kProbe
         __syncwarp();
     }
 }
@@ -470,12 +489,16 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         e = cudaFuncSetAttribute(lanes_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<1>::kSmem));
         if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lanes_attention_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<1>::kSmem));
+        if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(lanes_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    if (p.decode_probe) lanes_attention_kernel<1, true><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
     else lanes_attention_kernel<2><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }

@@ -119,7 +119,11 @@ typedef struct cf_b200_sealed_attention_desc {
 
 #define CF_B200_KERNEL_AUTO 0u     /* lane-per-block tensor-core kernel when the geometry allows, else generic */
 #define CF_B200_KERNEL_GENERIC 1u  /* any geometry within the format limits */
-#define CF_B200_KERNEL_LANES 2u    /* head_dim 128, page_tokens 16, block_size 64, group <= 8; else UNSUPPORTED */
+#define CF_B200_KERNEL_LANES 2u    /* head_dim 128, page_tokens 16, block_size 64, group <= 16; else UNSUPPORTED */
+/* Measurement only: the lanes kernel's page fetch and entropy decode without its attention — every symbol the launch
+ * would decode is folded into a checksum that replaces the partials; the output of the call is meaningless. Use it
+ * with CF_B200_STAGE_PLAN | CF_B200_STAGE_ATTENTION to time the decode floor of a workload. */
+#define CF_B200_KERNEL_DECODE_PROBE 3u
 
 #define CF_B200_DEVSTAT_BAD_RECORD 0x1u      /* version / codebook id / size mismatch in a record header */
 #define CF_B200_DEVSTAT_WAIT_EXPIRED 0x2u    /* a bounded wait on a bulk copy ran out */

@@ -223,3 +223,33 @@ def test_prefill_query_tokens_share_the_sealed_history(native, oracle):
     a = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=early, shared_prefix_pages=128).cpu().numpy()
     b = layer.attention(q, slots=slots, kernel=native.KERNEL_LANES, query_positions=early).cpu().numpy()
     assert np.array_equal(a, b) and layer.device_status() == 0x20
+
+
+@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8"])
+def test_decode_probe_folds_exactly_the_symbols_of_every_page(native, oracle, coder):
+    """CF_B200_KERNEL_DECODE_PROBE runs the lanes kernel's fetch + entropy decode without attention and leaves, per
+    (chunk, kv head), the XOR of every 4-symbol word it decoded: it must equal the XOR over the symbols the decode
+    probe kernel (and the oracle, which that kernel is checked against) recovers from the same pages."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, info = build_sealed_layer(np.array([160, 64]), coder=coder, seed=85)
+    q = _q(2, 32, 86)
+    layer.attention(q, kernel=native.KERNEL_DECODE_PROBE, stages=native.STAGE_PLAN | native.STAGE_ATTENTION)
+    torch.cuda.synchronize()
+    assert layer.device_status() == 0
+    ws = layer.workspace
+    base = (-ws.data_ptr()) % 256
+    raw = ws[base:].cpu().numpy()
+    header = raw[:64].view(np.uint32)
+    chunks, pages_per_unit = int(header[0]), int(header[1])
+    assert chunks == 2 and pages_per_unit >= 10                       # one chunk per sequence here
+    partials_offset = (64 + 4 * 3 + 255) // 256 * 256
+    stride = 130                                                      # floats per (chunk, query head)
+    partials = raw[partials_offset:partials_offset + chunks * 32 * stride * 4].view(np.uint32).reshape(chunks, 32, stride)
+    for seq, pages in ((0, 10), (1, 4)):
+        ks, vs = layer.decode_pages(layer.h_page_table[seq, :pages])
+        ks, vs = ks.cpu().numpy(), vs.cpu().numpy()
+        for head in range(8):
+            want = (np.bitwise_xor.reduce(np.ascontiguousarray(ks[:, head]).view("<u4").ravel()) ^
+                    np.bitwise_xor.reduce(np.ascontiguousarray(vs[:, head]).view("<u4").ravel()))
+            assert int(partials[seq, head * 4, 0]) == int(want), (seq, head)
