@@ -381,9 +381,9 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     }
                     // P rows as A fragments. Rows g / g+8 of the fragment belong to lane tags g>>2 / (g>>2)+2; a lane
                     // feeds the row whose tag is its own t and zeros (read from the zero row) otherwise.
+                    uint32_t ra[2][NG][8], rb[2][NG][8];   // [fp16(p) | its rounding residue][group][fragment words]
 #pragma unroll
-                    for (int part = 0; part < 2; ++part) {  // fp16(p), then the rounding residue
-                        uint32_t ra[NG][8], rb[NG][8];
+                    for (int part = 0; part < 2; ++part) {
 #pragma unroll
                         for (int n = 0; n < NG; ++n) {
                             const __half *rows = (part ? p_rows_lo : p_rows) + (4u * n + o_head) * 16u;
@@ -393,21 +393,24 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                             const uint4 a_hi = *reinterpret_cast<const uint4 *>(row_a + 8);
                             const uint4 b_lo = *reinterpret_cast<const uint4 *>(row_b);
                             const uint4 b_hi = *reinterpret_cast<const uint4 *>(row_b + 8);
-                            ra[n][0] = a_lo.x; ra[n][1] = a_lo.y; ra[n][2] = a_lo.z; ra[n][3] = a_lo.w;
-                            ra[n][4] = a_hi.x; ra[n][5] = a_hi.y; ra[n][6] = a_hi.z; ra[n][7] = a_hi.w;
-                            rb[n][0] = b_lo.x; rb[n][1] = b_lo.y; rb[n][2] = b_lo.z; rb[n][3] = b_lo.w;
-                            rb[n][4] = b_hi.x; rb[n][5] = b_hi.y; rb[n][6] = b_hi.z; rb[n][7] = b_hi.w;
+                            ra[part][n][0] = a_lo.x; ra[part][n][1] = a_lo.y; ra[part][n][2] = a_lo.z; ra[part][n][3] = a_lo.w;
+                            ra[part][n][4] = a_hi.x; ra[part][n][5] = a_hi.y; ra[part][n][6] = a_hi.z; ra[part][n][7] = a_hi.w;
+                            rb[part][n][0] = b_lo.x; rb[part][n][1] = b_lo.y; rb[part][n][2] = b_lo.z; rb[part][n][3] = b_lo.w;
+                            rb[part][n][4] = b_hi.x; rb[part][n][5] = b_hi.y; rb[part][n][6] = b_hi.z; rb[part][n][7] = b_hi.w;
                         }
+                    }
 #pragma unroll
-                        for (int tq = 0; tq < 4; ++tq) {   // token quads outside: consecutive mma feed different accumulators
+                    for (int tq = 0; tq < 4; ++tq) {   // token quads outside: consecutive mma feed different accumulators
 #pragma unroll
-                            for (int dd = 0; dd < 4; ++dd) {
-                                uint32_t lo, hi;
-                                quad_to_half2(u.vq[dd * 4 + tq], lo, hi);
+                        for (int dd = 0; dd < 4; ++dd) {
+                            uint32_t lo, hi;
+                            quad_to_half2(u.vq[dd * 4 + tq], lo, hi);   // converted once, used by both parts
+#pragma unroll
+                            for (int part = 0; part < 2; ++part)
 #pragma unroll
                                 for (int n = 0; n < NG; ++n)
-                                    mma_16816(u.acc[n][dd], ra[n][2 * tq], rb[n][2 * tq], ra[n][2 * tq + 1], rb[n][2 * tq + 1], lo, hi);
-                            }
+                                    mma_16816(u.acc[n][dd], ra[part][n][2 * tq], rb[part][n][2 * tq], ra[part][n][2 * tq + 1],
+                                              rb[part][n][2 * tq + 1], lo, hi);
                         }
                     }
                     }   // !kProbe
