@@ -1,0 +1,478 @@
+// sealed_attention_prefix_tc.cu — attention over a SHARED sealed prefix on the 5th-generation tensor cores
+// (tcgen05.mma with shared-memory operands and accumulators in tensor memory). Geometry: head_dim 128,
+// page_tokens 16, block 64. Same job as described in sealed_attention_prefix.cu's header: pages that every sequence
+// of the batch references are decoded once per tile of 128 query rows and contracted with all those rows at once.
+//
+// One CTA (8 warps) owns a unit = (prefix chunk, kv head, tile of 128 rows = sequences x group heads).
+//   Q tile           128 rows x 128 channels binary16 in shared memory, loaded once per unit     (A of S = Q K^T)
+//   per round of 8 pages = 128 tokens:
+//     decode         warp w gets page round+w by one bulk async copy (mbarrier, bounded wait), decodes it with the
+//                    lane-per-block decoders and writes exact binary16 codes: K tile [token][channel] (B of S),
+//                    V tile [channel][token] (B of O = P V)
+//     S              one thread issues 8 tcgen05.mma (M 128, N 128, K 16 each) into tensor-memory columns 0..127
+//     softmax        warps 0..3: thread t owns row t = TMEM lane t; tcgen05.ld of its 128 scores, page K scales and
+//                    masks applied, running max / sum updated, O in tensor memory rescaled (tcgen05.ld / .st) only
+//                    when some row of the warp moved its max, P written as binary16 to shared memory (A of P V)
+//     O              8 tcgen05.mma accumulate P V into tensor-memory columns 128..255
+//   unit end         O read back, scaled, written with (max, sum) to the shared-prefix partials
+// Operand tiles use the no-swizzle K-major canonical layout of the instruction: 8 rows x 16 bytes core matrices,
+// element (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
+// P is rounded to binary16 once and the SAME rounded weights enter the running sum, so the result is an exactly
+// normalised average with weights perturbed by < 2^-11 each; the page's V scale relative to the unit's first page
+// rides on P, O is kept in units of that first scale.
+// Every wait (copies, tensor-core commits) is bounded; on expiry the CTA raises CF_B200_DEVSTAT_WAIT_EXPIRED, stops
+// taking units and frees its tensor memory.
+
+#include "lanes_decoders.cuh"
+
+namespace cfb {
+namespace {
+
+using namespace lanes;
+
+constexpr int kTcWarps = 8;
+constexpr int kTcThreads = kTcWarps * 32;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one operand tile: 128 rows x 128 binary16
+constexpr uint32_t kOffStages = kTableBytes;
+constexpr uint32_t kOffQ = (kOffStages + kTcWarps * kStageBytes + 127u) / 128u * 128u;
+constexpr uint32_t kOffK = kOffQ + kTileBytes;
+constexpr uint32_t kOffV = kOffK + kTileBytes;
+constexpr uint32_t kOffP = kOffV + kTileBytes;
+constexpr uint32_t kOffMeta = kOffP + kTileBytes;              // per page of the round: k scale, v scale, token count, -
+constexpr uint32_t kOffBars = kOffMeta + kTcWarps * 16;        // 8 copy barriers + S barrier + O barrier
+constexpr uint32_t kOffMisc = kOffBars + (kTcWarps + 2) * 8;   // tmem base, unit, abort flag
+constexpr uint32_t kTcSmem = kOffMisc + 32;
+static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
+constexpr uint32_t kTmemColumns = 256;                         // S: 0..127, O: 128..255
+// instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ uint32_t tile_offset(uint32_t row, uint32_t chunk) {
+    return (row & 7u) * 16u + (row >> 3) * 2048u + chunk * 128u;
+}
+// shared-memory matrix descriptor: start address, leading (K) offset 128 B, stride (row group) offset 2048 B, version 1
+__device__ __forceinline__ uint64_t tile_desc(uint32_t smem_address) {
+    return static_cast<uint64_t>((smem_address >> 4) & 0x3fffu) | (static_cast<uint64_t>(128u >> 4) << 16) |
+           (static_cast<uint64_t>(2048u >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Two quads of symbols (8 codes) -> one 16-byte chunk of binary16 codes, exact.
+__device__ __forceinline__ uint4 codes8(uint32_t qa, uint32_t qb) {
+    uint4 r;
+    quad_to_half2(qa, r.x, r.y);
+    quad_to_half2(qb, r.z, r.w);
+    return r;
+}
+
+// Decode one record into the round's tiles. K quad q of lane l = token l/2, channels 64(l&1)+4q..+3 -> K tile row
+// 16*slot + l/2; V quad q of lane l = channel 4l + q/4, tokens 4(q%4)..+3 -> V tile row = channel, token chunk 2*slot(+1).
+template <class KLane, class VLane>
+__device__ __forceinline__ void decode_to_tiles(KLane &k, VLane &v, uint8_t *k_tile, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
+    const uint32_t k_row = 16u * slot + (lane >> 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {   // c = channel of the lane's V block, and a quarter of its K block
+        uint32_t kq[4], vq[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
+                kq[j] = k.quad();
+                vq[j] = v.quad();
+            } else {
+                k.reload();
+                v.reload();
+                uint32_t ke[4], ve[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    ke[i] = k.symbol();
+                    ve[i] = v.symbol();
+                }
+                kq[j] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+                vq[j] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
+            }
+        }
+        const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
+        const uint32_t v_row = 4u * lane + c;
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
+    }
+}
+template <class KLane>
+__device__ __forceinline__ void decode_k_to_tiles(KLane &k, uint8_t *k_tile, uint32_t slot, uint32_t lane) {
+    const uint32_t k_row = 16u * slot + (lane >> 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t kq[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kq[j] = k.quad();
+        const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
+    }
+}
+template <class VLane>
+__device__ __forceinline__ void decode_v_to_tiles(VLane &v, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t vq[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) vq[j] = v.quad();
+        const uint32_t v_row = 4u * lane + c;
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
+    }
+}
+// A page that is absent (past the chunk's end, or refused) leaves zeros in its slot of both tiles.
+__device__ __forceinline__ void zero_slot(uint8_t *k_tile, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t k_row = 16u * slot + (lane >> 1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, 8u * (lane & 1u) + c)) = z;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(4u * lane + c, 2u * slot)) = z;
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(4u * lane + c, 2u * slot + 1u)) = z;
+    }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(AttentionParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t *k_slot = reinterpret_cast<const uint32_t *>(smem);
+    const uint32_t *v_slot = k_slot + 4096;
+    const uint16_t *k_lut = reinterpret_cast<const uint16_t *>(v_slot + 4096);
+    const uint16_t *v_lut = k_lut + 4096;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint8_t *stage = smem + kOffStages + warp * kStageBytes;
+    uint8_t *q_tile = smem + kOffQ, *k_tile = smem + kOffK, *v_tile = smem + kOffV, *p_tile = smem + kOffP;
+    float *meta = reinterpret_cast<float *>(smem + kOffMeta);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
+    uint64_t *bar = bars + warp, *bar_s = bars + kTcWarps, *bar_o = bars + kTcWarps + 1;
+    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);   // [0] tmem base, [1] unit, [2] abort
+
+    PlanHeader *hdr = plan_header(p);
+    const uint32_t shared_pages = hdr->shared_pages, chunks = hdr->shared_chunks, per_chunk = hdr->shared_pages_per_chunk;
+    if (shared_pages == 0 || chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
+
+    load_tables(smem, p, tid, kTcThreads);
+    if (lane == 0) mbar_init(bar, 1);
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        misc[2] = 0u;
+    }
+    if (lane == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    if (warp == 0) {   // one whole warp allocates the CTA's tensor memory and frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&misc[0])), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+    const uint32_t tmem_row = tmem + (((warp & 3u) * 32u) << 16);   // this warp's quarter of the 128 lanes
+    uint32_t copy_phase = 0, s_phase = 0, o_phase = 0;
+
+    const uint32_t G = p.group;
+    const uint32_t rows_total = p.seq_count * G;
+    const uint32_t row_tiles = (rows_total + 127u) / 128u;
+    const uint32_t unit_count = chunks * p.kv_head_span * row_tiles;
+    const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
+
+    for (;;) {
+        __syncthreads();   // everyone has read the previous unit number; the previous unit's tiles are free
+        if (tid == 0) misc[1] = atomicAdd(&hdr->next_shared_unit, 1u);
+        __syncthreads();
+        const uint32_t unit = misc[1];
+        if (unit >= unit_count || misc[2]) break;
+        const uint32_t tile_index = unit % row_tiles;
+        const uint32_t head_local = (unit / row_tiles) % p.kv_head_span;
+        const uint32_t chunk = unit / (row_tiles * p.kv_head_span);
+        const uint32_t kv_head = p.kv_head_begin + head_local;
+        const uint32_t page_begin = chunk * per_chunk, page_end = min(page_begin + per_chunk, shared_pages);
+
+        // Q tile: row r of the tile = (sequence, head of the group); 16 chunks of 8 channels per row
+        for (uint32_t i = tid; i < 128u * 16u; i += kTcThreads) {
+            const uint32_t r = i >> 4, c = i & 15u, row = tile_index * 128u + r;
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows_total)
+                x = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.queries) +
+                                                     (static_cast<uint64_t>(row / G) * p.query_head_count + kv_head * G + row % G) * 128u + 8u * c);
+            *reinterpret_cast<uint4 *>(q_tile + tile_offset(r, c)) = x;
+        }
+        const uint32_t my_row = tile_index * 128u + (tid & 127u);
+        float m_run = -CUDART_INF_F, l_run = 0.0f;   // rows of warps 0..3 (warps 4..7 carry unused copies)
+        float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
+        bool o_started = false;
+
+        auto dir_entry = [&](uint32_t page) -> uint64_t {
+            return p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + kv_head];
+        };
+        auto entry_ok = [&](uint64_t entry) {
+            const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
+            return units16 != 0 && units16 * 16u <= kStageBytes - 32u;
+        };
+        auto issue = [&](uint64_t entry) {
+            if (lane == 0 && entry_ok(entry)) {
+                const uint32_t bytes = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry)) * 16u;
+                mbar_expect_tx(bar, bytes);
+                bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
+            }
+        };
+        uint64_t entry = page_begin + warp < page_end ? dir_entry(page_begin + warp) : 0ull;
+        issue(entry);
+
+        for (uint32_t round = page_begin; round < page_end; round += kTcWarps) {
+            // ---- decode: warp w takes page round + w into slot w of the tiles ----
+            const uint32_t my_page = round + warp;
+            float k_scale = 0.0f, v_scale = 0.0f;
+            uint32_t token_count = 0;
+            if (my_page < page_end) {
+                if (!entry_ok(entry)) {
+                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                } else if (!mbar_wait(bar, copy_phase & 1u)) {
+                    if (lane == 0) {
+                        raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                        misc[2] = 1u;
+                    }
+                } else {
+                    copy_phase ^= 1u;
+                    const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
+                    if (!record_header_ok(hv, entry, p.codebook_id)) {
+                        if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                    } else {
+                        const uint32_t k_units = hv.x & 0xffffu;
+                        const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu;
+                        const uint8_t *k_part = stage + 16, *v_part = k_part + 16u * k_units;
+                        token_count = hv.y >> 16;
+                        k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) * (p.softmax_scale * kLog2e);
+                        v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
+                        if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
+                            RansLane k, v;
+                            k.open(k_part, lane, k_slot);
+                            v.open(v_part, lane, v_slot);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
+                        } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
+                            HuffLane k, v;
+                            k.open(k_part, lane, k_lut);
+                            v.open(v_part, lane, v_lut);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
+                        } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
+                            FixedLane k, v;
+                            k.open(k_part, lane);
+                            v.open(v_part, lane);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
+                        } else {
+                            if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            else { FixedLane k; k.open(k_part, lane); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_to_tiles(v, v_tile, warp, lane); }
+                            else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_to_tiles(v, v_tile, warp, lane); }
+                            else { FixedLane v; v.open(v_part, lane); decode_v_to_tiles(v, v_tile, warp, lane); }
+                        }
+                    }
+                }
+            }
+            if (token_count == 0u) zero_slot(k_tile, v_tile, warp, lane);
+            if (lane == 0) {
+                meta[4 * warp] = k_scale;
+                meta[4 * warp + 1] = v_scale;
+                meta[4 * warp + 2] = __uint_as_float(token_count);   // 0: the page contributes nothing
+            }
+            __syncwarp();   // every lane is done with the stage
+            entry = my_page + kTcWarps < page_end ? dir_entry(my_page + kTcWarps) : 0ull;
+            if (my_page + kTcWarps < page_end) issue(entry);
+            fence_async_smem();   // the tiles were written through the generic proxy; the tensor core reads through the async one
+            tc_fence_before();
+            __syncthreads();
+            if (misc[2]) break;   // uniform: a copy never arrived
+
+            // ---- S = Q K^T ----
+            if (tid == 0) {
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t s = 0; s < 8; ++s)
+                    umma(tmem, tile_desc(smem_addr(q_tile) + 256u * s), tile_desc(smem_addr(k_tile) + 256u * s), s);
+                umma_commit(bar_s);
+            }
+
+            // ---- softmax on rows: warps 0..3, thread = row ----
+            const uint32_t in_round = min(static_cast<uint32_t>(kTcWarps), page_end - round);
+            if (v_unit == 0.0f)
+                for (uint32_t pg = 0; pg < in_round; ++pg)
+                    if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
+            const bool s_ready = mbar_wait(bar_s, s_phase & 1u);
+            s_phase ^= 1u;
+            if (!s_ready && lane == 0) {
+                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                misc[2] = 1u;
+            }
+            tc_fence_after();
+            if (warp < 4 && s_ready) {
+                // pass 1: the row's maximum over the round's visible tokens
+                float r_max = -CUDART_INF_F;
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
+                    uint32_t s_raw[32];
+                    tmem_load32(tmem_row + c0, s_raw);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t pg = (c0 + j) >> 4, tok = (c0 + j) & 15u;
+                        if (tok < __float_as_uint(meta[4 * pg + 2])) r_max = fmaxf(r_max, __uint_as_float(s_raw[j]) * meta[4 * pg]);
+                    }
+                }
+                const float m_new = fmaxf(m_run, r_max);
+                const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
+                const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
+                m_run = m_new;
+                // O in tensor memory follows the new maximum; skipped when no row of this warp moved
+                if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+#pragma unroll 1
+                    for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
+                        uint32_t o_raw[32];
+                        tmem_load32(tmem_row + 128u + c0, o_raw);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
+                        tmem_store32(tmem_row + 128u + c0, o_raw);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                // pass 2: weights, rounded to binary16 once; the rounded weights also form the sum
+                float sum = 0.0f;
+                const uint32_t r = tid;   // row of the tile = TMEM lane
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
+                    uint32_t s_raw[32];
+                    tmem_load32(tmem_row + c0, s_raw);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const uint32_t pg = (c0 + j) >> 4, tok = (c0 + j) & 15u;   // j and j + 1 lie in the same page
+                        const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
+                        const float ks = meta[4 * pg];
+                        const float ratio = count ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;   // V scale relative to the unit's
+                        const float inverse = count ? __fdividef(v_unit, meta[4 * pg + 1]) : 0.0f;
+                        const float w0 = tok < count ? exp2f(__uint_as_float(s_raw[j]) * ks - z) : 0.0f;
+                        const float w1 = tok + 1u < count ? exp2f(__uint_as_float(s_raw[j + 1]) * ks - z) : 0.0f;
+                        const __half2 h = __floats2half2_rn(w0 * ratio, w1 * ratio);
+                        const float2 back = __half22float2(h);
+                        sum += (back.x + back.y) * inverse;
+                        packed[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)   // 8 tokens = one 16-byte chunk of the row
+                        *reinterpret_cast<uint4 *>(p_tile + tile_offset(r, (c0 >> 3) + c)) =
+                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                }
+                l_run = l_run * alpha + sum;
+            }
+            fence_async_smem();
+            tc_fence_before();
+            __syncthreads();
+            if (misc[2]) break;
+
+            // ---- O += P V ----
+            if (tid == 0) {
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t s = 0; s < 8; ++s)
+                    umma(tmem + 128u, tile_desc(smem_addr(p_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s),
+                         (o_started || s) ? 1u : 0u);
+                umma_commit(bar_o);
+            }
+            o_started = true;
+            const bool o_ready = mbar_wait(bar_o, o_phase & 1u);   // the tiles are reused by the next round's decode
+            o_phase ^= 1u;
+            if (!o_ready && lane == 0) {
+                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                misc[2] = 1u;
+            }
+            tc_fence_after();
+        }
+
+        // ---- partials of the unit: one (max, sum, weighted[128]) per row ----
+        if (warp < 4 && o_started && !misc[2]) {   // whole warps: the tensor-memory loads are warp-wide
+            const bool live = my_row < rows_total;
+            float *dst = live ? shared_partial_ptr(p, chunk, my_row / G, head_local * G + my_row % G) : nullptr;
+            if (live) {
+                dst[0] = m_run;
+                dst[1] = l_run;
+            }
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
+                uint32_t o_raw[32];
+                tmem_load32(tmem_row + 128u + c0, o_raw);
+                if (live) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2 *>(dst + 2 + c0 + j) =
+                            make_float2(__uint_as_float(o_raw[j]) * v_unit, __uint_as_float(o_raw[j + 1]) * v_unit);
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    // teardown: a copy whose wait ran out gets one more bounded chance to land; tensor memory is returned
+    if (misc[2]) mbar_wait(bar, copy_phase & 1u);
+    tc_fence_before();
+    __syncthreads();
+    if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns));
+}
+
+}  // namespace
+
+cudaError_t launch_prefix_attention_tc(const AttentionParams &p, cudaStream_t stream) {
+    static int sm_count = 0;
+    static bool configured = false;
+    if (!configured) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(prefix_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    prefix_attention_tc_kernel<<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace cfb
