@@ -10,16 +10,16 @@
 //                    lane-per-block decoders and writes exact binary16 codes: K tile [token][channel] (B of S),
 //                    V tile [channel][token] (B of O = P V)
 //     S              one thread issues 8 tcgen05.mma (M 128, N 128, K 16 each) into tensor-memory columns 0..127
-//     softmax        warps 0..3: thread t owns row t = TMEM lane t; tcgen05.ld of its 128 scores, page K scales and
-//                    masks applied, running max / sum updated, O in tensor memory rescaled (tcgen05.ld / .st) only
-//                    when some row of the warp moved its max, P written as binary16 to shared memory (A of P V)
-//     O              8 tcgen05.mma accumulate P V into tensor-memory columns 128..255
+//     softmax        all 8 warps: a thread owns one row (= TMEM lane, in its warp's quarter) and half of the round's 128
+//                    score columns; tcgen05.ld of its 64 scores, page K scales and masks applied, the row's two
+//                    threads share their maxima through shared memory, running max / sum updated, O in tensor memory rescaled (tcgen05.ld / .st) only
+//                    when some row of the warp moved its max, P written to shared memory as binary16 (the P tile) plus
+//                    its rounding residue (into the K tile, free once S is complete): two A operands of P V
+//     O              16 tcgen05.mma accumulate P V into tensor-memory columns 128..255
 //   unit end         O read back, scaled, written with (max, sum) to the shared-prefix partials
 // Operand tiles use the no-swizzle K-major canonical layout of the instruction: 8 rows x 16 bytes core matrices,
 // element (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
-// P is rounded to binary16 once and the SAME rounded weights enter the running sum, so the result is an exactly
-// normalised average with weights perturbed by < 2^-11 each; the page's V scale relative to the unit's first page
-// rides on P, O is kept in units of that first scale.
+// The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
 // Every wait (copies, tensor-core commits) is bounded; on expiry the CTA raises CF_B200_DEVSTAT_WAIT_EXPIRED, stops
 // taking units and frees its tensor memory.
 
@@ -41,7 +41,8 @@ constexpr uint32_t kOffP = kOffV + kTileBytes;
 constexpr uint32_t kOffMeta = kOffP + kTileBytes;              // per page of the round: k scale, v scale, token count, -
 constexpr uint32_t kOffBars = kOffMeta + kTcWarps * 16;        // 8 copy barriers + S barrier + O barrier
 constexpr uint32_t kOffMisc = kOffBars + (kTcWarps + 2) * 8;   // tmem base, unit, abort flag
-constexpr uint32_t kTcSmem = kOffMisc + 32;
+constexpr uint32_t kOffRowMax = kOffMisc + 32;                 // [2 column halves][128 rows]
+constexpr uint32_t kTcSmem = kOffRowMax + 2 * 128 * 4;
 static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
 constexpr uint32_t kTmemColumns = 256;                         // S: 0..127, O: 128..255
 // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
@@ -75,8 +76,8 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
           "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -185,6 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(Atte
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
     uint64_t *bar = bars + warp, *bar_s = bars + kTcWarps, *bar_o = bars + kTcWarps + 1;
     uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);   // [0] tmem base, [1] unit, [2] abort
+    float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
 
     PlanHeader *hdr = plan_header(p);
     const uint32_t shared_pages = hdr->shared_pages, chunks = hdr->shared_chunks, per_chunk = hdr->shared_pages_per_chunk;
@@ -237,8 +239,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(Atte
                                                      (static_cast<uint64_t>(row / G) * p.query_head_count + kv_head * G + row % G) * 128u + 8u * c);
             *reinterpret_cast<uint4 *>(q_tile + tile_offset(r, c)) = x;
         }
-        const uint32_t my_row = tile_index * 128u + (tid & 127u);
-        float m_run = -CUDART_INF_F, l_run = 0.0f;   // rows of warps 0..3 (warps 4..7 carry unused copies)
+        float m_run = -CUDART_INF_F, l_run = 0.0f;   // the row's running maximum; this thread's half of its running sum
         float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
         bool o_started = false;
 
@@ -333,75 +334,91 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(Atte
                 umma_commit(bar_s);
             }
 
-            // ---- softmax on rows: warps 0..3, thread = row ----
+            // ---- softmax: thread = (row, half of the round's columns) ----
             const uint32_t in_round = min(static_cast<uint32_t>(kTcWarps), page_end - round);
             if (v_unit == 0.0f)
                 for (uint32_t pg = 0; pg < in_round; ++pg)
                     if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
-            const bool s_ready = mbar_wait(bar_s, s_phase & 1u);
+            const bool s_ready = __all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u));   // warp-uniform: warp-wide loads follow
             s_phase ^= 1u;
             if (!s_ready && lane == 0) {
                 raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
                 misc[2] = 1u;
             }
             tc_fence_after();
-            if (warp < 4 && s_ready) {
-                // pass 1: the row's maximum over the round's visible tokens
-                float r_max = -CUDART_INF_F;
-#pragma unroll 1
-                for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
-                    uint32_t s_raw[32];
-                    tmem_load32(tmem_row + c0, s_raw);
+            // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the
+            // 64 score columns (4 pages) of half w >> 2; the two threads of a row meet through row_max[].
+            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
+            uint32_t s_raw[2][32];
+            if (s_ready) {
+                tmem_load32(tmem_row + 64u * half, s_raw[0]);
+                tmem_load32(tmem_row + 64u * half + 32u, s_raw[1]);
+                tmem_load_wait();
+            }
+            float part_max = -CUDART_INF_F;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t pg = (c0 + j) >> 4, tok = (c0 + j) & 15u;
-                        if (tok < __float_as_uint(meta[4 * pg + 2])) r_max = fmaxf(r_max, __uint_as_float(s_raw[j]) * meta[4 * pg]);
-                    }
+            for (int q = 0; q < 4; ++q) {   // page 4 half + q: scale, mask, maximum — in place
+                const uint32_t pg = 4u * half + q;
+                const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
+                const float ks = meta[4 * pg];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    uint32_t &cell = s_raw[q >> 1][16 * (q & 1) + j];
+                    const float v = static_cast<uint32_t>(j) < count ? __uint_as_float(cell) * ks : -CUDART_INF_F;
+                    cell = __float_as_uint(v);
+                    part_max = fmaxf(part_max, v);
                 }
-                const float m_new = fmaxf(m_run, r_max);
+            }
+            row_max[half * 128u + row_in_tile] = part_max;
+            __syncthreads();
+            if (s_ready) {
+                const float m_new = fmaxf(m_run, fmaxf(row_max[row_in_tile], row_max[128u + row_in_tile]));
                 const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
                 const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
                 m_run = m_new;
-                // O in tensor memory follows the new maximum; skipped when no row of this warp moved
+                // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
                 if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
 #pragma unroll 1
-                    for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
+                    for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
                         uint32_t o_raw[32];
-                        tmem_load32(tmem_row + 128u + c0, o_raw);
+                        tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
+                        tmem_load_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
-                        tmem_store32(tmem_row + 128u + c0, o_raw);
+                        tmem_store32(tmem_row + 128u + 64u * half + c0, o_raw);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
-                // pass 2: weights, rounded to binary16 once; the rounded weights also form the sum
+                // weights as binary16 plus their rounding residue (two A operands: the P tile, and the K tile, which the
+                // tensor core is done with once the scores are complete), so that P V is accurate to fp32 level whatever
+                // the spread of the V scales
                 float sum = 0.0f;
-                const uint32_t r = tid;   // row of the tile = TMEM lane
-#pragma unroll 1
-                for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
-                    uint32_t s_raw[32];
-                    tmem_load32(tmem_row + c0, s_raw);
-                    uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const uint32_t pg = (c0 + j) >> 4, tok = (c0 + j) & 15u;   // j and j + 1 lie in the same page
-                        const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
-                        const float ks = meta[4 * pg];
-                        const float ratio = count ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;   // V scale relative to the unit's
-                        const float inverse = count ? __fdividef(v_unit, meta[4 * pg + 1]) : 0.0f;
-                        const float w0 = tok < count ? exp2f(__uint_as_float(s_raw[j]) * ks - z) : 0.0f;
-                        const float w1 = tok + 1u < count ? exp2f(__uint_as_float(s_raw[j + 1]) * ks - z) : 0.0f;
-                        const __half2 h = __floats2half2_rn(w0 * ratio, w1 * ratio);
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t pg = 4u * half + q;
+                    const float ratio = __float_as_uint(meta[4 * pg + 2]) ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float w0 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) - z);       // masked: exp2(-inf) = 0
+                        const float w1 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]) - z);
+                        sum += w0 + w1;
+                        const float a0 = w0 * ratio, a1 = w1 * ratio;
+                        const __half2 h = __floats2half2_rn(a0, a1);
                         const float2 back = __half22float2(h);
-                        sum += (back.x + back.y) * inverse;
-                        packed[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                        const __half2 l = __floats2half2_rn(a0 - back.x, a1 - back.y);
+                        hi[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                        lo[j >> 1] = *reinterpret_cast<const uint32_t *>(&l);
                     }
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)   // 8 tokens = one 16-byte chunk of the row
-                        *reinterpret_cast<uint4 *>(p_tile + tile_offset(r, (c0 >> 3) + c)) =
-                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                    for (int c = 0; c < 2; ++c) {   // 8 tokens = one 16-byte chunk of the row
+                        *reinterpret_cast<uint4 *>(p_tile + tile_offset(row_in_tile, 2u * pg + c)) =
+                            make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+                        *reinterpret_cast<uint4 *>(k_tile + tile_offset(row_in_tile, 2u * pg + c)) =
+                            make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+                    }
                 }
-                l_run = l_run * alpha + sum;
+                l_run = l_run * alpha + sum;   // this thread's half of the row's sum; the halves are added at the unit's end
             }
             fence_async_smem();
             tc_fence_before();
@@ -415,6 +432,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(Atte
                 for (uint32_t s = 0; s < 8; ++s)
                     umma(tmem + 128u, tile_desc(smem_addr(p_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s),
                          (o_started || s) ? 1u : 0u);
+#pragma unroll
+                for (uint32_t s = 0; s < 8; ++s)   // the residue of P, staged in the K tile
+                    umma(tmem + 128u, tile_desc(smem_addr(k_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s), 1u);
                 umma_commit(bar_o);
             }
             o_started = true;
@@ -427,23 +447,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_tc_kernel(Atte
             tc_fence_after();
         }
 
-        // ---- partials of the unit: one (max, sum, weighted[128]) per row ----
-        if (warp < 4 && o_started && !misc[2]) {   // whole warps: the tensor-memory loads are warp-wide
-            const bool live = my_row < rows_total;
-            float *dst = live ? shared_partial_ptr(p, chunk, my_row / G, head_local * G + my_row % G) : nullptr;
-            if (live) {
-                dst[0] = m_run;
-                dst[1] = l_run;
-            }
+        // ---- partials of the unit: one (max, sum, weighted[128]) per row; each thread writes its 64 channels ----
+        {
+            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
+            const uint32_t row = tile_index * 128u + row_in_tile;
+            row_max[half * 128u + row_in_tile] = l_run;   // reused: the two halves of the row's sum
+            __syncthreads();
+            if (o_started && !misc[2]) {   // whole warps: the tensor-memory loads are warp-wide
+                const bool live = row < rows_total;
+                float *dst = live ? shared_partial_ptr(p, chunk, row / G, head_local * G + row % G) : nullptr;
+                if (live && half == 0) {
+                    dst[0] = m_run;
+                    dst[1] = row_max[row_in_tile] + row_max[128u + row_in_tile];
+                }
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < 128u; c0 += 32u) {
-                uint32_t o_raw[32];
-                tmem_load32(tmem_row + 128u + c0, o_raw);
-                if (live) {
+                for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+                    uint32_t o_raw[32];
+                    tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
+                    tmem_load_wait();
+                    if (live) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2)
-                        *reinterpret_cast<float2 *>(dst + 2 + c0 + j) =
-                            make_float2(__uint_as_float(o_raw[j]) * v_unit, __uint_as_float(o_raw[j + 1]) * v_unit);
+                        for (int j = 0; j < 32; j += 2)
+                            *reinterpret_cast<float2 *>(dst + 2 + 64u * half + c0 + j) =
+                                make_float2(__uint_as_float(o_raw[j]) * v_unit, __uint_as_float(o_raw[j + 1]) * v_unit);
+                    }
                 }
             }
         }
