@@ -92,8 +92,6 @@ bool lanes_kernel_supports(const AttentionParams &p);
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream);
 // Implemented in sealed_attention_prefix.cu
 cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t stream);
-// Implemented in sealed_attention_prefix_tc.cu
-cudaError_t launch_prefix_attention_tc(const AttentionParams &p, cudaStream_t stream);
 // Implemented in dense_attention.cu
 cudaError_t launch_dense_attention(const AttentionParams &p, cudaStream_t stream);
 

@@ -589,7 +589,7 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     }
     if ((stages & CF_B200_STAGE_PLAN) && cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
     if (stages & CF_B200_STAGE_ATTENTION) {
-        if (p.shared_prefix_pages && cfb::launch_prefix_attention_tc(p, s) != cudaSuccess) return CF_ERR_CUDA;
+        if (p.shared_prefix_pages && cfb::launch_prefix_attention(p, s) != cudaSuccess) return CF_ERR_CUDA;
         const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
         if (e != cudaSuccess) return CF_ERR_CUDA;
     }

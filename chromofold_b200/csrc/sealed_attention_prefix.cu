@@ -1,26 +1,33 @@
 // sealed_attention_prefix.cu — attention over a SHARED sealed prefix: pages that every sequence of the batch
 // references (one copy in the arena, the same page ids at the head of every page-table row; the reference's
-// shared-page semantics, src/multisequence_cache.cpp:235-292). Geometry: head_dim 128, page_tokens 16, block 64.
+// shared-page semantics, src/multisequence_cache.cpp:235-292), on the 5th-generation tensor cores (tcgen05.mma with
+// shared-memory operands and accumulators in tensor memory). Geometry: head_dim 128, page_tokens 16, block 64.
 //
-// The per-sequence kernel would decode such a page once per sequence. Here a page is decoded once per row tile and
-// the contraction against all the query rows that share it runs on the tensor cores:
+// The per-sequence kernel would decode such a page once per sequence. Here a page is decoded once per tile of 128
+// query rows (rows = sequence x query head of the kv head's group) and contracted with all those rows at once.
 //
-//   * rows = (sequence, query head of the kv head's group), 128 rows per CTA, 16 per warp (8 warps);
-//     a unit is (prefix chunk, kv head, row tile).
-//   * Round of 8 pages: warp w receives page j+w as one bulk async copy (mbarrier, bounded wait), decodes it with the
-//     lane-per-block decoders and writes the symbols as int8 tiles to shared memory, K as [token][channel] with the
-//     16-byte chunks of a row rotated by a per-token amount, V as [channel][token] — the layouts from which every
-//     mma B fragment is one conflict-free 32-bit load. The next round's copy is issued as soon as the warp has
-//     decoded, so it lands while the tensor-core phase runs.
-//   * Then every warp runs S = Q K^T (Q fragments in registers), an online softmax over two pages at a time, and
-//     O += P V for its 16 rows over the 8 decoded pages. Symbols become exact binary16 codes with byte permutes on
-//     the way into the fragments; the page's K scale multiplies S, its V scale (relative to the step's first page)
-//     multiplies P; P is fed as fp16 plus its rounding residue, so P V is accurate to fp32 level.
-//   * Each unit writes (max, sum, weighted[128]) per row to the shared-prefix partials; the combine kernel merges
-//     them with the per-sequence partials of the private pages and the tail.
-//
-// The contraction's k-order is permuted (channels 4t..4t+3 sit at k = 2t, 2t+1, 2t+8, 2t+9; S columns 2t+e of the
-// two n-tiles are tokens 4t+e and 4t+2+e) so that A and B fragments come from contiguous bytes.
+// One CTA (8 warps) owns a unit = (prefix chunk, kv head, row tile); units are handed out by an atomic counter.
+//   Q tile           128 rows x 128 channels binary16 in shared memory, loaded once per unit     (A of S = Q K^T)
+//   per round of 8 pages = 128 tokens:
+//     decode         warp w gets page round+w by one bulk async copy (mbarrier, bounded wait), decodes it with the
+//                    lane-per-block decoders and writes exact binary16 codes: K tile [token][channel] (B of S),
+//                    V tile [channel][token] (B of O = P V); the next round's copy is issued as soon as the warp
+//                    has decoded, so it lands while the tensor-core phase runs
+//     S              one thread issues 8 tcgen05.mma (M 128, N 128, K 16 each) into tensor-memory columns 0..127
+//     softmax        all 8 warps: a thread owns one row (= tensor-memory lane, in its warp's quarter) and half of the
+//                    round's 128 score columns, which it holds in registers after one tcgen05.ld; page K scales and
+//                    masks applied, the row's two threads share their maxima through shared memory, running max /
+//                    sum updated, O in tensor memory rescaled (tcgen05.ld / .st) only when some row of the warp
+//                    moved its max, P written to shared memory as binary16 (the P tile) plus its rounding residue
+//                    (into the K tile, free once S is complete): two A operands of P V
+//     O              16 tcgen05.mma accumulate P V into tensor-memory columns 128..255
+//   unit end         O read back, scaled, written with (max, sum) to the shared-prefix partials; the combine kernel
+//                    merges them with the per-sequence partials of the private pages and the tail
+// Operand tiles use the no-swizzle K-major canonical layout of the instruction: 8 rows x 16 bytes core matrices,
+// element (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
+// The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
+// Every wait (copies, tensor-core commits) is bounded; on expiry the CTA raises CF_B200_DEVSTAT_WAIT_EXPIRED, stops
+// taking units and frees its tensor memory.
 
 #include "lanes_decoders.cuh"
 
@@ -29,33 +36,90 @@ namespace {
 
 using namespace lanes;
 
-constexpr int kPvInFlight = 4;   // independent accumulators between an mma and the next one on the same accumulator
-constexpr int kPWarps = 8;
-constexpr int kPThreads = kPWarps * 32;
-constexpr uint32_t kTileBytes = 4096;                       // K int8 [16][128] + V int8 [128][16]
+constexpr int kTcWarps = 8;
+constexpr int kTcThreads = kTcWarps * 32;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one operand tile: 128 rows x 128 binary16
 constexpr uint32_t kOffStages = kTableBytes;
-constexpr uint32_t kOffTiles = kOffStages + kPWarps * kStageBytes;
-constexpr uint32_t kOffMeta = kOffTiles + kPWarps * kTileBytes;   // per page of the round: k scale, v scale, token count
-constexpr uint32_t kOffBars = kOffMeta + kPWarps * 16;
-constexpr uint32_t kPrefixSmem = kOffBars + kPWarps * 8;
+constexpr uint32_t kOffQ = (kOffStages + kTcWarps * kStageBytes + 127u) / 128u * 128u;
+constexpr uint32_t kOffK = kOffQ + kTileBytes;
+constexpr uint32_t kOffV = kOffK + kTileBytes;
+constexpr uint32_t kOffP = kOffV + kTileBytes;
+constexpr uint32_t kOffMeta = kOffP + kTileBytes;              // per page of the round: k scale, v scale, token count, -
+constexpr uint32_t kOffBars = kOffMeta + kTcWarps * 16;        // 8 copy barriers + S barrier + O barrier
+constexpr uint32_t kOffMisc = kOffBars + (kTcWarps + 2) * 8;   // tmem base, unit, abort flag
+constexpr uint32_t kOffRowMax = kOffMisc + 32;                 // [2 column halves][128 rows]
+constexpr uint32_t kTcSmem = kOffRowMax + 2 * 128 * 4;
+static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
+constexpr uint32_t kTmemColumns = 256;                         // S: 0..127, O: 128..255
+// instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const uint32_t *>(&h);
+__device__ __forceinline__ uint32_t tile_offset(uint32_t row, uint32_t chunk) {
+    return (row & 7u) * 16u + (row >> 3) * 2048u + chunk * 128u;
+}
+// Row of the V tile (= column of O) that holds channel 4 * lane + c, the c-th channel of the block lane decodes: the 32
+// lanes of one store spread over all 8 rows of a core matrix, so a 16-byte store per lane meets no bank conflict.
+// Inverse: column n of O is channel 4 * ((n & 7) + 8 * (n >> 5)) + ((n >> 3) & 3).
+__device__ __forceinline__ uint32_t v_tile_row(uint32_t lane, uint32_t c) {
+    return (lane & 7u) + 8u * c + 32u * (lane >> 3);
+}
+// shared-memory matrix descriptor: start address, leading (K) offset 128 B, stride (row group) offset 2048 B, version 1
+__device__ __forceinline__ uint64_t tile_desc(uint32_t smem_address) {
+    return static_cast<uint64_t>((smem_address >> 4) & 0x3fffu) | (static_cast<uint64_t>(128u >> 4) << 16) |
+           (static_cast<uint64_t>(2048u >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Two quads of symbols (8 codes) -> one 16-byte chunk of binary16 codes, exact.
+__device__ __forceinline__ uint4 codes8(uint32_t qa, uint32_t qb) {
+    uint4 r;
+    quad_to_half2(qa, r.x, r.y);
+    quad_to_half2(qb, r.z, r.w);
+    return r;
 }
 
-// Rotation (in 16-byte chunks) of token `tok`'s K row: the eight tokens of either n-tile get eight different values.
-__device__ __forceinline__ uint32_t k_rotation(uint32_t tok) { return ((tok >> 2) << 1) | (tok & 1u); }
-
-// Decode one record into the warp's tile. K quad q of lane l = token l/2, channels 64(l&1)+4q..+3; V quad q of lane l
-// = stream positions 64l+4q..+3 of the token-minor V stream = [channel][token] bytes as they are.
+// Decode one record into the round's tiles. K quad q of lane l = token l/2, channels 64(l&1)+4q..+3 -> K tile row
+// 16*slot + l/2; V quad q of lane l = channel 4l + q/4, tokens 4(q%4)..+3 -> V tile row = channel, token chunk 2*slot(+1).
 template <class KLane, class VLane>
-__device__ __forceinline__ void decode_to_tile(KLane &k, VLane &v, uint8_t *tile, uint32_t lane) {
-    const uint32_t tok = lane >> 1, rot = k_rotation(tok);
-    uint4 *k_row = reinterpret_cast<uint4 *>(tile + tok * 128u);
-    uint4 *v_out = reinterpret_cast<uint4 *>(tile + 2048u + lane * 64u);
+__device__ __forceinline__ void decode_to_tiles(KLane &k, VLane &v, uint8_t *k_tile, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
+    const uint32_t k_row = 16u * slot + (lane >> 1);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 4; ++c) {   // c = channel of the lane's V block, and a quarter of its K block
         uint32_t kq[4], vq[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -75,62 +139,90 @@ __device__ __forceinline__ void decode_to_tile(KLane &k, VLane &v, uint8_t *tile
                 vq[j] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
             }
         }
-        k_row[(4u * (lane & 1u) + c + rot) & 7u] = make_uint4(kq[0], kq[1], kq[2], kq[3]);
-        v_out[c] = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+        const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
+        const uint32_t v_row = v_tile_row(lane, c);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
     }
 }
-
 template <class KLane>
-__device__ __forceinline__ void decode_k_to_tile(KLane &k, uint8_t *tile, uint32_t lane) {
-    const uint32_t tok = lane >> 1, rot = k_rotation(tok);
-    uint4 *k_row = reinterpret_cast<uint4 *>(tile + tok * 128u);
+__device__ __forceinline__ void decode_k_to_tiles(KLane &k, uint8_t *k_tile, uint32_t slot, uint32_t lane) {
+    const uint32_t k_row = 16u * slot + (lane >> 1);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         uint32_t kq[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) kq[j] = k.quad();
-        k_row[(4u * (lane & 1u) + c + rot) & 7u] = make_uint4(kq[0], kq[1], kq[2], kq[3]);
+        const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
     }
 }
-
 template <class VLane>
-__device__ __forceinline__ void decode_v_to_tile(VLane &v, uint8_t *tile, uint32_t lane) {
-    uint4 *v_out = reinterpret_cast<uint4 *>(tile + 2048u + lane * 64u);
+__device__ __forceinline__ void decode_v_to_tiles(VLane &v, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         uint32_t vq[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) vq[j] = v.quad();
-        v_out[c] = make_uint4(vq[0], vq[1], vq[2], vq[3]);
+        const uint32_t v_row = v_tile_row(lane, c);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
+    }
+}
+// A page that is absent (past the chunk's end, or refused) leaves zeros in its slot of both tiles.
+__device__ __forceinline__ void zero_slot(uint8_t *k_tile, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t k_row = 16u * slot + (lane >> 1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, 8u * (lane & 1u) + c)) = z;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_tile_row(lane, c), 2u * slot)) = z;
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_tile_row(lane, c), 2u * slot + 1u)) = z;
     }
 }
 
-__global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(AttentionParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(AttentionParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t *k_slot = reinterpret_cast<const uint32_t *>(smem);
     const uint32_t *v_slot = k_slot + 4096;
     const uint16_t *k_lut = reinterpret_cast<const uint16_t *>(v_slot + 4096);
     const uint16_t *v_lut = k_lut + 4096;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t g = lane >> 2, t = lane & 3u;
     uint8_t *stage = smem + kOffStages + warp * kStageBytes;
-    uint8_t *tiles = smem + kOffTiles;
-    float *meta = reinterpret_cast<float *>(smem + kOffMeta);   // [page of the round][4]: k scale, v scale, tokens, -
-    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + kOffBars) + warp;
+    uint8_t *q_tile = smem + kOffQ, *k_tile = smem + kOffK, *v_tile = smem + kOffV, *p_tile = smem + kOffP;
+    float *meta = reinterpret_cast<float *>(smem + kOffMeta);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
+    uint64_t *bar = bars + warp, *bar_s = bars + kTcWarps, *bar_o = bars + kTcWarps + 1;
+    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);   // [0] tmem base, [1] unit, [2] abort
+    float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
 
     PlanHeader *hdr = plan_header(p);
-    __shared__ uint32_t s_unit;
     const uint32_t shared_pages = hdr->shared_pages, chunks = hdr->shared_chunks, per_chunk = hdr->shared_pages_per_chunk;
     if (shared_pages == 0 || chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
 
-    load_tables(smem, p, tid, kPThreads);
-    if (lane == 0) {
-        mbar_init(bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    load_tables(smem, p, tid, kTcThreads);
+    if (lane == 0) mbar_init(bar, 1);
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        misc[2] = 0u;
     }
+    if (lane == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+    if (warp == 0) {   // one whole warp allocates the CTA's tensor memory and frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&misc[0])), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
     __syncthreads();
-    uint32_t phase = 0;
-    bool expired = false;   // a bounded wait ran out: its copy may still be in flight when the kernel ends
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+    const uint32_t tmem_row = tmem + (((warp & 3u) * 32u) << 16);   // this warp's quarter of the 128 lanes
+    uint32_t copy_phase = 0, s_phase = 0, o_phase = 0;
 
     const uint32_t G = p.group;
     const uint32_t rows_total = p.seq_count * G;
@@ -139,41 +231,29 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
     const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
 
     for (;;) {
-        __syncthreads();   // everyone has read the previous s_unit
-        if (tid == 0) s_unit = atomicAdd(&hdr->next_shared_unit, 1u);
+        __syncthreads();   // everyone has read the previous unit number; the previous unit's tiles are free
+        if (tid == 0) misc[1] = atomicAdd(&hdr->next_shared_unit, 1u);
         __syncthreads();
-        const uint32_t unit = s_unit;
-        if (unit >= unit_count) break;
+        const uint32_t unit = misc[1];
+        if (unit >= unit_count || misc[2]) break;
         const uint32_t tile_index = unit % row_tiles;
         const uint32_t head_local = (unit / row_tiles) % p.kv_head_span;
         const uint32_t chunk = unit / (row_tiles * p.kv_head_span);
         const uint32_t kv_head = p.kv_head_begin + head_local;
         const uint32_t page_begin = chunk * per_chunk, page_end = min(page_begin + per_chunk, shared_pages);
 
-        // this lane's two rows: row g and row g+8 of the warp's sixteen
-        const uint32_t row0 = tile_index * 128u + warp * 16u + g, row1 = row0 + 8u;
-        const bool live0 = row0 < rows_total, live1 = row1 < rows_total;
-        // Q as A fragments, k-step s: (a0, a2) = channels 16s+4t..+3 of row g, (a1, a3) the same of row g+8
-        uint32_t qa[8][4];
-        {
-            const __half *qbase = reinterpret_cast<const __half *>(p.queries);
-            const __half *q0 = qbase + (static_cast<uint64_t>(live0 ? row0 / G : 0u) * p.query_head_count + kv_head * G + (live0 ? row0 % G : 0u)) * 128u;
-            const __half *q1 = qbase + (static_cast<uint64_t>(live1 ? row1 / G : 0u) * p.query_head_count + kv_head * G + (live1 ? row1 % G : 0u)) * 128u;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                const uint2 x = live0 ? *reinterpret_cast<const uint2 *>(q0 + 16 * s + 4 * t) : make_uint2(0u, 0u);
-                const uint2 y = live1 ? *reinterpret_cast<const uint2 *>(q1 + 16 * s + 4 * t) : make_uint2(0u, 0u);
-                qa[s][0] = x.x;
-                qa[s][1] = y.x;
-                qa[s][2] = x.y;
-                qa[s][3] = y.y;
-            }
+        // Q tile: row r of the tile = (sequence, head of the group); 16 chunks of 8 channels per row
+        for (uint32_t i = tid; i < 128u * 16u; i += kTcThreads) {
+            const uint32_t r = i >> 4, c = i & 15u, row = tile_index * 128u + r;
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows_total)
+                x = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.queries) +
+                                                     (static_cast<uint64_t>(row / G) * p.query_head_count + kv_head * G + row % G) * 128u + 8u * c);
+            *reinterpret_cast<uint4 *>(q_tile + tile_offset(r, c)) = x;
         }
-        float o[16][4];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-        float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.0f, l1 = 0.0f;
-        float v_unit = 1.0f;   // O is kept in units of the V scale of the step's first present page
+        float m_run = -CUDART_INF_F, l_run = 0.0f;   // the row's running maximum; this thread's half of its running sum
+        float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
+        bool o_started = false;
 
         auto dir_entry = [&](uint32_t page) -> uint64_t {
             return p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + kv_head];
@@ -189,25 +269,26 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
                 bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
             }
         };
-
         uint64_t entry = page_begin + warp < page_end ? dir_entry(page_begin + warp) : 0ull;
-        __syncthreads();   // the previous unit's tiles and stages are free
         issue(entry);
 
-        for (uint32_t round = page_begin; round < page_end; round += kPWarps) {
-            // ---- decode: warp w takes page round + w ----
+        for (uint32_t round = page_begin; round < page_end; round += kTcWarps) {
+            // ---- decode: warp w takes page round + w into slot w of the tiles ----
             const uint32_t my_page = round + warp;
-            uint8_t *tile = tiles + warp * kTileBytes;
+            // the next round's directory entry is fetched now (two dependent loads), needed only after this page's decode
+            const uint64_t next_entry = my_page + kTcWarps < page_end ? dir_entry(my_page + kTcWarps) : 0ull;
             float k_scale = 0.0f, v_scale = 0.0f;
             uint32_t token_count = 0;
             if (my_page < page_end) {
                 if (!entry_ok(entry)) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
-                } else if (!mbar_wait(bar, phase & 1u)) {
-                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
-                    expired = true;
+                } else if (!mbar_wait(bar, copy_phase & 1u)) {
+                    if (lane == 0) {
+                        raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                        misc[2] = 1u;
+                    }
                 } else {
-                    phase ^= 1u;
+                    copy_phase ^= 1u;
                     const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
                     if (!record_header_ok(hv, entry, p.codebook_id)) {
                         if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
@@ -222,181 +303,202 @@ __global__ void __launch_bounds__(kPThreads, 1) prefix_attention_kernel(Attentio
                             RansLane k, v;
                             k.open(k_part, lane, k_slot);
                             v.open(v_part, lane, v_slot);
-                            decode_to_tile(k, v, tile, lane);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
                         } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
                             HuffLane k, v;
                             k.open(k_part, lane, k_lut);
                             v.open(v_part, lane, v_lut);
-                            decode_to_tile(k, v, tile, lane);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
                         } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
                             FixedLane k, v;
                             k.open(k_part, lane);
                             v.open(v_part, lane);
-                            decode_to_tile(k, v, tile, lane);
+                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
                         } else {
-                            if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_to_tile(k, tile, lane); }
-                            else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_to_tile(k, tile, lane); }
-                            else { FixedLane k; k.open(k_part, lane); decode_k_to_tile(k, tile, lane); }
-                            if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_to_tile(v, tile, lane); }
-                            else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_to_tile(v, tile, lane); }
-                            else { FixedLane v; v.open(v_part, lane); decode_v_to_tile(v, tile, lane); }
+                            if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            else { FixedLane k; k.open(k_part, lane); decode_k_to_tiles(k, k_tile, warp, lane); }
+                            if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_to_tiles(v, v_tile, warp, lane); }
+                            else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_to_tiles(v, v_tile, warp, lane); }
+                            else { FixedLane v; v.open(v_part, lane); decode_v_to_tiles(v, v_tile, warp, lane); }
                         }
                     }
                 }
             }
+            if (token_count == 0u) zero_slot(k_tile, v_tile, warp, lane);
             if (lane == 0) {
                 meta[4 * warp] = k_scale;
                 meta[4 * warp + 1] = v_scale;
                 meta[4 * warp + 2] = __uint_as_float(token_count);   // 0: the page contributes nothing
             }
             __syncwarp();   // every lane is done with the stage
-            entry = my_page + kPWarps < page_end ? dir_entry(my_page + kPWarps) : 0ull;
-            if (my_page + kPWarps < page_end) issue(entry);
-            __syncthreads();   // tiles of the round are complete
+            entry = next_entry;
+            if (my_page + kTcWarps < page_end) issue(entry);
+            fence_async_smem();   // the tiles were written through the generic proxy; the tensor core reads through the async one
+            tc_fence_before();
+            __syncthreads();
+            if (misc[2]) break;   // uniform: a copy never arrived
 
-            // ---- tensor-core phase: this warp's 16 rows against the round's pages, two pages per softmax step ----
-            const uint32_t in_round = min(static_cast<uint32_t>(kPWarps), page_end - round);
-            for (uint32_t pg = 0; pg < in_round; pg += 2) {
-                float s[2][2][4];   // [page of the pair][n-tile][fragment]
-                float ks[2], vs[2];
-                uint32_t tc[2];
-                if (__float_as_uint(meta[4 * pg + 2]) == 0u && (pg + 1 >= in_round || __float_as_uint(meta[4 * pg + 6]) == 0u))
-                    continue;   // neither page of the pair is present (uniform across the block)
-                const uint32_t *krow[2][2];
-                uint32_t krot[2];
+            // ---- S = Q K^T ----
+            if (tid == 0) {
+                tc_fence_after();
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const bool present = pg + h < in_round;
-                    ks[h] = present ? meta[4 * (pg + h)] : 0.0f;
-                    vs[h] = present ? meta[4 * (pg + h) + 1] : 0.0f;
-                    tc[h] = present ? __float_as_uint(meta[4 * (pg + h) + 2]) : 0u;
+                for (uint32_t s = 0; s < 8; ++s)
+                    umma(tmem, tile_desc(smem_addr(q_tile) + 256u * s), tile_desc(smem_addr(k_tile) + 256u * s), s);
+                umma_commit(bar_s);
+            }
+
+            // ---- softmax: thread = (row, half of the round's columns) ----
+            const uint32_t in_round = min(static_cast<uint32_t>(kTcWarps), page_end - round);
+            if (v_unit == 0.0f)
+                for (uint32_t pg = 0; pg < in_round; ++pg)
+                    if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
+            const bool s_ready = __all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u));   // warp-uniform: warp-wide loads follow
+            s_phase ^= 1u;
+            if (!s_ready && lane == 0) {
+                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                misc[2] = 1u;
+            }
+            tc_fence_after();
+            // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the
+            // 64 score columns (4 pages) of half w >> 2; the two threads of a row meet through row_max[].
+            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
+            uint32_t s_raw[2][32];
+            if (s_ready) {
+                tmem_load32(tmem_row + 64u * half, s_raw[0]);
+                tmem_load32(tmem_row + 64u * half + 32u, s_raw[1]);
+                tmem_load_wait();
+            }
+            float part_max = -CUDART_INF_F;
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt) {
-                        s[h][nt][0] = s[h][nt][1] = s[h][nt][2] = s[h][nt][3] = 0.0f;
-                        const uint32_t tok = 4u * (g >> 1) + (g & 1u) + 2u * nt;   // the token of column n = g
-                        krow[h][nt] = reinterpret_cast<const uint32_t *>(tiles + (pg + h) * kTileBytes + tok * 128u) + t;
-                        krot[nt] = k_rotation(tok);
-                    }
-                }
-#pragma unroll
-                for (int ss = 0; ss < 8; ++ss)   // k-steps outside: consecutive mma feed different accumulators
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        if (tc[h] == 0u) continue;   // uniform across the warp
-#pragma unroll
-                        for (int nt = 0; nt < 2; ++nt) {
-                            uint32_t b0, b1;
-                            quad_to_half2(krow[h][nt][4u * ((ss + krot[nt]) & 7u)], b0, b1);
-                            mma_16816(s[h][nt], qa[ss][0], qa[ss][1], qa[ss][2], qa[ss][3], b0, b1);
-                        }
-                    }
-                // scores, masks, row maxima (row g: fragments 0,1; row g+8: fragments 2,3; columns 2t+e)
-                float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const uint32_t tok = 4u * t + 2u * nt + e;
-                            const bool vis = tok < tc[h];
-                            s[h][nt][e] = vis ? s[h][nt][e] * ks[h] : -CUDART_INF_F;
-                            s[h][nt][2 + e] = vis ? s[h][nt][2 + e] * ks[h] : -CUDART_INF_F;
-                            r0 = fmaxf(r0, s[h][nt][e]);
-                            r1 = fmaxf(r1, s[h][nt][2 + e]);
-                        }
-                r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 1));
-                r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 2));
-                r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 1));
-                r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 2));
-                const float n0 = fmaxf(m0, r0), n1 = fmaxf(m1, r1);
-                const float z0 = n0 == -CUDART_INF_F ? 0.0f : n0, z1 = n1 == -CUDART_INF_F ? 0.0f : n1;
-                const float v_ref = tc[0] ? vs[0] : vs[1];
-                const float v_ratio = v_unit / v_ref;
-                v_unit = v_ref;
-                const float a0 = exp2f(m0 - z0), a1 = exp2f(m1 - z1);
-                const float beta0 = a0 * v_ratio, beta1 = a1 * v_ratio;
-                const float vr[2] = {tc[0] ? vs[0] / v_ref : 0.0f, tc[1] ? vs[1] / v_ref : 0.0f};
-                m0 = n0;
-                m1 = n1;
-                float sum0 = 0.0f, sum1 = 0.0f;
-                uint32_t pa[2][2][4];   // [page][hi | residue][A fragment registers]
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    float pr[2][4];
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float w0 = exp2f(s[h][nt][e] - z0), w1 = exp2f(s[h][nt][2 + e] - z1);
-                            sum0 += w0;
-                            sum1 += w1;
-                            pr[nt][e] = w0 * vr[h];       // the page's V scale relative to the step's unit rides on P
-                            pr[nt][2 + e] = w1 * vr[h];
-                        }
-                    // A fragment: a0 = row g, k 2t,2t+1 = tile 0; a1 = row g+8 of tile 0; a2, a3 = the same of tile 1
-                    pa[h][0][0] = pack_half2(pr[0][0], pr[0][1]);
-                    pa[h][0][1] = pack_half2(pr[0][2], pr[0][3]);
-                    pa[h][0][2] = pack_half2(pr[1][0], pr[1][1]);
-                    pa[h][0][3] = pack_half2(pr[1][2], pr[1][3]);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const __half2 hi = *reinterpret_cast<const __half2 *>(&pa[h][0][i]);
-                        const float2 back = __half22float2(hi);
-                        const int nt = i >> 1, base = (i & 1) * 2;
-                        pa[h][1][i] = pack_half2(pr[nt][base] - back.x, pr[nt][base + 1] - back.y);
-                    }
-                }
-                l0 = l0 * a0 + sum0;
-                l1 = l1 * a1 + sum1;
+            for (int q = 0; q < 4; ++q) {   // page 4 half + q: scale, mask, maximum — in place
+                const uint32_t pg = 4u * half + q;
+                const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
+                const float ks = meta[4 * pg];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    o[j][0] *= beta0;
-                    o[j][1] *= beta0;
-                    o[j][2] *= beta1;
-                    o[j][3] *= beta1;
+                    uint32_t &cell = s_raw[q >> 1][16 * (q & 1) + j];
+                    const float v = static_cast<uint32_t>(j) < count ? __uint_as_float(cell) * ks : -CUDART_INF_F;
+                    cell = __float_as_uint(v);
+                    part_max = fmaxf(part_max, v);
                 }
+            }
+            row_max[half * 128u + row_in_tile] = part_max;
+            __syncthreads();
+            if (s_ready) {
+                const float m_new = fmaxf(m_run, fmaxf(row_max[row_in_tile], row_max[128u + row_in_tile]));
+                const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
+                const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
+                m_run = m_new;
+                // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
+                if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+#pragma unroll 1
+                    for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+                        uint32_t o_raw[32];
+                        tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
+                        tmem_load_wait();
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (tc[h] == 0u) continue;
-                    const uint32_t *vt = reinterpret_cast<const uint32_t *>(tiles + (pg + h) * kTileBytes + 2048u);
+                        for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
+                        tmem_store32(tmem_row + 128u + 64u * half + c0, o_raw);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                // weights as binary16 plus their rounding residue (two A operands: the P tile, and the K tile, which the
+                // tensor core is done with once the scores are complete), so that P V is accurate to fp32 level whatever
+                // the spread of the V scales
+                float sum = 0.0f;
 #pragma unroll
-                    for (int j0 = 0; j0 < 16; j0 += kPvInFlight) {   // channels 8j + g, tokens 4t..4t+3
-                        uint32_t b0[kPvInFlight], b1[kPvInFlight];
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t pg = 4u * half + q;
+                    const float ratio = __float_as_uint(meta[4 * pg + 2]) ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
+                    uint32_t hi[8], lo[8];
 #pragma unroll
-                        for (int j = 0; j < kPvInFlight; ++j) quad_to_half2(vt[(8u * (j0 + j) + g) * 4u + t], b0[j], b1[j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        const float w0 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) - z);       // masked: exp2(-inf) = 0
+                        const float w1 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]) - z);
+                        sum += w0 + w1;
+                        const float a0 = w0 * ratio, a1 = w1 * ratio;
+                        const __half2 h = __floats2half2_rn(a0, a1);
+                        const float2 back = __half22float2(h);
+                        const __half2 l = __floats2half2_rn(a0 - back.x, a1 - back.y);
+                        hi[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                        lo[j >> 1] = *reinterpret_cast<const uint32_t *>(&l);
+                    }
 #pragma unroll
-                        for (int j = 0; j < kPvInFlight; ++j) mma_16816(o[j0 + j], pa[h][0][0], pa[h][0][1], pa[h][0][2], pa[h][0][3], b0[j], b1[j]);
+                    for (int c = 0; c < 2; ++c) {   // 8 tokens = one 16-byte chunk of the row
+                        *reinterpret_cast<uint4 *>(p_tile + tile_offset(row_in_tile, 2u * pg + c)) =
+                            make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+                        *reinterpret_cast<uint4 *>(k_tile + tile_offset(row_in_tile, 2u * pg + c)) =
+                            make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+                    }
+                }
+                l_run = l_run * alpha + sum;   // this thread's half of the row's sum; the halves are added at the unit's end
+            }
+            fence_async_smem();
+            tc_fence_before();
+            __syncthreads();
+            if (misc[2]) break;
+
+            // ---- O += P V ----
+            if (tid == 0) {
+                tc_fence_after();
 #pragma unroll
-                        for (int j = 0; j < kPvInFlight; ++j) mma_16816(o[j0 + j], pa[h][1][0], pa[h][1][1], pa[h][1][2], pa[h][1][3], b0[j], b1[j]);
+                for (uint32_t s = 0; s < 8; ++s)
+                    umma(tmem + 128u, tile_desc(smem_addr(p_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s),
+                         (o_started || s) ? 1u : 0u);
+#pragma unroll
+                for (uint32_t s = 0; s < 8; ++s)   // the residue of P, staged in the K tile
+                    umma(tmem + 128u, tile_desc(smem_addr(k_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s), 1u);
+                umma_commit(bar_o);
+            }
+            o_started = true;
+            const bool o_ready = mbar_wait(bar_o, o_phase & 1u);   // the tiles are reused by the next round's decode
+            o_phase ^= 1u;
+            if (!o_ready && lane == 0) {
+                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+                misc[2] = 1u;
+            }
+            tc_fence_after();
+        }
+
+        // ---- partials of the unit: one (max, sum, weighted[128]) per row; each thread writes its 64 channels ----
+        {
+            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
+            const uint32_t row = tile_index * 128u + row_in_tile;
+            row_max[half * 128u + row_in_tile] = l_run;   // reused: the two halves of the row's sum
+            __syncthreads();
+            if (o_started && !misc[2]) {   // whole warps: the tensor-memory loads are warp-wide
+                const bool live = row < rows_total;
+                float *dst = live ? shared_partial_ptr(p, chunk, row / G, head_local * G + row % G) : nullptr;
+                if (live && half == 0) {
+                    dst[0] = m_run;
+                    dst[1] = row_max[row_in_tile] + row_max[128u + row_in_tile];
+                }
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+                    uint32_t o_raw[32];
+                    tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
+                    tmem_load_wait();
+                    if (live) {
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {   // columns t, t + 8, t + 16, t + 24 of the 32 are 4 consecutive channels
+                            float *out = dst + 2 + 64u * half + c0 + 4 * t;
+                            *reinterpret_cast<float2 *>(out) =
+                                make_float2(__uint_as_float(o_raw[t]) * v_unit, __uint_as_float(o_raw[t + 8]) * v_unit);
+                            *reinterpret_cast<float2 *>(out + 2) =
+                                make_float2(__uint_as_float(o_raw[t + 16]) * v_unit, __uint_as_float(o_raw[t + 24]) * v_unit);
+                        }
                     }
                 }
             }
-            __syncthreads();   // the round's tiles may be overwritten
         }
-
-        // ---- partials of the unit: one (max, sum, weighted[128]) per row ----
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const uint32_t row = r ? row1 : row0;
-            if (!(r ? live1 : live0)) continue;
-            float *dst = shared_partial_ptr(p, chunk, row / G, head_local * G + row % G);
-            if (t == 0) {
-                dst[0] = r ? m1 : m0;
-                dst[1] = r ? l1 : l0;
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                *reinterpret_cast<float2 *>(dst + 2 + 8 * j + 2 * t) = make_float2(o[j][2 * r] * v_unit, o[j][2 * r + 1] * v_unit);
-        }
+        tc_fence_before();
     }
-    // A copy is issued only for a page the loop goes on to wait for, so nothing is in flight here unless a wait ran
-    // out; then the copy gets one more bounded chance to land before the block's shared memory goes away.
-    if (expired) mbar_wait(bar, phase & 1u);
+    // teardown: a copy whose wait ran out gets one more bounded chance to land; tensor memory is returned
+    if (misc[2]) mbar_wait(bar, copy_phase & 1u);
+    tc_fence_before();
+    __syncthreads();
+    if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns));
 }
 
 }  // namespace
@@ -410,11 +512,11 @@ cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t strea
         if (e != cudaSuccess) return e;
         e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(prefix_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrefixSmem));
+        e = cudaFuncSetAttribute(prefix_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    prefix_attention_kernel<<<sm_count, kPThreads, kPrefixSmem, stream>>>(p);
+    prefix_attention_kernel<<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 
