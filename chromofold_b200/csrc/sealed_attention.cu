@@ -35,6 +35,19 @@ __device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint
     return pages - first;
 }
 
+// Shared-prefix hint, part one: block s compares the first `shared_prefix_pages` ids of entry s's page-table row with the
+// first entry's and leaves the verdict (1 = differs) in the entry's cell of the chunk-prefix array, which the plan kernel
+// reads before it overwrites the array with the real prefix sums.
+__global__ void __launch_bounds__(256) verify_prefix_kernel(AttentionParams p) {
+    const uint32_t s = blockIdx.x;
+    const uint32_t *row0 = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
+    const uint32_t *row = p.page_table + static_cast<uint64_t>(slot_of(p, s)) * p.page_table_stride;
+    int bad = 0;
+    for (uint32_t pg = threadIdx.x; pg < p.shared_prefix_pages; pg += blockDim.x) bad |= row[pg] != row0[pg];
+    bad = __syncthreads_or(bad);
+    if (threadIdx.x == 0) chunk_prefix(p)[s] = bad ? 1u : 0u;
+}
+
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     __shared__ uint32_t scan[kPlanThreads];
     __shared__ uint32_t s_total;
@@ -46,21 +59,15 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     uint32_t *prefix = chunk_prefix(p);
 
     // Shared prefix: taken only if every listed sequence has the pages sealed and its page-table row starts with the
-    // same ids as the first sequence's. The pages are then cut into chunks for the shared-prefix kernel and left out
-    // of the per-sequence chunks below.
+    // same ids as the first sequence's (compared by verify_prefix_kernel, verdict per entry in prefix[]). The pages are
+    // then cut into chunks for the shared-prefix kernel and left out of the per-sequence chunks below.
     uint32_t shared = p.shared_prefix_pages;
     if (shared) {
-        const uint32_t *row0 = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
         int bad = 0;
         for (uint32_t s = begin; s < end; ++s) {   // the pages must be sealed and wholly visible to the entry's query token
             const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
             const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
-            if (sealed / p.page_tokens < shared || qpos + 1u < shared * p.page_tokens) bad = 1;
-        }
-        const uint64_t cells = static_cast<uint64_t>(p.seq_count) * shared;
-        for (uint64_t i = tid; i < cells && !bad; i += kPlanThreads) {
-            const uint32_t s = static_cast<uint32_t>(i / shared), pg = static_cast<uint32_t>(i % shared);
-            if (p.page_table[static_cast<uint64_t>(slot_of(p, s)) * p.page_table_stride + pg] != row0[pg]) bad = 1;
+            if (sealed / p.page_tokens < shared || qpos + 1u < shared * p.page_tokens || prefix[s] != 0u) bad = 1;
         }
         if (__syncthreads_or(bad)) {
             shared = 0;
@@ -485,6 +492,7 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
 }  // namespace
 
 cudaError_t launch_plan(const AttentionParams &p, cudaStream_t stream) {
+    if (p.shared_prefix_pages) verify_prefix_kernel<<<p.seq_count, 256, 0, stream>>>(p);
     plan_kernel<<<1, kPlanThreads, 0, stream>>>(p);
     return cudaPeekAtLastError();
 }

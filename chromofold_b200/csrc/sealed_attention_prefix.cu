@@ -1,33 +1,37 @@
 // sealed_attention_prefix.cu — attention over a SHARED sealed prefix: pages that every sequence of the batch
 // references (one copy in the arena, the same page ids at the head of every page-table row; the reference's
 // shared-page semantics, src/multisequence_cache.cpp:235-292), on the 5th-generation tensor cores (tcgen05.mma with
-// shared-memory operands and accumulators in tensor memory). Geometry: head_dim 128, page_tokens 16, block 64.
+// accumulators and the A operands in tensor memory). Geometry: head_dim 128, page_tokens 16, block 64.
 //
 // The per-sequence kernel would decode such a page once per sequence. Here a page is decoded once per tile of 128
 // query rows (rows = sequence x query head of the kv head's group) and contracted with all those rows at once.
 //
-// One CTA (8 warps) owns a unit = (prefix chunk, kv head, row tile); units are handed out by an atomic counter.
-//   Q tile           128 rows x 128 channels binary16 in shared memory, loaded once per unit     (A of S = Q K^T)
-//   per round of 8 pages = 128 tokens:
-//     decode         warp w gets page round+w by one bulk async copy (mbarrier, bounded wait), decodes it with the
-//                    lane-per-block decoders and writes exact binary16 codes: K tile [token][channel] (B of S),
-//                    V tile [channel][token] (B of O = P V); the next round's copy is issued as soon as the warp
-//                    has decoded, so it lands while the tensor-core phase runs
-//     S              one thread issues 8 tcgen05.mma (M 128, N 128, K 16 each) into tensor-memory columns 0..127
-//     softmax        all 8 warps: a thread owns one row (= tensor-memory lane, in its warp's quarter) and half of the
-//                    round's 128 score columns, which it holds in registers after one tcgen05.ld; page K scales and
-//                    masks applied, the row's two threads share their maxima through shared memory, running max /
-//                    sum updated, O in tensor memory rescaled (tcgen05.ld / .st) only when some row of the warp
-//                    moved its max, P written to shared memory as binary16 (the P tile) plus its rounding residue
-//                    (into the K tile, free once S is complete): two A operands of P V
-//     O              16 tcgen05.mma accumulate P V into tensor-memory columns 128..255
-//   unit end         O read back, scaled, written with (max, sum) to the shared-prefix partials; the combine kernel
-//                    merges them with the per-sequence partials of the private pages and the tail
-// Operand tiles use the no-swizzle K-major canonical layout of the instruction: 8 rows x 16 bytes core matrices,
-// element (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
+// One CTA of 16 warps per SM works on units = (prefix chunk, kv head, row tile) handed out by an atomic counter, in
+// rounds of 8 pages = 128 tokens. The warps are specialised, and the two groups run one round apart:
+//   decoder warps 0..7   warp w receives page round+w by one bulk async copy (mbarrier, bounded wait), decodes it with
+//                        the lane-per-block decoders and writes exact binary16 codes into one of TWO tile pairs in
+//                        shared memory: K tile [token][channel] (B of S = Q K^T), V tile [channel][token] (B of
+//                        O = P V); then arrives on the pair's "full" barrier. A pair is reused when the tensor core's
+//                        commit for the round that read it has arrived on its "free" barrier.
+//   softmax warps 8..15  a thread owns one row (= tensor-memory lane, in its warp's quarter) and half of the round's
+//                        128 score columns. Thread 0 of the group issues the tensor-core work:
+//                          S     8 tcgen05.mma (M 128, N 128, K 16): Q from tensor memory x K tile -> columns 0..127
+//                          O    16 tcgen05.mma: P (binary16, then its rounding residue) from tensor memory x V tile
+//                                -> columns 128..255, then commits to the "O" barrier and the pair's "free" barrier
+//                        All threads: one tcgen05.ld of their 64 scores (kept in registers), page K scales and masks,
+//                        the row's two threads share their maxima through shared memory, running max / sum updated,
+//                        O rescaled in tensor memory (tcgen05.ld / .st) only when some row of the warp moved its max,
+//                        P and its residue written to tensor memory (tcgen05.st) as the next A operands.
+//                        Unit start: the Q rows go from global memory straight to tensor memory. Unit end: O read back,
+//                        scaled, written with (max, sum) to the shared-prefix partials; the combine kernel merges
+//                        them with the per-sequence partials of the private pages and the tail.
+// Tensor memory (512 columns): S 0..127, O 128..255, Q 256..319, P 320..383, P residue 384..447 (binary16 pairs per
+// column, row = lane). B tiles use the no-swizzle K-major canonical layout: 8 rows x 16 bytes core matrices, element
+// (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
 // The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
-// Every wait (copies, tensor-core commits) is bounded; on expiry the CTA raises CF_B200_DEVSTAT_WAIT_EXPIRED, stops
-// taking units and frees its tensor memory.
+// Every mbarrier wait is bounded. A thread whose wait ran out raises CF_B200_DEVSTAT_WAIT_EXPIRED, skips all later
+// waits and work, but keeps taking part in its group's barriers; those barriers OR-reduce the failure so that every
+// thread of a group leaves its loop at the same point; the CTA then frees its tensor memory.
 
 #include "lanes_decoders.cuh"
 
@@ -36,21 +40,25 @@ namespace {
 
 using namespace lanes;
 
-constexpr int kTcWarps = 8;
-constexpr int kTcThreads = kTcWarps * 32;
+constexpr int kDecodeWarps = 8;
+constexpr int kGroupThreads = 256;   // decoder group = softmax group = 8 warps
+constexpr int kTcThreads = 2 * kGroupThreads;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one operand tile: 128 rows x 128 binary16
 constexpr uint32_t kOffStages = kTableBytes;
-constexpr uint32_t kOffQ = (kOffStages + kTcWarps * kStageBytes + 127u) / 128u * 128u;
-constexpr uint32_t kOffK = kOffQ + kTileBytes;
-constexpr uint32_t kOffV = kOffK + kTileBytes;
-constexpr uint32_t kOffP = kOffV + kTileBytes;
-constexpr uint32_t kOffMeta = kOffP + kTileBytes;              // per page of the round: k scale, v scale, token count, -
-constexpr uint32_t kOffBars = kOffMeta + kTcWarps * 16;        // 8 copy barriers + S barrier + O barrier
-constexpr uint32_t kOffMisc = kOffBars + (kTcWarps + 2) * 8;   // tmem base, unit, abort flag
+constexpr uint32_t kOffTiles = (kOffStages + kDecodeWarps * kStageBytes + 127u) / 128u * 128u;   // K[0] V[0] K[1] V[1]
+constexpr uint32_t kOffMeta = kOffTiles + 4 * kTileBytes;      // [pair][page of the round]: k scale, v scale, token count, -
+constexpr uint32_t kOffRound = kOffMeta + 2 * kDecodeWarps * 16;   // [pair]: unit, flags, -, -
+constexpr uint32_t kOffBars = kOffRound + 2 * 16;              // 8 copy barriers, full[2], free[2], S, O
+constexpr uint32_t kOffMisc = kOffBars + 14 * 8;               // [0] tmem base, [4..5] the decoders' unit slots
 constexpr uint32_t kOffRowMax = kOffMisc + 32;                 // [2 column halves][128 rows]
 constexpr uint32_t kTcSmem = kOffRowMax + 2 * 128 * 4;
 static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
-constexpr uint32_t kTmemColumns = 256;                         // S: 0..127, O: 128..255
+constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColP = 320, kColPResidue = 384;
+constexpr uint32_t kStopUnit = 0xffffffffu;
+constexpr uint32_t kFirstRound = 1u, kLastRound = 2u;   // round flags
+constexpr uint32_t kDecoderBarrier = 1, kSoftmaxBarrier = 2;   // named barriers (0 is __syncthreads)
+constexpr int kDecoderRegs = 96, kSoftmaxRegs = 160;    // 256 * (96 + 160) = the SM's 64 K registers
 // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -68,15 +76,31 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t smem_address) {
     return static_cast<uint64_t>((smem_address >> 4) & 0x3fffu) | (static_cast<uint64_t>(128u >> 4) << 16) |
            (static_cast<uint64_t>(2048u >> 4) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+// D[tmem_d] (+)= A[tmem_a: 128 lanes x 8 columns of binary16 pairs] x B[shared-memory tile]^T, one K step of 16
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(kIdesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// Barrier over one group (whole warps) that also ORs a predicate: every thread of the group gets the same answer.
+__device__ __forceinline__ bool group_any(uint32_t barrier_id, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, %2, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(pred)), "r"(barrier_id), "r"(static_cast<uint32_t>(kGroupThreads))
+        : "memory");
+    return r != 0;
 }
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
@@ -185,78 +209,69 @@ __device__ __forceinline__ void zero_slot(uint8_t *k_tile, uint8_t *v_tile, uint
     }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(AttentionParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
+__device__ __forceinline__ void tmem_store8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]),
+                 "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// What both groups derive from a unit number.
+struct UnitShape {
+    uint32_t tile_index, head_local, chunk, kv_head, page_begin, page_end;
+};
+__device__ __forceinline__ UnitShape unit_shape(const AttentionParams &p, uint32_t unit, uint32_t row_tiles, uint32_t per_chunk,
+                                                uint32_t shared_pages) {
+    UnitShape u;
+    u.tile_index = unit % row_tiles;
+    u.head_local = (unit / row_tiles) % p.kv_head_span;
+    u.chunk = unit / (row_tiles * p.kv_head_span);
+    u.kv_head = p.kv_head_begin + u.head_local;
+    u.page_begin = u.chunk * per_chunk;
+    u.page_end = min(u.page_begin + per_chunk, shared_pages);
+    return u;
+}
+
+// ---- decoder group: warps 0..7 -----------------------------------------------------------------------------------
+__device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t warp, uint32_t lane,
+                                             uint32_t row_tiles, uint32_t unit_count) {
     const uint32_t *k_slot = reinterpret_cast<const uint32_t *>(smem);
     const uint32_t *v_slot = k_slot + 4096;
     const uint16_t *k_lut = reinterpret_cast<const uint16_t *>(v_slot + 4096);
     const uint16_t *v_lut = k_lut + 4096;
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint8_t *stage = smem + kOffStages + warp * kStageBytes;
-    uint8_t *q_tile = smem + kOffQ, *k_tile = smem + kOffK, *v_tile = smem + kOffV, *p_tile = smem + kOffP;
-    float *meta = reinterpret_cast<float *>(smem + kOffMeta);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
-    uint64_t *bar = bars + warp, *bar_s = bars + kTcWarps, *bar_o = bars + kTcWarps + 1;
-    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);   // [0] tmem base, [1] unit, [2] abort
-    float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
-
-    PlanHeader *hdr = plan_header(p);
-    const uint32_t shared_pages = hdr->shared_pages, chunks = hdr->shared_chunks, per_chunk = hdr->shared_pages_per_chunk;
-    if (shared_pages == 0 || chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
-
-    load_tables(smem, p, tid, kTcThreads);
-    if (lane == 0) mbar_init(bar, 1);
-    if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
-        misc[2] = 0u;
-    }
-    if (lane == 0) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncwarp();
-    if (warp == 0) {   // one whole warp allocates the CTA's tensor memory and frees it at the end
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&misc[0])), "r"(kTmemColumns));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = misc[0];
-    const uint32_t tmem_row = tmem + (((warp & 3u) * 32u) << 16);   // this warp's quarter of the 128 lanes
-    uint32_t copy_phase = 0, s_phase = 0, o_phase = 0;
-
-    const uint32_t G = p.group;
-    const uint32_t rows_total = p.seq_count * G;
-    const uint32_t row_tiles = (rows_total + 127u) / 128u;
-    const uint32_t unit_count = chunks * p.kv_head_span * row_tiles;
+    uint64_t *bar = bars + warp, *bar_full = bars + 8, *bar_free = bars + 10;
+    uint32_t *round_desc = reinterpret_cast<uint32_t *>(smem + kOffRound);
+    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);
+    const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
     const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
 
-    for (;;) {
-        __syncthreads();   // everyone has read the previous unit number; the previous unit's tiles are free
-        if (tid == 0) misc[1] = atomicAdd(&hdr->next_shared_unit, 1u);
-        __syncthreads();
-        const uint32_t unit = misc[1];
-        if (unit >= unit_count || misc[2]) break;
-        const uint32_t tile_index = unit % row_tiles;
-        const uint32_t head_local = (unit / row_tiles) % p.kv_head_span;
-        const uint32_t chunk = unit / (row_tiles * p.kv_head_span);
-        const uint32_t kv_head = p.kv_head_begin + head_local;
-        const uint32_t page_begin = chunk * per_chunk, page_end = min(page_begin + per_chunk, shared_pages);
-
-        // Q tile: row r of the tile = (sequence, head of the group); 16 chunks of 8 channels per row
-        for (uint32_t i = tid; i < 128u * 16u; i += kTcThreads) {
-            const uint32_t r = i >> 4, c = i & 15u, row = tile_index * 128u + r;
-            uint4 x = make_uint4(0u, 0u, 0u, 0u);
-            if (row < rows_total)
-                x = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.queries) +
-                                                     (static_cast<uint64_t>(row / G) * p.query_head_count + kv_head * G + row % G) * 128u + 8u * c);
-            *reinterpret_cast<uint4 *>(q_tile + tile_offset(r, c)) = x;
+    uint32_t copy_phase = 0, it = 0, fetched = 0;
+    bool failed = false;   // warp-uniform
+    // The pair `it & 1` is free once the tensor core has finished the round that used it last (round it - 2).
+    auto wait_pair_free = [&]() {
+        if (it >= 2u && !failed && !__all_sync(0xffffffffu, mbar_wait(&bar_free[it & 1u], ((it >> 1) - 1u) & 1u))) {
+            failed = true;
+            if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
-        float m_run = -CUDART_INF_F, l_run = 0.0f;   // the row's running maximum; this thread's half of its running sum
-        float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
-        bool o_started = false;
-
+    };
+    for (;;) {
+        if (warp == 0 && lane == 0) misc[4 + (fetched & 1u)] = atomicAdd(&hdr->next_shared_unit, 1u);
+        const bool give_up = group_any(kDecoderBarrier, failed);
+        const uint32_t unit = misc[4 + (fetched & 1u)];
+        ++fetched;
+        if (give_up || unit >= unit_count) {   // uniform over the group: tell the softmax group to stop
+            wait_pair_free();
+            if (lane == 0) {
+                if (warp == 0) round_desc[4 * (it & 1u)] = kStopUnit;
+                mbar_arrive(&bar_full[it & 1u]);
+            }
+            break;
+        }
+        const UnitShape u = unit_shape(p, unit, row_tiles, per_chunk, shared_pages);
         auto dir_entry = [&](uint32_t page) -> uint64_t {
-            return p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + kv_head];
+            return p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + u.kv_head];
         };
         auto entry_ok = [&](uint64_t entry) {
             const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
@@ -269,24 +284,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
                 bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
             }
         };
-        uint64_t entry = page_begin + warp < page_end ? dir_entry(page_begin + warp) : 0ull;
-        issue(entry);
+        uint64_t entry = u.page_begin + warp < u.page_end ? dir_entry(u.page_begin + warp) : 0ull;
+        if (!failed) issue(entry);
 
-        for (uint32_t round = page_begin; round < page_end; round += kTcWarps) {
-            // ---- decode: warp w takes page round + w into slot w of the tiles ----
+        for (uint32_t round = u.page_begin; round < u.page_end; round += kDecodeWarps, ++it) {
+            const uint32_t pair = it & 1u;
+            uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
+            float *meta = reinterpret_cast<float *>(smem + kOffMeta) + pair * 4u * kDecodeWarps;
             const uint32_t my_page = round + warp;
             // the next round's directory entry is fetched now (two dependent loads), needed only after this page's decode
-            const uint64_t next_entry = my_page + kTcWarps < page_end ? dir_entry(my_page + kTcWarps) : 0ull;
+            const uint64_t next_entry = my_page + kDecodeWarps < u.page_end ? dir_entry(my_page + kDecodeWarps) : 0ull;
+            wait_pair_free();
             float k_scale = 0.0f, v_scale = 0.0f;
             uint32_t token_count = 0;
-            if (my_page < page_end) {
+            if (my_page < u.page_end && !failed) {
                 if (!entry_ok(entry)) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
-                } else if (!mbar_wait(bar, copy_phase & 1u)) {
-                    if (lane == 0) {
-                        raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
-                        misc[2] = 1u;
-                    }
+                } else if (!__all_sync(0xffffffffu, mbar_wait(bar, copy_phase & 1u))) {
+                    failed = true;
+                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
                 } else {
                     copy_phase ^= 1u;
                     const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
@@ -330,175 +346,279 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
                 meta[4 * warp] = k_scale;
                 meta[4 * warp + 1] = v_scale;
                 meta[4 * warp + 2] = __uint_as_float(token_count);   // 0: the page contributes nothing
+                if (warp == 0) {
+                    round_desc[4 * pair] = unit;
+                    round_desc[4 * pair + 1] = (round == u.page_begin ? kFirstRound : 0u) |
+                                               (round + kDecodeWarps >= u.page_end ? kLastRound : 0u);
+                }
             }
             __syncwarp();   // every lane is done with the stage
             entry = next_entry;
-            if (my_page + kTcWarps < page_end) issue(entry);
+            if (my_page + kDecodeWarps < u.page_end && !failed) issue(entry);
             fence_async_smem();   // the tiles were written through the generic proxy; the tensor core reads through the async one
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_full[pair]);
+        }
+    }
+    // a copy whose wait ran out gets one more bounded chance to land before the CTA's shared memory is given back
+    if (failed) mbar_wait(bar, copy_phase & 1u);
+}
+
+// ---- softmax group: warps 8..15; its thread 0 also issues the tensor-core work ---------------------------------------
+__device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t tmem, uint32_t warp,
+                                             uint32_t lane, uint32_t row_tiles) {
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
+    uint64_t *bar_full = bars + 8, *bar_free = bars + 10, *bar_s = bars + 12, *bar_o = bars + 13;
+    const uint32_t *round_desc = reinterpret_cast<const uint32_t *>(smem + kOffRound);
+    float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
+    const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
+    const uint32_t G = p.group, rows_total = p.seq_count * G;
+    // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the 64 score
+    // columns (4 pages) of half (w - 8) >> 2; the two threads of a row meet through row_max[].
+    const uint32_t half = (warp - kDecodeWarps) >> 2, row_in_tile = (warp & 3u) * 32u + lane;
+    const uint32_t tmem_row = tmem + (((warp & 3u) * 32u) << 16);
+    const bool issuer = warp == kDecodeWarps && lane == 0;
+
+    uint32_t s_phase = 0, o_phase = 0;
+    bool failed = false;      // warp-uniform
+    bool o_pending = false;   // a P V commit whose arrival on the O barrier has not been waited for yet
+    auto wait_o = [&]() {     // O and P in tensor memory may be touched again once the last P V has completed
+        if (!o_pending) return;
+        o_pending = false;
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_o, o_phase & 1u))) {
+            failed = true;
+            if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+        }
+        o_phase ^= 1u;
+        tc_fence_after();
+    };
+    UnitShape u = {};
+    float m_run = -CUDART_INF_F, l_run = 0.0f;   // the row's running maximum; this thread's half of its running sum
+    float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
+    bool o_started = false;
+
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t pair = it & 1u;
+        uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
+        const float *meta = reinterpret_cast<const float *>(smem + kOffMeta) + pair * 4u * kDecodeWarps;
+        // ---- the round's tiles are decoded (one thread waits, the barrier passes the news on) ----
+        if (issuer && !failed && !mbar_wait(&bar_full[pair], (it >> 1) & 1u)) {
+            failed = true;
+            raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+        }
+        failed = __any_sync(0xffffffffu, failed);
+        if (group_any(kSoftmaxBarrier, failed)) break;
+        const uint32_t unit = round_desc[4 * pair], flags = round_desc[4 * pair + 1];
+        if (unit == kStopUnit) break;
+
+        if (flags & kFirstRound) {   // Q rows of the unit: global memory -> tensor memory (binary16 pairs, 64 columns)
+            u = unit_shape(p, unit, row_tiles, per_chunk, shared_pages);
+            m_run = -CUDART_INF_F;
+            l_run = 0.0f;
+            v_unit = 0.0f;
+            o_started = false;
+            const uint32_t row = u.tile_index * 128u + row_in_tile;
+            uint32_t q_raw[32];
+            if (row < rows_total) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(
+                    reinterpret_cast<const __half *>(p.queries) +
+                    (static_cast<uint64_t>(row / G) * p.query_head_count + u.kv_head * G + row % G) * 128u + 64u * half);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 x = src[c];
+                    q_raw[4 * c] = x.x;
+                    q_raw[4 * c + 1] = x.y;
+                    q_raw[4 * c + 2] = x.z;
+                    q_raw[4 * c + 3] = x.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) q_raw[j] = 0u;
+            }
+            tmem_store32(tmem_row + kColQ + 32u * half, q_raw);
+            tmem_store_wait();
             tc_fence_before();
-            __syncthreads();
-            if (misc[2]) break;   // uniform: a copy never arrived
-
-            // ---- S = Q K^T ----
-            if (tid == 0) {
-                tc_fence_after();
-#pragma unroll
-                for (uint32_t s = 0; s < 8; ++s)
-                    umma(tmem, tile_desc(smem_addr(q_tile) + 256u * s), tile_desc(smem_addr(k_tile) + 256u * s), s);
-                umma_commit(bar_s);
-            }
-
-            // ---- softmax: thread = (row, half of the round's columns) ----
-            const uint32_t in_round = min(static_cast<uint32_t>(kTcWarps), page_end - round);
-            if (v_unit == 0.0f)
-                for (uint32_t pg = 0; pg < in_round; ++pg)
-                    if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
-            const bool s_ready = __all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u));   // warp-uniform: warp-wide loads follow
-            s_phase ^= 1u;
-            if (!s_ready && lane == 0) {
-                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
-                misc[2] = 1u;
-            }
-            tc_fence_after();
-            // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the
-            // 64 score columns (4 pages) of half w >> 2; the two threads of a row meet through row_max[].
-            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
-            uint32_t s_raw[2][32];
-            if (s_ready) {
-                tmem_load32(tmem_row + 64u * half, s_raw[0]);
-                tmem_load32(tmem_row + 64u * half + 32u, s_raw[1]);
-                tmem_load_wait();
-            }
-            float part_max = -CUDART_INF_F;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {   // page 4 half + q: scale, mask, maximum — in place
-                const uint32_t pg = 4u * half + q;
-                const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
-                const float ks = meta[4 * pg];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    uint32_t &cell = s_raw[q >> 1][16 * (q & 1) + j];
-                    const float v = static_cast<uint32_t>(j) < count ? __uint_as_float(cell) * ks : -CUDART_INF_F;
-                    cell = __float_as_uint(v);
-                    part_max = fmaxf(part_max, v);
-                }
-            }
-            row_max[half * 128u + row_in_tile] = part_max;
-            __syncthreads();
-            if (s_ready) {
-                const float m_new = fmaxf(m_run, fmaxf(row_max[row_in_tile], row_max[128u + row_in_tile]));
-                const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
-                const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
-                m_run = m_new;
-                // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
-                if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
-#pragma unroll 1
-                    for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
-                        uint32_t o_raw[32];
-                        tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
-                        tmem_load_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
-                        tmem_store32(tmem_row + 128u + 64u * half + c0, o_raw);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                }
-                // weights as binary16 plus their rounding residue (two A operands: the P tile, and the K tile, which the
-                // tensor core is done with once the scores are complete), so that P V is accurate to fp32 level whatever
-                // the spread of the V scales
-                float sum = 0.0f;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t pg = 4u * half + q;
-                    const float ratio = __float_as_uint(meta[4 * pg + 2]) ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
-                    uint32_t hi[8], lo[8];
-#pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const float w0 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) - z);       // masked: exp2(-inf) = 0
-                        const float w1 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]) - z);
-                        sum += w0 + w1;
-                        const float a0 = w0 * ratio, a1 = w1 * ratio;
-                        const __half2 h = __floats2half2_rn(a0, a1);
-                        const float2 back = __half22float2(h);
-                        const __half2 l = __floats2half2_rn(a0 - back.x, a1 - back.y);
-                        hi[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
-                        lo[j >> 1] = *reinterpret_cast<const uint32_t *>(&l);
-                    }
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {   // 8 tokens = one 16-byte chunk of the row
-                        *reinterpret_cast<uint4 *>(p_tile + tile_offset(row_in_tile, 2u * pg + c)) =
-                            make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-                        *reinterpret_cast<uint4 *>(k_tile + tile_offset(row_in_tile, 2u * pg + c)) =
-                            make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-                    }
-                }
-                l_run = l_run * alpha + sum;   // this thread's half of the row's sum; the halves are added at the unit's end
-            }
-            fence_async_smem();
-            tc_fence_before();
-            __syncthreads();
-            if (misc[2]) break;
-
-            // ---- O += P V ----
-            if (tid == 0) {
-                tc_fence_after();
-#pragma unroll
-                for (uint32_t s = 0; s < 8; ++s)
-                    umma(tmem + 128u, tile_desc(smem_addr(p_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s),
-                         (o_started || s) ? 1u : 0u);
-#pragma unroll
-                for (uint32_t s = 0; s < 8; ++s)   // the residue of P, staged in the K tile
-                    umma(tmem + 128u, tile_desc(smem_addr(k_tile) + 256u * s), tile_desc(smem_addr(v_tile) + 256u * s), 1u);
-                umma_commit(bar_o);
-            }
-            o_started = true;
-            const bool o_ready = mbar_wait(bar_o, o_phase & 1u);   // the tiles are reused by the next round's decode
-            o_phase ^= 1u;
-            if (!o_ready && lane == 0) {
-                raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
-                misc[2] = 1u;
-            }
-            tc_fence_after();
+            if (group_any(kSoftmaxBarrier, false)) break;
         }
 
-        // ---- partials of the unit: one (max, sum, weighted[128]) per row; each thread writes its 64 channels ----
-        {
-            const uint32_t half = warp >> 2, row_in_tile = (warp & 3u) * 32u + lane;
-            const uint32_t row = tile_index * 128u + row_in_tile;
-            row_max[half * 128u + row_in_tile] = l_run;   // reused: the two halves of the row's sum
-            __syncthreads();
-            if (o_started && !misc[2]) {   // whole warps: the tensor-memory loads are warp-wide
-                const bool live = row < rows_total;
-                float *dst = live ? shared_partial_ptr(p, chunk, row / G, head_local * G + row % G) : nullptr;
-                if (live && half == 0) {
-                    dst[0] = m_run;
-                    dst[1] = row_max[row_in_tile] + row_max[128u + row_in_tile];
-                }
+        // ---- S = Q K^T ----
+        if (issuer) {
+            tc_fence_after();
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) umma(tmem + kColS, tmem + kColQ + 8u * s, tile_desc(smem_addr(k_tile) + 256u * s), s);
+            umma_commit(bar_s);
+        }
+        if (v_unit == 0.0f)
+            for (uint32_t pg = 0; pg < kDecodeWarps; ++pg)
+                if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u))) {
+            failed = true;
+            if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+        }
+        s_phase ^= 1u;
+        tc_fence_after();
+        uint32_t s_raw[2][32];
+        if (!failed) {
+            tmem_load32(tmem_row + kColS + 64u * half, s_raw[0]);
+            tmem_load32(tmem_row + kColS + 64u * half + 32u, s_raw[1]);
+            tmem_load_wait();
+        }
+        float part_max = -CUDART_INF_F;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {   // page 4 half + q: scale, mask, maximum — in place
+            const uint32_t pg = 4u * half + q;
+            const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
+            const float ks = meta[4 * pg];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                uint32_t &cell = s_raw[q >> 1][16 * (q & 1) + j];
+                const float v = static_cast<uint32_t>(j) < count ? __uint_as_float(cell) * ks : -CUDART_INF_F;
+                cell = __float_as_uint(v);
+                part_max = fmaxf(part_max, v);
+            }
+        }
+        row_max[half * 128u + row_in_tile] = part_max;
+        tc_fence_before();   // this thread's reads of S are complete: the next round's S may overwrite it
+        if (group_any(kSoftmaxBarrier, failed)) break;
+
+        wait_o();   // the previous round's P V is done with O and P
+        if (!failed) {
+            const float m_new = fmaxf(m_run, fmaxf(row_max[row_in_tile], row_max[128u + row_in_tile]));
+            const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
+            const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
+            m_run = m_new;
+            // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
+            if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
 #pragma unroll 1
                 for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
                     uint32_t o_raw[32];
-                    tmem_load32(tmem_row + 128u + 64u * half + c0, o_raw);
+                    tmem_load32(tmem_row + kColO + 64u * half + c0, o_raw);
                     tmem_load_wait();
-                    if (live) {
 #pragma unroll
-                        for (int t = 0; t < 8; ++t) {   // columns t, t + 8, t + 16, t + 24 of the 32 are 4 consecutive channels
-                            float *out = dst + 2 + 64u * half + c0 + 4 * t;
-                            *reinterpret_cast<float2 *>(out) =
-                                make_float2(__uint_as_float(o_raw[t]) * v_unit, __uint_as_float(o_raw[t + 8]) * v_unit);
-                            *reinterpret_cast<float2 *>(out + 2) =
-                                make_float2(__uint_as_float(o_raw[t + 16]) * v_unit, __uint_as_float(o_raw[t + 24]) * v_unit);
-                        }
+                    for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
+                    tmem_store32(tmem_row + kColO + 64u * half + c0, o_raw);
+                }
+            }
+            // weights as binary16 plus their rounding residue (two A operands), so that P V is accurate to fp32 level
+            // whatever the spread of the V scales
+            float sum = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t pg = 4u * half + q;
+                const float ratio = __float_as_uint(meta[4 * pg + 2]) ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
+                uint32_t hi[8], lo[8];
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float w0 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) - z);       // masked: exp2(-inf) = 0
+                    const float w1 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]) - z);
+                    sum += w0 + w1;
+                    const float a0 = w0 * ratio, a1 = w1 * ratio;
+                    const __half2 h = __floats2half2_rn(a0, a1);
+                    const float2 back = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(a0 - back.x, a1 - back.y);
+                    hi[j >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                    lo[j >> 1] = *reinterpret_cast<const uint32_t *>(&l);
+                }
+                tmem_store8(tmem_row + kColP + 8u * pg, hi);          // 16 tokens = 8 columns of pairs
+                tmem_store8(tmem_row + kColPResidue + 8u * pg, lo);
+            }
+            tmem_store_wait();
+            l_run = l_run * alpha + sum;   // this thread's half of the row's sum; the halves are added at the unit's end
+        }
+        tc_fence_before();
+        if (group_any(kSoftmaxBarrier, failed)) break;
+
+        // ---- O += P V ----
+        if (issuer) {
+            tc_fence_after();
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s)
+                umma(tmem + kColO, tmem + kColP + 8u * s, tile_desc(smem_addr(v_tile) + 256u * s), (o_started || s) ? 1u : 0u);
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) umma(tmem + kColO, tmem + kColPResidue + 8u * s, tile_desc(smem_addr(v_tile) + 256u * s), 1u);
+            umma_commit(bar_o);
+            umma_commit(&bar_free[pair]);   // the decoders may refill this pair of tiles
+        }
+        o_started = true;
+        o_pending = true;
+
+        // ---- last round of the unit: one (max, sum, weighted[128]) per row; each thread writes its 64 channels ----
+        if (flags & kLastRound) {
+            wait_o();
+            row_max[half * 128u + row_in_tile] = l_run;   // reused: the two halves of the row's sum
+            if (group_any(kSoftmaxBarrier, failed)) break;
+            const uint32_t row = u.tile_index * 128u + row_in_tile;
+            const bool live = row < rows_total;   // whole warps go on: the tensor-memory loads are warp-wide
+            float *dst = live ? shared_partial_ptr(p, u.chunk, row / G, u.head_local * G + row % G) : nullptr;
+            if (live && half == 0) {
+                dst[0] = m_run;
+                dst[1] = row_max[row_in_tile] + row_max[128u + row_in_tile];
+            }
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+                uint32_t o_raw[32];
+                tmem_load32(tmem_row + kColO + 64u * half + c0, o_raw);
+                tmem_load_wait();
+                if (live) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {   // columns t, t + 8, t + 16, t + 24 of the 32 are 4 consecutive channels
+                        float *out = dst + 2 + 64u * half + c0 + 4 * t;
+                        *reinterpret_cast<float2 *>(out) =
+                            make_float2(__uint_as_float(o_raw[t]) * v_unit, __uint_as_float(o_raw[t + 8]) * v_unit);
+                        *reinterpret_cast<float2 *>(out + 2) =
+                            make_float2(__uint_as_float(o_raw[t + 16]) * v_unit, __uint_as_float(o_raw[t + 24]) * v_unit);
                     }
                 }
             }
+            tc_fence_before();
         }
-        tc_fence_before();
     }
-    // teardown: a copy whose wait ran out gets one more bounded chance to land; tensor memory is returned
-    if (misc[2]) mbar_wait(bar, copy_phase & 1u);
+    // leaving early: give the tensor core's last commit a bounded chance to arrive before tensor memory is freed
+    if (o_pending && !failed) mbar_wait(bar_o, o_phase & 1u);
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(AttentionParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
+    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);
+
+    PlanHeader *hdr = plan_header(p);
+    if (hdr->shared_pages == 0 || hdr->shared_chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
+
+    load_tables(smem, p, tid, kTcThreads);
+    if (tid == 0) {
+        for (uint32_t w = 0; w < 8; ++w) mbar_init(bars + w, 1);   // copies
+        mbar_init(bars + 8, kDecodeWarps);                          // full[0], full[1]: one arrival per decoder warp
+        mbar_init(bars + 9, kDecodeWarps);
+        for (uint32_t i = 10; i < 14; ++i) mbar_init(bars + i, 1);  // free[0], free[1], S, O: tensor-core commits
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 0) {   // one whole warp allocates the CTA's tensor memory and frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&misc[0])), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
     tc_fence_before();
     __syncthreads();
-    if (tid < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns));
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+
+    const uint32_t rows_total = p.seq_count * p.group;
+    const uint32_t row_tiles = (rows_total + 127u) / 128u;
+    const uint32_t unit_count = hdr->shared_chunks * p.kv_head_span * row_tiles;
+
+    if (warp < kDecodeWarps) {   // whole warpgroups on either side: the register split is per warpgroup
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDecoderRegs));
+        decoder_role(p, smem, hdr, warp, lane, row_tiles, unit_count);
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+        softmax_role(p, smem, hdr, tmem, warp, lane, row_tiles);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns));
 }
 
 }  // namespace
