@@ -6,14 +6,18 @@
 // The per-sequence kernel would decode such a page once per sequence. Here a page is decoded once per tile of 128
 // query rows (rows = sequence x query head of the kv head's group) and contracted with all those rows at once.
 //
-// One CTA of 16 warps per SM works on units = (prefix chunk, kv head, row tile) handed out by an atomic counter, in
-// rounds of 8 pages = 128 tokens. The warps are specialised, and the two groups run one round apart:
-//   decoder warps 0..7   warp w receives page round+w by one bulk async copy (mbarrier, bounded wait), decodes it with
-//                        the lane-per-block decoders and writes exact binary16 codes into one of TWO tile pairs in
-//                        shared memory: K tile [token][channel] (B of S = Q K^T), V tile [channel][token] (B of
-//                        O = P V); then arrives on the pair's "full" barrier. A pair is reused when the tensor core's
-//                        commit for the round that read it has arrived on its "free" barrier.
-//   softmax warps 8..15  a thread owns one row (= tensor-memory lane, in its warp's quarter) and half of the round's
+// One CTA of 20 warps per SM works on units = (prefix chunk, kv head, row tile): CTA b takes units b, b + grid, ...
+// (equal-sized, so a static split balances), in rounds of 8 pages = 128 tokens. The warps are specialised:
+//   decoder warps 0..11  the page slots of the CTA's units form one sequence; warp w takes slots w, w + 12, ... It
+//                        receives the record by one bulk async copy (mbarrier, bounded wait), decodes it with the
+//                        lane-per-block decoders INTO REGISTERS (32 packed quads per lane), starts the copy of its next
+//                        record, and only then waits for the tile pair of the slot's round to be free; the symbols
+//                        are written as exact binary16 codes into one of TWO tile pairs in shared memory: K tile
+//                        [token][channel] (B of S = Q K^T), V tile [channel][token] (B of O = P V); then the warp
+//                        arrives on the pair's "full" barrier (8 arrivals = one round). A pair is free when the tensor
+//                        core's commit for the round that read it has arrived on its "free" barrier. Twelve warps keep
+//                        decoding while the other group works on the previous round.
+//   softmax warps 12..19 a thread owns one row (= tensor-memory lane, in its warp's quarter) and half of the round's
 //                        128 score columns. Thread 0 of the group issues the tensor-core work:
 //                          S     8 tcgen05.mma (M 128, N 128, K 16): Q from tensor memory x K tile -> columns 0..127
 //                          O    16 tcgen05.mma: P (binary16, then its rounding residue) from tensor memory x V tile
@@ -25,13 +29,15 @@
 //                        Unit start: the Q rows go from global memory straight to tensor memory. Unit end: O read back,
 //                        scaled, written with (max, sum) to the shared-prefix partials; the combine kernel merges
 //                        them with the per-sequence partials of the private pages and the tail.
+// Registers: the kernel starts at 96 per thread; the decoders drop to 80 and the softmax warps rise to 120 (setmaxnreg).
 // Tensor memory (512 columns): S 0..127, O 128..255, Q 256..319, P 320..383, P residue 384..447 (binary16 pairs per
 // column, row = lane). B tiles use the no-swizzle K-major canonical layout: 8 rows x 16 bytes core matrices, element
 // (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
 // The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
-// Every mbarrier wait is bounded. A thread whose wait ran out raises CF_B200_DEVSTAT_WAIT_EXPIRED, skips all later
-// waits and work, but keeps taking part in its group's barriers; those barriers OR-reduce the failure so that every
-// thread of a group leaves its loop at the same point; the CTA then frees its tensor memory.
+// Every mbarrier wait is bounded. A warp whose wait ran out raises CF_B200_DEVSTAT_WAIT_EXPIRED and skips all later
+// waits and work; a decoder warp still arrives for each of its slots, a softmax warp still takes part in its group's
+// barriers, which OR-reduce the failure so that the whole group leaves its loop at the same point; the CTA then frees
+// its tensor memory.
 
 #include "lanes_decoders.cuh"
 
@@ -40,16 +46,19 @@ namespace {
 
 using namespace lanes;
 
-constexpr int kDecodeWarps = 8;
-constexpr int kGroupThreads = 256;   // decoder group = softmax group = 8 warps
-constexpr int kTcThreads = 2 * kGroupThreads;
+constexpr int kDecodeWarps = 12;     // warps 0..11 (three warpgroups)
+constexpr int kSoftmaxWarps = 8;     // warps 12..19 (two warpgroups)
+constexpr int kRoundPages = 8;
+constexpr int kGroupThreads = kSoftmaxWarps * 32;
+constexpr int kTcThreads = (kDecodeWarps + kSoftmaxWarps) * 32;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one operand tile: 128 rows x 128 binary16
 constexpr uint32_t kOffStages = kTableBytes;
 constexpr uint32_t kOffTiles = (kOffStages + kDecodeWarps * kStageBytes + 127u) / 128u * 128u;   // K[0] V[0] K[1] V[1]
 constexpr uint32_t kOffMeta = kOffTiles + 4 * kTileBytes;      // [pair][page of the round]: k scale, v scale, token count, -
-constexpr uint32_t kOffRound = kOffMeta + 2 * kDecodeWarps * 16;   // [pair]: unit, flags, -, -
-constexpr uint32_t kOffBars = kOffRound + 2 * 16;              // 8 copy barriers, full[2], free[2], S, O
-constexpr uint32_t kOffMisc = kOffBars + 14 * 8;               // [0] tmem base, [4..5] the decoders' unit slots
+constexpr uint32_t kOffRound = kOffMeta + 2 * kRoundPages * 16;    // [pair]: unit, flags, -, -
+constexpr uint32_t kOffBars = kOffRound + 2 * 16;              // 12 copy barriers, full[2], free[2], S, O
+constexpr uint32_t kBarFull = kDecodeWarps, kBarFree = kBarFull + 2, kBarS = kBarFree + 2, kBarO = kBarS + 1, kBarCount = kBarO + 1;
+constexpr uint32_t kOffMisc = kOffBars + kBarCount * 8;        // [0] tmem base
 constexpr uint32_t kOffRowMax = kOffMisc + 32;                 // [2 column halves][128 rows]
 constexpr uint32_t kTcSmem = kOffRowMax + 2 * 128 * 4;
 static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
@@ -57,8 +66,14 @@ constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColP = 320, kColPResidue = 384;
 constexpr uint32_t kStopUnit = 0xffffffffu;
 constexpr uint32_t kFirstRound = 1u, kLastRound = 2u;   // round flags
-constexpr uint32_t kDecoderBarrier = 1, kSoftmaxBarrier = 2;   // named barriers (0 is __syncthreads)
-constexpr int kDecoderRegs = 96, kSoftmaxRegs = 160;    // 256 * (96 + 160) = the SM's 64 K registers
+constexpr uint32_t kSoftmaxBarrier = 1;   // named barrier (0 is __syncthreads)
+// Register split (setmaxnreg). A CTA can only redistribute the registers it was launched with: kLaunchRegs per thread,
+// the most that 640 threads can have. What the softmax warps ask for must not exceed what the decoders give back, or
+// the request would wait forever; the launch function checks kLaunchRegs against the compiled kernel.
+constexpr int kLaunchRegs = 96, kDecoderRegs = 80, kSoftmaxRegs = 120;
+static_assert(kLaunchRegs * kTcThreads <= 65536 && kDecoderRegs % 8 == 0 && kSoftmaxRegs % 8 == 0 &&
+                  kDecodeWarps * 32 * kDecoderRegs + kSoftmaxWarps * 32 * kSoftmaxRegs <= kLaunchRegs * kTcThreads,
+              "the register split must fit the CTA's own registers");
 // instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, N = 128, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -137,63 +152,47 @@ __device__ __forceinline__ uint4 codes8(uint32_t qa, uint32_t qb) {
     return r;
 }
 
-// Decode one record into the round's tiles. K quad q of lane l = token l/2, channels 64(l&1)+4q..+3 -> K tile row
-// 16*slot + l/2; V quad q of lane l = channel 4l + q/4, tokens 4(q%4)..+3 -> V tile row = channel, token chunk 2*slot(+1).
+// Decode one record into registers: quad q of a stream = symbols 4q..4q+3 of the block this lane decodes.
 template <class KLane, class VLane>
-__device__ __forceinline__ void decode_to_tiles(KLane &k, VLane &v, uint8_t *k_tile, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
-    const uint32_t k_row = 16u * slot + (lane >> 1);
+__device__ __forceinline__ void decode_page(KLane &k, VLane &v, uint32_t (&kq)[16], uint32_t (&vq)[16]) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {   // c = channel of the lane's V block, and a quarter of its K block
-        uint32_t kq[4], vq[4];
+    for (int q = 0; q < 16; ++q) {
+        if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
+            kq[q] = k.quad();
+            vq[q] = v.quad();
+        } else {   // both entropy coded: the two chains interleave symbol by symbol
+            k.reload();
+            v.reload();
+            uint32_t ke[4], ve[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
-                kq[j] = k.quad();
-                vq[j] = v.quad();
-            } else {
-                k.reload();
-                v.reload();
-                uint32_t ke[4], ve[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    ke[i] = k.symbol();
-                    ve[i] = v.symbol();
-                }
-                kq[j] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
-                vq[j] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
+            for (int i = 0; i < 4; ++i) {
+                ke[i] = k.symbol();
+                ve[i] = v.symbol();
             }
+            kq[q] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+            vq[q] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
         }
-        const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
-        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
-        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
-        const uint32_t v_row = v_tile_row(lane, c);
-        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
-        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
     }
 }
-template <class KLane>
-__device__ __forceinline__ void decode_k_to_tiles(KLane &k, uint8_t *k_tile, uint32_t slot, uint32_t lane) {
+template <class Lane>
+__device__ __forceinline__ void decode_stream(Lane &s, uint32_t (&quads)[16]) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) quads[q] = s.quad();
+}
+// The decoded page goes into slot `slot` of the round's tiles as exact binary16 codes. K quad q of lane l = token l/2,
+// channels 64(l&1)+4q..+3 -> K tile row 16*slot + l/2; V quad q of lane l = channel 4l + q/4, tokens 4(q%4)..+3 -> V tile
+// row v_tile_row(l, q/4), token chunks 2*slot and 2*slot+1.
+__device__ __forceinline__ void store_tiles(const uint32_t (&kq)[16], const uint32_t (&vq)[16], uint8_t *k_tile, uint8_t *v_tile,
+                                            uint32_t slot, uint32_t lane) {
     const uint32_t k_row = 16u * slot + (lane >> 1);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        uint32_t kq[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) kq[j] = k.quad();
         const uint32_t k_chunk = 8u * (lane & 1u) + 2u * c;
-        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[0], kq[1]);
-        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[2], kq[3]);
-    }
-}
-template <class VLane>
-__device__ __forceinline__ void decode_v_to_tiles(VLane &v, uint8_t *v_tile, uint32_t slot, uint32_t lane) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        uint32_t vq[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) vq[j] = v.quad();
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk)) = codes8(kq[4 * c], kq[4 * c + 1]);
+        *reinterpret_cast<uint4 *>(k_tile + tile_offset(k_row, k_chunk + 1u)) = codes8(kq[4 * c + 2], kq[4 * c + 3]);
         const uint32_t v_row = v_tile_row(lane, c);
-        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[0], vq[1]);
-        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[2], vq[3]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot)) = codes8(vq[4 * c], vq[4 * c + 1]);
+        *reinterpret_cast<uint4 *>(v_tile + tile_offset(v_row, 2u * slot + 1u)) = codes8(vq[4 * c + 2], vq[4 * c + 3]);
     }
 }
 // A page that is absent (past the chunk's end, or refused) leaves zeros in its slot of both tiles.
@@ -214,6 +213,12 @@ __device__ __forceinline__ void tmem_store8(uint32_t taddr, const uint32_t (&v)[
                  "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
                  : "memory");
 }
+// 2^x by the special-function unit (inputs below -126 give 0, -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // What both groups derive from a unit number.
@@ -232,7 +237,15 @@ __device__ __forceinline__ UnitShape unit_shape(const AttentionParams &p, uint32
     return u;
 }
 
-// ---- decoder group: warps 0..7 -----------------------------------------------------------------------------------
+// ---- decoder group: warps 0..11 -----------------------------------------------------------------------------------
+// The CTA's units are blockIdx.x, blockIdx.x + gridDim.x, ... Their page slots (pages of a unit padded to whole rounds of
+// eight) form one sequence; decoder warp w takes slots w, w + 12, w + 24, ... A slot is decoded into registers first;
+// only then does the warp wait for the tile pair of the slot's round, so that decoding never waits for the tensor core.
+struct SlotCursor {
+    uint32_t unit, valid, first_slot, first_round, slots;   // of the unit that holds the slot
+    UnitShape u;
+};
+
 __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t warp, uint32_t lane,
                                              uint32_t row_tiles, uint32_t unit_count) {
     const uint32_t *k_slot = reinterpret_cast<const uint32_t *>(smem);
@@ -241,140 +254,167 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
     const uint16_t *v_lut = k_lut + 4096;
     uint8_t *stage = smem + kOffStages + warp * kStageBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
-    uint64_t *bar = bars + warp, *bar_full = bars + 8, *bar_free = bars + 10;
+    uint64_t *bar = bars + warp, *bar_full = bars + kBarFull, *bar_free = bars + kBarFree;
     uint32_t *round_desc = reinterpret_cast<uint32_t *>(smem + kOffRound);
-    uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
     const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
 
-    uint32_t copy_phase = 0, it = 0, fetched = 0;
-    bool failed = false;   // warp-uniform
-    // The pair `it & 1` is free once the tensor core has finished the round that used it last (round it - 2).
-    auto wait_pair_free = [&]() {
+    auto load_unit = [&](SlotCursor &c) {
+        c.valid = c.unit < unit_count;
+        if (c.valid) {
+            c.u = unit_shape(p, c.unit, row_tiles, per_chunk, shared_pages);
+            c.slots = (c.u.page_end - c.u.page_begin + 7u) / 8u * 8u;
+        }
+    };
+    auto seek = [&](SlotCursor &c, uint32_t n) {   // the unit that holds slot n (n only grows)
+        while (c.valid && n >= c.first_slot + c.slots) {
+            c.first_slot += c.slots;
+            c.first_round += c.slots / 8u;
+            c.unit += gridDim.x;
+            load_unit(c);
+        }
+    };
+    // directory entry of slot n, 0 if the slot is padding or past the CTA's last unit
+    auto slot_entry = [&](const SlotCursor &c, uint32_t n) -> uint64_t {
+        if (!c.valid) return 0ull;
+        const uint32_t page = c.u.page_begin + (n - c.first_slot);
+        return page < c.u.page_end ? p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + c.u.kv_head] : 0ull;
+    };
+    auto entry_ok = [&](uint64_t entry) {
+        const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
+        return units16 != 0 && units16 * 16u <= kStageBytes - 32u;
+    };
+    auto issue = [&](uint64_t entry) {
+        if (lane == 0 && entry_ok(entry)) {
+            const uint32_t bytes = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry)) * 16u;
+            mbar_expect_tx(bar, bytes);
+            bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
+        }
+    };
+    uint32_t copy_phase = 0;
+    bool failed = false;   // warp-uniform; once set, the warp waits for nothing and decodes nothing, but keeps arriving
+    // The pair of round `it` is free once the tensor core has finished round it - 2. The parity wait is sound because a
+    // warp's slots are 12 apart, less than two rounds: it has always seen the completion before the one it waits for.
+    auto wait_pair_free = [&](uint32_t it) {
         if (it >= 2u && !failed && !__all_sync(0xffffffffu, mbar_wait(&bar_free[it & 1u], ((it >> 1) - 1u) & 1u))) {
             failed = true;
             if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
     };
-    for (;;) {
-        if (warp == 0 && lane == 0) misc[4 + (fetched & 1u)] = atomicAdd(&hdr->next_shared_unit, 1u);
-        const bool give_up = group_any(kDecoderBarrier, failed);
-        const uint32_t unit = misc[4 + (fetched & 1u)];
-        ++fetched;
-        if (give_up || unit >= unit_count) {   // uniform over the group: tell the softmax group to stop
-            wait_pair_free();
-            if (lane == 0) {
-                if (warp == 0) round_desc[4 * (it & 1u)] = kStopUnit;
-                mbar_arrive(&bar_full[it & 1u]);
+
+    SlotCursor cur;
+    cur.unit = blockIdx.x;
+    cur.first_slot = 0;
+    cur.first_round = 0;
+    cur.slots = 0;
+    load_unit(cur);
+    uint32_t n = warp;
+    seek(cur, n);
+    uint64_t entry = slot_entry(cur, n);
+    issue(entry);
+
+    for (;; n += kDecodeWarps) {
+        if (!cur.valid) {   // past the last unit: the eight slots after it make the round that tells the softmax group to stop
+            if (n < cur.first_slot + 8u) {
+                wait_pair_free(cur.first_round);
+                if (lane == 0) {
+                    if (n == cur.first_slot) round_desc[4 * (cur.first_round & 1u)] = kStopUnit;
+                    mbar_arrive(&bar_full[cur.first_round & 1u]);
+                }
             }
             break;
         }
-        const UnitShape u = unit_shape(p, unit, row_tiles, per_chunk, shared_pages);
-        auto dir_entry = [&](uint32_t page) -> uint64_t {
-            return p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + u.kv_head];
-        };
-        auto entry_ok = [&](uint64_t entry) {
-            const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
-            return units16 != 0 && units16 * 16u <= kStageBytes - 32u;
-        };
-        auto issue = [&](uint64_t entry) {
-            if (lane == 0 && entry_ok(entry)) {
-                const uint32_t bytes = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry)) * 16u;
-                mbar_expect_tx(bar, bytes);
-                bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
-            }
-        };
-        uint64_t entry = u.page_begin + warp < u.page_end ? dir_entry(u.page_begin + warp) : 0ull;
-        if (!failed) issue(entry);
+        const uint32_t in_unit = n - cur.first_slot, slot = in_unit & 7u, it = cur.first_round + (in_unit >> 3), pair = it & 1u;
+        // the warp's next slot: its directory entry is fetched now (dependent loads), needed only after this decode
+        SlotCursor next = cur;
+        seek(next, n + kDecodeWarps);
+        const uint64_t next_entry = slot_entry(next, n + kDecodeWarps);
 
-        for (uint32_t round = u.page_begin; round < u.page_end; round += kDecodeWarps, ++it) {
-            const uint32_t pair = it & 1u;
-            uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
-            float *meta = reinterpret_cast<float *>(smem + kOffMeta) + pair * 4u * kDecodeWarps;
-            const uint32_t my_page = round + warp;
-            // the next round's directory entry is fetched now (two dependent loads), needed only after this page's decode
-            const uint64_t next_entry = my_page + kDecodeWarps < u.page_end ? dir_entry(my_page + kDecodeWarps) : 0ull;
-            wait_pair_free();
-            float k_scale = 0.0f, v_scale = 0.0f;
-            uint32_t token_count = 0;
-            if (my_page < u.page_end && !failed) {
-                if (!entry_ok(entry)) {
+        float k_scale = 0.0f, v_scale = 0.0f;
+        uint32_t token_count = 0;
+        uint32_t kq[16], vq[16];
+        if (cur.u.page_begin + in_unit < cur.u.page_end && !failed) {
+            if (!entry_ok(entry)) {
+                if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+            } else if (!__all_sync(0xffffffffu, mbar_wait(bar, copy_phase & 1u))) {
+                failed = true;
+                if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
+            } else {
+                copy_phase ^= 1u;
+                const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
+                if (!record_header_ok(hv, entry, p.codebook_id)) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
-                } else if (!__all_sync(0xffffffffu, mbar_wait(bar, copy_phase & 1u))) {
-                    failed = true;
-                    if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
                 } else {
-                    copy_phase ^= 1u;
-                    const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
-                    if (!record_header_ok(hv, entry, p.codebook_id)) {
-                        if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                    const uint32_t k_units = hv.x & 0xffffu;
+                    const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu;
+                    const uint8_t *k_part = stage + 16, *v_part = k_part + 16u * k_units;
+                    token_count = hv.y >> 16;
+                    k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) * (p.softmax_scale * kLog2e);
+                    v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
+                    if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
+                        RansLane k, v;
+                        k.open(k_part, lane, k_slot);
+                        v.open(v_part, lane, v_slot);
+                        decode_page(k, v, kq, vq);
+                    } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
+                        HuffLane k, v;
+                        k.open(k_part, lane, k_lut);
+                        v.open(v_part, lane, v_lut);
+                        decode_page(k, v, kq, vq);
+                    } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
+                        FixedLane k, v;
+                        k.open(k_part, lane);
+                        v.open(v_part, lane);
+                        decode_page(k, v, kq, vq);
                     } else {
-                        const uint32_t k_units = hv.x & 0xffffu;
-                        const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu;
-                        const uint8_t *k_part = stage + 16, *v_part = k_part + 16u * k_units;
-                        token_count = hv.y >> 16;
-                        k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) * (p.softmax_scale * kLog2e);
-                        v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
-                        if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
-                            RansLane k, v;
-                            k.open(k_part, lane, k_slot);
-                            v.open(v_part, lane, v_slot);
-                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
-                        } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
-                            HuffLane k, v;
-                            k.open(k_part, lane, k_lut);
-                            v.open(v_part, lane, v_lut);
-                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
-                        } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
-                            FixedLane k, v;
-                            k.open(k_part, lane);
-                            v.open(v_part, lane);
-                            decode_to_tiles(k, v, k_tile, v_tile, warp, lane);
-                        } else {
-                            if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_to_tiles(k, k_tile, warp, lane); }
-                            else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_to_tiles(k, k_tile, warp, lane); }
-                            else { FixedLane k; k.open(k_part, lane); decode_k_to_tiles(k, k_tile, warp, lane); }
-                            if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_to_tiles(v, v_tile, warp, lane); }
-                            else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_to_tiles(v, v_tile, warp, lane); }
-                            else { FixedLane v; v.open(v_part, lane); decode_v_to_tiles(v, v_tile, warp, lane); }
-                        }
+                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_stream(k, kq); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_stream(k, kq); }
+                        else { FixedLane k; k.open(k_part, lane); decode_stream(k, kq); }
+                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_stream(v, vq); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_stream(v, vq); }
+                        else { FixedLane v; v.open(v_part, lane); decode_stream(v, vq); }
                     }
                 }
             }
-            if (token_count == 0u) zero_slot(k_tile, v_tile, warp, lane);
-            if (lane == 0) {
-                meta[4 * warp] = k_scale;
-                meta[4 * warp + 1] = v_scale;
-                meta[4 * warp + 2] = __uint_as_float(token_count);   // 0: the page contributes nothing
-                if (warp == 0) {
-                    round_desc[4 * pair] = unit;
-                    round_desc[4 * pair + 1] = (round == u.page_begin ? kFirstRound : 0u) |
-                                               (round + kDecodeWarps >= u.page_end ? kLastRound : 0u);
-                }
-            }
-            __syncwarp();   // every lane is done with the stage
-            entry = next_entry;
-            if (my_page + kDecodeWarps < u.page_end && !failed) issue(entry);
-            fence_async_smem();   // the tiles were written through the generic proxy; the tensor core reads through the async one
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_full[pair]);
         }
+        __syncwarp();   // every lane is done with the stage: the next record may land in it
+        if (!failed) issue(next_entry);
+
+        wait_pair_free(it);
+        uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
+        if (token_count != 0u) store_tiles(kq, vq, k_tile, v_tile, slot, lane);
+        else zero_slot(k_tile, v_tile, slot, lane);
+        if (lane == 0) {
+            float *meta = reinterpret_cast<float *>(smem + kOffMeta) + pair * 32u + 4u * slot;
+            meta[0] = k_scale;
+            meta[1] = v_scale;
+            meta[2] = __uint_as_float(token_count);   // 0: the page contributes nothing
+            if (slot == 0) {
+                round_desc[4 * pair] = cur.unit;
+                round_desc[4 * pair + 1] = (in_unit < 8u ? kFirstRound : 0u) | (in_unit + 8u >= cur.slots ? kLastRound : 0u);
+            }
+        }
+        fence_async_smem();   // the tiles were written through the generic proxy; the tensor core reads through the async one
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_full[pair]);
+        cur = next;
+        entry = next_entry;
     }
     // a copy whose wait ran out gets one more bounded chance to land before the CTA's shared memory is given back
     if (failed) mbar_wait(bar, copy_phase & 1u);
 }
 
-// ---- softmax group: warps 8..15; its thread 0 also issues the tensor-core work ---------------------------------------
+// ---- softmax group: warps 12..19; its thread 0 also issues the tensor-core work ---------------------------------------
 __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t tmem, uint32_t warp,
                                              uint32_t lane, uint32_t row_tiles) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
-    uint64_t *bar_full = bars + 8, *bar_free = bars + 10, *bar_s = bars + 12, *bar_o = bars + 13;
+    uint64_t *bar_full = bars + kBarFull, *bar_free = bars + kBarFree, *bar_s = bars + kBarS, *bar_o = bars + kBarO;
     const uint32_t *round_desc = reinterpret_cast<const uint32_t *>(smem + kOffRound);
     float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
     const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
     const uint32_t G = p.group, rows_total = p.seq_count * G;
     // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the 64 score
-    // columns (4 pages) of half (w - 8) >> 2; the two threads of a row meet through row_max[].
+    // columns (4 pages) of half (w - 12) >> 2; the two threads of a row meet through row_max[].
     const uint32_t half = (warp - kDecodeWarps) >> 2, row_in_tile = (warp & 3u) * 32u + lane;
     const uint32_t tmem_row = tmem + (((warp & 3u) * 32u) << 16);
     const bool issuer = warp == kDecodeWarps && lane == 0;
@@ -400,7 +440,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
     for (uint32_t it = 0;; ++it) {
         const uint32_t pair = it & 1u;
         uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
-        const float *meta = reinterpret_cast<const float *>(smem + kOffMeta) + pair * 4u * kDecodeWarps;
+        const float *meta = reinterpret_cast<const float *>(smem + kOffMeta) + pair * 4u * kRoundPages;
         // ---- the round's tiles are decoded (one thread waits, the barrier passes the news on) ----
         if (issuer && !failed && !mbar_wait(&bar_full[pair], (it >> 1) & 1u)) {
             failed = true;
@@ -449,7 +489,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             umma_commit(bar_s);
         }
         if (v_unit == 0.0f)
-            for (uint32_t pg = 0; pg < kDecodeWarps; ++pg)
+            for (uint32_t pg = 0; pg < kRoundPages; ++pg)
                 if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
         if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u))) {
             failed = true;
@@ -463,18 +503,26 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             tmem_load32(tmem_row + kColS + 64u * half + 32u, s_raw[1]);
             tmem_load_wait();
         }
+        // maximum of the scaled, masked scores of this thread's 4 pages; the raw scores stay in the registers
         float part_max = -CUDART_INF_F;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {   // page 4 half + q: scale, mask, maximum — in place
+        for (int q = 0; q < 4; ++q) {
             const uint32_t pg = 4u * half + q;
             const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
             const float ks = meta[4 * pg];
+            if (count == 16u) {   // a full page (the usual case): the scale is applied to the extreme, not to every score
+                float hi = __uint_as_float(s_raw[q >> 1][16 * (q & 1)]), lo = hi;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                uint32_t &cell = s_raw[q >> 1][16 * (q & 1) + j];
-                const float v = static_cast<uint32_t>(j) < count ? __uint_as_float(cell) * ks : -CUDART_INF_F;
-                cell = __float_as_uint(v);
-                part_max = fmaxf(part_max, v);
+                for (int j = 1; j < 16; ++j) {
+                    hi = fmaxf(hi, __uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]));
+                    lo = fminf(lo, __uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]));
+                }
+                part_max = fmaxf(part_max, fmaxf(hi * ks, lo * ks));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (static_cast<uint32_t>(j) < count)
+                        part_max = fmaxf(part_max, __uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) * ks);
             }
         }
         row_max[half * 128u + row_in_tile] = part_max;
@@ -485,7 +533,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
         if (!failed) {
             const float m_new = fmaxf(m_run, fmaxf(row_max[row_in_tile], row_max[128u + row_in_tile]));
             const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
-            const float alpha = exp2f(m_run - z);   // m_run = -inf gives 0
+            const float alpha = fast_exp2(m_run - z);   // m_run = -inf gives 0
             m_run = m_new;
             // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
             if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
@@ -505,12 +553,18 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t pg = 4u * half + q;
-                const float ratio = __float_as_uint(meta[4 * pg + 2]) ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
+                const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
+                const float ks = meta[4 * pg];
+                const float ratio = count ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
                 uint32_t hi[8], lo[8];
 #pragma unroll
                 for (int j = 0; j < 16; j += 2) {
-                    const float w0 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]) - z);       // masked: exp2(-inf) = 0
-                    const float w1 = exp2f(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]) - z);
+                    float w0 = fast_exp2(fmaf(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j]), ks, -z));
+                    float w1 = fast_exp2(fmaf(__uint_as_float(s_raw[q >> 1][16 * (q & 1) + j + 1]), ks, -z));
+                    if (count != 16u) {   // tokens past the page's count weigh nothing
+                        w0 = static_cast<uint32_t>(j) < count ? w0 : 0.0f;
+                        w1 = static_cast<uint32_t>(j + 1) < count ? w1 : 0.0f;
+                    }
                     sum += w0 + w1;
                     const float a0 = w0 * ratio, a1 = w1 * ratio;
                     const __half2 h = __floats2half2_rn(a0, a1);
@@ -588,10 +642,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
 
     load_tables(smem, p, tid, kTcThreads);
     if (tid == 0) {
-        for (uint32_t w = 0; w < 8; ++w) mbar_init(bars + w, 1);   // copies
-        mbar_init(bars + 8, kDecodeWarps);                          // full[0], full[1]: one arrival per decoder warp
-        mbar_init(bars + 9, kDecodeWarps);
-        for (uint32_t i = 10; i < 14; ++i) mbar_init(bars + i, 1);  // free[0], free[1], S, O: tensor-core commits
+        for (uint32_t w = 0; w < kDecodeWarps; ++w) mbar_init(bars + w, 1);   // copies
+        mbar_init(bars + kBarFull, kRoundPages);                    // full[0], full[1]: one arrival per page slot of the round
+        mbar_init(bars + kBarFull + 1, kRoundPages);
+        for (uint32_t i = kBarFree; i < kBarCount; ++i) mbar_init(bars + i, 1);   // free[0], free[1], S, O: tensor-core commits
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -634,6 +688,10 @@ cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t strea
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(prefix_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
         if (e != cudaSuccess) return e;
+        cudaFuncAttributes attr;
+        e = cudaFuncGetAttributes(&attr, prefix_attention_kernel);
+        if (e != cudaSuccess) return e;
+        if (attr.numRegs != kLaunchRegs) return cudaErrorLaunchOutOfResources;   // the register split assumes this count
         configured = true;
     }
     prefix_attention_kernel<<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
