@@ -155,22 +155,33 @@ __device__ __forceinline__ uint4 codes8(uint32_t qa, uint32_t qb) {
 // Decode one record into registers: quad q of a stream = symbols 4q..4q+3 of the block this lane decodes.
 template <class KLane, class VLane>
 __device__ __forceinline__ void decode_page(KLane &k, VLane &v, uint32_t (&kq)[16], uint32_t (&vq)[16]) {
+    // Four passes of four quads per stream. The pass is a real loop (its body is a quarter of the unrolled code, which
+    // the instruction cache shares with the softmax warps' code); the results shift down the register arrays, so that
+    // after the fourth pass quad q sits in element q.
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-        if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
-            kq[q] = k.quad();
-            vq[q] = v.quad();
-        } else {   // both entropy coded: the two chains interleave symbol by symbol
-            k.reload();
-            v.reload();
-            uint32_t ke[4], ve[4];
+        for (int i = 0; i < 12; ++i) {
+            kq[i] = kq[i + 4];
+            vq[i] = vq[i + 4];
+        }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                ke[i] = k.symbol();
-                ve[i] = v.symbol();
+        for (int q = 12; q < 16; ++q) {
+            if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
+                kq[q] = k.quad();
+                vq[q] = v.quad();
+            } else {   // both entropy coded: the two chains interleave symbol by symbol
+                k.reload();
+                v.reload();
+                uint32_t ke[4], ve[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    ke[i] = k.symbol();
+                    ve[i] = v.symbol();
+                }
+                kq[q] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+                vq[q] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
             }
-            kq[q] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
-            vq[q] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
         }
     }
 }
@@ -332,7 +343,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
 
         float k_scale = 0.0f, v_scale = 0.0f;
         uint32_t token_count = 0;
-        uint32_t kq[16], vq[16];
+        uint32_t kq[16] = {}, vq[16] = {};
         if (cur.u.page_begin + in_unit < cur.u.page_end && !failed) {
             if (!entry_ok(entry)) {
                 if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
