@@ -29,7 +29,7 @@ struct PlanHeader {
     uint32_t shared_pages;            // pages at the head of every sequence that the shared-prefix kernel handles (0 = none)
     uint32_t shared_chunks;           // the shared prefix is cut into this many chunks of
     uint32_t shared_pages_per_chunk;  // this many pages
-    uint32_t next_shared_unit;        // work counter of the shared-prefix kernel; the plan kernel clears it
+    uint32_t reserved_shared;         // unused (the shared-prefix kernel splits its units statically)
     uint32_t pad[7];
 };
 

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     uint32_t shared_chunks = 0, shared_per_chunk = 0;
     if (shared) {
         const uint32_t row_tiles = (p.seq_count * p.group + 127u) / 128u;
-        // about six units per SM, handed out by a counter, so that the last wave is short
+        // about six equal units per SM (CTA b takes units b, b + grid, ...), so that the last wave is short
         const uint32_t wanted = (6u * p.sm_count + p.kv_head_span * row_tiles - 1u) / (p.kv_head_span * row_tiles);
         shared_chunks = min(max(wanted, 1u), min(CF_B200_SHARED_CHUNKS_MAX, (shared + 15u) / 16u));
         shared_per_chunk = ((shared + shared_chunks - 1u) / shared_chunks + 7u) / 8u * 8u;   // whole rounds of eight pages
@@ -120,7 +120,6 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         hdr->shared_pages = overflow ? 0u : shared;
         hdr->shared_chunks = overflow ? 0u : shared_chunks;
         hdr->shared_pages_per_chunk = shared_per_chunk;
-        hdr->next_shared_unit = 0;
         if (overflow) raise_status(p, CF_B200_DEVSTAT_WORKSPACE);
     }
 }
