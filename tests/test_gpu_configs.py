@@ -174,6 +174,41 @@ def test_shared_prefix_is_decoded_once_for_all_sequences(native, oracle, coder, 
     assert layer.device_status() == 0
 
 
+@pytest.mark.parametrize("coder", ["rans", "huffman"])
+def test_shared_prefix_with_several_units_per_cta(native, oracle, coder):
+    """More units than SMs: 16 chunks x 8 kv heads x 3 row tiles (the last one 64 rows) = 384 units, so that a CTA of the
+    shared-prefix kernel walks through several units (new Q rows in tensor memory, O started afresh, decoders running
+    ahead across the unit boundary). Checked against the per-sequence path on every row and against the oracle on a
+    few sequences."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    n, prefix = 80, 5136                       # 321 shared pages: the last chunk's last round holds a single page
+    layer, info = build_sealed_layer(np.array([prefix] + [0] * (n - 1)), coder=coder, seed=90, extra_pages_per_sequence=4,
+                                     reserve_pages=2 * n)
+    for s in range(1, n):
+        layer.copy_sequence(0, s)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(91)
+    slots = list(range(n))
+    for step in range(19):                     # one sealed private page and a 3-token tail per sequence
+        k = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append(slots, k, v)
+        layer.seal_full_pages()
+    q = _q(n, 32, 92)
+    plain = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    shared = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=prefix // 16).cpu().numpy()
+    assert layer.device_status() == 0
+    ok, err = attention_close(shared, plain)
+    assert ok, err
+    some = [0, 37, 79]
+    want = oracle_from_layer(layer, q.cpu().numpy()[some], slots=some)
+    ok, err = attention_close(shared[some], want)
+    assert ok, err
+    again = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=prefix // 16).cpu().numpy()
+    assert np.array_equal(again, shared)       # the static unit split makes the result repeatable bit for bit
+
+
 def test_shared_prefix_claim_that_does_not_hold_falls_back(native, oracle):
     """A claim the page tables do not bear out is refused by the plan kernel: the status word says so and the
     result is the per-sequence one."""
