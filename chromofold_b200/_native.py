@@ -121,6 +121,25 @@ EXPORTS = {
         "cf_attention_compare_async", "cf_attention_invalidate_graphs", "cf_attention_get_counters",
         "cf_attention_last_error",
     ],
+    "compat_bridges.h": [
+        "cf_llama_runtime_options_validate", "cf_llama_runtime_create", "cf_llama_runtime_destroy", "cf_llama_runtime_append",
+        "cf_llama_runtime_record_compressed_launch", "cf_llama_runtime_record_dense_fallback",
+        "cf_llama_runtime_record_cuda_error", "cf_llama_runtime_snapshot_get", "cf_llama_runtime_write_json",
+        "cf_llama_runtime_last_error",
+        "cf_llama_graph_options_validate", "cf_llama_model_topology_validate", "cf_llama_graph_create",
+        "cf_llama_graph_destroy", "cf_llama_graph_append_device", "cf_llama_graph_record_attention",
+        "cf_llama_graph_record_dense_dispatch", "cf_llama_graph_get_counters", "cf_llama_graph_write_evidence",
+        "cf_llama_graph_last_error",
+        "cf_llama_device_seal_bridge_create", "cf_llama_device_seal_bridge_destroy", "cf_llama_device_seal_bridge_stage",
+        "cf_llama_device_seal_bridge_seal", "cf_llama_device_seal_bridge_attention", "cf_llama_device_seal_bridge_evidence",
+        "cf_llama_device_seal_bridge_last_error",
+        "cf_llama_device_graph_create", "cf_llama_device_graph_destroy", "cf_llama_device_graph_append_async",
+        "cf_llama_device_graph_attention_async", "cf_llama_device_graph_get_counters", "cf_llama_device_graph_last_error",
+        "cf_llama_server_cuda_bridge_create", "cf_llama_server_cuda_bridge_destroy", "cf_llama_server_cuda_slot_create",
+        "cf_llama_server_cuda_slot_copy_async", "cf_llama_server_cuda_slot_cancel_async",
+        "cf_llama_server_cuda_slot_reset_async", "cf_llama_server_cuda_dispatch_batch_async",
+        "cf_llama_server_cuda_shutdown_audit", "cf_llama_server_cuda_last_error",
+    ],
     "compat_adapter.h": [
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",
         "cf_llama_kv_attention", "cf_llama_kv_attention_host", "cf_llama_kv_flush", "cf_llama_kv_seq_rm",
@@ -139,7 +158,30 @@ FORMAT_VERSION = 1   # CF_B200_FORMAT_VERSION of include/chromofold_b200/sealed_
 TRANSFER_MAGIC = 0x3147504643
 DEVSTAT_CHECKSUM = 0x40
 
+# Exported by libchromofold_b200_llama_ms.so (its names clash with compat_mscache.h's llama-server runtime)
+MS_BRIDGE_EXPORTS = {
+    "compat_llama_ms_bridge.h": [
+        "cf_llama_server_multisequence_create", "cf_llama_server_multisequence_destroy", "cf_llama_server_slot_create",
+        "cf_llama_server_slot_reset_async", "cf_llama_server_sequence_copy_async", "cf_llama_server_sequence_remove_async",
+        "cf_llama_server_context_shift_async", "cf_llama_server_cancel_sequence_async",
+        "cf_llama_server_batch_attention_async", "cf_llama_server_audit", "cf_llama_server_multisequence_last_error",
+    ],
+}
+MS_BRIDGE_LIB_PATH = os.path.join(os.path.dirname(LIB_PATH), "libchromofold_b200_llama_ms.so")
+
 _lib = None
+_ms_bridge_lib = None
+
+
+def ms_bridge_lib():
+    """The llama-server multi-sequence bridge library (built beside the main one, linked against it)."""
+    global _ms_bridge_lib
+    if _ms_bridge_lib is None:
+        lib()   # the bridge needs the main library's symbols
+        if not os.path.exists(MS_BRIDGE_LIB_PATH):
+            raise RuntimeError(f"{MS_BRIDGE_LIB_PATH} is missing: build it with `python -m chromofold_b200.build`")
+        _ms_bridge_lib = C.CDLL(MS_BRIDGE_LIB_PATH)
+    return _ms_bridge_lib
 
 
 def lib():

@@ -1,4 +1,5 @@
-"""Compile the CUDA sources of this package into chromofold_b200/libchromofold_b200.so (sm_100a only)."""
+"""Compile the CUDA sources of this package into chromofold_b200/libchromofold_b200.so (sm_100a only), and the
+llama-server multi-sequence bridge (host code, linked against it) into chromofold_b200/libchromofold_b200_llama_ms.so."""
 import glob
 import os
 import shutil
@@ -8,17 +9,22 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libchromofold_b200.so")
+MS_BRIDGE_LIB = os.path.join(HERE, "libchromofold_b200_llama_ms.so")
 
 
 def sources():
     return sorted(glob.glob(os.path.join(HERE, "csrc", "*.cu")) + glob.glob(os.path.join(HERE, "csrc", "*.cpp")))
 
 
+def bridge_sources():
+    return sorted(glob.glob(os.path.join(HERE, "csrc_llama_ms_bridge", "*.cpp")))
+
+
 def stale():
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(MS_BRIDGE_LIB):
         return True
-    built = os.path.getmtime(LIB)
-    deps = sources() + glob.glob(os.path.join(HERE, "csrc", "*.cuh")) + glob.glob(
+    built = min(os.path.getmtime(LIB), os.path.getmtime(MS_BRIDGE_LIB))
+    deps = sources() + bridge_sources() + glob.glob(os.path.join(HERE, "csrc", "*.cuh")) + glob.glob(
         os.path.join(ROOT, "include", "chromofold_b200", "*.h"))
     return any(os.path.getmtime(f) > built for f in deps)
 
@@ -40,6 +46,13 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed")
     if verbose:
         sys.stderr.write(proc.stderr)
+    gxx = shutil.which("g++") or "g++"
+    cmd = [gxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I" + os.path.join(ROOT, "include")] + bridge_sources() + [
+        "-o", MS_BRIDGE_LIB, "-L" + HERE, "-lchromofold_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-Bsymbolic"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("g++ failed on the llama-server multi-sequence bridge")
     return LIB
 
 

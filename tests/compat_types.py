@@ -224,3 +224,54 @@ class MultigpuCounters(C.Structure):
         "host_staged_bytes", "collective_calls", "collective_bytes", "mixed_codec_pages_consumed", "remote_pages_loaded",
         "migrations_completed", "device_failures_detected", "fail_closed_rejections", "cross_device_contamination",
         "dense_fallback_launches", "cuda_errors", "transfer_errors", "page_refs_at_shutdown", "snapshot_refs_at_shutdown")]
+
+
+# ---- llama.cpp-side bridges (include/chromofold_b200/compat_bridges.h, compat_llama_ms_bridge.h) ----
+class LlamaTensorView(C.Structure):
+    _fields_ = [("data", _vp), ("token_stride_bytes", _u64), ("head_stride_bytes", _u64), ("element_stride_bytes", _u64),
+                ("token_count", _u32), ("head_count", _u32), ("head_dim", _u32), ("scalar_type", _u32)]
+
+
+class LlamaRuntimeOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("kv", LlamaKvOptions), ("causal_window", _u32), ("require_cuda", _u32),
+                ("allow_dense_fallback", _u32), ("emit_stats", _u32)]
+
+
+class LlamaRuntimeCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in ("append_calls", "appended_values", "compressed_attention_launches",
+                                    "sealed_values_consumed", "active_values_consumed", "dense_fallback_launches",
+                                    "rejected_operations", "cuda_errors")]
+
+
+class LlamaRuntimeSnapshot(C.Structure):
+    _fields_ = [("kv", LlamaKvStats), ("counters", LlamaRuntimeCounters), ("backend_selected", _u32), ("initialized", _u32),
+                ("dense_fallback_allowed", _u32), ("evidence_complete", _u32)]
+
+
+class LlamaModelTopology(C.Structure):
+    _fields_ = [(n, _u32) for n in ("struct_size", "layer_count", "query_head_count", "kv_head_count", "head_dim",
+                                    "context_size", "uniform_kv_geometry", "causal", "recurrent")]
+
+
+class LlamaGraphOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("backend", _u32), ("page_size", _u32), ("window", _u32), ("emit_stats", _u32),
+                ("evidence_path", C.c_char_p)]
+
+
+class LlamaGraphCounters(C.Structure):
+    _fields_ = [(n, _u64) for n in ("graph_append_calls", "graph_attention_dispatches", "graph_dense_dispatches",
+                                    "query_layout_conversions", "output_layout_conversions", "unsupported_graphs")]
+
+
+class LlamaDeviceSealOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("seal", DeviceSealConfig), ("require_cuda", _u32), ("allow_dense_fallback", _u32)]
+
+
+class LlamaDeviceGraphOptions(C.Structure):
+    _fields_ = [("struct_size", _u32), ("kv", DeviceKvConfig), ("causal", _u32), ("linear_sequence_only", _u32),
+                ("dense_fallback_forbidden", _u32)]
+
+
+class LlamaServerMultisequenceConfig(C.Structure):
+    _fields_ = [("cache", MultisequenceConfig), ("strict_no_fallback", _u32), ("enable_prefix_sharing", _u32),
+                ("enable_speculative_transactions", _u32)]

@@ -22,8 +22,10 @@ def test_every_declared_symbol_is_exported(native):
     headers = [h for h in os.listdir(os.path.join(ROOT, "include", "chromofold_b200")) if h.endswith(".h")]
     seen = 0
     for h in headers:
+        # one header's functions live in a library of their own (its names clash with another header's)
+        where = native.ms_bridge_lib() if h in native.MS_BRIDGE_EXPORTS else lib
         for name in _declared(h):
-            assert hasattr(lib, name), f"{h}: {name} is declared but not exported"
+            assert hasattr(where, name), f"{h}: {name} is declared but not exported"
             seen += 1
     assert seen >= 10
     assert b"sm_100a" in lib.cf_b200_build_info()
