@@ -205,3 +205,205 @@ def test_forwarding_bridges_refuse_bad_options_without_a_gpu(native):
     assert ms.cf_llama_server_slot_create(None, C.c_int64(0), C.c_int64(0)) == -1
     assert ms.cf_llama_server_audit(None) == -1
     assert ms.cf_llama_server_multisequence_last_error(None) == b"null llama-server multisequence bridge"
+
+
+# ---- on a GPU: each bridge must behave exactly like the ABI it forwards to ----------------------------------------
+@pytest.mark.gpu
+def test_runtime_bridge_and_graph_state_on_the_chromofold_backend(native, tmp_path):
+    import torch  # noqa: F401  (makes sure a CUDA context can be had)
+    lib = native.lib()
+    lib.cf_llama_runtime_create.restype = C.c_void_p
+    lib.cf_llama_runtime_last_error.restype = C.c_char_p
+    lib.cf_llama_graph_create.restype = C.c_void_p
+    lib.cf_llama_graph_last_error.restype = C.c_char_p
+    layers, hq, hkv, dim, page, tokens = 2, 8, 2, 64, 64, 70
+    o = _runtime_options(layers=layers, hq=hq, hkv=hkv, dim=dim, page=page)
+    r = C.c_void_p(lib.cf_llama_runtime_create(C.byref(o)))
+    assert r
+    rng = np.random.default_rng(3)
+    k = rng.standard_normal((tokens, hkv, dim)).astype(np.float32)
+    v = rng.standard_normal((tokens, hkv, dim)).astype(np.float32)
+
+    def view(a, begin, count, dtype_code=0):
+        return LlamaTensorView(a[begin:].ctypes.data, hkv * dim * 4, dim * 4, 4, count, hkv, dim, dtype_code)
+
+    for layer in range(layers):
+        for begin, count in ((0, 50), (50, 20)):
+            kv, vv = view(k, begin, count), view(v, begin, count)
+            assert lib.cf_llama_runtime_append(r, layer, begin, C.byref(kv), C.byref(vv), None) == 0, lib.cf_llama_runtime_last_error(r)
+    # refused and counted: a strided view, a half-precision view, a head count that is not the cache's, a gap in positions
+    kv, vv = view(k, 0, 1), view(v, 0, 1)
+    kv.head_stride_bytes = (dim + 8) * 4
+    assert lib.cf_llama_runtime_append(r, 0, tokens, C.byref(kv), C.byref(vv), None) == -1
+    assert b"contiguous fp32" in lib.cf_llama_runtime_last_error(r)
+    kv = view(k, 0, 1, dtype_code=1)
+    assert lib.cf_llama_runtime_append(r, 0, tokens, C.byref(kv), C.byref(vv), None) == -1
+    one = LlamaTensorView(k.ctypes.data, dim * 4, dim * 4, 4, 1, 1, dim, 0)
+    assert lib.cf_llama_runtime_append(r, 0, tokens, C.byref(one), C.byref(one), None) == -1
+    assert b"topology" in lib.cf_llama_runtime_last_error(r)
+    kv, vv = view(k, 0, 1), view(v, 0, 1)
+    assert lib.cf_llama_runtime_append(r, 0, tokens + 5, C.byref(kv), C.byref(vv), None) == -1      # the adapter's refusal
+    assert b"contiguous" in lib.cf_llama_runtime_last_error(r)
+    assert lib.cf_llama_runtime_record_dense_fallback(r) == -1
+    assert lib.cf_llama_runtime_last_error(r) == b"dense fallback is disabled"
+    s = LlamaRuntimeSnapshot()
+    assert lib.cf_llama_runtime_snapshot_get(r, C.byref(s)) == 0
+    assert s.counters.append_calls == 2 * layers and s.counters.appended_values == layers * tokens * hkv * dim * 2
+    assert s.counters.rejected_operations == 5 and s.counters.dense_fallback_launches == 1
+    assert s.kv.appended_tokens == layers * hkv * tokens and s.kv.sealed_pages == layers * hkv and s.kv.active_tokens == layers * hkv * 6
+    assert s.evidence_complete == 0                       # a dense fallback was recorded: the evidence stays incomplete
+    lib.cf_llama_runtime_destroy(r)
+
+    # the graph state owns such a runtime; its evidence file is the runtime's JSON
+    path = str(tmp_path / "graph.json").encode()
+    g = C.c_void_p(lib.cf_llama_graph_create(C.byref(_graph_options(page=page, path=path)), C.byref(_topology(layers, hq, hkv, dim))))
+    assert g
+    kv, vv = view(k, 0, 64), view(v, 0, 64)
+    assert lib.cf_llama_graph_append_device(g, 0, 0, C.byref(kv), C.byref(vv), None) == 0, lib.cf_llama_graph_last_error(g)
+    assert lib.cf_llama_graph_append_device(g, 0, 3, C.byref(kv), C.byref(vv), None) == -1
+    assert lib.cf_llama_graph_record_attention(g, C.c_uint64(64 * hkv * dim * 2), C.c_uint64(0)) == 0
+    assert lib.cf_llama_graph_write_evidence(g) == 0
+    doc = json.load(open(path))
+    assert doc["backend_selected"] == 1 and doc["evidence_complete"] == 1
+    assert doc["kv"]["sealed_pages"] == hkv and doc["counters"]["compressed_attention_launches"] == 1
+    assert lib.cf_llama_graph_record_dense_dispatch(g) == -1
+    assert lib.cf_llama_graph_last_error(g) == b"dense graph dispatch is forbidden for ChromoFold"
+    assert lib.cf_llama_graph_write_evidence(g) == 0
+    assert json.load(open(path))["evidence_complete"] == 0          # the forbidden dispatch shows in the evidence
+    c = LlamaGraphCounters()
+    lib.cf_llama_graph_get_counters(g, C.byref(c))
+    assert (c.graph_append_calls, c.graph_attention_dispatches, c.graph_dense_dispatches, c.unsupported_graphs) == (1, 1, 1, 2)
+    lib.cf_llama_graph_destroy(g)
+
+
+@pytest.mark.gpu
+def test_device_seal_bridge_and_device_graph_bridge_equal_their_engines(native):
+    import torch
+    from compat_types import DeviceKvConfig, DeviceSealConfig
+    lib = native.lib()
+    for f in ("cf_llama_device_seal_bridge_create", "cf_llama_device_graph_create", "cf_device_seal_create", "cf_device_kv_create"):
+        getattr(lib, f).restype = C.c_void_p
+    lib.cf_llama_device_seal_bridge_last_error.restype = C.c_char_p
+    lib.cf_llama_device_graph_last_error.restype = C.c_char_p
+    layers, hkv, hq, d, page = 1, 2, 8, 128, 64
+    rng = np.random.default_rng(12)
+    tokens = page + 5
+    dk = torch.from_numpy(rng.standard_normal((tokens, hkv, d)).astype(np.float32)).cuda()
+    dv = torch.from_numpy(rng.standard_normal((tokens, hkv, d)).astype(np.float32)).cuda()
+    q = torch.from_numpy(rng.standard_normal((2, hq, d)).astype(np.float32)).cuda()
+    qv = TensorView(q.data_ptr(), 3, 2, hq, d, hq * d * 4, d * 4, 4, 0)
+    scale = C.c_float(1.0 / np.sqrt(d))
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+
+    so = LlamaDeviceSealOptions()
+    so.struct_size, so.seal, so.require_cuda = C.sizeof(so), DeviceSealConfig(layers, hkv, hq, d, page, hq // hkv, 64, 0), 1
+    b = C.c_void_p(lib.cf_llama_device_seal_bridge_create(C.byref(so)))
+    e = C.c_void_p(lib.cf_device_seal_create(C.byref(so.seal)))
+    assert b and e
+    n, complete = DeviceSealCounters(), C.c_uint32(9)
+    assert lib.cf_llama_device_seal_bridge_seal(b, 0, None) == -1                  # nothing staged: the engine's refusal and text
+    assert lib.cf_llama_device_seal_bridge_last_error(b) != b""
+    assert lib.cf_llama_device_seal_bridge_stage(b, 0, 0, ptr(dk), ptr(dv), page, None) == 0
+    assert lib.cf_llama_device_seal_bridge_last_error(b) == b""
+    assert lib.cf_llama_device_seal_bridge_evidence(b, C.byref(n), C.byref(complete)) == 0 and complete.value == 0
+    assert lib.cf_llama_device_seal_bridge_seal(b, 0, None) == 0
+    assert lib.cf_llama_device_seal_bridge_stage(b, 0, page, ptr(dk[page:]), ptr(dv[page:]), 5, None) == 0
+    assert lib.cf_device_seal_stage_active_page(e, 0, 0, ptr(dk), ptr(dv), page, None) == 0
+    assert lib.cf_device_seal_full_page_async(e, 0, None) == 0
+    assert lib.cf_device_seal_stage_active_page(e, 0, page, ptr(dk[page:]), ptr(dv[page:]), 5, None) == 0
+    out_b = torch.zeros((2, hq, d), dtype=torch.float32, device="cuda")
+    out_e = torch.zeros_like(out_b)
+    strides = (C.c_uint64(hq * d * 4), C.c_uint64(d * 4), C.c_uint64(4))
+    assert lib.cf_llama_device_seal_bridge_attention(b, 0, C.byref(qv), ptr(out_b), 3, *strides, tokens - 2, scale, 0, None) == 0
+    assert lib.cf_device_seal_attention_async(e, 0, C.byref(qv), ptr(out_e), 3, *strides, tokens - 2, scale, 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out_b, out_e) and float(out_b.abs().max()) > 0
+    assert lib.cf_llama_device_seal_bridge_evidence(b, C.byref(n), C.byref(complete)) == 0
+    assert complete.value == 1 and n.seal_successes == 1 and n.descriptor_publications == 1 and n.compressed_attention_launches == 1
+    lib.cf_llama_device_seal_bridge_destroy(b, None)
+    lib.cf_device_seal_destroy(e, None)
+
+    go = LlamaDeviceGraphOptions()
+    go.struct_size, go.kv = C.sizeof(go), DeviceKvConfig(layers, hkv, hq, d, page, hq // hkv, 0)
+    go.causal, go.linear_sequence_only, go.dense_fallback_forbidden = 1, 1, 1
+    gb = C.c_void_p(lib.cf_llama_device_graph_create(C.byref(go)))
+    p = C.c_void_p(lib.cf_device_kv_create(C.byref(go.kv)))
+    assert gb and p
+    kview = lambda t, begin, count: TensorView(t[begin:].data_ptr(), 3, count, hkv, d, hkv * d * 4, d * 4, 4, 0)
+    for begin, count in ((0, 30), (30, 10)):
+        kv, vv = kview(dk, begin, count), kview(dv, begin, count)
+        assert lib.cf_llama_device_graph_append_async(gb, 0, begin, C.byref(kv), C.byref(vv), None) == 0
+        assert lib.cf_device_kv_append_async(p, 0, begin, C.byref(kv), C.byref(vv), None) == 0
+    kv, vv = kview(dk, 0, 1), kview(dv, 0, 1)
+    assert lib.cf_llama_device_graph_append_async(gb, 0, 3, C.byref(kv), C.byref(vv), None) == -1
+    assert b"non-contiguous" in lib.cf_llama_device_graph_last_error(gb)
+    out_g, out_p = torch.zeros((2, hq, d), dtype=torch.float32, device="cuda"), torch.zeros((2, hq, d), dtype=torch.float32, device="cuda")
+    assert lib.cf_llama_device_graph_attention_async(gb, 0, ptr(q), ptr(out_g), 2, 38, scale, 0, None) == 0
+    assert lib.cf_llama_device_graph_last_error(gb) == b""
+    assert lib.cf_device_kv_attention_async(p, 0, ptr(q), ptr(out_p), 2, 38, scale, 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out_g, out_p) and float(out_g.abs().max()) > 0
+    # the bridge has no seal call (nor has the reference's): once the active page is full the next append is refused
+    kv, vv = kview(dk, 40, page - 40), kview(dv, 40, page - 40)
+    assert lib.cf_llama_device_graph_append_async(gb, 0, 40, C.byref(kv), C.byref(vv), None) == 0
+    kv, vv = kview(dk, page, 1), kview(dv, page, 1)
+    assert lib.cf_llama_device_graph_append_async(gb, 0, page, C.byref(kv), C.byref(vv), None) == -1
+    assert b"seal before retry" in lib.cf_llama_device_graph_last_error(gb)
+    c = DeviceKvCounters()
+    assert lib.cf_llama_device_graph_get_counters(gb, C.byref(c)) == 0 and c.device_append_calls == 3 and c.dense_fallback_launches == 0
+    lib.cf_llama_device_graph_destroy(gb, None)
+    lib.cf_device_kv_destroy(p, None)
+
+
+@pytest.mark.gpu
+def test_llama_server_slot_bridges_over_the_resolver_and_the_cache(native):
+    """Slots of llama-server over the CUDA sequence resolver (llama_server_cuda_resolver_bridge.cpp) and over the
+    multi-sequence cache (llama_server_multisequence_bridge.cpp): create / duplicate / copy / cancel / reset / audit."""
+    import torch  # noqa: F401
+    lib, ms = native.lib(), native.ms_bridge_lib()
+    lib.cf_llama_server_cuda_bridge_create.restype = C.c_void_p
+    lib.cf_llama_server_cuda_last_error.restype = C.c_char_p
+    i64 = C.c_int64
+    b = C.c_void_p(lib.cf_llama_server_cuda_bridge_create(C.byref(MsConfig(1, 8, 32, 128, 64, 4, 0))))
+    assert b
+    assert lib.cf_llama_server_cuda_slot_create(b, i64(3)) == 0
+    assert lib.cf_llama_server_cuda_slot_create(b, i64(3)) == -1              # the resolver refuses a duplicate id
+    first_error = lib.cf_llama_server_cuda_last_error(b)
+    assert first_error != b""
+    assert lib.cf_llama_server_cuda_slot_copy_async(b, i64(3), i64(4), None) == 0
+    assert lib.cf_llama_server_cuda_last_error(b) == first_error              # this bridge keeps the last failure's text
+    assert lib.cf_llama_server_cuda_slot_copy_async(b, i64(99), i64(5), None) == -1
+    assert lib.cf_llama_server_cuda_slot_cancel_async(b, i64(4), None) == 0
+    assert lib.cf_llama_server_cuda_slot_reset_async(b, i64(3), None) == 0
+    assert lib.cf_llama_server_cuda_slot_reset_async(b, i64(3), None) == -1   # gone
+    assert lib.cf_llama_server_cuda_dispatch_batch_async(b, None, 0, None) == -1
+    assert lib.cf_llama_server_cuda_shutdown_audit(b) == 0
+    lib.cf_llama_server_cuda_bridge_destroy(b, None)
+
+    ms.cf_llama_server_multisequence_create.restype = C.c_void_p
+    ms.cf_llama_server_multisequence_last_error.restype = C.c_char_p
+    cfg = LlamaServerMultisequenceConfig()
+    cfg.cache.layer_count, cfg.cache.kv_head_count, cfg.cache.query_head_count = 1, 8, 32
+    cfg.cache.head_dim, cfg.cache.page_size, cfg.cache.gqa_group_size = 128, 16, 4
+    cfg.strict_no_fallback = 1
+    m = C.c_void_p(ms.cf_llama_server_multisequence_create(C.byref(cfg)))
+    assert m
+    assert ms.cf_llama_server_slot_create(m, i64(0), i64(100)) == 0
+    assert ms.cf_llama_server_slot_create(m, i64(0), i64(101)) == -1
+    assert ms.cf_llama_server_multisequence_last_error(m) == b"slot already exists"
+    assert ms.cf_llama_server_slot_create(m, i64(1), i64(100)) == -1          # the cache refuses a duplicate sequence id
+    assert ms.cf_llama_server_multisequence_last_error(m) not in (b"", b"slot already exists")
+    assert ms.cf_llama_server_sequence_copy_async(m, i64(100), i64(200), 0, 0, None) == 0
+    assert ms.cf_llama_server_multisequence_last_error(m) == b""
+    assert ms.cf_llama_server_context_shift_async(m, i64(100), 0, 0, 0, None) == 0
+    assert ms.cf_llama_server_sequence_remove_async(m, i64(200), i64(-1), i64(-1), None) == 0
+    assert ms.cf_llama_server_sequence_remove_async(m, i64(200), i64(-1), i64(-1), None) == -1
+    assert ms.cf_llama_server_slot_reset_async(m, i64(7), None) == -1
+    assert ms.cf_llama_server_multisequence_last_error(m) == b"slot does not exist"
+    assert ms.cf_llama_server_slot_reset_async(m, i64(0), None) == 0          # removes sequence 100 and reclaims
+    assert ms.cf_llama_server_slot_create(m, i64(0), i64(100)) == 0           # both ids are free again
+    assert ms.cf_llama_server_cancel_sequence_async(m, i64(100), None) == 0
+    assert ms.cf_llama_server_slot_create(m, i64(0), i64(102)) == 0           # the cancel forgot slot 0
+    assert ms.cf_llama_server_batch_attention_async(m, None, 0, None) == -1
+    assert ms.cf_llama_server_audit(m) == 0
+    ms.cf_llama_server_multisequence_destroy(m, None)
