@@ -209,6 +209,42 @@ def test_shared_prefix_with_several_units_per_cta(native, oracle, coder):
     assert np.array_equal(again, shared)       # the static unit split makes the result repeatable bit for bit
 
 
+def test_shared_prefix_under_kv_head_sharding_and_fp32_queries(native, oracle):
+    """The hint combined with the other launch options: a kv-head shard (each rank of a head-sharded deployment passes
+    kv_head_begin / kv_head_span) writes exactly its heads' columns of the unsharded result; fp32 queries give the
+    fp16-query result within tolerance whichever kernel serves them."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    n, prefix = 40, 2048
+    layer, info = build_sealed_layer(np.array([prefix] + [0] * (n - 1)), coder="rans", seed=95, extra_pages_per_sequence=4,
+                                     reserve_pages=2 * n)
+    for s in range(1, n):
+        layer.copy_sequence(0, s)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(96)
+    for step in range(5):                       # a private tail of 5 tokens per sequence
+        k = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((n, 8, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append(list(range(n)), k, v)
+    q = _q(n, 32, 97)
+    pages = prefix // 16
+    full = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=pages).cpu().numpy()
+    ok, err = attention_close(full, layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy())
+    assert ok, err
+    group = 4
+    for begin, span in ((0, 2), (2, 2), (4, 4)):
+        out = torch.full((n, 32, 128), 7.0, dtype=torch.float32, device="cuda")
+        layer.attention(q, out=out, kernel=native.KERNEL_LANES, shared_prefix_pages=pages, kv_head_begin=begin, kv_head_span=span)
+        got = out.cpu().numpy()
+        lo, hi = begin * group, (begin + span) * group
+        assert np.array_equal(got[:, lo:hi], full[:, lo:hi])                  # same units, same arithmetic
+        assert np.all(got[:, :lo] == 7.0) and np.all(got[:, hi:] == 7.0)      # other heads' columns untouched
+    f32 = layer.attention(q.float(), shared_prefix_pages=pages).cpu().numpy()
+    ok, err = attention_close(f32, full)
+    assert ok, err
+    assert layer.device_status() == 0
+
+
 def test_shared_prefix_claim_that_does_not_hold_falls_back(native, oracle):
     """A claim the page tables do not bear out is refused by the plan kernel: the status word says so and the
     result is the per-sequence one."""
