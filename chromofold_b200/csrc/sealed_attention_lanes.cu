@@ -143,11 +143,16 @@ struct WarpLayout {
 };
 static_assert(WarpLayout<2>::kSmem <= 232448, "the eight-head kernel must fit the 227 KB of one CTA");
 
-template <int NG, bool kProbe = false>
+// kSplitQ (with NG = 2): the queries are fp32. A pass serves four heads; their rows are split into binary16(q) and
+// binary16(q - binary16(q)), stored as the rows of group 0 and group 1, the two score fragments are added, and one
+// softmax / P V follows: the scores equal fp32-query scores to 2^-22 relative, at the cost of a second score mma.
+template <int NG, bool kProbe = false, bool kSplitQ = false>
 __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
+    static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
     using L = WarpLayout<NG>;
     using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
-    constexpr uint32_t kPassHeads = 4u * NG;
+    constexpr uint32_t kPassHeads = kSplitQ ? 4u : 4u * NG;
+    constexpr int NS = kSplitQ ? 1 : NG;   // groups that go through softmax and P V
     extern __shared__ __align__(128) uint8_t smem[];
     uint32_t *k_slot = reinterpret_cast<uint32_t *>(smem);
     uint32_t *v_slot = k_slot + 4096;
@@ -226,6 +231,23 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                 qs.bq[s][0] = v.x;
                 qs.bq[s][1] = v.y;
             }
+        } else if constexpr (kSplitQ) {
+            const float2 *qsrc = reinterpret_cast<const float2 *>(
+                reinterpret_cast<const float *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * 128u);
+            __syncwarp();  // the previous unit's readers are done
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {    // 4 heads x 64 channel pairs; row = head*2 + half, residues 8 rows further
+                const uint32_t i = lane + 32u * j, head = i >> 6;
+                const float2 x = head < G ? qsrc[i] : make_float2(0.0f, 0.0f);
+                const __half2 hi = __floats2half2_rn(x.x, x.y);
+                const float2 back = __half22float2(hi);
+                const __half2 lo = __floats2half2_rn(x.x - back.x, x.y - back.y);
+                q_rows[(i >> 5) * L::kQRowWords + (i & 31u)] = *reinterpret_cast<const uint32_t *>(&hi);
+                q_rows[((i >> 5) + 8u) * L::kQRowWords + (i & 31u)] = *reinterpret_cast<const uint32_t *>(&lo);
+            }
+            __syncwarp();
+            qs.addr = q_col_mine ? smem_addr(q_rows + (q_head_of_col * 2u + (t & 1u)) * L::kQRowWords) : smem_addr(zero_row);
+            qs.group_stride = q_col_mine ? 8u * L::kQRowWords * 4u : 0u;
         } else {
             const uint32_t *qsrc = reinterpret_cast<const uint32_t *>(
                 reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * 128u);
@@ -332,13 +354,17 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                         else { FixedLane v; v.open(v_part, lane); decode_v_only(v, u); }
                     }
 
+                    if constexpr (kSplitQ) {   // K q = K binary16(q) + K residue
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) u.score[0][c] += u.score[1][c];
+                    }
                     if constexpr (!kProbe) {
                     // ---- online softmax for this page (fp32), per group of four heads ----
                     const uint32_t token = (page_begin + i) * 16u + my_token;
                     const bool visible = my_token < token_count && token >= first_token && token < sealed && token <= qpos;
                     __syncwarp();  // the previous page's readers of the scratch are done
 #pragma unroll
-                    for (int n = 0; n < NG; ++n) {
+                    for (int n = 0; n < NS; ++n) {
                         const float s0 = visible ? u.score[n][0] * k_scale : -CUDART_INF_F;
                         const float s1 = visible ? u.score[n][1] * k_scale : -CUDART_INF_F;
                         float r0 = s0, r1 = s1;
@@ -372,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     const float v_ratio = v_scale_prev / v_scale;   // O is kept in units of the current page's V scale
                     v_scale_prev = v_scale;
 #pragma unroll
-                    for (int n = 0; n < NG; ++n) {
+                    for (int n = 0; n < NS; ++n) {
                         const float beta = alpha_s[4u * n + o_head] * v_ratio;
 #pragma unroll
                         for (int dd = 0; dd < 4; ++dd)
@@ -381,11 +407,11 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     }
                     // P rows as A fragments. Rows g / g+8 of the fragment belong to lane tags g>>2 / (g>>2)+2; a lane
                     // feeds the row whose tag is its own t and zeros (read from the zero row) otherwise.
-                    uint32_t ra[2][NG][8], rb[2][NG][8];   // [fp16(p) | its rounding residue][group][fragment words]
+                    uint32_t ra[2][NS][8], rb[2][NS][8];   // [fp16(p) | its rounding residue][group][fragment words]
 #pragma unroll
                     for (int part = 0; part < 2; ++part) {
 #pragma unroll
-                        for (int n = 0; n < NG; ++n) {
+                        for (int n = 0; n < NS; ++n) {
                             const __half *rows = (part ? p_rows_lo : p_rows) + (4u * n + o_head) * 16u;
                             const __half *row_a = row_lo_mine ? rows : zero_row;
                             const __half *row_b = row_hi_mine ? rows : zero_row;
@@ -408,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 #pragma unroll
                             for (int part = 0; part < 2; ++part)
 #pragma unroll
-                                for (int n = 0; n < NG; ++n)
+                                for (int n = 0; n < NS; ++n)
                                     mma_16816(u.acc[n][dd], ra[part][n][2 * tq], rb[part][n][2 * tq], ra[part][n][2 * tq + 1],
                                               rb[part][n][2 * tq + 1], lo, hi);
                         }
@@ -434,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
         } else {
         // ---- unit partials ----
 #pragma unroll
-        for (int n = 0; n < NG; ++n) {
+        for (int n = 0; n < NS; ++n) {
             float l0 = u.l0[n], l1 = u.l1[n];
 #pragma unroll
             for (int o = 2; o <= 16; o <<= 1) {
@@ -475,11 +501,12 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
 bool lanes_kernel_supports(const AttentionParams &p) {
     return p.head_dim == 128 && p.page_tokens == 16 && p.block_size == 64 && p.group >= 1 && p.group <= 16 &&
-           p.query_type == CF_B200_F16;
+           (p.query_type == CF_B200_F16 || p.query_type == CF_B200_F32);
 }
 
 // Query groups of up to four heads per kv head run the four-head kernel; larger groups run the eight-head one, which
-// decodes a page once for eight query heads (its query operands live in shared memory instead of registers).
+// decodes a page once for eight query heads (its query operands live in shared memory instead of registers). fp32
+// queries (the reference's own ABIs pass nothing else) run the split-query kernel, four heads per pass.
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream) {
     static int sm_count = 0;
     static bool configured = false;
@@ -498,9 +525,13 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         e = cudaFuncSetAttribute(lanes_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lanes_attention_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<2>::kSmem));
+        if (e != cudaSuccess) return e;
         configured = true;
     }
     if (p.decode_probe) lanes_attention_kernel<1, true><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, false, true><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
     else lanes_attention_kernel<2><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();

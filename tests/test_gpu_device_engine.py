@@ -38,7 +38,7 @@ def test_seal_engine_state_machine_faults_and_attention(native, oracle):
     lib = native.lib()
     lib.cf_device_seal_create.restype = C.c_void_p
     lib.cf_device_seal_last_error.restype = C.c_char_p
-    layers, hkv, hq, d, page = 2, 2, 8, 128, 64          # tiles of 32 tokens: two records per page and head
+    layers, hkv, hq, d, page = 2, 2, 8, 128, 64          # tiles of 16 tokens at head_dim 128: four records per page and head
     cfg = DeviceSealConfig(layers, hkv, hq, d, page, hq // hkv, 64, 0)
     e = C.c_void_p(lib.cf_device_seal_create(C.byref(cfg)))
     rng = np.random.default_rng(77)
@@ -94,7 +94,7 @@ def test_seal_engine_state_machine_faults_and_attention(native, oracle):
                                             C.c_uint64((d + 4) * 2), C.c_uint64(2), pos[0], C.c_float(scale), window, None)
     assert rc == 0, lib.cf_device_seal_last_error(e)
     torch.cuda.synchronize()
-    want = _expected(oracle, k, v, 2 * page, 32, q.astype(np.float32), pos, window, scale, hq // hkv)
+    want = _expected(oracle, k, v, 2 * page, 16, q.astype(np.float32), pos, window, scale, hq // hkv)
     got = out[:, :, :d].float().cpu().numpy()
     assert np.abs(got - want).max() <= 2e-2                       # bf16 output: 8 mantissa bits
     # fp32 dense query and output: the tight bar
