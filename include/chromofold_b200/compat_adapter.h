@@ -14,7 +14,8 @@
  * What differs: pages are quantised to int8 with one fp16 scale per stream and entropy coded (format v1) on the GPU,
  * whatever kv_bits says (kv_bits selects 4-/8-bit fixed-width pages in the reference, chromofold_kv_adapter.cpp:30-31);
  * physically a reference page of page_size tokens is stored as page_size / T records of T tokens with
- * T * head_dim <= 4096; statistics are reported in the reference's units.
+ * T * head_dim <= 4096 (T = 16 at head_dim 128, the record geometry of the lane-per-block attention kernel, which
+ * takes the fp32 queries of this ABI as binary16 + residue rows); statistics are reported in the reference's units.
  * Environment: CHROMOFOLD_B200_CODER = rans (default) | huffman | fixed8. */
 #ifndef CHROMOFOLD_B200_COMPAT_ADAPTER_H
 #define CHROMOFOLD_B200_COMPAT_ADAPTER_H
