@@ -583,8 +583,7 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || d->kernel == CF_B200_KERNEL_DECODE_PROBE ||
                            (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
-    if (use_lanes && !p.decode_probe && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0 &&
-        d->query_type == CF_B200_F16) {   // the shared-prefix kernel takes binary16 queries only
+    if (use_lanes && !p.decode_probe && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static int sm_count = 0;
         if (sm_count == 0) {
             int device = 0;

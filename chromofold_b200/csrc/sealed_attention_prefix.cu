@@ -30,7 +30,8 @@
 //                        scaled, written with (max, sum) to the shared-prefix partials; the combine kernel merges
 //                        them with the per-sequence partials of the private pages and the tail.
 // Registers: the kernel starts at 96 per thread; the decoders drop to 80 and the softmax warps rise to 120 (setmaxnreg).
-// Tensor memory (512 columns): S 0..127, O 128..255, Q 256..319, P 320..383, P residue 384..447 (binary16 pairs per
+// Tensor memory (512 columns): S 0..127, O 128..255, Q 256..319, P 320..383, P residue 384..447, Q residue 448..511 (fp32
+// queries only: the row is split into binary16(q) and its rounding residue, S = Q K^T + Q residue K^T) (binary16 pairs per
 // column, row = lane). B tiles use the no-swizzle K-major canonical layout: 8 rows x 16 bytes core matrices, element
 // (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
 // The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
@@ -63,7 +64,7 @@ constexpr uint32_t kOffRowMax = kOffMisc + 32;                 // [2 column halv
 constexpr uint32_t kTcSmem = kOffRowMax + 2 * 128 * 4;
 static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB of one CTA");
 constexpr uint32_t kTmemColumns = 512;
-constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColP = 320, kColPResidue = 384;
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColP = 320, kColPResidue = 384, kColQResidue = 448;
 constexpr uint32_t kStopUnit = 0xffffffffu;
 constexpr uint32_t kFirstRound = 1u, kLastRound = 2u;   // round flags
 constexpr uint32_t kSoftmaxBarrier = 1;   // named barrier (0 is __syncthreads)
@@ -416,6 +417,9 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
 }
 
 // ---- softmax group: warps 12..19; its thread 0 also issues the tensor-core work ---------------------------------------
+// kSplitQ: the queries are fp32; a row goes to tensor memory as binary16(q) and as binary16(q - binary16(q)), and S is the
+// sum of two products, which equals the fp32-query product to 2^-22 relative.
+template <bool kSplitQ>
 __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t tmem, uint32_t warp,
                                              uint32_t lane, uint32_t row_tiles) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
@@ -469,6 +473,30 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             v_unit = 0.0f;
             o_started = false;
             const uint32_t row = u.tile_index * 128u + row_in_tile;
+            if constexpr (kSplitQ) {
+                const float4 *src = reinterpret_cast<const float4 *>(
+                    reinterpret_cast<const float *>(p.queries) +
+                    (static_cast<uint64_t>(min(row, rows_total - 1u) / G) * p.query_head_count + u.kv_head * G + min(row, rows_total - 1u) % G) * 128u +
+                    64u * half);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {   // 16 channels = 8 columns of pairs at a time
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float4 x = src[4 * c + j];
+                        if (row >= rows_total) x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        const __half2 h0 = __floats2half2_rn(x.x, x.y), h1 = __floats2half2_rn(x.z, x.w);
+                        const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+                        const __half2 l0 = __floats2half2_rn(x.x - b0.x, x.y - b0.y), l1 = __floats2half2_rn(x.z - b1.x, x.w - b1.y);
+                        hi[2 * j] = *reinterpret_cast<const uint32_t *>(&h0);
+                        hi[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                        lo[2 * j] = *reinterpret_cast<const uint32_t *>(&l0);
+                        lo[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&l1);
+                    }
+                    tmem_store8(tmem_row + kColQ + 32u * half + 8u * c, hi);
+                    tmem_store8(tmem_row + kColQResidue + 32u * half + 8u * c, lo);
+                }
+            } else {
             uint32_t q_raw[32];
             if (row < rows_total) {
                 const uint4 *src = reinterpret_cast<const uint4 *>(
@@ -487,6 +515,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
                 for (int j = 0; j < 32; ++j) q_raw[j] = 0u;
             }
             tmem_store32(tmem_row + kColQ + 32u * half, q_raw);
+            }
             tmem_store_wait();
             tc_fence_before();
             if (group_any(kSoftmaxBarrier, false)) break;
@@ -497,6 +526,10 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             tc_fence_after();
 #pragma unroll
             for (uint32_t s = 0; s < 8; ++s) umma(tmem + kColS, tmem + kColQ + 8u * s, tile_desc(smem_addr(k_tile) + 256u * s), s);
+            if constexpr (kSplitQ) {
+#pragma unroll
+                for (uint32_t s = 0; s < 8; ++s) umma(tmem + kColS, tmem + kColQResidue + 8u * s, tile_desc(smem_addr(k_tile) + 256u * s), 1u);
+            }
             umma_commit(bar_s);
         }
         if (v_unit == 0.0f)
@@ -642,6 +675,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
     if (o_pending && !failed) mbar_wait(bar_o, o_phase & 1u);
 }
 
+template <bool kSplitQ>
 __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(AttentionParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -678,7 +712,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
         decoder_role(p, smem, hdr, warp, lane, row_tiles, unit_count);
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        softmax_role(p, smem, hdr, tmem, warp, lane, row_tiles);
+        softmax_role<kSplitQ>(p, smem, hdr, tmem, warp, lane, row_tiles);
     }
 
     tc_fence_before();
@@ -697,15 +731,20 @@ cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t strea
         if (e != cudaSuccess) return e;
         e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(prefix_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
-        if (e != cudaSuccess) return e;
-        cudaFuncAttributes attr;
-        e = cudaFuncGetAttributes(&attr, prefix_attention_kernel);
-        if (e != cudaSuccess) return e;
-        if (attr.numRegs != kLaunchRegs) return cudaErrorLaunchOutOfResources;   // the register split assumes this count
+        for (int split = 0; split < 2; ++split) {
+            const void *kernel = split ? reinterpret_cast<const void *>(prefix_attention_kernel<true>)
+                                       : reinterpret_cast<const void *>(prefix_attention_kernel<false>);
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTcSmem));
+            if (e != cudaSuccess) return e;
+            cudaFuncAttributes attr;
+            e = cudaFuncGetAttributes(&attr, kernel);
+            if (e != cudaSuccess) return e;
+            if (attr.numRegs != kLaunchRegs) return cudaErrorLaunchOutOfResources;   // the register split assumes this count
+        }
         configured = true;
     }
-    prefix_attention_kernel<<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
+    if (p.query_type == CF_B200_F32) prefix_attention_kernel<true><<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
+    else prefix_attention_kernel<false><<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

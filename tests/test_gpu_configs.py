@@ -242,6 +242,15 @@ def test_shared_prefix_under_kv_head_sharding_and_fp32_queries(native, oracle):
     f32 = layer.attention(q.float(), shared_prefix_pages=pages).cpu().numpy()
     ok, err = attention_close(f32, full)
     assert ok, err
+    # queries that binary16 cannot hold: both kernels split them into binary16 + residue, the results must agree tightly
+    g.manual_seed(98)
+    q32 = torch.randn((n, 32, 128), generator=g, device="cuda") * 1.7
+    with_hint = layer.attention(q32, shared_prefix_pages=pages).cpu().numpy()
+    without = layer.attention(q32).cpu().numpy()
+    generic = layer.attention(q32, kernel=native.KERNEL_GENERIC).cpu().numpy()
+    assert np.abs(with_hint - generic).max() <= 2e-5 and np.abs(without - generic).max() <= 2e-5
+    rounded = layer.attention(q32.half()).cpu().numpy()
+    assert np.abs(rounded - generic).max() > 2e-5           # rounding the queries to binary16 would have shown
     assert layer.device_status() == 0
 
 
