@@ -72,7 +72,7 @@ EXPORTS = {
         "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async", "cf_b200_codebook_build",
         "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
         "cf_b200_dense_attention_async", "cf_b200_build_info", "cf_b200_sealed_attention_static_async",
-        "cf_b200_sealed_attention_static_error",
+        "cf_b200_sealed_attention_static_error", "cf_b200_shared_prefix_launches",
     ],
     "compat_kv.h": [
         "cf_kv_validate_page", "cf_kv_validate_layout", "cf_kv_page_resident_bytes", "cf_kv_cache_memory_stats",

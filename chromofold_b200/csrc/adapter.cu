@@ -15,6 +15,7 @@
 
 #include "chromofold_b200/compat_adapter.h"
 #include "chromofold_b200/sealed_kv.h"
+#include "cf_device_common.cuh"
 
 namespace {
 
@@ -403,6 +404,16 @@ extern "C" int cf_llama_kv_attention(cf_llama_kv_adapter *adapter, uint32_t laye
         d.workspace = reinterpret_cast<void *>(aligned);
         d.workspace_bytes = adapter->workspace.count - (aligned - ws);
         d.status = adapter->status.ptr;
+        // Prefill (llama.cpp evaluates a prompt in batches of query tokens): they all see the layer's sealed records in
+        // full, which the shared-prefix kernel then decodes once per 128 query rows instead of once per query token.
+        // Only a hint (the plan kernel checks it), given where it pays and the workspace has room for the extra partials.
+        if (query_count >= 4 && causal_window == 0) {
+            const uint32_t tiles = std::min(h0.sealed / adapter->tile_tokens, (query_token_begin + 1u) / adapter->tile_tokens);
+            if (tiles >= 8 && tiles <= adapter->stride &&
+                cfb::workspace_layout(query_count, query_head_count, adapter->opt.head_dim, d.workspace_bytes, true).chunk_capacity >=
+                    2ull * query_count)
+                d.shared_prefix_pages = tiles;
+        }
         if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("ChromoFold paged attention launch rejected");
     });
 }

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "chromofold_b200/compat_ms.h"
+#include "cf_device_common.cuh"
 #include "engine_common.cuh"
 
 using namespace cfb_engine;
@@ -634,6 +635,41 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
     });
 }
 
+// Sealed records that every row of a layer's batch shares: sequences forked from one prompt reference the same pages
+// (copy shares pages by reference), and the query tokens of one prefill item all see the item's sealed history. Such
+// records are decoded once per 128 query rows by the shared-prefix kernel instead of once per row; the number returned
+// here is only a hint, the plan kernel checks it against the page tables. 0 = not worth it or not applicable.
+static uint32_t shared_leading_tiles(cf_ms_cuda_resolver *r, const cf_ms_batch_item *items, uint32_t item_count, uint32_t layer,
+                                     uint32_t rows, uint32_t window) {
+    if (rows < 4 || window != 0) return 0;   // a handful of rows is served faster one by one
+    const LayerSeq *first = nullptr;
+    size_t common_refs = 0;
+    uint32_t lowest_position = 0xffffffffu;
+    for (uint32_t i = 0; i < item_count; ++i) {
+        if (items[i].layer != layer) continue;
+        lowest_position = std::min(lowest_position, items[i].query_token_begin);
+        const LayerSeq &L = r->sequences.at(items[i].sequence_id).layers[layer];
+        if (!first) {
+            first = &L;
+            common_refs = L.pages.size();
+            continue;
+        }
+        if (&L == first) continue;
+        size_t n = 0;
+        while (n < common_refs && n < L.pages.size() && L.pages[n].page_id == first->pages[n].page_id) ++n;
+        common_refs = n;
+    }
+    if (!first) return 0;
+    uint32_t tiles = 0;
+    for (size_t n = 0; n < common_refs; ++n) {
+        const PageRef &ref = first->pages[n];
+        if (ref.tokens != ref.tiles * r->tile) break;   // a record that is not full ends the run of whole records
+        tiles += ref.tiles;
+    }
+    tiles = std::min(tiles, (lowest_position + 1u) / r->tile);   // every query token must see the shared records in full
+    return tiles >= 8 ? tiles : 0;
+}
+
 extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_ms_batch_item *items, uint32_t item_count,
                                               void *stream) {
     if (!r || !items || !item_count) return -1;
@@ -737,6 +773,12 @@ extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_m
             const uintptr_t ws = reinterpret_cast<uintptr_t>(r->workspace.ptr), aligned = (ws + 255) / 256 * 256;
             d.workspace = reinterpret_cast<void *>(aligned);
             d.workspace_bytes = r->workspace.count - (aligned - ws);
+            d.shared_prefix_pages = shared_leading_tiles(r, items, item_count, layer, count, window);
+            // the shared-prefix partials take their own region of the workspace: use the hint only where that leaves
+            // room for at least two chunks per row
+            if (d.shared_prefix_pages &&
+                cfb::workspace_layout(count, Hq, D, d.workspace_bytes, true).chunk_capacity < 2ull * count)
+                d.shared_prefix_pages = 0;
             d.status = r->status.ptr;
             if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("multi-sequence attention launch rejected");
             ++r->counters.sequence_attention_launches;

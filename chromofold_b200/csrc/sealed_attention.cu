@@ -7,9 +7,12 @@
 // query heads of the group at once (a K/V code is decoded once, not once per query head), and the partial
 // (max, sum, weighted) triples are merged with the rule of cf_online_softmax_merge (src/runtime/kv_runtime.cpp:219-243).
 
+#include <atomic>
 #include <math_constants.h>
 
 #include "attention_params.cuh"
+
+static std::atomic<unsigned long long> g_shared_prefix_launches{0};
 
 namespace cfb {
 
@@ -596,12 +599,19 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     }
     if ((stages & CF_B200_STAGE_PLAN) && cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
     if (stages & CF_B200_STAGE_ATTENTION) {
-        if (p.shared_prefix_pages && cfb::launch_prefix_attention(p, s) != cudaSuccess) return CF_ERR_CUDA;
+        if (p.shared_prefix_pages) {
+            if (cfb::launch_prefix_attention(p, s) != cudaSuccess) return CF_ERR_CUDA;
+            g_shared_prefix_launches.fetch_add(1, std::memory_order_relaxed);
+        }
         const cudaError_t e = use_lanes ? cfb::launch_lanes_attention(p, s) : cfb::launch_generic_attention(p, s);
         if (e != cudaSuccess) return CF_ERR_CUDA;
     }
     if ((stages & CF_B200_STAGE_COMBINE) && cfb::launch_combine(p, s) != cudaSuccess) return CF_ERR_CUDA;
     return CF_OK;
+}
+
+extern "C" unsigned long long cf_b200_shared_prefix_launches(void) {
+    return g_shared_prefix_launches.load(std::memory_order_relaxed);
 }
 
 extern "C" cf_status cf_b200_sealed_attention_async(const cf_b200_sealed_attention_desc *d, void *stream) {

@@ -265,6 +265,11 @@ cf_status cf_b200_dense_attention_async(const cf_b200_dense_attention_desc *desc
 /* Build identification; also what a loader calls to check that the library carries device code. */
 const char *cf_b200_build_info(void);
 
+/* Diagnostics: how many attention calls of this process launched the shared-prefix kernel (a shared_prefix_pages hint
+ * given by the caller, or worked out by one of the stores behind the reference's ABIs for forked sequences and
+ * prefill batches). A launch whose hint the plan kernel then refuses raises CF_B200_DEVSTAT_PREFIX_MISMATCH. */
+unsigned long long cf_b200_shared_prefix_launches(void);
+
 #ifdef __cplusplus
 }
 #endif

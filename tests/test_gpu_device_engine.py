@@ -175,3 +175,47 @@ def test_dataplane_append_seal_attention(native, oracle, dtype):
     assert lib.cf_device_kv_clear_async(p, None) == 0
     assert append(0, 5) == 0                                       # usable after clear
     lib.cf_device_kv_destroy(p, None)
+
+
+def test_prefill_through_the_dataplane_takes_the_shared_prefix_path(native, oracle):
+    """A call with several query tokens (llama.cpp evaluating a prompt batch) over a sealed history: the engine passes
+    the shared-prefix hint by itself; the answers equal the ones the same query tokens get one at a time."""
+    import torch
+    lib = native.lib()
+    lib.cf_device_kv_create.restype = C.c_void_p
+    lib.cf_device_kv_last_error.restype = C.c_char_p
+    lib.cf_b200_shared_prefix_launches.restype = C.c_uint64
+    layers, hkv, hq, d, page = 1, 2, 8, 128, 64
+    p = C.c_void_p(lib.cf_device_kv_create(C.byref(DeviceKvConfig(layers, hkv, hq, d, page, hq // hkv, 0))))
+    rng = np.random.default_rng(15)
+    tokens = 4 * page + 9                                      # 16 sealed records of 16 tokens + a 9-token tail
+    k = torch.from_numpy(rng.standard_normal((tokens, hkv, d)).astype(np.float32)).cuda()
+    v = torch.from_numpy(rng.standard_normal((tokens, hkv, d)).astype(np.float32)).cuda()
+    view = lambda t, begin, count: TensorView(t[begin:].data_ptr(), 3, count, hkv, d, hkv * d * 4, d * 4, 4, 0)
+    for begin in range(0, tokens, page):
+        count = min(page, tokens - begin)
+        kv, vv = view(k, begin, count), view(v, begin, count)
+        assert lib.cf_device_kv_append_async(p, 0, begin, C.byref(kv), C.byref(vv), None) == 0, lib.cf_device_kv_last_error(p)
+        if count == page:
+            assert lib.cf_device_kv_seal_full_pages_async(p, None) == 0
+    nq, scale = 6, C.c_float(1.0 / np.sqrt(d))
+    q = torch.from_numpy(rng.standard_normal((nq, hq, d)).astype(np.float32)).cuda()
+    out = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda")
+    before = lib.cf_b200_shared_prefix_launches()
+    assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(q.data_ptr()), C.c_void_p(out.data_ptr()), nq, tokens - nq, scale, 0, None) == 0
+    torch.cuda.synchronize()
+    assert lib.cf_b200_shared_prefix_launches() == before + 1
+    single = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda")
+    for i in range(nq):
+        assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(q[i:].data_ptr()), C.c_void_p(single[i:].data_ptr()), 1,
+                                                tokens - nq + i, scale, 0, None) == 0
+    torch.cuda.synchronize()
+    assert lib.cf_b200_shared_prefix_launches() == before + 1
+    assert float((out - single).abs().max()) <= 2e-5 and float(out.abs().max()) > 0
+    want = _expected(oracle, k.cpu().numpy(), v.cpu().numpy(), 4 * page, 16, q.cpu().numpy(),
+                     [tokens - nq + i for i in range(nq)], 0, 1.0 / np.sqrt(d), hq // hkv)
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-4
+    # a sliding window turns the hint off (the shared-prefix kernel serves whole histories only)
+    assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(q.data_ptr()), C.c_void_p(out.data_ptr()), nq, tokens - nq, scale, 100, None) == 0
+    assert lib.cf_b200_shared_prefix_launches() == before + 1
+    lib.cf_device_kv_destroy(p, None)

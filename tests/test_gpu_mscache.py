@@ -176,3 +176,77 @@ def test_server_runtime_appends_whole_prompts_and_runs_interleaved_batches(nativ
         assert np.allclose(out.cpu().numpy(), want, rtol=2e-3, atol=1e-3), (seq, layer)
     assert lib.cf_llama_server_shutdown_async(s, None) == 0, err()
     lib.cf_llama_server_runtime_destroy(s, None)
+
+
+def test_forked_sequences_and_prefill_items_take_the_shared_prefix_path(native, oracle):
+    """Sequences forked from one prompt share its sealed pages; a batch over them (and a prefill item, whose query tokens
+    all see the item's sealed history) is served by the shared-prefix kernel without the caller saying anything: the
+    resolver works the hint out from its own page references. The answers must equal the ones the same items get one by
+    one (batches of fewer than four rows never take that path) and the oracle's."""
+    import torch
+    lib = native.lib()
+    lib.cf_multisequence_create.restype = C.c_void_p
+    lib.cf_multisequence_last_error.restype = C.c_char_p
+    c = C.c_void_p(lib.cf_multisequence_create(C.byref(MultisequenceConfig(1, HKV, HQ, D, PAGE, HQ // HKV, 0, 1))))
+    err = lambda: lib.cf_multisequence_last_error(c)
+    i64 = C.c_int64
+    rng = np.random.default_rng(91)
+    rows = {}
+
+    def append(seq, tokens):
+        begin = rows[seq][0].shape[0] if seq in rows else 0
+        done = 0
+        while done < tokens:                                   # page by page: an append never crosses a page boundary
+            n = min(tokens - done, PAGE - (begin + done) % PAGE)
+            k = torch.from_numpy(rng.standard_normal((n, HKV, D)).astype(np.float32) * 0.8).cuda()
+            v = torch.from_numpy(rng.standard_normal((n, HKV, D)).astype(np.float32) * 0.8).cuda()
+            assert lib.cf_sequence_append_async(c, i64(seq), 0, begin + done, C.byref(_view(k, n)), C.byref(_view(v, n)), None) == 0, err()
+            old = rows.get(seq, [np.zeros((0, HKV, D), np.float32)] * 2)
+            rows[seq] = [np.concatenate([old[0], k.cpu().numpy()]), np.concatenate([old[1], v.cpu().numpy()])]
+            done += n
+
+    assert lib.cf_sequence_create(c, i64(1)) == 0
+    append(1, 20 * PAGE)                                       # a 320-token prompt: 20 sealed pages
+    forks = list(range(2, 10))
+    for seq in forks:
+        assert lib.cf_sequence_copy_async(c, i64(1), i64(seq), 0, 1 << 30, None) == 0, err()
+        rows[seq] = [a.copy() for a in rows[1]]
+        append(seq, 3 + seq)                                   # private continuations of different lengths, some sealing a page
+    qs = {s: torch.from_numpy(rng.standard_normal((1, HQ, D)).astype(np.float32)).cuda() for s in forks}
+
+    def run(seqs):
+        outs = {s: torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda") for s in seqs}
+        items = (MsBatchItem * len(seqs))()
+        for i, s in enumerate(seqs):
+            items[i] = _item(s, 0, qs[s], outs[s], rows[s][0].shape[0] - 1)
+        assert lib.cf_multisequence_attention_async(c, items, len(seqs), None) == 0, err()
+        torch.cuda.synchronize()
+        return {s: outs[s].cpu().numpy() for s in seqs}
+
+    lib.cf_b200_shared_prefix_launches.restype = C.c_uint64
+    before = lib.cf_b200_shared_prefix_launches()
+    together = run(forks)                                      # 8 rows sharing 20 pages: the shared-prefix path
+    assert lib.cf_b200_shared_prefix_launches() == before + 1
+    for s in forks:
+        alone = run([s])[s]                                    # one row: the per-sequence path
+        assert lib.cf_b200_shared_prefix_launches() == before + 1
+        assert np.abs(together[s] - alone).max() <= 2e-5, s
+        k, v = rows[s]
+        want = _expected(oracle, k, v, k.shape[0] // PAGE * PAGE, 16, qs[s].cpu().numpy(), [k.shape[0] - 1], 1.0 / np.sqrt(D), HQ // HKV)
+        assert np.allclose(together[s], want, rtol=2e-3, atol=1e-3), s
+
+    # prefill: six query tokens of sequence 1 in one item, at the last six positions of a 5-token tail after the prompt
+    append(1, 5)
+    n = rows[1][0].shape[0]
+    q = torch.from_numpy(rng.standard_normal((5, HQ, D)).astype(np.float32)).cuda()
+    out = torch.zeros((5, HQ, D), dtype=torch.float32, device="cuda")
+    items = (MsBatchItem * 1)()
+    items[0] = _item(1, 0, q, out, n - 5)
+    assert lib.cf_multisequence_attention_async(c, items, 1, None) == 0, err()
+    torch.cuda.synchronize()
+    assert lib.cf_b200_shared_prefix_launches() == before + 2  # five query tokens over 20 sealed pages
+    k, v = rows[1]
+    want = _expected(oracle, k, v, 20 * PAGE, 16, q.cpu().numpy(), list(range(n - 5, n)), 1.0 / np.sqrt(D), HQ // HKV)
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-3, atol=1e-3)
+    assert lib.cf_multisequence_audit(c) == 0
+    lib.cf_multisequence_destroy(c, None)
