@@ -15,7 +15,6 @@
 
 #include "chromofold_b200/compat_adapter.h"
 #include "chromofold_b200/sealed_kv.h"
-#include "cf_device_common.cuh"
 
 namespace {
 
@@ -399,21 +398,26 @@ extern "C" int cf_llama_kv_attention(cf_llama_kv_adapter *adapter, uint32_t laye
         d.output_type = CF_B200_F32;
         d.softmax_scale = softmax_scale;
         d.causal_window = causal_window;
+        // Prefill (llama.cpp evaluates a prompt in batches of query tokens): they all see the layer's sealed records in
+        // full, which the shared-prefix kernel then decodes once per 128 query rows instead of once per query token.
+        // Only a hint (the plan kernel checks it), given where it pays and the workspace has or can get the room.
+        if (query_count >= 4 && causal_window == 0) {
+            const uint32_t tiles = std::min(h0.sealed / adapter->tile_tokens, (query_token_begin + 1u) / adapter->tile_tokens);
+            if (tiles >= 8 && tiles <= adapter->stride) {
+                cf_b200_sealed_attention_desc room = d;   // the workspace grows for the extra partials, up to 1 GiB
+                room.shared_prefix_pages = 1;
+                uint64_t bytes = 0;
+                if (cf_b200_sealed_attention_workspace_bytes(&room, 65536, &bytes) == CF_OK && bytes + 256 <= (1ull << 30)) {
+                    adapter->workspace.ensure(bytes + 256, s);
+                    d.shared_prefix_pages = tiles;
+                }
+            }
+        }
         const uintptr_t ws = reinterpret_cast<uintptr_t>(adapter->workspace.ptr);
         const uintptr_t aligned = (ws + 255) / 256 * 256;
         d.workspace = reinterpret_cast<void *>(aligned);
         d.workspace_bytes = adapter->workspace.count - (aligned - ws);
         d.status = adapter->status.ptr;
-        // Prefill (llama.cpp evaluates a prompt in batches of query tokens): they all see the layer's sealed records in
-        // full, which the shared-prefix kernel then decodes once per 128 query rows instead of once per query token.
-        // Only a hint (the plan kernel checks it), given where it pays and the workspace has room for the extra partials.
-        if (query_count >= 4 && causal_window == 0) {
-            const uint32_t tiles = std::min(h0.sealed / adapter->tile_tokens, (query_token_begin + 1u) / adapter->tile_tokens);
-            if (tiles >= 8 && tiles <= adapter->stride &&
-                cfb::workspace_layout(query_count, query_head_count, adapter->opt.head_dim, d.workspace_bytes, true).chunk_capacity >=
-                    2ull * query_count)
-                d.shared_prefix_pages = tiles;
-        }
         if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("ChromoFold paged attention launch rejected");
     });
 }

@@ -301,19 +301,18 @@ void core_attention(Core &c, uint32_t layer, const void *q, uint32_t q_type, flo
     d.output_type = CF_B200_F32;
     d.softmax_scale = softmax_scale;
     d.causal_window = window;
+    // Prefill: the query tokens of one call all see the layer's sealed records in full, so those records are decoded
+    // once per 128 query rows by the shared-prefix kernel instead of once per query token. Only a hint (the plan kernel
+    // checks it), given where it pays and where the workspace has or can get room for the extra partials.
+    if (count >= 4 && window == 0) {
+        const uint32_t tiles = std::min(L.sealed_tokens / c.tile, (query_begin + 1u) / c.tile);
+        if (tiles >= 8 && tiles <= c.stride && shared_prefix_room(c.workspace, count, c.cfg.kv_heads, c.cfg.query_heads, c.cfg.head_dim, s))
+            d.shared_prefix_pages = tiles;
+    }
     const uintptr_t ws = reinterpret_cast<uintptr_t>(c.workspace.ptr), aligned = (ws + 255) / 256 * 256;
     d.workspace = reinterpret_cast<void *>(aligned);
     d.workspace_bytes = c.workspace.count - (aligned - ws);
     d.status = c.status.ptr;
-    // Prefill: the query tokens of one call all see the layer's sealed records in full, so those records are decoded
-    // once per 128 query rows by the shared-prefix kernel instead of once per query token. Only a hint (the plan kernel
-    // checks it), given where it pays and where the workspace has room for the extra partials.
-    if (count >= 4 && window == 0) {
-        const uint32_t tiles = std::min(L.sealed_tokens / c.tile, (query_begin + 1u) / c.tile);
-        if (tiles >= 8 && tiles <= c.stride &&
-            cfb::workspace_layout(count, c.cfg.query_heads, c.cfg.head_dim, d.workspace_bytes, true).chunk_capacity >= 2ull * count)
-            d.shared_prefix_pages = tiles;
-    }
     if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("compressed attention launch rejected");
 }
 

@@ -97,6 +97,24 @@ static __global__ void dense_to_view_kernel(const float *dense, void *out, uint3
     store_scalar(out, t * ts + h * hs + d * es, type, dense[i]);
 }
 
+// Room in an engine's attention workspace for the shared-prefix partials of `rows` query rows (the extra region of
+// cf_device_common.cuh's layout). The workspace grows for it, once per larger batch size, up to kSharedWorkspaceCap;
+// false = no room, the caller then leaves the hint out. Call before the descriptor's workspace pointer is taken.
+constexpr uint64_t kSharedWorkspaceCap = 1ull << 30;
+inline bool shared_prefix_room(Buffer<uint8_t> &workspace, uint32_t rows, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
+                               cudaStream_t s) {
+    cf_b200_sealed_attention_desc d{};
+    d.kv_head_count = kv_heads;
+    d.query_head_count = query_heads;
+    d.head_dim = head_dim;
+    d.seq_count = rows;
+    d.shared_prefix_pages = 1;
+    uint64_t bytes = 0;
+    if (cf_b200_sealed_attention_workspace_bytes(&d, 65536, &bytes) != CF_OK || bytes + 256 > kSharedWorkspaceCap) return false;
+    workspace.ensure(bytes + 256, s);
+    return true;
+}
+
 inline uint32_t choose_tile_tokens(uint32_t page_size, uint32_t head_dim) {
     // 16-token records at head_dim 128 are the geometry of the lane-per-block attention kernel
     if (head_dim == 128 && page_size % 16 == 0) return 16;

@@ -770,15 +770,13 @@ extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_m
             d.output_type = CF_B200_F32;
             d.softmax_scale = softmax_scale;
             d.causal_window = window;
+            // the shared-prefix partials take their own region of the workspace, which grows for them if it has to
+            d.shared_prefix_pages = shared_leading_tiles(r, items, item_count, layer, count, window);
+            if (d.shared_prefix_pages && !shared_prefix_room(r->workspace, count, r->config.kv_head_count, Hq, D, s))
+                d.shared_prefix_pages = 0;
             const uintptr_t ws = reinterpret_cast<uintptr_t>(r->workspace.ptr), aligned = (ws + 255) / 256 * 256;
             d.workspace = reinterpret_cast<void *>(aligned);
             d.workspace_bytes = r->workspace.count - (aligned - ws);
-            d.shared_prefix_pages = shared_leading_tiles(r, items, item_count, layer, count, window);
-            // the shared-prefix partials take their own region of the workspace: use the hint only where that leaves
-            // room for at least two chunks per row
-            if (d.shared_prefix_pages &&
-                cfb::workspace_layout(count, Hq, D, d.workspace_bytes, true).chunk_capacity < 2ull * count)
-                d.shared_prefix_pages = 0;
             d.status = r->status.ptr;
             if (cf_b200_sealed_attention_async(&d, s) != CF_OK) throw std::runtime_error("multi-sequence attention launch rejected");
             ++r->counters.sequence_attention_launches;
