@@ -56,6 +56,8 @@ def parse():
     ap.add_argument("--ctx-hi", type=int, default=CTX_HI)
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "lanes"])
     ap.add_argument("--min-pages-per-unit", type=int, default=0)
+    ap.add_argument("--f32-queries", action="store_true",
+                    help="pass the queries as fp32, as the reference's own ABIs do (split-query kernel); default fp16")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed comparison kernel")
     ap.add_argument("--no-others", action="store_true", help="skip the legs that time the same workload sealed with the other coders")
@@ -67,7 +69,8 @@ def parse():
 
 def workload_name(a):
     return (f"llama3-8b-gqa-decode: {HQ}q/{HKV}kv heads, head_dim {D}, batch {a.batch}, ctx U[{a.ctx_lo},{a.ctx_hi}], "
-            f"{T}-token pages, int8 Laplace(b={a.laplace_b:g}) codes, fp16 scale per page-head, {a.coder}-sealed, 1 layer")
+            f"{T}-token pages, int8 Laplace(b={a.laplace_b:g}) codes, fp16 scale per page-head, {a.coder}-sealed, 1 layer"
+            + (", fp32 queries" if getattr(a, "f32_queries", False) else ""))
 
 
 class ClockSampler:
@@ -262,6 +265,8 @@ def main():
     gen = torch.Generator(device=device)
     gen.manual_seed(5 + 1000 * rank)
     q = torch.randn((n_local, HQ, D), generator=gen, device=device, dtype=torch.float32).half()
+    if a.f32_queries:
+        q = q.float()
     out = torch.zeros((n_local, HQ, D), dtype=torch.float32, device=device)
     kernel = {"auto": N.KERNEL_AUTO, "generic": N.KERNEL_GENERIC, "lanes": N.KERNEL_LANES}[a.kernel]
     kw = dict(kernel=kernel, min_pages_per_unit=a.min_pages_per_unit)
@@ -351,7 +356,7 @@ def main():
         from chromofold_b200.cache import dense_attention
         try:
             out_d = torch.zeros_like(out)
-            dfn = lambda: dense_attention(layer, info["dense_k"], info["dense_v"], q, out_d)
+            dfn = lambda: dense_attention(layer, info["dense_k"], info["dense_v"], q.half(), out_d)
             for _ in range(3):
                 dfn()
             ms_d = timed(dfn, a.steps)
