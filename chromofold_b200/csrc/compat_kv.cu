@@ -5,6 +5,8 @@
 // The descriptors are the reference's (one 104-byte descriptor per page and kv head, per-page LUTs, K per-channel and
 // V per-token fp32 scales), so this path keeps their cost; the sealed-KV entry points are the fast path.
 
+#include <mutex>
+#include <algorithm>
 #include <math_constants.h>
 
 #include "cf_device_common.cuh"
@@ -60,9 +62,20 @@ __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, u
     return s;
 }
 
-// One block per (query row, kv head): all query heads of the group share every decoded symbol.
+// One block per (query row, kv head, split): all query heads of the group share every decoded symbol.
+// Split-KV: with `splits` > 1 block z of a (query row, kv head) takes every splits-th page of its head (split 0 also the
+// active tail) and leaves (max, sum, weighted[D]) per query head in `partials`, merged by compat_combine_kernel.
+// The partials live in a fixed array inside the library image (this ABI has no workspace argument and its calls must
+// not allocate): kCompatSlots slots, handed out in turn; a slot is reused only after the call that used it last has
+// finished on the device (an event per slot, waited for on the new call's stream).
+constexpr uint32_t kCompatSlots = 4;
+constexpr uint32_t kCompatSlotFloats = 512u * 1024u;   // 2 MiB per slot
+constexpr uint32_t kCompatMaxSplits = 64;
+__device__ float g_compat_partials[kCompatSlots * kCompatSlotFloats];
+
 __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_paged_attention_desc desc,
-                                                                          uint32_t batch_tokens) {
+                                                                          uint32_t batch_tokens, uint32_t splits,
+                                                                          float *partials) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t G = desc.gqa_group_size, D = desc.head_dim;
     const Smem lay = smem_layout(G, D, batch_tokens);
@@ -75,7 +88,8 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     float *ml = reinterpret_cast<float *>(smem + lay.off_ml);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t query_row = blockIdx.x, kv_head = blockIdx.y;
+    const uint32_t query_row = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
+    uint32_t pages_of_head = 0;   // pages of this kv head met so far: page n belongs to split n % splits
     const uint32_t query_token = desc.query_token_begin + query_row;
     const uint32_t first_token = window_begin(query_token, desc.causal_window);
 
@@ -126,6 +140,7 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     for (uint32_t pi = 0; pi < desc.page_count; ++pi) {
         const cf_kv_device_page page = desc.pages[pi];
         if (page.kv_head != kv_head || page.head_dim != D) continue;
+        if (pages_of_head++ % splits != split) continue;
         if (page.token_begin > query_token || page.token_begin + page.token_count <= first_token) continue;
         const uint32_t total = page.token_count * D;
         const int zp = static_cast<int>(page.zero_point);
@@ -167,8 +182,9 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     }
 
     // dense fp32 tail [active_token_count][kv_head_count][head_dim] (paged_kv_attention.cu:154-166)
-    for (uint32_t t0 = 0; t0 < desc.active_token_count; t0 += batch_tokens) {
-        const uint32_t count = min(batch_tokens, desc.active_token_count - t0);
+    const uint32_t tail_tokens = split == 0 ? desc.active_token_count : 0u;
+    for (uint32_t t0 = 0; t0 < tail_tokens; t0 += batch_tokens) {
+        const uint32_t count = min(batch_tokens, tail_tokens - t0);
         __syncthreads();
         for (uint32_t pair = warp; pair < G * count; pair += kThreads / 32) {
             const uint32_t g = pair / count, t = pair % count;
@@ -188,11 +204,43 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
         });
     }
 
+    if (splits > 1) {
+        for (uint32_t i = tid; i < G * D; i += kThreads) {
+            const uint32_t g = i / D;
+            float *dst = partials + ((static_cast<uint64_t>(query_row) * desc.query_head_count + kv_head * G + g) * splits + split) * (D + 2u);
+            if (i % D == 0) {
+                dst[0] = ml[2 * g];
+                dst[1] = ml[2 * g + 1];
+            }
+            dst[2 + i % D] = acc[i];
+        }
+        return;
+    }
     for (uint32_t i = tid; i < G * D; i += kThreads) {
         const uint32_t g = i / D;
         const float l = ml[2 * g + 1];
         desc.output[(static_cast<uint64_t>(query_row) * desc.query_head_count + kv_head * G + g) * D + i % D] =
             l > 0.0f ? acc[i] / l : 0.0f;  // no visible token: zeros (paged_kv_attention.cu:170-173)
+    }
+}
+
+// One block per (query row, query head): merges the splits' partials (cf_online_softmax_merge rule, scores in log2 units).
+__global__ void compat_combine_kernel(float *output, const float *partials, uint32_t query_heads, uint32_t head_dim, uint32_t splits) {
+    const uint64_t row = static_cast<uint64_t>(blockIdx.x) * query_heads + blockIdx.y;
+    const float *src = partials + row * splits * (head_dim + 2u);
+    float m = -CUDART_INF_F;
+    for (uint32_t s = 0; s < splits; ++s) m = fmaxf(m, src[s * (head_dim + 2u)]);
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float l = 0.0f, a = 0.0f;
+        if (m != -CUDART_INF_F)
+            for (uint32_t s = 0; s < splits; ++s) {
+                const float *p = src + s * (head_dim + 2u);
+                if (p[0] == -CUDART_INF_F) continue;
+                const float w = exp2f(p[0] - m);
+                l += p[1] * w;
+                a += p[2 + d] * w;
+            }
+        output[row * head_dim + d] = l > 0.0f ? a / l : 0.0f;   // no visible token: zeros
     }
 }
 
@@ -355,17 +403,63 @@ extern "C" cf_status cf_kv_validate_paged_attention_desc(const cf_kv_paged_atten
     return CF_OK;
 }
 
+namespace {
+// Slots of the partials array, per device: whose turn it is and when the slot's last user is done.
+struct CompatSlots {
+    std::mutex lock;
+    bool made = false;
+    cudaEvent_t done[cfb::kCompatSlots] = {};
+    float *base = nullptr;
+    uint32_t next = 0;
+    int sm_count = 0;
+};
+CompatSlots g_compat_slots[64];
+}  // namespace
+
+// The pages of a kv head are dealt out to enough splits to fill the GPU: a decode step has only kv_head_count
+// (query row, kv head) pairs.
 extern "C" cf_status cf_kv_paged_attention_async(const cf_kv_paged_attention_desc *d, void *stream) {
     const cf_status valid = cf_kv_validate_paged_attention_desc(d);
     if (valid != CF_OK) return valid;
     if (d->gqa_group_size > cfb::kMaxGroup) return CF_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint32_t batch_tokens = cfb::kBatchSymbols / d->head_dim;
     const cfb::Smem lay = cfb::smem_layout(d->gqa_group_size, d->head_dim, batch_tokens);
     if (cudaFuncSetAttribute(cfb::compat_paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(lay.total)) != cudaSuccess)
         return CF_ERR_CUDA;
-    cfb::compat_paged_attention_kernel<<<dim3(d->query_count, d->kv_head_count), cfb::kThreads, lay.total,
-                                         static_cast<cudaStream_t>(stream)>>>(*d, batch_tokens);
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return CF_ERR_CUDA;
+    uint32_t splits = 1, slot = 0;
+    CompatSlots *slots = device >= 0 && device < 64 ? &g_compat_slots[device] : nullptr;
+    if (slots) {
+        std::lock_guard<std::mutex> guard(slots->lock);
+        if (!slots->made) {   // first call on this device: events, the array's address, the SM count
+            for (cudaEvent_t &e : slots->done)
+                if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return CF_ERR_CUDA;
+            if (cudaGetSymbolAddress(reinterpret_cast<void **>(&slots->base), cfb::g_compat_partials) != cudaSuccess ||
+                cudaDeviceGetAttribute(&slots->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+                return CF_ERR_CUDA;
+            slots->made = true;
+        }
+        const uint64_t pairs = static_cast<uint64_t>(d->query_count) * d->kv_head_count;
+        const uint64_t pages_per_head = std::max<uint64_t>(d->page_count / d->kv_head_count, 1);
+        const uint64_t room = cfb::kCompatSlotFloats / (static_cast<uint64_t>(d->query_count) * d->query_head_count * (d->head_dim + 2u));
+        const uint64_t wanted = (2ull * slots->sm_count + pairs - 1) / pairs;
+        splits = static_cast<uint32_t>(std::max<uint64_t>(1, std::min({wanted, pages_per_head, room, static_cast<uint64_t>(cfb::kCompatMaxSplits)})));
+        if (splits > 1) {
+            slot = slots->next++ % cfb::kCompatSlots;
+            if (cudaStreamWaitEvent(s, slots->done[slot], 0) != cudaSuccess) return CF_ERR_CUDA;   // the slot's last user
+        }
+    }
+    float *partials = splits > 1 ? slots->base + static_cast<size_t>(slot) * cfb::kCompatSlotFloats : nullptr;
+    cfb::compat_paged_attention_kernel<<<dim3(d->query_count, d->kv_head_count, splits), cfb::kThreads, lay.total, s>>>(
+        *d, batch_tokens, splits, partials);
+    if (splits > 1) {
+        cfb::compat_combine_kernel<<<dim3(d->query_count, d->query_head_count), 128, 0, s>>>(d->output, partials, d->query_head_count,
+                                                                                          d->head_dim, splits);
+        if (cudaEventRecord(slots->done[slot], s) != cudaSuccess) return CF_ERR_CUDA;
+    }
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }
 
