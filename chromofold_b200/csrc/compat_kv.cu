@@ -13,6 +13,9 @@
 #include "chromofold_b200/compat_kv.h"
 
 namespace cfb {
+// Implemented in flat_rans_decode.cu
+cudaError_t launch_flat_rans_decode(const uint8_t *data, const int32_t *byte_off, const uint32_t *state0, const int32_t *slot2sym,
+                                    const int32_t *freq, const int32_t *cum, uint32_t groups, int32_t *out, cudaStream_t stream);
 namespace {
 
 constexpr int kThreads = 128;
@@ -247,8 +250,8 @@ __global__ void compat_combine_kernel(float *output, const float *partials, uint
 // One thread per coded block (rans.cu:28-36), recurrence of rans.cu:20-23.
 __global__ void compat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint32_t *state0,
                                           const int32_t *slot2sym, const int32_t *freq, const int32_t *cum, int block,
-                                          int n, int32_t *out) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+                                          int n, int32_t *out, int first_block) {
+    const int b = first_block + blockIdx.x * blockDim.x + threadIdx.x;
     const long long base = static_cast<long long>(b) * block;
     if (base >= n) return;
     const int count = static_cast<int>(min(static_cast<long long>(block), n - base));
@@ -470,8 +473,16 @@ extern "C" cf_status cf_rans_decode_async(const uint8_t *data, const int32_t *by
     if (block <= 0 || n < 0) return CF_ERR_INVALID_ARGUMENT;
     if (n == 0) return CF_OK;
     const int blocks = (n + block - 1) / block;
-    cfb::compat_rans_decode_kernel<<<(blocks + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        data, byte_off, state0, slot2sym, freq, cum, block, n, out);
+    int first_block = 0;
+    if (block == 64 && blocks > 64) {   // whole groups of 64 blocks: the lane-per-block decoder (flat_rans_decode.cu)
+        const uint32_t groups = static_cast<uint32_t>(blocks - 1) / 64u;
+        if (cfb::launch_flat_rans_decode(data, byte_off, state0, slot2sym, freq, cum, groups, out, static_cast<cudaStream_t>(stream)) !=
+            cudaSuccess)
+            return CF_ERR_CUDA;
+        first_block = static_cast<int>(groups * 64u);
+    }
+    cfb::compat_rans_decode_kernel<<<(blocks - first_block + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        data, byte_off, state0, slot2sym, freq, cum, block, n, out, first_block);
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }
 

@@ -38,7 +38,10 @@ def test_rans_decode_entry_matches_oracle_and_reference_kernel(native, oracle):
     encoder: equals the source symbols, and equals what the reference's own cf_rans_decode_async kernel returns."""
     import torch
     rng = np.random.default_rng(8)
-    for block, n, b in [(64, 100000, 12.0), (1024, 70001, 0.6), (100, 5000, 40.0)]:
+    # block 64 with more than 64 blocks takes the lane-per-block decoder for its whole groups of 64 blocks and the
+    # reference-shaped kernel for the rest; 64 * 64 + 1 symbols leave exactly one symbol to the latter
+    for block, n, b in [(64, 100000, 12.0), (1024, 70001, 0.6), (100, 5000, 40.0), (64, 1 << 20, 3.0), (64, 64 * 64 + 1, 0.05),
+                        (64, 64 * 65, 25.0), (64, 4096, 12.0)]:
         sym = (laplace_codes(rng, n, b).astype(np.int16) + 128).astype(np.uint8)
         cb = oracle.codebook_from_hist(hist_of(sym))
         data, off, st = oracle.rans_encode(sym, block, cb)
