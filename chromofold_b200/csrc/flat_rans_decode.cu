@@ -38,11 +38,21 @@ flat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint
     uint32_t *tile = reinterpret_cast<uint32_t *>(mine + 2 * kPartBytes);
 
     int bad = 0;
-    for (uint32_t slot = tid; slot < 4096; slot += kFlatThreads) {
-        const uint32_t s = static_cast<uint32_t>(slot2sym[slot]);
-        const uint32_t f = s < 256u ? static_cast<uint32_t>(freq[s]) : 4096u, c = s < 256u ? static_cast<uint32_t>(cum[s]) : 0u;
-        bad |= s >= 256u || f >= 4096u || slot - c >= 4096u;
-        table[slot] = (s & 0xffu) | ((slot - c) & 0xfffu) << 8 | (f & 0xfffu) << 20;
+    {   // 16 slots per thread; the loads of each level are issued together, so the CTA pays two memory latencies, not 32
+        uint32_t sym[16], f[16], c[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sym[i] = static_cast<uint32_t>(slot2sym[tid + i * kFlatThreads]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            f[i] = sym[i] < 256u ? static_cast<uint32_t>(freq[sym[i]]) : 4096u;
+            c[i] = sym[i] < 256u ? static_cast<uint32_t>(cum[sym[i]]) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t slot = tid + i * kFlatThreads;
+            bad |= sym[i] >= 256u || f[i] >= 4096u || slot - c[i] >= 4096u;
+            table[slot] = (sym[i] & 0xffu) | ((slot - c[i]) & 0xfffu) << 8 | (f[i] & 0xfffu) << 20;
+        }
     }
     const bool packed_ok = !__syncthreads_or(bad);   // false: the tables do not fit the packed entry, every group goes the slow way
 
