@@ -435,6 +435,9 @@ extern "C" cf_status cf_kv_paged_attention_async(const cf_kv_paged_attention_des
     if (cudaGetDevice(&device) != cudaSuccess) return CF_ERR_CUDA;
     uint32_t splits = 1, slot = 0;
     CompatSlots *slots = device >= 0 && device < 64 ? &g_compat_slots[device] : nullptr;
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capture) != cudaSuccess) return CF_ERR_CUDA;
+    if (capture != cudaStreamCaptureStatusNone) slots = nullptr;   // a captured call keeps to one launch and no events
     if (slots) {
         std::lock_guard<std::mutex> guard(slots->lock);
         if (!slots->made) {   // first call on this device: events, the array's address, the SM count

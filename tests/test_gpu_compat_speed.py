@@ -118,3 +118,44 @@ def test_flat_fused_attention_entry_is_not_slower_than_the_reference_kernel(nati
         print(f"cf_kv_attn_fused_async, {seq} tokens x {nq} queries, window {window}: {name:17s} {times[name]:9.1f} us")
     assert np.allclose(outs["this library"], outs["reference kernel"], rtol=1e-5, atol=1e-6)
     assert times["this library"] <= times["reference kernel"]
+
+
+def test_paged_attention_entry_can_be_captured_in_a_cuda_graph(native, oracle):
+    """The split-KV form of cf_kv_paged_attention_async hands out slots guarded by events; under stream capture the call
+    keeps to the single launch, so that a caller's CUDA graph still captures it, and replays give the eager result."""
+    import torch
+    hq, hkv, d, page, npages = 32, 8, 128, 128, 8
+    rng = np.random.default_rng(4)
+    made = _fixture_pages(oracle, rng, hkv, d, [page] * npages, 8)
+    if made is None:
+        pytest.skip("needs oracle/_ref (the reference's fixture encoder)")
+    pages, keep, dk, dv = made
+    q = rng.standard_normal((1, hq, d)).astype(np.float32)
+    arr = (DevicePage * len(pages))(*pages)
+    d_pages, d_q = _dev(np.frombuffer(bytes(arr), np.uint8)), _dev(q)
+    desc = PagedAttentionDesc()
+    desc.struct_size, desc.abi_version = C.sizeof(desc), 0
+    desc.pages, desc.page_count = d_pages.data_ptr(), len(pages)
+    desc.kv_head_count, desc.query_head_count, desc.gqa_group_size = hkv, hq, hq // hkv
+    desc.queries, desc.query_token_begin, desc.query_count = d_q.data_ptr(), page * npages - 1, 1
+    desc.head_dim, desc.causal_window, desc.softmax_scale = d, 0, 1.0 / np.sqrt(d)
+    lib = native.lib()
+    eager = torch.zeros((1, hq, d), dtype=torch.float32, device="cuda")
+    desc.output = eager.data_ptr()
+    assert lib.cf_kv_paged_attention_async(C.byref(desc), None) == 0          # split-KV, events
+    torch.cuda.synchronize()
+    captured = torch.zeros_like(eager)
+    desc.output = captured.data_ptr()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        rc = lib.cf_kv_paged_attention_async(C.byref(desc), C.c_void_p(side.cuda_stream))
+        graph.capture_end()
+    assert rc == 0
+    torch.cuda.current_stream().wait_stream(side)
+    assert float(captured.abs().max()) == 0.0                                   # captured, not run
+    graph.replay()
+    torch.cuda.synchronize()
+    assert float((captured - eager).abs().max()) <= 1e-6 and float(eager.abs().max()) > 0
