@@ -298,3 +298,36 @@ def test_dense_comparison_kernel_matches_oracle(native, oracle, hq, hkv):
     dense_attention(layer, pool_k, pool_v, torch.from_numpy(q).cuda(), out)
     ok, err = attention_close(out.cpu().numpy(), np.stack(want))
     assert ok, err
+
+
+@pytest.mark.gpu
+def test_decode_step_replays_from_a_cuda_graph(native, oracle):
+    """The attention call allocates nothing, synchronises nothing and copies nothing between host and device, so a
+    serving loop can capture a decode step (plan, attention, combine) once and replay it: the replay reads the current
+    queries and page tables, and gives the eager result bit for bit."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, info = build_sealed_layer(np.array([640, 1296, 48]), coder="rans", seed=21)
+    q = torch.randn((3, 32, 128), device="cuda").half()
+    out = torch.zeros((3, 32, 128), dtype=torch.float32, device="cuda")
+    eager = layer.attention(q, out=out).clone()                  # also the first call: one-time kernel attributes are set
+    torch.cuda.synchronize()
+    out.zero_()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        layer.attention(q, out=out)
+        graph.capture_end()
+    torch.cuda.current_stream().wait_stream(side)
+    assert float(out.abs().max()) == 0.0                          # captured, not run
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    q.copy_(torch.randn((3, 32, 128), device="cuda").half())     # new queries in the same buffer: the replay sees them
+    graph.replay()
+    torch.cuda.synchronize()
+    again = out.clone()
+    assert torch.equal(again, layer.attention(q).to(again.dtype)) and not torch.equal(again, eager)
+    assert layer.device_status() == 0
