@@ -57,12 +57,17 @@ struct OnlineRow {  // one query head's state in one lane: four channels (lane +
     }
 };
 
+// With `splits` > 1, block (item, kv head * splits + split, query token) takes every splits-th page of the item (split 0
+// also the active tail) and leaves (max, sum, weighted[D]) per query head in `partials`
+// [(item * max_tokens + query token) * query heads + head][split][D + 2] for batch_combine_kernel: a batch of a few long
+// items then still fills the GPU.
 __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_attention_batch_item *items, Shape shape,
-                                                                   unsigned long long *byte_counters) {
+                                                                   unsigned long long *byte_counters, uint32_t splits,
+                                                                   float *partials) {
     __shared__ float s_m[kWarps][kPassHeads], s_l[kWarps][kPassHeads];
     __shared__ float s_acc[kWarps][kPassHeads][128];
     const cf_attention_batch_item item = items[blockIdx.x];
-    const uint32_t kv_head = blockIdx.y, qtok = blockIdx.z;
+    const uint32_t kv_head = blockIdx.y / splits, split = blockIdx.y % splits, qtok = blockIdx.z;
     if (qtok >= item.query.token_count) return;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t D = shape.dim, G = shape.group, HKV = shape.hkv;
@@ -100,7 +105,7 @@ __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_atte
                 row[g].add(cfb::warp_sum(dot), v);
             }
         };
-        for (uint32_t pi = 0; pi < item.sealed_page_count; ++pi) {
+        for (uint32_t pi = split; pi < item.sealed_page_count; pi += splits) {
             const cf_device_page_descriptor page = item.sealed_pages[pi];
             if (!page.key_payload || !page.value_payload || !page.key_scales || !page.value_scales) continue;
             if (page.head_dim != D || page.kv_head_count != HKV || page.block_size == 0) continue;
@@ -123,7 +128,7 @@ __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_atte
                 take(k, v);
             }
         }
-        for (uint32_t t = warp; t < item.active_token_count; t += kWarps) {
+        for (uint32_t t = warp; t < (split == 0 ? item.active_token_count : 0u); t += kWarps) {
             const uint32_t absolute = item.active_token_begin + t;
             if (absolute < first || absolute > qpos) continue;
             const uint64_t flat0 = (static_cast<uint64_t>(t) * HKV + kv_head) * D;
@@ -159,10 +164,20 @@ __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_atte
                     l += s_l[w][g] * sw;
                     a += s_acc[w][g][d] * sw;
                 }
-            store_scalar(item.output,
-                         qtok * item.output_token_stride_bytes + (kv_head * G + g0 + g) * item.output_head_stride_bytes +
-                             d * item.output_element_stride_bytes,
-                         item.output_type, l > 0.0f ? a / l : 0.0f);
+            if (splits > 1) {
+                float *dst = partials + ((static_cast<uint64_t>(blockIdx.x) * gridDim.z + qtok) * shape.hq + kv_head * G + g0 + g) *
+                                            splits * (D + 2u) + split * (D + 2u);
+                if (d == 0) {
+                    dst[0] = m;
+                    dst[1] = l;
+                }
+                dst[2 + d] = a;
+            } else {
+                store_scalar(item.output,
+                             qtok * item.output_token_stride_bytes + (kv_head * G + g0 + g) * item.output_head_stride_bytes +
+                                 d * item.output_element_stride_bytes,
+                             item.output_type, l > 0.0f ? a / l : 0.0f);
+            }
         }
     }
     if (tid == 0 && byte_counters) {
@@ -173,6 +188,30 @@ __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_atte
 
 // CF_ATTENTION_REFERENCE: the plain form the reference's kernel has (production_attention.cu:59-139): one warp per
 // (item, query head, query token), tokens in order, lanes over channels; same nibble and visibility rules as above.
+// One block per (item, query head, query token): merges the splits' partials and writes the item's strided, typed output.
+__global__ void batch_combine_kernel(const cf_attention_batch_item *items, Shape shape, uint32_t splits, const float *partials) {
+    const cf_attention_batch_item item = items[blockIdx.x];
+    const uint32_t head = blockIdx.y, qtok = blockIdx.z, D = shape.dim;
+    if (qtok >= item.query.token_count) return;
+    const float *src = partials + ((static_cast<uint64_t>(blockIdx.x) * gridDim.z + qtok) * shape.hq + head) * splits * (D + 2u);
+    float m = -CUDART_INF_F;
+    for (uint32_t s = 0; s < splits; ++s) m = fmaxf(m, src[s * (D + 2u)]);
+    for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
+        float l = 0.0f, a = 0.0f;
+        if (m != -CUDART_INF_F)
+            for (uint32_t s = 0; s < splits; ++s) {
+                const float *p = src + s * (D + 2u);
+                if (p[0] == -CUDART_INF_F) continue;
+                const float w = exp2f(p[0] - m);
+                l += p[1] * w;
+                a += p[2 + d] * w;
+            }
+        store_scalar(item.output,
+                     qtok * item.output_token_stride_bytes + head * item.output_head_stride_bytes + d * item.output_element_stride_bytes,
+                     item.output_type, l > 0.0f ? a / l : 0.0f);
+    }
+}
+
 __global__ void __launch_bounds__(32) plain_attention_kernel(const cf_attention_batch_item *items, Shape shape) {
     const cf_attention_batch_item item = items[blockIdx.x];
     const uint32_t q_head = blockIdx.y, qtok = blockIdx.z, lane = threadIdx.x;
@@ -276,6 +315,9 @@ struct cf_attention_runtime {
     unsigned long long *byte_counters = nullptr;   // device: payload bytes, scale bytes
     cfb_engine::Buffer<float> scratch_a, scratch_b, compare_result;
     uint64_t reserved_bytes = 0;
+    float *partials = nullptr;     // split partials of the optimized kernel, grow-only
+    uint64_t partial_floats = 0;
+    int sm_count = 0;
 };
 
 namespace {
@@ -352,7 +394,32 @@ void launch(cf_attention_runtime &r, bool optimized, const cf_attention_batch_it
             cuda_check(cudaMalloc(reinterpret_cast<void **>(&r.byte_counters), 16), "byte counters");
             cuda_check(cudaMemsetAsync(r.byte_counters, 0, 16, s), "byte counters");
         }
-        batch_attention_kernel<<<dim3(count, shape.hkv, max_tokens), kThreads, 0, s>>>(device_items, shape, r.byte_counters);
+        // split the pages of every item over enough blocks to fill the GPU when the batch alone does not
+        if (r.sm_count == 0) {
+            int device = 0;
+            cuda_check(cudaGetDevice(&device), "cudaGetDevice");
+            cuda_check(cudaDeviceGetAttribute(&r.sm_count, cudaDevAttrMultiProcessorCount, device), "SM count");
+        }
+        const uint64_t blocks = static_cast<uint64_t>(count) * shape.hkv * max_tokens;
+        const uint32_t splits = static_cast<uint32_t>(std::min<uint64_t>(32, std::max<uint64_t>(1, (2ull * r.sm_count + blocks - 1) / blocks)));
+        if (splits > 1) {
+            const uint64_t floats = static_cast<uint64_t>(count) * max_tokens * shape.hq * splits * (shape.dim + 2u);
+            if (r.partial_floats < floats) {
+                if (r.partials) {
+                    cuda_check(cudaStreamSynchronize(s), "drain before the partials grow");
+                    cudaFree(r.partials);
+                    r.partials = nullptr;
+                    r.reserved_bytes -= r.partial_floats * 4;
+                }
+                cuda_check(cudaMalloc(reinterpret_cast<void **>(&r.partials), floats * 4), "split partials");
+                r.partial_floats = floats;
+                r.reserved_bytes += floats * 4;
+                ++r.counters.allocation_count;
+            }
+        }
+        batch_attention_kernel<<<dim3(count, shape.hkv * splits, max_tokens), kThreads, 0, s>>>(device_items, shape, r.byte_counters, splits,
+                                                                                             r.partials);
+        if (splits > 1) batch_combine_kernel<<<dim3(count, shape.hq, max_tokens), 128, 0, s>>>(device_items, shape, splits, r.partials);
         ++r.counters.optimized_launches;
     } else {
         plain_attention_kernel<<<dim3(count, shape.hq, max_tokens), 32, 0, s>>>(device_items, shape);
@@ -406,6 +473,7 @@ extern "C" void cf_attention_runtime_destroy(cf_attention_runtime *r, void *stre
         if (slot.device) cudaFree(slot.device);
     }
     if (r->byte_counters) cudaFree(r->byte_counters);
+    if (r->partials) cudaFree(r->partials);
     delete r;
 }
 
