@@ -59,6 +59,29 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(uint32_t seq_count, 
     return w;
 }
 
+// One-time set-up of a launcher, kept per device: kernel attributes (the dynamic shared-memory opt-in) and the SM
+// count belong to a device, and one process may drive several. Returns the current device's slot, or nullptr with *error
+// set. Concurrent first calls repeat the same idempotent set-up.
+struct LauncherState {
+    bool configured = false;
+    int sm_count = 0;
+};
+inline LauncherState *launcher_state(LauncherState (&table)[64], cudaError_t *error) {
+    int device = 0;
+    *error = cudaGetDevice(&device);
+    if (*error != cudaSuccess) return nullptr;
+    if (device < 0 || device >= 64) {
+        *error = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    LauncherState *state = &table[device];
+    if (state->sm_count == 0) {
+        *error = cudaDeviceGetAttribute(&state->sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (*error != cudaSuccess) return nullptr;
+    }
+    return state;
+}
+
 // First token a query at `query_token` may see (src/cuda/paged_kv_attention.cu:50-52).
 __host__ __device__ inline uint32_t window_begin(uint32_t query_token, uint32_t causal_window) {
     return causal_window == 0 || query_token + 1u <= causal_window ? 0u : query_token + 1u - causal_window;

@@ -237,20 +237,17 @@ __global__ void __launch_bounds__(kThreads, 1) dense_attention_kernel(AttentionP
 }  // namespace
 
 cudaError_t launch_dense_attention(const AttentionParams &p, cudaStream_t stream) {
-    static int sm_count = 0;
-    static bool configured = false;
-    if (!configured) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
+    static LauncherState table[64];
+    cudaError_t e;
+    LauncherState *state = launcher_state(table, &e);
+    if (!state) return e;
+    if (!state->configured) {
         e = cudaFuncSetAttribute(dense_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kSmemBytes));
         if (e != cudaSuccess) return e;
-        configured = true;
+        state->configured = true;
     }
-    dense_attention_kernel<<<sm_count, kThreads, kSmemBytes, stream>>>(p);
+    dense_attention_kernel<<<state->sm_count, kThreads, kSmemBytes, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

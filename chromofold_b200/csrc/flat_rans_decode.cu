@@ -124,18 +124,16 @@ flat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint
 // ends the last group's bytes).
 cudaError_t launch_flat_rans_decode(const uint8_t *data, const int32_t *byte_off, const uint32_t *state0, const int32_t *slot2sym,
                                     const int32_t *freq, const int32_t *cum, uint32_t groups, int32_t *out, cudaStream_t stream) {
-    static int sm_count = 0;
-    static bool configured = false;
-    if (!configured) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
+    static LauncherState table[64];
+    cudaError_t e;
+    LauncherState *state = launcher_state(table, &e);
+    if (!state) return e;
+    if (!state->configured) {
         e = cudaFuncSetAttribute(flat_rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kFlatSmem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        state->configured = true;
     }
+    const int sm_count = state->sm_count;
     const uint32_t wanted = (groups + kFlatWarps - 1) / kFlatWarps;
     const uint32_t grid = std::max(1u, std::min(wanted, static_cast<uint32_t>(2 * sm_count)));
     flat_rans_decode_kernel<<<grid, kFlatThreads, kFlatSmem, stream>>>(data, byte_off, state0, slot2sym, freq, cum, groups, out);

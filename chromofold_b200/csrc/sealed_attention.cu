@@ -506,16 +506,13 @@ cudaError_t launch_combine(const AttentionParams &p, cudaStream_t stream) {
 }
 
 cudaError_t launch_generic_attention(const AttentionParams &p, cudaStream_t stream) {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
-    }
+    static LauncherState table[64];
+    cudaError_t e;
+    LauncherState *state = launcher_state(table, &e);
+    if (!state) return e;
+    const int sm_count = state->sm_count;
     const GenericSmem lay = generic_smem(p.symbols, p.group, p.head_dim, p.page_tokens);
-    cudaError_t e = cudaFuncSetAttribute(generic_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(generic_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(lay.total));
     if (e != cudaSuccess) return e;
     generic_attention_kernel<<<sm_count * 4, kGenericThreads, lay.total, stream>>>(p);
@@ -587,15 +584,12 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
                            (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
     if (use_lanes && !p.decode_probe && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
-        static int sm_count = 0;
-        if (sm_count == 0) {
-            int device = 0;
-            if (cudaGetDevice(&device) != cudaSuccess ||
-                cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-                return CF_ERR_CUDA;
-        }
+        static cfb::LauncherState table[64];
+        cudaError_t e;
+        const cfb::LauncherState *state = cfb::launcher_state(table, &e);
+        if (!state) return CF_ERR_CUDA;
         p.shared_prefix_pages = d->shared_prefix_pages;
-        p.sm_count = static_cast<uint32_t>(sm_count);
+        p.sm_count = static_cast<uint32_t>(state->sm_count);
     }
     if ((stages & CF_B200_STAGE_PLAN) && cfb::launch_plan(p, s) != cudaSuccess) return CF_ERR_CUDA;
     if (stages & CF_B200_STAGE_ATTENTION) {

@@ -508,14 +508,12 @@ bool lanes_kernel_supports(const AttentionParams &p) {
 // decodes a page once for eight query heads (its query operands live in shared memory instead of registers). fp32
 // queries (the reference's own ABIs pass nothing else) run the split-query kernel, four heads per pass.
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream) {
-    static int sm_count = 0;
-    static bool configured = false;
-    if (!configured) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
+    static LauncherState table[64];
+    cudaError_t e;
+    LauncherState *state = launcher_state(table, &e);
+    if (!state) return e;
+    const int sm_count = state->sm_count;
+    if (!state->configured) {
         e = cudaFuncSetAttribute(lanes_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<1>::kSmem));
         if (e != cudaSuccess) return e;
@@ -528,7 +526,7 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         e = cudaFuncSetAttribute(lanes_attention_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        state->configured = true;
     }
     if (p.decode_probe) lanes_attention_kernel<1, true><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
     else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, false, true><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);

@@ -723,14 +723,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
 }  // namespace
 
 cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t stream) {
-    static int sm_count = 0;
-    static bool configured = false;
-    if (!configured) {
-        int device = 0;
-        cudaError_t e = cudaGetDevice(&device);
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
+    static LauncherState table[64];
+    cudaError_t e;
+    LauncherState *state = launcher_state(table, &e);
+    if (!state) return e;
+    const int sm_count = state->sm_count;
+    if (!state->configured) {
         for (int split = 0; split < 2; ++split) {
             const void *kernel = split ? reinterpret_cast<const void *>(prefix_attention_kernel<true>)
                                        : reinterpret_cast<const void *>(prefix_attention_kernel<false>);
@@ -741,7 +739,7 @@ cudaError_t launch_prefix_attention(const AttentionParams &p, cudaStream_t strea
             if (e != cudaSuccess) return e;
             if (attr.numRegs != kLaunchRegs) return cudaErrorLaunchOutOfResources;   // the register split assumes this count
         }
-        configured = true;
+        state->configured = true;
     }
     if (p.query_type == CF_B200_F32) prefix_attention_kernel<true><<<sm_count, kTcThreads, kTcSmem, stream>>>(p);
     else prefix_attention_kernel<false><<<sm_count, kTcThreads, kTcSmem, stream>>>(p);

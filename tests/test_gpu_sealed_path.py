@@ -331,3 +331,28 @@ def test_decode_step_replays_from_a_cuda_graph(native, oracle):
     again = out.clone()
     assert torch.equal(again, layer.attention(q).to(again.dtype)) and not torch.equal(again, eager)
     assert layer.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_one_process_drives_two_devices(native, oracle):
+    """Kernel attributes (the dynamic shared-memory opt-in) belong to a device: a process that works on a second GPU
+    after the first must find its kernels configured there too. Same layer, same queries on both devices: same bits."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    results = []
+    for index in (0, 1):
+        device = torch.device("cuda", index)
+        with torch.cuda.device(device):
+            layer, info = build_sealed_layer(np.array([512, 2064, 96]), coder="rans", seed=33, device=device)
+            g = torch.Generator(device=device)
+            g.manual_seed(34)
+            q = torch.randn((3, 32, 128), generator=g, device=device).half()
+            outs = [layer.attention(q), layer.attention(q.float()), layer.attention(q, kernel=native.KERNEL_GENERIC),
+                    layer.attention(q, shared_prefix_pages=0)]
+            torch.cuda.synchronize(device)
+            assert layer.device_status() == 0
+            results.append([o.cpu().numpy() for o in outs])
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
