@@ -3,7 +3,8 @@
 //   cf_kv_validate_paged_attention_desc / cf_kv_paged_attention_async   (src/cuda/paged_kv_attention.cu:280-327)
 //   cf_rans_decode_async                                                (src/cuda/rans.cu:38-50)
 // The descriptors are the reference's (one 104-byte descriptor per page and kv head, per-page LUTs, K per-channel and
-// V per-token fp32 scales), so this path keeps their cost; the sealed-KV entry points are the fast path.
+// V per-token fp32 scales), so this path keeps their cost; it is split over the pages of a kv head to fill the GPU
+// and runs faster than the reference's kernels on the same descriptors, but the sealed-KV entry points are the fast path.
 
 #include <mutex>
 #include <algorithm>
