@@ -14,11 +14,11 @@
 namespace {
 
 // Outcome of one bridge call: ok, or refused with a reason.
-struct Verdict {
+struct Outcome {
     bool ok;
     std::string why;
-    static Verdict yes() { return {true, {}}; }
-    static Verdict no(const char *reason) { return {false, reason ? reason : "unknown error"}; }
+    static Outcome yes() { return {true, {}}; }
+    static Outcome no(const char *reason) { return {false, reason ? reason : "unknown error"}; }
 };
 
 // A forwarded call: 0 clears the bridge's error text, anything else copies the owner's.
@@ -49,7 +49,7 @@ struct cf_llama_runtime {
     std::vector<float> head_k, head_v;   // one head's rows, gathered for the adapter's per-head append
 
     // every refused operation is counted (chromofold_runtime_bridge.cpp:20-31)
-    int settle(const Verdict &v) {
+    int settle(const Outcome &v) {
         if (v.ok) {
             error.clear();
             return 0;
@@ -91,20 +91,20 @@ extern "C" void cf_llama_runtime_destroy(cf_llama_runtime *runtime) {
 extern "C" int cf_llama_runtime_append(cf_llama_runtime *runtime, uint32_t layer, uint32_t token_begin, const cf_llama_tensor_view *keys,
                                        const cf_llama_tensor_view *values, void *stream) {
     if (!runtime) return -1;
-    auto run = [&]() -> Verdict {
-        if (!is_chromofold(runtime->options.kv) || !runtime->adapter) return Verdict::no("ChromoFold backend is not selected");
-        if (!packed_f32(keys) || !packed_f32(values)) return Verdict::no("initial runtime bridge requires contiguous fp32 K/V tensors");
+    auto run = [&]() -> Outcome {
+        if (!is_chromofold(runtime->options.kv) || !runtime->adapter) return Outcome::no("ChromoFold backend is not selected");
+        if (!packed_f32(keys) || !packed_f32(values)) return Outcome::no("initial runtime bridge requires contiguous fp32 K/V tensors");
         const cf_llama_kv_options &kv = runtime->options.kv;
         if (keys->token_count != values->token_count || keys->head_count != values->head_count || keys->head_dim != values->head_dim ||
             keys->head_count != kv.kv_head_count || keys->head_dim != kv.head_dim)
-            return Verdict::no("K/V tensor topology does not match configured cache");
+            return Outcome::no("K/V tensor topology does not match configured cache");
         const uint32_t tokens = keys->token_count, heads = keys->head_count, dim = keys->head_dim;
         const float *k = static_cast<const float *>(keys->data), *v = static_cast<const float *>(values->data);
         try {
             runtime->head_k.resize(static_cast<size_t>(tokens) * dim);
             runtime->head_v.resize(static_cast<size_t>(tokens) * dim);
         } catch (...) {
-            return Verdict::no("out of host memory");
+            return Outcome::no("out of host memory");
         }
         for (uint32_t h = 0; h < heads; ++h) {   // the adapter takes one head's rows at a time
             for (uint32_t t = 0; t < tokens; ++t) {
@@ -113,34 +113,34 @@ extern "C" int cf_llama_runtime_append(cf_llama_runtime *runtime, uint32_t layer
                 std::memcpy(&runtime->head_v[dst], v + src, dim * sizeof(float));
             }
             if (cf_llama_kv_append(runtime->adapter, layer, h, token_begin, runtime->head_k.data(), runtime->head_v.data(), tokens, stream) != 0)
-                return Verdict::no(cf_llama_kv_last_error(runtime->adapter));
+                return Outcome::no(cf_llama_kv_last_error(runtime->adapter));
         }
         ++runtime->counters.append_calls;
         runtime->counters.appended_values += static_cast<uint64_t>(tokens) * heads * dim * 2u;
-        return Verdict::yes();
+        return Outcome::yes();
     };
     return runtime->settle(run());
 }
 
 extern "C" int cf_llama_runtime_record_compressed_launch(cf_llama_runtime *runtime, uint64_t sealed_values, uint64_t active_values) {
     if (!runtime) return -1;
-    if (!is_chromofold(runtime->options.kv)) return runtime->settle(Verdict::no("compressed launch recorded for dense backend"));
+    if (!is_chromofold(runtime->options.kv)) return runtime->settle(Outcome::no("compressed launch recorded for dense backend"));
     ++runtime->counters.compressed_attention_launches;
     runtime->counters.sealed_values_consumed += sealed_values;
     runtime->counters.active_values_consumed += active_values;
-    return runtime->settle(Verdict::yes());
+    return runtime->settle(Outcome::yes());
 }
 
 extern "C" int cf_llama_runtime_record_dense_fallback(cf_llama_runtime *runtime) {
     if (!runtime) return -1;
     ++runtime->counters.dense_fallback_launches;   // counted even when it is refused
-    return runtime->settle(runtime->options.allow_dense_fallback ? Verdict::yes() : Verdict::no("dense fallback is disabled"));
+    return runtime->settle(runtime->options.allow_dense_fallback ? Outcome::yes() : Outcome::no("dense fallback is disabled"));
 }
 
 extern "C" int cf_llama_runtime_record_cuda_error(cf_llama_runtime *runtime) {
     if (!runtime) return -1;
     ++runtime->counters.cuda_errors;
-    return runtime->settle(Verdict::no("CUDA execution failed"));   // recording an error is itself reported as one
+    return runtime->settle(Outcome::no("CUDA execution failed"));   // recording an error is itself reported as one
 }
 
 extern "C" int cf_llama_runtime_snapshot_get(const cf_llama_runtime *runtime, cf_llama_runtime_snapshot *snapshot) {
@@ -196,7 +196,7 @@ struct cf_llama_graph_state {
     cf_llama_graph_counters counters{};
     std::string evidence_path, error;
 
-    int settle(const Verdict &v) {   // every refused graph operation is counted (chromofold_graph_contract.cpp:18-31)
+    int settle(const Outcome &v) {   // every refused graph operation is counted (chromofold_graph_contract.cpp:18-31)
         if (v.ok) {
             error.clear();
             return 0;
@@ -265,28 +265,28 @@ extern "C" void cf_llama_graph_destroy(cf_llama_graph_state *state) {
 extern "C" int cf_llama_graph_append_device(cf_llama_graph_state *state, uint32_t layer, uint32_t token_begin,
                                             const cf_llama_tensor_view *keys, const cf_llama_tensor_view *values, void *stream) {
     if (!state) return -1;
-    if (!state->runtime) return state->settle(Verdict::no("ChromoFold graph backend is not active"));
+    if (!state->runtime) return state->settle(Outcome::no("ChromoFold graph backend is not active"));
     if (cf_llama_runtime_append(state->runtime, layer, token_begin, keys, values, stream) != 0)
-        return state->settle(Verdict::no(cf_llama_runtime_last_error(state->runtime)));
+        return state->settle(Outcome::no(cf_llama_runtime_last_error(state->runtime)));
     ++state->counters.graph_append_calls;
-    return state->settle(Verdict::yes());
+    return state->settle(Outcome::yes());
 }
 
 extern "C" int cf_llama_graph_record_attention(cf_llama_graph_state *state, uint64_t sealed_values, uint64_t active_values) {
     if (!state) return -1;
-    if (!state->runtime) return state->settle(Verdict::no("compressed attention recorded without runtime"));
+    if (!state->runtime) return state->settle(Outcome::no("compressed attention recorded without runtime"));
     if (cf_llama_runtime_record_compressed_launch(state->runtime, sealed_values, active_values) != 0)
-        return state->settle(Verdict::no(cf_llama_runtime_last_error(state->runtime)));
+        return state->settle(Outcome::no(cf_llama_runtime_last_error(state->runtime)));
     ++state->counters.graph_attention_dispatches;
-    return state->settle(Verdict::yes());
+    return state->settle(Outcome::yes());
 }
 
 extern "C" int cf_llama_graph_record_dense_dispatch(cf_llama_graph_state *state) {
     if (!state) return -1;
     ++state->counters.graph_dense_dispatches;
-    if (state->options.backend != CF_LLAMA_KV_BACKEND_CHROMOFOLD) return state->settle(Verdict::yes());
+    if (state->options.backend != CF_LLAMA_KV_BACKEND_CHROMOFOLD) return state->settle(Outcome::yes());
     if (state->runtime) cf_llama_runtime_record_dense_fallback(state->runtime);   // shows up in the runtime's evidence too
-    return state->settle(Verdict::no("dense graph dispatch is forbidden for ChromoFold"));
+    return state->settle(Outcome::no("dense graph dispatch is forbidden for ChromoFold"));
 }
 
 extern "C" int cf_llama_graph_get_counters(const cf_llama_graph_state *state, cf_llama_graph_counters *counters) {
