@@ -39,7 +39,7 @@ __device__ __forceinline__ uint32_t visible_pages(const AttentionParams &p, uint
 }
 
 // Shared-prefix hint, part one: block s compares the first `shared_prefix_pages` ids of entry s's page-table row with the
-// first entry's and leaves the verdict (1 = differs) in the entry's cell of the chunk-prefix array, which the plan kernel
+// first entry's and leaves the result (1 = differs) in the entry's cell of the chunk-prefix array, which the plan kernel
 // reads before it overwrites the array with the real prefix sums.
 __global__ void __launch_bounds__(256) verify_prefix_kernel(AttentionParams p) {
     const uint32_t s = blockIdx.x;
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     uint32_t *prefix = chunk_prefix(p);
 
     // Shared prefix: taken only if every listed sequence has the pages sealed and its page-table row starts with the
-    // same ids as the first sequence's (compared by verify_prefix_kernel, verdict per entry in prefix[]). The pages are
+    // same ids as the first sequence's (compared by verify_prefix_kernel, result per entry in prefix[]). The pages are
     // then cut into chunks for the shared-prefix kernel and left out of the per-sequence chunks below.
     uint32_t shared = p.shared_prefix_pages;
     if (shared) {
