@@ -51,7 +51,7 @@ __device__ void decode_block_range(const uint32_t *words, const int32_t *offsets
 }
 
 struct Smem {
-    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, total;
+    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, off_scan, off_match, total;
 };
 __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, uint32_t batch_tokens) {
     Smem s;
@@ -62,12 +62,14 @@ __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, u
     s.off_acc = s.off_qk + group * head_dim * 4;
     s.off_scores = s.off_acc + group * head_dim * 4;
     s.off_ml = s.off_scores + group * batch_tokens * 4;
-    s.total = s.off_ml + group * 8 + 16;
+    s.off_scan = s.off_ml + group * 8 + 16;          // per-thread match counts of the descriptor scan
+    s.off_match = s.off_scan + kThreads * 4;            // indices of this kv head's descriptors, in order (uint16)
+    s.total = s.off_match + 2 * 4096 + 16;              // a call names at most 4096 descriptors
     return s;
 }
 
 // One block per (query row, kv head, split): all query heads of the group share every decoded symbol.
-// Split-KV: with `splits` > 1 block z of a (query row, kv head) takes every splits-th page of its head (split 0 also the
+// Split-KV: with `splits` > 1 block z of a (query row, kv head) takes every splits-th token batch of its head's pages (split 0 also the
 // active tail) and leaves (max, sum, weighted[D]) per query head in `partials`, merged by compat_combine_kernel.
 // The partials live in a fixed array inside the library image (this ABI has no workspace argument and its calls must
 // not allocate): kCompatSlots slots, handed out in turn; a slot is reused only after the call that used it last has
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t query_row = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
-    uint32_t pages_of_head = 0;   // pages of this kv head met so far: page n belongs to split n % splits
+    uint32_t batches_of_head = 0;   // token batches of this kv head's pages met so far: batch n belongs to split n % splits
     const uint32_t query_token = desc.query_token_begin + query_row;
     const uint32_t first_token = window_begin(query_token, desc.causal_window);
 
@@ -141,15 +143,40 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
         __syncthreads();
     };
 
-    for (uint32_t pi = 0; pi < desc.page_count; ++pi) {
-        const cf_kv_device_page page = desc.pages[pi];
-        if (page.kv_head != kv_head || page.head_dim != D) continue;
-        if (pages_of_head++ % splits != split) continue;
+    // The descriptors of this kv head, found by all threads at once (a serial walk over up to 4096 descriptors in global
+    // memory would cost one memory latency each): thread t looks at a contiguous run and the runs' matches are
+    // concatenated in order.
+    uint32_t *scan = reinterpret_cast<uint32_t *>(smem + lay.off_scan);
+    uint16_t *match = reinterpret_cast<uint16_t *>(smem + lay.off_match);
+    const uint32_t run = (desc.page_count + kThreads - 1) / kThreads;
+    const uint32_t run_begin = min(tid * run, desc.page_count), run_end = min(run_begin + run, desc.page_count);
+    uint32_t mine = 0;
+    for (uint32_t pi = run_begin; pi < run_end; ++pi) mine += desc.pages[pi].kv_head == kv_head && desc.pages[pi].head_dim == D;
+    scan[tid] = mine;
+    __syncthreads();
+    uint32_t before = 0, matches = 0;
+    for (uint32_t t = 0; t < kThreads; ++t) {
+        const uint32_t n = scan[t];
+        before += t < tid ? n : 0u;
+        matches += n;
+    }
+    for (uint32_t pi = run_begin; pi < run_end; ++pi)
+        if (desc.pages[pi].kv_head == kv_head && desc.pages[pi].head_dim == D) match[before++] = static_cast<uint16_t>(pi);
+    __syncthreads();
+
+    for (uint32_t mi = 0; mi < matches; ++mi) {
+        const cf_kv_device_page page = desc.pages[match[mi]];
         if (page.token_begin > query_token || page.token_begin + page.token_count <= first_token) continue;
         const uint32_t total = page.token_count * D;
         const int zp = static_cast<int>(page.zero_point);
-        for (uint32_t i = tid; i < G * D; i += kThreads) qk[i] = q[i] * page.k_scales[i % D];
+        bool scaled = false;   // the page's K scales are folded into the queries when its first batch comes up
         for (uint32_t t0 = 0; t0 < page.token_count; t0 += batch_tokens) {
+            if (batches_of_head++ % splits != split) continue;
+            if (!scaled) {
+                __syncthreads();   // the previous page's readers of qk are done
+                for (uint32_t i = tid; i < G * D; i += kThreads) qk[i] = q[i] * page.k_scales[i % D];
+                scaled = true;
+            }
             const uint32_t count = min(batch_tokens, page.token_count - t0);
             const uint32_t lo = t0 * D, hi = (t0 + count) * D;
             const uint32_t b_first = lo / page.block_size, b_last = (hi - 1) / page.block_size;
@@ -230,20 +257,31 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
 
 // One block per (query row, query head): merges the splits' partials (cf_online_softmax_merge rule, scores in log2 units).
 __global__ void compat_combine_kernel(float *output, const float *partials, uint32_t query_heads, uint32_t head_dim, uint32_t splits) {
+    __shared__ float weight[kCompatMaxSplits];
+    __shared__ float total;
     const uint64_t row = static_cast<uint64_t>(blockIdx.x) * query_heads + blockIdx.y;
-    const float *src = partials + row * splits * (head_dim + 2u);
-    float m = -CUDART_INF_F;
-    for (uint32_t s = 0; s < splits; ++s) m = fmaxf(m, src[s * (head_dim + 2u)]);
+    const uint32_t stride = head_dim + 2u;
+    const float *src = partials + row * splits * stride;
+    if (threadIdx.x < 32) {   // one warp: the splits' maxima and sums, in parallel over the splits
+        float m = -CUDART_INF_F;
+        for (uint32_t s = threadIdx.x; s < splits; s += 32) m = fmaxf(m, src[s * stride]);
+        m = warp_max(m);
+        float l = 0.0f;
+        for (uint32_t s = threadIdx.x; s < splits; s += 32) {
+            const float ms = src[s * stride];
+            const float w = ms == -CUDART_INF_F ? 0.0f : exp2f(ms - m);
+            weight[s] = w;
+            l += src[s * stride + 1] * w;
+        }
+        l = warp_sum(l);
+        if (threadIdx.x == 0) total = l;
+    }
+    __syncthreads();
+    const float l = total;
     for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float l = 0.0f, a = 0.0f;
-        if (m != -CUDART_INF_F)
-            for (uint32_t s = 0; s < splits; ++s) {
-                const float *p = src + s * (head_dim + 2u);
-                if (p[0] == -CUDART_INF_F) continue;
-                const float w = exp2f(p[0] - m);
-                l += p[1] * w;
-                a += p[2 + d] * w;
-            }
+        float a = 0.0f;
+#pragma unroll 8
+        for (uint32_t s = 0; s < splits; ++s) a += src[s * stride + 2 + d] * weight[s];   // independent loads
         output[row * head_dim + d] = l > 0.0f ? a / l : 0.0f;   // no visible token: zeros
     }
 }
@@ -450,10 +488,9 @@ extern "C" cf_status cf_kv_paged_attention_async(const cf_kv_paged_attention_des
             slots->made = true;
         }
         const uint64_t pairs = static_cast<uint64_t>(d->query_count) * d->kv_head_count;
-        const uint64_t pages_per_head = std::max<uint64_t>(d->page_count / d->kv_head_count, 1);
         const uint64_t room = cfb::kCompatSlotFloats / (static_cast<uint64_t>(d->query_count) * d->query_head_count * (d->head_dim + 2u));
         const uint64_t wanted = (2ull * slots->sm_count + pairs - 1) / pairs;
-        splits = static_cast<uint32_t>(std::max<uint64_t>(1, std::min({wanted, pages_per_head, room, static_cast<uint64_t>(cfb::kCompatMaxSplits)})));
+        splits = static_cast<uint32_t>(std::max<uint64_t>(1, std::min({wanted, room, static_cast<uint64_t>(cfb::kCompatMaxSplits)})));
         if (splits > 1) {
             slot = slots->next++ % cfb::kCompatSlots;
             if (cudaStreamWaitEvent(s, slots->done[slot], 0) != cudaSuccess) return CF_ERR_CUDA;   // the slot's last user

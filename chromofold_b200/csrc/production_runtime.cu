@@ -190,22 +190,26 @@ __global__ void __launch_bounds__(kThreads) batch_attention_kernel(const cf_atte
 // (item, query head, query token), tokens in order, lanes over channels; same nibble and visibility rules as above.
 // One block per (item, query head, query token): merges the splits' partials and writes the item's strided, typed output.
 __global__ void batch_combine_kernel(const cf_attention_batch_item *items, Shape shape, uint32_t splits, const float *partials) {
+    __shared__ float weight[32];   // splits <= 32
+    __shared__ float total;
     const cf_attention_batch_item item = items[blockIdx.x];
-    const uint32_t head = blockIdx.y, qtok = blockIdx.z, D = shape.dim;
+    const uint32_t head = blockIdx.y, qtok = blockIdx.z, D = shape.dim, stride = D + 2u;
     if (qtok >= item.query.token_count) return;
-    const float *src = partials + ((static_cast<uint64_t>(blockIdx.x) * gridDim.z + qtok) * shape.hq + head) * splits * (D + 2u);
-    float m = -CUDART_INF_F;
-    for (uint32_t s = 0; s < splits; ++s) m = fmaxf(m, src[s * (D + 2u)]);
+    const float *src = partials + ((static_cast<uint64_t>(blockIdx.x) * gridDim.z + qtok) * shape.hq + head) * splits * stride;
+    if (threadIdx.x < 32) {   // one warp: the splits' maxima and sums, in parallel over the splits
+        const float ms = threadIdx.x < splits ? src[threadIdx.x * stride] : -CUDART_INF_F;
+        const float m = cfb::warp_max(ms);
+        const float w = ms == -CUDART_INF_F ? 0.0f : exp2f(ms - m);
+        if (threadIdx.x < splits) weight[threadIdx.x] = w;
+        const float l = cfb::warp_sum(threadIdx.x < splits ? src[threadIdx.x * stride + 1] * w : 0.0f);
+        if (threadIdx.x == 0) total = l;
+    }
+    __syncthreads();
+    const float l = total;
     for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
-        float l = 0.0f, a = 0.0f;
-        if (m != -CUDART_INF_F)
-            for (uint32_t s = 0; s < splits; ++s) {
-                const float *p = src + s * (D + 2u);
-                if (p[0] == -CUDART_INF_F) continue;
-                const float w = exp2f(p[0] - m);
-                l += p[1] * w;
-                a += p[2 + d] * w;
-            }
+        float a = 0.0f;
+#pragma unroll 8
+        for (uint32_t s = 0; s < splits; ++s) a += src[s * stride + 2 + d] * weight[s];   // independent loads
         store_scalar(item.output,
                      qtok * item.output_token_stride_bytes + head * item.output_head_stride_bytes + d * item.output_element_stride_bytes,
                      item.output_type, l > 0.0f ? a / l : 0.0f);
