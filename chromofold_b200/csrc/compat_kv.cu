@@ -51,7 +51,7 @@ __device__ void decode_block_range(const uint32_t *words, const int32_t *offsets
 }
 
 struct Smem {
-    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, off_scan, off_match, total;
+    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, off_scan, off_match, off_tokens, total;
 };
 __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, uint32_t batch_tokens) {
     Smem s;
@@ -64,7 +64,8 @@ __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, u
     s.off_ml = s.off_scores + group * batch_tokens * 4;
     s.off_scan = s.off_ml + group * 8 + 16;          // per-thread match counts of the descriptor scan
     s.off_match = s.off_scan + kThreads * 4;            // indices of this kv head's descriptors, in order (uint16)
-    s.total = s.off_match + 2 * 4096 + 16;              // a call names at most 4096 descriptors
+    s.off_tokens = s.off_match + 2 * 4096;              // their token counts (uint32); a call names at most 4096 descriptors
+    s.total = s.off_tokens + 4 * 4096 + 16;
     return s;
 }
 
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     // concatenated in order.
     uint32_t *scan = reinterpret_cast<uint32_t *>(smem + lay.off_scan);
     uint16_t *match = reinterpret_cast<uint16_t *>(smem + lay.off_match);
+    uint32_t *match_tokens = reinterpret_cast<uint32_t *>(smem + lay.off_tokens);
     const uint32_t run = (desc.page_count + kThreads - 1) / kThreads;
     const uint32_t run_begin = min(tid * run, desc.page_count), run_end = min(run_begin + run, desc.page_count);
     uint32_t mine = 0;
@@ -161,12 +163,26 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
         matches += n;
     }
     for (uint32_t pi = run_begin; pi < run_end; ++pi)
-        if (desc.pages[pi].kv_head == kv_head && desc.pages[pi].head_dim == D) match[before++] = static_cast<uint16_t>(pi);
+        if (desc.pages[pi].kv_head == kv_head && desc.pages[pi].head_dim == D) {
+            match[before] = static_cast<uint16_t>(pi);
+            match_tokens[before++] = desc.pages[pi].token_count;
+        }
     __syncthreads();
 
     for (uint32_t mi = 0; mi < matches; ++mi) {
+        // Two fields decide whether any token batch of the page is this split's; only then is the descriptor read whole.
+        // Every block counts the batches of every page of the head the same way, whether it works on them or not.
+        const uint32_t page_batches = (match_tokens[mi] + batch_tokens - 1) / batch_tokens;
+        const uint32_t first_mine = (split + splits - batches_of_head % splits) % splits;   // offset of this split's next batch
+        if (first_mine >= page_batches) {
+            batches_of_head += page_batches;
+            continue;
+        }
         const cf_kv_device_page page = desc.pages[match[mi]];
-        if (page.token_begin > query_token || page.token_begin + page.token_count <= first_token) continue;
+        if (page.token_begin > query_token || page.token_begin + page.token_count <= first_token) {
+            batches_of_head += page_batches;
+            continue;
+        }
         const uint32_t total = page.token_count * D;
         const int zp = static_cast<int>(page.zero_point);
         bool scaled = false;   // the page's K scales are folded into the queries when its first batch comes up
