@@ -33,9 +33,17 @@ __device__ void decode_block_range(const uint32_t *words, const int32_t *offsets
     const uint32_t last = min(first + block_size, total);
     if (fixed_bits) {  // symbol i sits at bit i * fixed_bits, never crossing a word (kv_gpu_fixture.cpp:36-40)
         const uint32_t mask = (1u << fixed_bits) - 1u;
-        for (uint32_t i = max(first, lo); i < min(last, hi); ++i) {
+        uint32_t i = max(first, lo);
+        const uint32_t end = min(last, hi);
+        while (i < end) {   // one load per word, every symbol of the word that is wanted
             const uint32_t bit = i * fixed_bits;
-            emit(i, (words[bit >> 5] >> ((32u - fixed_bits) - (bit & 31u))) & mask);
+            const uint32_t w = words[bit >> 5];
+            uint32_t pos = bit & 31u;
+            do {
+                emit(i, (w >> ((32u - fixed_bits) - pos)) & mask);
+                ++i;
+                pos += fixed_bits;
+            } while (pos + fixed_bits <= 32u && i < end);
         }
         return;
     }
@@ -51,7 +59,7 @@ __device__ void decode_block_range(const uint32_t *words, const int32_t *offsets
 }
 
 struct Smem {
-    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, off_scan, off_match, off_tokens, total;
+    uint32_t off_ksym, off_vsym, off_q, off_qk, off_acc, off_scores, off_ml, off_alpha, off_scan, off_match, off_tokens, total;
 };
 __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, uint32_t batch_tokens) {
     Smem s;
@@ -62,7 +70,8 @@ __host__ __device__ inline Smem smem_layout(uint32_t group, uint32_t head_dim, u
     s.off_acc = s.off_qk + group * head_dim * 4;
     s.off_scores = s.off_acc + group * head_dim * 4;
     s.off_ml = s.off_scores + group * batch_tokens * 4;
-    s.off_scan = s.off_ml + group * 8 + 16;          // per-thread match counts of the descriptor scan
+    s.off_alpha = s.off_ml + group * 8 + 16;         // per query head: factor of the running sums in the current update
+    s.off_scan = s.off_alpha + group * 4 + 16;       // per-thread match counts of the descriptor scan
     s.off_match = s.off_scan + kThreads * 4;            // indices of this kv head's descriptors, in order (uint16)
     s.off_tokens = s.off_match + 2 * 4096;              // their token counts (uint32); a call names at most 4096 descriptors
     s.total = s.off_tokens + 4 * 4096 + 16;
@@ -93,6 +102,7 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     float *acc = reinterpret_cast<float *>(smem + lay.off_acc);
     float *scores = reinterpret_cast<float *>(smem + lay.off_scores);
     float *ml = reinterpret_cast<float *>(smem + lay.off_ml);
+    float *alpha_s = reinterpret_cast<float *>(smem + lay.off_alpha);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t query_row = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
@@ -112,35 +122,45 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
     }
     __syncthreads();
 
-    // Online-softmax update from scores[g][0..count) and a value getter; every thread owns channel `tid`.
-    auto update = [&](uint32_t count, auto value_of) {
-        float new_m[kMaxGroup], new_l[kMaxGroup];
-        for (uint32_t g = 0; g < G; ++g) {
+    // Online-softmax update from scores[g][0..count). First the weights, once: warp w takes query heads w, w + 4, ...,
+    // its lanes the tokens; scores[g][t] becomes exp2(s - max) * scale_of(t) (the V scale of the token rides on the
+    // weight) and (max, sum) move on. Then thread d adds its channel: acc[g][d] = acc * alpha + sum_t weight * value.
+    auto update = [&](uint32_t count, auto raw_value_of, auto scale_of) {
+        for (uint32_t g = warp; g < G; g += kThreads / 32) {
+            float *row = scores + g * batch_tokens;
             const float m_old = ml[2 * g], l_old = ml[2 * g + 1];
             float pm = -CUDART_INF_F;
-            for (uint32_t t = 0; t < count; ++t) pm = fmaxf(pm, scores[g * batch_tokens + t]);
-            const float m_new = fmaxf(m_old, pm);
-            new_m[g] = m_new;
-            new_l[g] = l_old;
-            if (m_new == -CUDART_INF_F) continue;
-            const float alpha = m_old == -CUDART_INF_F ? 0.0f : exp2f(m_old - m_new);
-            float lsum = 0.0f, a = 0.0f;
-            for (uint32_t t = 0; t < count; ++t) {
-                const float s = scores[g * batch_tokens + t];
-                if (s == -CUDART_INF_F) continue;
-                const float w = exp2f(s - m_new);
+            for (uint32_t t = lane; t < count; t += 32) pm = fmaxf(pm, row[t]);
+            const float m_new = fmaxf(m_old, warp_max(pm));
+            float lsum = 0.0f;
+            for (uint32_t t = lane; t < count; t += 32) {
+                const float sc = row[t];
+                const float w = sc == -CUDART_INF_F ? 0.0f : exp2f(sc - m_new);   // m_new is finite whenever sc is
                 lsum += w;
-                if (tid < D) a += w * value_of(t, tid);
+                row[t] = w * scale_of(t);
             }
-            new_l[g] = l_old * alpha + lsum;
-            if (tid < D) acc[g * D + tid] = acc[g * D + tid] * alpha + a;
+            lsum = warp_sum(lsum);
+            if (lane == 0) {
+                const float alpha = m_old == -CUDART_INF_F ? 0.0f : exp2f(m_old - m_new);   // nothing visible so far: 0 * 0
+                ml[2 * g] = m_new;
+                ml[2 * g + 1] = m_new == -CUDART_INF_F ? l_old : l_old * alpha + lsum;
+                alpha_s[g] = m_new == -CUDART_INF_F ? 1.0f : alpha;
+            }
         }
         __syncthreads();
-        if (tid == 0)
+        if (tid < D) {
             for (uint32_t g = 0; g < G; ++g) {
-                ml[2 * g] = new_m[g];
-                ml[2 * g + 1] = new_l[g];
+                const float *row = scores + g * batch_tokens;
+                float a0 = 0.0f, a1 = 0.0f;
+                uint32_t t = 0;
+                for (; t + 1 < count; t += 2) {
+                    a0 += row[t] * raw_value_of(t, tid);
+                    a1 += row[t + 1] * raw_value_of(t + 1, tid);
+                }
+                if (t < count) a0 += row[t] * raw_value_of(t, tid);
+                acc[g * D + tid] = acc[g * D + tid] * alpha_s[g] + (a0 + a1);
             }
+        }
         __syncthreads();
     };
 
@@ -209,22 +229,29 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
                                        [&](uint32_t i, uint32_t s) { ksym[i - lo] = static_cast<uint8_t>(s); });
             }
             __syncthreads();
-            for (uint32_t pair = warp; pair < G * count; pair += kThreads / 32) {
-                const uint32_t g = pair / count, t = pair % count;
+            for (uint32_t t = warp; t < count; t += kThreads / 32) {   // a warp per token: its codes are read once for all heads
                 const uint32_t token = page.token_begin + t0 + t;
-                float s = -CUDART_INF_F;
-                if (token >= first_token && token <= query_token) {
-                    float dot = 0.0f;
-                    for (uint32_t d = lane; d < D; d += 32)
-                        dot += qk[g * D + d] * static_cast<float>(static_cast<int>(ksym[t * D + d]) - zp);
-                    s = warp_sum(dot);
+                const bool visible = token >= first_token && token <= query_token;
+                float k[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t d = lane + 32u * j;
+                    k[j] = visible && d < D ? static_cast<float>(static_cast<int>(ksym[t * D + d]) - zp) : 0.0f;
                 }
-                if (lane == 0) scores[g * batch_tokens + t] = s;
+                for (uint32_t g = 0; g < G; ++g) {
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t d = lane + 32u * j;
+                        if (d < D) dot += qk[g * D + d] * k[j];
+                    }
+                    dot = warp_sum(dot);
+                    if (lane == 0) scores[g * batch_tokens + t] = visible ? dot : -CUDART_INF_F;
+                }
             }
             __syncthreads();
-            update(count, [&](uint32_t t, uint32_t d) {
-                return static_cast<float>(static_cast<int>(vsym[t * D + d]) - zp) * page.v_scales[t0 + t];
-            });
+            update(count, [&](uint32_t t, uint32_t d) { return static_cast<float>(static_cast<int>(vsym[t * D + d]) - zp); },
+                   [&](uint32_t t) { return page.v_scales[t0 + t]; });
         }
     }
 
@@ -246,9 +273,9 @@ __global__ void __launch_bounds__(kThreads) compat_paged_attention_kernel(cf_kv_
             if (lane == 0) scores[g * batch_tokens + t] = s;
         }
         __syncthreads();
-        update(count, [&](uint32_t t, uint32_t d) {
-            return desc.active_v[(static_cast<uint64_t>(t0 + t) * desc.kv_head_count + kv_head) * D + d];
-        });
+        update(count,
+               [&](uint32_t t, uint32_t d) { return desc.active_v[(static_cast<uint64_t>(t0 + t) * desc.kv_head_count + kv_head) * D + d]; },
+               [&](uint32_t) { return 1.0f; });
     }
 
     if (splits > 1) {
