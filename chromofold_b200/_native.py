@@ -12,7 +12,7 @@ CF_OK, CF_ERR_INVALID_ARGUMENT, CF_ERR_UNSUPPORTED, CF_ERR_CUDA = 0, 1, 2, 3
 ABI_VERSION = 1
 F16, BF16, F32 = 1, 2, 3
 CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES, KERNEL_DECODE_PROBE = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES, KERNEL_DECODE_PROBE, KERNEL_DECODE_DUMP = 0, 1, 2, 3, 4
 STATIC_WORKSPACE_BYTES = 8 << 20
 STAGE_PLAN, STAGE_ATTENTION, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 7
 DEVSTAT_BAD_RECORD, DEVSTAT_WAIT_EXPIRED, DEVSTAT_WORKSPACE, DEVSTAT_NONFINITE, DEVSTAT_ARENA_FULL = 1, 2, 4, 8, 16

@@ -308,6 +308,24 @@ class SealedKvLayer:
             raise N.CfError(self.lib.cf_b200_sealed_attention_static_error().decode(), status)
         return out
 
+    def dump_lane_decoders(self, queries, slots=None, *, shared_prefix_pages=0, query_positions=None):
+        """Test aid (CF_B200_KERNEL_DECODE_DUMP): run the plan and the attention kernels of a call on `queries`, with the
+        lane-per-block decoders of the attention kernels storing every symbol they decode instead of consuming it.
+        Returns uint8 [page ids][kv_heads][2 (K, V)][page_tokens*head_dim]; pages the call does not reach stay 0xFF."""
+        n = queries.shape[0]
+        page_ids = self.page_dir.numel() // self.kv_heads
+        dump = torch.full((page_ids, self.kv_heads, 2, self.page_tokens * self.head_dim), 0xFF, dtype=torch.uint8,
+                          device=self.device)
+        d = self._attention_desc(queries, dump, n, slots)
+        d.softmax_scale = 1.0
+        d.kernel, d.reserved0 = N.KERNEL_DECODE_DUMP, page_ids
+        d.shared_prefix_pages = shared_prefix_pages
+        if query_positions is not None:
+            d.query_positions = query_positions.data_ptr()
+        N.check("decode dump", self.lib.cf_b200_sealed_attention_stages_async(
+            C.byref(d), C.c_uint32(N.STAGE_PLAN | N.STAGE_ATTENTION), _stream_ptr()))
+        return dump
+
     def decode_pages(self, page_ids):
         """Decode whole records to symbols on the GPU: returns (k, v) uint8 [pages, kv_heads, page_tokens*head_dim]."""
         ids = torch.as_tensor(np.asarray(page_ids, np.int32), device=self.device)

@@ -36,7 +36,9 @@ struct AttentionParams {
     uint32_t min_pages_per_unit;
     uint32_t shared_prefix_pages;   // the caller's hint, already zeroed when the launch cannot use it
     uint32_t sm_count;
-    uint32_t decode_probe;          // measurement: decode every page, fold the symbols into a checksum, no attention
+    uint32_t decode_probe;          // 1 = measurement: decode every page, fold the symbols into a checksum, no attention;
+                                    // 2 = test: store every decoded symbol to `output` ([page id][kv head][K | V stream])
+    uint32_t dump_pages;            // page ids the dump buffer covers (1 when decode_probe != 2)
     uint32_t *status;
     // uncompressed comparison pools (dense kernel only)
     const __half *pool_k, *pool_v;

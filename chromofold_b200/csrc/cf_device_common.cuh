@@ -105,14 +105,18 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // One rANS symbol: src/cuda/rans.cu:20-23 with the three table reads folded into one packed word
 // (sym | freq << 8 | (slot - cum) << 20).
+// Records are not trusted: a start offset past the payload is pulled back to its end, bytes past the end read as 0, and
+// the renormalisation runs at most three times per symbol (a valid stream needs two: the state is >= 2^11 after the
+// update), so a corrupt record yields wrong symbols but neither a stray read nor an endless loop.
 template <class Emit>
-__device__ __forceinline__ void rans_decode_block(const uint8_t *payload, uint32_t pos, uint32_t state,
+__device__ __forceinline__ void rans_decode_block(const uint8_t *payload, uint32_t payload_bytes, uint32_t pos, uint32_t state,
                                                   const uint32_t *slot_table, int count, Emit emit) {
+    pos = min(pos, payload_bytes);
     for (int j = 0; j < count; ++j) {
         const uint32_t e = slot_table[state & (CF_B200_RANS_M - 1u)];
         state = ((e >> 8) & 0xfffu) * (state >> CF_B200_RANS_PROB_BITS) + (e >> 20);
-        while (state < kRansL) {
-            state = (state << 8) | payload[pos];
+        for (int r = 0; r < 3 && state < kRansL; ++r) {
+            state = (state << 8) | (pos < payload_bytes ? payload[pos] : 0u);
             ++pos;
         }
         emit(j, e & 0xffu);
@@ -122,11 +126,12 @@ __device__ __forceinline__ void rans_decode_block(const uint8_t *payload, uint32
 // One Huffman symbol per step: the next 12 bits MSB-first index the LUT
 // (include/chromofold/detail/block_huffman_device.cuh:12-19), read here from two words at once.
 template <class Emit>
-__device__ __forceinline__ void huffman_decode_block(const uint32_t *words, uint32_t bit, const uint16_t *lut,
+__device__ __forceinline__ void huffman_decode_block(const uint32_t *words, uint32_t word_count, uint32_t bit, const uint16_t *lut,
                                                      int count, Emit emit) {
+    bit = min(bit, 32u * word_count);   // an untrusted start offset stays inside the part; words past its end read as 0
     for (int j = 0; j < count; ++j) {
         const uint32_t w = bit >> 5;
-        const uint64_t two = (static_cast<uint64_t>(words[w]) << 32) | words[w + 1];
+        const uint64_t two = (static_cast<uint64_t>(w < word_count ? words[w] : 0u) << 32) | (w + 1u < word_count ? words[w + 1] : 0u);
         const uint32_t look = static_cast<uint32_t>(two >> (64u - CF_B200_HUFF_MAXLEN - (bit & 31u))) &
                               (CF_B200_HUFF_LUT_SIZE - 1u);
         const uint32_t sl = lut[look];
@@ -145,10 +150,24 @@ __device__ __forceinline__ void fixed8_decode_block(const uint32_t *words, uint3
     }
 }
 
-// Decode block `b` of one stream part (layout in sealed_page_format.h). `part` must be 16-byte aligned and readable
-// 8 bytes past its end.
+// Start offset of block `b` against the part's length: false = the record's block table is corrupt.
+__device__ __forceinline__ bool part_block_start_ok(const uint8_t *part, uint32_t part_bytes, uint32_t coder, uint32_t nblocks,
+                                                    uint32_t b, uint32_t symbols) {
+    if (coder == CF_B200_CODER_RANS) {
+        const uint32_t head = align_up_u32(6u * nblocks, 4u);
+        return part_bytes >= head && reinterpret_cast<const uint16_t *>(part + 4u * nblocks)[b] <= part_bytes - head;
+    }
+    if (coder == CF_B200_CODER_HUFFMAN) {
+        const uint32_t head = align_up_u32(2u * nblocks, 4u);
+        return part_bytes >= head && reinterpret_cast<const uint16_t *>(part)[b] <= 8u * (part_bytes - head);
+    }
+    return part_bytes >= align_up_u32(symbols, 4u);
+}
+
+// Decode block `b` of one stream part of part_bytes bytes (layout in sealed_page_format.h). `part` must be 16-byte
+// aligned. Nothing outside [part, part + part_bytes) is read, whatever the part's block table says.
 template <class Emit>
-__device__ __forceinline__ void decode_part_block(const uint8_t *part, uint32_t coder, uint32_t nblocks, uint32_t b,
+__device__ __forceinline__ void decode_part_block(const uint8_t *part, uint32_t part_bytes, uint32_t coder, uint32_t nblocks, uint32_t b,
                                                   uint32_t block_size, uint32_t symbols,
                                                   const cf_b200_codebook_tables *tables, Emit emit) {
     const uint32_t base = b * block_size;
@@ -156,13 +175,17 @@ __device__ __forceinline__ void decode_part_block(const uint8_t *part, uint32_t 
     if (coder == CF_B200_CODER_RANS) {
         const uint32_t *state0 = reinterpret_cast<const uint32_t *>(part);
         const uint16_t *off = reinterpret_cast<const uint16_t *>(part + 4u * nblocks);
-        const uint8_t *payload = part + align_up_u32(6u * nblocks, 4u);
-        rans_decode_block(payload, off[b], state0[b], tables->rans_slot, count, emit);
+        const uint32_t head = align_up_u32(6u * nblocks, 4u);
+        if (part_bytes < head) return;
+        rans_decode_block(part + head, part_bytes - head, off[b], state0[b], tables->rans_slot, count, emit);
     } else if (coder == CF_B200_CODER_HUFFMAN) {
         const uint16_t *off = reinterpret_cast<const uint16_t *>(part);
-        const uint32_t *words = reinterpret_cast<const uint32_t *>(part + align_up_u32(2u * nblocks, 4u));
-        huffman_decode_block(words, off[b], tables->huff_lut, count, emit);
+        const uint32_t head = align_up_u32(2u * nblocks, 4u);
+        if (part_bytes < head) return;
+        huffman_decode_block(reinterpret_cast<const uint32_t *>(part + head), (part_bytes - head) / 4u, off[b], tables->huff_lut,
+                             count, emit);
     } else {
+        if (part_bytes < align_up_u32(symbols, 4u)) return;
         fixed8_decode_block(reinterpret_cast<const uint32_t *>(part), base, count, emit);
     }
 }

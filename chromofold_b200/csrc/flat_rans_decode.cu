@@ -67,8 +67,12 @@ flat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint
             const uint32_t skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(data + start) & 3u), length = end - start;
             fits = end >= start && skew + length + 16u <= kPartPayload;   // whole words are copied: the bytes keep their alignment
             if (!fits) break;
+            // the ABI does not promise ordered offsets: a block that starts outside [start, end] sends the group the slow way
+            const uint32_t mine_off = static_cast<uint32_t>(byte_off[first + lane]);
+            fits = __all_sync(0xffffffffu, mine_off >= start && mine_off <= end);
+            if (!fits) break;
             reinterpret_cast<uint32_t *>(dst)[lane] = state0[first + lane];
-            reinterpret_cast<uint16_t *>(dst + 128)[lane] = static_cast<uint16_t>(static_cast<uint32_t>(byte_off[first + lane]) - start + skew);
+            reinterpret_cast<uint16_t *>(dst + 128)[lane] = static_cast<uint16_t>(mine_off - start + skew);
             const uint32_t *src = reinterpret_cast<const uint32_t *>(data + (start - skew));
             uint32_t *payload = reinterpret_cast<uint32_t *>(dst + 192);
             for (uint32_t w = lane; w < (skew + length + 3u) / 4u; w += 32u) payload[w] = src[w];
@@ -82,16 +86,19 @@ flat_rans_decode_kernel(const uint8_t *data, const int32_t *byte_off, const uint
                 for (uint32_t j = 0; j < 64u; ++j) {
                     const uint32_t slot = x & (CF_B200_RANS_M - 1u);
                     const int s = slot2sym[slot];
-                    x = static_cast<uint32_t>(freq[s]) * (x >> CF_B200_RANS_PROB_BITS) + slot - static_cast<uint32_t>(cum[s]);
-                    while (x < (1u << 23)) x = (x << 8) | *bytes++;
+                    const uint32_t si = static_cast<uint32_t>(s) & 255u;   // a symbol outside the tables must not index past them
+                    x = static_cast<uint32_t>(freq[si]) * (x >> CF_B200_RANS_PROB_BITS) + slot - static_cast<uint32_t>(cum[si]);
+                    // a valid stream needs at most two bytes here (the state is >= 2^11 after the update); the bound keeps
+                    // a corrupt table (frequency 0) from reading on without end
+                    for (int r = 0; r < 3 && x < (1u << 23); ++r) x = (x << 8) | *bytes++;
                     out[static_cast<uint64_t>(b) * 64u + j] = s;
                 }
             }
             continue;
         }
         RansLane a, b;   // blocks b0 + lane and b0 + 32 + lane
-        a.open(mine, lane, table);
-        b.open(mine + kPartBytes, lane, table);
+        a.open(mine, kPartBytes, lane, table);
+        b.open(mine + kPartBytes, kPartBytes, lane, table);
 #pragma unroll 4
         for (uint32_t q = 0; q < 16; ++q) {
             a.reload();

@@ -92,9 +92,13 @@ struct RansLane {
     uint32_t x, whi, wlo, used;   // state; window (next byte = top byte of whi); bits taken since the reload
     uint32_t pos;                 // shared-memory byte address of the first byte not yet taken at the last reload
     uint32_t table;               // shared-memory byte address of the slot table
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint32_t *slot_table) {
+    // The block's start offset is clamped to the part (part_bytes from the record header): whatever the block table
+    // says, the decoder starts inside its own part, and from there a block takes at most 64 * 2 bytes plus one
+    // 12-byte window, which stays inside the warp's own shared memory (part_offsets_ok reports the bad table).
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint32_t *slot_table) {
         x = reinterpret_cast<const uint32_t *>(part)[lane];
-        pos = smem_addr(part) + 192u + reinterpret_cast<const uint16_t *>(part + 128)[lane];
+        const uint32_t payload = part_bytes > 192u ? part_bytes - 192u : 0u;
+        pos = smem_addr(part) + 192u + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 128)[lane]), payload);
         table = smem_addr(slot_table);
         used = 0;
     }
@@ -138,8 +142,10 @@ struct HuffLane {
     uint32_t whi, wlo, used;   // window of upcoming bits, MSB first; bits taken since the reload
     uint32_t words, bit;       // shared-memory address of the payload words; bit position at the last reload
     uint32_t table;
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane, const uint16_t *lut) {
-        bit = reinterpret_cast<const uint16_t *>(part)[lane];
+    // Start offset clamped to the part as in RansLane::open; a block takes at most 64 * 12 bits plus one window.
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint16_t *lut) {
+        const uint32_t payload_bits = part_bytes > 64u ? (part_bytes - 64u) * 8u : 0u;
+        bit = min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part)[lane]), payload_bits);
         words = smem_addr(part) + 64u;
         table = smem_addr(lut);
         used = 0;
@@ -176,7 +182,8 @@ struct FixedLane {
     static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
     static constexpr int kSymbolsPerReload = 4;
     const uint32_t *words;
-    __device__ __forceinline__ void open(const uint8_t *part, uint32_t lane) {
+    // A fixed-width part is 2048 bytes at a 16-byte aligned offset of at most 16 + 2048 into the stage: always inside it.
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t, uint32_t lane) {
         words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
     }
     // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
@@ -209,6 +216,17 @@ __device__ __forceinline__ bool record_header_ok(const uint4 &hv, uint64_t dir_e
     return version == CF_B200_FORMAT_VERSION && codebook == codebook_id &&
            1u + k_units + v_units == CF_B200_DIR_LENGTH_UNITS(dir_entry) && k_units <= 128u && v_units <= 128u &&
            k_coder <= 2u && v_coder <= 2u && token_count >= 1u && token_count <= 16u;
+}
+
+// The block table of a staged part against the part's length: lane l checks the start of block l. The reference
+// validates its descriptors on the host before the launch (src/cuda/paged_kv_attention.cu:280-299); records here are
+// written by the sealer, by import or by unpack, so the check runs where the table is read.
+__device__ __forceinline__ bool part_offsets_ok(const uint8_t *part, uint32_t coder, uint32_t part_bytes, uint32_t lane) {
+    if (coder == CF_B200_CODER_RANS)
+        return part_bytes >= 192u && reinterpret_cast<const uint16_t *>(part + 128)[lane] <= part_bytes - 192u;
+    if (coder == CF_B200_CODER_HUFFMAN)
+        return part_bytes >= 64u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - 64u) * 8u;
+    return part_bytes == 2048u;
 }
 
 }  // namespace lanes

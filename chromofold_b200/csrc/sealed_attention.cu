@@ -233,15 +233,24 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
             }
             const uint8_t *k_part = record + 16;
             const uint8_t *v_part = record + 16 + 16u * h.k_part_units;
+            const uint32_t k_bytes = 16u * h.k_part_units, v_bytes = 16u * h.v_part_units;
+            int bad_table = 0;
+            for (uint32_t b = tid; b < 2u * p.nblocks; b += kGenericThreads)
+                bad_table |= b < p.nblocks ? !part_block_start_ok(k_part, k_bytes, h.k_coder, p.nblocks, b, p.symbols)
+                                           : !part_block_start_ok(v_part, v_bytes, h.v_coder, p.nblocks, b - p.nblocks, p.symbols);
+            if (__syncthreads_or(bad_table)) {   // a block starts outside its part
+                if (tid == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
+                continue;
+            }
             for (uint32_t b = tid; b < 2u * p.nblocks; b += kGenericThreads) {
                 if (b < p.nblocks) {
                     uint8_t *dst = ksym + b * p.block_size;
-                    decode_part_block(k_part, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
+                    decode_part_block(k_part, k_bytes, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
                                       [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
                 } else {
                     const uint32_t vb = b - p.nblocks;
                     uint8_t *dst = vsym + vb * p.block_size;
-                    decode_part_block(v_part, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
+                    decode_part_block(v_part, v_bytes, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
                                       [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
                 }
             }
@@ -432,12 +441,12 @@ __global__ void decode_pages_kernel(AttentionParams p, const uint32_t *page_ids,
     for (uint32_t b = threadIdx.x; b < 2u * p.nblocks; b += blockDim.x) {
         if (b < p.nblocks) {
             uint8_t *dst = k_out + base + b * p.block_size;
-            decode_part_block(k_part, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
+            decode_part_block(k_part, 16u * h.k_part_units, h.k_coder, p.nblocks, b, p.block_size, p.symbols, p.k_tables,
                               [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
         } else {
             const uint32_t vb = b - p.nblocks;
             uint8_t *dst = v_out + base + vb * p.block_size;
-            decode_part_block(v_part, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
+            decode_part_block(v_part, 16u * h.v_part_units, h.v_coder, p.nblocks, vb, p.block_size, p.symbols, p.v_tables,
                               [&](int j, uint32_t s) { dst[j] = static_cast<uint8_t>(s); });
         }
     }
@@ -484,7 +493,8 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
     p->shared_prefix_pages = 0;   // the launch code sets it when the lanes kernels serve the call
     p->sm_count = 0;
-    p->decode_probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE ? 1u : 0u;
+    p->decode_probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE ? 1u : d->kernel == CF_B200_KERNEL_DECODE_DUMP ? 2u : 0u;
+    p->dump_pages = p->decode_probe == 2u ? d->reserved0 : 1u;
     p->status = d->status;
     p->pool_k = nullptr;
     p->pool_v = nullptr;
@@ -539,7 +549,7 @@ extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_atte
         return CF_ERR_INVALID_ARGUMENT;
     if (d->tail_tokens != nullptr && (d->tail_k == nullptr || d->tail_v == nullptr)) return CF_ERR_INVALID_ARGUMENT;
     if ((d->query_type != CF_B200_F16 && d->query_type != CF_B200_F32) ||
-        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_DECODE_PROBE ||
+        (d->output_type != CF_B200_F16 && d->output_type != CF_B200_F32) || d->kernel > CF_B200_KERNEL_DECODE_DUMP ||
         (d->tail_type != 0 && d->tail_type != CF_B200_F16 && d->tail_type != CF_B200_F32))
         return CF_ERR_INVALID_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(d->arena) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->workspace) & 255u) != 0)
@@ -552,7 +562,9 @@ extern "C" cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_atte
     const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, span * (d->query_head_count / d->kv_head_count),
                                                          d->head_dim, d->workspace_bytes, d->shared_prefix_pages != 0);
     if (w.chunk_capacity < d->seq_count) return CF_ERR_INVALID_ARGUMENT;  // at least one chunk per sequence
-    if (d->shared_prefix_pages > d->page_table_stride || d->reserved0 != 0) return CF_ERR_INVALID_ARGUMENT;
+    if (d->shared_prefix_pages > d->page_table_stride) return CF_ERR_INVALID_ARGUMENT;
+    // reserved0 has one use: the number of page ids the dump buffer of CF_B200_KERNEL_DECODE_DUMP covers
+    if ((d->kernel == CF_B200_KERNEL_DECODE_DUMP) != (d->reserved0 != 0)) return CF_ERR_INVALID_ARGUMENT;
     return CF_OK;
 }
 
@@ -578,12 +590,14 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     AttentionParams p;
     cfb::fill_params(d, &p);
     const bool lanes_ok = cfb::lanes_kernel_supports(p);
-    if ((d->kernel == CF_B200_KERNEL_LANES || d->kernel == CF_B200_KERNEL_DECODE_PROBE) && !lanes_ok) return CF_ERR_UNSUPPORTED;
+    const bool probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE || d->kernel == CF_B200_KERNEL_DECODE_DUMP;
+    if ((d->kernel == CF_B200_KERNEL_LANES || probe) && !lanes_ok) return CF_ERR_UNSUPPORTED;
+    if (d->kernel == CF_B200_KERNEL_DECODE_DUMP && (stages & CF_B200_STAGE_COMBINE)) return CF_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || d->kernel == CF_B200_KERNEL_DECODE_PROBE ||
+    const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || probe ||
                            (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
-    if (use_lanes && !p.decode_probe && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
+    if (use_lanes && p.decode_probe != 1u && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static cfb::LauncherState table[64];
         cudaError_t e;
         const cfb::LauncherState *state = cfb::launcher_state(table, &e);

@@ -43,7 +43,12 @@ struct UnitState {
     float acc[NG][4][4];     // O fragments: [group][channel of the lane's V block][fragment register]
     uint32_t vq[16];         // V symbols of the current page, [channel*4 + token quad]
     float m0[NG], m1[NG], l0[NG], l1[NG];  // running max / partial sum of the lane's two heads of each group
+    uint32_t *dump;          // kDump only: where this lane's quads of the current record go (K at +0, V at +512 words)
 };
+
+// What the kernel does with the symbols: attention; or (measurement) fold them into a checksum; or (test) store
+// every quad the lane decoders yield to global memory, so that they can be compared symbol for symbol.
+constexpr int kAttend = 0, kFold = 1, kDump = 2;
 
 // Where a lane finds its B fragments of S = K * Q^T (column n = parity*4 + head; zero where the lane's slice of the
 // contraction belongs to the other token of the pair).
@@ -79,15 +84,19 @@ __device__ __forceinline__ void score_quad(UnitState<NG> &u, const QSrc &qs, int
     }
 }
 
-// kProbe: the symbols are only folded into a checksum (u.vq[0]) — the decode work of the kernel without its attention.
-template <bool kProbe = false, class KLane, class VLane, int NG, class QSrc>
+// kFold: the symbols are only folded into a checksum (u.vq[0]) — the decode work of the kernel without its attention.
+// kDump: lane l's quad q of a stream holds the symbols 64 l + 4 q .. + 3 of that stream, first symbol in byte 0.
+template <int kMode = kAttend, class KLane, class VLane, int NG, class QSrc>
 __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &u, const QSrc &qs) {
     if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
             const uint32_t kq = k.quad();
-            if constexpr (kProbe) {
+            if constexpr (kMode == kFold) {
                 u.vq[0] ^= kq ^ v.quad();
+            } else if constexpr (kMode == kDump) {
+                u.dump[q] = kq;
+                u.dump[512 + q] = v.quad();
             } else {
                 u.vq[q] = v.quad();
                 score_quad(u, qs, q, kq);
@@ -104,8 +113,11 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &
             ke[i & 3] = k.symbol();
             ve[i & 3] = v.symbol();
             if ((i & 3) == 3) {
-                if constexpr (kProbe) {
+                if constexpr (kMode == kFold) {
                     u.vq[0] ^= pack_low_bytes(ve[0], ve[1], ve[2], ve[3]) ^ pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+                } else if constexpr (kMode == kDump) {
+                    u.dump[i >> 2] = pack_low_bytes(ke[0], ke[1], ke[2], ke[3]);
+                    u.dump[512 + (i >> 2)] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
                 } else {
                     u.vq[i >> 2] = pack_low_bytes(ve[0], ve[1], ve[2], ve[3]);
                     score_quad(u, qs, i >> 2, pack_low_bytes(ke[0], ke[1], ke[2], ke[3]));
@@ -115,16 +127,26 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &
     }
 }
 
-template <class KLane, int NG, class QSrc>
+template <int kMode = kAttend, class KLane, int NG, class QSrc>
 __device__ __forceinline__ void decode_k_only(KLane &k, UnitState<NG> &u, const QSrc &qs) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) score_quad(u, qs, q, k.quad());
+    for (int q = 0; q < 16; ++q) {
+        const uint32_t kq = k.quad();
+        if constexpr (kMode == kFold) u.vq[0] ^= kq;
+        else if constexpr (kMode == kDump) u.dump[q] = kq;
+        else score_quad(u, qs, q, kq);
+    }
 }
 
-template <class VLane, int NG>
+template <int kMode = kAttend, class VLane, int NG>
 __device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) u.vq[q] = v.quad();
+    for (int q = 0; q < 16; ++q) {
+        const uint32_t vq = v.quad();
+        if constexpr (kMode == kFold) u.vq[0] ^= vq;
+        else if constexpr (kMode == kDump) u.dump[512 + q] = vq;
+        else u.vq[q] = vq;
+    }
 }
 
 // Shared memory of one warp: two record stages, the softmax scratch, two mbarriers and (NG = 2) the query rows.
@@ -146,8 +168,9 @@ static_assert(WarpLayout<2>::kSmem <= 232448, "the eight-head kernel must fit th
 // kSplitQ (with NG = 2): the queries are fp32. A pass serves four heads; their rows are split into binary16(q) and
 // binary16(q - binary16(q)), stored as the rows of group 0 and group 1, the two score fragments are added, and one
 // softmax / P V follows: the scores equal fp32-query scores to 2^-22 relative, at the cost of a second score mma.
-template <int NG, bool kProbe = false, bool kSplitQ = false>
+template <int NG, int kMode = kAttend, bool kSplitQ = false>
 __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
+    constexpr bool kProbe = kMode != kAttend;
     static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
     using L = WarpLayout<NG>;
     using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
@@ -264,6 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
         UnitState<NG> u;
         if constexpr (kProbe) u.vq[0] = 0u;
+        u.dump = nullptr;
 #pragma unroll
         for (int n = 0; n < NG; ++n) {
 #pragma unroll
@@ -316,14 +340,21 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                 phase_bits ^= 1u << st;
                 const uint8_t *rec = warp_mem + st * kStageBytes;
                 const uint4 hv = *reinterpret_cast<const uint4 *>(rec);
-                const uint32_t k_units = hv.x & 0xffffu;
+                const uint32_t k_bytes = 16u * (hv.x & 0xffffu), v_bytes = 16u * (hv.x >> 16);
                 const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu, token_count = hv.y >> 16;
-                const bool good = record_header_ok(hv, entry_cur, p.codebook_id);
-                if (!good) {
+                const uint8_t *k_part = rec + 16;
+                const uint8_t *v_part = k_part + k_bytes;
+                const bool good = record_header_ok(hv, entry_cur, p.codebook_id) &&
+                                  __all_sync(0xffffffffu, part_offsets_ok(k_part, k_coder, k_bytes, lane) &&
+                                                              part_offsets_ok(v_part, v_coder, v_bytes, lane));
+                uint32_t dump_page = 0u;
+                if constexpr (kMode == kDump) dump_page = table_row[page_begin + i];
+                if (!good || dump_page >= p.dump_pages) {   // dump_pages is 1 outside the dump mode
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
                 } else {
-                    const uint8_t *k_part = rec + 16;
-                    const uint8_t *v_part = k_part + 16u * k_units;
+                    if constexpr (kMode == kDump)   // [page id][kv head][K stream | V stream], one byte per symbol
+                        u.dump = reinterpret_cast<uint32_t *>(p.output) +
+                                 (static_cast<uint64_t>(dump_page) * p.kv_head_count + kv_head) * 1024u + 16u * lane;
                     const float k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) *
                                           (p.softmax_scale * kLog2e);
                     const float v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
@@ -332,26 +363,26 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 
                     if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
                         RansLane k, v;
-                        k.open(k_part, lane, k_slot);
-                        v.open(v_part, lane, v_slot);
-                        decode_fused<kProbe>(k, v, u, qs);
+                        k.open(k_part, k_bytes, lane, k_slot);
+                        v.open(v_part, v_bytes, lane, v_slot);
+                        decode_fused<kMode>(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
                         HuffLane k, v;
-                        k.open(k_part, lane, k_lut);
-                        v.open(v_part, lane, v_lut);
-                        decode_fused<kProbe>(k, v, u, qs);
+                        k.open(k_part, k_bytes, lane, k_lut);
+                        v.open(v_part, v_bytes, lane, v_lut);
+                        decode_fused<kMode>(k, v, u, qs);
                     } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
                         FixedLane k, v;
-                        k.open(k_part, lane);
-                        v.open(v_part, lane);
-                        decode_fused<kProbe>(k, v, u, qs);
+                        k.open(k_part, k_bytes, lane);
+                        v.open(v_part, v_bytes, lane);
+                        decode_fused<kMode>(k, v, u, qs);
                     } else {  // mixed coders (one stream fell back to fixed width): one stream after the other
-                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_k_only(k, u, qs); }
-                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_k_only(k, u, qs); }
-                        else { FixedLane k; k.open(k_part, lane); decode_k_only(k, u, qs); }
-                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_v_only(v, u); }
-                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_v_only(v, u); }
-                        else { FixedLane v; v.open(v_part, lane); decode_v_only(v, u); }
+                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, k_bytes, lane, k_slot); decode_k_only<kMode>(k, u, qs); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, k_bytes, lane, k_lut); decode_k_only<kMode>(k, u, qs); }
+                        else { FixedLane k; k.open(k_part, k_bytes, lane); decode_k_only<kMode>(k, u, qs); }
+                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, v_bytes, lane, v_slot); decode_v_only<kMode>(v, u); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, v_bytes, lane, v_lut); decode_v_only<kMode>(v, u); }
+                        else { FixedLane v; v.open(v_part, v_bytes, lane); decode_v_only<kMode>(v, u); }
                     }
 
                     if constexpr (kSplitQ) {   // K q = K binary16(q) + K residue
@@ -452,7 +483,8 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
             return;
         }
 
-        if constexpr (kProbe) {   // the checksum of everything the unit decoded, so that the work cannot be dropped
+        if constexpr (kMode == kDump) {
+        } else if constexpr (kMode == kFold) {   // the checksum of everything the unit decoded, so that the work cannot be dropped
             uint32_t x = u.vq[0];
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) x ^= __shfl_xor_sync(0xffffffffu, x, o);
@@ -517,19 +549,23 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         e = cudaFuncSetAttribute(lanes_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<1>::kSmem));
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(lanes_attention_kernel<1, kFold>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<1>::kSmem));
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(lanes_attention_kernel<1, kDump>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<1>::kSmem));
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(lanes_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(lanes_attention_kernel<2, kAttend, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<2>::kSmem));
         if (e != cudaSuccess) return e;
         state->configured = true;
     }
-    if (p.decode_probe) lanes_attention_kernel<1, true><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
-    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, false, true><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
+    if (p.decode_probe == 2u) lanes_attention_kernel<1, kDump><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.decode_probe) lanes_attention_kernel<1, kFold><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, kAttend, true><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
     else lanes_attention_kernel<2><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();

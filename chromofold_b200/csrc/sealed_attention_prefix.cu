@@ -354,37 +354,51 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
             } else {
                 copy_phase ^= 1u;
                 const uint4 hv = *reinterpret_cast<const uint4 *>(stage);
-                if (!record_header_ok(hv, entry, p.codebook_id)) {
+                const uint32_t k_bytes = 16u * (hv.x & 0xffffu), v_bytes = 16u * (hv.x >> 16);
+                const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu;
+                const uint8_t *k_part = stage + 16, *v_part = k_part + k_bytes;
+                if (!record_header_ok(hv, entry, p.codebook_id) ||
+                    !__all_sync(0xffffffffu, part_offsets_ok(k_part, k_coder, k_bytes, lane) &&
+                                                 part_offsets_ok(v_part, v_coder, v_bytes, lane))) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
                 } else {
-                    const uint32_t k_units = hv.x & 0xffffu;
-                    const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu;
-                    const uint8_t *k_part = stage + 16, *v_part = k_part + 16u * k_units;
                     token_count = hv.y >> 16;
                     k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) * (p.softmax_scale * kLog2e);
                     v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
                     if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
                         RansLane k, v;
-                        k.open(k_part, lane, k_slot);
-                        v.open(v_part, lane, v_slot);
+                        k.open(k_part, k_bytes, lane, k_slot);
+                        v.open(v_part, v_bytes, lane, v_slot);
                         decode_page(k, v, kq, vq);
                     } else if (k_coder == CF_B200_CODER_HUFFMAN && v_coder == CF_B200_CODER_HUFFMAN) {
                         HuffLane k, v;
-                        k.open(k_part, lane, k_lut);
-                        v.open(v_part, lane, v_lut);
+                        k.open(k_part, k_bytes, lane, k_lut);
+                        v.open(v_part, v_bytes, lane, v_lut);
                         decode_page(k, v, kq, vq);
                     } else if (k_coder == CF_B200_CODER_FIXED8 && v_coder == CF_B200_CODER_FIXED8) {
                         FixedLane k, v;
-                        k.open(k_part, lane);
-                        v.open(v_part, lane);
+                        k.open(k_part, k_bytes, lane);
+                        v.open(v_part, v_bytes, lane);
                         decode_page(k, v, kq, vq);
                     } else {
-                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, lane, k_slot); decode_stream(k, kq); }
-                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, lane, k_lut); decode_stream(k, kq); }
-                        else { FixedLane k; k.open(k_part, lane); decode_stream(k, kq); }
-                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, lane, v_slot); decode_stream(v, vq); }
-                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, lane, v_lut); decode_stream(v, vq); }
-                        else { FixedLane v; v.open(v_part, lane); decode_stream(v, vq); }
+                        if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, k_bytes, lane, k_slot); decode_stream(k, kq); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, k_bytes, lane, k_lut); decode_stream(k, kq); }
+                        else { FixedLane k; k.open(k_part, k_bytes, lane); decode_stream(k, kq); }
+                        if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, v_bytes, lane, v_slot); decode_stream(v, vq); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, v_bytes, lane, v_lut); decode_stream(v, vq); }
+                        else { FixedLane v; v.open(v_part, v_bytes, lane); decode_stream(v, vq); }
+                    }
+                    if (p.decode_probe == 2u) {   // test mode: the quads as decoded, [page id][kv head][K stream | V stream]
+                        const uint32_t page_id = table_row[cur.u.page_begin + in_unit];
+                        if (page_id < p.dump_pages) {
+                            uint32_t *dump = reinterpret_cast<uint32_t *>(p.output) +
+                                             (static_cast<uint64_t>(page_id) * p.kv_head_count + cur.u.kv_head) * 1024u + 16u * lane;
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) {
+                                dump[q] = kq[q];
+                                dump[512 + q] = vq[q];
+                            }
+                        }
                     }
                 }
             }

@@ -124,6 +124,13 @@ typedef struct cf_b200_sealed_attention_desc {
  * would decode is folded into a checksum that replaces the partials; the output of the call is meaningless. Use it
  * with CF_B200_STAGE_PLAN | CF_B200_STAGE_ATTENTION to time the decode floor of a workload. */
 #define CF_B200_KERNEL_DECODE_PROBE 3u
+/* Test only: the lanes kernel (and, with shared_prefix_pages set, the shared-prefix kernel) runs its page fetch and
+ * its per-lane block decoders as in an attention call, and stores every symbol they yield instead of consuming it:
+ * `output` is then a device byte buffer [reserved0 page ids][kv_head_count][2][page_tokens * head_dim] — the K stream
+ * and the V stream of each record, in stream order, one byte per symbol — and reserved0 (otherwise 0) is the number
+ * of page ids it covers; records of other page ids are refused with CF_B200_DEVSTAT_BAD_RECORD. Only pages some
+ * listed sequence reaches are written. Stages: CF_B200_STAGE_PLAN | CF_B200_STAGE_ATTENTION. */
+#define CF_B200_KERNEL_DECODE_DUMP 4u
 
 #define CF_B200_DEVSTAT_BAD_RECORD 0x1u      /* version / codebook id / size mismatch in a record header */
 #define CF_B200_DEVSTAT_WAIT_EXPIRED 0x2u    /* a bounded wait on a bulk copy ran out */

@@ -23,8 +23,10 @@ def _random_kv(rng, hkv, tokens, d, b=12.0, scale=0.01):
     return k, v
 
 
-def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails, b=12.0):
-    """A GPU layer and a CPU HostCache holding the same sealed pages (sealed by the ORACLE and imported)."""
+def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails, b=12.0, noisy_k_pages=(), **layer_kw):
+    """A GPU layer and a CPU HostCache holding the same sealed pages (sealed by the ORACLE and imported).
+    noisy_k_pages: (sequence, page) pairs whose K values are uniform over the code range, so that their K stream does
+    not shrink and is stored fixed-width while the V stream keeps the page's coder (a mixed-coder record)."""
     import torch
     n = len(contexts)
     stride = max(1, max((c + t - 1) // t for c in contexts))
@@ -34,7 +36,7 @@ def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails,
     vcb = oracle.codebook_from_hist(hist[::-1].copy())
     layer = _layer(native, kv_heads=hkv, query_heads=hq, head_dim=d, page_tokens=t, block_size=block, coder=coder,
                    max_sequences=n, max_pages_per_sequence=stride, max_pages=n * stride + 2,
-                   arena_bytes=max(1 << 16, n * stride * hkv * (2 * d * t + 64)))
+                   arena_bytes=max(1 << 16, n * stride * hkv * (2 * d * t + 64)), **layer_kw)
     layer.set_codebooks(hist, hist[::-1].copy())
     host = HostCache(hkv, d, t, block, coder, kcb, vcb)
     tail_k = np.zeros((n, hkv, t, d), np.float16)
@@ -44,6 +46,8 @@ def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails,
         while done < ctx:
             tokens = min(t, ctx - done)
             k, v = _random_kv(rng, hkv, tokens, d, b)
+            if (s, done // t) in noisy_k_pages:
+                k = (rng.integers(-127, 128, (hkv, tokens, d)).astype(np.float32) * 0.01).astype(np.float16).astype(np.float32)
             host.seal_page(s, k, v)
             done += tokens
         if s in host.records:
@@ -85,6 +89,62 @@ def test_gpu_decode_is_bit_exact(native, oracle, coder):
                 back_k, back_v = oracle.open_record(host.records[s][p][h], 128, 16, 64, kcb, vcb)
                 assert np.array_equal(back_k, want_k) and np.array_equal(back_v, want_v)
     assert layer.device_status() == 0
+
+
+def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None):
+    """Every record of `sequences` (page ids in import order from 1): the dumped K and V symbols against the symbols
+    the CPU quantiser produced and against what the restated reference decoders recover from the record's bytes."""
+    pid, checked = 1, 0
+    for s in sorted(host.records):
+        for p, page in enumerate(host.records[s]):
+            if s in sequences:
+                for h, rec in enumerate(page):
+                    want_k, want_v = host.symbols[s][p][h]
+                    back_k, back_v = oracle.open_record(rec, 128, 16, 64, kcb, vcb)
+                    assert np.array_equal(back_k, want_k) and np.array_equal(back_v, want_v)
+                    assert np.array_equal(dump[pid, h, 0], want_k), ("K", s, p, h)
+                    assert np.array_equal(dump[pid, h, 1], want_v), ("V", s, p, h)
+                    checked += 1
+            pid += 1
+    return checked
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_lane_decoders_yield_exactly_the_oracle_symbols(native, oracle, coder):
+    """CF_B200_KERNEL_DECODE_DUMP: the per-lane block decoders of the attention kernel (RansLane / HuffLane / FixedLane in
+    lanes_attention_kernel, the code that is timed) write out every symbol they decode; all of them must equal the CPU
+    quantiser's codes and the restated reference decoders' output. Covers a ragged last page (5 tokens), a
+    single-page sequence and a mixed-coder record (K fixed-width, V entropy coded)."""
+    import torch
+    rng = np.random.default_rng(12)
+    contexts = [48, 16, 37, 160]
+    layer, host, kcb, vcb, *_ = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=CODERS[coder],
+                                       contexts=contexts, tails=[0, 0, 0, 0], noisy_k_pages={(3, 1), (3, 7)})
+    if coder != "fixed8":   # the noisy K streams fell back to fixed width, their V streams did not
+        rec = host.records[3][1][0]
+        assert rec[4] == CODERS["fixed8"] and rec[5] == CODERS[coder]
+    q = torch.zeros((4, 4, 128), dtype=torch.float16, device="cuda")
+    dump = layer.dump_lane_decoders(q).cpu().numpy()
+    assert layer.device_status() == 0
+    assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}) == 2 * (3 + 1 + 3 + 10)
+
+
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_shared_prefix_decoders_yield_exactly_the_oracle_symbols(native, oracle, coder):
+    """The same symbol-for-symbol check for the decoder warps of prefix_attention_kernel: five query rows over one
+    sequence share its first eight pages (decoded by the shared-prefix kernel), the last two pages go through the
+    per-entry kernel; together they must have written every record of the sequence."""
+    import torch
+    rng = np.random.default_rng(13)
+    layer, host, kcb, vcb, *_ = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=CODERS[coder],
+                                       contexts=[157], tails=[0], noisy_k_pages={(0, 2)}, workspace_bytes=4 << 20)
+    before = native.lib().cf_b200_shared_prefix_launches()
+    q = torch.zeros((5, 4, 128), dtype=torch.float16, device="cuda")
+    positions = torch.tensor([156, 150, 140, 130, 128], dtype=torch.int32, device="cuda")
+    dump = layer.dump_lane_decoders(q, slots=[0] * 5, shared_prefix_pages=8, query_positions=positions).cpu().numpy()
+    assert layer.device_status() == 0
+    assert native.lib().cf_b200_shared_prefix_launches() == before + 1
+    assert _expect_dump(dump, host, oracle, kcb, vcb, {0}) == 2 * 10
 
 
 GEOMETRIES = [
@@ -262,6 +322,43 @@ def test_bad_records_are_reported_not_faulted(native, oracle):
     layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=3)   # the shared-prefix kernel skips it too
     torch.cuda.synchronize()
     assert layer.device_status() & native.DEVSTAT_BAD_RECORD
+
+
+@pytest.mark.parametrize("coder", ["rans", "huffman"])
+def test_block_offsets_past_their_part_are_reported(native, oracle, coder):
+    """A record with a well-formed header whose block table sends one block past the end of its part (a bad producer,
+    not transport damage): every kernel refuses the page with CF_B200_DEVSTAT_BAD_RECORD and the other pages still
+    count. The bad offset chosen here still lies inside the record, so the read it would cause is in bounds with or
+    without the check."""
+    import torch
+    rng = np.random.default_rng(32)
+    layer, host, kcb, vcb, *_ = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=CODERS[coder],
+                                       contexts=[48], tails=[0])
+    q = torch.from_numpy(rng.standard_normal((1, 4, 128)).astype(np.float16)).cuda()
+    good = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    assert layer.device_status() == 0
+    rec = host.records[0][1][0]                        # page 1 (page id 2), kv head 0
+    k_bytes = 16 * int(rec[0] | rec[1] << 8)
+    entry = int(layer.page_dir[2 * 2 + 0].item())
+    base = (entry & 0xFFFFFFFFFF) * 16 + 16            # the K part in the arena
+    if coder == "rans":                                # u32 state0[32] | u16 byte_off[32] | bytes
+        at, bad = base + 128 + 2 * 5, k_bytes - 192 + 32
+    else:                                              # u16 bit_off[32] | words
+        at, bad = base + 2 * 5, (k_bytes - 64) * 8 + 256
+    layer.arena[at] = bad & 0xFF
+    layer.arena[at + 1] = bad >> 8
+    outs = []
+    for kw in (dict(kernel=native.KERNEL_GENERIC), dict(kernel=native.KERNEL_LANES),
+               dict(kernel=native.KERNEL_LANES, shared_prefix_pages=3)):
+        layer.status.zero_()
+        outs.append(layer.attention(q, **kw).cpu().numpy())
+        assert layer.device_status() == native.DEVSTAT_BAD_RECORD, kw
+    # the page is skipped whole for that kv head (query heads 0, 1); the other kv head's result is untouched
+    assert np.array_equal(outs[1][:, 2:], good[:, 2:]) and not np.array_equal(outs[1][:, :2], good[:, :2])
+    ok, err = attention_close(outs[0], outs[1])
+    assert ok, err
+    ok, err = attention_close(outs[2], outs[1])
+    assert ok, err
 
 
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 8), (16, 2), (6, 2)])
