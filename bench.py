@@ -49,7 +49,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"])
+    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"],
+                    help="page coder; rans4 / huffman4 are the nibble-split variants (raw low nibbles, pairs of high nibbles coded)")
     ap.add_argument("--laplace-b", type=float, default=12.0)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx-lo", type=int, default=CTX_LO)

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(HERE, "libchromofold_b200.so")
 CF_OK, CF_ERR_INVALID_ARGUMENT, CF_ERR_UNSUPPORTED, CF_ERR_CUDA = 0, 1, 2, 3
 ABI_VERSION = 1
 F16, BF16, F32 = 1, 2, 3
-CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
+CODER_FIXED8, CODER_HUFFMAN, CODER_RANS, CODER_RANS_SPLIT4, CODER_HUFFMAN_SPLIT4 = 0, 1, 2, 3, 4
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES, KERNEL_DECODE_PROBE, KERNEL_DECODE_DUMP = 0, 1, 2, 3, 4
 STATIC_WORKSPACE_BYTES = 8 << 20
 STAGE_PLAN, STAGE_ATTENTION, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 7

@@ -223,7 +223,7 @@ def main():
     ap.add_argument("--transfer", action="store_true", help="time the pack / unpack kernels of transfer images instead")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8"], help="configurations 4 and 5")
+    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
     ap.add_argument("--blocks", action="store_true", help="configuration 3: the block-size dial instead of the p sweep")
     ap.add_argument("--batch4", type=int, default=8)
     ap.add_argument("--ctx4", type=int, default=131072)

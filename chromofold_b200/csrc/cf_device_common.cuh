@@ -161,6 +161,14 @@ __device__ __forceinline__ bool part_block_start_ok(const uint8_t *part, uint32_
         const uint32_t head = align_up_u32(2u * nblocks, 4u);
         return part_bytes >= head && reinterpret_cast<const uint16_t *>(part)[b] <= 8u * (part_bytes - head);
     }
+    if (coder == CF_B200_CODER_RANS_SPLIT4) {   // block table | raw low-nibble plane (symbols / 2 bytes) | payload
+        const uint32_t head = align_up_u32(6u * nblocks, 4u) + symbols / 2u;
+        return part_bytes >= head && reinterpret_cast<const uint16_t *>(part + 4u * nblocks)[b] <= part_bytes - head;
+    }
+    if (coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
+        const uint32_t head = align_up_u32(2u * nblocks, 4u) + symbols / 2u;
+        return part_bytes >= head && reinterpret_cast<const uint16_t *>(part)[b] <= 8u * (part_bytes - head);
+    }
     return part_bytes >= align_up_u32(symbols, 4u);
 }
 
@@ -184,6 +192,26 @@ __device__ __forceinline__ void decode_part_block(const uint8_t *part, uint32_t 
         if (part_bytes < head) return;
         huffman_decode_block(reinterpret_cast<const uint32_t *>(part + head), (part_bytes - head) / 4u, off[b], tables->huff_lut,
                              count, emit);
+    } else if (coder == CF_B200_CODER_RANS_SPLIT4 || coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
+        // nibble-split: the stream codes pairs of high nibbles (count / 2 steps); the low nibbles come from the raw plane,
+        // word lo[j][b] = symbols 8j..8j+7 of block b (symbol 8j+i at bits 8i..8i+3 for i < 4, 8j+4+i at bits 8i+4..8i+7)
+        const bool rans = coder == CF_B200_CODER_RANS_SPLIT4;
+        const uint32_t head = align_up_u32(rans ? 6u * nblocks : 2u * nblocks, 4u), plane_bytes = (block_size / 8u) * nblocks * 4u;
+        if (part_bytes < head + plane_bytes) return;
+        const uint32_t *plane = reinterpret_cast<const uint32_t *>(part + head);
+        auto emit_pair = [&](int k, uint32_t pair) {
+            const uint32_t w = plane[(static_cast<uint32_t>(k) >> 2) * nblocks + b], at = (2u * static_cast<uint32_t>(k)) & 7u;
+            const uint32_t shift = at < 4u ? 8u * at : 8u * (at - 4u) + 4u;   // at is even: at + 1 sits 8 bits further
+            emit(2 * k, (pair & 0xf0u) | ((w >> shift) & 0x0fu));
+            emit(2 * k + 1, ((pair & 0x0fu) << 4) | ((w >> (shift + 8u)) & 0x0fu));
+        };
+        const uint8_t *payload = part + head + plane_bytes;
+        if (rans)
+            rans_decode_block(payload, part_bytes - head - plane_bytes, reinterpret_cast<const uint16_t *>(part + 4u * nblocks)[b],
+                              reinterpret_cast<const uint32_t *>(part)[b], tables->rans_slot, count / 2, emit_pair);
+        else
+            huffman_decode_block(reinterpret_cast<const uint32_t *>(payload), (part_bytes - head - plane_bytes) / 4u,
+                                 reinterpret_cast<const uint16_t *>(part)[b], tables->huff_lut, count / 2, emit_pair);
     } else {
         if (part_bytes < align_up_u32(symbols, 4u)) return;
         fixed8_decode_block(reinterpret_cast<const uint32_t *>(part), base, count, emit);

@@ -129,10 +129,48 @@ struct RansLane {
         used = imad(shift, 1u, used);
         return e;
     }
-    __device__ __forceinline__ uint32_t quad() {
+    __device__ __forceinline__ uint32_t quad(int) {   // quad index: the decoders that need it get it from an unrolled loop
         reload();
         const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
         return pack_low_bytes(e0, e1, e2, e3);
+    }
+};
+
+// Low nibbles of the four symbols of a quad (in the low nibble of each byte of w; its high nibbles are ignored) under
+// the two pair symbols that hold their high nibbles (table entries, pair A:B in the low byte): four symbols, first in byte 0.
+__device__ __forceinline__ uint32_t merge_split_quad(uint32_t e0, uint32_t e1, uint32_t w) {
+    const uint32_t t = __byte_perm(e0, e1, 0x4400);             // (s1, s1, s0, s0), s = A:B
+    const uint32_t t4 = imad(t, 16u, 0u);                       // bytes 1 and 3 now start with B
+    const uint32_t h = __byte_perm(t, t4, 0x7250);              // (B1:*, A1:*, B0:*, A0:*)
+    return (h & 0xf0f0f0f0u) | (w & 0x0f0f0f0fu);
+}
+
+// Nibble-split rANS (CF_B200_CODER_RANS_SPLIT4): the low nibble of every symbol is stored raw in a lane-interleaved
+// plane, and the rANS stream codes PAIRS of high nibbles (pair symbol = hi(2k) << 4 | hi(2k + 1)), so a block of 64
+// symbols is 32 steps of the same recurrence. Part layout: u32 state0[32] | u16 byte_off[32] | u32 lo[8][32] | bytes;
+// lo[j][l] holds the low nibbles of symbols 8j..8j+7 of block l: symbol 8j + i at bits 8i..8i+3 for i < 4, symbol
+// 8j + 4 + i at bits 8i+4..8i+7.
+struct RansSplitLane : RansLane {
+    static constexpr bool kWholeQuads = true;   // callers ask for a quad at a time (the window is refilled inside)
+    static constexpr uint32_t kPlaneBytes = 1024u;
+    uint32_t lo;   // shared-memory byte address of lo[0][lane]
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint32_t *slot_table) {
+        x = reinterpret_cast<const uint32_t *>(part)[lane];
+        const uint32_t payload = part_bytes > 192u + kPlaneBytes ? part_bytes - 192u - kPlaneBytes : 0u;
+        lo = smem_addr(part) + 192u + 4u * lane;
+        pos = smem_addr(part) + 192u + kPlaneBytes + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 128)[lane]), payload);
+        table = smem_addr(slot_table);
+        used = 0;
+    }
+    __device__ __forceinline__ uint32_t lo_word(int j) const {
+        uint32_t w;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 128u * j));
+        return w;
+    }
+    __device__ __forceinline__ uint32_t quad(int q) {   // one stream on its own (mixed-coder records)
+        if ((q & 1) == 0) reload();
+        const uint32_t e0 = symbol(), e1 = symbol();
+        return merge_split_quad(e0, e1, lo_word(q >> 1) >> (4 * (q & 1)));
     }
 };
 
@@ -171,10 +209,35 @@ struct HuffLane {
         used = imad(len, 1u, used);
         return e;
     }
-    __device__ __forceinline__ uint32_t quad() {
+    __device__ __forceinline__ uint32_t quad(int) {
         reload();
         const uint32_t e0 = symbol(), e1 = symbol(), e2 = symbol(), e3 = symbol();
         return pack_low_bytes(e0, e1, e2, e3);
+    }
+};
+
+// Nibble-split Huffman (CF_B200_CODER_HUFFMAN_SPLIT4): u16 bit_off[32] | u32 lo[8][32] | words; one LUT hit = a pair.
+struct HuffSplitLane : HuffLane {
+    static constexpr bool kWholeQuads = true;
+    static constexpr uint32_t kPlaneBytes = 1024u;
+    uint32_t lo;
+    __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint16_t *lut) {
+        const uint32_t payload_bits = part_bytes > 64u + kPlaneBytes ? (part_bytes - 64u - kPlaneBytes) * 8u : 0u;
+        bit = min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part)[lane]), payload_bits);
+        lo = smem_addr(part) + 64u + 4u * lane;
+        words = smem_addr(part) + 64u + kPlaneBytes;
+        table = smem_addr(lut);
+        used = 0;
+    }
+    __device__ __forceinline__ uint32_t lo_word(int j) const {
+        uint32_t w;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 128u * j));
+        return w;
+    }
+    __device__ __forceinline__ uint32_t quad(int q) {
+        if ((q & 1) == 0) reload();   // four pair symbols take at most 48 bits
+        const uint32_t e0 = symbol(), e1 = symbol();
+        return merge_split_quad(e0, e1, lo_word(q >> 1) >> (4 * (q & 1)));
     }
 };
 
@@ -187,7 +250,7 @@ struct FixedLane {
         words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
     }
     // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
-    __device__ __forceinline__ uint32_t quad() { return __byte_perm(*words++, 0u, 0x0123); }
+    __device__ __forceinline__ uint32_t quad(int) { return __byte_perm(*words++, 0u, 0x0123); }
 };
 
 // Coding tables into shared memory, once per CTA: [k rANS slots | v rANS slots | k Huffman LUT | v Huffman LUT].
@@ -215,7 +278,7 @@ __device__ __forceinline__ bool record_header_ok(const uint4 &hv, uint64_t dir_e
     const uint32_t codebook = hv.w & 0xffffu, version = hv.w >> 24;
     return version == CF_B200_FORMAT_VERSION && codebook == codebook_id &&
            1u + k_units + v_units == CF_B200_DIR_LENGTH_UNITS(dir_entry) && k_units <= 128u && v_units <= 128u &&
-           k_coder <= 2u && v_coder <= 2u && token_count >= 1u && token_count <= 16u;
+           k_coder <= CF_B200_CODER_MAX && v_coder <= CF_B200_CODER_MAX && token_count >= 1u && token_count <= 16u;
 }
 
 // The block table of a staged part against the part's length: lane l checks the start of block l. The reference
@@ -226,6 +289,10 @@ __device__ __forceinline__ bool part_offsets_ok(const uint8_t *part, uint32_t co
         return part_bytes >= 192u && reinterpret_cast<const uint16_t *>(part + 128)[lane] <= part_bytes - 192u;
     if (coder == CF_B200_CODER_HUFFMAN)
         return part_bytes >= 64u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - 64u) * 8u;
+    if (coder == CF_B200_CODER_RANS_SPLIT4)
+        return part_bytes >= 192u + 1024u && reinterpret_cast<const uint16_t *>(part + 128)[lane] <= part_bytes - 192u - 1024u;
+    if (coder == CF_B200_CODER_HUFFMAN_SPLIT4)
+        return part_bytes >= 64u + 1024u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - 64u - 1024u) * 8u;
     return part_bytes == 2048u;
 }
 

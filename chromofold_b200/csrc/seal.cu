@@ -16,8 +16,13 @@ namespace {
 constexpr int kSealThreads = 128;
 
 struct SealSmem {
-    uint32_t off_ksym, off_vsym, off_scratch, off_part, off_blk, off_enc, part_capacity, slot_bytes, total;
+    uint32_t off_ksym, off_vsym, off_kpair, off_vpair, off_scratch, off_part, off_blk, off_enc, part_capacity, slot_bytes, total;
 };
+
+__host__ __device__ inline bool split_coder(uint32_t coder) {
+    return coder == CF_B200_CODER_RANS_SPLIT4 || coder == CF_B200_CODER_HUFFMAN_SPLIT4;
+}
+__host__ __device__ inline bool rans_family(uint32_t coder) { return coder == CF_B200_CODER_RANS || coder == CF_B200_CODER_RANS_SPLIT4; }
 
 __host__ __device__ inline SealSmem seal_smem(uint32_t symbols, uint32_t nblocks, uint32_t block_size) {
     SealSmem s;
@@ -25,7 +30,9 @@ __host__ __device__ inline SealSmem seal_smem(uint32_t symbols, uint32_t nblocks
     s.part_capacity = align_up_u32(symbols, 16u) + 16u;
     s.off_ksym = 0;
     s.off_vsym = s.off_ksym + align_up_u32(symbols, 16u);
-    s.off_scratch = s.off_vsym + align_up_u32(symbols, 16u);
+    s.off_kpair = s.off_vsym + align_up_u32(symbols, 16u);          // pair symbols of the nibble-split coders
+    s.off_vpair = s.off_kpair + align_up_u32(symbols / 2u, 16u);
+    s.off_scratch = s.off_vpair + align_up_u32(symbols / 2u, 16u);
     s.off_part = s.off_scratch + 2u * nblocks * s.slot_bytes;   // one scratch area per stream
     s.off_blk = s.off_part + 2u * s.part_capacity;
     s.off_enc = align_up_u32(s.off_blk + 6u * nblocks * 4u, 8u);
@@ -135,6 +142,7 @@ __device__ __forceinline__ void put_bits(uint32_t *words, uint32_t bit, uint32_t
 // size (a multiple of 16), coder_out[w] the coder actually stored.
 struct StreamJob {
     const uint8_t *sym;
+    uint8_t *pairs;      // room for symbols / 2 pair symbols (nibble-split coders)
     const cf_b200_codebook_tables *tables;
     const uint2 *enc;
     uint8_t *part;
@@ -147,17 +155,39 @@ __device__ void encode_streams(const SealParams &p, const SealSmem &lay, const S
     const uint32_t fixed_bytes = align_up_u32(n, 16u);
     uint32_t coder[2] = {p.coder, p.coder};
     bytes_out[0] = bytes_out[1] = fixed_bytes;
+    // What the entropy coder sees: the symbols, or (nibble-split) the pairs of high nibbles, half as many per block; the
+    // raw low-nibble plane of a split part sits between the block table and the payload.
+    const bool split = split_coder(p.coder), rans = rans_family(p.coder);
+    const uint32_t per = split ? 2u : 1u, head = align_up_u32(rans ? 6u * nb : 2u * nb, 4u);
+    const uint32_t plane_bytes = split ? (p.block_size / 8u) * nb * 4u : 0u;
+    if (split) {
+        for (uint32_t i = tid; i < n; i += kSealThreads) {   // pair symbols, and every symbol's low nibble into its plane word
+            const uint32_t w = i / (n / 2u), k = i % (n / 2u);
+            const uint8_t *sym = job[w].sym;
+            job[w].pairs[k] = static_cast<uint8_t>((sym[2u * k] & 0xf0u) | (sym[2u * k + 1u] >> 4));
+        }
+        for (uint32_t i = tid; i < 2u * plane_bytes / 4u; i += kSealThreads) {
+            const uint32_t w = i / (plane_bytes / 4u), r = i % (plane_bytes / 4u), j = r / nb, b = r % nb;
+            const uint32_t first = b * p.block_size + 8u * j;   // lo[j][b]: symbols first .. first + 7
+            uint32_t word = 0u;
+            for (uint32_t a = 0; a < 8u; ++a)
+                if (first + a < n) word |= static_cast<uint32_t>(job[w].sym[first + a] & 0x0fu) << (a < 4u ? 8u * a : 8u * (a - 4u) + 4u);
+            reinterpret_cast<uint32_t *>(job[w].part + head)[r] = word;
+        }
+        __syncthreads();
+    }
     if (p.coder != CF_B200_CODER_FIXED8) {
         for (uint32_t j = tid; j < 2u * nb; j += kSealThreads) {  // pass 1: coded length of every block
             const uint32_t w = j / nb, b = j % nb, base = b * p.block_size;
-            const int count = static_cast<int>(min(p.block_size, n - base));
-            if (p.coder == CF_B200_CODER_RANS) {
+            const int count = static_cast<int>(min(p.block_size, n - base) / per);
+            const uint8_t *src = split ? job[w].pairs + base / 2u : job[w].sym + base;
+            if (rans) {
                 uint32_t st;
-                blk_len[j] = rans_encode_block(job[w].sym + base, count, job[w].enc, scratch + (j + 1) * lay.slot_bytes, &st);
+                blk_len[j] = rans_encode_block(src, count, job[w].enc, scratch + (j + 1) * lay.slot_bytes, &st);
                 blk_state[j] = st;
             } else {
                 uint32_t bits = 0;
-                for (int i = 0; i < count; ++i) bits += job[w].tables->huff_code[job[w].sym[base + i]] >> 16;
+                for (int i = 0; i < count; ++i) bits += job[w].tables->huff_code[src[i]] >> 16;
                 blk_len[j] = bits;
             }
         }
@@ -168,9 +198,8 @@ __device__ void encode_streams(const SealParams &p, const SealSmem &lay, const S
                 blk_off[tid * nb + b] = run;
                 run += blk_len[tid * nb + b];
             }
-            const uint32_t bytes = p.coder == CF_B200_CODER_RANS
-                                       ? align_up_u32(align_up_u32(6u * nb, 4u) + run, 16u)
-                                       : align_up_u32(align_up_u32(2u * nb, 4u) + 4u * ((run + 31u) / 32u), 16u);
+            const uint32_t bytes = rans ? align_up_u32(head + plane_bytes + run, 16u)
+                                        : align_up_u32(head + plane_bytes + 4u * ((run + 31u) / 32u), 16u);
             s_flag[2 * tid] = bytes > fixed_bytes ? 1u : 0u;  // would not shrink: store fixed-width instead
             s_flag[2 * tid + 1] = bytes;
         }
@@ -183,25 +212,28 @@ __device__ void encode_streams(const SealParams &p, const SealSmem &lay, const S
     for (uint32_t j = tid; j < 2u * nb; j += kSealThreads) {   // pass 2: tables and payload of the coded streams
         const uint32_t w = j / nb, b = j % nb;
         uint8_t *part = job[w].part;
-        if (coder[w] == CF_B200_CODER_RANS) {
+        if (coder[w] == CF_B200_CODER_FIXED8) continue;
+        if (rans) {
             reinterpret_cast<uint32_t *>(part)[b] = blk_state[j];
             reinterpret_cast<uint16_t *>(part + 4u * nb)[b] = static_cast<uint16_t>(blk_off[j]);
             const uint8_t *src = scratch + (j + 1) * lay.slot_bytes - blk_len[j];
-            uint8_t *dst = part + align_up_u32(6u * nb, 4u) + blk_off[j];
+            uint8_t *dst = part + head + plane_bytes + blk_off[j];
             for (uint32_t i = 0; i < blk_len[j]; ++i) dst[i] = src[i];
-        } else if (coder[w] == CF_B200_CODER_HUFFMAN) {
-            uint32_t *words = reinterpret_cast<uint32_t *>(part + align_up_u32(2u * nb, 4u));
+        } else {
+            uint32_t *words = reinterpret_cast<uint32_t *>(part + head + plane_bytes);
             const uint32_t base = b * p.block_size;
-            const int count = static_cast<int>(min(p.block_size, n - base));
+            const int count = static_cast<int>(min(p.block_size, n - base) / per);
+            const uint8_t *src = split ? job[w].pairs + base / 2u : job[w].sym + base;
             uint32_t bit = blk_off[j];
             reinterpret_cast<uint16_t *>(part)[b] = static_cast<uint16_t>(bit);
             for (int i = 0; i < count; ++i) {
-                const uint32_t cl = job[w].tables->huff_code[job[w].sym[base + i]];
+                const uint32_t cl = job[w].tables->huff_code[src[i]];
                 put_bits(words, bit, cl & 0xffffu, cl >> 16);
                 bit += cl >> 16;
             }
         }
     }
+    // (a split stream that fell back to fixed width: the fixed words below overwrite the plane its part already holds)
     for (int w = 0; w < 2; ++w) {
         if (coder[w] != CF_B200_CODER_FIXED8) continue;
         uint32_t *words = reinterpret_cast<uint32_t *>(job[w].part);
@@ -268,14 +300,15 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     quantise_tiles(p, tile, rows, __half2float(__ushort_as_half(k_bits)), __half2float(__ushort_as_half(v_bits)), ksym,
                    vsym);
     for (uint32_t i = tid; i < 2u * lay.part_capacity / 4u; i += kSealThreads) reinterpret_cast<uint32_t *>(k_part)[i] = 0u;
-    if (p.coder == CF_B200_CODER_RANS)
+    if (rans_family(p.coder))
         for (uint32_t i = tid; i < 512u; i += kSealThreads) {
             const cf_b200_codebook_tables *t = i < 256u ? p.k_tables : p.v_tables;
             enc[i] = encoder_entry(t->rans_freq[i & 255u], t->rans_cum[i & 255u]);
         }
     __syncthreads();
 
-    const StreamJob jobs[2] = {{ksym, p.k_tables, enc, k_part}, {vsym, p.v_tables, enc + 256, v_part}};
+    const StreamJob jobs[2] = {{ksym, smem + lay.off_kpair, p.k_tables, enc, k_part},
+                               {vsym, smem + lay.off_vpair, p.v_tables, enc + 256, v_part}};
     uint32_t coders[2], bytes[2];
     encode_streams(p, lay, jobs, scratch, blk_len, blk_off, blk_state, s_flag, coders, bytes);
     const uint32_t k_coder = coders[0], v_coder = coders[1], k_bytes = bytes[0], v_bytes = bytes[1];
@@ -330,9 +363,25 @@ __global__ void __launch_bounds__(kSealThreads) histogram_kernel(SealParams p, u
     if (rows == 0 || k_bad || v_bad) return;
     const float ks = __half2float(__ushort_as_half(scale_bits_from_absmax(k_max)));
     const float vs = __half2float(__ushort_as_half(scale_bits_from_absmax(v_max)));
-    for (uint32_t i = tid; i < rows * p.head_dim; i += kSealThreads) {
-        atomicAdd(&hk[quantise_symbol(tile_value(p.tail_k, p.tail_type, tile + i), ks)], 1u);
-        atomicAdd(&hv[quantise_symbol(tile_value(p.tail_v, p.tail_type, tile + i), vs)], 1u);
+    if (split_coder(p.coder)) {   // the symbols these coders code: hi(s[2k]) << 4 | hi(s[2k+1]) in stream order
+        const uint32_t D = p.head_dim, T = p.page_tokens;
+        auto k_sym = [&](uint32_t t, uint32_t d) {
+            return t < rows ? quantise_symbol(tile_value(p.tail_k, p.tail_type, tile + t * D + d), ks) : static_cast<uint32_t>(kZero);
+        };
+        auto v_sym = [&](uint32_t t, uint32_t d) {
+            return t < rows ? quantise_symbol(tile_value(p.tail_v, p.tail_type, tile + t * D + d), vs) : static_cast<uint32_t>(kZero);
+        };
+        for (uint32_t i = tid; i < p.symbols / 2u; i += kSealThreads) {
+            const uint32_t kt = (2u * i) / D, kd = (2u * i) % D;        // K stream: token-major
+            atomicAdd(&hk[(k_sym(kt, kd) & 0xf0u) | (k_sym((2u * i + 1u) / D, (2u * i + 1u) % D) >> 4)], 1u);
+            const uint32_t vd = (2u * i) / T, vt = (2u * i) % T;        // V stream: token-minor
+            atomicAdd(&hv[(v_sym(vt, vd) & 0xf0u) | (v_sym((2u * i + 1u) % T, (2u * i + 1u) / T) >> 4)], 1u);
+        }
+    } else {
+        for (uint32_t i = tid; i < rows * p.head_dim; i += kSealThreads) {
+            atomicAdd(&hk[quantise_symbol(tile_value(p.tail_k, p.tail_type, tile + i), ks)], 1u);
+            atomicAdd(&hv[quantise_symbol(tile_value(p.tail_v, p.tail_type, tile + i), vs)], 1u);
+        }
     }
     __syncthreads();
     for (uint32_t i = tid; i < 256; i += kSealThreads) {
@@ -386,11 +435,13 @@ cf_status validate_common(const cf_b200_seal_desc *d) {
 extern "C" cf_status cf_b200_seal_validate(const cf_b200_seal_desc *d) {
     const cf_status s = cfb::validate_common(d);
     if (s != CF_OK) return s;
-    if (d->coder > CF_B200_CODER_RANS || d->codebook_id > 65535u || d->k_tables == nullptr || d->v_tables == nullptr ||
+    if (d->coder > CF_B200_CODER_MAX || d->codebook_id > 65535u || d->k_tables == nullptr || d->v_tables == nullptr ||
         d->arena == nullptr || d->arena_cursor_units == nullptr || d->page_dir == nullptr ||
         (d->job_count != 0 && d->job_pages == nullptr) || (reinterpret_cast<uintptr_t>(d->arena) & 15u) != 0 ||
         d->arena_units >= (1ull << 40))
         return CF_ERR_INVALID_ARGUMENT;
+    if (cfb::split_coder(d->coder) && (d->block_size % 8u != 0 || (d->head_dim * d->page_tokens) % 8u != 0))
+        return CF_ERR_UNSUPPORTED;   // the raw low-nibble plane is cut into words of eight symbols
     return CF_OK;
 }
 

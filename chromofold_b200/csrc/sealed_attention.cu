@@ -226,8 +226,8 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
             const cf_b200_record_header h = *reinterpret_cast<const cf_b200_record_header *>(record);
             if (h.version != CF_B200_FORMAT_VERSION || h.codebook_id != p.codebook_id ||
                 1u + h.k_part_units + h.v_part_units != units || h.k_part_units > max_part_units ||
-                h.v_part_units > max_part_units || h.token_count == 0 || h.token_count > T || h.k_coder > 2 ||
-                h.v_coder > 2) {
+                h.v_part_units > max_part_units || h.token_count == 0 || h.token_count > T || h.k_coder > CF_B200_CODER_MAX ||
+                h.v_coder > CF_B200_CODER_MAX) {
                 if (tid == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
                 continue;
             }
@@ -431,7 +431,7 @@ __global__ void decode_pages_kernel(AttentionParams p, const uint32_t *page_ids,
     }
     const uint8_t *record = p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry);
     const cf_b200_record_header h = *reinterpret_cast<const cf_b200_record_header *>(record);
-    if (h.version != CF_B200_FORMAT_VERSION || h.k_coder > 2 || h.v_coder > 2) {
+    if (h.version != CF_B200_FORMAT_VERSION || h.k_coder > CF_B200_CODER_MAX || h.v_coder > CF_B200_CODER_MAX) {
         if (threadIdx.x == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
         return;
     }

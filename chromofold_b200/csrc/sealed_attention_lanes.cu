@@ -34,8 +34,13 @@ using namespace lanes;
 #ifndef CFB_LANES_WARPS
 #define CFB_LANES_WARPS 16
 #endif
-constexpr int kWarps = CFB_LANES_WARPS;
-constexpr int kThreads = kWarps * 32;
+#ifndef CFB_LANES_WARPS2
+#define CFB_LANES_WARPS2 16
+#endif
+// Warps per CTA (one CTA per SM): the four-head kernel and the kernels whose query rows live in shared memory (they
+// need 2.3 KB more per warp) are sized separately.
+template <int NG> constexpr int kWarpsOf = NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
+template <int NG> constexpr int kThreadsOf = kWarpsOf<NG> * 32;
 // Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
 template <int NG>
 struct UnitState {
@@ -91,14 +96,14 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &
     if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-            const uint32_t kq = k.quad();
+            const uint32_t kq = k.quad(q);
             if constexpr (kMode == kFold) {
-                u.vq[0] ^= kq ^ v.quad();
+                u.vq[0] ^= kq ^ v.quad(q);
             } else if constexpr (kMode == kDump) {
                 u.dump[q] = kq;
-                u.dump[512 + q] = v.quad();
+                u.dump[512 + q] = v.quad(q);
             } else {
-                u.vq[q] = v.quad();
+                u.vq[q] = v.quad(q);
                 score_quad(u, qs, q, kq);
             }
         }
@@ -127,11 +132,46 @@ __device__ __forceinline__ void decode_fused(KLane &k, VLane &v, UnitState<NG> &
     }
 }
 
+// Both streams nibble-split with the same coder: 32 interleaved steps per stream, a quad from every two of them.
+template <int kMode = kAttend, class Lane, int NG, class QSrc>
+__device__ __forceinline__ void decode_fused_split(Lane &k, Lane &v, UnitState<NG> &u, const QSrc &qs) {
+    uint32_t ke[2], ve[2], kw = 0u, vw = 0u;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (i % 4 == 0) {
+            k.reload();
+            v.reload();
+        }
+        ke[i & 1] = k.symbol();
+        ve[i & 1] = v.symbol();
+        if (i & 1) {
+            const int q = i >> 1;
+            if ((q & 1) == 0) {
+                kw = k.lo_word(q >> 1);
+                vw = v.lo_word(q >> 1);
+            } else {
+                kw >>= 4;
+                vw >>= 4;
+            }
+            const uint32_t kq = merge_split_quad(ke[0], ke[1], kw), vq = merge_split_quad(ve[0], ve[1], vw);
+            if constexpr (kMode == kFold) {
+                u.vq[0] ^= kq ^ vq;
+            } else if constexpr (kMode == kDump) {
+                u.dump[q] = kq;
+                u.dump[512 + q] = vq;
+            } else {
+                u.vq[q] = vq;
+                score_quad(u, qs, q, kq);
+            }
+        }
+    }
+}
+
 template <int kMode = kAttend, class KLane, int NG, class QSrc>
 __device__ __forceinline__ void decode_k_only(KLane &k, UnitState<NG> &u, const QSrc &qs) {
 #pragma unroll
     for (int q = 0; q < 16; ++q) {
-        const uint32_t kq = k.quad();
+        const uint32_t kq = k.quad(q);
         if constexpr (kMode == kFold) u.vq[0] ^= kq;
         else if constexpr (kMode == kDump) u.dump[q] = kq;
         else score_quad(u, qs, q, kq);
@@ -142,7 +182,7 @@ template <int kMode = kAttend, class VLane, int NG>
 __device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
 #pragma unroll
     for (int q = 0; q < 16; ++q) {
-        const uint32_t vq = v.quad();
+        const uint32_t vq = v.quad(q);
         if constexpr (kMode == kFold) u.vq[0] ^= vq;
         else if constexpr (kMode == kDump) u.dump[512 + q] = vq;
         else u.vq[q] = vq;
@@ -161,15 +201,15 @@ struct WarpLayout {
     static constexpr uint32_t kQRows = kBars + 32;
     static constexpr uint32_t kQRowWords = 36;
     static constexpr uint32_t kBytes = (kQRows + (NG == 2 ? 16 * kQRowWords * 4 : 0) + 15u) / 16u * 16u;
-    static constexpr uint32_t kSmem = kTableBytes + kWarps * kBytes;
+    static constexpr uint32_t kSmem = kTableBytes + kWarpsOf<NG> * kBytes;
 };
-static_assert(WarpLayout<2>::kSmem <= 232448, "the eight-head kernel must fit the 227 KB of one CTA");
+static_assert(WarpLayout<1>::kSmem <= 232448 && WarpLayout<2>::kSmem <= 232448, "a CTA has 227 KB of shared memory");
 
 // kSplitQ (with NG = 2): the queries are fp32. A pass serves four heads; their rows are split into binary16(q) and
 // binary16(q - binary16(q)), stored as the rows of group 0 and group 1, the two score fragments are added, and one
 // softmax / P V follows: the scores equal fp32-query scores to 2^-22 relative, at the cost of a second score mma.
 template <int NG, int kMode = kAttend, bool kSplitQ = false>
-__global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionParams p) {
+__global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(AttentionParams p) {
     constexpr bool kProbe = kMode != kAttend;
     static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
     using L = WarpLayout<NG>;
@@ -191,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + L::kBars);
     uint32_t *q_rows = reinterpret_cast<uint32_t *>(warp_mem + L::kQRows);     // NG == 2 only
 
-    load_tables(smem, p, tid, kThreads);   // coding tables: once per CTA
+    load_tables(smem, p, tid, kThreadsOf<NG>);   // coding tables: once per CTA
     reinterpret_cast<uint32_t *>(warp_mem + L::kZero)[lane] = 0u;   // the zero row inactive lanes read their fragments from
     if (lane == 0) {
         mbar_init(&bars[0], 1);
@@ -361,7 +401,17 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
 #pragma unroll
                     for (int n = 0; n < NG; ++n) u.score[n][0] = u.score[n][1] = u.score[n][2] = u.score[n][3] = 0.0f;
 
-                    if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
+                    if (k_coder == CF_B200_CODER_RANS_SPLIT4 && v_coder == CF_B200_CODER_RANS_SPLIT4) {
+                        RansSplitLane k, v;
+                        k.open(k_part, k_bytes, lane, k_slot);
+                        v.open(v_part, v_bytes, lane, v_slot);
+                        decode_fused_split<kMode>(k, v, u, qs);
+                    } else if (k_coder == CF_B200_CODER_HUFFMAN_SPLIT4 && v_coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
+                        HuffSplitLane k, v;
+                        k.open(k_part, k_bytes, lane, k_lut);
+                        v.open(v_part, v_bytes, lane, v_lut);
+                        decode_fused_split<kMode>(k, v, u, qs);
+                    } else if (k_coder == CF_B200_CODER_RANS && v_coder == CF_B200_CODER_RANS) {
                         RansLane k, v;
                         k.open(k_part, k_bytes, lane, k_slot);
                         v.open(v_part, v_bytes, lane, v_slot);
@@ -379,9 +429,13 @@ __global__ void __launch_bounds__(kThreads, 1) lanes_attention_kernel(AttentionP
                     } else {  // mixed coders (one stream fell back to fixed width): one stream after the other
                         if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, k_bytes, lane, k_slot); decode_k_only<kMode>(k, u, qs); }
                         else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, k_bytes, lane, k_lut); decode_k_only<kMode>(k, u, qs); }
+                        else if (k_coder == CF_B200_CODER_RANS_SPLIT4) { RansSplitLane k; k.open(k_part, k_bytes, lane, k_slot); decode_k_only<kMode>(k, u, qs); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN_SPLIT4) { HuffSplitLane k; k.open(k_part, k_bytes, lane, k_lut); decode_k_only<kMode>(k, u, qs); }
                         else { FixedLane k; k.open(k_part, k_bytes, lane); decode_k_only<kMode>(k, u, qs); }
                         if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, v_bytes, lane, v_slot); decode_v_only<kMode>(v, u); }
                         else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, v_bytes, lane, v_lut); decode_v_only<kMode>(v, u); }
+                        else if (v_coder == CF_B200_CODER_RANS_SPLIT4) { RansSplitLane v; v.open(v_part, v_bytes, lane, v_slot); decode_v_only<kMode>(v, u); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN_SPLIT4) { HuffSplitLane v; v.open(v_part, v_bytes, lane, v_lut); decode_v_only<kMode>(v, u); }
                         else { FixedLane v; v.open(v_part, v_bytes, lane); decode_v_only<kMode>(v, u); }
                     }
 
@@ -563,11 +617,11 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         if (e != cudaSuccess) return e;
         state->configured = true;
     }
-    if (p.decode_probe == 2u) lanes_attention_kernel<1, kDump><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
-    else if (p.decode_probe) lanes_attention_kernel<1, kFold><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
-    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, kAttend, true><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
-    else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreads, WarpLayout<1>::kSmem, stream>>>(p);
-    else lanes_attention_kernel<2><<<sm_count, kThreads, WarpLayout<2>::kSmem, stream>>>(p);
+    if (p.decode_probe == 2u) lanes_attention_kernel<1, kDump><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.decode_probe) lanes_attention_kernel<1, kFold><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
+    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, kAttend, true><<<sm_count, kThreadsOf<2>, WarpLayout<2>::kSmem, stream>>>(p);
+    else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
+    else lanes_attention_kernel<2><<<sm_count, kThreadsOf<2>, WarpLayout<2>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

@@ -168,9 +168,9 @@ __device__ __forceinline__ void decode_page(KLane &k, VLane &v, uint32_t (&kq)[1
         }
 #pragma unroll
         for (int q = 12; q < 16; ++q) {
-            if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {
-                kq[q] = k.quad();
-                vq[q] = v.quad();
+            if constexpr (KLane::kWholeQuads || VLane::kWholeQuads) {   // fixed width or nibble-split: a quad per call
+                kq[q] = k.quad(4 * pass + (q - 12));
+                vq[q] = v.quad(4 * pass + (q - 12));
             } else {   // both entropy coded: the two chains interleave symbol by symbol
                 k.reload();
                 v.reload();
@@ -189,7 +189,7 @@ __device__ __forceinline__ void decode_page(KLane &k, VLane &v, uint32_t (&kq)[1
 template <class Lane>
 __device__ __forceinline__ void decode_stream(Lane &s, uint32_t (&quads)[16]) {
 #pragma unroll
-    for (int q = 0; q < 16; ++q) quads[q] = s.quad();
+    for (int q = 0; q < 16; ++q) quads[q] = s.quad(q);
 }
 // The decoded page goes into slot `slot` of the round's tiles as exact binary16 codes. K quad q of lane l = token l/2,
 // channels 64(l&1)+4q..+3 -> K tile row 16*slot + l/2; V quad q of lane l = channel 4l + q/4, tokens 4(q%4)..+3 -> V tile
@@ -380,12 +380,26 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
                         k.open(k_part, k_bytes, lane);
                         v.open(v_part, v_bytes, lane);
                         decode_page(k, v, kq, vq);
+                    } else if (k_coder == CF_B200_CODER_RANS_SPLIT4 && v_coder == CF_B200_CODER_RANS_SPLIT4) {
+                        RansSplitLane k, v;
+                        k.open(k_part, k_bytes, lane, k_slot);
+                        v.open(v_part, v_bytes, lane, v_slot);
+                        decode_page(k, v, kq, vq);
+                    } else if (k_coder == CF_B200_CODER_HUFFMAN_SPLIT4 && v_coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
+                        HuffSplitLane k, v;
+                        k.open(k_part, k_bytes, lane, k_lut);
+                        v.open(v_part, v_bytes, lane, v_lut);
+                        decode_page(k, v, kq, vq);
                     } else {
                         if (k_coder == CF_B200_CODER_RANS) { RansLane k; k.open(k_part, k_bytes, lane, k_slot); decode_stream(k, kq); }
                         else if (k_coder == CF_B200_CODER_HUFFMAN) { HuffLane k; k.open(k_part, k_bytes, lane, k_lut); decode_stream(k, kq); }
+                        else if (k_coder == CF_B200_CODER_RANS_SPLIT4) { RansSplitLane k; k.open(k_part, k_bytes, lane, k_slot); decode_stream(k, kq); }
+                        else if (k_coder == CF_B200_CODER_HUFFMAN_SPLIT4) { HuffSplitLane k; k.open(k_part, k_bytes, lane, k_lut); decode_stream(k, kq); }
                         else { FixedLane k; k.open(k_part, k_bytes, lane); decode_stream(k, kq); }
                         if (v_coder == CF_B200_CODER_RANS) { RansLane v; v.open(v_part, v_bytes, lane, v_slot); decode_stream(v, vq); }
                         else if (v_coder == CF_B200_CODER_HUFFMAN) { HuffLane v; v.open(v_part, v_bytes, lane, v_lut); decode_stream(v, vq); }
+                        else if (v_coder == CF_B200_CODER_RANS_SPLIT4) { RansSplitLane v; v.open(v_part, v_bytes, lane, v_slot); decode_stream(v, vq); }
+                        else if (v_coder == CF_B200_CODER_HUFFMAN_SPLIT4) { HuffSplitLane v; v.open(v_part, v_bytes, lane, v_lut); decode_stream(v, vq); }
                         else { FixedLane v; v.open(v_part, v_bytes, lane); decode_stream(v, vq); }
                     }
                     if (p.decode_probe == 2u) {   // test mode: the quads as decoded, [page id][kv head][K stream | V stream]

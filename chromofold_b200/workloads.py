@@ -9,7 +9,8 @@ import torch
 from . import _native as N
 from .cache import SealedKvLayer, swizzle_dense_tiles
 
-CODERS = {"fixed8": N.CODER_FIXED8, "huffman": N.CODER_HUFFMAN, "rans": N.CODER_RANS}
+CODERS = {"fixed8": N.CODER_FIXED8, "huffman": N.CODER_HUFFMAN, "rans": N.CODER_RANS,
+          "rans4": N.CODER_RANS_SPLIT4, "huffman4": N.CODER_HUFFMAN_SPLIT4}   # the last two: nibble-split (sealed_page_format.h)
 
 
 def uniform_contexts(batch, lo, hi, page_tokens, seed):
@@ -91,6 +92,15 @@ def build_sealed_layer(contexts, *, query_heads=32, kv_heads=8, head_dim=128, pa
                                                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)))
             hist_k, hist_v = hk.cpu().numpy().astype(np.uint64), hv.cpu().numpy().astype(np.uint64)
             layer.set_codebooks(hist_k, hist_v)
+            if CODERS[coder] in (N.CODER_RANS_SPLIT4, N.CODER_HUFFMAN_SPLIT4):
+                # the codebooks were built over pair symbols; the entropy reported per code is that of the plain symbols
+                hk.zero_()
+                hv.zero_()
+                d.coder = N.CODER_RANS
+                N.check("histogram", layer.lib.cf_b200_histogram_async(C.byref(d), C.c_void_p(hk.data_ptr()),
+                                                                        C.c_void_p(hv.data_ptr()),
+                                                                        C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                hist_k, hist_v = hk.cpu().numpy().astype(np.uint64), hv.cpu().numpy().astype(np.uint64)
         first_id = layer.next_page_id
         layer.seal_tiles(slots, k_tiles, v_tiles)
         if keep_dense:

@@ -28,6 +28,18 @@
  *   HUFFMAN : u16 bit_off[nblocks] | pad to 4 | payload u32 words (MSB-first) | pad to 16
  *             bit_off is relative to the first payload bit.
  *   FIXED8  : payload u32 words, symbol i in bits [31-8*(i%4)-7 .. 31-8*(i%4)] of word i/4
+ *   RANS_SPLIT4    : u32 state0[nblocks] | u16 byte_off[nblocks] | pad to 4 | u32 lo[block_size/8][nblocks] | payload | pad to 16
+ *   HUFFMAN_SPLIT4 : u16 bit_off[nblocks] | pad to 4 | u32 lo[block_size/8][nblocks] | payload u32 words | pad to 16
+ *
+ * The nibble-split coders store the LOW nibble of every symbol raw and entropy-code the HIGH nibbles two at a
+ * time: pair symbol k of a block = hi(symbol 2k) << 4 | hi(symbol 2k+1), coded by the same block-rANS / block-
+ * Huffman stream as above (block_size/2 pair symbols per block, tables built over pair symbols). One step of the
+ * reference's recurrence (rans.cu:20-23) or one LUT hit then yields two codes, and at 5-7 bits of entropy per code
+ * the low nibble is so close to uniform that storing it raw costs ~1.5 % (Laplace b = 12). The raw plane is the
+ * reference's fixed-width idea (kv_gpu_fixture.cpp:20-43) at 4 bits, laid out for the decoder: lo[j][b] holds the
+ * low nibbles of symbols 8j..8j+7 of block b — symbol 8j+i at bits 8i..8i+3 for i < 4, symbol 8j+4+i at bits
+ * 8i+4..8i+7 — word-interleaved across blocks, so that 32 lanes decoding 32 blocks read 32 different banks.
+ * Needs block_size % 8 == 0 and page_tokens*head_dim % 8 == 0.
  *
  * Symbol order inside a stream:
  *   K: flat index = token * head_dim + dim   (the reference order, kv_gpu_fixture.cpp:83)
@@ -56,6 +68,9 @@ extern "C" {
 #define CF_B200_CODER_FIXED8 0u
 #define CF_B200_CODER_HUFFMAN 1u
 #define CF_B200_CODER_RANS 2u
+#define CF_B200_CODER_RANS_SPLIT4 3u
+#define CF_B200_CODER_HUFFMAN_SPLIT4 4u
+#define CF_B200_CODER_MAX 4u
 
 /* rans.cu:11-13 */
 #define CF_B200_RANS_PROB_BITS 12u

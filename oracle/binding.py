@@ -9,7 +9,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-CODER_FIXED8, CODER_HUFFMAN, CODER_RANS = 0, 1, 2
+CODER_FIXED8, CODER_HUFFMAN, CODER_RANS, CODER_RANS_SPLIT4, CODER_HUFFMAN_SPLIT4 = 0, 1, 2, 3, 4
 
 
 def build(with_ref=None):

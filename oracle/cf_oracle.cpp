@@ -276,67 +276,102 @@ struct Geometry {
     uint32_t nblocks() const { return (symbols() + block_size - 1) / block_size; }
 };
 
-// One stream part in the record layout of sealed_page_format.h.
-void encode_part(const uint8_t *sym, const Geometry &g, uint32_t coder, const int32_t *freq, const int32_t *cum,
-                 const uint8_t *hlen, const uint32_t *hcode, std::vector<uint8_t> *part) {
-    const uint32_t n = g.symbols();
-    const uint32_t nb = g.nblocks();
-    part->clear();
+bool is_split(uint32_t coder) { return coder == CF_B200_CODER_RANS_SPLIT4 || coder == CF_B200_CODER_HUFFMAN_SPLIT4; }
+
+// Nibble-split coders (sealed_page_format.h): pair symbols and the raw low-nibble plane of a stream.
+void split_symbols(const uint8_t *sym, const Geometry &g, std::vector<uint8_t> *pairs, std::vector<uint32_t> *plane) {
+    const uint32_t n = g.symbols(), nb = g.nblocks(), words_per_block = g.block_size / 8;
+    pairs->assign(n / 2, 0);
+    plane->assign(static_cast<size_t>(words_per_block) * nb, 0u);
+    for (uint32_t i = 0; i < n; i += 2) (*pairs)[i / 2] = static_cast<uint8_t>((sym[i] & 0xf0u) | (sym[i + 1] >> 4));
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint32_t b = i / g.block_size, r = i % g.block_size, j = r / 8, at = r % 8;
+        const uint32_t shift = at < 4 ? 8 * at : 8 * (at - 4) + 4;
+        (*plane)[static_cast<size_t>(j) * nb + b] |= static_cast<uint32_t>(sym[i] & 0x0fu) << shift;
+    }
+}
+uint8_t plane_nibble(const uint32_t *plane, const Geometry &g, uint32_t i) {
+    const uint32_t b = i / g.block_size, r = i % g.block_size, j = r / 8, at = r % 8;
+    const uint32_t shift = at < 4 ? 8 * at : 8 * (at - 4) + 4;
+    return static_cast<uint8_t>((plane[static_cast<size_t>(j) * g.nblocks() + b] >> shift) & 0x0fu);
+}
+
+// The block table and the payload of one plain coded stream (RANS / HUFFMAN / FIXED8) over `n` symbols.
+void encode_stream(const uint8_t *sym, uint32_t n, uint32_t block_size, uint32_t coder, const int32_t *freq, const int32_t *cum,
+                   const uint8_t *hlen, const uint32_t *hcode, std::vector<uint8_t> *table, std::vector<uint8_t> *payload) {
+    const uint32_t nb = (n + block_size - 1) / block_size;
+    table->clear();
+    payload->clear();
     if (coder == CF_B200_CODER_RANS) {
         std::vector<uint32_t> state0(nb);
         std::vector<uint16_t> off(nb);
-        std::vector<uint8_t> payload;
         for (uint32_t b = 0; b < nb; ++b) {
-            const uint32_t base = b * g.block_size;
-            const int cnt = static_cast<int>(std::min(g.block_size, n - base));
-            off[b] = static_cast<uint16_t>(payload.size());
-            state0[b] = rans_encode_block(sym + base, cnt, freq, cum, &payload);
+            const uint32_t base = b * block_size;
+            const int cnt = static_cast<int>(std::min(block_size, n - base));
+            off[b] = static_cast<uint16_t>(payload->size());
+            state0[b] = rans_encode_block(sym + base, cnt, freq, cum, payload);
         }
-        const size_t table = align_up(nb * 4 + nb * 2, 4);
-        part->assign(align_up(table + payload.size(), 16), 0);
-        std::memcpy(part->data(), state0.data(), nb * 4);
-        std::memcpy(part->data() + nb * 4, off.data(), nb * 2);
-        std::memcpy(part->data() + table, payload.data(), payload.size());
+        table->assign(align_up(nb * 4 + nb * 2, 4), 0);
+        std::memcpy(table->data(), state0.data(), nb * 4);
+        std::memcpy(table->data() + nb * 4, off.data(), nb * 2);
     } else if (coder == CF_B200_CODER_HUFFMAN) {
         std::vector<uint16_t> off(nb);
         BitWriter w;
         for (uint32_t i = 0; i < n; ++i) {
-            if (i % g.block_size == 0) off[i / g.block_size] = static_cast<uint16_t>(w.bits);
+            if (i % block_size == 0) off[i / block_size] = static_cast<uint16_t>(w.bits);
             w.put(hcode[sym[i]], hlen[sym[i]]);
         }
-        const size_t table = align_up(nb * 2, 4);
-        part->assign(align_up(table + w.words.size() * 4, 16), 0);
-        std::memcpy(part->data(), off.data(), nb * 2);
-        std::memcpy(part->data() + table, w.words.data(), w.words.size() * 4);
+        table->assign(align_up(nb * 2, 4), 0);
+        std::memcpy(table->data(), off.data(), nb * 2);
+        payload->assign(w.words.size() * 4, 0);
+        std::memcpy(payload->data(), w.words.data(), payload->size());
     } else {
         BitWriter w;
         for (uint32_t i = 0; i < n; ++i) w.put(sym[i], 8);
-        part->assign(align_up(w.words.size() * 4, 16), 0);
-        std::memcpy(part->data(), w.words.data(), w.words.size() * 4);
+        payload->assign(w.words.size() * 4, 0);
+        std::memcpy(payload->data(), w.words.data(), payload->size());
     }
 }
 
-void decode_part(const uint8_t *part, const Geometry &g, uint32_t coder, const int32_t *slot2sym,
-                 const int32_t *freq, const int32_t *cum, const int32_t *lut, uint8_t *sym) {
-    const uint32_t n = g.symbols();
-    const uint32_t nb = g.nblocks();
+// One stream part in the record layout of sealed_page_format.h: table | (raw low-nibble plane) | payload | pad to 16.
+void encode_part(const uint8_t *sym, const Geometry &g, uint32_t coder, const int32_t *freq, const int32_t *cum,
+                 const uint8_t *hlen, const uint32_t *hcode, std::vector<uint8_t> *part) {
+    std::vector<uint8_t> table, payload, pairs;
+    std::vector<uint32_t> plane;
+    if (is_split(coder)) {   // the pair symbols go through the plain coder with half the block size
+        split_symbols(sym, g, &pairs, &plane);
+        encode_stream(pairs.data(), g.symbols() / 2, g.block_size / 2,
+                      coder == CF_B200_CODER_RANS_SPLIT4 ? CF_B200_CODER_RANS : CF_B200_CODER_HUFFMAN, freq, cum, hlen, hcode,
+                      &table, &payload);
+    } else {
+        encode_stream(sym, g.symbols(), g.block_size, coder, freq, cum, hlen, hcode, &table, &payload);
+    }
+    part->assign(align_up(table.size() + plane.size() * 4 + payload.size(), 16), 0);
+    std::memcpy(part->data(), table.data(), table.size());
+    if (!plane.empty()) std::memcpy(part->data() + table.size(), plane.data(), plane.size() * 4);
+    if (!payload.empty()) std::memcpy(part->data() + table.size() + plane.size() * 4, payload.data(), payload.size());
+}
+
+// A plain coded stream back to its `n` symbols: `table` and `payload` as encode_stream laid them out.
+void decode_stream(const uint8_t *table, const uint8_t *payload, uint32_t n, uint32_t block_size, uint32_t coder,
+                   const int32_t *slot2sym, const int32_t *freq, const int32_t *cum, const int32_t *lut, uint8_t *sym) {
+    const uint32_t nb = (n + block_size - 1) / block_size;
     if (coder == CF_B200_CODER_RANS) {
-        const uint32_t *state0 = reinterpret_cast<const uint32_t *>(part);
-        const uint16_t *off = reinterpret_cast<const uint16_t *>(part + nb * 4);
-        const uint8_t *payload = part + align_up(nb * 6, 4);
-        std::vector<int32_t> tmp(g.block_size);
+        const uint32_t *state0 = reinterpret_cast<const uint32_t *>(table);
+        const uint16_t *off = reinterpret_cast<const uint16_t *>(table + nb * 4);
+        std::vector<int32_t> tmp(block_size);
         for (uint32_t b = 0; b < nb; ++b) {  // rans.cu:28-36, one block per loop turn
-            const uint32_t base = b * g.block_size;
-            const int cnt = static_cast<int>(std::min(g.block_size, n - base));
+            const uint32_t base = b * block_size;
+            const int cnt = static_cast<int>(std::min(block_size, n - base));
             rans_decode_block(payload, off[b], state0[b], slot2sym, freq, cum, cnt, tmp.data());
             for (int j = 0; j < cnt; ++j) sym[base + j] = static_cast<uint8_t>(tmp[j]);
         }
     } else if (coder == CF_B200_CODER_HUFFMAN) {
-        const uint16_t *off = reinterpret_cast<const uint16_t *>(part);
-        const uint32_t *words = reinterpret_cast<const uint32_t *>(part + align_up(nb * 2, 4));
+        const uint16_t *off = reinterpret_cast<const uint16_t *>(table);
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(payload);
         for (uint32_t b = 0; b < nb; ++b) {
-            const uint32_t base = b * g.block_size;
-            const uint32_t cnt = std::min(g.block_size, n - base);
+            const uint32_t base = b * block_size;
+            const uint32_t cnt = std::min(block_size, n - base);
             int pos = off[b];
             for (uint32_t j = 0; j < cnt; ++j) {  // paged_kv_attention.cu:101-106 walk
                 const int sl = bh_decode_at(words, lut, CF_B200_HUFF_MAXLEN, pos);
@@ -345,12 +380,32 @@ void decode_part(const uint8_t *part, const Geometry &g, uint32_t coder, const i
             }
         }
     } else {
-        const uint32_t *words = reinterpret_cast<const uint32_t *>(part);
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(payload);
         for (uint32_t i = 0; i < n; ++i) {  // kv_gpu_fixture.cpp:110-116 at 8 bits
             const uint32_t bit = i * 8;
             sym[i] = static_cast<uint8_t>((words[bit >> 5] >> (24 - (bit & 31u))) & 0xffu);
         }
     }
+}
+
+void decode_part(const uint8_t *part, const Geometry &g, uint32_t coder, const int32_t *slot2sym,
+                 const int32_t *freq, const int32_t *cum, const int32_t *lut, uint8_t *sym) {
+    const uint32_t n = g.symbols(), nb = g.nblocks();
+    if (is_split(coder)) {   // the pair symbols through the restated reference decoder, then the nibbles put together
+        const bool rans = coder == CF_B200_CODER_RANS_SPLIT4;
+        const size_t table = align_up(rans ? nb * 6 : nb * 2, 4), plane_bytes = static_cast<size_t>(g.block_size / 8) * nb * 4;
+        std::vector<uint8_t> pairs(n / 2);
+        decode_stream(part, part + table + plane_bytes, n / 2, g.block_size / 2, rans ? CF_B200_CODER_RANS : CF_B200_CODER_HUFFMAN,
+                      slot2sym, freq, cum, lut, pairs.data());
+        const uint32_t *plane = reinterpret_cast<const uint32_t *>(part + table);
+        for (uint32_t i = 0; i < n; i += 2) {
+            sym[i] = static_cast<uint8_t>((pairs[i / 2] & 0xf0u) | plane_nibble(plane, g, i));
+            sym[i + 1] = static_cast<uint8_t>(((pairs[i / 2] & 0x0fu) << 4) | plane_nibble(plane, g, i + 1));
+        }
+        return;
+    }
+    const size_t table = coder == CF_B200_CODER_RANS ? align_up(nb * 6, 4) : coder == CF_B200_CODER_HUFFMAN ? align_up(nb * 2, 4) : 0;
+    decode_stream(part, part + table, n, g.block_size, coder, slot2sym, freq, cum, lut, sym);
 }
 
 // kv_gpu_fixture.cpp:12-16 with one scale per stream: scale = absmax/127 stored as binary16 (1.0 when

@@ -26,6 +26,21 @@ def hist_of(symbols):
     return np.bincount(np.asarray(symbols, np.uint8).ravel(), minlength=256).astype(np.uint64)
 
 
+SPLIT_CODERS = (3, 4)   # CF_B200_CODER_RANS_SPLIT4, CF_B200_CODER_HUFFMAN_SPLIT4
+
+
+def pair_hist_of(symbols):
+    """Histogram of the pair symbols the nibble-split coders code: hi(s[2k]) << 4 | hi(s[2k+1])."""
+    s = np.asarray(symbols, np.uint8).ravel()
+    s = s[:s.size // 2 * 2]
+    return np.bincount((s[0::2] & 0xF0) | (s[1::2] >> 4), minlength=256).astype(np.uint64)
+
+
+def hist_for_coder(symbols, coder):
+    """The histogram a codebook for `coder` is built from: pair symbols for the nibble-split coders."""
+    return pair_hist_of(symbols) if coder in SPLIT_CODERS else hist_of(symbols)
+
+
 class HostCache:
     """CPU-side sealed cache built with the oracle encoder: the reference point for GPU parity checks."""
 

@@ -131,7 +131,7 @@ def test_config5_shared_prefix_with_gpu_sealed_suffixes(native, oracle):
     assert layer.h_page_table[0, prefix // 16] != layer.h_page_table[7, prefix // 16]
 
 
-@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8"])
+@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8", "rans4", "huffman4"])
 @pytest.mark.parametrize("heads", [(32, 8), (64, 8), (8, 8)], ids=str)
 def test_shared_prefix_is_decoded_once_for_all_sequences(native, oracle, coder, heads):
     """The shared-prefix kernel: with the hint the sealed prefix pages are decoded once per 128 query rows and
@@ -305,7 +305,7 @@ def test_prefill_query_tokens_share_the_sealed_history(native, oracle):
     assert np.array_equal(a, b) and layer.device_status() == 0x20
 
 
-@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8"])
+@pytest.mark.parametrize("coder", ["rans", "huffman", "fixed8", "rans4", "huffman4"])
 def test_decode_probe_folds_exactly_the_symbols_of_every_page(native, oracle, coder):
     """CF_B200_KERNEL_DECODE_PROBE runs the lanes kernel's fetch + entropy decode without attention and leaves, per
     (chunk, kv head), the XOR of every 4-symbol word it decoded: it must equal the XOR over the symbols the decode

@@ -2,11 +2,11 @@
 import numpy as np
 import pytest
 
-from helpers import HostCache, attention_close, hist_of, laplace_codes
+from helpers import HostCache, attention_close, hist_for_coder, hist_of, laplace_codes
 
 pytestmark = pytest.mark.gpu
 
-CODERS = {"fixed8": 0, "huffman": 1, "rans": 2}
+CODERS = {"fixed8": 0, "huffman": 1, "rans": 2, "rans4": 3, "huffman4": 4}   # the last two: nibble-split
 
 
 def _layer(native, **kw):
@@ -31,7 +31,7 @@ def _build(native, oracle, rng, *, hq, hkv, d, t, block, coder, contexts, tails,
     n = len(contexts)
     stride = max(1, max((c + t - 1) // t for c in contexts))
     calib = laplace_codes(rng, 1 << 16, b)
-    hist = hist_of(calib.astype(np.int16) + 128)
+    hist = hist_for_coder(calib.astype(np.int16) + 128, coder)
     kcb = oracle.codebook_from_hist(hist)
     vcb = oracle.codebook_from_hist(hist[::-1].copy())
     layer = _layer(native, kv_heads=hkv, query_heads=hq, head_dim=d, page_tokens=t, block_size=block, coder=coder,
@@ -186,7 +186,7 @@ def test_gpu_sealer_is_byte_exact(native, oracle, coder):
     import torch
     rng = np.random.default_rng(23)
     hkv, d, t = 2, 128, 16
-    hist = hist_of(laplace_codes(rng, 1 << 16, 4.0).astype(np.int16) + 128)
+    hist = hist_for_coder(laplace_codes(rng, 1 << 16, 4.0).astype(np.int16) + 128, CODERS[coder])
     kcb = oracle.codebook_from_hist(hist)
     vcb = oracle.codebook_from_hist(hist)
     layer = _layer(native, kv_heads=hkv, query_heads=4, coder=CODERS[coder], max_sequences=5)

@@ -3,7 +3,7 @@ quantiser properties, edge cases."""
 import numpy as np
 import pytest
 
-from helpers import geometric_codes, hist_of, laplace_codes
+from helpers import geometric_codes, hist_for_coder, hist_of, laplace_codes
 
 
 def _streams(rng):
@@ -47,12 +47,12 @@ def test_rans_size_tracks_entropy(oracle):
     assert h0 < bits < h0 + 0.65   # 32-bit start state per 64 symbols is 0.5 bit/symbol
 
 
-@pytest.mark.parametrize("coder", [0, 1, 2])
+@pytest.mark.parametrize("coder", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("geo", [(128, 16, 64), (64, 32, 64), (32, 16, 32), (96, 16, 128), (128, 32, 1024)])
 def test_record_round_trip(oracle, coder, geo):
     d, t, block = geo
     rng = np.random.default_rng(4)
-    cb = oracle.codebook_from_hist(hist_of(laplace_codes(rng, 1 << 15, 6.0).astype(np.int16) + 128))
+    cb = oracle.codebook_from_hist(hist_for_coder(laplace_codes(rng, 1 << 15, 6.0).astype(np.int16) + 128, coder))
     for rows in (t, 1, t - 1):
         k = (rng.standard_normal((rows, d)) * 0.3).astype(np.float16).astype(np.float32)
         v = (rng.standard_normal((rows, d)) * 2.0).astype(np.float16).astype(np.float32)
@@ -71,6 +71,32 @@ def test_record_round_trip(oracle, coder, geo):
         vq = (vs.reshape(d, t).T[:rows].astype(np.float32) - 128.0) * vsc   # V is stored token-minor
         assert np.max(np.abs(vq - v)) <= 0.51 * vsc
         assert np.all(ks.reshape(t, d)[rows:] == 128) and np.all(vs.reshape(d, t)[:, rows:] == 128)
+
+
+def test_nibble_split_record_layout_and_size(oracle):
+    """CF_B200_CODER_RANS_SPLIT4 / _HUFFMAN_SPLIT4: the part is table | raw low-nibble plane | coded pair symbols; the
+    plane holds exactly the low nibbles in the documented bit positions; at Laplace(b = 12) the record is within 3 % of
+    the plain coder's."""
+    rng = np.random.default_rng(5)
+    calib = (laplace_codes(rng, 1 << 16, 12.0).astype(np.int16) + 128).astype(np.uint8)
+    codes = laplace_codes(rng, (16, 128), 12.0)
+    codes[0, 0] = 127
+    k = (codes.astype(np.float32) * 0.01).astype(np.float16).astype(np.float32)
+    sizes = {}
+    for coder in (1, 2, 3, 4):
+        cb = oracle.codebook_from_hist(hist_for_coder(calib, coder))
+        rec, ks, vs = oracle.seal_record(k, k, 16, 128, 16, 64, coder, 0, cb, cb)
+        assert rec[4] == coder and rec[5] == coder
+        sizes[coder] = rec.size
+        assert np.array_equal(ks, (codes.astype(np.int16) + 128).astype(np.uint8).ravel())
+        if coder in (3, 4):
+            table = 192 if coder == 3 else 64
+            plane = rec[16 + table:16 + table + 1024].view("<u4").reshape(8, 32)       # lo[j][block]
+            for block in (0, 7, 31):
+                for i in range(64):
+                    shift = 8 * (i % 4) + (4 if i % 8 >= 4 else 0)
+                    assert (int(plane[i // 8, block]) >> shift) & 15 == int(ks[64 * block + i]) & 15
+    assert sizes[3] <= 1.03 * sizes[2] and sizes[4] <= 1.03 * sizes[1]
 
 
 def test_incompressible_stream_falls_back_to_fixed_width(oracle):
