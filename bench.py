@@ -36,7 +36,8 @@ if ROOT not in sys.path:
 
 # DRAM bytes (read + write) of one attention launch over its algorithmic bytes, from the ncu captures of the batch-16
 # case of the same workload (profiles/lanes_attention_kernel_batch16.md); traffic grows in proportion to the pages read.
-DRAM_TRAFFIC_RATIO = {"rans": 410.8 / 387.9, "huffman": 388.5 / 365.6, "fixed8": 481.9 / 457.0}
+DRAM_TRAFFIC_RATIO = {"rans": 410.8 / 387.9, "huffman": 388.5 / 365.6, "fixed8": 481.9 / 457.0,
+                      "rans4": 410.8 / 387.9, "huffman4": 388.5 / 365.6}
 METRIC = "sealed-KV decode attn seq-tokens/s"
 UNIT = "seq-tokens/s"
 HQ, HKV, D, T, BLOCK = 32, 8, 128, 16, 64
@@ -49,7 +50,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"],
+    ap.add_argument("--coder", default="rans4", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"],
                     help="page coder; rans4 / huffman4 are the nibble-split variants (raw low nibbles, pairs of high nibbles coded)")
     ap.add_argument("--laplace-b", type=float, default=12.0)
     ap.add_argument("--batch", type=int, default=BATCH)
@@ -426,7 +427,7 @@ def main():
         info.pop("dense_v", None)
         del layer
         torch.cuda.empty_cache()
-        for coder in ("rans", "huffman", "fixed8"):
+        for coder in ("rans", "rans4", "huffman", "huffman4", "fixed8"):
             if coder == a.coder:
                 continue
             other, oinfo = build_sealed_layer(contexts, query_heads=HQ, kv_heads=HKV, head_dim=D, page_tokens=T,
