@@ -108,6 +108,10 @@ EXPORTS = {
         "cf_llama_server_append_layer_async", "cf_llama_server_execute_batch_async", "cf_llama_server_shutdown_async",
         "cf_llama_server_get_stats", "cf_llama_server_last_error",
     ],
+    "sealed_kv_multigpu.h": [
+        "cf_b200_mg_create", "cf_b200_mg_destroy", "cf_b200_mg_last_error", "cf_b200_mg_set_device_failed",
+        "cf_b200_mg_plan_sequences", "cf_b200_mg_plan_kv_heads", "cf_b200_mg_execute_async", "cf_b200_mg_get_counters",
+    ],
     "page_transfer.h": ["cf_b200_pages_pack_async", "cf_b200_pages_unpack_async", "cf_b200_fnv1a",
                         "cf_b200_record_checksum"],
     "compat_multigpu.h": [
@@ -147,6 +151,23 @@ EXPORTS = {
         "cf_llama_kv_last_error",
     ],
 }
+
+class MgConfig(C.Structure):   # cf_b200_mg_config
+    _fields_ = [("struct_size", _u32), ("abi_version", _u32), ("device_count", _u32), ("device_ordinals", _vp),
+                ("max_rows", _u32), ("query_head_count", _u32), ("head_dim", _u32), ("query_type", _u32)]
+
+
+class MgShard(C.Structure):    # cf_b200_mg_shard
+    _fields_ = [("desc", SealedAttentionDesc), ("rows", _vp)]
+
+
+class MgCounters(C.Structure):
+    _fields_ = [("steps", _u64), ("attention_launches", _u64), ("peer_copies", _u64), ("peer_bytes", _u64),
+                ("refused_batches", _u64)]
+
+
+MG_BY_SEQUENCE, MG_BY_KV_HEAD = 1, 2
+
 
 class TransferHeader(C.Structure):
     _fields_ = [("magic", _u64), ("version", _u32), ("format_version", _u32), ("kv_head_count", _u32), ("head_dim", _u32),
@@ -200,6 +221,10 @@ def lib():
                      "cf_b200_dense_attention_async", "cf_b200_sealed_attention_static_async"):
             getattr(_lib, name).restype = C.c_int
         _lib.cf_b200_sealed_attention_static_error.restype = C.c_char_p
+        _lib.cf_b200_mg_create.restype = C.c_void_p
+        _lib.cf_b200_mg_last_error.restype = C.c_char_p
+        _lib.cf_b200_mg_last_error.argtypes = [C.c_void_p]
+        _lib.cf_b200_mg_destroy.argtypes = [C.c_void_p]
     return _lib
 
 

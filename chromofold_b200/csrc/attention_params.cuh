@@ -33,7 +33,7 @@ struct AttentionParams {
     // split-KV
     uint8_t *workspace;
     WorkspaceLayout layout;
-    uint32_t min_pages_per_unit;
+    uint32_t min_pages_per_unit;    // 0 = the plan kernel chooses (default_pages_per_unit)
     uint32_t shared_prefix_pages;   // the caller's hint, already zeroed when the launch cannot use it
     uint32_t sm_count;
     uint32_t decode_probe;          // 1 = measurement: decode every page, fold the symbols into a checksum, no attention;

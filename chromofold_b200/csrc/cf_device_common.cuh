@@ -82,6 +82,15 @@ inline LauncherState *launcher_state(LauncherState (&table)[64], cudaError_t *er
     return state;
 }
 
+// Pages per (chunk, kv head) unit when the caller leaves the choice to the library: 16, or fewer (down to 4) when the
+// batch is so small that units of 16 pages would not give every resident warp of the attention kernel (148 SMs x 16
+// warps) about four units to balance over.
+__host__ __device__ inline uint32_t default_pages_per_unit(uint64_t total_pages, uint32_t kv_head_span) {
+    const uint64_t slots = 4ull * 148ull * 16ull;
+    const uint64_t wanted = (total_pages * kv_head_span + slots - 1ull) / slots;
+    return static_cast<uint32_t>(wanted < 4ull ? 4ull : wanted > 16ull ? 16ull : wanted);
+}
+
 // First token a query at `query_token` may see (src/cuda/paged_kv_attention.cu:50-52).
 __host__ __device__ inline uint32_t window_begin(uint32_t query_token, uint32_t causal_window) {
     return causal_window == 0 || query_token + 1u <= causal_window ? 0u : query_token + 1u - causal_window;

@@ -87,9 +87,22 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         shared_chunks = (shared + shared_per_chunk - 1u) / shared_per_chunk;
     }
 
-    uint32_t pages_per_unit = max(p.min_pages_per_unit, 1u);
+    uint32_t pages_per_unit = p.min_pages_per_unit;
     uint32_t overflow = 0;
     uint32_t local = 0;  // chunks of this thread's sequences at the current pages_per_unit
+    if (pages_per_unit == 0u) {   // the library's choice: by the number of pages this launch will read
+        for (uint32_t s = begin; s < end; ++s) local += visible_pages(p, s, nullptr, shared);
+        scan[tid] = local;
+        __syncthreads();
+        if (tid == 0) {
+            uint64_t total = 0;
+            for (uint32_t i = 0; i < kPlanThreads; ++i) total += scan[i];
+            s_total = default_pages_per_unit(total, p.kv_head_span);
+        }
+        __syncthreads();
+        pages_per_unit = s_total;
+        __syncthreads();
+    }
     for (int attempt = 0; attempt < 32; ++attempt) {
         local = 0;
         for (uint32_t s = begin; s < end; ++s) local += (visible_pages(p, s, nullptr, shared) + pages_per_unit - 1u) / pages_per_unit;
@@ -490,7 +503,7 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->workspace = static_cast<uint8_t *>(d->workspace);
     p->layout = workspace_layout(d->seq_count, p->kv_head_span * p->group, d->head_dim, d->workspace_bytes,
                                  d->shared_prefix_pages != 0);
-    p->min_pages_per_unit = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    p->min_pages_per_unit = d->min_pages_per_unit;
     p->shared_prefix_pages = 0;   // the launch code sets it when the lanes kernels serve the call
     p->sm_count = 0;
     p->decode_probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE ? 1u : d->kernel == CF_B200_KERNEL_DECODE_DUMP ? 2u : 0u;
@@ -575,7 +588,7 @@ extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_seal
         return CF_ERR_INVALID_ARGUMENT;
     const uint32_t span = d->kv_head_span ? d->kv_head_span : d->kv_head_count - d->kv_head_begin;
     const uint32_t local_q = span * (d->query_head_count / d->kv_head_count);
-    const uint32_t ppu = d->min_pages_per_unit ? d->min_pages_per_unit : 16u;
+    const uint32_t ppu = d->min_pages_per_unit ? d->min_pages_per_unit : cfb::default_pages_per_unit(total_pages, span);
     const uint64_t chunks = total_pages / ppu + d->seq_count + 1;  // each sequence may round up once
     const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, local_q, d->head_dim, 0, d->shared_prefix_pages != 0);
     *out_bytes = w.partials_offset + chunks * w.partial_stride_floats * 4ull * local_q;

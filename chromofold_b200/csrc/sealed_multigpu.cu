@@ -1,0 +1,371 @@
+// sealed_multigpu.cu — the batch scheduler of include/chromofold_b200/sealed_kv_multigpu.h: one host process, one
+// stream per GPU, sequences or kv heads sharded over the GPUs of a box, query rows out and output rows back as plain
+// peer copies. No kernel here reads or writes another GPU's memory; the two row-permutation kernels run on the root
+// GPU over the root GPU's own buffers.
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <numeric>
+#include <string>
+#include <vector>
+
+#include "chromofold_b200/sealed_kv_multigpu.h"
+
+namespace {
+
+// dst row j = src row perm[j] (kGather) or dst row perm[j] = src row j (scatter); rows are whole 16-byte units.
+template <bool kGather>
+__global__ void permute_rows_kernel(const uint4 *src, uint4 *dst, const uint32_t *perm, uint32_t rows, uint32_t units_per_row) {
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < static_cast<uint64_t>(rows) * units_per_row;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t j = static_cast<uint32_t>(i / units_per_row), u = static_cast<uint32_t>(i % units_per_row);
+        const uint64_t other = static_cast<uint64_t>(perm[j]) * units_per_row + u;
+        if (kGather) dst[i] = src[other];
+        else dst[other] = src[i];
+    }
+}
+
+struct DeviceGuard {   // the calling thread's current device is put back when the call returns
+    int saved = -1;
+    DeviceGuard() { cudaGetDevice(&saved); }
+    ~DeviceGuard() {
+        if (saved >= 0) cudaSetDevice(saved);
+    }
+};
+
+}  // namespace
+
+struct cf_b200_mg_scheduler {
+    cf_b200_mg_config config{};
+    std::vector<int32_t> ordinals;
+    std::vector<cudaStream_t> streams;
+    std::vector<cudaEvent_t> done;
+    std::vector<uint8_t> failed;
+    cudaEvent_t ready = nullptr;
+    uint8_t *staging_q = nullptr;      // root device, max_rows query rows in device-major order
+    float *staging_out = nullptr;      // root device, max_rows output rows in device-major order
+    uint32_t *d_perm = nullptr;        // root device
+    uint32_t *h_perm = nullptr;        // pinned
+    std::vector<uint32_t> last_perm;   // what d_perm holds
+    cf_b200_mg_counters counters{};
+    mutable std::mutex mutex;
+    std::string error;
+
+    size_t query_row_bytes() const {
+        return static_cast<size_t>(config.query_head_count) * config.head_dim * (config.query_type == CF_B200_F32 ? 4u : 2u);
+    }
+    size_t output_row_bytes() const { return static_cast<size_t>(config.query_head_count) * config.head_dim * 4u; }
+    cf_status fail(cf_status code, const std::string &why) {
+        error = why;
+        return code;
+    }
+    cf_status cuda_fail(cudaError_t e, const char *where) {
+        error = std::string(where) + ": " + cudaGetErrorString(e);
+        return CF_ERR_CUDA;
+    }
+    void release() {
+        DeviceGuard guard;
+        for (size_t d = 0; d < ordinals.size(); ++d) {
+            if (cudaSetDevice(ordinals[d]) != cudaSuccess) continue;
+            if (d < streams.size() && streams[d]) cudaStreamDestroy(streams[d]);
+            if (d < done.size() && done[d]) cudaEventDestroy(done[d]);
+        }
+        if (!ordinals.empty() && cudaSetDevice(ordinals[0]) == cudaSuccess) {
+            if (ready) cudaEventDestroy(ready);
+            if (staging_q) cudaFree(staging_q);
+            if (staging_out) cudaFree(staging_out);
+            if (d_perm) cudaFree(d_perm);
+        }
+        if (h_perm) cudaFreeHost(h_perm);
+    }
+};
+
+extern "C" cf_b200_mg_scheduler *cf_b200_mg_create(const cf_b200_mg_config *c) {
+    if (!c || c->struct_size != sizeof(cf_b200_mg_config) || c->abi_version != CF_B200_ABI_VERSION || c->device_count == 0 ||
+        c->device_count > CF_B200_MG_MAX_DEVICES || !c->device_ordinals || c->max_rows == 0 || c->query_head_count == 0 ||
+        c->head_dim == 0 || (c->query_type != CF_B200_F16 && c->query_type != CF_B200_F32) ||
+        (static_cast<uint64_t>(c->query_head_count) * c->head_dim * 2u) % 16u != 0)
+        return nullptr;
+    for (uint32_t i = 0; i < c->device_count; ++i)
+        for (uint32_t j = 0; j < i; ++j)
+            if (c->device_ordinals[i] == c->device_ordinals[j] || c->device_ordinals[i] < 0) return nullptr;
+    auto s = std::make_unique<cf_b200_mg_scheduler>();
+    s->config = *c;
+    s->ordinals.assign(c->device_ordinals, c->device_ordinals + c->device_count);
+    s->config.device_ordinals = nullptr;
+    s->streams.assign(c->device_count, nullptr);
+    s->done.assign(c->device_count, nullptr);
+    s->failed.assign(c->device_count, 0);
+    DeviceGuard guard;
+    bool ok = true;
+    for (uint32_t d = 0; d < c->device_count && ok; ++d) {
+        ok = cudaSetDevice(s->ordinals[d]) == cudaSuccess &&
+             cudaStreamCreateWithFlags(&s->streams[d], cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&s->done[d], cudaEventDisableTiming) == cudaSuccess;
+        if (ok && d > 0) {   // a direct path between the root and this device, both ways, where the box has one
+            int can = 0;
+            if (cudaDeviceCanAccessPeer(&can, s->ordinals[d], s->ordinals[0]) == cudaSuccess && can) {
+                const cudaError_t e = cudaDeviceEnablePeerAccess(s->ordinals[0], 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) ok = false;
+                cudaGetLastError();
+            }
+        }
+    }
+    if (ok) ok = cudaSetDevice(s->ordinals[0]) == cudaSuccess;
+    for (uint32_t d = 1; d < c->device_count && ok; ++d) {
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, s->ordinals[0], s->ordinals[d]) == cudaSuccess && can) {
+            const cudaError_t e = cudaDeviceEnablePeerAccess(s->ordinals[d], 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) ok = false;
+            cudaGetLastError();
+        }
+    }
+    ok = ok && cudaEventCreateWithFlags(&s->ready, cudaEventDisableTiming) == cudaSuccess &&
+         cudaMalloc(&s->staging_q, s->query_row_bytes() * c->max_rows) == cudaSuccess &&
+         cudaMalloc(&s->staging_out, s->output_row_bytes() * c->max_rows) == cudaSuccess &&
+         cudaMalloc(&s->d_perm, sizeof(uint32_t) * c->max_rows) == cudaSuccess &&
+         cudaMallocHost(&s->h_perm, sizeof(uint32_t) * c->max_rows) == cudaSuccess;
+    if (!ok) {
+        s->release();
+        return nullptr;
+    }
+    return s.release();
+}
+
+extern "C" void cf_b200_mg_destroy(cf_b200_mg_scheduler *s) {
+    if (!s) return;
+    {
+        DeviceGuard guard;
+        for (size_t d = 0; d < s->ordinals.size(); ++d)
+            if (cudaSetDevice(s->ordinals[d]) == cudaSuccess) cudaStreamSynchronize(s->streams[d]);
+    }
+    s->release();
+    delete s;
+}
+
+extern "C" const char *cf_b200_mg_last_error(const cf_b200_mg_scheduler *s) { return s ? s->error.c_str() : "scheduler is null"; }
+
+extern "C" cf_status cf_b200_mg_set_device_failed(cf_b200_mg_scheduler *s, int32_t ordinal, uint32_t failed) {
+    if (!s) return CF_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(s->mutex);
+    for (size_t d = 0; d < s->ordinals.size(); ++d)
+        if (s->ordinals[d] == ordinal) {
+            s->failed[d] = failed ? 1 : 0;
+            return CF_OK;
+        }
+    return s->fail(CF_ERR_INVALID_ARGUMENT, "unknown device ordinal");
+}
+
+namespace {
+// Indices of the devices that may take work.
+std::vector<uint32_t> usable_devices(const cf_b200_mg_scheduler *s, uint32_t device_count) {
+    std::vector<uint32_t> out;
+    for (uint32_t d = 0; d < device_count; ++d)
+        if (!s || d >= s->failed.size() || !s->failed[d]) out.push_back(d);
+    return out;
+}
+}  // namespace
+
+extern "C" cf_status cf_b200_mg_plan_sequences(const cf_b200_mg_scheduler *s, const uint64_t *lengths, uint32_t n, uint32_t device_count,
+                                               uint32_t *out_device) {
+    if ((!lengths && n) || (!out_device && n) || device_count == 0 || device_count > CF_B200_MG_MAX_DEVICES ||
+        (s && device_count != s->ordinals.size()))
+        return CF_ERR_INVALID_ARGUMENT;
+    std::vector<uint32_t> devices;
+    if (s) {
+        std::lock_guard<std::mutex> lock(s->mutex);
+        devices = usable_devices(s, device_count);
+    } else {
+        devices = usable_devices(nullptr, device_count);
+    }
+    if (devices.empty()) return CF_ERR_UNSUPPORTED;
+    // longest processing time first: sequences by falling length (ties: lower index), each to the least loaded device
+    // (ties: lower device index)
+    std::vector<uint32_t> order(n);
+    std::iota(order.begin(), order.end(), 0u);
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return lengths[a] > lengths[b]; });
+    std::vector<uint64_t> load(devices.size(), 0);
+    for (uint32_t i : order) {
+        size_t best = 0;
+        for (size_t d = 1; d < devices.size(); ++d)
+            if (load[d] < load[best]) best = d;
+        out_device[i] = devices[best];
+        load[best] += lengths[i];
+    }
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_mg_plan_kv_heads(const cf_b200_mg_scheduler *s, uint32_t kv_heads, uint32_t device_count, uint32_t *out_begin,
+                                              uint32_t *out_span) {
+    if (kv_heads == 0 || device_count == 0 || device_count > CF_B200_MG_MAX_DEVICES || !out_begin || !out_span ||
+        (s && device_count != s->ordinals.size()))
+        return CF_ERR_INVALID_ARGUMENT;
+    std::vector<uint32_t> devices;
+    if (s) {
+        std::lock_guard<std::mutex> lock(s->mutex);
+        devices = usable_devices(s, device_count);
+    } else {
+        devices = usable_devices(nullptr, device_count);
+    }
+    if (devices.empty()) return CF_ERR_UNSUPPORTED;
+    for (uint32_t d = 0; d < device_count; ++d) out_begin[d] = out_span[d] = 0;
+    const uint32_t active = std::min<uint32_t>(static_cast<uint32_t>(devices.size()), kv_heads);
+    const uint32_t base = kv_heads / active, extra = kv_heads % active;
+    uint32_t begin = 0;
+    for (uint32_t i = 0; i < active; ++i) {   // contiguous blocks, the first `extra` devices take one head more
+        const uint32_t span = base + (i < extra ? 1u : 0u);
+        out_begin[devices[i]] = begin;
+        out_span[devices[i]] = span;
+        begin += span;
+    }
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_b200_mg_shard *shards, uint32_t shard_count,
+                                              const void *root_queries, void *root_output, uint32_t row_count, uint32_t mode,
+                                              void *root_stream_ptr) {
+    if (!s) return CF_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(s->mutex);
+    const uint32_t devices = static_cast<uint32_t>(s->ordinals.size());
+    if (!shards || shard_count != devices || !root_queries || !root_output || row_count == 0 || row_count > s->config.max_rows ||
+        (mode != CF_B200_MG_BY_SEQUENCE && mode != CF_B200_MG_BY_KV_HEAD))
+        return s->fail(CF_ERR_INVALID_ARGUMENT, "bad arguments");
+    uint32_t listed = 0;
+    for (uint32_t d = 0; d < devices; ++d) {
+        const cf_b200_sealed_attention_desc &desc = shards[d].desc;
+        if (desc.seq_count == 0) continue;
+        if (s->failed[d]) {
+            ++s->counters.refused_batches;
+            return s->fail(CF_ERR_UNSUPPORTED, "a shard names a device that is marked failed");
+        }
+        if (desc.query_head_count != s->config.query_head_count || desc.head_dim != s->config.head_dim ||
+            desc.query_type != s->config.query_type || desc.output_type != CF_B200_F32 || !desc.queries || !desc.output ||
+            desc.seq_count > s->config.max_rows)
+            return s->fail(CF_ERR_INVALID_ARGUMENT, "a shard does not match the scheduler's row shape");
+        for (uint32_t i = 0; shards[d].rows && i < desc.seq_count; ++i)
+            if (shards[d].rows[i] >= row_count) return s->fail(CF_ERR_INVALID_ARGUMENT, "a shard lists a row outside the batch");
+        if (!shards[d].rows && desc.seq_count > row_count) return s->fail(CF_ERR_INVALID_ARGUMENT, "a shard has more entries than rows");
+        const cf_status valid = cf_b200_sealed_attention_validate(&desc);
+        if (valid != CF_OK) return s->fail(valid, "a shard's descriptor is not valid");
+        listed += desc.seq_count;
+    }
+    if (listed == 0) return s->fail(CF_ERR_INVALID_ARGUMENT, "no device has work");
+    if (mode == CF_B200_MG_BY_SEQUENCE && listed > s->config.max_rows) return s->fail(CF_ERR_INVALID_ARGUMENT, "more entries than max_rows");
+
+    DeviceGuard guard;
+    cudaStream_t root_stream = static_cast<cudaStream_t>(root_stream_ptr);
+    const size_t q_row = s->query_row_bytes(), o_row = s->output_row_bytes();
+    cudaError_t e = cudaSetDevice(s->ordinals[0]);
+    if (e != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+
+    if (mode == CF_B200_MG_BY_SEQUENCE) {
+        // query rows into device-major order on the root (one kernel), one copy per device out, one per device back,
+        // output rows back into batch order (one kernel)
+        uint32_t at = 0;
+        bool changed = s->last_perm.size() != listed;
+        for (uint32_t d = 0; d < devices; ++d)
+            for (uint32_t i = 0; i < shards[d].desc.seq_count; ++i, ++at) {
+                const uint32_t row = shards[d].rows ? shards[d].rows[i] : i;
+                if (!changed && s->last_perm[at] != row) changed = true;
+                s->h_perm[at] = row;
+            }
+        if (changed) {   // a new placement: the row order goes to the root device (a few hundred bytes)
+            e = cudaMemcpyAsync(s->d_perm, s->h_perm, sizeof(uint32_t) * listed, cudaMemcpyHostToDevice, root_stream);
+            if (e != cudaSuccess) return s->cuda_fail(e, "row order upload");
+            e = cudaStreamSynchronize(root_stream);   // h_perm is rewritten by the next call
+            if (e != cudaSuccess) return s->cuda_fail(e, "row order upload");
+            s->last_perm.assign(s->h_perm, s->h_perm + listed);
+        }
+        const uint32_t q_units = static_cast<uint32_t>(q_row / 16u), o_units = static_cast<uint32_t>(o_row / 16u);
+        const uint32_t blocks = std::min<uint32_t>(1024u, (listed * q_units + 255u) / 256u);
+        permute_rows_kernel<true><<<blocks, 256, 0, root_stream>>>(static_cast<const uint4 *>(root_queries),
+                                                                   reinterpret_cast<uint4 *>(s->staging_q), s->d_perm, listed, q_units);
+        e = cudaEventRecord(s->ready, root_stream);
+        if (e != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
+        at = 0;
+        for (uint32_t d = 0; d < devices; ++d) {
+            const cf_b200_sealed_attention_desc &desc = shards[d].desc;
+            if (desc.seq_count == 0) continue;
+            cudaStream_t stream = s->streams[d];
+            if ((e = cudaSetDevice(s->ordinals[d])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+            if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
+            e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], s->staging_q + q_row * at, s->ordinals[0],
+                                    q_row * desc.seq_count, stream);
+            if (e != cudaSuccess) return s->cuda_fail(e, "query rows out");
+            const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
+            if (launched != CF_OK) return s->fail(launched, "attention launch failed on a device");
+            e = cudaMemcpyPeerAsync(s->staging_out + (o_row / 4u) * at, s->ordinals[0], desc.output, s->ordinals[d],
+                                    o_row * desc.seq_count, stream);
+            if (e != cudaSuccess) return s->cuda_fail(e, "output rows back");
+            if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
+            ++s->counters.attention_launches;
+            s->counters.peer_copies += d == 0 ? 0u : 2u;
+            s->counters.peer_bytes += d == 0 ? 0u : (q_row + o_row) * desc.seq_count;
+            at += desc.seq_count;
+        }
+        if ((e = cudaSetDevice(s->ordinals[0])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+        for (uint32_t d = 0; d < devices; ++d)
+            if (shards[d].desc.seq_count && (e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess)
+                return s->cuda_fail(e, "cudaStreamWaitEvent");
+        const uint32_t oblocks = std::min<uint32_t>(1024u, (listed * o_units + 255u) / 256u);
+        permute_rows_kernel<false><<<oblocks, 256, 0, root_stream>>>(reinterpret_cast<const uint4 *>(s->staging_out),
+                                                                     static_cast<uint4 *>(root_output), s->d_perm, listed, o_units);
+        if ((e = cudaPeekAtLastError()) != cudaSuccess) return s->cuda_fail(e, "row permutation");
+    } else {
+        // every device serves the same rows with its own kv heads: all query rows out, its query-head columns back
+        e = cudaEventRecord(s->ready, root_stream);
+        if (e != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
+        for (uint32_t d = 0; d < devices; ++d) {
+            const cf_b200_sealed_attention_desc &desc = shards[d].desc;
+            if (desc.seq_count == 0) continue;
+            if (shards[d].rows || desc.seq_count != row_count)
+                return s->fail(CF_ERR_INVALID_ARGUMENT, "kv-head sharding serves every row on every device");
+            const uint32_t group = desc.query_head_count / desc.kv_head_count;
+            const uint32_t span = desc.kv_head_span ? desc.kv_head_span : desc.kv_head_count - desc.kv_head_begin;
+            cudaStream_t stream = s->streams[d];
+            if ((e = cudaSetDevice(s->ordinals[d])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+            if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
+            if (desc.queries != root_queries) {   // the root device may read the caller's rows in place
+                e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], root_queries, s->ordinals[0], q_row * row_count, stream);
+                if (e != cudaSuccess) return s->cuda_fail(e, "query rows out");
+            }
+            const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
+            if (launched != CF_OK) return s->fail(launched, "attention launch failed on a device");
+            // columns [kv_head_begin * group, (kv_head_begin + span) * group) of every row: one pitched peer copy
+            cudaMemcpy3DPeerParms parms{};
+            const size_t column = static_cast<size_t>(desc.kv_head_begin) * group * desc.head_dim * 4u;
+            const size_t width = static_cast<size_t>(span) * group * desc.head_dim * 4u;
+            parms.srcDevice = s->ordinals[d];
+            parms.dstDevice = s->ordinals[0];
+            parms.srcPtr = make_cudaPitchedPtr(desc.output, o_row, o_row, row_count);
+            parms.dstPtr = make_cudaPitchedPtr(root_output, o_row, o_row, row_count);
+            parms.srcPos = make_cudaPos(column, 0, 0);
+            parms.dstPos = make_cudaPos(column, 0, 0);
+            parms.extent = make_cudaExtent(width, row_count, 1);
+            if (desc.output != root_output && (e = cudaMemcpy3DPeerAsync(&parms, stream)) != cudaSuccess)   // the root may write in place
+                return s->cuda_fail(e, "output columns back");
+            if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
+            ++s->counters.attention_launches;
+            s->counters.peer_copies += d == 0 ? 0u : 2u;
+            s->counters.peer_bytes += d == 0 ? 0u : q_row * row_count + width * row_count;
+        }
+        if ((e = cudaSetDevice(s->ordinals[0])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+        for (uint32_t d = 0; d < devices; ++d)
+            if (shards[d].desc.seq_count && (e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess)
+                return s->cuda_fail(e, "cudaStreamWaitEvent");
+    }
+    ++s->counters.steps;
+    s->error.clear();
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_mg_get_counters(const cf_b200_mg_scheduler *s, cf_b200_mg_counters *out) {
+    if (!s || !out) return CF_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(s->mutex);
+    *out = s->counters;
+    return CF_OK;
+}

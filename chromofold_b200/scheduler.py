@@ -12,7 +12,13 @@ Attention of one (sequence, kv head) depends on nothing else, so the path shards
     include/chromofold/multigpu_cuda_runtime.h:53-66).
 
 The only exchange is the optional gather of outputs to rank 0 (torch.distributed: NCCL on GPUs, gloo on CPU ranks).
+
+MultiGpuScheduler is the other way to run the same split: ONE process drives every GPU of the box through the C ABI
+of include/chromofold_b200/sealed_kv_multigpu.h (a stream per GPU, the placement rules above in C++, query rows out and
+output rows back as peer copies).
 """
+import ctypes as C
+
 import numpy as np
 
 
@@ -86,3 +92,122 @@ def gather_head_outputs(local_out, head_shards, group, rank, world_size, dist=No
         if span:
             full[:, begin * group:(begin + span) * group] = bucket[r][:, begin * group:(begin + span) * group]
     return full
+
+
+class MultiGpuScheduler:
+    """One process, several GPUs: cf_b200_mg_* over one SealedKvLayer per device (layers[0] lives on the root device,
+    where the queries arrive and the outputs are gathered)."""
+
+    def __init__(self, layers, max_rows, query_dtype=None):
+        import torch
+        from . import _native as N
+        self.N, self.torch, self.lib = N, torch, N.lib()
+        self.layers = list(layers)
+        self.ordinals = [lay.device.index if lay.device.index is not None else 0 for lay in self.layers]
+        first = self.layers[0]
+        self.query_dtype = query_dtype or torch.float16
+        self._ordinals = (C.c_int32 * len(self.ordinals))(*self.ordinals)
+        cfg = N.MgConfig()
+        cfg.struct_size, cfg.abi_version = C.sizeof(N.MgConfig), N.ABI_VERSION
+        cfg.device_count, cfg.device_ordinals = len(self.ordinals), C.cast(self._ordinals, C.c_void_p)
+        cfg.max_rows, cfg.query_head_count, cfg.head_dim = max_rows, first.query_heads, first.head_dim
+        cfg.query_type = N.F16 if self.query_dtype == torch.float16 else N.F32
+        self.handle = self.lib.cf_b200_mg_create(C.byref(cfg))
+        if not self.handle:
+            raise RuntimeError("cf_b200_mg_create failed (bad config or no such CUDA devices)")
+        self.max_rows = max_rows
+        shape = (max_rows, first.query_heads, first.head_dim)
+        self.q_local = [torch.zeros(shape, dtype=self.query_dtype, device=lay.device) for lay in self.layers]
+        self.out_local = [torch.zeros(shape, dtype=torch.float32, device=lay.device) for lay in self.layers]
+        self._keep = None
+
+    def close(self):
+        if self.handle:
+            self.lib.cf_b200_mg_destroy(C.c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, what, status):
+        if status != self.N.CF_OK:
+            raise self.N.CfError(what + ": " + self.lib.cf_b200_mg_last_error(C.c_void_p(self.handle)).decode(), status)
+
+    def set_device_failed(self, ordinal, failed=True):
+        self._check("set_device_failed", self.lib.cf_b200_mg_set_device_failed(C.c_void_p(self.handle), C.c_int32(ordinal),
+                                                                              C.c_uint32(1 if failed else 0)))
+
+    def plan_sequences(self, context_lengths):
+        """-> per device index the list of sequence indices it serves (ascending)."""
+        lengths = np.ascontiguousarray(context_lengths, np.uint64)
+        out = np.zeros(len(lengths), np.uint32)
+        self._check("plan_sequences", self.lib.cf_b200_mg_plan_sequences(
+            C.c_void_p(self.handle), lengths.ctypes.data_as(C.c_void_p), C.c_uint32(len(lengths)), C.c_uint32(len(self.layers)),
+            out.ctypes.data_as(C.c_void_p)))
+        return [np.nonzero(out == d)[0].tolist() for d in range(len(self.layers))]
+
+    def plan_kv_heads(self, kv_heads):
+        begin = np.zeros(len(self.layers), np.uint32)
+        span = np.zeros(len(self.layers), np.uint32)
+        self._check("plan_kv_heads", self.lib.cf_b200_mg_plan_kv_heads(
+            C.c_void_p(self.handle), C.c_uint32(kv_heads), C.c_uint32(len(self.layers)), begin.ctypes.data_as(C.c_void_p),
+            span.ctypes.data_as(C.c_void_p)))
+        return list(zip(begin.tolist(), span.tolist()))
+
+    def counters(self):
+        c = self.N.MgCounters()
+        self._check("get_counters", self.lib.cf_b200_mg_get_counters(C.c_void_p(self.handle), C.byref(c)))
+        return {name: int(getattr(c, name)) for name, _ in c._fields_}
+
+    def _shards(self, per_device, mode, row_count, **desc_kw):
+        """per_device[d] = (local slots, root rows or None, kv_head_begin, kv_head_span)."""
+        N = self.N
+        shards = (N.MgShard * len(self.layers))()
+        keep = []
+        for d, lay in enumerate(self.layers):
+            slots, rows, begin, span = per_device[d]
+            n = len(slots)
+            if n == 0:
+                continue
+            out = self.out_local[d] if not (mode == N.MG_BY_KV_HEAD and d == 0 and desc_kw.get("root_out") is not None) else desc_kw["root_out"]
+            desc = lay._attention_desc(self.q_local[d], out, n, slots)
+            desc.softmax_scale = 1.0 / float(np.sqrt(lay.head_dim))
+            desc.kv_head_begin, desc.kv_head_span = begin, span
+            desc.min_pages_per_unit = desc_kw.get("min_pages_per_unit", 0)
+            keep.append(lay._slots_keepalive)
+            shards[d].desc = desc
+            if rows is not None:
+                arr = np.ascontiguousarray(rows, np.uint32)
+                keep.append(arr)
+                shards[d].rows = arr.ctypes.data_as(C.c_void_p)
+        self._keep = keep
+        return shards
+
+    def attention_by_sequence(self, queries, out, assignment, local_slots, **kw):
+        """queries/out: root-device tensors [rows][Hq][D]; assignment[d] = rows served by device d; local_slots[d] = the
+        slots those sequences occupy in layers[d] (same order)."""
+        N = self.N
+        per = [(local_slots[d], assignment[d], 0, 0) for d in range(len(self.layers))]
+        shards = self._shards(per, N.MG_BY_SEQUENCE, queries.shape[0], **kw)
+        stream = self.torch.cuda.current_stream(self.layers[0].device).cuda_stream
+        self._check("mg_execute", self.lib.cf_b200_mg_execute_async(
+            C.c_void_p(self.handle), shards, C.c_uint32(len(self.layers)), C.c_void_p(queries.data_ptr()), C.c_void_p(out.data_ptr()),
+            C.c_uint32(queries.shape[0]), C.c_uint32(N.MG_BY_SEQUENCE), C.c_void_p(stream)))
+        return out
+
+    def attention_by_kv_head(self, queries, out, head_shards, slots, **kw):
+        """Every device serves every row with its block of kv heads (head_shards[d] = (begin, span)); device-local slot ids
+        are `slots` on every device. The root device writes its columns straight into `out`."""
+        N = self.N
+        per = [(slots if head_shards[d][1] else [], None, head_shards[d][0], head_shards[d][1]) for d in range(len(self.layers))]
+        shards = self._shards(per, N.MG_BY_KV_HEAD, queries.shape[0], root_out=out, **kw)
+        if head_shards[0][1]:
+            shards[0].desc.queries = queries.data_ptr()   # the root reads the caller's rows in place
+        stream = self.torch.cuda.current_stream(self.layers[0].device).cuda_stream
+        self._check("mg_execute", self.lib.cf_b200_mg_execute_async(
+            C.c_void_p(self.handle), shards, C.c_uint32(len(self.layers)), C.c_void_p(queries.data_ptr()), C.c_void_p(out.data_ptr()),
+            C.c_uint32(queries.shape[0]), C.c_uint32(N.MG_BY_KV_HEAD), C.c_void_p(stream)))
+        return out

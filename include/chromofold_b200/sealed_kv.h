@@ -95,7 +95,8 @@ typedef struct cf_b200_sealed_attention_desc {
 
     void *workspace;                     /* split-KV partials; see cf_b200_sealed_attention_workspace_bytes */
     uint64_t workspace_bytes;
-    uint32_t min_pages_per_unit;         /* 0 = default (16) */
+    uint32_t min_pages_per_unit;         /* pages per split-KV unit; 0 = the library chooses: 16, or down to 4 for batches
+                                            too small to fill the GPU with units of 16 */
     uint32_t kernel;                     /* CF_B200_KERNEL_* */
     uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
     uint32_t tail_type;                  /* CF_B200_F16 (0 means F16 too) or CF_B200_F32: element type of the tails */

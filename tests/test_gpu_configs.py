@@ -314,7 +314,8 @@ def test_decode_probe_folds_exactly_the_symbols_of_every_page(native, oracle, co
     from chromofold_b200.workloads import build_sealed_layer
     layer, info = build_sealed_layer(np.array([160, 64]), coder=coder, seed=85)
     q = _q(2, 32, 86)
-    layer.attention(q, kernel=native.KERNEL_DECODE_PROBE, stages=native.STAGE_PLAN | native.STAGE_ATTENTION)
+    layer.attention(q, kernel=native.KERNEL_DECODE_PROBE, stages=native.STAGE_PLAN | native.STAGE_ATTENTION,
+                    min_pages_per_unit=16)
     torch.cuda.synchronize()
     assert layer.device_status() == 0
     ws = layer.workspace

@@ -1,0 +1,96 @@
+"""The one-process batch scheduler (include/chromofold_b200/sealed_kv_multigpu.h) on the GPUs that are there: with one
+GPU it still goes through its own streams, row permutation and copies; with two or more it shards for real."""
+import numpy as np
+import pytest
+
+from helpers import attention_close, oracle_from_layer
+
+pytestmark = pytest.mark.gpu
+
+
+def _queries(n, hq, seed, device):
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.randn((n, hq, 128), generator=g, device=device, dtype=torch.float32).half()
+
+
+def _devices():
+    import torch
+    return min(torch.cuda.device_count(), 4)
+
+
+@pytest.mark.parametrize("coder", ["rans4", "huffman"])
+def test_sequences_sharded_over_the_devices_of_one_process(native, oracle, coder):
+    """A batch of 11 sequences placed by the C planner; every device holds only its own sequences' pages; the gathered
+    output equals what one store holding everything returns, and the oracle's result."""
+    import torch
+    from chromofold_b200.scheduler import MultiGpuScheduler
+    from chromofold_b200.workloads import build_sealed_layer
+    world = _devices()
+    contexts = (np.arange(11) * 37 % 23 + 1) * 16 * 4
+    whole, _ = build_sealed_layer(contexts, coder=coder, seed=90, device="cuda:0")
+    q = _queries(11, 32, 91, "cuda:0")
+    want = whole.attention(q, min_pages_per_unit=16).cpu().numpy()   # units pinned: the same split-KV cut in every store
+    ok, err = attention_close(want, oracle_from_layer(whole, q.cpu().numpy()))
+    assert ok, err
+    # the same pages, spread: the records are copied out of the one store into per-device stores, page by page
+    from chromofold_b200.scheduler import shard_sequences
+    assignment = shard_sequences(contexts, world)     # the C planner gives the same placement (checked below)
+    layers, local_slots = [], []
+    for d in range(world):
+        mine = assignment[d]
+        lay, _ = build_sealed_layer(np.array([0] * max(len(mine), 1)), coder=coder, seed=93 + d, device=f"cuda:{d}",
+                                    extra_pages_per_sequence=int(contexts.max()) // 16 + 2, reserve_pages=int(contexts.sum()) // 16 + 8)
+        lay.k_tables.copy_(whole.k_tables.to(lay.device))
+        lay.v_tables.copy_(whole.v_tables.to(lay.device))
+        lay.host_tables = whole.host_tables
+        for local, seq in enumerate(mine):
+            pages = int(contexts[seq]) // 16
+            recs = [[whole.record_bytes(int(whole.h_page_table[seq, p]), h) for h in range(8)] for p in range(pages)]
+            lay.import_records(local, recs)
+        layers.append(lay)
+        local_slots.append(list(range(len(mine))))
+    sched = MultiGpuScheduler(layers, max_rows=16)
+    assert sched.plan_sequences(contexts) == assignment
+    out = torch.zeros((11, 32, 128), dtype=torch.float32, device="cuda:0")
+    for _ in range(2):    # the second step reuses the cached row order
+        out.zero_()
+        sched.attention_by_sequence(q, out, assignment, local_slots, min_pages_per_unit=16)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+    c = sched.counters()
+    assert c["steps"] == 2 and c["attention_launches"] == 2 * sum(1 for a in assignment if a)
+    assert all(lay.device_status() == 0 for lay in layers)
+    # a device marked failed: the batch that names it is refused, the planner routes around it
+    if world > 1:
+        sched.set_device_failed(1)
+        with pytest.raises(native.CfError):
+            sched.attention_by_sequence(q, out, assignment, local_slots, min_pages_per_unit=16)
+        assert sched.plan_sequences(contexts)[1] == []
+        assert sched.counters()["refused_batches"] == 1
+    sched.close()
+
+
+def test_kv_heads_sharded_over_the_devices_of_one_process(native, oracle):
+    """70B-shaped groups (64 query / 8 kv heads): every device serves all rows with its block of kv heads (a replica of
+    the store per device here) and its query-head columns are gathered into the root's output."""
+    import torch
+    from chromofold_b200.scheduler import MultiGpuScheduler
+    from chromofold_b200.workloads import build_sealed_layer
+    world = _devices()
+    contexts = np.array([1024, 2048, 512])
+    layers = [build_sealed_layer(contexts, query_heads=64, kv_heads=8, coder="rans4", seed=95, device=f"cuda:{d}")[0] for d in range(world)]
+    q = _queries(3, 64, 96, "cuda:0")
+    want = layers[0].attention(q, min_pages_per_unit=16).cpu().numpy()
+    ok, err = attention_close(want, oracle_from_layer(layers[0], q.cpu().numpy()))
+    assert ok, err
+    sched = MultiGpuScheduler(layers, max_rows=8)
+    for ways in sorted({1, world}):
+        heads = sched.plan_kv_heads(8) if ways == world else [(0, 8)] + [(0, 0)] * (world - 1)
+        assert sum(s for _, s in heads) == 8
+        out = torch.zeros((3, 64, 128), dtype=torch.float32, device="cuda:0")
+        sched.attention_by_kv_head(q, out, heads, [0, 1, 2], min_pages_per_unit=16)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want), ways
+    sched.close()

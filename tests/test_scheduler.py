@@ -62,3 +62,27 @@ def test_output_gather_world_size_2_gloo():
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret["seq"] == [[float(100 * s + h) for h in range(8)] for s in range(11)]
     assert ret["head"] == [[0.0, 1.0, 2.0, 3.0, 14.0, 15.0, 16.0, 17.0]] * 3
+
+
+def test_c_planners_follow_the_same_rules(native):
+    """cf_b200_mg_plan_sequences / _plan_kv_heads (the one-process scheduler's placement, host arithmetic only) give the
+    placements of shard_sequences / shard_kv_heads; arguments are checked before anything else."""
+    import ctypes as C
+    lib = native.lib()
+    rng = np.random.default_rng(5)
+    for n, world in ((64, 8), (64, 3), (11, 2), (5, 8), (0, 4)):
+        ctx = (rng.integers(2048, 32769, n) // 16 * 16).astype(np.uint64)
+        out = np.full(n, 99, np.uint32)
+        assert lib.cf_b200_mg_plan_sequences(None, ctx.ctypes.data_as(C.c_void_p), n, world, out.ctypes.data_as(C.c_void_p)) == 0
+        assert [np.nonzero(out == d)[0].tolist() for d in range(world)] == shard_sequences(ctx, world)
+    for heads, world in ((8, 1), (8, 4), (8, 8), (8, 3), (2, 4)):
+        begin, span = np.zeros(world, np.uint32), np.zeros(world, np.uint32)
+        assert lib.cf_b200_mg_plan_kv_heads(None, heads, world, begin.ctypes.data_as(C.c_void_p), span.ctypes.data_as(C.c_void_p)) == 0
+        assert list(zip(begin.tolist(), span.tolist())) == shard_kv_heads(heads, world)
+    one = np.ones(1, np.uint64)
+    assert lib.cf_b200_mg_plan_sequences(None, one.ctypes.data_as(C.c_void_p), 1, 0, one.ctypes.data_as(C.c_void_p)) == native.CF_ERR_INVALID_ARGUMENT
+    assert lib.cf_b200_mg_plan_sequences(None, None, 1, 2, one.ctypes.data_as(C.c_void_p)) == native.CF_ERR_INVALID_ARGUMENT
+    assert lib.cf_b200_mg_plan_kv_heads(None, 0, 2, one.ctypes.data_as(C.c_void_p), one.ctypes.data_as(C.c_void_p)) == native.CF_ERR_INVALID_ARGUMENT
+    assert lib.cf_b200_mg_create(None) is None
+    assert lib.cf_b200_mg_execute_async(None, None, 0, None, None, 0, 1, None) == native.CF_ERR_INVALID_ARGUMENT
+    assert C.sizeof(native.MgShard) == C.sizeof(native.SealedAttentionDesc) + 8 and C.sizeof(native.MgConfig) == 40
