@@ -63,6 +63,9 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed comparison kernel")
     ap.add_argument("--no-others", action="store_true", help="skip the legs that time the same workload sealed with the other coders")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the other configurations (3, 4, 5 at full size with their oracle checks; on several GPUs the "
+                         "strong-scaling and kv-head-sharding legs of the one-process scheduler)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every rank has its own batch; strong: one batch sharded over the ranks by the scheduler")
@@ -185,6 +188,79 @@ def run_reference(a, rank):
                  "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                  "gpu_launches": 0})
     print(json.dumps(line))
+
+
+def _oracle_books(layer):
+    """The oracle's codebooks filled with the very tables the device uses."""
+    from oracle import binding as ob
+    books = []
+    for host in layer.host_tables:
+        cb = ob.codebook_from_hist(np.ones(256, np.uint64))
+        slot = np.ctypeslib.as_array(host.rans_slot)
+        cb.slot2sym[:] = (slot & 0xFF).astype(np.int32).tolist()
+        cb.freq[:] = np.ctypeslib.as_array(host.rans_freq).astype(np.int32).tolist()
+        cb.cum[:] = np.ctypeslib.as_array(host.rans_cum).astype(np.int32).tolist()
+        cb.lut[:] = np.ctypeslib.as_array(host.huff_lut).astype(np.int32).tolist()
+        books.append(cb)
+    return books
+
+
+def oracle_check(layer, q, out, slots=None, rows=None):
+    """The checker handed to the configuration runs: the CPU oracle (restated reference decoders, dequantise, double
+    online softmax) over the very records, page table and tails `layer` holds on the GPU, for the batch entries `rows`
+    of q / out (entry i = slot i), or for all of q / out when `slots` names their slots."""
+    from oracle import binding as ob
+    import torch
+    if rows is not None:
+        idx = torch.as_tensor(rows, device=q.device)
+        q, out, slots = q[idx], out[idx], list(rows)
+    elif slots is None:
+        slots = list(range(q.shape[0]))
+    kcb, vcb = _oracle_books(layer)
+    with torch.cuda.device(layer.device):
+        arena = layer.arena[:layer.sealed_bytes() + 64].cpu().numpy()
+        offsets = (layer.page_dir.cpu().numpy().astype(np.uint64) & np.uint64(0xFFFFFFFFFF)) * np.uint64(16)
+        sel = np.asarray(slots)
+        table = layer.page_table.cpu().numpy().astype(np.uint32)[sel]
+        sealed = layer.sealed_tokens.cpu().numpy().astype(np.uint32)[sel]
+        tails = layer.tail_tokens.cpu().numpy().astype(np.uint32)[sel]
+        tk, tv = layer.tail_k.cpu().numpy()[sel], layer.tail_v.cpu().numpy()[sel]
+    want = ob.sealed_decode_attention(arena, offsets, table, sealed, q.cpu().numpy(), layer.query_heads, layer.kv_heads,
+                                      layer.head_dim, layer.page_tokens, layer.block_size, 0, 1.0 / np.sqrt(layer.head_dim),
+                                      kcb, vcb, tail_k=tk, tail_v=tv, tail_count=tails, threads=os.cpu_count() or 1)
+    err = np.abs(out.cpu().numpy() - want)
+    return {"sequences_checked": len(slots), "seq_tokens_checked": int(sealed.sum() + tails.sum()), "max_abs_err": float(err.max()),
+            "within_2e-3_rel_1e-3_abs": bool(np.all(err <= 1e-3 + 2e-3 * np.abs(want)))}
+
+
+def other_configurations(a, device):
+    """Configurations 3, 4 and 5 of the benchmark at their stated sizes on this GPU, each checked against the CPU oracle
+    on a sample of its sequences (configuration 4: all eight)."""
+    from types import SimpleNamespace
+    from chromofold_b200 import config_bench as cb
+    args = SimpleNamespace(steps=max(a.steps // 5, 5), warmup=3, coder=a.coder, batch4=8, ctx4=131072, seqs5=256,
+                           prefix5=16384, suffix5=512)
+    extra = {"config3": cb.config3(args, device, check=oracle_check)}
+    extra["config4"] = cb.config4(args, device, 0, 1, check=oracle_check)
+    extra["config5"] = cb.config5(args, device, check=oracle_check)
+    rows = [r for rows in extra.values() for r in rows if "oracle_check" in r]
+    extra["all_within_2e-3_rel_1e-3_abs"] = all(r["oracle_check"]["within_2e-3_rel_1e-3_abs"] for r in rows)
+    return extra
+
+
+def one_process_legs(a, world, contexts, single_gpu_ms):
+    """What rank 0 adds to a multi-GPU run: the same batch placed over all GPUs (strong scaling) and configuration 4 with
+    its kv heads sharded, both driven by this one process through the C-ABI batch scheduler (cf_b200_mg_*)."""
+    from types import SimpleNamespace
+    from chromofold_b200 import config_bench as cb
+    devices = [f"cuda:{d}" for d in range(world)]
+    args = SimpleNamespace(steps=max(a.steps // 2, 10), warmup=5, coder=a.coder, batch4=8, ctx4=131072)
+    legs = {"strong_scaling": cb.strong_scaling_one_process(args, devices, contexts, a.coder, check=oracle_check,
+                                                            single_gpu_ms=single_gpu_ms)}
+    import torch
+    torch.cuda.empty_cache()
+    legs["config4"] = cb.config4_one_process(args, devices, check=oracle_check)
+    return legs
 
 
 def cpu_baseline(a, layer, contexts, q_host, out_gpu):
@@ -446,9 +522,17 @@ def main():
             del other, oinfo
             torch.cuda.empty_cache()
         line["other_coders"] = others
-    print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if not a.no_configs:
+        try:
+            del layer
+        except NameError:
+            pass
+        torch.cuda.empty_cache()
+        line["extra"] = (other_configurations(a, device) if world == 1
+                         else one_process_legs(a, world, contexts, ms / a.steps))
+    print(json.dumps(line))
 
 
 if __name__ == "__main__":

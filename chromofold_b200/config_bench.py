@@ -5,6 +5,7 @@ cross-request dedup decode with GPU-sealed suffixes. One JSON line per measured 
     python -m chromofold_b200.config_bench --config 3
     python -m chromofold_b200.config_bench --config 4            # one GPU: every shard width timed in turn
     python -m torch.distributed.run --nproc-per-node N -m chromofold_b200.config_bench --config 4   # N GPUs, gather timed
+    python -m chromofold_b200.config_bench --config 4 --one-process N   # N GPUs, one process, the C-ABI batch scheduler
     python -m chromofold_b200.config_bench --config 5
 
 Timing: CUDA events around `--steps` launches after `--warmup` untimed ones; every configuration reads more sealed
@@ -41,30 +42,43 @@ def _queries(n, heads, seed, device):
     return torch.randn((n, heads, 128), generator=g, device=device, dtype=torch.float32).half()
 
 
-def config3(a, device):
+def _checked(result, check, layer, q, out, slots=None, rows=None):
+    """Adds the caller's comparison of `out` with its own reference (bench.py passes the CPU oracle; nothing in this
+    package computes attention on the CPU) to a result row."""
+    if check is not None:
+        result["oracle_check"] = check(layer, q, out, slots=slots, rows=rows)
+    return result
+
+
+def config3(a, device, check=None, coders=("rans", "huffman", "rans4", "huffman4"), ps=(0.05, 0.1, 0.2, 0.4, 0.7)):
     """Coder crossover: 32 query / 8 kv heads, batch 32, context 8192, two-sided geometric codes."""
     contexts = np.full(32, 8192)
-    for p in (0.05, 0.1, 0.2, 0.4, 0.7):
-        for coder in ("rans", "huffman"):
+    results = []
+    for p in ps:
+        for coder in coders:
             layer, info = build_sealed_layer(contexts, coder=coder, dist=("geometric", p), seed=40, device=device)
             q = _queries(32, 32, 41, device)
             out = torch.zeros((32, 32, 128), dtype=torch.float32, device=device)
             ms = _time(lambda: layer.attention(q, out=out), a.steps, a.warmup)
             tokens = int(contexts.sum())
-            print(json.dumps({"config": 3, "p": p, "coder": coder, "h0_bits_per_code": round(info["h0_bits_k"], 3),
-                              "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
-                              "kv_memory_reduction_vs_fp16": round(4096 / info["bytes_per_seq_token"], 3),
-                              "ms_per_step": round(ms, 4), "seq_tokens_per_s": round(tokens / ms * 1e3),
-                              "sealed_gbs": round(info["sealed_bytes"] / ms / 1e6, 1), "device_status": layer.device_status()}))
+            results.append(_checked({
+                "config": 3, "p": p, "coder": coder, "h0_bits_per_code": round(info["h0_bits_k"], 3),
+                "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
+                "kv_memory_reduction_vs_fp16": round(4096 / info["bytes_per_seq_token"], 3),
+                "ms_per_step": round(ms, 4), "seq_tokens_per_s": round(tokens / ms * 1e3),
+                "sealed_gbs": round(info["sealed_bytes"] / ms / 1e6, 1), "device_status": layer.device_status()},
+                check, layer, q, out, rows=[0, 13, 31]))
             del layer, info
             torch.cuda.empty_cache()
+    return results
 
 
-def config3_blocks(a, device):
+def config3_blocks(a, device, check=None):
     """Block-size dial of the coder crossover: what 128- and 256-symbol blocks save in bytes (fewer per-block states
     and offsets) and what they cost (they run on the any-geometry kernel; the lane-per-block kernel is built for
     32 blocks of 64 symbols per stream)."""
     contexts = np.full(8, 8192)
+    results = []
     for p in (0.1, 0.4):
         for coder in ("rans", "huffman"):
             for block in (64, 128, 256):
@@ -73,35 +87,42 @@ def config3_blocks(a, device):
                 q = _queries(8, 32, 41, device)
                 out = torch.zeros((8, 32, 128), dtype=torch.float32, device=device)
                 ms = _time(lambda: layer.attention(q, out=out), max(a.steps // 3, 3), 2)
-                print(json.dumps({"config": 3, "p": p, "coder": coder, "block_size": block,
-                                  "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
-                                  "bits_per_code_stored": round(info["bytes_per_seq_token"] * 8 / 2048, 3),
-                                  "h0_bits_per_code": round(info["h0_bits_k"], 3),
-                                  "kernel": "lanes" if block == 64 else "generic", "ms_per_step": round(ms, 4),
-                                  "seq_tokens_per_s": round(int(contexts.sum()) / ms * 1e3),
-                                  "device_status": layer.device_status()}))
+                results.append({"config": 3, "p": p, "coder": coder, "block_size": block,
+                                "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
+                                "bits_per_code_stored": round(info["bytes_per_seq_token"] * 8 / 2048, 3),
+                                "h0_bits_per_code": round(info["h0_bits_k"], 3),
+                                "kernel": "lanes" if block == 64 else "generic", "ms_per_step": round(ms, 4),
+                                "seq_tokens_per_s": round(int(contexts.sum()) / ms * 1e3),
+                                "device_status": layer.device_status()})
                 del layer, info
                 torch.cuda.empty_cache()
+    return results
 
 
-def config4(a, device, rank, world):
-    """Long context, 70B shape: 64 query / 8 kv heads, 8 sequences x 131072 tokens, kv heads sharded."""
+def config4(a, device, rank, world, check=None):
+    """Long context, 70B shape: 64 query / 8 kv heads, 8 sequences x 131072 tokens, kv heads sharded. One process:
+    every shard width timed in turn on this GPU. Several processes (torchrun): a shard per rank, outputs gathered to
+    rank 0 with torch.distributed (the one-process scheduler's version of the same split is config4_one_process)."""
     import torch.distributed as dist
     contexts = np.full(a.batch4, a.ctx4)
     layer, info = build_sealed_layer(contexts, query_heads=64, kv_heads=8, coder=a.coder, seed=50, device=device)
     q = _queries(len(contexts), 64, 51, device)
     out = torch.zeros((len(contexts), 64, 128), dtype=torch.float32, device=device)
     tokens = int(contexts.sum())
+    results = []
     if world == 1:
         for ways in (1, 2, 4, 8):
             begin, span = shard_kv_heads(8, ways)[0]
             ms = _time(lambda: layer.attention(q, out=out, kv_head_begin=begin, kv_head_span=span), a.steps, a.warmup)
-            print(json.dumps({"config": 4, "gpus": 1, "shard_ways": ways, "kv_heads_on_this_gpu": span, "ms_per_step": round(ms, 4),
-                              "seq_tokens_per_s_if_every_shard_takes_this_long": round(tokens / ms * 1e3),
-                              "sealed_gbs_this_gpu": round(info["sealed_bytes"] * span / 8 / ms / 1e6, 1),
-                              "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
-                              "device_status": layer.device_status()}))
-        return
+            row = {"config": 4, "gpus": 1, "coder": a.coder, "shard_ways": ways, "kv_heads_on_this_gpu": span, "ms_per_step": round(ms, 4),
+                   "seq_tokens_per_s_if_every_shard_takes_this_long": round(tokens / ms * 1e3),
+                   "sealed_gbs_this_gpu": round(info["sealed_bytes"] * span / 8 / ms / 1e6, 1),
+                   "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
+                   "device_status": layer.device_status()}
+            if ways == 1:
+                _checked(row, check, layer, q, out)     # all eight sequences, every head
+            results.append(row)
+        return results
     shards = shard_kv_heads(8, world)
     begin, span = shards[rank]
     step = lambda: layer.attention(q, out=out, kv_head_begin=begin, kv_head_span=span)
@@ -123,15 +144,103 @@ def config4(a, device, rank, world):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         whole = layer.attention(q)   # every head on this rank, to check the gathered result
-        print(json.dumps({"config": 4, "gpus": world, "shard_ways": world, "kv_heads_per_gpu": span,
-                          "attention_ms_max_over_ranks": round(float(t[0]), 4), "gather_ms_max_over_ranks": round(float(t[1]), 4),
-                          "seq_tokens_per_s": round(tokens / float(t[0]) * 1e3),
-                          "seq_tokens_per_s_with_gather": round(tokens / float(t[0] + t[1]) * 1e3),
-                          "gathered_equals_single_gpu": bool(torch.equal(gathered, whole)),
-                          "device_status": layer.device_status()}))
+        results.append({"config": 4, "gpus": world, "shard_ways": world, "kv_heads_per_gpu": span,
+                        "attention_ms_max_over_ranks": round(float(t[0]), 4), "gather_ms_max_over_ranks": round(float(t[1]), 4),
+                        "seq_tokens_per_s": round(tokens / float(t[0]) * 1e3),
+                        "seq_tokens_per_s_with_gather": round(tokens / float(t[0] + t[1]) * 1e3),
+                        "gathered_equals_single_gpu": bool(torch.equal(gathered, whole)),
+                        "device_status": layer.device_status()})
+    return results
 
 
-def config5(a, device):
+def _time_on(stream_device, fn, steps, warmup):
+    """CUDA events on the current stream of `stream_device` (the scheduler's root stream) around `steps` calls."""
+    with torch.cuda.device(stream_device):
+        for _ in range(warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for d in range(torch.cuda.device_count()):
+            torch.cuda.synchronize(d)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+
+def config4_one_process(a, devices, check=None):
+    """Configuration 4 through the one-process batch scheduler (cf_b200_mg_*): a replica of the store on every GPU,
+    kv heads sharded `len(devices)` ways, query rows out and query-head columns back as peer copies. The timed step
+    is everything between two events on the root stream: copies out, attention on every GPU, gather."""
+    from .scheduler import MultiGpuScheduler
+    contexts = np.full(a.batch4, a.ctx4)
+    layers = [build_sealed_layer(contexts, query_heads=64, kv_heads=8, coder=a.coder, seed=50, device=d)[0] for d in devices]
+    root = devices[0]
+    q = _queries(len(contexts), 64, 51, root)
+    out = torch.zeros((len(contexts), 64, 128), dtype=torch.float32, device=root)
+    sched = MultiGpuScheduler(layers, max_rows=len(contexts))
+    heads = sched.plan_kv_heads(8)
+    slots = list(range(len(contexts)))
+    ms = _time_on(root, lambda: sched.attention_by_kv_head(q, out, heads, slots), a.steps, max(a.warmup, 3))
+    with torch.cuda.device(root):
+        begin, span = heads[0]
+        local = torch.zeros_like(out)
+        ms_attn = _time(lambda: layers[0].attention(q, out=local, kv_head_begin=begin, kv_head_span=span), a.steps, 2)
+        whole = layers[0].attention(q)
+        sched.attention_by_kv_head(q, out, heads, slots)
+        torch.cuda.synchronize()
+    tokens = int(contexts.sum())
+    row = {"config": 4, "gpus": len(devices), "coder": a.coder, "how": "one process, cf_b200_mg_execute_async, kv heads sharded",
+           "kv_head_blocks": heads, "step_ms_copies_attention_gather": round(ms, 4),
+           "attention_ms_root_shard_alone": round(ms_attn, 4), "copies_and_gather_ms": round(max(ms - ms_attn, 0.0), 4),
+           "seq_tokens_per_s": round(tokens / ms * 1e3), "max_abs_diff_vs_one_gpu_all_heads": float((out - whole).abs().max().item()),
+           "counters": sched.counters(), "device_status": [lay.device_status() for lay in layers]}
+    _checked(row, check, layers[0], q, out)
+    sched.close()
+    return [row]
+
+
+def strong_scaling_one_process(a, devices, contexts, coder, check=None, single_gpu_ms=None):
+    """One batch (the headline workload's sequences) placed over the GPUs by the C planner (longest context first),
+    every GPU holding only its own sequences' pages, timed through cf_b200_mg_execute_async."""
+    from .scheduler import MultiGpuScheduler, imbalance
+    from . import _native as N
+    contexts = np.asarray(contexts, np.int64)
+    import ctypes as C
+    out_dev = np.zeros(len(contexts), np.uint32)
+    lengths = contexts.astype(np.uint64)
+    N.check("plan", N.lib().cf_b200_mg_plan_sequences(None, lengths.ctypes.data_as(C.c_void_p), C.c_uint32(len(contexts)),
+                                                       C.c_uint32(len(devices)), out_dev.ctypes.data_as(C.c_void_p)))
+    assignment = [np.nonzero(out_dev == d)[0].tolist() for d in range(len(devices))]
+    layers = [build_sealed_layer(contexts[assignment[d]], coder=coder, seed=4 + 17 * d, device=dev)[0] for d, dev in enumerate(devices)]
+    root = devices[0]
+    q = _queries(len(contexts), 32, 6, root)
+    out = torch.zeros((len(contexts), 32, 128), dtype=torch.float32, device=root)
+    sched = MultiGpuScheduler(layers, max_rows=len(contexts))
+    local_slots = [list(range(len(assignment[d]))) for d in range(len(devices))]
+    ms = _time_on(root, lambda: sched.attention_by_sequence(q, out, assignment, local_slots), a.steps, max(a.warmup, 3))
+    with torch.cuda.device(root):
+        sched.attention_by_sequence(q, out, assignment, local_slots)
+        torch.cuda.synchronize()
+    tokens = int(contexts.sum())
+    row = {"scaling": "strong", "gpus": len(devices), "coder": coder, "how": "one process, cf_b200_mg_execute_async, sequences placed longest first",
+           "sequences": len(contexts), "seq_tokens": tokens, "load_imbalance_max_over_mean": round(imbalance(contexts, assignment), 4),
+           "step_ms_copies_attention_gather": round(ms, 4), "seq_tokens_per_s": round(tokens / ms * 1e3),
+           "counters": sched.counters(), "device_status": [lay.device_status() for lay in layers]}
+    if single_gpu_ms:
+        row["single_gpu_step_ms_same_batch"] = round(single_gpu_ms, 4)
+        row["speedup_vs_one_gpu"] = round(single_gpu_ms / ms, 3)
+        row["efficiency"] = round(single_gpu_ms / ms / len(devices), 3)
+    if check is not None:   # the root device's own sequences against the caller's reference
+        with torch.cuda.device(root):
+            rows = assignment[0][:4]
+            row["oracle_check"] = check(layers[0], q[rows].contiguous(), out[rows].contiguous(), slots=local_slots[0][:4])
+    sched.close()
+    return [row]
+
+
+def config5(a, device, check=None):
     """Dedup: 256 sequences share one sealed 16384-token prefix (one copy) and own a 512-token sealed suffix each; a
     step appends one token to every sequence, seals the pages that filled up, and runs the decode attention."""
     n, prefix, suffix = a.seqs5, a.prefix5, a.suffix5
@@ -165,17 +274,23 @@ def config5(a, device):
     ms = _time(step, a.steps, a.warmup)
     ms_attn = _time(lambda: layer.attention(q, out=out, shared_prefix_pages=shared), a.steps, a.warmup)
     ms_per_sequence = _time(lambda: layer.attention(q, out=out), max(a.steps // 4, 2), 2)   # every page decoded per sequence
+    layer.attention(q, out=out, shared_prefix_pages=shared)
+    torch.cuda.synchronize()
     logical_tokens = n * (prefix + suffix)
     unique_bytes = layer.sealed_bytes()
     flops = 4 * 128 * 32 * logical_tokens
-    print(json.dumps({"config": 5, "coder": a.coder, "sequences": n, "shared_prefix_tokens": prefix, "private_suffix_tokens": suffix,
-                      "unique_sealed_bytes": unique_bytes, "logical_sealed_bytes": int(one_copy * n + (unique_bytes - one_copy)),
-                      "ms_per_step_append_seal_attention": round(ms, 4), "ms_attention_only": round(ms_attn, 4),
-                      "ms_attention_without_the_shared_prefix_kernel": round(ms_per_sequence, 4),
-                      "seq_tokens_per_s": round(logical_tokens / ms * 1e3),
-                      "unique_gbs": round(unique_bytes / ms_attn / 1e6, 1),
-                      "logical_gbs": round((one_copy * n + unique_bytes - one_copy) / ms_attn / 1e6, 1),
-                      "attention_tflops": round(flops / ms_attn / 1e9, 2), "device_status": layer.device_status()}))
+    row = {"config": 5, "coder": a.coder, "sequences": n, "shared_prefix_tokens": prefix, "private_suffix_tokens": suffix,
+           "unique_sealed_bytes": unique_bytes, "logical_sealed_bytes": int(one_copy * n + (unique_bytes - one_copy)),
+           "ms_per_step_append_seal_attention": round(ms, 4), "ms_attention_only": round(ms_attn, 4),
+           "ms_attention_without_the_shared_prefix_kernel": round(ms_per_sequence, 4),
+           "seq_tokens_per_s": round(logical_tokens / ms * 1e3),
+           "unique_gbs": round(unique_bytes / ms_attn / 1e6, 1),
+           "logical_gbs": round((one_copy * n + unique_bytes - one_copy) / ms_attn / 1e6, 1),
+           "attention_tflops": round(flops / ms_attn / 1e9, 2), "device_status": layer.device_status()}
+    picked = sorted({0, n - 1} | set(range(0, n, max(n // 14, 1))))[:16] if n > 16 else list(range(n))
+    picked = sorted(set(picked) | {n - 1})
+    _checked(row, check, layer, q, out, rows=picked)   # slot 0, the last slot and an even spread between them
+    return [row]
 
 
 def transfer(a, device):
@@ -211,10 +326,10 @@ def transfer(a, device):
     ms_pack = _time(pack, a.steps, a.warmup)
     ms_unpack = _time(unpack, a.steps, a.warmup)
     gb = info["sealed_bytes"] / 1e9
-    print(json.dumps({"transfer": "2048 pages x 8 kv heads", "sealed_bytes": info["sealed_bytes"],
-                      "pack_ms": round(ms_pack, 4), "pack_gbs_read_plus_write": round(2 * gb / ms_pack * 1e3, 1),
-                      "unpack_ms": round(ms_unpack, 4), "unpack_gbs_read_plus_write": round(2 * gb / ms_unpack * 1e3, 1),
-                      "status": [src.device_status(), dst.device_status()]}))
+    return [{"transfer": "2048 pages x 8 kv heads", "sealed_bytes": info["sealed_bytes"],
+             "pack_ms": round(ms_pack, 4), "pack_gbs_read_plus_write": round(2 * gb / ms_pack * 1e3, 1),
+             "unpack_ms": round(ms_unpack, 4), "unpack_gbs_read_plus_write": round(2 * gb / ms_unpack * 1e3, 1),
+             "status": [src.device_status(), dst.device_status()]}]
 
 
 def main():
@@ -225,6 +340,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
     ap.add_argument("--blocks", action="store_true", help="configuration 3: the block-size dial instead of the p sweep")
+    ap.add_argument("--one-process", type=int, default=0, metavar="N",
+                    help="configuration 4 on N GPUs driven by this one process through the C-ABI batch scheduler")
     ap.add_argument("--batch4", type=int, default=8)
     ap.add_argument("--ctx4", type=int, default=131072)
     ap.add_argument("--seqs5", type=int, default=256)
@@ -242,15 +359,19 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
     if a.transfer:
-        transfer(a, device)
+        rows = transfer(a, device)
     elif a.config == 3 and a.blocks:
-        config3_blocks(a, device)
+        rows = config3_blocks(a, device)
     elif a.config == 3:
-        config3(a, device)
+        rows = config3(a, device)
+    elif a.config == 4 and a.one_process:
+        rows = config4_one_process(a, [f"cuda:{d}" for d in range(a.one_process)])
     elif a.config == 4:
-        config4(a, device, rank, world)
+        rows = config4(a, device, rank, world)
     else:
-        config5(a, device)
+        rows = config5(a, device)
+    for row in rows:
+        print(json.dumps(row))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
