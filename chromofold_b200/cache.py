@@ -22,6 +22,18 @@ def _stream_ptr():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _on_own_device(method):
+    """Runs a method with the layer's GPU as the current CUDA device: the library launches on the current device, and a
+    kernel must only ever be given memory of the GPU it runs on."""
+    import functools
+
+    @functools.wraps(method)
+    def wrapper(self, *args, **kw):
+        with torch.cuda.device(self.device):
+            return method(self, *args, **kw)
+    return wrapper
+
+
 class SealedKvLayer:
     """One layer of sealed KV pages for up to `max_sequences` sequence slots on one GPU."""
 
@@ -64,12 +76,14 @@ class SealedKvLayer:
         self.host_tables = (N.CodebookTables(), N.CodebookTables())
 
     # -- codebooks ---------------------------------------------------------------------------------
+    @_on_own_device
     def set_codebooks(self, hist_k, hist_v):
         for hist, host, dev in ((hist_k, self.host_tables[0], self.k_tables), (hist_v, self.host_tables[1], self.v_tables)):
             h = np.ascontiguousarray(hist, np.uint64)
             N.check("codebook_build", self.lib.cf_b200_codebook_build(h.ctypes.data_as(C.c_void_p), C.byref(host)))
             dev.copy_(torch.frombuffer(bytearray(bytes(host)), dtype=torch.uint8))
 
+    @_on_own_device
     def histograms(self, slots=None):
         """Symbol histograms of the quantised streams of the current tails (GPU)."""
         slots = self._slots_tensor(slots)
@@ -80,6 +94,7 @@ class SealedKvLayer:
         return hk.cpu().numpy().astype(np.uint64), hv.cpu().numpy().astype(np.uint64)
 
     # -- append / seal -------------------------------------------------------------------------------
+    @_on_own_device
     def append(self, slots, k, v):
         """Append one token per listed slot. k, v: float16 device tensors [len(slots), kv_heads, head_dim]."""
         slots = np.asarray(slots, np.int64)
@@ -92,6 +107,7 @@ class SealedKvLayer:
         self.h_tail[slots] += 1
         self.tail_tokens[idx] += 1
 
+    @_on_own_device
     def fill_tails(self, slots, k, v, tokens):
         """Set whole tails at once. k, v: float16 [len(slots), kv_heads, page_tokens, head_dim]."""
         slots = np.asarray(slots, np.int64)
@@ -101,6 +117,7 @@ class SealedKvLayer:
         self.h_tail[slots] = tokens
         self.tail_tokens[idx] = int(tokens)
 
+    @_on_own_device
     def seal_full_pages(self, slots=None, force=False):
         """Seal the tails that hold page_tokens rows (all non-empty tails with force=True, the reference's flush)."""
         cand = np.arange(self.max_sequences) if slots is None else np.asarray(slots, np.int64)
@@ -128,6 +145,7 @@ class SealedKvLayer:
         self.tail_tokens[d_slots.long()] = 0
         return int(full.size)
 
+    @_on_own_device
     def seal_tiles(self, slots, k_tiles, v_tiles):
         """Append one full page to every listed slot straight from tile tensors (bulk loading).
         k_tiles, v_tiles: float16 device tensors [len(slots), kv_heads, page_tokens, head_dim]; a slot may appear
@@ -157,6 +175,7 @@ class SealedKvLayer:
             self.h_sealed[s] += c * self.page_tokens
         self.sealed_tokens.copy_(torch.as_tensor(self.h_sealed.astype(np.int32)))
 
+    @_on_own_device
     def copy_sequence(self, src, dst):
         """Give slot `dst` the history of slot `src` without copying a sealed byte: the sealed pages are shared by page
         id (the reference's shared-page semantics, src/multisequence_cache.cpp:235-292); the unsealed tail is copied."""
@@ -170,6 +189,7 @@ class SealedKvLayer:
         self.tail_v[dst] = self.tail_v[src]
 
     # -- import of records sealed elsewhere ------------------------------------------------------------
+    @_on_own_device
     def import_records(self, slot, records, tokens_per_page=None):
         """Append already sealed pages to `slot`. records[p][h] is the record (bytes-like) of page p, kv head h."""
         blobs, entries = [], []
@@ -200,6 +220,7 @@ class SealedKvLayer:
         self.sealed_tokens[slot] += added
 
     # -- transfer images (warm-start file / hand-over to another GPU) -------------------------------------
+    @_on_own_device
     def export_pages(self, slot):
         """The sealed pages of `slot` as one transfer image (bytes): header, manifest, packed records
         (include/chromofold_b200/page_transfer.h). Packed and checksummed on the GPU."""
@@ -225,6 +246,7 @@ class SealedKvLayer:
         tokens = np.minimum(self.page_tokens, self.h_sealed[slot] - np.arange(n) * self.page_tokens).astype(np.uint32)
         return bytes(header) + man + payload[:used].cpu().numpy().tobytes() + tokens.tobytes()
 
+    @_on_own_device
     def import_pages(self, slot, image):
         """Append the pages of a transfer image to `slot`. The image must match this layer's geometry and codebook
         id; every record is verified against its checksum on the GPU (a bad one is not published and raises
@@ -266,6 +288,7 @@ class SealedKvLayer:
         return n
 
     # -- attention -----------------------------------------------------------------------------------
+    @_on_own_device
     def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
                   kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL, shared_prefix_pages=0,
                   query_positions=None):
@@ -290,6 +313,7 @@ class SealedKvLayer:
                                                                                       _stream_ptr()))
         return out
 
+    @_on_own_device
     def attention_no_alloc(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0,
                            kernel=N.KERNEL_AUTO):
         """The same decode-step attention through the entry point that uses the library's built-in workspace
@@ -308,6 +332,7 @@ class SealedKvLayer:
             raise N.CfError(self.lib.cf_b200_sealed_attention_static_error().decode(), status)
         return out
 
+    @_on_own_device
     def dump_lane_decoders(self, queries, slots=None, *, shared_prefix_pages=0, query_positions=None):
         """Test aid (CF_B200_KERNEL_DECODE_DUMP): run the plan and the attention kernels of a call on `queries`, with the
         lane-per-block decoders of the attention kernels storing every symbol they decode instead of consuming it.
@@ -326,6 +351,7 @@ class SealedKvLayer:
             C.byref(d), C.c_uint32(N.STAGE_PLAN | N.STAGE_ATTENTION), _stream_ptr()))
         return dump
 
+    @_on_own_device
     def decode_pages(self, page_ids):
         """Decode whole records to symbols on the GPU: returns (k, v) uint8 [pages, kv_heads, page_tokens*head_dim]."""
         ids = torch.as_tensor(np.asarray(page_ids, np.int32), device=self.device)
@@ -337,15 +363,18 @@ class SealedKvLayer:
                                                                       _ptr(ks), _ptr(vs), _stream_ptr()))
         return ks, vs
 
+    @_on_own_device
     def record_bytes(self, page_id, kv_head):
         """Copy one record back to the host (for byte-exactness checks and statistics)."""
         e = int(self.page_dir[page_id * self.kv_heads + kv_head].item())
         off, units = e & 0xFFFFFFFFFF, (e >> 40) & 0xFFFF
         return self.arena[off * 16:(off + units) * 16].cpu().numpy()
 
+    @_on_own_device
     def sealed_bytes(self):
         return int(self.cursor.item()) * 16
 
+    @_on_own_device
     def device_status(self):
         return int(self.status.item())
 
@@ -413,6 +442,11 @@ def swizzle_dense_tiles(tiles):
 def dense_attention(layer, pool_k, pool_v, queries, out, *, softmax_scale=None, causal_window=0, slots=None):
     """The comparison kernel: attention over uncompressed binary16 pages addressed by `layer`'s page table.
     pool_k / pool_v: swizzled tiles [page_id][kv_heads][16][128] (see swizzle_dense_tiles)."""
+    with torch.cuda.device(layer.device):
+        return _dense_attention(layer, pool_k, pool_v, queries, out, softmax_scale, causal_window, slots)
+
+
+def _dense_attention(layer, pool_k, pool_v, queries, out, softmax_scale, causal_window, slots):
     d = N.DenseAttentionDesc()
     d.struct_size, d.abi_version = C.sizeof(N.DenseAttentionDesc), N.ABI_VERSION
     d.kv_head_count, d.query_head_count, d.head_dim, d.page_tokens = layer.kv_heads, layer.query_heads, layer.head_dim, layer.page_tokens

@@ -182,7 +182,8 @@ def config4_one_process(a, devices, check=None):
     sched = MultiGpuScheduler(layers, max_rows=len(contexts))
     heads = sched.plan_kv_heads(8)
     slots = list(range(len(contexts)))
-    ms = _time_on(root, lambda: sched.attention_by_kv_head(q, out, heads, slots), a.steps, max(a.warmup, 3))
+    prepared = sched.prepare_by_kv_head(heads, slots, out, q)
+    ms = _time_on(root, lambda: sched.run(prepared, q, out), a.steps, max(a.warmup, 3))
     with torch.cuda.device(root):
         begin, span = heads[0]
         local = torch.zeros_like(out)
@@ -219,7 +220,8 @@ def strong_scaling_one_process(a, devices, contexts, coder, check=None, single_g
     out = torch.zeros((len(contexts), 32, 128), dtype=torch.float32, device=root)
     sched = MultiGpuScheduler(layers, max_rows=len(contexts))
     local_slots = [list(range(len(assignment[d]))) for d in range(len(devices))]
-    ms = _time_on(root, lambda: sched.attention_by_sequence(q, out, assignment, local_slots), a.steps, max(a.warmup, 3))
+    prepared = sched.prepare_by_sequence(assignment, local_slots)
+    ms = _time_on(root, lambda: sched.run(prepared, q, out), a.steps, max(a.warmup, 3))
     with torch.cuda.device(root):
         sched.attention_by_sequence(q, out, assignment, local_slots)
         torch.cuda.synchronize()

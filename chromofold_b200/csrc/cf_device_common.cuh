@@ -91,6 +91,20 @@ __host__ __device__ inline uint32_t default_pages_per_unit(uint64_t total_pages,
     return static_cast<uint32_t>(wanted < 4ull ? 4ull : wanted > 16ull ? 16ull : wanted);
 }
 
+// A device pointer against the current device: false when it is memory of ANOTHER GPU. Kernels are launched on the
+// current device and must only be given that device's memory, so the entry points refuse such a pointer instead of
+// launching (host, managed and unregistered pointers are left to the usual CUDA checks).
+inline bool on_current_device(const void *ptr) {
+    if (ptr == nullptr) return true;
+    cudaPointerAttributes attr;
+    int device = -1;
+    if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess || cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+        return true;
+    }
+    return attr.type != cudaMemoryTypeDevice || attr.device == device;
+}
+
 // First token a query at `query_token` may see (src/cuda/paged_kv_attention.cu:50-52).
 __host__ __device__ inline uint32_t window_begin(uint32_t query_token, uint32_t causal_window) {
     return causal_window == 0 || query_token + 1u <= causal_window ? 0u : query_token + 1u - causal_window;

@@ -449,6 +449,8 @@ extern "C" cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *d, void *
     const cf_status s = cf_b200_seal_validate(d);
     if (s != CF_OK) return s;
     if (d->job_count == 0) return CF_OK;
+    if (!cfb::on_current_device(d->arena) || !cfb::on_current_device(d->tail_k) || !cfb::on_current_device(d->page_dir))
+        return CF_ERR_INVALID_ARGUMENT;   // memory of another GPU: the call must be made with that GPU current
     cfb::SealParams p;
     cfb::fill(d, &p);
     const cfb::SealSmem lay = cfb::seal_smem(p.symbols, p.nblocks, p.block_size);
@@ -466,6 +468,7 @@ extern "C" cf_status cf_b200_histogram_async(const cf_b200_seal_desc *d, unsigne
     if (s != CF_OK) return s;
     if (hist_k == nullptr || hist_v == nullptr) return CF_ERR_INVALID_ARGUMENT;
     if (d->job_count == 0) return CF_OK;
+    if (!cfb::on_current_device(d->tail_k) || !cfb::on_current_device(hist_k)) return CF_ERR_INVALID_ARGUMENT;
     cfb::SealParams p;
     cfb::fill(d, &p);
     cfb::histogram_kernel<<<dim3(d->job_count, d->job_heads ? 1u : d->kv_head_count), cfb::kSealThreads, 0,

@@ -600,6 +600,9 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     const cf_status valid = cf_b200_sealed_attention_validate(d);
     if (valid != CF_OK) return valid;
     if (stages == 0 || stages > 7u) return CF_ERR_INVALID_ARGUMENT;
+    if (!cfb::on_current_device(d->arena) || !cfb::on_current_device(d->workspace) || !cfb::on_current_device(d->queries) ||
+        !cfb::on_current_device(d->output))
+        return CF_ERR_INVALID_ARGUMENT;   // memory of another GPU: the call must be made with that GPU current
     AttentionParams p;
     cfb::fill_params(d, &p);
     const bool lanes_ok = cfb::lanes_kernel_supports(p);

@@ -186,28 +186,35 @@ class MultiGpuScheduler:
         self._keep = keep
         return shards
 
-    def attention_by_sequence(self, queries, out, assignment, local_slots, **kw):
-        """queries/out: root-device tensors [rows][Hq][D]; assignment[d] = rows served by device d; local_slots[d] = the
-        slots those sequences occupy in layers[d] (same order)."""
-        N = self.N
+    def prepare_by_sequence(self, assignment, local_slots, **kw):
+        """The per-device descriptors of a placement, built once: assignment[d] = rows served by device d, local_slots[d] =
+        the slots those sequences occupy in layers[d] (same order). Returns a handle for run()."""
         per = [(local_slots[d], assignment[d], 0, 0) for d in range(len(self.layers))]
-        shards = self._shards(per, N.MG_BY_SEQUENCE, queries.shape[0], **kw)
+        rows = sum(len(a) for a in assignment)
+        return (self._shards(per, self.N.MG_BY_SEQUENCE, rows, **kw), self._keep, self.N.MG_BY_SEQUENCE, None)
+
+    def prepare_by_kv_head(self, head_shards, slots, root_out, root_queries, **kw):
+        """Every device serves every row with its block of kv heads (head_shards[d] = (begin, span)); device-local slot ids
+        are `slots` on every device. The root device reads `root_queries` and writes its columns of `root_out` in place."""
+        per = [(slots if head_shards[d][1] else [], None, head_shards[d][0], head_shards[d][1]) for d in range(len(self.layers))]
+        shards = self._shards(per, self.N.MG_BY_KV_HEAD, len(slots), root_out=root_out, **kw)
+        if head_shards[0][1]:
+            shards[0].desc.queries = root_queries.data_ptr()
+        return (shards, self._keep, self.N.MG_BY_KV_HEAD, (root_queries.data_ptr(), root_out.data_ptr()))
+
+    def run(self, prepared, queries, out):
+        """One step of a prepared placement: a single call into the library."""
+        shards, _, mode, bound = prepared
+        if bound is not None and bound != (queries.data_ptr(), out.data_ptr()):
+            raise ValueError("a kv-head placement is bound to the query / output tensors it was prepared with")
         stream = self.torch.cuda.current_stream(self.layers[0].device).cuda_stream
         self._check("mg_execute", self.lib.cf_b200_mg_execute_async(
             C.c_void_p(self.handle), shards, C.c_uint32(len(self.layers)), C.c_void_p(queries.data_ptr()), C.c_void_p(out.data_ptr()),
-            C.c_uint32(queries.shape[0]), C.c_uint32(N.MG_BY_SEQUENCE), C.c_void_p(stream)))
+            C.c_uint32(queries.shape[0]), C.c_uint32(mode), C.c_void_p(stream)))
         return out
 
+    def attention_by_sequence(self, queries, out, assignment, local_slots, **kw):
+        return self.run(self.prepare_by_sequence(assignment, local_slots, **kw), queries, out)
+
     def attention_by_kv_head(self, queries, out, head_shards, slots, **kw):
-        """Every device serves every row with its block of kv heads (head_shards[d] = (begin, span)); device-local slot ids
-        are `slots` on every device. The root device writes its columns straight into `out`."""
-        N = self.N
-        per = [(slots if head_shards[d][1] else [], None, head_shards[d][0], head_shards[d][1]) for d in range(len(self.layers))]
-        shards = self._shards(per, N.MG_BY_KV_HEAD, queries.shape[0], root_out=out, **kw)
-        if head_shards[0][1]:
-            shards[0].desc.queries = queries.data_ptr()   # the root reads the caller's rows in place
-        stream = self.torch.cuda.current_stream(self.layers[0].device).cuda_stream
-        self._check("mg_execute", self.lib.cf_b200_mg_execute_async(
-            C.c_void_p(self.handle), shards, C.c_uint32(len(self.layers)), C.c_void_p(queries.data_ptr()), C.c_void_p(out.data_ptr()),
-            C.c_uint32(queries.shape[0]), C.c_uint32(N.MG_BY_KV_HEAD), C.c_void_p(stream)))
-        return out
+        return self.run(self.prepare_by_kv_head(head_shards, slots, out, queries, **kw), queries, out)

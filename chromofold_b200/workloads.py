@@ -55,6 +55,13 @@ def build_sealed_layer(contexts, *, query_heads=32, kv_heads=8, head_dim=128, pa
     """Seal `contexts[i]` tokens for slot i. Returns (layer, info). With keep_dense=True the binary16 tiles are also
     kept as an uncompressed pool [page_id][kv_heads][page_tokens][head_dim] for the comparison kernel.
     `reserve_pages` more pages (directory entries and arena room) are set aside for pages sealed later."""
+    with torch.cuda.device(device):   # the library launches on the current device
+        return _build_sealed_layer(contexts, query_heads, kv_heads, head_dim, page_tokens, block_size, coder, dist, seed, device,
+                                   tiles_per_launch, extra_pages_per_sequence, keep_dense, reserve_pages)
+
+
+def _build_sealed_layer(contexts, query_heads, kv_heads, head_dim, page_tokens, block_size, coder, dist, seed, device,
+                        tiles_per_launch, extra_pages_per_sequence, keep_dense, reserve_pages):
     contexts = np.asarray(contexts, np.int64)
     assert np.all(contexts % page_tokens == 0)
     pages = contexts // page_tokens

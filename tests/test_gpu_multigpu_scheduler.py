@@ -94,3 +94,26 @@ def test_kv_heads_sharded_over_the_devices_of_one_process(native, oracle):
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), want), ways
     sched.close()
+
+
+def test_memory_of_another_gpu_is_refused_before_any_launch(native):
+    """The entry points launch on the current device; a descriptor whose arena lies on another GPU is turned down with
+    CF_ERR_INVALID_ARGUMENT instead of being launched (nothing runs, nothing faults)."""
+    import ctypes as C
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    layer, _ = build_sealed_layer(np.array([64, 32]), coder="rans4", seed=97, device="cuda:1")
+    q = _queries(2, 32, 98, "cuda:1")
+    out = torch.zeros((2, 32, 128), dtype=torch.float32, device="cuda:1")
+    desc = layer._attention_desc(q, out, 2, None)
+    desc.softmax_scale = 0.088
+    with torch.cuda.device(0):
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert native.lib().cf_b200_sealed_attention_async(C.byref(desc), stream) == native.CF_ERR_INVALID_ARGUMENT
+    with torch.cuda.device(1):
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert native.lib().cf_b200_sealed_attention_async(C.byref(desc), stream) == native.CF_OK
+        torch.cuda.synchronize()
+    assert layer.device_status() == 0
