@@ -6,11 +6,14 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <condition_variable>
 #include <cstring>
 #include <memory>
 #include <mutex>
 #include <numeric>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "chromofold_b200/sealed_kv_multigpu.h"
@@ -39,8 +42,29 @@ struct DeviceGuard {   // the calling thread's current device is put back when t
 
 }  // namespace
 
+// What every device does in a step; filled by the calling thread, read by the submitting threads.
+struct StepJob {
+    const cf_b200_mg_shard *shards = nullptr;
+    uint32_t mode = 0, row_count = 0;
+    const void *root_queries = nullptr;
+    void *root_output = nullptr;
+    uint32_t first_row[CF_B200_MG_MAX_DEVICES] = {};   // by-sequence: where the device's rows start in device-major order
+};
+
 struct cf_b200_mg_scheduler {
     cf_b200_mg_config config{};
+    // One submitting thread per device beyond the root: queueing a device's copies and launches takes tens of
+    // microseconds of host time, which in one thread would add up to more than a step takes on eight GPUs. A thread
+    // spins briefly for the next step, then sleeps.
+    std::vector<std::thread> workers;
+    std::atomic<uint64_t> step_seq{0};
+    std::atomic<uint32_t> pending{0};
+    std::atomic<bool> stopping{false};
+    std::mutex wake_mutex;
+    std::condition_variable wake_cv;
+    StepJob job;
+    cf_status device_status[CF_B200_MG_MAX_DEVICES] = {};
+    std::string device_error[CF_B200_MG_MAX_DEVICES];
     std::vector<int32_t> ordinals;
     std::vector<cudaStream_t> streams;
     std::vector<cudaEvent_t> done;
@@ -67,7 +91,18 @@ struct cf_b200_mg_scheduler {
         error = std::string(where) + ": " + cudaGetErrorString(e);
         return CF_ERR_CUDA;
     }
+    void stop_workers() {
+        stopping.store(true, std::memory_order_release);
+        {
+            std::lock_guard<std::mutex> lock(wake_mutex);
+        }
+        wake_cv.notify_all();
+        for (std::thread &t : workers)
+            if (t.joinable()) t.join();
+        workers.clear();
+    }
     void release() {
+        stop_workers();
         DeviceGuard guard;
         for (size_t d = 0; d < ordinals.size(); ++d) {
             if (cudaSetDevice(ordinals[d]) != cudaSuccess) continue;
@@ -83,6 +118,98 @@ struct cf_b200_mg_scheduler {
         if (h_perm) cudaFreeHost(h_perm);
     }
 };
+
+namespace {
+
+// Queues one device's share of the current step on that device's stream: wait for the root, query rows in, the
+// attention launches, output rows (or columns) back to the root, done-event. The calling thread has the device current.
+cf_status submit_device(cf_b200_mg_scheduler *s, uint32_t d) {
+    const StepJob &job = s->job;
+    const cf_b200_sealed_attention_desc &desc = job.shards[d].desc;
+    const size_t q_row = s->query_row_bytes(), o_row = s->output_row_bytes();
+    cudaStream_t stream = s->streams[d];
+    std::string &error = s->device_error[d];
+    auto cuda_fail = [&](cudaError_t e, const char *where) {
+        error = std::string(where) + ": " + cudaGetErrorString(e);
+        return CF_ERR_CUDA;
+    };
+    cudaError_t e;
+    if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+    if (job.mode == CF_B200_MG_BY_SEQUENCE) {
+        const uint32_t at = job.first_row[d];
+        e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], s->staging_q + q_row * at, s->ordinals[0],
+                                q_row * desc.seq_count, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "query rows out");
+        const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
+        if (launched != CF_OK) {
+            error = "attention launch failed on a device";
+            return launched;
+        }
+        e = cudaMemcpyPeerAsync(s->staging_out + (o_row / 4u) * at, s->ordinals[0], desc.output, s->ordinals[d],
+                                o_row * desc.seq_count, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "output rows back");
+    } else {
+        const uint32_t group = desc.query_head_count / desc.kv_head_count;
+        const uint32_t span = desc.kv_head_span ? desc.kv_head_span : desc.kv_head_count - desc.kv_head_begin;
+        if (desc.queries != job.root_queries) {   // the root device may read the caller's rows in place
+            e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], job.root_queries, s->ordinals[0],
+                                    q_row * job.row_count, stream);
+            if (e != cudaSuccess) return cuda_fail(e, "query rows out");
+        }
+        const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
+        if (launched != CF_OK) {
+            error = "attention launch failed on a device";
+            return launched;
+        }
+        if (desc.output != job.root_output) {   // (the root may write in place)
+            // columns [kv_head_begin * group, (kv_head_begin + span) * group) of every row: one pitched peer copy
+            cudaMemcpy3DPeerParms parms{};
+            const size_t column = static_cast<size_t>(desc.kv_head_begin) * group * desc.head_dim * 4u;
+            const size_t width = static_cast<size_t>(span) * group * desc.head_dim * 4u;
+            parms.srcDevice = s->ordinals[d];
+            parms.dstDevice = s->ordinals[0];
+            parms.srcPtr = make_cudaPitchedPtr(desc.output, o_row, o_row, job.row_count);
+            parms.dstPtr = make_cudaPitchedPtr(job.root_output, o_row, o_row, job.row_count);
+            parms.srcPos = make_cudaPos(column, 0, 0);
+            parms.dstPos = make_cudaPos(column, 0, 0);
+            parms.extent = make_cudaExtent(width, job.row_count, 1);
+            if ((e = cudaMemcpy3DPeerAsync(&parms, stream)) != cudaSuccess) return cuda_fail(e, "output columns back");
+        }
+    }
+    if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+    return CF_OK;
+}
+
+void worker_main(cf_b200_mg_scheduler *s, uint32_t d) {
+    const bool usable = cudaSetDevice(s->ordinals[d]) == cudaSuccess;
+    uint64_t seen = 0;
+    for (;;) {
+        uint32_t spins = 0;
+        while (s->step_seq.load(std::memory_order_acquire) == seen && !s->stopping.load(std::memory_order_acquire)) {
+            if (++spins < 20000u) {
+                std::this_thread::yield();
+            } else {
+                std::unique_lock<std::mutex> lock(s->wake_mutex);
+                s->wake_cv.wait_for(lock, std::chrono::milliseconds(2), [&] {
+                    return s->step_seq.load(std::memory_order_acquire) != seen || s->stopping.load(std::memory_order_acquire);
+                });
+            }
+        }
+        if (s->stopping.load(std::memory_order_acquire)) return;
+        seen = s->step_seq.load(std::memory_order_acquire);
+        if (s->job.shards[d].desc.seq_count != 0) {
+            if (usable) {
+                s->device_status[d] = submit_device(s, d);
+            } else {
+                s->device_status[d] = CF_ERR_CUDA;
+                s->device_error[d] = "the device could not be made current";
+            }
+        }
+        s->pending.fetch_sub(1u, std::memory_order_release);
+    }
+}
+
+}  // namespace
 
 extern "C" cf_b200_mg_scheduler *cf_b200_mg_create(const cf_b200_mg_config *c) {
     if (!c || c->struct_size != sizeof(cf_b200_mg_config) || c->abi_version != CF_B200_ABI_VERSION || c->device_count == 0 ||
@@ -130,6 +257,12 @@ extern "C" cf_b200_mg_scheduler *cf_b200_mg_create(const cf_b200_mg_config *c) {
          cudaMalloc(&s->d_perm, sizeof(uint32_t) * c->max_rows) == cudaSuccess &&
          cudaMallocHost(&s->h_perm, sizeof(uint32_t) * c->max_rows) == cudaSuccess;
     if (!ok) {
+        s->release();
+        return nullptr;
+    }
+    try {
+        for (uint32_t d = 1; d < c->device_count; ++d) s->workers.emplace_back(worker_main, s.get(), d);
+    } catch (...) {
         s->release();
         return nullptr;
     }
@@ -261,18 +394,27 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
     const size_t q_row = s->query_row_bytes(), o_row = s->output_row_bytes();
     cudaError_t e = cudaSetDevice(s->ordinals[0]);
     if (e != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+    StepJob &job = s->job;
+    job.shards = shards;
+    job.mode = mode;
+    job.row_count = row_count;
+    job.root_queries = root_queries;
+    job.root_output = root_output;
+    const uint32_t q_units = static_cast<uint32_t>(q_row / 16u), o_units = static_cast<uint32_t>(o_row / 16u);
 
     if (mode == CF_B200_MG_BY_SEQUENCE) {
         // query rows into device-major order on the root (one kernel), one copy per device out, one per device back,
         // output rows back into batch order (one kernel)
         uint32_t at = 0;
         bool changed = s->last_perm.size() != listed;
-        for (uint32_t d = 0; d < devices; ++d)
+        for (uint32_t d = 0; d < devices; ++d) {
+            job.first_row[d] = at;
             for (uint32_t i = 0; i < shards[d].desc.seq_count; ++i, ++at) {
                 const uint32_t row = shards[d].rows ? shards[d].rows[i] : i;
                 if (!changed && s->last_perm[at] != row) changed = true;
                 s->h_perm[at] = row;
             }
+        }
         if (changed) {   // a new placement: the row order goes to the root device (a few hundred bytes)
             e = cudaMemcpyAsync(s->d_perm, s->h_perm, sizeof(uint32_t) * listed, cudaMemcpyHostToDevice, root_stream);
             if (e != cudaSuccess) return s->cuda_fail(e, "row order upload");
@@ -280,83 +422,43 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
             if (e != cudaSuccess) return s->cuda_fail(e, "row order upload");
             s->last_perm.assign(s->h_perm, s->h_perm + listed);
         }
-        const uint32_t q_units = static_cast<uint32_t>(q_row / 16u), o_units = static_cast<uint32_t>(o_row / 16u);
         const uint32_t blocks = std::min<uint32_t>(1024u, (listed * q_units + 255u) / 256u);
         permute_rows_kernel<true><<<blocks, 256, 0, root_stream>>>(static_cast<const uint4 *>(root_queries),
                                                                    reinterpret_cast<uint4 *>(s->staging_q), s->d_perm, listed, q_units);
-        e = cudaEventRecord(s->ready, root_stream);
-        if (e != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
-        at = 0;
-        for (uint32_t d = 0; d < devices; ++d) {
-            const cf_b200_sealed_attention_desc &desc = shards[d].desc;
-            if (desc.seq_count == 0) continue;
-            cudaStream_t stream = s->streams[d];
-            if ((e = cudaSetDevice(s->ordinals[d])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
-            if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
-            e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], s->staging_q + q_row * at, s->ordinals[0],
-                                    q_row * desc.seq_count, stream);
-            if (e != cudaSuccess) return s->cuda_fail(e, "query rows out");
-            const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
-            if (launched != CF_OK) return s->fail(launched, "attention launch failed on a device");
-            e = cudaMemcpyPeerAsync(s->staging_out + (o_row / 4u) * at, s->ordinals[0], desc.output, s->ordinals[d],
-                                    o_row * desc.seq_count, stream);
-            if (e != cudaSuccess) return s->cuda_fail(e, "output rows back");
-            if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
-            ++s->counters.attention_launches;
-            s->counters.peer_copies += d == 0 ? 0u : 2u;
-            s->counters.peer_bytes += d == 0 ? 0u : (q_row + o_row) * desc.seq_count;
-            at += desc.seq_count;
-        }
-        if ((e = cudaSetDevice(s->ordinals[0])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
+    } else {
         for (uint32_t d = 0; d < devices; ++d)
-            if (shards[d].desc.seq_count && (e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess)
-                return s->cuda_fail(e, "cudaStreamWaitEvent");
+            if (shards[d].desc.seq_count && (shards[d].rows || shards[d].desc.seq_count != row_count))
+                return s->fail(CF_ERR_INVALID_ARGUMENT, "kv-head sharding serves every row on every device");
+    }
+    if ((e = cudaEventRecord(s->ready, root_stream)) != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
+
+    // every device's share is queued by its own thread (the root's by this one), then the root stream waits for all
+    for (uint32_t d = 0; d < devices; ++d) s->device_status[d] = CF_OK;
+    s->pending.store(static_cast<uint32_t>(s->workers.size()), std::memory_order_release);
+    s->step_seq.fetch_add(1u, std::memory_order_release);
+    if (!s->workers.empty()) s->wake_cv.notify_all();
+    if (shards[0].desc.seq_count) s->device_status[0] = submit_device(s, 0);
+    while (s->pending.load(std::memory_order_acquire) != 0u) std::this_thread::yield();
+    for (uint32_t d = 0; d < devices; ++d) {
+        if (shards[d].desc.seq_count == 0) continue;
+        if (s->device_status[d] != CF_OK) return s->fail(s->device_status[d], s->device_error[d]);
+        ++s->counters.attention_launches;
+        if (d != 0) {
+            const cf_b200_sealed_attention_desc &desc = shards[d].desc;
+            const uint32_t span = desc.kv_head_span ? desc.kv_head_span : desc.kv_head_count - desc.kv_head_begin;
+            s->counters.peer_copies += 2u;
+            s->counters.peer_bytes += mode == CF_B200_MG_BY_SEQUENCE
+                                          ? (q_row + o_row) * desc.seq_count
+                                          : q_row * row_count + static_cast<size_t>(span) * (desc.query_head_count / desc.kv_head_count) *
+                                                                    desc.head_dim * 4u * row_count;
+        }
+        if ((e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
+    }
+    if (mode == CF_B200_MG_BY_SEQUENCE) {
         const uint32_t oblocks = std::min<uint32_t>(1024u, (listed * o_units + 255u) / 256u);
         permute_rows_kernel<false><<<oblocks, 256, 0, root_stream>>>(reinterpret_cast<const uint4 *>(s->staging_out),
                                                                      static_cast<uint4 *>(root_output), s->d_perm, listed, o_units);
         if ((e = cudaPeekAtLastError()) != cudaSuccess) return s->cuda_fail(e, "row permutation");
-    } else {
-        // every device serves the same rows with its own kv heads: all query rows out, its query-head columns back
-        e = cudaEventRecord(s->ready, root_stream);
-        if (e != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
-        for (uint32_t d = 0; d < devices; ++d) {
-            const cf_b200_sealed_attention_desc &desc = shards[d].desc;
-            if (desc.seq_count == 0) continue;
-            if (shards[d].rows || desc.seq_count != row_count)
-                return s->fail(CF_ERR_INVALID_ARGUMENT, "kv-head sharding serves every row on every device");
-            const uint32_t group = desc.query_head_count / desc.kv_head_count;
-            const uint32_t span = desc.kv_head_span ? desc.kv_head_span : desc.kv_head_count - desc.kv_head_begin;
-            cudaStream_t stream = s->streams[d];
-            if ((e = cudaSetDevice(s->ordinals[d])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
-            if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
-            if (desc.queries != root_queries) {   // the root device may read the caller's rows in place
-                e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], root_queries, s->ordinals[0], q_row * row_count, stream);
-                if (e != cudaSuccess) return s->cuda_fail(e, "query rows out");
-            }
-            const cf_status launched = cf_b200_sealed_attention_async(&desc, stream);
-            if (launched != CF_OK) return s->fail(launched, "attention launch failed on a device");
-            // columns [kv_head_begin * group, (kv_head_begin + span) * group) of every row: one pitched peer copy
-            cudaMemcpy3DPeerParms parms{};
-            const size_t column = static_cast<size_t>(desc.kv_head_begin) * group * desc.head_dim * 4u;
-            const size_t width = static_cast<size_t>(span) * group * desc.head_dim * 4u;
-            parms.srcDevice = s->ordinals[d];
-            parms.dstDevice = s->ordinals[0];
-            parms.srcPtr = make_cudaPitchedPtr(desc.output, o_row, o_row, row_count);
-            parms.dstPtr = make_cudaPitchedPtr(root_output, o_row, o_row, row_count);
-            parms.srcPos = make_cudaPos(column, 0, 0);
-            parms.dstPos = make_cudaPos(column, 0, 0);
-            parms.extent = make_cudaExtent(width, row_count, 1);
-            if (desc.output != root_output && (e = cudaMemcpy3DPeerAsync(&parms, stream)) != cudaSuccess)   // the root may write in place
-                return s->cuda_fail(e, "output columns back");
-            if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return s->cuda_fail(e, "cudaEventRecord");
-            ++s->counters.attention_launches;
-            s->counters.peer_copies += d == 0 ? 0u : 2u;
-            s->counters.peer_bytes += d == 0 ? 0u : q_row * row_count + width * row_count;
-        }
-        if ((e = cudaSetDevice(s->ordinals[0])) != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
-        for (uint32_t d = 0; d < devices; ++d)
-            if (shards[d].desc.seq_count && (e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess)
-                return s->cuda_fail(e, "cudaStreamWaitEvent");
     }
     ++s->counters.steps;
     s->error.clear();
