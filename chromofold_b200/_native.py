@@ -94,7 +94,7 @@ EXPORTS = {
         "cf_ms_cuda_shift_sequence", "cf_ms_cuda_execute_batch_async", "cf_ms_cuda_cancel_sequence_async",
         "cf_ms_cuda_reclaim_async", "cf_ms_cuda_audit", "cf_ms_cuda_get_counters", "cf_ms_cuda_last_error",
         "cf_b200_ms_append_active_async", "cf_b200_ms_seal_active_async", "cf_b200_ms_truncate_async",
-        "cf_b200_ms_sequence_tokens", "cf_b200_ms_page_sharing",
+        "cf_b200_ms_sequence_tokens", "cf_b200_ms_page_sharing", "cf_b200_ms_arena_stats",
     ],
     "compat_mscache.h": [
         "cf_multisequence_create", "cf_multisequence_destroy", "cf_sequence_create", "cf_sequence_copy_async",

@@ -23,6 +23,7 @@ struct PageRef { uint64_t page_id; int64_t logical_begin; uint32_t tokens; uint3
 struct SharedPage {
     uint64_t logical_refs = 0, in_flight_refs = 0, resident_bytes = 0, seal_generation = 0;
     bool retired = false;
+    uint64_t record_bytes = 0;        // what the sealer wrote into the page's arena slot
     std::vector<uint32_t> store_ids;  // page ids of its tiles in the arena's directory
 };
 struct LayerSeq {
@@ -106,9 +107,14 @@ struct cf_ms_cuda_resolver {
     std::string error;
     // device side
     uint32_t tile = 0, tiles_per_page = 0, slot_capacity = 0, stride = 256;
-    uint32_t next_store_id = 1;
-    std::vector<uint32_t> free_store_ids;
-    uint64_t records = 0;
+    // Arena room is handed out in page slots: a slot holds the records of one page (tiles_per_page tiles x kv heads, each
+    // at its largest possible size) at a fixed place, store ids slot * tiles_per_page + 1 + tile. A reclaimed page gives
+    // its slot back, and the next page sealed into it overwrites the old bytes: the arena stops growing once the number
+    // of live pages does, however many sequences come and go.
+    uint32_t next_page_slot = 0;
+    std::vector<uint32_t> free_page_slots;
+    uint64_t live_record_bytes = 0;      // bytes the sealer actually wrote into live slots
+    uint32_t device_status_seen = 0;     // CF_B200_DEVSTAT_* bits read back at the resolver's synchronisation points
     std::vector<bool> calibrated;
     bool ready = false;
     Buffer<uint8_t> arena, workspace;
@@ -256,20 +262,22 @@ uint32_t seal_rows(cf_ms_cuda_resolver *r, Sequence &q, uint32_t layer, const fl
     LayerSeq &L = q.layers[layer];
     const uint32_t n = (token_count + r->tile - 1) / r->tile;
     r->grow_stride(L.tiles + n, s);
-    r->records += static_cast<uint64_t>(n) * r->config.kv_head_count;
-    r->arena.ensure(r->records * r->max_record_bytes() + 4096, s);
+    if (n > r->tiles_per_page) throw std::invalid_argument("more rows than a page holds");
+    const bool recycled = !r->free_page_slots.empty();
+    const uint32_t page_slot = recycled ? r->free_page_slots.back() : r->next_page_slot;
+    const uint64_t slot_units = static_cast<uint64_t>(r->tiles_per_page) * r->config.kv_head_count * (r->max_record_bytes() / 16u);
+    const unsigned long long region_begin = 1ull + page_slot * slot_units;   // unit 0 stays unused
+    r->arena.ensure((region_begin + slot_units) * 16u + 4096, s);
     std::vector<uint32_t> host(4 * n);
     for (uint32_t j = 0; j < n; ++j) {
-        uint32_t id;
-        if (!r->free_store_ids.empty()) { id = r->free_store_ids.back(); r->free_store_ids.pop_back(); }
-        else id = r->next_store_id++;
+        const uint32_t id = page_slot * r->tiles_per_page + 1u + j;
         page.store_ids.push_back(id);
         host[j] = 0;
         host[n + j] = id;
         host[2 * n + j] = std::min(r->tile, token_count - j * r->tile);
         host[3 * n + j] = j * r->tile;
     }
-    r->page_dir.ensure(static_cast<size_t>(r->next_store_id + 1) * r->config.kv_head_count, s);
+    r->page_dir.ensure((static_cast<size_t>(page_slot + 1) * r->tiles_per_page + 2) * r->config.kv_head_count, s);
     r->jobs.ensure(4 * n, s);
     cuda_check(cudaMemcpyAsync(r->jobs.ptr, host.data(), host.size() * 4, cudaMemcpyHostToDevice, s), "upload seal jobs");
     cf_b200_seal_desc sd{};
@@ -293,7 +301,7 @@ uint32_t seal_rows(cf_ms_cuda_resolver *r, Sequence &q, uint32_t layer, const fl
     sd.job_rows = r->jobs.ptr + 3 * n;
     sd.job_count = n;
     sd.arena = r->arena.ptr;
-    sd.arena_units = r->arena.count / 16;
+    sd.arena_units = region_begin + slot_units;   // the sealer takes room from the cursor: it starts at the slot and may not leave it
     sd.arena_cursor_units = r->cursor.ptr;
     sd.page_dir = r->page_dir.ptr;
     sd.status = r->status.ptr;
@@ -313,7 +321,30 @@ uint32_t seal_rows(cf_ms_cuda_resolver *r, Sequence &q, uint32_t layer, const fl
         cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
         r->calibrated[layer] = true;
     }
+    cuda_check(cudaMemcpyAsync(r->cursor.ptr, &region_begin, sizeof region_begin, cudaMemcpyHostToDevice, s), "place arena cursor");
     if (cf_b200_seal_pages_async(&sd, s) != CF_OK) throw std::runtime_error("seal launch rejected");
+    // The sealer publishes nothing for a tile that holds NaN / Inf or found no room, so its outcome is read back before
+    // the page becomes part of the sequence (the reference synchronises at the same point,
+    // src/cuda/device_kv_seal_attention.cu:265). A refused page leaves the sequence, the slot list and the counters as
+    // they were.
+    uint32_t status = 0;
+    unsigned long long cursor_after = 0;
+    cuda_check(cudaMemcpyAsync(&status, r->status.ptr, 4, cudaMemcpyDeviceToHost, s), "read seal status");
+    cuda_check(cudaMemcpyAsync(&cursor_after, r->cursor.ptr, sizeof cursor_after, cudaMemcpyDeviceToHost, s), "read arena cursor");
+    cuda_check(cudaStreamSynchronize(s), "seal validation sync");
+    r->device_status_seen |= status;
+    if (status & (CF_B200_DEVSTAT_NONFINITE | CF_B200_DEVSTAT_ARENA_FULL)) {
+        for (uint32_t id : page.store_ids)   // whatever some kv heads of the page did publish goes back to "not there"
+            cuda_check(cudaMemsetAsync(r->page_dir.ptr + static_cast<size_t>(id) * r->config.kv_head_count, 0,
+                                       r->config.kv_head_count * sizeof(uint64_t), s), "unpublish refused page");
+        cuda_check(cudaMemsetAsync(r->status.ptr, 0, 4, s), "clear status");
+        page.store_ids.clear();
+        throw std::runtime_error(status & CF_B200_DEVSTAT_NONFINITE ? "page contains NaN or Inf" : "arena slot is too small for the page");
+    }
+    if (recycled) r->free_page_slots.pop_back();
+    else ++r->next_page_slot;
+    page.record_bytes = (cursor_after - region_begin) * 16ull;
+    r->live_record_bytes += page.record_bytes;
     cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(layer, q.slot) * r->stride + L.tiles, host.data() + n, n * 4,
                                cudaMemcpyHostToDevice, s), "publish page ids");
     return n;
@@ -845,15 +876,14 @@ extern "C" int cf_ms_cuda_reclaim_async(cf_ms_cuda_resolver *r, void *stream) {
         for (auto it = r->pages.begin(); it != r->pages.end();) {
             SharedPage &page = it->second;
             if (page.retired && page.logical_refs == 0 && page.in_flight_refs == 0) {
-                // the directory rows of its tiles go back to "not there" and the ids can be handed out again; the
-                // record bytes stay in the arena until it is rebuilt
-                for (uint32_t id : page.store_ids) {
+                // the directory rows of its tiles go back to "not there"; its arena slot is handed to the next page sealed
+                for (uint32_t id : page.store_ids)
                     if (r->ready)
                         cuda_check(cudaMemsetAsync(r->page_dir.ptr + static_cast<size_t>(id) * r->config.kv_head_count, 0,
                                                    r->config.kv_head_count * sizeof(uint64_t), static_cast<cudaStream_t>(stream)),
                                    "clear directory rows");
-                    r->free_store_ids.push_back(id);
-                }
+                if (!page.store_ids.empty()) r->free_page_slots.push_back((page.store_ids.front() - 1u) / r->tiles_per_page);
+                r->live_record_bytes -= std::min<uint64_t>(r->live_record_bytes, page.record_bytes);
                 r->counters.pending_reclamation_bytes -= page.resident_bytes;
                 ++r->counters.pages_reclaimed;
                 it = r->pages.erase(it);
@@ -862,6 +892,18 @@ extern "C" int cf_ms_cuda_reclaim_async(cf_ms_cuda_resolver *r, void *stream) {
             }
         }
     });
+}
+
+extern "C" int cf_b200_ms_arena_stats(const cf_ms_cuda_resolver *r, uint64_t *slots_in_use, uint64_t *slots_free,
+                                      uint64_t *live_record_bytes, uint64_t *arena_bytes, uint32_t *device_status_seen) {
+    if (!r) return -1;
+    std::lock_guard<std::mutex> guard(r->mutex);
+    if (slots_in_use) *slots_in_use = r->next_page_slot - r->free_page_slots.size();
+    if (slots_free) *slots_free = r->free_page_slots.size();
+    if (live_record_bytes) *live_record_bytes = r->live_record_bytes;
+    if (arena_bytes) *arena_bytes = r->arena.count;
+    if (device_status_seen) *device_status_seen = r->device_status_seen;
+    return 0;
 }
 
 extern "C" int cf_ms_cuda_shift_sequence(cf_ms_cuda_resolver *r, int64_t id, uint32_t begin, uint32_t end, int32_t delta) {

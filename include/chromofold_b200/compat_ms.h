@@ -98,6 +98,12 @@ int cf_b200_ms_sequence_tokens(const cf_ms_cuda_resolver *resolver, int64_t sequ
 int cf_b200_ms_page_sharing(const cf_ms_cuda_resolver *resolver, uint64_t *shared_pages, uint64_t *shared_references,
                             uint64_t *reference_increments, uint64_t *reference_decrements);
 
+/* Arena bookkeeping: room is handed out in page slots (one page's records at their largest size), a reclaimed page's
+ * slot is reused by the next page sealed, so the arena stops growing once the number of live pages does.
+ * device_status_seen: CF_B200_DEVSTAT_* bits the resolver has read back at its synchronisation points (every seal). */
+int cf_b200_ms_arena_stats(const cf_ms_cuda_resolver *resolver, uint64_t *slots_in_use, uint64_t *slots_free,
+                           uint64_t *live_record_bytes, uint64_t *arena_bytes, uint32_t *device_status_seen);
+
 #ifdef __cplusplus
 }
 #endif

@@ -152,3 +152,73 @@ def test_resolver_publish_share_batch_reclaim(native, oracle):
     assert n.pages_retired == 4 and n.pages_reclaimed == 4 and n.pending_reclamation_bytes == 0
     assert lib.cf_ms_cuda_audit(r) == 0 and n.dense_fallback_launches == 0
     lib.cf_ms_cuda_destroy(r, None)
+
+
+def test_refused_seal_leaves_the_sequence_untouched_and_arena_slots_are_reused(native):
+    """A tail with a NaN row: the seal call fails, the sequence keeps its rows and its token counts, nothing is
+    published, the status bit is reported. Then churn: forty sequences are sealed, removed and reclaimed one after the
+    other, and the arena does not grow past its first slots."""
+    import torch
+    lib = native.lib()
+    lib.cf_ms_cuda_create.restype = C.c_void_p
+    lib.cf_ms_cuda_last_error.restype = C.c_char_p
+    hkv, hq, d, page = 2, 8, 128, 16
+    r = C.c_void_p(lib.cf_ms_cuda_create(C.byref(MsConfig(1, hkv, hq, d, page, hq // hkv, 0))))
+    rng = np.random.default_rng(33)
+
+    def view(t):
+        es = t.element_size()
+        return TensorView(t.data_ptr(), 3, t.shape[0], t.shape[1], t.shape[2], t.stride(0) * es, t.stride(1) * es, es, 0)
+
+    def rows(n, poison=False):
+        x = rng.standard_normal((n, hkv, d)).astype(np.float32)
+        if poison:
+            x[3, 1, 7] = np.nan
+        return torch.from_numpy(x).cuda()
+
+    def stats():
+        v = [C.c_uint64(0) for _ in range(4)]
+        bits = C.c_uint32(0)
+        assert lib.cf_b200_ms_arena_stats(r, *[C.byref(x) for x in v], C.byref(bits)) == 0
+        return [int(x.value) for x in v] + [int(bits.value)]
+
+    def tokens(seq):
+        a, b = C.c_uint32(0), C.c_uint32(0)
+        assert lib.cf_b200_ms_sequence_tokens(r, C.c_int64(seq), 0, C.byref(a), C.byref(b)) == 0
+        return int(a.value), int(b.value)
+
+    assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(1)) == 0
+    k, v = rows(16, poison=True), rows(16)
+    assert lib.cf_b200_ms_append_active_async(r, C.c_int64(1), 0, 0, C.byref(view(k)), C.byref(view(v)), None) == 0
+    n = MsCounters()
+    lib.cf_ms_cuda_get_counters(r, C.byref(n))
+    registered = n.pages_registered
+    assert lib.cf_b200_ms_seal_active_async(r, C.c_int64(1), 0, None) == -1
+    assert b"NaN" in lib.cf_ms_cuda_last_error(r)
+    assert tokens(1) == (0, 16)                           # nothing sealed, the rows are still the active tail
+    in_use, free, live, arena0, bits = stats()
+    assert in_use == 0 and live == 0 and bits & native.DEVSTAT_NONFINITE
+    lib.cf_ms_cuda_get_counters(r, C.byref(n))
+    assert n.pages_registered == registered
+    # the caller repairs the tail (drops it, appends clean rows) and seals
+    assert lib.cf_b200_ms_truncate_async(r, C.c_int64(1), 0, None) == 0
+    k = rows(16)
+    assert lib.cf_b200_ms_append_active_async(r, C.c_int64(1), 0, 0, C.byref(view(k)), C.byref(view(v)), None) == 0
+    assert lib.cf_b200_ms_seal_active_async(r, C.c_int64(1), 0, None) == 0, lib.cf_ms_cuda_last_error(r)
+    assert tokens(1) == (16, 0)
+    in_use, free, live, arena1, _ = stats()
+    assert in_use == 1 and 0 < live <= hkv * (16 + 2 * 2048)
+    for seq in range(100, 140):
+        assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(seq)) == 0
+        k, v = rows(16), rows(16)
+        assert lib.cf_b200_ms_append_active_async(r, C.c_int64(seq), 0, 0, C.byref(view(k)), C.byref(view(v)), None) == 0
+        assert lib.cf_b200_ms_seal_active_async(r, C.c_int64(seq), 0, None) == 0
+        assert lib.cf_ms_cuda_sequence_remove_async(r, C.c_int64(seq), None) == 0
+        torch.cuda.synchronize()
+        assert lib.cf_ms_cuda_reclaim_async(r, None) == 0
+    in_use, free, live2, arena2, _ = stats()
+    assert in_use == 1 and free <= 1 and arena2 == arena1 and live2 == live
+    lib.cf_ms_cuda_get_counters(r, C.byref(n))
+    assert n.pages_reclaimed == 40
+    assert lib.cf_ms_cuda_audit(r) == 0
+    lib.cf_ms_cuda_destroy(r, None)
