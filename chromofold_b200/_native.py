@@ -72,7 +72,7 @@ EXPORTS = {
         "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async", "cf_b200_codebook_build",
         "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
         "cf_b200_dense_attention_async", "cf_b200_build_info", "cf_b200_sealed_attention_static_async",
-        "cf_b200_sealed_attention_static_error", "cf_b200_shared_prefix_launches",
+        "cf_b200_sealed_attention_static_error", "cf_b200_shared_prefix_launches", "cf_b200_test_wait_expiry",
     ],
     "compat_kv.h": [
         "cf_kv_validate_page", "cf_kv_validate_layout", "cf_kv_page_resident_bytes", "cf_kv_cache_memory_stats",
@@ -94,6 +94,7 @@ EXPORTS = {
         "cf_ms_cuda_shift_sequence", "cf_ms_cuda_execute_batch_async", "cf_ms_cuda_cancel_sequence_async",
         "cf_ms_cuda_reclaim_async", "cf_ms_cuda_audit", "cf_ms_cuda_get_counters", "cf_ms_cuda_last_error",
         "cf_b200_ms_append_active_async", "cf_b200_ms_seal_active_async", "cf_b200_ms_truncate_async",
+        "cf_b200_ms_drop_prefix_async",
         "cf_b200_ms_sequence_tokens", "cf_b200_ms_page_sharing", "cf_b200_ms_arena_stats",
     ],
     "compat_mscache.h": [
@@ -148,7 +149,7 @@ EXPORTS = {
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",
         "cf_llama_kv_attention", "cf_llama_kv_attention_host", "cf_llama_kv_flush", "cf_llama_kv_seq_rm",
         "cf_llama_kv_seq_cp", "cf_llama_kv_seq_shift", "cf_llama_kv_clear", "cf_llama_kv_get_stats",
-        "cf_llama_kv_last_error",
+        "cf_llama_kv_last_error", "cf_b200_llama_kv_reference_page",
     ],
 }
 

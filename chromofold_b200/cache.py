@@ -315,7 +315,7 @@ class SealedKvLayer:
 
     @_on_own_device
     def attention_no_alloc(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0,
-                           kernel=N.KERNEL_AUTO):
+                           kernel=N.KERNEL_AUTO, shared_prefix_pages=0):
         """The same decode-step attention through the entry point that uses the library's built-in workspace
         (for callers that cannot allocate device memory). `out` must be given by such a caller; it is created here
         only as a convenience for tests."""
@@ -327,6 +327,7 @@ class SealedKvLayer:
         d.softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / float(np.sqrt(self.head_dim))
         d.causal_window = causal_window
         d.kernel = kernel
+        d.shared_prefix_pages = shared_prefix_pages
         status = self.lib.cf_b200_sealed_attention_static_async(C.byref(d), _stream_ptr())
         if status != N.CF_OK:
             raise N.CfError(self.lib.cf_b200_sealed_attention_static_error().decode(), status)

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -14,6 +15,7 @@
 #include <cuda_runtime.h>
 
 #include "chromofold_b200/compat_adapter.h"
+#include "chromofold_b200/compat_kv.h"
 #include "chromofold_b200/sealed_kv.h"
 
 namespace {
@@ -42,6 +44,92 @@ struct DeviceBuffer {  // grow-only device array; growing copies the old content
         count = next;
     }
 };
+
+// ---- the reference's own page quantiser on the GPU ---------------------------------------------------------------
+// What the reference's adapter stores for kv_bits 4 / 8 (integrations/llama.cpp/chromofold_kv_adapter.cpp:30-31) is what
+// gpu_fixture::encode_int{4,8}_page makes on the host (src/runtime/kv_gpu_fixture.cpp:46-95): K with one fp32 scale per
+// channel, V with one per token, scale = absmax / qmax (1 when the row or column is all zero), symbol =
+// clamp(lrint(x / scale), -(qmax+1), qmax) + 2^(bits-1), symbols packed MSB-first at `bits` bits, block offsets
+// b * 64 * bits, the LUT s | bits << 8. The kernel below makes the same page, bit for bit, from rows already on the GPU.
+struct KiviLayout {
+    size_t k_words, v_words, k_scales, v_scales, k_offsets, v_offsets, total;   // byte offsets inside a page block
+    uint32_t word_count, block_count;
+};
+inline KiviLayout kivi_layout(uint32_t tokens, uint32_t dim, uint32_t bits) {
+    KiviLayout l{};
+    const uint64_t symbols = static_cast<uint64_t>(tokens) * dim;
+    l.word_count = static_cast<uint32_t>((symbols * bits + 31u) / 32u);
+    l.block_count = static_cast<uint32_t>((symbols + 63u) / 64u);
+    size_t at = 0;
+    auto take = [&](size_t bytes) { const size_t here = at; at += (bytes + 15u) / 16u * 16u; return here; };
+    l.k_words = take(4ull * l.word_count);
+    l.v_words = take(4ull * l.word_count);
+    l.k_scales = take(4ull * dim);
+    l.v_scales = take(4ull * tokens);
+    l.k_offsets = take(4ull * l.block_count);
+    l.v_offsets = take(4ull * l.block_count);
+    l.total = at;
+    return l;
+}
+
+// One CTA per page. rows: K / V as [token][row_stride floats], this head's `dim` values first in each row.
+__global__ void __launch_bounds__(256) kivi_quantise_kernel(const float *k_rows, const float *v_rows, uint32_t row_stride,
+                                                            uint32_t tokens, uint32_t dim, uint32_t bits, uint8_t *block,
+                                                            KiviLayout lay, uint32_t *status) {
+    extern __shared__ float scales[];   // [dim] K scales | [tokens] V scales
+    float *k_scale = scales, *v_scale = scales + dim;
+    const int qmax = (1 << (bits - 1)) - 1, zero = 1 << (bits - 1);
+    int bad = 0;
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) {   // per channel over the tokens
+        float m = 0.0f;
+        for (uint32_t t = 0; t < tokens; ++t) {
+            const float x = k_rows[static_cast<size_t>(t) * row_stride + d];
+            bad |= !isfinite(x);
+            m = fmaxf(m, fabsf(x));
+        }
+        k_scale[d] = m == 0.0f ? 1.0f : __fdiv_rn(m, static_cast<float>(qmax));
+    }
+    for (uint32_t t = threadIdx.x / 32u; t < tokens; t += blockDim.x / 32u) {   // per token over the channels: a warp each
+        float m = 0.0f;
+        for (uint32_t d = threadIdx.x % 32u; d < dim; d += 32u) {
+            const float x = v_rows[static_cast<size_t>(t) * row_stride + d];
+            bad |= !isfinite(x);
+            m = fmaxf(m, fabsf(x));
+        }
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x % 32u == 0) v_scale[t] = m == 0.0f ? 1.0f : __fdiv_rn(m, static_cast<float>(qmax));
+    }
+    if (__syncthreads_or(bad)) {   // kv_gpu_fixture.cpp:13: a non-finite value is an error; nothing of the page is used
+        if (threadIdx.x == 0) atomicOr(status, 1u);
+        return;
+    }
+    const uint32_t per_word = 32u / bits;
+    uint32_t *kw = reinterpret_cast<uint32_t *>(block + lay.k_words), *vw = reinterpret_cast<uint32_t *>(block + lay.v_words);
+    const uint64_t symbols = static_cast<uint64_t>(tokens) * dim;
+    auto symbol = [&](float x, float scale) {
+        const int q = max(-(qmax + 1), min(qmax, __float2int_rn(__fdiv_rn(x, scale))));   // lrint(x / scale), clamped
+        return static_cast<uint32_t>(q + zero);
+    };
+    for (uint32_t w = threadIdx.x; w < lay.word_count; w += blockDim.x) {
+        uint32_t kword = 0, vword = 0;
+        for (uint32_t j = 0; j < per_word; ++j) {
+            const uint64_t i = static_cast<uint64_t>(w) * per_word + j;
+            if (i >= symbols) break;
+            const uint32_t t = static_cast<uint32_t>(i / dim), d = static_cast<uint32_t>(i % dim);
+            const uint32_t shift = (32u - bits) - j * bits;
+            kword |= symbol(k_rows[static_cast<size_t>(t) * row_stride + d], k_scale[d]) << shift;
+            vword |= symbol(v_rows[static_cast<size_t>(t) * row_stride + d], v_scale[t]) << shift;
+        }
+        kw[w] = kword;
+        vw[w] = vword;
+    }
+    for (uint32_t d = threadIdx.x; d < dim; d += blockDim.x) reinterpret_cast<float *>(block + lay.k_scales)[d] = k_scale[d];
+    for (uint32_t t = threadIdx.x; t < tokens; t += blockDim.x) reinterpret_cast<float *>(block + lay.v_scales)[t] = v_scale[t];
+    for (uint32_t b = threadIdx.x; b < lay.block_count; b += blockDim.x) {
+        reinterpret_cast<int32_t *>(block + lay.k_offsets)[b] = static_cast<int32_t>(b * 64u * bits);
+        reinterpret_cast<int32_t *>(block + lay.v_offsets)[b] = static_cast<int32_t>(b * 64u * bits);
+    }
+}
 
 struct HeadState {   // per (layer, kv head), in tokens
     uint64_t appended = 0;      // everything ever appended
@@ -85,6 +173,112 @@ struct cf_llama_kv_adapter {
     DeviceBuffer<uint8_t> workspace;
     static constexpr uint32_t kMaxQueries = 4096;
 
+    // Reference-exact mode (the default): pages as the reference's own fixed-width descriptors, made by
+    // kivi_quantise_kernel, attended by cf_kv_paged_attention_async. CHROMOFOLD_B200_CODER switches to format v1.
+    bool kivi = true;
+    uint32_t kivi_bits = 4;
+    static constexpr size_t kKiviChunk = 32u << 20;
+    std::vector<uint8_t *> kivi_chunks;      // page blocks never move: descriptors hold their addresses
+    size_t kivi_chunk_index = 0, kivi_chunk_used = 0;
+    DeviceBuffer<float> kivi_tail_k, kivi_tail_v;   // [layer][page_size][kv_head][head_dim]: the layout the attention reads
+    DeviceBuffer<int32_t> kivi_lut;
+    std::vector<std::unique_ptr<DeviceBuffer<cf_kv_device_page>>> kivi_descs;   // per layer, device
+    std::vector<std::vector<cf_kv_device_page>> kivi_host_descs;                // per layer, the same on the host
+    uint64_t kivi_resident_bytes = 0;
+
+    ~cf_llama_kv_adapter() {
+        for (uint8_t *c : kivi_chunks) cudaFree(c);
+    }
+    size_t kivi_row_floats() const { return static_cast<size_t>(opt.kv_head_count) * opt.head_dim; }
+    float *kivi_tail(DeviceBuffer<float> &buffer, uint32_t layer) const {
+        return buffer.ptr + static_cast<size_t>(layer) * opt.page_size * kivi_row_floats();
+    }
+    uint8_t *kivi_take(size_t bytes) {
+        if (bytes > kKiviChunk) throw std::runtime_error("page is larger than an adapter memory chunk");
+        if (kivi_chunk_index < kivi_chunks.size() && kivi_chunk_used + bytes > kKiviChunk) {
+            ++kivi_chunk_index;
+            kivi_chunk_used = 0;
+        }
+        if (kivi_chunk_index >= kivi_chunks.size()) {
+            uint8_t *fresh = nullptr;
+            cuda_check(cudaMalloc(reinterpret_cast<void **>(&fresh), kKiviChunk), "cudaMalloc");
+            kivi_chunks.push_back(fresh);
+            kivi_chunk_used = 0;
+        }
+        uint8_t *at = kivi_chunks[kivi_chunk_index] + kivi_chunk_used;
+        kivi_chunk_used += (bytes + 255u) / 256u * 256u;
+        return at;
+    }
+    void kivi_create() {
+        cudaStream_t s = nullptr;
+        const size_t tail = static_cast<size_t>(opt.layer_count) * opt.page_size * kivi_row_floats();
+        kivi_tail_k.ensure(tail, s);
+        kivi_tail_v.ensure(tail, s);
+        const uint32_t levels = 1u << kivi_bits;
+        std::vector<int32_t> lut(levels);
+        for (uint32_t v = 0; v < levels; ++v) lut[v] = static_cast<int32_t>(v | (kivi_bits << 8));
+        kivi_lut.ensure(levels, s);
+        cuda_check(cudaMemcpy(kivi_lut.ptr, lut.data(), levels * 4, cudaMemcpyHostToDevice), "upload lut");
+        status.ensure(1, s);
+        kivi_descs.clear();
+        for (uint32_t l = 0; l < opt.layer_count; ++l) {
+            kivi_descs.push_back(std::make_unique<DeviceBuffer<cf_kv_device_page>>());
+            kivi_descs.back()->ensure(64, s);
+        }
+        kivi_host_descs.assign(opt.layer_count, {});
+        cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    }
+    void kivi_reset() {
+        kivi_chunk_index = 0;
+        kivi_chunk_used = 0;
+        kivi_resident_bytes = 0;
+        for (auto &d : kivi_host_descs) d.clear();
+    }
+    // Quantise the tail rows of (layer, kv_head) into one page (the reference's seal_full_pages / flush for one head).
+    void kivi_seal(uint32_t layer, uint32_t kv_head, cudaStream_t s) {
+        HeadState &h = head(layer, kv_head);
+        if (h.tail == 0) return;
+        const uint32_t D = opt.head_dim, tokens = h.tail;
+        const KiviLayout lay = kivi_layout(tokens, D, kivi_bits);
+        uint8_t *block = kivi_take(lay.total);
+        cuda_check(cudaMemsetAsync(status.ptr, 0, 4, s), "clear status");
+        const size_t smem = (static_cast<size_t>(D) + tokens) * sizeof(float);
+        kivi_quantise_kernel<<<1, 256, smem, s>>>(kivi_tail(kivi_tail_k, layer) + static_cast<size_t>(kv_head) * D,
+                                                  kivi_tail(kivi_tail_v, layer) + static_cast<size_t>(kv_head) * D,
+                                                  static_cast<uint32_t>(kivi_row_floats()), tokens, D, kivi_bits, block, lay, status.ptr);
+        cuda_check(cudaGetLastError(), "page quantise launch");
+        uint32_t bad = 0;   // the reference quantises on the host and throws at once; so does this front
+        cuda_check(cudaMemcpyAsync(&bad, status.ptr, 4, cudaMemcpyDeviceToHost, s), "read status");
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+        if (bad) throw std::invalid_argument("invalid quantization input");
+        cf_kv_device_page page{};
+        page.k_words = reinterpret_cast<const uint32_t *>(block + lay.k_words);
+        page.v_words = reinterpret_cast<const uint32_t *>(block + lay.v_words);
+        page.k_scales = reinterpret_cast<const float *>(block + lay.k_scales);
+        page.v_scales = reinterpret_cast<const float *>(block + lay.v_scales);
+        page.k_block_offsets = reinterpret_cast<const int32_t *>(block + lay.k_offsets);
+        page.v_block_offsets = reinterpret_cast<const int32_t *>(block + lay.v_offsets);
+        page.k_lut = page.v_lut = kivi_lut.ptr;
+        page.token_begin = h.next_token - h.tail;
+        page.token_count = tokens;
+        page.head_dim = D;
+        page.block_size = 64;
+        page.k_max_code_length = page.v_max_code_length = page.fixed_code_length = kivi_bits;
+        page.zero_point = 1u << (kivi_bits - 1);
+        page.kv_head = kv_head;
+        std::vector<cf_kv_device_page> &host = kivi_host_descs[layer];
+        host.push_back(page);
+        DeviceBuffer<cf_kv_device_page> &dev = *kivi_descs[layer];
+        dev.ensure(host.size(), s);
+        cuda_check(cudaMemcpyAsync(dev.ptr + host.size() - 1, &host.back(), sizeof page, cudaMemcpyHostToDevice, s), "publish page");
+        // EncodedKvPage::resident_bytes: words, offsets, both LUTs, scales
+        kivi_resident_bytes += 8ull * lay.word_count + 8ull * lay.block_count + 8ull * (1u << kivi_bits) + 4ull * (D + tokens);
+        if (h.tail < opt.page_size) h.flushed_partial = true;
+        h.sealed += h.tail;
+        h.tail = 0;
+        ++sealed_tiles;
+    }
+
     HeadState &head(uint32_t layer, uint32_t h) { return heads[static_cast<size_t>(layer) * opt.kv_head_count + h]; }
     size_t tile_values() const { return static_cast<size_t>(tile_tokens) * opt.head_dim; }
     size_t max_record_bytes() const { return 16 + 2 * ((tile_values() + 15) / 16 * 16); }
@@ -94,6 +288,7 @@ struct cf_llama_kv_adapter {
         layers.assign(opt.layer_count, LayerState{});
         next_page_id = 1;
         sealed_tiles = 0;
+        kivi_reset();
         if (cursor.ptr) cuda_check(cudaMemsetAsync(cursor.ptr, 0, sizeof(unsigned long long), s), "memset cursor");
         if (page_dir.ptr) cuda_check(cudaMemsetAsync(page_dir.ptr, 0, page_dir.count * sizeof(uint64_t), s), "memset dir");
         if (status.ptr) cuda_check(cudaMemsetAsync(status.ptr, 0, sizeof(uint32_t), s), "memset status");
@@ -289,12 +484,19 @@ extern "C" cf_llama_kv_adapter *cf_llama_kv_create(const cf_llama_kv_options *op
         auto *a = new cf_llama_kv_adapter();
         a->opt = *options;
         a->tile_tokens = choose_tile_tokens(options->page_size, options->head_dim);
-        if (const char *env = std::getenv("CHROMOFOLD_B200_CODER")) {
+        a->kivi_bits = options->kv_bits == 8 ? 8u : 4u;   // chromofold_kv_adapter.cpp:30-31: 8 selects int8, anything else int4
+        if (const char *env = std::getenv("CHROMOFOLD_B200_CODER")) {   // opt in to entropy-coded format-v1 pages
+            a->kivi = false;
             if (std::strcmp(env, "huffman") == 0) a->coder = CF_B200_CODER_HUFFMAN;
             else if (std::strcmp(env, "fixed8") == 0) a->coder = CF_B200_CODER_FIXED8;
+            else if (std::strcmp(env, "rans4") == 0) a->coder = CF_B200_CODER_RANS_SPLIT4;
+            else if (std::strcmp(env, "huffman4") == 0) a->coder = CF_B200_CODER_HUFFMAN_SPLIT4;
+            else if (std::strcmp(env, "rans") != 0) a->kivi = true;   // not a coder name: the default stands
         }
+        if (a->kivi) a->tile_tokens = options->page_size;
         try {
-            a->create_buffers();
+            if (a->kivi) a->kivi_create();
+            else a->create_buffers();
             a->reset(nullptr);
         } catch (...) {
             delete a;
@@ -317,12 +519,31 @@ extern "C" int cf_llama_kv_append(cf_llama_kv_adapter *adapter, uint32_t layer, 
         cudaStream_t s = static_cast<cudaStream_t>(stream);
         HeadState &h = adapter->head(layer, kv_head);
         if (h.started && token_begin != h.next_token) throw std::invalid_argument("KV append must be logically contiguous");
-        if (h.flushed_partial) throw std::runtime_error("append after a partial flush is not supported by the sealed format");
+        if (h.flushed_partial && !adapter->kivi)
+            throw std::runtime_error("append after a partial flush is not supported by the sealed format");
         if (!h.started) {
             h.started = true;
             h.next_token = token_begin;
         }
         const uint32_t D = adapter->opt.head_dim, T = adapter->tile_tokens;
+        if (adapter->kivi) {   // rows into the [token][kv head][dim] tail the attention reads; a full tail becomes a page
+            const size_t row = adapter->kivi_row_floats();
+            uint32_t done = 0;
+            while (done < token_count) {
+                const uint32_t take = std::min(token_count - done, T - h.tail);
+                const size_t at = static_cast<size_t>(h.tail) * row + static_cast<size_t>(kv_head) * D;
+                cuda_check(cudaMemcpy2DAsync(adapter->kivi_tail(adapter->kivi_tail_k, layer) + at, row * 4, keys + static_cast<size_t>(done) * D,
+                                             D * 4ull, D * 4ull, take, cudaMemcpyHostToDevice, s), "append keys");
+                cuda_check(cudaMemcpy2DAsync(adapter->kivi_tail(adapter->kivi_tail_v, layer) + at, row * 4, values + static_cast<size_t>(done) * D,
+                                             D * 4ull, D * 4ull, take, cudaMemcpyHostToDevice, s), "append values");
+                h.tail += take;
+                h.next_token += take;
+                done += take;
+                if (h.tail == T) adapter->kivi_seal(layer, kv_head, s);
+            }
+            h.appended += token_count;
+            return;
+        }
         const size_t tile = (static_cast<size_t>(layer) * adapter->opt.kv_head_count + kv_head) * adapter->tile_values();
         uint32_t done = 0;
         while (done < token_count) {
@@ -358,6 +579,29 @@ extern "C" int cf_llama_kv_attention(cf_llama_kv_adapter *adapter, uint32_t laye
         for (uint32_t k = 1; k < adapter->opt.kv_head_count; ++k) {
             const HeadState &h = adapter->head(layer, k);
             if (h.sealed != h0.sealed || h.tail != h0.tail) throw std::runtime_error("KV active tails are not aligned across heads");
+        }
+        if (adapter->kivi) {   // the reference's own call over the reference's own page descriptors (its adapter, :107-131)
+            cf_kv_paged_attention_desc desc{};
+            desc.struct_size = sizeof desc;
+            desc.abi_version = CF_KV_CUDA_ABI_VERSION;
+            desc.pages = adapter->kivi_descs[layer]->ptr;
+            desc.page_count = static_cast<uint32_t>(adapter->kivi_host_descs[layer].size());
+            desc.kv_head_count = adapter->opt.kv_head_count;
+            desc.query_head_count = query_head_count;
+            desc.gqa_group_size = gqa_group_size;
+            desc.active_k = h0.tail ? adapter->kivi_tail(adapter->kivi_tail_k, layer) : nullptr;
+            desc.active_v = h0.tail ? adapter->kivi_tail(adapter->kivi_tail_v, layer) : nullptr;
+            desc.active_token_begin = h0.next_token - h0.tail;
+            desc.active_token_count = h0.tail;
+            desc.queries = queries_device;
+            desc.output = output_device;
+            desc.query_token_begin = query_token_begin;
+            desc.query_count = query_count;
+            desc.head_dim = adapter->opt.head_dim;
+            desc.causal_window = causal_window;
+            desc.softmax_scale = softmax_scale;
+            if (cf_kv_paged_attention_async(&desc, s) != CF_OK) throw std::runtime_error("ChromoFold paged attention launch rejected");
+            return;
         }
         LayerState &ls = adapter->layers[layer];
         const uint32_t L = adapter->opt.layer_count;
@@ -453,8 +697,10 @@ extern "C" int cf_llama_kv_attention_host(cf_llama_kv_adapter *adapter, uint32_t
 extern "C" int cf_llama_kv_flush(cf_llama_kv_adapter *adapter, void *stream) {
     return guarded(adapter, [&] {
         for (uint32_t layer = 0; layer < adapter->opt.layer_count; ++layer)
-            for (uint32_t h = 0; h < adapter->opt.kv_head_count; ++h)
-                adapter->seal_tail(layer, h, static_cast<cudaStream_t>(stream));
+            for (uint32_t h = 0; h < adapter->opt.kv_head_count; ++h) {
+                if (adapter->kivi) adapter->kivi_seal(layer, h, static_cast<cudaStream_t>(stream));
+                else adapter->seal_tail(layer, h, static_cast<cudaStream_t>(stream));
+            }
     });
 }
 
@@ -500,14 +746,32 @@ extern "C" int cf_llama_kv_get_stats(const cf_llama_kv_adapter *adapter, cf_llam
         out.active_tokens += h.sealed + h.tail - sealed_tokens;
     }
     out.dense_active_bytes = out.active_tokens * adapter->opt.head_dim * 2 * sizeof(float);
-    unsigned long long units = 0;
-    if (adapter->cursor.ptr) cudaMemcpy(&units, adapter->cursor.ptr, sizeof units, cudaMemcpyDeviceToHost);
-    out.compressed_bytes = units * 16ull;
-    out.descriptor_bytes = static_cast<uint64_t>(adapter->next_page_id) * adapter->opt.kv_head_count * sizeof(uint64_t);
+    if (adapter->kivi) {
+        out.compressed_bytes = adapter->kivi_resident_bytes;
+        for (const auto &layer : adapter->kivi_host_descs) out.descriptor_bytes += layer.size() * sizeof(cf_kv_device_page);
+    } else {
+        unsigned long long units = 0;
+        if (adapter->cursor.ptr) cudaMemcpy(&units, adapter->cursor.ptr, sizeof units, cudaMemcpyDeviceToHost);
+        out.compressed_bytes = units * 16ull;
+        out.descriptor_bytes = static_cast<uint64_t>(adapter->next_page_id) * adapter->opt.kv_head_count * sizeof(uint64_t);
+    }
     *stats = out;
     return 0;
 }
 
 extern "C" const char *cf_llama_kv_last_error(const cf_llama_kv_adapter *adapter) {
     return adapter == nullptr ? "invalid ChromoFold KV adapter" : adapter->last_error.c_str();
+}
+
+
+// Additive: the device descriptor of a page of reference-exact mode (the reference's cf_kv_device_page: fixed-width words,
+// K per-channel and V per-token fp32 scales), so that a test or a tool can read back exactly what was stored.
+// page_index counts the pages of `layer` in the order they were sealed, over all kv heads. Returns -1 in format-v1 mode.
+extern "C" int cf_b200_llama_kv_reference_page(const cf_llama_kv_adapter *adapter, uint32_t layer, uint32_t page_index,
+                                               cf_kv_device_page *out_page) {
+    if (adapter == nullptr || out_page == nullptr || !adapter->kivi || layer >= adapter->kivi_host_descs.size() ||
+        page_index >= adapter->kivi_host_descs[layer].size())
+        return -1;
+    *out_page = adapter->kivi_host_descs[layer][page_index];
+    return 0;
 }

@@ -6,6 +6,8 @@
 
 namespace cfb {
 
+constexpr uint32_t kDefaultWaitPolls = 1u << 22;   // about a microsecond each at most: seconds before a wait gives up
+
 struct AttentionParams {
     // geometry
     uint32_t kv_head_count, query_head_count, head_dim, page_tokens, block_size;
@@ -39,6 +41,8 @@ struct AttentionParams {
     uint32_t decode_probe;          // 1 = measurement: decode every page, fold the symbols into a checksum, no attention;
                                     // 2 = test: store every decoded symbol to `output` ([page id][kv head][K | V stream])
     uint32_t dump_pages;            // page ids the dump buffer covers (1 when decode_probe != 2)
+    uint32_t wait_polls;            // bound of every wait on a copy or a barrier, in polls
+    uint32_t skip_copy_page;        // test hook: the record of this page id is never fetched (its wait must run out); 0 = off
     uint32_t *status;
     // uncompressed comparison pools (dense kernel only)
     const __half *pool_k, *pool_v;

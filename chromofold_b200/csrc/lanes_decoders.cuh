@@ -14,7 +14,6 @@ namespace lanes {
 
 constexpr uint32_t kStageBytes = 4160;   // 16 header + 2 * 2048 payload max + 48 slack (decoders read ahead)
 constexpr uint32_t kTableBytes = 2 * 4096 * 4 + 2 * 4096 * 2;
-constexpr uint32_t kWaitSpins = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kMagic = 0x64646464u;       // fp16 1024.0 high byte, for the byte-permute conversion
 constexpr uint32_t kBias2 = 0x64806480u;       // half2(1152, 1152) = 1024 + zero point
@@ -28,20 +27,22 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
+// One poll; the warp may be suspended for up to about a microsecond inside it (the hint bounds a single poll, so that
+// a number of polls is a bound on time).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(1000u)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the copy did not land within kWaitSpins polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitSpins; ++i)
+// Bounded wait: false if the barrier did not complete within `polls` polls (AttentionParams::wait_polls).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t polls) {
+    for (uint32_t i = 0; i < polls; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

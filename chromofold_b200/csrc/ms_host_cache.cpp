@@ -29,6 +29,10 @@ struct Speculation {
 };
 struct SequenceState {
     Speculation speculation;
+    // Logical position of the first token the device store holds for this sequence. The store keeps a sequence's tokens
+    // contiguous from its token 0; a copy of a range that starts later, or a context shift of the whole sequence, only
+    // moves this offset (sealed records carry no position).
+    uint32_t base = 0;
 };
 
 bool valid_config(const cf_multisequence_config &c) {
@@ -62,6 +66,17 @@ SequenceState &find(cf_multisequence_cache *c, int64_t id, const char *what = "s
     auto it = c->sequences.find(id);
     if (it == c->sequences.end()) throw std::runtime_error(what);
     return it->second;
+}
+
+// Sealed tokens of the sequence's longest layer.
+uint32_t sealed_tokens(cf_multisequence_cache *c, int64_t id) {
+    uint32_t most = 0;
+    for (uint32_t layer = 0; layer < c->config.layer_count; ++layer) {
+        uint32_t sealed = 0, active = 0;
+        if (cf_b200_ms_sequence_tokens(c->device, id, layer, &sealed, &active) != 0) throw std::runtime_error("sequence does not exist");
+        most = std::max(most, sealed);
+    }
+    return most;
 }
 
 // Longest layer of the sequence, in tokens (sealed + active).
@@ -158,18 +173,29 @@ extern "C" int cf_sequence_copy_async(cf_multisequence_cache *c, int64_t source,
                                       uint32_t token_end, void *stream) {
     if (!c || source == destination || token_end < token_begin) return -1;
     return guarded(c, [&] {
-        find(c, source, "source sequence does not exist");
-        if (token_begin != 0) throw Unsupported("a copy range must start at token 0");
-        const uint32_t total = total_tokens(c, source);
+        // src/multisequence_cache.cpp:235-292: the destination gets the sealed pages that lie wholly inside
+        // [token_begin, token_end) and the active tail if it lies wholly inside; nothing is an error. A range whose end
+        // is not above its begin (the reference's own test passes 0, 0) copies nothing.
+        const uint32_t base = find(c, source, "source sequence does not exist").base;
+        const uint32_t page = c->config.page_size, total = total_tokens(c, source), sealed = sealed_tokens(c, source);
+        const uint64_t lo = token_begin > base ? token_begin - base : 0u;                 // the range in the store's coordinates
+        const uint64_t hi = token_end > base ? std::min<uint64_t>(token_end - base, total) : 0u;
+        uint64_t keep_end = hi >= total ? total : std::min<uint64_t>(hi / page * page, sealed);
+        uint64_t keep_begin = std::min<uint64_t>((lo + page - 1) / page * page, keep_end);
+        if (keep_begin > sealed) keep_begin = keep_end;   // the range starts inside the active tail: the tail is not wholly inside
+        if (keep_begin >= keep_end) keep_begin = keep_end = 0;
         device_check(c, cf_ms_cuda_copy_sequence_async(c->device, source, destination, stream));
-        if (token_end < total && cf_b200_ms_truncate_async(c->device, destination, token_end, stream) != 0) {
+        if ((keep_end < total && cf_b200_ms_truncate_async(c->device, destination, static_cast<uint32_t>(keep_end), stream) != 0) ||
+            (keep_begin > 0 && cf_b200_ms_drop_prefix_async(c->device, destination, static_cast<uint32_t>(keep_begin), stream) != 0)) {
             const std::string why = cf_ms_cuda_last_error(c->device);
             cf_ms_cuda_sequence_remove_async(c->device, destination, stream);
             c->sequences.erase(destination);
             update_active_peak(c);
-            throw Unsupported(why);
+            throw std::runtime_error(why);
         }
-        c->sequences[destination] = SequenceState{};
+        SequenceState fresh;
+        fresh.base = base + static_cast<uint32_t>(keep_begin);
+        c->sequences[destination] = fresh;
         ++c->counters.sequences_copied;
         update_active_peak(c);
         maybe_audit(c);
@@ -189,7 +215,9 @@ extern "C" int cf_sequence_remove_async(cf_multisequence_cache *c, int64_t id, i
             maybe_audit(c);
             return;
         }
-        if (position_begin < 0) position_begin = 0;
+        const int64_t base = find(c, id).base;   // positions are logical; the store counts from the sequence's first held token
+        position_begin = std::max<int64_t>(position_begin - base, 0);
+        position_end = position_end < 0 ? position_end : std::max<int64_t>(position_end - base, 0);
         const uint32_t total = total_tokens(c, id);
         if (position_begin >= total) return;   // nothing cached there
         if (position_end < total) throw Unsupported("only a suffix of a sequence can be removed");
@@ -204,9 +232,24 @@ extern "C" int cf_sequence_shift_async(cf_multisequence_cache *c, int64_t id, ui
                                        int32_t delta, void *) {
     if (!c || position_end < position_begin) return -1;
     return guarded(c, [&] {
-        find(c, id);
-        if (cf_ms_cuda_shift_sequence(c->device, id, position_begin, position_end, delta) != 0)
-            throw Unsupported(cf_ms_cuda_last_error(c->device));
+        // src/multisequence_cache.cpp:357-380: pages (and the active tail) wholly inside the range move by delta, a page the
+        // range cuts is an error. The store holds a sequence's tokens contiguously, so what it can express is a move of
+        // everything it holds (the offset changes), of nothing, or by zero; a move of only some of the pages would open
+        // a gap or an overlap inside the sequence and is refused as unsupported.
+        SequenceState &q = find(c, id);
+        const uint32_t page = c->config.page_size, total = total_tokens(c, id), sealed = sealed_tokens(c, id);
+        const uint64_t lo = position_begin > q.base ? position_begin - q.base : 0u;
+        const uint64_t hi = position_end > q.base ? std::min<uint64_t>(position_end - q.base, total) : 0u;
+        const bool cuts_a_page = (lo < sealed && lo % page != 0) || (hi < sealed && hi % page != 0) ||
+                                 (lo > sealed && lo < total) || (hi > sealed && hi < total);
+        if (lo < hi && cuts_a_page) throw Unsupported("context shift must align with immutable page boundaries");
+        const bool everything = lo == 0 && hi >= total, nothing = lo >= hi;
+        if (!nothing && !everything && delta != 0)
+            throw Unsupported("a shift of part of a sequence would leave a gap in its stored tokens");
+        if (everything && total > 0) {
+            if (static_cast<int64_t>(q.base) + delta < 0) throw std::runtime_error("context shift produces negative token position");
+            q.base = static_cast<uint32_t>(static_cast<int64_t>(q.base) + delta);
+        }
         ++c->counters.sequences_shifted;
         maybe_audit(c);
     });
@@ -219,7 +262,8 @@ extern "C" int cf_sequence_append_async(cf_multisequence_cache *c, int64_t id, u
         return -1;
     return guarded(c, [&] {
         SequenceState &q = find(c, id);
-        device_check(c, cf_b200_ms_append_active_async(c->device, id, layer, token_begin, keys, values, stream));
+        if (token_begin < q.base) throw std::runtime_error("non-contiguous sequence append");
+        device_check(c, cf_b200_ms_append_active_async(c->device, id, layer, token_begin - q.base, keys, values, stream));
         uint32_t sealed = 0, active = 0;
         cf_b200_ms_sequence_tokens(c->device, id, layer, &sealed, &active);
         if (active == c->config.page_size && !q.speculation.active)   // a full page is sealed on the GPU at once
@@ -233,16 +277,26 @@ extern "C" int cf_multisequence_attention_async(cf_multisequence_cache *c, const
     if (!c || !items || item_count == 0) return -1;
     return guarded(c, [&] {
         std::set<int64_t> observed;
+        bool rebased = false;
         for (uint32_t i = 0; i < item_count; ++i) {
             const cf_sequence_attention_item &item = items[i];
-            if (!c->sequences.count(item.sequence_id)) throw std::runtime_error("attention item references unknown sequence");
+            auto it = c->sequences.find(item.sequence_id);
+            if (it == c->sequences.end()) throw std::runtime_error("attention item references unknown sequence");
             if (item.layer >= c->config.layer_count || cf_device_tensor_validate(&item.query) != 0 || !item.output)
                 throw std::runtime_error("invalid sequence attention item");
+            if (item.query_token_begin < it->second.base) throw std::runtime_error("query position lies before the sequence's first token");
+            rebased = rebased || it->second.base != 0;
             observed.insert(item.sequence_id);
         }
         ++c->counters.batches_dispatched;
         c->counters.sequences_per_batch_peak = std::max<uint64_t>(c->counters.sequences_per_batch_peak, observed.size());
-        device_check(c, cf_ms_cuda_execute_batch_async(c->device, reinterpret_cast<const cf_ms_batch_item *>(items), item_count, stream));
+        if (!rebased) {
+            device_check(c, cf_ms_cuda_execute_batch_async(c->device, reinterpret_cast<const cf_ms_batch_item *>(items), item_count, stream));
+            return;
+        }
+        std::vector<cf_sequence_attention_item> local(items, items + item_count);   // logical positions -> the store's
+        for (cf_sequence_attention_item &item : local) item.query_token_begin -= c->sequences.at(item.sequence_id).base;
+        device_check(c, cf_ms_cuda_execute_batch_async(c->device, reinterpret_cast<const cf_ms_batch_item *>(local.data()), item_count, stream));
     });
 }
 

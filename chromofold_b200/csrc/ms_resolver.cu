@@ -570,7 +570,6 @@ extern "C" int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *r, int64_t id, uin
                     L.tiles -= ref.tiles;
                     SharedPage &page = r->pages.at(ref.page_id);
                     --page.logical_refs;
-                ++r->ref_decrements;
                     ++r->ref_decrements;
                     retire_if_unreferenced(r, page);
                 }
@@ -580,6 +579,62 @@ extern "C" int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *r, int64_t id, uin
             }
             ++L.active_generation;
             if (r->ready) r->push_scalars(q, layer, s);
+        }
+        ++q.topology_generation;
+    });
+}
+
+// Forget the first `token_count` tokens of every layer (whole pages only, all of them sealed): the sequence drops its
+// reference to those pages, the later pages move to the front of its page-table row, and device token 0 becomes what
+// was token `token_count` — the caller keeps the logical position of that token (a copy of a range that does not start
+// at token 0, src/multisequence_cache.cpp:257-258).
+extern "C" int cf_b200_ms_drop_prefix_async(cf_ms_cuda_resolver *r, int64_t id, uint32_t token_count, void *stream) {
+    if (!r) return -1;
+    return locked(r, false, [&] {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        Sequence &q = find_sequence(r, id, "sequence is missing");
+        if (token_count == 0) return;
+        for (const LayerSeq &L : q.layers) {   // the whole cut is checked before anything changes
+            uint32_t covered = 0;
+            for (const PageRef &ref : L.pages) {
+                if (covered >= token_count) break;
+                covered += ref.tokens;
+            }
+            if (covered != token_count && !(L.pages.empty() && L.sealed_tokens == 0 && L.active_count == 0))
+                throw std::invalid_argument("a prefix cut must fall on a page boundary of sealed pages");
+        }
+        for (uint32_t layer = 0; layer < q.layers.size(); ++layer) {
+            LayerSeq &L = q.layers[layer];
+            if (L.pages.empty()) continue;
+            uint32_t dropped_tokens = 0, dropped_tiles = 0;
+            size_t dropped_pages = 0;
+            while (dropped_tokens < token_count) {
+                const PageRef &ref = L.pages[dropped_pages++];
+                dropped_tokens += ref.tokens;
+                dropped_tiles += ref.tiles;
+                SharedPage &page = r->pages.at(ref.page_id);
+                --page.logical_refs;
+                ++r->ref_decrements;
+                retire_if_unreferenced(r, page);
+            }
+            L.pages.erase(L.pages.begin(), L.pages.begin() + static_cast<std::ptrdiff_t>(dropped_pages));
+            std::vector<uint32_t> row;
+            for (PageRef &ref : L.pages) {
+                ref.logical_begin -= token_count;
+                ref.first_tile -= dropped_tiles;
+                const SharedPage &page = r->pages.at(ref.page_id);
+                row.insert(row.end(), page.store_ids.begin(), page.store_ids.end());
+            }
+            L.sealed_tokens -= dropped_tokens;
+            L.tiles -= dropped_tiles;
+            L.active_begin = L.sealed_tokens;
+            ++L.descriptor_generation;
+            if (r->ready) {
+                if (!row.empty())
+                    cuda_check(cudaMemcpyAsync(r->page_table.ptr + r->row(layer, q.slot) * r->stride, row.data(), row.size() * 4,
+                                               cudaMemcpyHostToDevice, s), "re-base page table row");
+                r->push_scalars(q, layer, s);
+            }
         }
         ++q.topology_generation;
     });
@@ -625,7 +680,6 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
                 for (const auto &ref : layer.pages) {
                     SharedPage &page = r->pages.at(ref.page_id);
                     --page.logical_refs;
-                ++r->ref_decrements;
                     ++r->ref_decrements;
                     retire_if_unreferenced(r, page);
                 }

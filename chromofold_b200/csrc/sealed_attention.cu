@@ -467,6 +467,9 @@ __global__ void decode_pages_kernel(AttentionParams p, const uint32_t *page_ids,
 
 bool finite_float(float v) { return v == v && v - v == 0.0f; }
 
+// Test hooks (cf_b200_test_wait_expiry): a lowered wait bound and one page whose copy is armed but never issued.
+std::atomic<uint32_t> g_test_wait_polls{0}, g_test_skip_copy_page{0};
+
 bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->kv_head_count = d->kv_head_count;
     p->query_head_count = d->query_head_count;
@@ -508,6 +511,9 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->sm_count = 0;
     p->decode_probe = d->kernel == CF_B200_KERNEL_DECODE_PROBE ? 1u : d->kernel == CF_B200_KERNEL_DECODE_DUMP ? 2u : 0u;
     p->dump_pages = p->decode_probe == 2u ? d->reserved0 : 1u;
+    const uint32_t polls = g_test_wait_polls.load(std::memory_order_relaxed);
+    p->wait_polls = polls ? polls : kDefaultWaitPolls;
+    p->skip_copy_page = g_test_skip_copy_page.load(std::memory_order_relaxed);
     p->status = d->status;
     p->pool_k = nullptr;
     p->pool_v = nullptr;
@@ -631,6 +637,12 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
         if (e != cudaSuccess) return CF_ERR_CUDA;
     }
     if ((stages & CF_B200_STAGE_COMBINE) && cfb::launch_combine(p, s) != cudaSuccess) return CF_ERR_CUDA;
+    return CF_OK;
+}
+
+extern "C" cf_status cf_b200_test_wait_expiry(uint32_t skip_copy_page_id, uint32_t wait_polls) {
+    cfb::g_test_skip_copy_page.store(skip_copy_page_id, std::memory_order_relaxed);
+    cfb::g_test_wait_polls.store(wait_polls, std::memory_order_relaxed);
     return CF_OK;
 }
 

@@ -339,15 +339,18 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
         }
         float v_scale_prev = 1.0f;
 
+        // bit 63 of an entry (reserved, 0 in the directory) marks the page of the wait-expiry test: armed, never fetched
         auto load_entry = [&](uint32_t page) -> uint64_t {
             const uint32_t page_id = table_row[page];
-            return p.page_dir[static_cast<uint64_t>(page_id) * p.kv_head_count + kv_head];
+            const uint64_t entry = p.page_dir[static_cast<uint64_t>(page_id) * p.kv_head_count + kv_head];
+            return page_id == p.skip_copy_page ? entry | (1ull << 63) : entry;
         };
         auto issue = [&](uint32_t st, uint64_t entry) {
             const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
             if (lane == 0 && units16 != 0 && units16 * 16u <= kStageBytes - 32u) {
                 mbar_expect_tx(&bars[st], units16 * 16u);
-                bulk_load(warp_mem + st * kStageBytes, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
+                if (!(entry >> 63))
+                    bulk_load(warp_mem + st * kStageBytes, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), units16 * 16u, &bars[st]);
             }
         };
         auto entry_ok = [&](uint64_t entry) {
@@ -372,7 +375,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
             if (!entry_ok(entry_cur)) {
                 if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
             } else {
-                if (!mbar_wait(&bars[st], (phase_bits >> st) & 1u)) {
+                if (!mbar_wait(&bars[st], (phase_bits >> st) & 1u, p.wait_polls)) {
                     if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
                     alive = false;
                     break;
@@ -532,8 +535,8 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
         }
         if (!alive) {
             // give the copies still in flight a bounded chance to land before this warp's buffers go away
-            mbar_wait(&bars[0], phase_bits & 1u);
-            mbar_wait(&bars[1], (phase_bits >> 1) & 1u);
+            mbar_wait(&bars[0], phase_bits & 1u, p.wait_polls);
+            mbar_wait(&bars[1], (phase_bits >> 1) & 1u, p.wait_polls);
             return;
         }
 

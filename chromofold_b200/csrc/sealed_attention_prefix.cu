@@ -290,7 +290,10 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
     auto slot_entry = [&](const SlotCursor &c, uint32_t n) -> uint64_t {
         if (!c.valid) return 0ull;
         const uint32_t page = c.u.page_begin + (n - c.first_slot);
-        return page < c.u.page_end ? p.page_dir[static_cast<uint64_t>(table_row[page]) * p.kv_head_count + c.u.kv_head] : 0ull;
+        if (page >= c.u.page_end) return 0ull;
+        const uint32_t page_id = table_row[page];   // bit 63 marks the page of the wait-expiry test: armed, never fetched
+        const uint64_t e = p.page_dir[static_cast<uint64_t>(page_id) * p.kv_head_count + c.u.kv_head];
+        return page_id == p.skip_copy_page ? e | (1ull << 63) : e;
     };
     auto entry_ok = [&](uint64_t entry) {
         const uint32_t units16 = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry));
@@ -300,7 +303,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
         if (lane == 0 && entry_ok(entry)) {
             const uint32_t bytes = static_cast<uint32_t>(CF_B200_DIR_LENGTH_UNITS(entry)) * 16u;
             mbar_expect_tx(bar, bytes);
-            bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
+            if (!(entry >> 63)) bulk_load(stage, p.arena + 16ull * CF_B200_DIR_OFFSET_UNITS(entry), bytes, bar);
         }
     };
     uint32_t copy_phase = 0;
@@ -308,7 +311,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
     // The pair of round `it` is free once the tensor core has finished round it - 2. The parity wait is sound because a
     // warp's slots are 12 apart, less than two rounds: it has always seen the completion before the one it waits for.
     auto wait_pair_free = [&](uint32_t it) {
-        if (it >= 2u && !failed && !__all_sync(0xffffffffu, mbar_wait(&bar_free[it & 1u], ((it >> 1) - 1u) & 1u))) {
+        if (it >= 2u && !failed && !__all_sync(0xffffffffu, mbar_wait(&bar_free[it & 1u], ((it >> 1) - 1u) & 1u, p.wait_polls))) {
             failed = true;
             if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
@@ -348,7 +351,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
         if (cur.u.page_begin + in_unit < cur.u.page_end && !failed) {
             if (!entry_ok(entry)) {
                 if (lane == 0) raise_status(p, CF_B200_DEVSTAT_BAD_RECORD);
-            } else if (!__all_sync(0xffffffffu, mbar_wait(bar, copy_phase & 1u))) {
+            } else if (!__all_sync(0xffffffffu, mbar_wait(bar, copy_phase & 1u, p.wait_polls))) {
                 failed = true;
                 if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
             } else {
@@ -441,7 +444,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
         entry = next_entry;
     }
     // a copy whose wait ran out gets one more bounded chance to land before the CTA's shared memory is given back
-    if (failed) mbar_wait(bar, copy_phase & 1u);
+    if (failed) mbar_wait(bar, copy_phase & 1u, p.wait_polls);
 }
 
 // ---- softmax group: warps 12..19; its thread 0 also issues the tensor-core work ---------------------------------------
@@ -468,7 +471,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
     auto wait_o = [&]() {     // O and P in tensor memory may be touched again once the last P V has completed
         if (!o_pending) return;
         o_pending = false;
-        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_o, o_phase & 1u))) {
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_o, o_phase & 1u, p.wait_polls))) {
             failed = true;
             if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
@@ -485,7 +488,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
         uint8_t *k_tile = smem + kOffTiles + pair * 2u * kTileBytes, *v_tile = k_tile + kTileBytes;
         const float *meta = reinterpret_cast<const float *>(smem + kOffMeta) + pair * 4u * kRoundPages;
         // ---- the round's tiles are decoded (one thread waits, the barrier passes the news on) ----
-        if (issuer && !failed && !mbar_wait(&bar_full[pair], (it >> 1) & 1u)) {
+        if (issuer && !failed && !mbar_wait(&bar_full[pair], (it >> 1) & 1u, p.wait_polls)) {
             failed = true;
             raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
@@ -563,7 +566,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
         if (v_unit == 0.0f)
             for (uint32_t pg = 0; pg < kRoundPages; ++pg)
                 if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
-        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u))) {
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u, p.wait_polls))) {
             failed = true;
             if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
         }
@@ -700,7 +703,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
         }
     }
     // leaving early: give the tensor core's last commit a bounded chance to arrive before tensor memory is freed
-    if (o_pending && !failed) mbar_wait(bar_o, o_phase & 1u);
+    if (o_pending && !failed) mbar_wait(bar_o, o_phase & 1u, p.wait_polls);
 }
 
 template <bool kSplitQ>

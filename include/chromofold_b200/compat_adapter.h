@@ -11,12 +11,15 @@
  * token query_token_begin + i and sees tokens <= its position inside the causal window
  * (src/cuda/paged_kv_attention.cu:48-52,67-69); all kv heads must hold the same tokens when attention runs
  * (compressed_kv_cache.cu:152-154).
- * What differs: pages are quantised to int8 with one fp16 scale per stream and entropy coded (format v1) on the GPU,
- * whatever kv_bits says (kv_bits selects 4-/8-bit fixed-width pages in the reference, chromofold_kv_adapter.cpp:30-31);
- * physically a reference page of page_size tokens is stored as page_size / T records of T tokens with
- * T * head_dim <= 4096 (T = 16 at head_dim 128, the record geometry of the lane-per-block attention kernel, which
- * takes the fp32 queries of this ABI as binary16 + residue rows); statistics are reported in the reference's units.
- * Environment: CHROMOFOLD_B200_CODER = rans (default) | huffman | fixed8. */
+ * Pages. By default they are the reference's own: kv_bits 8 gives int8, anything else int4 (chromofold_kv_adapter.cpp:30-31),
+ * K with one fp32 scale per channel and V with one per token (src/runtime/kv_gpu_fixture.cpp:46-95), made on the GPU bit
+ * for bit as gpu_fixture::encode_int{4,8}_page makes them on the host, one page per page_size tokens, and attended through
+ * cf_kv_paged_attention_async as the reference's adapter does — so a caller that swaps this library in gets the
+ * reference's numbers. With CHROMOFOLD_B200_CODER = rans | huffman | fixed8 | rans4 | huffman4 in the environment the pages
+ * are instead quantised to int8 with one fp16 scale per stream and entropy coded (format v1, sealed_page_format.h):
+ * physically a page of page_size tokens is then page_size / T records of T tokens with T * head_dim <= 4096 (T = 16 at
+ * head_dim 128, the record geometry of the lane-per-block attention kernel, which takes the fp32 queries of this ABI as
+ * binary16 + residue rows). Statistics are reported in the reference's units in both modes. */
 #ifndef CHROMOFOLD_B200_COMPAT_ADAPTER_H
 #define CHROMOFOLD_B200_COMPAT_ADAPTER_H
 
@@ -78,6 +81,12 @@ int cf_llama_kv_seq_shift(cf_llama_kv_adapter *adapter, uint64_t sequence_id, in
 int cf_llama_kv_clear(cf_llama_kv_adapter *adapter);                                  /* :88 */
 int cf_llama_kv_get_stats(const cf_llama_kv_adapter *adapter, cf_llama_kv_stats *stats); /* :89 */
 const char *cf_llama_kv_last_error(const cf_llama_kv_adapter *adapter);               /* :91 */
+
+#include "chromofold_b200/compat_kv.h"
+/* Additive: the descriptor (device pointers) of page `page_index` of `layer` in reference-exact mode, pages counted in
+ * the order they were sealed over all kv heads; -1 in format-v1 mode or out of range. */
+int cf_b200_llama_kv_reference_page(const cf_llama_kv_adapter *adapter, uint32_t layer, uint32_t page_index,
+                                    cf_kv_device_page *out_page);
 
 #ifdef __cplusplus
 }

@@ -92,6 +92,9 @@ int cf_b200_ms_seal_active_async(cf_ms_cuda_resolver *resolver, int64_t sequence
 /* Keep the first token_count tokens of every layer: drops later whole pages (this sequence's reference to them) and
  * shortens the active tail; a cut inside a sealed page is refused. */
 int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t token_count, void *stream);
+/* Forget the first token_count tokens of every layer (whole sealed pages only): later pages move to the front of the
+ * sequence's page-table row and its token 0 becomes what was token token_count. */
+int cf_b200_ms_drop_prefix_async(cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t token_count, void *stream);
 int cf_b200_ms_sequence_tokens(const cf_ms_cuda_resolver *resolver, int64_t sequence_id, uint32_t layer,
                                uint32_t *sealed_tokens, uint32_t *active_tokens);
 /* Pages referenced by two or more sequences, the references they hold, and the references taken / dropped so far. */

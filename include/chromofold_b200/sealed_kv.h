@@ -141,6 +141,13 @@ typedef struct cf_b200_sealed_attention_desc {
 #define CF_B200_DEVSTAT_PREFIX_MISMATCH 0x20u /* shared_prefix_pages was set but the page-table rows differ */
 #define CF_B200_SHARED_CHUNKS_MAX 16u        /* a shared prefix is cut into at most this many chunks */
 
+/* Test hook for the bounded waits of the attention kernels: from the next launch on, the record of page id
+ * skip_copy_page_id is armed on its barrier but never fetched, and every wait gives up after wait_polls polls (each
+ * poll is bounded to about a microsecond). The warp whose wait runs out raises CF_B200_DEVSTAT_WAIT_EXPIRED and leaves
+ * in an orderly way (copies still in flight are given a bounded chance to land, tensor memory is freed); the launch
+ * ends normally with an incomplete result. (0, 0) switches the hook off and restores the default bound. Process-wide. */
+cf_status cf_b200_test_wait_expiry(uint32_t skip_copy_page_id, uint32_t wait_polls);
+
 /* Host-side structural validation; dereferences nothing on the device
  * (cf_kv_validate_paged_attention_desc, src/cuda/paged_kv_attention.cu:280-299). */
 cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_attention_desc *desc);
@@ -168,8 +175,10 @@ cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_attention_d
  * library image instead: CF_B200_STATIC_WORKSPACE_BYTES per GPU that loads the library, held until exit.
  *   - It calls no cudaMalloc, cudaFree or allocating library routine.
  *   - A batch whose partials cannot fit (seq_count x local query heads x (head_dim + 2) floats, one chunk per
- *     sequence at least) is rejected with CF_ERR_UNSUPPORTED; cf_b200_sealed_attention_static_error() says why.
- *     Larger contexts are fine: chunks grow to fit the array.
+ *     sequence at least) is rejected with CF_ERR_UNSUPPORTED; cf_b200_sealed_attention_static_error() says why and
+ *     how many bytes were needed. Larger contexts are fine: chunks grow to fit the array. A shared_prefix_pages hint
+ *     needs CF_B200_SHARED_CHUNKS_MAX more partials per sequence and query head; when only those do not fit, the
+ *     call is served without the hint (every page then handled per sequence) instead of refused.
  *   - The first call on a device looks up the array's device address; make that call outside any stream capture.
  *   - All calls on a device share the array. Calls that overlap on the GPU race; order them on one stream or with
  *     events. Nothing has to be cleared between calls: each call rewrites what it reads. */

@@ -265,6 +265,108 @@ def test_adapter_round_trip(native, oracle, head_dim, coder, monkeypatch):
     lib.cf_llama_kv_destroy(a)
 
 
+def _read_device(ptr, count, dtype):
+    """`count` elements of raw device memory (not a torch tensor) to the host."""
+    from cuda.bindings import runtime as cudart
+    out = np.zeros(count, dtype)
+    err, = cudart.cudaMemcpy(out.ctypes.data, ptr, out.nbytes, cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+    assert int(err) == 0
+    return out
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_adapter_default_pages_are_the_references_own(native, oracle, bits, head_dim, monkeypatch):
+    """Without CHROMOFOLD_B200_CODER the adapter stores what the reference's adapter stores: kv_bits picks int4 / int8,
+    K quantised per channel and V per token (gpu_fixture::encode_int{4,8}_page). Every page the GPU quantiser made is
+    compared bit for bit — packed words, fp32 scales, block offsets — with the reference's own encoder (oracle/_ref) on
+    the same rows, and attention is compared with a double-precision softmax over the reference's dequantised values
+    plus the raw tail at the reference's 2e-4."""
+    import torch
+    ref = oracle.ref_cpu()
+    if ref is None:
+        pytest.skip("the reference's encoder was not built (oracle/_ref)")
+    monkeypatch.delenv("CHROMOFOLD_B200_CODER", raising=False)
+    lib = native.lib()
+    lib.cf_llama_kv_create.restype = C.c_void_p
+    lib.cf_llama_kv_last_error.restype = C.c_char_p
+    hq, hkv, page, tokens, layers = 14, 2, 32, 70, 2
+    o = LlamaKvOptions()
+    o.struct_size, o.backend = C.sizeof(o), 1
+    o.layer_count, o.kv_head_count, o.query_head_count, o.head_dim, o.page_size, o.gqa_group_size = layers, hkv, hq, head_dim, page, hq // hkv
+    o.kv_bits = bits if bits == 8 else 0                 # anything but 8 means int4 in the reference
+    a = C.c_void_p(lib.cf_llama_kv_create(C.byref(o)))
+    assert a.value
+    rng = np.random.default_rng(9100 + bits)
+    k = rng.standard_normal((layers, hkv, tokens, head_dim)).astype(np.float32)
+    v = rng.standard_normal((layers, hkv, tokens, head_dim)).astype(np.float32)
+    k[0, 0, 40:64, 3] = 0.0                              # an all-zero channel of a page: its scale must be 1
+    p = lambda x: np.ascontiguousarray(x).ctypes.data_as(C.c_void_p)
+    for layer in range(layers):
+        for begin, count in [(0, 50), (50, 20)]:
+            for h in range(hkv):
+                assert lib.cf_llama_kv_append(a, layer, h, begin, p(k[layer, h, begin:begin + count]),
+                                              p(v[layer, h, begin:begin + count]), count, None) == 0, lib.cf_llama_kv_last_error(a)
+    st = LlamaKvStats()
+    assert lib.cf_llama_kv_get_stats(a, C.byref(st)) == 0
+    assert st.sealed_pages == layers * hkv * 2 and st.active_tokens == layers * hkv * 6
+    deq_k, deq_v = k.copy(), v.copy()
+    n = page * head_dim
+    words, nb = (n * bits + 31) // 32, (n + 63) // 64
+    seen = set()
+    for layer in range(layers):
+        for index in range(hkv * 2):
+            pg = DevicePage()
+            assert lib.cf_b200_llama_kv_reference_page(a, layer, index, C.byref(pg)) == 0
+            h, begin = pg.kv_head, pg.token_begin
+            seen.add((layer, h, begin))
+            assert (pg.token_count, pg.head_dim, pg.block_size, pg.fixed_code_length, pg.zero_point) == (page, head_dim, 64, bits, 1 << (bits - 1))
+            kw, vw = np.zeros(words + 1, np.uint32), np.zeros(words + 1, np.uint32)
+            ko, vo = np.zeros(nb, np.int32), np.zeros(nb, np.int32)
+            lut = np.zeros(1 << bits, np.int32)
+            ks, vs = np.zeros(head_dim, np.float32), np.zeros(page, np.float32)
+            dk, dv = np.zeros(n, np.float32), np.zeros(n, np.float32)
+            rows_k, rows_v = k[layer, h, begin:begin + page].ravel(), v[layer, h, begin:begin + page].ravel()
+            assert ref.ref_fixture_encode(p(rows_k), p(rows_v), C.c_uint32(begin), C.c_uint32(page), C.c_uint32(head_dim), C.c_uint32(h),
+                                          C.c_uint32(64), C.c_uint32(bits), p(kw), p(ko), p(vw), p(vo), p(lut), p(ks), p(vs),
+                                          p(dk), p(dv), None) == 0
+            assert np.array_equal(_read_device(pg.k_words, words, np.uint32), kw[:words])
+            assert np.array_equal(_read_device(pg.v_words, words, np.uint32), vw[:words])
+            assert np.array_equal(_read_device(pg.k_scales, head_dim, np.float32).view(np.uint32), ks.view(np.uint32))
+            assert np.array_equal(_read_device(pg.v_scales, page, np.float32).view(np.uint32), vs.view(np.uint32))
+            assert np.array_equal(_read_device(pg.k_block_offsets, nb, np.int32), ko)
+            assert np.array_equal(_read_device(pg.k_lut, 1 << bits, np.int32), lut)
+            deq_k[layer, h, begin:begin + page] = dk.reshape(page, head_dim)
+            deq_v[layer, h, begin:begin + page] = dv.reshape(page, head_dim)
+    assert len(seen) == layers * hkv * 2
+    assert lib.cf_b200_llama_kv_reference_page(a, 0, hkv * 2, C.byref(DevicePage())) == -1
+    nq, window = 3, 40
+    q = rng.standard_normal((nq, hq, head_dim)).astype(np.float32)
+    pos = [tokens - nq + i for i in range(nq)]
+    d_q = _dev(q)
+    for layer in range(layers):
+        out = torch.zeros((nq, hq, head_dim), dtype=torch.float32, device="cuda")
+        assert lib.cf_llama_kv_attention(a, layer, C.c_void_p(d_q.data_ptr()), C.c_void_p(out.data_ptr()), nq, hq, hq // hkv,
+                                         tokens - nq, C.c_float(1.0 / np.sqrt(head_dim)), window, None) == 0, lib.cf_llama_kv_last_error(a)
+        torch.cuda.synchronize()
+        want = _softmax_attention(deq_k[layer], deq_v[layer], q, pos, [max(0, x + 1 - window) for x in pos], 1.0 / np.sqrt(head_dim), hq // hkv)
+        assert np.abs(out.cpu().numpy() - want).max() <= 2e-4
+    # a non-finite row is refused as the reference's quantiser refuses it (kv_gpu_fixture.cpp:13)
+    bad = np.full((26, head_dim), np.nan, np.float32)
+    assert lib.cf_llama_kv_append(a, 0, 0, tokens, p(bad), p(bad), 26, None) == -1
+    assert b"invalid quantization input" in lib.cf_llama_kv_last_error(a)
+    # flush makes a short page of the six active rows, and the cache keeps growing after it, as the reference's does
+    b = C.c_void_p(lib.cf_llama_kv_create(C.byref(o)))
+    for h in range(hkv):
+        assert lib.cf_llama_kv_append(b, 0, h, 0, p(k[0, h, :38]), p(v[0, h, :38]), 38, None) == 0
+    assert lib.cf_llama_kv_flush(b, None) == 0
+    for h in range(hkv):
+        assert lib.cf_llama_kv_append(b, 0, h, 38, p(k[0, h, 38:45]), p(v[0, h, 38:45]), 7, None) == 0, lib.cf_llama_kv_last_error(b)
+    assert lib.cf_llama_kv_get_stats(b, C.byref(st)) == 0 and st.sealed_pages == hkv * 2 and st.active_tokens == hkv * 7
+    lib.cf_llama_kv_destroy(a)
+    lib.cf_llama_kv_destroy(b)
+
+
 @pytest.mark.parametrize("shape", [(64, 32, 64, 16, 64), (300, 128, 40, 512, 64), (97, 80, 97, 33, 100)], ids=str)
 def test_flat_fused_and_dense_attention(native, oracle, shape):
     """cf_kv_attn_fused_async / cf_kv_attn_dense_async (include/chromofold/chromofold.h:81-98) on block-Huffman K / V

@@ -99,7 +99,29 @@ def test_cache_appends_seal_share_speculate_and_attend(native, oracle):
     for layer in range(LAYERS):
         hist[(7, layer)] = [a[:32].copy() for a in hist[(5, layer)]]
     attend([(7, 1)])
-    assert lib.cf_sequence_copy_async(c, i64(5), i64(8), 0, 20, None) == -1 and b"immutable page" in err()
+    # a range that cuts a page keeps the pages wholly inside it, nothing else (src/multisequence_cache.cpp:257-258)
+    assert lib.cf_sequence_copy_async(c, i64(5), i64(8), 0, 20, None) == 0, err()
+    for layer in range(LAYERS):
+        hist[(8, layer)] = [a[:16].copy() for a in hist[(5, layer)]]
+    attend([(8, 0)])
+    # a range that starts later: page 1 and the five active rows, at their old positions 16..36
+    assert lib.cf_sequence_copy_async(c, i64(5), i64(9), 10, 1 << 30, None) == 0, err()
+    for layer in range(LAYERS):
+        hist[(9, layer)] = [a[16:].copy() for a in hist[(5, layer)]]
+    attend([(9, 0), (9, 1)], positions=[36, 36])
+    bad_q = torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda")
+    early = (MsBatchItem * 1)(_item(9, 0, bad_q, bad_q.clone(), 12))
+    assert lib.cf_multisequence_attention_async(c, early, 1, None) == -1 and b"before" in err()
+    assert append(9, 0, 2, torch.float16) == -1              # hist-based begin 21 is not the logical 37
+    # context shift: the whole sequence moves (only its offset changes), part of it cannot, a cut through a page is an error
+    assert lib.cf_sequence_shift_async(c, i64(9), 0, 1 << 30, -16, None) == 0, err()
+    attend([(9, 0), (9, 1)], positions=[20, 20])
+    assert lib.cf_sequence_shift_async(c, i64(9), 0, 1 << 30, -1, None) == -1 and b"negative" in err()
+    assert lib.cf_sequence_shift_async(c, i64(5), 16, 1 << 30, -8, None) == -1 and b"gap" in err()
+    assert lib.cf_sequence_shift_async(c, i64(5), 8, 24, 0, None) == -1 and b"align" in err()
+    assert lib.cf_sequence_shift_async(c, i64(5), 16, 32, 0, None) == 0 and lib.cf_sequence_shift_async(c, i64(5), 500, 600, 7, None) == 0
+    assert append(9, 0, 2, torch.float16) == 0, err()         # after the shift the next position is 21 = its row count
+    attend([(9, 0)], positions=[22])
 
     # speculation: three provisional tokens, one accepted; then a rollback of two more
     spec = lib.cf_sequence_speculation_begin(c, i64(5))
@@ -127,13 +149,13 @@ def test_cache_appends_seal_share_speculate_and_attend(native, oracle):
         hist[(6, layer)] = [a[:32] for a in hist[(6, layer)]]
     attend([(6, 0), (6, 1)])
     assert lib.cf_sequence_remove_async(c, i64(6), i64(4), i64(10), None) == -1                # not a suffix
-    for seq in (5, 6, 7):
+    for seq in (5, 6, 7, 8, 9):
         assert lib.cf_sequence_remove_async(c, i64(seq), i64(-1), i64(-1), None) == 0, err()
     torch.cuda.synchronize()
     assert lib.cf_multisequence_reclaim_async(c, None) == 0 and lib.cf_multisequence_audit(c) == 0
     lib.cf_multisequence_get_counters(c, C.byref(k))
     assert k.active_sequences == 0 and k.pages_pending_reclamation == 0 and k.pages_reclaimed == 2 * LAYERS + 1
-    assert k.invariant_failures == 0 and k.dense_fallback_launches == 0 and k.unsupported_operations == 3
+    assert k.invariant_failures == 0 and k.dense_fallback_launches == 0 and k.unsupported_operations == 4
     assert k.speculative_transactions_committed == 1 and k.speculative_transactions_rolled_back == 1
     lib.cf_multisequence_destroy(c, None)
 

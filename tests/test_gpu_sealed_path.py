@@ -453,3 +453,32 @@ def test_one_process_drives_two_devices(native, oracle):
             results.append([o.cpu().numpy() for o in outs])
     for a, b in zip(*results):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("prefix", [0, 8])
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(native, oracle, prefix):
+    """The bounded waits on the page copies: with the test hook one record is armed on its barrier and never fetched, and
+    the bound is lowered to 2000 polls. The warp that waits for it gives up, raises CF_B200_DEVSTAT_WAIT_EXPIRED and
+    leaves; the launch ends by itself. With the hook off the very next call on the same store gives the right answer
+    (prefix = 8: the same through the shared-prefix kernel, whose leaving path also has to free its tensor memory)."""
+    import torch
+    rng = np.random.default_rng(35)
+    layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=64, coder=CODERS["rans4"],
+                                                           contexts=[160, 160], tails=[0, 0], workspace_bytes=4 << 20)
+    if prefix:
+        layer.copy_sequence(0, 1)      # both entries now name the same ten pages
+    q = torch.from_numpy(rng.standard_normal((2, 4, 128)).astype(np.float16)).cuda()
+    kw = dict(kernel=native.KERNEL_LANES, shared_prefix_pages=prefix)
+    good = layer.attention(q, **kw).cpu().numpy()
+    assert layer.device_status() == 0
+    lib = native.lib()
+    try:
+        assert lib.cf_b200_test_wait_expiry(3, 2000) == 0       # page id 3 = third page of sequence 0
+        layer.attention(q, **kw)
+        torch.cuda.synchronize()
+        assert layer.device_status() & native.DEVSTAT_WAIT_EXPIRED
+    finally:
+        assert lib.cf_b200_test_wait_expiry(0, 0) == 0
+    layer.status.zero_()
+    again = layer.attention(q, **kw).cpu().numpy()
+    assert layer.device_status() == 0 and np.array_equal(again, good)

@@ -57,6 +57,55 @@ def test_no_alloc_entry_matches_the_ordinary_one_twice(native):
         assert layer.device_status() == 0
 
 
+def test_no_alloc_entry_grows_its_units_to_fit_the_fixed_array(native):
+    """The one code path a fixed-size workspace adds: a batch with more (chunk, head) partials at the usual unit size
+    than the array holds. 4 sequences x 9000 pages at 16 pages per unit are 2250 chunks x 8 query heads x 520 B = 9.4 MB
+    against the array's 8 MiB, so the plan kernel has to double its unit size; the result must still equal the ordinary
+    entry point's (which has all the room it wants), on two calls in a row."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, _ = build_sealed_layer(np.array([16 * 9000] * 4), query_heads=8, kv_heads=2, coder="rans4", seed=52)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(53)
+    q = torch.randn((4, 8, 128), generator=g, device="cuda", dtype=torch.float32).half()
+    want = layer.attention(q, kernel=native.KERNEL_LANES, min_pages_per_unit=16).cpu().numpy()
+    got1 = layer.attention_no_alloc(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    got2 = layer.attention_no_alloc(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    assert layer.device_status() == 0
+    for got in (got1, got2):
+        err = np.abs(got - want)
+        assert np.all(err <= 1e-3 + 2e-3 * np.abs(want)), float(err.max())
+    assert np.array_equal(got1, got2)
+
+
+def test_no_alloc_entry_with_a_shared_prefix_hint(native):
+    """The hint needs 16 more partials per sequence and query head. Six sequences that share 24 pages: it fits and the
+    shared-prefix kernel runs. 900 batch entries over the same pages: only the plain partials fit (900 x 8 x 520 B =
+    3.7 MB, x 17 with the hint), so the call is served without the hint instead of refused."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    layer, _ = build_sealed_layer(np.array([16 * 24] + [0] * 5), query_heads=8, kv_heads=2, coder="rans4", seed=54,
+                                  extra_pages_per_sequence=4)
+    for s in range(1, 6):
+        layer.copy_sequence(0, s)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(55)
+    q = torch.randn((900, 8, 128), generator=g, device="cuda", dtype=torch.float32).half()
+    launches = native.lib().cf_b200_shared_prefix_launches
+    launches.restype = C.c_ulonglong
+    before = launches()
+    want = layer.attention(q[:6].contiguous(), kernel=native.KERNEL_LANES).cpu().numpy()
+    got = layer.attention_no_alloc(q[:6].contiguous(), kernel=native.KERNEL_LANES, shared_prefix_pages=24).cpu().numpy()
+    assert launches() == before + 1 and layer.device_status() == 0
+    err = np.abs(got - want)
+    assert np.all(err <= 1e-3 + 2e-3 * np.abs(want)), float(err.max())
+    slots = [i % 6 for i in range(900)]
+    big = layer.attention_no_alloc(q, slots=slots, kernel=native.KERNEL_LANES, shared_prefix_pages=24).cpu().numpy()
+    assert launches() == before + 1 and layer.device_status() == 0          # served, without the shared-prefix kernel
+    err = np.abs(big[:6] - want)                  # entries 0..5 are the six sequences with the same queries as above
+    assert np.all(err <= 1e-3 + 2e-3 * np.abs(want)), float(err.max())
+
+
 def test_no_alloc_entry_refuses_a_batch_that_cannot_fit(native):
     layer, q = _small_layer(native, [16 * 2], seed=60)
     d = layer._attention_desc(q, q.float(), 1, None)
