@@ -263,6 +263,81 @@ def one_process_legs(a, world, contexts, single_gpu_ms):
     return legs
 
 
+def reference_abi_leg(a, contexts, device):
+    """The same decode step through one of the reference's OWN calls: cf_llama_server_execute_batch_async (the llama-server
+    runtime ABI, include/chromofold/llama_server_runtime.h:58-86) over slots filled with cf_llama_server_append_layer_async,
+    with host buffers: every timed step copies the fp32 queries (the only query type that ABI has) from pinned host
+    memory, makes the one call for all sequences, and copies the outputs back. The rows appended are Laplace values; the
+    store behind the ABI quantises them per 16-token tile and seals them on the GPU as they arrive."""
+    import ctypes as C
+    import torch
+    from chromofold_b200 import _native as N
+    from chromofold_b200.workloads import laplace_codes
+    lib = N.lib()
+    lib.cf_llama_server_runtime_create.restype = C.c_void_p
+    lib.cf_llama_server_last_error.restype = C.c_char_p
+    cfg = N.LlamaServerConfig(1, HQ, HKV, D, T, BLOCK, 1 << 20, HQ // HKV, int(str(device).split(":")[-1]), 1, None,
+                              b"benchmark", b"0" * 64)
+    rt = C.c_void_p(lib.cf_llama_server_runtime_create(C.byref(cfg)))
+    if not rt.value:
+        return {"unavailable": "cf_llama_server_runtime_create refused the configuration"}
+    err = lambda: lib.cf_llama_server_last_error(rt).decode()
+    gen = torch.Generator(device=device)
+    gen.manual_seed(11)
+    n = len(contexts)
+    t_build = time.time()
+    for i, ctx in enumerate(contexts):
+        if lib.cf_llama_server_slot_create(rt, C.c_int64(i + 1)) != 0:
+            return {"unavailable": "slot_create: " + err()}
+        for begin in range(0, int(ctx), 4096):
+            tokens = min(4096, int(ctx) - begin)
+            k = laplace_codes((tokens, HKV, D), a.laplace_b, gen, device) * 0.01
+            v = laplace_codes((tokens, HKV, D), a.laplace_b, gen, device) * 0.01
+            if lib.cf_llama_server_append_layer_async(rt, C.c_int64(i + 1), 0, begin, C.c_void_p(k.data_ptr()),
+                                                      C.c_void_p(v.data_ptr()), tokens, None) != 0:
+                return {"unavailable": "append_layer: " + err()}
+    torch.cuda.synchronize()
+    t_build = time.time() - t_build
+    q_pin = torch.randn((n, HQ, D), dtype=torch.float32).pin_memory()
+    out_pin = torch.zeros((n, HQ, D), dtype=torch.float32).pin_memory()
+    q_dev = torch.zeros((n, HQ, D), dtype=torch.float32, device=device)
+    out_dev = torch.zeros((n, HQ, D), dtype=torch.float32, device=device)
+    items = (N.SequenceAttentionItem * n)()
+    for i, ctx in enumerate(contexts):
+        it = items[i]
+        it.sequence_id, it.layer = i + 1, 0
+        it.query = N.TensorView(q_dev[i].data_ptr(), N.F32, 1, HQ, D, HQ * D * 4, D * 4, 4, 0)
+        it.output, it.output_type = out_dev[i].data_ptr(), N.F32
+        it.output_token_stride_bytes, it.output_head_stride_bytes, it.output_element_stride_bytes = HQ * D * 4, D * 4, 4
+        it.query_token_begin, it.softmax_scale, it.causal_window = int(ctx), 1.0 / float(np.sqrt(D)), 0
+    batch = N.LlamaServerBatch(None, 0, C.cast(items, C.c_void_p), n)
+
+    def step():
+        q_dev.copy_(q_pin, non_blocking=True)
+        if lib.cf_llama_server_execute_batch_async(rt, C.byref(batch), C.c_void_p(torch.cuda.current_stream().cuda_stream)) != 0:
+            raise RuntimeError("execute_batch: " + err())
+        out_pin.copy_(out_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.steps
+    tokens = int(np.sum(contexts))
+    result = {"call": "cf_llama_server_execute_batch_async (fp32 queries, one call for the batch)", "value": tokens / ms * 1e3,
+              "unit": UNIT, "ms_per_step": ms, "h2d_bytes_per_step": int(q_pin.numel() * 4), "d2h_bytes_per_step": int(out_pin.numel() * 4),
+              "fill_seconds_append_and_seal": round(t_build, 2), "finite_output": bool(torch.isfinite(out_pin).all().item())}
+    lib.cf_llama_server_shutdown_async(rt, None)
+    lib.cf_llama_server_runtime_destroy(rt, None)
+    return result
+
+
 def cpu_baseline(a, layer, contexts, q_host, out_gpu):
     """The CPU oracle on the same sealed records: restated reference decoders, dequantise, double online softmax,
     all host threads. Also the full-size parity check of the GPU result on the sampled sequences."""
@@ -524,6 +599,13 @@ def main():
         line["other_coders"] = others
     if world > 1:
         dist.destroy_process_group()
+    if world == 1 and not a.no_configs:
+        try:
+            del layer
+        except NameError:
+            pass
+        torch.cuda.empty_cache()
+        line["e2e"]["reference_abi"] = reference_abi_leg(a, contexts, device)
     if not a.no_configs:
         try:
             del layer

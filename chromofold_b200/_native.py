@@ -170,6 +170,29 @@ class MgCounters(C.Structure):
 MG_BY_SEQUENCE, MG_BY_KV_HEAD = 1, 2
 
 
+# ---- the reference's llama-server runtime ABI (include/chromofold_b200/compat_mscache.h, compat_device.h) ----
+class TensorView(C.Structure):       # cf_device_tensor_view
+    _fields_ = [("data", _vp), ("scalar_type", _u32), ("token_count", _u32), ("head_count", _u32), ("head_dim", _u32),
+                ("token_stride_bytes", _u64), ("head_stride_bytes", _u64), ("element_stride_bytes", _u64),
+                ("device_ordinal", C.c_int32)]
+
+
+class SequenceAttentionItem(C.Structure):   # cf_sequence_attention_item == cf_ms_batch_item
+    _fields_ = [("sequence_id", C.c_int64), ("layer", _u32), ("query", TensorView), ("output", _vp), ("output_type", _u32),
+                ("output_token_stride_bytes", _u64), ("output_head_stride_bytes", _u64), ("output_element_stride_bytes", _u64),
+                ("query_token_begin", _u32), ("softmax_scale", _f32), ("causal_window", _u32)]
+
+
+class LlamaServerConfig(C.Structure):
+    _fields_ = [(n, _u32) for n in ("layer_count", "query_head_count", "kv_head_count", "head_dim", "page_size",
+                                    "block_size", "context_window", "gqa_group_size", "cuda_device", "strict_mode")] + [
+        ("evidence_path", C.c_char_p), ("llama_commit", C.c_char_p), ("model_sha256", C.c_char_p)]
+
+
+class LlamaServerBatch(C.Structure):
+    _fields_ = [("tokens", _vp), ("token_item_count", _u32), ("attention_items", _vp), ("attention_item_count", _u32)]
+
+
 class TransferHeader(C.Structure):
     _fields_ = [("magic", _u64), ("version", _u32), ("format_version", _u32), ("kv_head_count", _u32), ("head_dim", _u32),
                 ("page_tokens", _u32), ("block_size", _u32), ("codebook_id", _u32), ("page_count", _u32),

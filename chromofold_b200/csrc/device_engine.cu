@@ -127,7 +127,7 @@ cf_b200_seal_desc core_seal_desc(Core &c, uint32_t layer) {
     d.head_dim = c.cfg.head_dim;
     d.page_tokens = c.tile;
     d.block_size = 64;
-    d.coder = CF_B200_CODER_RANS;
+    d.coder = engine_coder(c.tile * c.cfg.head_dim);
     d.codebook_id = layer;
     d.k_tables = c.tables.ptr + 2 * layer;
     d.v_tables = c.tables.ptr + 2 * layer + 1;

@@ -4,6 +4,7 @@
 #define CHROMOFOLD_B200_ENGINE_COMMON_CUH
 
 #include <algorithm>
+#include <cstdlib>
 #include <stdexcept>
 #include <string>
 
@@ -18,6 +19,24 @@ namespace cfb_engine {
 
 inline void cuda_check(cudaError_t e, const char *what) {
     if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// The coder the stores behind the reference's device ABIs seal with: nibble-split rANS unless CHROMOFOLD_B200_CODER names
+// another (rans | huffman | fixed8 | rans4 | huffman4). The split coders need tiles of a multiple of eight values.
+inline uint32_t engine_coder(uint32_t tile_values) {
+    uint32_t coder = CF_B200_CODER_RANS_SPLIT4;
+    if (const char *env = std::getenv("CHROMOFOLD_B200_CODER")) {
+        const std::string name(env);
+        if (name == "rans") coder = CF_B200_CODER_RANS;
+        else if (name == "huffman") coder = CF_B200_CODER_HUFFMAN;
+        else if (name == "fixed8") coder = CF_B200_CODER_FIXED8;
+        else if (name == "huffman4") coder = CF_B200_CODER_HUFFMAN_SPLIT4;
+    }
+    if (tile_values % 8u != 0) {
+        if (coder == CF_B200_CODER_RANS_SPLIT4) coder = CF_B200_CODER_RANS;
+        if (coder == CF_B200_CODER_HUFFMAN_SPLIT4) coder = CF_B200_CODER_HUFFMAN;
+    }
+    return coder;
 }
 
 inline size_t scalar_bytes(uint32_t type) {

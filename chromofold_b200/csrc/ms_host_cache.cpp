@@ -49,6 +49,7 @@ struct cf_multisequence_cache {
     std::map<int64_t, SequenceState> sequences;
     mutable cf_multisequence_counters counters{};
     cf_speculation_id next_speculation_id = 1;
+    uint64_t mutations_since_audit = 0;
     std::string last_error;
 };
 
@@ -103,8 +104,14 @@ void update_active_peak(cf_multisequence_cache *c) {
     c->counters.active_sequences_peak = std::max(c->counters.active_sequences_peak, c->counters.active_sequences);
 }
 
+// The audit walks every page, so running it after every mutation would make filling a cache quadratic in its size: it
+// runs after every mutation while the cache is small, and once per (pages / 64) mutations beyond that.
 void maybe_audit(cf_multisequence_cache *c) {
     if (!c->config.enable_invariant_auditor) return;
+    uint64_t pages_in_use = 0;
+    cf_b200_ms_arena_stats(c->device, &pages_in_use, nullptr, nullptr, nullptr, nullptr);
+    if (++c->mutations_since_audit * 64u < pages_in_use) return;
+    c->mutations_since_audit = 0;
     ++c->counters.invariant_audits;
     if (cf_ms_cuda_audit(c->device) != 0) {
         ++c->counters.invariant_failures;

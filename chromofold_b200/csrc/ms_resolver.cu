@@ -19,7 +19,10 @@ namespace {
 
 constexpr uint32_t kMaxBatchTokens = 2048;
 
-struct PageRef { uint64_t page_id; int64_t logical_begin; uint32_t tokens; uint32_t first_tile, tiles; };
+struct SharedPage;
+// `page` is the entry of cf_ms_cuda_resolver::pages for page_id (entries of that map do not move; set when the reference
+// is made), so that the per-batch bookkeeping over thousands of pages does not pay a hash look-up per page.
+struct PageRef { uint64_t page_id; int64_t logical_begin; uint32_t tokens; uint32_t first_tile, tiles; SharedPage *page = nullptr; };
 struct SharedPage {
     uint64_t logical_refs = 0, in_flight_refs = 0, resident_bytes = 0, seal_generation = 0;
     bool retired = false;
@@ -287,7 +290,7 @@ uint32_t seal_rows(cf_ms_cuda_resolver *r, Sequence &q, uint32_t layer, const fl
     sd.head_dim = r->config.head_dim;
     sd.page_tokens = r->tile;
     sd.block_size = 64;
-    sd.coder = CF_B200_CODER_RANS;
+    sd.coder = engine_coder(r->tile * r->config.head_dim);
     sd.codebook_id = layer;
     sd.k_tables = r->tables.ptr + 2 * layer;
     sd.v_tables = r->tables.ptr + 2 * layer + 1;
@@ -416,7 +419,7 @@ extern "C" int cf_ms_cuda_publish_page_async(cf_ms_cuda_resolver *r, const cf_ms
         ++r->ref_increments;
         const uint64_t id = r->next_page_id++;
         L.pages.push_back({id, static_cast<int64_t>(d.token_begin), d.token_count, L.tiles, n});
-        r->pages.emplace(id, std::move(page));
+        L.pages.back().page = &r->pages.emplace(id, std::move(page)).first->second;
         L.tiles += n;
         L.sealed_tokens += d.token_count;
         L.partial_last = d.token_count % r->tile != 0;
@@ -524,7 +527,7 @@ extern "C" int cf_b200_ms_seal_active_async(cf_ms_cuda_resolver *r, int64_t id, 
         page.resident_bytes = static_cast<uint64_t>(n) * r->config.kv_head_count * r->max_record_bytes();
         const uint64_t page_id = r->next_page_id++;
         L.pages.push_back({page_id, static_cast<int64_t>(L.sealed_tokens), L.active_count, L.tiles, n});
-        r->pages.emplace(page_id, std::move(page));
+        L.pages.back().page = &r->pages.emplace(page_id, std::move(page)).first->second;
         L.tiles += n;
         L.sealed_tokens += L.active_count;
         L.partial_last = L.active_count % r->tile != 0;
@@ -778,8 +781,10 @@ extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_m
         if (total_rows > kMaxBatchTokens || item_count > 1024) throw std::runtime_error("batch is larger than the resolver's staging buffers");
         for (uint32_t i = 0; i < item_count; ++i) {
             Snapshot snap{items[i].sequence_id, items[i].layer, {}};
-            for (const auto &ref : r->sequences.at(items[i].sequence_id).layers[items[i].layer].pages) {
-                SharedPage &page = r->pages.at(ref.page_id);
+            const auto &refs = r->sequences.at(items[i].sequence_id).layers[items[i].layer].pages;
+            snap.page_ids.reserve(refs.size());
+            for (const auto &ref : refs) {
+                SharedPage &page = ref.page ? *ref.page : r->pages.at(ref.page_id);
                 ++page.in_flight_refs;
                 ++r->counters.in_flight_page_references;
                 snap.page_ids.push_back(ref.page_id);
