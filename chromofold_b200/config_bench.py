@@ -334,10 +334,46 @@ def transfer(a, device):
              "status": [src.device_status(), dst.device_status()]}]
 
 
+def delta_fetch(a, device):
+    """cf_delta_fetch_async (token-id look-up in a reference/delta cluster, src/cuda/delta_apply.cu:30-44; the reference
+    quotes 6.1 G tokens/s on a 2080 Ti): 256 members of 1 Mi tokens each over one base, 2 % of the positions overridden,
+    every token of every member fetched in order. Algorithmic bytes per token: leaf + position in, token out, one base
+    read = 16 B; the binary search over the member's overrides (log2(21 k) = 15 probes) is what the kernel actually pays."""
+    import ctypes as C
+    lib = N.lib()
+    lib.cf_delta_fetch_async.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 7 + [C.c_size_t, C.c_void_p]
+    g = torch.Generator(device=device)
+    g.manual_seed(80)
+    nbase, leaves, per_leaf = 1 << 20, 256, (1 << 20) // 50
+    base = torch.randint(0, 128000, (nbase,), generator=g, device=device, dtype=torch.int32)
+    dpos = torch.stack([torch.sort(torch.randperm(nbase, generator=g, device=device)[:per_leaf])[0] for _ in range(leaves)]).to(torch.int32).reshape(-1)
+    dval = torch.randint(0, 128000, (leaves * per_leaf,), generator=g, device=device, dtype=torch.int32)
+    dstart = (torch.arange(leaves, device=device, dtype=torch.int32) * per_leaf)
+    dlen = torch.full((leaves,), per_leaf, device=device, dtype=torch.int32)
+    count = 1 << 26                                    # 64 members' worth per launch
+    leaf = (torch.arange(count, device=device, dtype=torch.int64) // nbase).to(torch.int32)
+    pos = (torch.arange(count, device=device, dtype=torch.int64) % nbase).to(torch.int32)
+    out = torch.zeros(count, device=device, dtype=torch.int32)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def fetch():
+        N.check("delta_fetch", lib.cf_delta_fetch_async(base.data_ptr(), nbase, dpos.data_ptr(), dval.data_ptr(), dstart.data_ptr(),
+                                                        dlen.data_ptr(), leaf.data_ptr(), pos.data_ptr(), out.data_ptr(), count, stream))
+    ms = _time(fetch, a.steps, a.warmup)
+    want0 = int(base[5].item())
+    hit = (dpos[:per_leaf] == 5).nonzero()
+    if hit.numel():
+        want0 = int(dval[int(hit[0].item())].item())
+    return [{"delta_fetch": "256 members x 1 Mi tokens, 2 % overridden, sequential fetch of 64 Mi tokens per launch",
+             "ms": round(ms, 4), "tokens_per_s": round(count / ms * 1e3), "algorithmic_gbs_at_16_bytes_per_token": round(16 * count / ms / 1e6, 1),
+             "spot_check": int(out[5].item()) == want0}]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, default=0, choices=[0, 3, 4, 5])
     ap.add_argument("--transfer", action="store_true", help="time the pack / unpack kernels of transfer images instead")
+    ap.add_argument("--delta", action="store_true", help="time cf_delta_fetch_async instead")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
@@ -360,7 +396,9 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
-    if a.transfer:
+    if a.delta:
+        rows = delta_fetch(a, device)
+    elif a.transfer:
         rows = transfer(a, device)
     elif a.config == 3 and a.blocks:
         rows = config3_blocks(a, device)

@@ -26,6 +26,7 @@ struct CoreConfig { uint32_t layers, kv_heads, query_heads, head_dim, page_size,
 struct LayerHost {
     uint32_t active_begin = 0, active_count = 0;   // the unsealed page: first token and rows held
     uint32_t sealed_tokens = 0;                    // tokens in sealed tiles
+    uint32_t base = 0;                             // logical position of the layer's first stored token (its first append's)
     uint32_t state = CF_SEAL_ACTIVE_FILLING;
     uint64_t generation = 0;
     bool calibrated = false;
@@ -388,11 +389,15 @@ extern "C" int cf_device_kv_append_async(cf_device_kv_dataplane *p, uint32_t lay
         const uint32_t next = L.active_begin + L.active_count;
         if ((L.active_count != 0 || L.sealed_tokens != 0) && token_begin != next)
             throw std::runtime_error("non-contiguous device token append");
-        if (L.active_count == 0 && L.sealed_tokens == 0 && token_begin != 0)
-            throw std::runtime_error("the first append of a layer must start at token 0");
+        // The reference adopts the caller's position whenever the active page is empty (src/cuda/device_kv_dataplane.cu:160-168).
+        // Sealed records here carry no position, so a layer's tokens stay contiguous: the first append fixes where the
+        // layer starts, and an append after a seal has to continue it (a gap is the one thing that is still refused).
         if (L.active_count + keys->token_count > p->config.page_size)
             throw std::runtime_error("append crosses active page boundary; seal before retry");
-        if (L.active_count == 0 && L.sealed_tokens == 0) L.active_begin = token_begin;
+        if (L.active_count == 0 && L.sealed_tokens == 0) {
+            L.active_begin = token_begin;
+            L.base = token_begin;
+        }
         core_copy_rows(p->core, layer, *keys, *values, L.active_count, static_cast<cudaStream_t>(stream));
         L.active_count += keys->token_count;
         L.state = L.active_count == p->config.page_size ? CF_SEAL_ACTIVE_FULL : CF_SEAL_ACTIVE_FILLING;
@@ -444,7 +449,8 @@ extern "C" int cf_device_kv_attention_async(cf_device_kv_dataplane *p, uint32_t 
     if (!p || layer >= p->core.layers.size() || !query || !output) return -1;
     try {
         const LayerHost &L = p->core.layers[layer];
-        core_attention(p->core, layer, query, CF_B200_F32, output, query_token_count, query_token_begin, softmax_scale,
+        if (query_token_begin < L.base) throw std::runtime_error("query position lies before the layer's first token");
+        core_attention(p->core, layer, query, CF_B200_F32, output, query_token_count, query_token_begin - L.base, softmax_scale,
                        causal_window, static_cast<cudaStream_t>(stream));
         p->counters.compressed_attention_launches++;
         p->counters.sealed_values_consumed += 2ull * L.sealed_tokens * p->config.kv_head_count * p->config.head_dim;

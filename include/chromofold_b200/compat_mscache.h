@@ -8,11 +8,16 @@
  * (compat_ms.h); an append writes the strided rows to the layer's active tail on the GPU and seals the tail into a
  * format-v1 page the moment it holds page_size tokens; attention runs the batched sealed-page kernels.
  * Kept from the reference: thread-safe handle, int 0 / -1 with last_error, ids may be any int64, duplicate ids are
- * refused, appends must be contiguous and never cross a page boundary, pages are immutable (a removal or copy range
- * that cuts a sealed page is refused and counted in unsupported_operations), speculation = begin / commit(accepted) /
- * rollback over the active tail (no page is sealed while a speculation is open), copy shares sealed pages by
- * reference and copies only the active tail, reclaim / audit / counters.
- * Narrower than the reference: a copy range must start at token 0; a shift must move nothing (as in compat_ms.h). */
+ * refused, appends must be contiguous and never cross a page boundary, pages are immutable (a removal that cuts a
+ * sealed page is refused and counted in unsupported_operations), speculation = begin / commit(accepted) / rollback over
+ * the active tail (no page is sealed while a speculation is open), reclaim / audit / counters.
+ * Copy (src/multisequence_cache.cpp:235-292): any range; the destination gets the sealed pages that lie wholly inside
+ * it, shared by reference, and the active tail if it lies wholly inside; a range that starts after token 0 gives a
+ * sequence whose first held token keeps its old position. Shift (:357-380): a range that cuts a sealed page is an
+ * error; a range that covers the whole sequence moves it (positions are not stored in sealed pages, so only the
+ * sequence's offset changes); a range that covers nothing, or a delta of 0, does nothing.
+ * Narrower than the reference: a non-zero shift of only part of a sequence (which would leave a gap inside it) and the
+ * removal of a range that is not a suffix are refused and counted in unsupported_operations. */
 #ifndef CHROMOFOLD_B200_COMPAT_MSCACHE_H
 #define CHROMOFOLD_B200_COMPAT_MSCACHE_H
 

@@ -173,6 +173,23 @@ def test_dataplane_append_seal_attention(native, oracle, dtype):
     want = _expected(oracle, k, v, 2 * page, 32, q, [tokens - 2, tokens - 1], 0, scale, hq // hkv)
     assert np.abs(out.cpu().numpy() - want).max() <= 2e-4
     assert lib.cf_device_kv_clear_async(p, None) == 0
+    # a layer may start anywhere (src/cuda/device_kv_dataplane.cu:160-168): the same rows appended from position 1000 on
+    # give the same answers at positions shifted by 1000; a gap after a seal is still refused
+    def append_at(base, begin, count):
+        kv, vv = view(k_src, begin, count), view(v_src, begin, count)
+        return lib.cf_device_kv_append_async(p, 0, base + begin, C.byref(kv), C.byref(vv), None)
+    assert append_at(1000, 0, 32) == 0 and lib.cf_device_kv_seal_full_pages_async(p, None) == 0
+    assert append_at(1005, 32, 8) == -1 and b"non-contiguous" in lib.cf_device_kv_last_error(p)
+    assert append_at(1000, 32, 32) == 0 and lib.cf_device_kv_seal_full_pages_async(p, None) == 0
+    assert append_at(1000, 64, 7) == 0
+    out2 = torch.zeros_like(out)
+    assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(dq.data_ptr()), C.c_void_p(out2.data_ptr()), nq, 1000 + tokens - nq,
+                                            C.c_float(scale), 0, None) == 0, lib.cf_device_kv_last_error(p)
+    torch.cuda.synchronize()
+    assert np.abs(out2.cpu().numpy() - want).max() <= 2e-4
+    assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(dq.data_ptr()), C.c_void_p(out2.data_ptr()), nq, 10,
+                                            C.c_float(scale), 0, None) == -1 and b"before" in lib.cf_device_kv_last_error(p)
+    assert lib.cf_device_kv_clear_async(p, None) == 0
     assert append(0, 5) == 0                                       # usable after clear
     lib.cf_device_kv_destroy(p, None)
 
