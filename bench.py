@@ -37,7 +37,7 @@ if ROOT not in sys.path:
 # DRAM bytes (read + write) of one attention launch over its algorithmic bytes, from the ncu captures of the batch-16
 # case of the same workload (profiles/lanes_attention_kernel_batch16.md); traffic grows in proportion to the pages read.
 DRAM_TRAFFIC_RATIO = {"rans": 410.8 / 387.9, "huffman": 388.5 / 365.6, "fixed8": 481.9 / 457.0,
-                      "rans4": 410.8 / 387.9, "huffman4": 388.5 / 365.6}
+                      "rans4": 416.4 / 393.3, "huffman4": 393.6 / 370.7}
 METRIC = "sealed-KV decode attn seq-tokens/s"
 UNIT = "seq-tokens/s"
 HQ, HKV, D, T, BLOCK = 32, 8, 128, 16, 64
