@@ -22,7 +22,7 @@ _u32, _u64, _vp, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_float
 
 class CodebookTables(C.Structure):
     _fields_ = [("rans_slot", _u32 * 4096), ("rans_freq", C.c_uint16 * 256), ("rans_cum", C.c_uint16 * 256),
-                ("huff_lut", C.c_uint16 * 4096), ("huff_code", _u32 * 256)]
+                ("huff_lut", C.c_uint16 * 4096), ("huff_code", _u32 * 256), ("rans_enc", _u32 * 2 * 256)]
 
 
 class SealedAttentionDesc(C.Structure):

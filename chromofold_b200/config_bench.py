@@ -334,6 +334,41 @@ def transfer(a, device):
              "status": [src.device_status(), dst.device_status()]}]
 
 
+def seal_rate(a, device, coders=("rans4", "huffman4", "rans", "huffman", "fixed8")):
+    """cf_b200_seal_pages_async alone: 2048 full pages x 8 kv heads per launch (quantise, code both streams, take arena
+    room, publish), Laplace(b=12) tiles resident in HBM, CUDA events around every launch; the same tiles are sealed
+    again and again into fresh page ids. Algorithmic bytes per page-head: 8192 in (binary16 K and V tiles) + the record out."""
+    import ctypes as C
+    from .workloads import laplace_codes, tiles_from_codes
+    rows, n, hkv = [], 2048, 8
+    launches = a.steps + a.warmup + 1
+    for coder in coders:
+        layer, info = build_sealed_layer(np.array([16 * n]), coder=coder, seed=90, device=device, reserve_pages=n * launches)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(91)
+        k = tiles_from_codes(laplace_codes((n, hkv, 16, 128), 12.0, gen, device), 0.005, 0.02, gen)
+        v = tiles_from_codes(laplace_codes((n, hkv, 16, 128), 12.0, gen, device), 0.005, 0.02, gen)
+        tiles = torch.arange(n, dtype=torch.int32, device=device)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def seal():
+            ids = torch.arange(layer.next_page_id, layer.next_page_id + n, dtype=torch.int32, device=device)
+            layer.next_page_id += n
+            d = layer._seal_desc(tiles, ids, None)
+            d.tail_k, d.tail_v = k.data_ptr(), v.data_ptr()
+            N.check("seal_pages", layer.lib.cf_b200_seal_pages_async(C.byref(d), stream))
+        before = int(layer.cursor.item())
+        seal()
+        torch.cuda.synchronize()
+        record_bytes = (int(layer.cursor.item()) - before) * 16
+        ms = _time(seal, a.steps, a.warmup)
+        rows.append({"seal": f"{n} pages x {hkv} kv heads per launch", "coder": coder, "ms_per_launch": round(ms, 4),
+                     "page_heads_per_s": round(n * hkv / ms * 1e3), "tokens_per_s_all_kv_heads": round(n * 16 / ms * 1e3),
+                     "gbs_in_plus_out": round((n * hkv * 8192 + record_bytes) / ms / 1e6, 1),
+                     "record_bytes_per_launch": record_bytes, "device_status": layer.device_status()})
+    return rows
+
+
 def delta_fetch(a, device):
     """cf_delta_fetch_async (token-id look-up in a reference/delta cluster, src/cuda/delta_apply.cu:30-44; the reference
     quotes 6.1 G tokens/s on a 2080 Ti): 256 members of 1 Mi tokens each over one base, 2 % of the positions overridden,
@@ -374,6 +409,7 @@ def main():
     ap.add_argument("--config", type=int, default=0, choices=[0, 3, 4, 5])
     ap.add_argument("--transfer", action="store_true", help="time the pack / unpack kernels of transfer images instead")
     ap.add_argument("--delta", action="store_true", help="time cf_delta_fetch_async instead")
+    ap.add_argument("--seal", action="store_true", help="time cf_b200_seal_pages_async alone, every coder")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
@@ -398,6 +434,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(device))
     if a.delta:
         rows = delta_fetch(a, device)
+    elif a.seal:
+        rows = seal_rate(a, device)
     elif a.transfer:
         rows = transfer(a, device)
     elif a.config == 3 and a.blocks:

@@ -128,6 +128,16 @@ extern "C" cf_status cf_b200_codebook_build(const uint64_t histogram[256], cf_b2
         out->rans_cum[s] = static_cast<uint16_t>(start);
         for (uint32_t k = 0; k < freq[s]; ++k)
             out->rans_slot[start + k] = static_cast<uint32_t>(s) | (freq[s] << 8) | (k << 20);
+        // the sealer's side: division by freq as a multiplication (sealed_page_format.h)
+        if (freq[s] < 2u) {
+            out->rans_enc[s][0] = 0xffffffffu;
+            out->rans_enc[s][1] = (start + 4095u) | (4095u << 13);
+        } else {
+            uint32_t shift = 0;
+            while ((1u << shift) < freq[s]) ++shift;
+            out->rans_enc[s][0] = static_cast<uint32_t>(((1ull << (31u + shift)) + freq[s] - 1u) / freq[s]);
+            out->rans_enc[s][1] = start | ((4096u - freq[s]) << 13) | ((shift - 1u) << 25);
+        }
         start += freq[s];
     }
     if (start != kSlots) return CF_ERR_UNSUPPORTED;

@@ -8,6 +8,8 @@
 // cf_device_common.cuh, takes room in the arena with one atomic add, writes the record and only then the directory
 // entry, so a reader never sees a half-written page and the host is not involved.
 
+#include <type_traits>
+
 #include "cf_device_common.cuh"
 
 namespace cfb {
@@ -97,30 +99,19 @@ __device__ float tile_absmax(const void *base, uint32_t type, uint64_t tile, uin
     return r;
 }
 
-// Per-symbol encoder entry in shared memory: x = freq | cum << 12 | shift << 24, y = ceil(2^(31 + shift) / freq) with
-// shift = ceil(log2 freq). Then floor(v / freq) = (v * y) >> (31 + shift) exactly for every v < 2^31, so the encoder
-// needs no division.
-__device__ __forceinline__ uint2 encoder_entry(uint32_t freq, uint32_t cum) {
-    const uint32_t shift = freq > 1u ? 32u - static_cast<uint32_t>(__clz(freq - 1u)) : 0u;
-    const unsigned long long rcp = ((1ull << (31u + shift)) + freq - 1u) / freq;
-    return make_uint2(freq | (cum << 12) | (shift << 24), static_cast<uint32_t>(rcp));
-}
-
 // Inverse of rans_decode_block: symbols pushed last to first from state L; bytes leave the low end of the state
 // and are written backwards so that they read forwards. Returns the byte count; *state0 gets the final state.
 __device__ uint32_t rans_encode_block(const uint8_t *sym, int count, const uint2 *enc, uint8_t *slot_end, uint32_t *state0) {
     uint32_t x = kRansL;
     uint8_t *p = slot_end;
     for (int j = count - 1; j >= 0; --j) {
-        const uint2 e = enc[sym[j]];
-        const uint32_t f = e.x & 0xfffu, cum = (e.x >> 12) & 0xfffu, shift = e.x >> 24;
-        const uint32_t x_max = f << 19;  // ((L >> 12) << 8) * f
+        const uint2 e = enc[sym[j]];   // rans_enc of the codebook: {rcp, cum | (4096 - f) << 13 | (shift - 1) << 25}
+        const uint32_t cmpl = (e.y >> 13) & 0xfffu, x_max = (4096u - cmpl) << 19;  // ((L >> 12) << 8) * f
         while (x >= x_max) {
             *--p = static_cast<uint8_t>(x & 0xffu);
             x >>= 8;
         }
-        const uint32_t q = static_cast<uint32_t>((static_cast<unsigned long long>(x) * e.y) >> (31u + shift));
-        x = (q << CF_B200_RANS_PROB_BITS) + (x - q * f) + cum;
+        x = x + (e.y & 0x1fffu) + (__umulhi(x, e.x) >> (e.y >> 25)) * cmpl;
     }
     *state0 = x;
     return static_cast<uint32_t>(slot_end - p);
@@ -303,7 +294,7 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     if (rans_family(p.coder))
         for (uint32_t i = tid; i < 512u; i += kSealThreads) {
             const cf_b200_codebook_tables *t = i < 256u ? p.k_tables : p.v_tables;
-            enc[i] = encoder_entry(t->rans_freq[i & 255u], t->rans_cum[i & 255u]);
+            enc[i] = make_uint2(t->rans_enc[i & 255u][0], t->rans_enc[i & 255u][1]);
         }
     __syncthreads();
 
@@ -344,6 +335,281 @@ __global__ void __launch_bounds__(kSealThreads) seal_pages_kernel(SealParams p) 
     if (tid == 0) {
         p.page_dir[static_cast<uint64_t>(p.job_pages[job]) * p.kv_head_count + kv_head] = CF_B200_DIR_ENTRY(offset, units);
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The sealer for the geometry the lane-per-block attention kernel reads: head_dim 128, 16-token pages, 64-symbol
+// blocks (32 blocks per stream). It writes the same records as seal_pages_kernel, byte for byte; what differs is
+// that the geometry is known at compile time, so nothing is divided at run time and a value is loaded once:
+//   * thread t owns the K symbols 16 t .. 16 t + 15 (token t / 8, sixteen channels: two 16-byte loads) and channel t
+//     of V with all its tokens, which are sixteen consecutive symbols of the token-minor V stream: both streams
+//     leave the quantiser as four packed words per thread, and the pair symbols and low-nibble plane words of the
+//     nibble-split coders are made from those registers;
+//   * warp w (0, 1) codes stream w, lane = block: block symbols read as words and indexed statically, block
+//     lengths turned into offsets with a warp scan, bytes moved into the part — no barrier inside the coder;
+//   * the encoder's division is a multiplication by the reciprocal the codebook carries (rans_enc of
+//     cf_b200_codebook_tables): the update of src/cuda/rans.cu:20-22 run backwards is
+//     x + cum + floor(x / f) * (4096 - f).
+#ifndef CFB_SEAL_CTAS
+#define CFB_SEAL_CTAS 8   // resident CTAs per SM the register budget is set for (64 registers per thread)
+#endif
+constexpr uint32_t kFastDim = 128, kFastTokens = 16, kFastBlock = 64, kFastSymbols = 2048, kFastBlocks = 32;
+constexpr uint32_t kFastPart = 2064;   // a part never exceeds the fixed-width 2048 bytes; one unit of slack for the coders
+constexpr uint32_t kFastSlot = 100;    // a block codes into at most 64 * 12 bits + the bytes the start state sheds
+
+// Symbols w[0..kCount/4) (first symbol in byte 0 of w[0]) pushed last to first; bytes written backwards from slot_end.
+template <int kCount>
+__device__ __forceinline__ uint32_t fast_rans_encode(const uint32_t *w, const uint2 *enc, uint8_t *slot_end, uint32_t *state0) {
+    uint32_t x = kRansL;
+    uint8_t *p = slot_end;
+#pragma unroll
+    for (int j = kCount - 1; j >= 0; --j) {
+        const uint2 e = enc[(w[j >> 2] >> (8 * (j & 3))) & 0xffu];
+        const uint32_t cmpl = (e.y >> 13) & 0xfffu, x_max = (4096u - cmpl) << 19;
+        if (x >= x_max) {   // the state is below 2^31 and x_max at least 2^19: two bytes at most
+            *--p = static_cast<uint8_t>(x);
+            x >>= 8;
+            if (x >= x_max) {
+                *--p = static_cast<uint8_t>(x);
+                x >>= 8;
+            }
+        }
+        x = x + (e.y & 0x1fffu) + (__umulhi(x, e.x) >> (e.y >> 25)) * cmpl;
+    }
+    *state0 = x;
+    return static_cast<uint32_t>(slot_end - p);
+}
+
+template <int kCount>
+__device__ __forceinline__ uint32_t fast_huffman_bits(const uint32_t *w, const uint2 *enc) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int j = 0; j < kCount; ++j) bits += enc[(w[j >> 2] >> (8 * (j & 3))) & 0xffu].x >> 16;
+    return bits;
+}
+
+// MSB-first codes of the block appended at bit `bit` of the zeroed word array. Only the first and the last word of a
+// block can be shared with a neighbour; those are OR-ed in atomically, the words between are plain stores.
+template <int kCount>
+__device__ __forceinline__ void fast_huffman_emit(const uint32_t *w, const uint2 *enc, uint32_t *words, uint32_t bit) {
+    uint32_t at = bit >> 5, filled = bit & 31u;
+    unsigned long long acc = 0;
+    bool first = true;
+#pragma unroll
+    for (int j = 0; j < kCount; ++j) {
+        const uint32_t cl = enc[(w[j >> 2] >> (8 * (j & 3))) & 0xffu].x, len = cl >> 16;
+        acc |= static_cast<unsigned long long>(cl & 0xffffu) << (64u - filled - len);
+        filled += len;
+        if (filled >= 32u) {
+            const uint32_t word = static_cast<uint32_t>(acc >> 32);
+            if (first) atomicOr(&words[at], word);
+            else words[at] = word;
+            first = false;
+            ++at;
+            acc <<= 32;
+            filled -= 32u;
+        }
+    }
+    if (filled) atomicOr(&words[at], static_cast<uint32_t>(acc >> 32));
+}
+
+// The coder of one stream, run by one warp (lane = block). Returns the part's size; *coder_out = the coder stored.
+template <int kCount>
+__device__ __forceinline__ uint32_t fast_code_stream(uint32_t coder, const uint8_t *src, const uint8_t *sym, const uint2 *enc,
+                                                     uint8_t *part, uint8_t *slot_end, uint32_t lane, uint32_t *coder_out) {
+    constexpr bool kSplit = kCount == 32;
+    const bool rans = rans_family(coder);
+    const uint32_t head = rans ? 6u * kFastBlocks : 2u * kFastBlocks, plane = kSplit ? 4u * 8u * kFastBlocks : 0u;
+    uint32_t w[kCount / 4];
+#pragma unroll
+    for (int i = 0; i < kCount / 16; ++i) {
+        const uint4 q = reinterpret_cast<const uint4 *>(src + kCount * lane)[i];
+        w[4 * i] = q.x, w[4 * i + 1] = q.y, w[4 * i + 2] = q.z, w[4 * i + 3] = q.w;
+    }
+    uint32_t state = 0;
+    const uint32_t len = rans ? fast_rans_encode<kCount>(w, enc, slot_end, &state) : fast_huffman_bits<kCount>(w, enc);
+    uint32_t incl = len;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= static_cast<uint32_t>(d)) incl += t;
+    }
+    const uint32_t off = incl - len, run = __shfl_sync(0xffffffffu, incl, 31);
+    const uint32_t bytes = align_up_u32(head + plane + (rans ? run : 4u * ((run + 31u) / 32u)), 16u);
+    if (bytes > kFastSymbols) {   // would not shrink: fixed-width words, most significant byte first, over the whole part
+        for (uint32_t i = lane; i < kFastSymbols / 4u; i += 32u)
+            reinterpret_cast<uint32_t *>(part)[i] = __byte_perm(reinterpret_cast<const uint32_t *>(sym)[i], 0u, 0x0123);
+        *coder_out = CF_B200_CODER_FIXED8;
+        return kFastSymbols;
+    }
+    if (rans) {
+        reinterpret_cast<uint32_t *>(part)[lane] = state;
+        reinterpret_cast<uint16_t *>(part + 4u * kFastBlocks)[lane] = static_cast<uint16_t>(off);
+        const uint8_t *from = slot_end - len;
+        uint8_t *to = part + head + plane + off;
+        for (uint32_t i = 0; i < len; ++i) to[i] = from[i];
+    } else {
+        reinterpret_cast<uint16_t *>(part)[lane] = static_cast<uint16_t>(off);
+        fast_huffman_emit<kCount>(w, enc, reinterpret_cast<uint32_t *>(part + head + plane), off);
+    }
+    *coder_out = coder;
+    return bytes;
+}
+
+template <bool kF32>
+__global__ void __launch_bounds__(kSealThreads, CFB_SEAL_CTAS) seal_pages_fast_kernel(SealParams p) {
+    __shared__ __align__(16) uint8_t s_sym[2][kFastSymbols];
+    __shared__ __align__(16) uint8_t s_pair[2][kFastSymbols / 2];
+    __shared__ __align__(16) uint8_t s_part[2][kFastPart];
+    __shared__ __align__(8) uint2 s_enc[2][256];
+    __shared__ __align__(4) uint8_t s_scratch[2 * kFastBlocks][kFastSlot];
+    __shared__ uint32_t s_red[8], s_coder[2], s_bytes[2];
+    __shared__ unsigned long long s_offset;
+    using Scalar = typename std::conditional<kF32, float, __half>::type;
+
+    const uint32_t job = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t kv_head = p.job_heads ? p.job_heads[job] : blockIdx.y;
+    const uint32_t slot = p.job_slots[job];
+    const uint32_t rows = p.job_tokens ? min(p.job_tokens[job], kFastTokens) : kFastTokens;
+    const uint64_t tile = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * p.tail_capacity +
+                           (p.job_rows ? p.job_rows[job] : 0u)) * kFastDim;
+    const Scalar *tk = static_cast<const Scalar *>(p.tail_k) + tile, *tv = static_cast<const Scalar *>(p.tail_v) + tile;
+    const bool split = split_coder(p.coder), rans = rans_family(p.coder);
+
+    // values: K row-wise (sixteen channels of token tid / 8), V column-wise (channel tid, every token)
+    float kf[16], vf[16];
+    const bool k_live = (tid >> 3) < rows;
+    if constexpr (kF32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 q = k_live ? reinterpret_cast<const float4 *>(tk + 16u * tid)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            kf[4 * i] = q.x, kf[4 * i + 1] = q.y, kf[4 * i + 2] = q.z, kf[4 * i + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 q = k_live ? reinterpret_cast<const uint4 *>(tk + 16u * tid)[i] : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t h[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h[j]));
+                kf[8 * i + 2 * j] = f.x, kf[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t t = 0; t < kFastTokens; ++t) {
+        if constexpr (kF32) vf[t] = t < rows ? tv[t * kFastDim + tid] : 0.f;
+        else vf[t] = t < rows ? __half2float(tv[t * kFastDim + tid]) : 0.f;
+    }
+    // absmax and the finite check at once: the magnitude bits of inf and NaN are above those of every finite value
+    uint32_t km = 0u, vm = 0u;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        km = max(km, __float_as_uint(kf[i]) & 0x7fffffffu);
+        vm = max(vm, __float_as_uint(vf[i]) & 0x7fffffffu);
+    }
+    km = __reduce_max_sync(0xffffffffu, km);
+    vm = __reduce_max_sync(0xffffffffu, vm);
+    if (lane == 0) {
+        s_red[warp] = km;
+        s_red[4 + warp] = vm;
+    }
+    for (uint32_t i = tid; i < 2u * kFastPart / 16u; i += kSealThreads) reinterpret_cast<uint4 *>(&s_part[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (uint32_t i = tid; i < 512u; i += kSealThreads) {
+        const cf_b200_codebook_tables *t = i < 256u ? p.k_tables : p.v_tables;
+        (&s_enc[0][0])[i] = rans ? make_uint2(t->rans_enc[i & 255u][0], t->rans_enc[i & 255u][1]) : make_uint2(t->huff_code[i & 255u], 0u);
+    }
+    __syncthreads();
+    km = max(max(s_red[0], s_red[1]), max(s_red[2], s_red[3]));
+    vm = max(max(s_red[4], s_red[5]), max(s_red[6], s_red[7]));
+    if (rows == 0 || km >= 0x7f800000u || vm >= 0x7f800000u) {  // finite validation failed: nothing is published
+        if (tid == 0 && p.status) atomicOr(p.status, CF_B200_DEVSTAT_NONFINITE);
+        return;
+    }
+    const uint16_t k_bits = scale_bits_from_absmax(__uint_as_float(km)), v_bits = scale_bits_from_absmax(__uint_as_float(vm));
+    const float k_scale = __half2float(__ushort_as_half(k_bits)), v_scale = __half2float(__ushort_as_half(v_bits));
+    uint32_t kw[4], vw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t a = 0u, b = 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            a |= (k_live ? quantise_symbol(kf[4 * i + j], k_scale) : static_cast<uint32_t>(kZero)) << (8 * j);
+            b |= (static_cast<uint32_t>(4 * i + j) < rows ? quantise_symbol(vf[4 * i + j], v_scale) : static_cast<uint32_t>(kZero)) << (8 * j);
+        }
+        kw[i] = a, vw[i] = b;
+    }
+    reinterpret_cast<uint4 *>(&s_sym[0][0])[tid] = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+    reinterpret_cast<uint4 *>(&s_sym[1][0])[tid] = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+    if (split) {
+        // pair symbol = hi(s[2k]) << 4 | hi(s[2k+1]): with h = w & 0xf0f0f0f0, bytes 0 and 2 of h | h >> 12
+        // plane word = low nibbles of eight symbols: first four in the low nibbles of the bytes, next four in the high ones
+        const uint32_t head = rans ? 6u * kFastBlocks : 2u * kFastBlocks, b = tid >> 2, j0 = 2u * (tid & 3u);
+#pragma unroll
+        for (int s2 = 0; s2 < 2; ++s2) {
+            const uint32_t *w = s2 ? vw : kw;
+            uint32_t t[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t h = w[i] & 0xf0f0f0f0u;
+                t[i] = h | (h >> 12);
+            }
+            reinterpret_cast<uint2 *>(&s_pair[s2][0])[tid] = make_uint2(__byte_perm(t[0], t[1], 0x6420), __byte_perm(t[2], t[3], 0x6420));
+            uint32_t *plane = reinterpret_cast<uint32_t *>(&s_part[s2][head]);
+            plane[j0 * kFastBlocks + b] = (w[0] & 0x0f0f0f0fu) | ((w[1] & 0x0f0f0f0fu) << 4);
+            plane[(j0 + 1u) * kFastBlocks + b] = (w[2] & 0x0f0f0f0fu) | ((w[3] & 0x0f0f0f0fu) << 4);
+        }
+    }
+    __syncthreads();
+
+    if (warp < 2u) {
+        uint32_t coder = p.coder, bytes = kFastSymbols;
+        uint8_t *slot_end = &s_scratch[warp * kFastBlocks + lane][kFastSlot];
+        if (p.coder == CF_B200_CODER_FIXED8) {
+            for (uint32_t i = lane; i < kFastSymbols / 4u; i += 32u)
+                reinterpret_cast<uint32_t *>(&s_part[warp][0])[i] = __byte_perm(reinterpret_cast<const uint32_t *>(&s_sym[warp][0])[i], 0u, 0x0123);
+        } else if (split) {
+            bytes = fast_code_stream<32>(p.coder, &s_pair[warp][0], &s_sym[warp][0], &s_enc[warp][0], &s_part[warp][0], slot_end, lane, &coder);
+        } else {
+            bytes = fast_code_stream<64>(p.coder, &s_sym[warp][0], &s_sym[warp][0], &s_enc[warp][0], &s_part[warp][0], slot_end, lane, &coder);
+        }
+        if (lane == 0) {
+            s_coder[warp] = coder;
+            s_bytes[warp] = bytes;
+        }
+    }
+    __syncthreads();
+    const uint32_t k_bytes = s_bytes[0], v_bytes = s_bytes[1];
+    const uint32_t units = 1u + k_bytes / 16u + v_bytes / 16u;
+    if (tid == 0) s_offset = atomicAdd(p.cursor, static_cast<unsigned long long>(units));
+    __syncthreads();
+    const unsigned long long offset = s_offset;
+    if (offset + units > p.arena_units) {
+        if (tid == 0 && p.status) atomicOr(p.status, CF_B200_DEVSTAT_ARENA_FULL);
+        return;
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(p.arena + 16ull * offset);
+    if (tid == 0) {
+        cf_b200_record_header h;
+        h.k_part_units = static_cast<uint16_t>(k_bytes / 16u);
+        h.v_part_units = static_cast<uint16_t>(v_bytes / 16u);
+        h.k_coder = static_cast<uint8_t>(s_coder[0]);
+        h.v_coder = static_cast<uint8_t>(s_coder[1]);
+        h.token_count = static_cast<uint16_t>(rows);
+        h.k_scale_f16 = k_bits;
+        h.v_scale_f16 = v_bits;
+        h.codebook_id = static_cast<uint16_t>(p.codebook_id);
+        h.flags = 0;
+        h.version = CF_B200_FORMAT_VERSION;
+        dst[0] = *reinterpret_cast<const uint4 *>(&h);
+    }
+    for (uint32_t i = tid; i < k_bytes / 16u; i += kSealThreads) dst[1 + i] = reinterpret_cast<const uint4 *>(&s_part[0][0])[i];
+    for (uint32_t i = tid; i < v_bytes / 16u; i += kSealThreads)
+        dst[1 + k_bytes / 16u + i] = reinterpret_cast<const uint4 *>(&s_part[1][0])[i];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) p.page_dir[static_cast<uint64_t>(p.job_pages[job]) * p.kv_head_count + kv_head] = CF_B200_DIR_ENTRY(offset, units);
 }
 
 __global__ void __launch_bounds__(kSealThreads) histogram_kernel(SealParams p, unsigned long long *hist_k,
@@ -453,6 +719,13 @@ extern "C" cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *d, void *
         return CF_ERR_INVALID_ARGUMENT;   // memory of another GPU: the call must be made with that GPU current
     cfb::SealParams p;
     cfb::fill(d, &p);
+    if (d->head_dim == cfb::kFastDim && d->page_tokens == cfb::kFastTokens && d->block_size == cfb::kFastBlock &&
+        ((reinterpret_cast<uintptr_t>(d->tail_k) | reinterpret_cast<uintptr_t>(d->tail_v)) & 15u) == 0) {
+        const dim3 grid(d->job_count, d->job_heads ? 1u : d->kv_head_count);
+        if (p.tail_type == CF_B200_F32) cfb::seal_pages_fast_kernel<true><<<grid, cfb::kSealThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        else cfb::seal_pages_fast_kernel<false><<<grid, cfb::kSealThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+    }
     const cfb::SealSmem lay = cfb::seal_smem(p.symbols, p.nblocks, p.block_size);
     if (cudaFuncSetAttribute(cfb::seal_pages_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(lay.total)) != cudaSuccess)

@@ -103,13 +103,17 @@ typedef struct cf_b200_record_header {
  *     freq >= 1 and freq <= 3841, so 12 bits hold it.
  *   rans_freq / rans_cum are the plain tables of rans.cu:17-18 (the sealer needs them).
  *   huff_lut[look] = sym | (len << 8), block_huffman_device.cuh:12-19.
- *   huff_code[sym] = code | (len << 16), the sealer's side of the same code. */
+ *   huff_code[sym] = code | (len << 16), the sealer's side of the same code.
+ *   rans_enc[sym] = { rcp, cum | (4096 - freq) << 13 | (shift - 1) << 25 } with shift = ceil(log2 freq) and
+ *     rcp = ceil(2^(31 + shift) / freq): the sealer's division-free step, floor(x / freq) = umulhi(x, rcp) >> (shift - 1)
+ *     for x < 2^31 and x' = x + cum + floor(x / freq) * (4096 - freq). freq = 1: { 2^32 - 1, (cum + 4095) | 4095 << 13 }. */
 typedef struct cf_b200_codebook_tables {
     uint32_t rans_slot[4096];
     uint16_t rans_freq[256];
     uint16_t rans_cum[256];
     uint16_t huff_lut[4096];
     uint32_t huff_code[256];
+    uint32_t rans_enc[256][2];
 } cf_b200_codebook_tables;
 
 #ifdef __cplusplus

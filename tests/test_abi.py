@@ -33,7 +33,7 @@ def test_every_declared_symbol_is_exported(native):
 
 def test_struct_sizes_match_the_headers(native):
     # computed by hand from the header layouts; a mismatch means the ctypes mirror drifted
-    assert C.sizeof(native.CodebookTables) == 4096 * 4 + 256 * 2 + 256 * 2 + 4096 * 2 + 256 * 4
+    assert C.sizeof(native.CodebookTables) == 4096 * 4 + 256 * 2 + 256 * 2 + 4096 * 2 + 256 * 4 + 256 * 8
     assert C.sizeof(native.SealedAttentionDesc) == 216
     assert C.sizeof(native.SealDesc) == 160
     assert C.sizeof(native.DenseAttentionDesc) == 120
@@ -93,3 +93,14 @@ def test_codebook_tables_match_oracle(native, oracle):
         assert np.array_equal(np.ctypeslib.as_array(t.huff_lut).astype(np.int32), cb.np("lut"))
         code = np.ctypeslib.as_array(t.huff_code)
         assert np.array_equal(code & 0xFFFF, cb.np("hcode")) and np.array_equal(code >> 16, cb.np("hlen"))
+        # the sealer's reciprocals divide exactly: floor(x / f) for states at both ends of the range and around multiples of f
+        enc = np.ctypeslib.as_array(t.rans_enc).astype(np.uint64)
+        f, cum = cb.np("freq").astype(np.uint64), cb.np("cum").astype(np.uint64)
+        assert np.array_equal((enc[:, 1] >> np.uint64(13)) & np.uint64(0xFFF), np.uint64(4096) - f)
+        for x in (1 << 23, (1 << 31) - 1, 12345678, (1 << 27) + 5):
+            xs = np.concatenate([np.full(256, x, np.uint64), (np.uint64(x) // f) * f, (np.uint64(x) // f) * f - np.uint64(1)])
+            e = np.tile(enc, (3, 1))
+            q = ((xs * e[:, 0]) >> np.uint64(32)) >> (e[:, 1] >> np.uint64(25))
+            nxt = xs + (e[:, 1] & np.uint64(0x1FFF)) + q * ((e[:, 1] >> np.uint64(13)) & np.uint64(0xFFF))
+            ff, cc = np.tile(f, 3), np.tile(cum, 3)
+            assert np.array_equal(nxt, ((xs // ff) << np.uint64(12)) + xs % ff + cc)
