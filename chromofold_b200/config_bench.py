@@ -75,25 +75,27 @@ def config3(a, device, check=None, coders=("rans", "huffman", "rans4", "huffman4
 
 def config3_blocks(a, device, check=None):
     """Block-size dial of the coder crossover: what 128- and 256-symbol blocks save in bytes (fewer per-block states
-    and offsets) and what they cost (they run on the any-geometry kernel; the lane-per-block kernel is built for
-    32 blocks of 64 symbols per stream)."""
-    contexts = np.full(8, 8192)
+    and offsets) and what they cost in the lane-per-block kernel (16 / 8 blocks per stream are decoded into a
+    shared-memory tile first; with 8 blocks half the lanes of a warp have no block to decode). Batch 32 x 8192 as in
+    the p sweep."""
+    contexts = np.full(32, 8192)
     results = []
     for p in (0.1, 0.4):
-        for coder in ("rans", "huffman"):
+        for coder in ("rans", "huffman", "rans4", "huffman4"):
             for block in (64, 128, 256):
                 layer, info = build_sealed_layer(contexts, coder=coder, dist=("geometric", p), seed=40, device=device,
                                                  block_size=block)
-                q = _queries(8, 32, 41, device)
-                out = torch.zeros((8, 32, 128), dtype=torch.float32, device=device)
-                ms = _time(lambda: layer.attention(q, out=out), max(a.steps // 3, 3), 2)
+                q = _queries(32, 32, 41, device)
+                out = torch.zeros((32, 32, 128), dtype=torch.float32, device=device)
+                ms = _time(lambda: layer.attention(q, out=out), a.steps, a.warmup)
                 results.append({"config": 3, "p": p, "coder": coder, "block_size": block,
                                 "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
                                 "bits_per_code_stored": round(info["bytes_per_seq_token"] * 8 / 2048, 3),
                                 "h0_bits_per_code": round(info["h0_bits_k"], 3),
-                                "kernel": "lanes" if block == 64 else "generic", "ms_per_step": round(ms, 4),
+                                "ms_per_step": round(ms, 4),
                                 "seq_tokens_per_s": round(int(contexts.sum()) / ms * 1e3),
                                 "device_status": layer.device_status()})
+                _checked(results[-1], check, layer, q, out, rows=[0, 31])
                 del layer, info
                 torch.cuda.empty_cache()
     return results

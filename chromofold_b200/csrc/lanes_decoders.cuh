@@ -1,7 +1,8 @@
 // lanes_decoders.cuh — pieces shared by the lane-per-block kernels (sealed_attention_lanes.cu,
 // sealed_attention_prefix.cu): PTX wrappers (bulk async copy + mbarrier with bounded waits, mma.sync), the exact
-// symbol -> binary16 conversion, and the per-lane block decoders for the geometry head_dim 128, page_tokens 16,
-// block_size 64 (32 blocks per stream, lane l decodes block l).
+// symbol -> binary16 conversion, and the per-lane block decoders for streams of 2048 symbols (head_dim 128, page_tokens
+// 16) cut into NB blocks: NB = 32 (block_size 64, lane l decodes block l: the layout every kernel is built around),
+// 16 or 8 (block_size 128 / 256, decoded into a shared-memory tile first, see sealed_attention_lanes.cu).
 #ifndef CHROMOFOLD_B200_LANES_DECODERS_CUH
 #define CHROMOFOLD_B200_LANES_DECODERS_CUH
 
@@ -87,8 +88,10 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t e0, uint32_t e1, uin
 // Both entropy decoders are written without branches so that the K chain and the V chain of a lane interleave in
 // one straight instruction stream. A 64-bit window holds the upcoming stream bits, top aligned; it is reloaded from
 // shared memory once per quad (four symbols), which is as often as it can run dry.
-struct RansLane {
+template <int NB>
+struct RansLaneT {
     static constexpr bool kWholeQuads = false;
+    static constexpr uint32_t kHead = (6u * NB + 3u) / 4u * 4u;   // u32 state0[NB] | u16 byte_off[NB]
     static constexpr int kSymbolsPerReload = 4;   // a symbol takes at most two bytes; the window holds eight
     uint32_t x, whi, wlo, used;   // state; window (next byte = top byte of whi); bits taken since the reload
     uint32_t pos;                 // shared-memory byte address of the first byte not yet taken at the last reload
@@ -98,8 +101,8 @@ struct RansLane {
     // 12-byte window, which stays inside the warp's own shared memory (part_offsets_ok reports the bad table).
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint32_t *slot_table) {
         x = reinterpret_cast<const uint32_t *>(part)[lane];
-        const uint32_t payload = part_bytes > 192u ? part_bytes - 192u : 0u;
-        pos = smem_addr(part) + 192u + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 128)[lane]), payload);
+        const uint32_t payload = part_bytes > kHead ? part_bytes - kHead : 0u;
+        pos = smem_addr(part) + kHead + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane]), payload);
         table = smem_addr(slot_table);
         used = 0;
     }
@@ -136,6 +139,7 @@ struct RansLane {
         return pack_low_bytes(e0, e1, e2, e3);
     }
 };
+using RansLane = RansLaneT<32>;
 
 // Low nibbles of the four symbols of a quad (in the low nibble of each byte of w; its high nibbles are ignored) under
 // the two pair symbols that hold their high nibbles (table entries, pair A:B in the low byte): four symbols, first in byte 0.
@@ -148,44 +152,50 @@ __device__ __forceinline__ uint32_t merge_split_quad(uint32_t e0, uint32_t e1, u
 
 // Nibble-split rANS (CF_B200_CODER_RANS_SPLIT4): the low nibble of every symbol is stored raw in a lane-interleaved
 // plane, and the rANS stream codes PAIRS of high nibbles (pair symbol = hi(2k) << 4 | hi(2k + 1)), so a block of 64
-// symbols is 32 steps of the same recurrence. Part layout: u32 state0[32] | u16 byte_off[32] | u32 lo[8][32] | bytes;
-// lo[j][l] holds the low nibbles of symbols 8j..8j+7 of block l: symbol 8j + i at bits 8i..8i+3 for i < 4, symbol
-// 8j + 4 + i at bits 8i+4..8i+7.
-struct RansSplitLane : RansLane {
+// symbols is 32 steps of the same recurrence. Part layout: u32 state0[NB] | u16 byte_off[NB] | u32 lo[2048/NB/8][NB] |
+// bytes; lo[j][l] holds the low nibbles of symbols 8j..8j+7 of block l: symbol 8j + i at bits 8i..8i+3 for i < 4,
+// symbol 8j + 4 + i at bits 8i+4..8i+7. The plane is 1024 bytes whatever the block size.
+template <int NB>
+struct RansSplitLaneT : RansLaneT<NB> {
+    using Base = RansLaneT<NB>;
+    using Base::x; using Base::pos; using Base::table; using Base::used; using Base::kHead;
     static constexpr bool kWholeQuads = true;   // callers ask for a quad at a time (the window is refilled inside)
     static constexpr uint32_t kPlaneBytes = 1024u;
     uint32_t lo;   // shared-memory byte address of lo[0][lane]
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint32_t *slot_table) {
         x = reinterpret_cast<const uint32_t *>(part)[lane];
-        const uint32_t payload = part_bytes > 192u + kPlaneBytes ? part_bytes - 192u - kPlaneBytes : 0u;
-        lo = smem_addr(part) + 192u + 4u * lane;
-        pos = smem_addr(part) + 192u + kPlaneBytes + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 128)[lane]), payload);
+        const uint32_t payload = part_bytes > kHead + kPlaneBytes ? part_bytes - kHead - kPlaneBytes : 0u;
+        lo = smem_addr(part) + kHead + 4u * lane;
+        pos = smem_addr(part) + kHead + kPlaneBytes + min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane]), payload);
         table = smem_addr(slot_table);
         used = 0;
     }
     __device__ __forceinline__ uint32_t lo_word(int j) const {
         uint32_t w;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 128u * j));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 4u * NB * j));
         return w;
     }
     __device__ __forceinline__ uint32_t quad(int q) {   // one stream on its own (mixed-coder records)
-        if ((q & 1) == 0) reload();
-        const uint32_t e0 = symbol(), e1 = symbol();
+        if ((q & 1) == 0) Base::reload();
+        const uint32_t e0 = Base::symbol(), e1 = Base::symbol();
         return merge_split_quad(e0, e1, lo_word(q >> 1) >> (4 * (q & 1)));
     }
 };
+using RansSplitLane = RansSplitLaneT<32>;
 
-struct HuffLane {
+template <int NB>
+struct HuffLaneT {
     static constexpr bool kWholeQuads = false;
+    static constexpr uint32_t kHead = (2u * NB + 3u) / 4u * 4u;   // u16 bit_off[NB]
     static constexpr int kSymbolsPerReload = 5;   // a code takes at most 12 bits; the window holds 64
     uint32_t whi, wlo, used;   // window of upcoming bits, MSB first; bits taken since the reload
     uint32_t words, bit;       // shared-memory address of the payload words; bit position at the last reload
     uint32_t table;
     // Start offset clamped to the part as in RansLane::open; a block takes at most 64 * 12 bits plus one window.
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint16_t *lut) {
-        const uint32_t payload_bits = part_bytes > 64u ? (part_bytes - 64u) * 8u : 0u;
+        const uint32_t payload_bits = part_bytes > kHead ? (part_bytes - kHead) * 8u : 0u;
         bit = min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part)[lane]), payload_bits);
-        words = smem_addr(part) + 64u;
+        words = smem_addr(part) + kHead;
         table = smem_addr(lut);
         used = 0;
     }
@@ -216,43 +226,50 @@ struct HuffLane {
         return pack_low_bytes(e0, e1, e2, e3);
     }
 };
+using HuffLane = HuffLaneT<32>;
 
-// Nibble-split Huffman (CF_B200_CODER_HUFFMAN_SPLIT4): u16 bit_off[32] | u32 lo[8][32] | words; one LUT hit = a pair.
-struct HuffSplitLane : HuffLane {
+// Nibble-split Huffman (CF_B200_CODER_HUFFMAN_SPLIT4): u16 bit_off[NB] | u32 lo[2048/NB/8][NB] | words; one LUT hit = a pair.
+template <int NB>
+struct HuffSplitLaneT : HuffLaneT<NB> {
+    using Base = HuffLaneT<NB>;
+    using Base::bit; using Base::words; using Base::table; using Base::used; using Base::kHead;
     static constexpr bool kWholeQuads = true;
     static constexpr uint32_t kPlaneBytes = 1024u;
     uint32_t lo;
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint16_t *lut) {
-        const uint32_t payload_bits = part_bytes > 64u + kPlaneBytes ? (part_bytes - 64u - kPlaneBytes) * 8u : 0u;
+        const uint32_t payload_bits = part_bytes > kHead + kPlaneBytes ? (part_bytes - kHead - kPlaneBytes) * 8u : 0u;
         bit = min(static_cast<uint32_t>(reinterpret_cast<const uint16_t *>(part)[lane]), payload_bits);
-        lo = smem_addr(part) + 64u + 4u * lane;
-        words = smem_addr(part) + 64u + kPlaneBytes;
+        lo = smem_addr(part) + kHead + 4u * lane;
+        words = smem_addr(part) + kHead + kPlaneBytes;
         table = smem_addr(lut);
         used = 0;
     }
     __device__ __forceinline__ uint32_t lo_word(int j) const {
         uint32_t w;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 128u * j));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(lo + 4u * NB * j));
         return w;
     }
     __device__ __forceinline__ uint32_t quad(int q) {
-        if ((q & 1) == 0) reload();   // four pair symbols take at most 48 bits
-        const uint32_t e0 = symbol(), e1 = symbol();
+        if ((q & 1) == 0) Base::reload();   // four pair symbols take at most 48 bits
+        const uint32_t e0 = Base::symbol(), e1 = Base::symbol();
         return merge_split_quad(e0, e1, lo_word(q >> 1) >> (4 * (q & 1)));
     }
 };
+using HuffSplitLane = HuffSplitLaneT<32>;
 
-struct FixedLane {
+template <int NB>
+struct FixedLaneT {
     static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
     static constexpr int kSymbolsPerReload = 4;
     const uint32_t *words;
     // A fixed-width part is 2048 bytes at a 16-byte aligned offset of at most 16 + 2048 into the stage: always inside it.
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t, uint32_t lane) {
-        words = reinterpret_cast<const uint32_t *>(part) + 16u * lane;
+        words = reinterpret_cast<const uint32_t *>(part) + (512u / NB) * lane;
     }
     // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
     __device__ __forceinline__ uint32_t quad(int) { return __byte_perm(*words++, 0u, 0x0123); }
 };
+using FixedLane = FixedLaneT<32>;
 
 // Coding tables into shared memory, once per CTA: [k rANS slots | v rANS slots | k Huffman LUT | v Huffman LUT].
 // Slot entries are re-packed for RansLane::symbol(): sym | (slot - cum) << 8 | freq << 20.
@@ -285,15 +302,17 @@ __device__ __forceinline__ bool record_header_ok(const uint4 &hv, uint64_t dir_e
 // The block table of a staged part against the part's length: lane l checks the start of block l. The reference
 // validates its descriptors on the host before the launch (src/cuda/paged_kv_attention.cu:280-299); records here are
 // written by the sealer, by import or by unpack, so the check runs where the table is read.
+template <int NB = 32>
 __device__ __forceinline__ bool part_offsets_ok(const uint8_t *part, uint32_t coder, uint32_t part_bytes, uint32_t lane) {
+    constexpr uint32_t kRansHead = RansLaneT<NB>::kHead, kHuffHead = HuffLaneT<NB>::kHead;
     if (coder == CF_B200_CODER_RANS)
-        return part_bytes >= 192u && reinterpret_cast<const uint16_t *>(part + 128)[lane] <= part_bytes - 192u;
+        return part_bytes >= kRansHead && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead;
     if (coder == CF_B200_CODER_HUFFMAN)
-        return part_bytes >= 64u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - 64u) * 8u;
+        return part_bytes >= kHuffHead && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - kHuffHead) * 8u;
     if (coder == CF_B200_CODER_RANS_SPLIT4)
-        return part_bytes >= 192u + 1024u && reinterpret_cast<const uint16_t *>(part + 128)[lane] <= part_bytes - 192u - 1024u;
+        return part_bytes >= kRansHead + 1024u && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead - 1024u;
     if (coder == CF_B200_CODER_HUFFMAN_SPLIT4)
-        return part_bytes >= 64u + 1024u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - 64u - 1024u) * 8u;
+        return part_bytes >= kHuffHead + 1024u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - kHuffHead - 1024u) * 8u;
     return part_bytes == 2048u;
 }
 

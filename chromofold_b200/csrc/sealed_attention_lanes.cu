@@ -1,6 +1,7 @@
 // sealed_attention_lanes.cu — the hot kernel: decode-step attention over sealed pages for the geometry
 // head_dim 128, page_tokens 16, block_size 64 (32 blocks per stream). Query groups larger than 4 heads per kv head are
-// served four heads at a time (the unit is then decoded once per sub-group).
+// served four heads at a time (the unit is then decoded once per sub-group). Blocks of 128 and 256 symbols (16 and 8
+// blocks per stream) run the same kernel behind a staging step, see stage_blocks below.
 //
 // What it computes is what src/cuda/paged_kv_attention.cu:183-276 computes for one query token; how it runs is new:
 //
@@ -22,6 +23,7 @@
 
 #include <math_constants.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "lanes_decoders.cuh"
@@ -39,8 +41,9 @@ using namespace lanes;
 #endif
 // Warps per CTA (one CTA per SM): the four-head kernel and the kernels whose query rows live in shared memory (they
 // need 2.3 KB more per warp) are sized separately.
-template <int NG> constexpr int kWarpsOf = NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
-template <int NG> constexpr int kThreadsOf = kWarpsOf<NG> * 32;
+// The kernels for larger blocks (NB = 16 or 8 blocks per stream) keep a 5 KB symbol tile per warp and run fewer warps.
+template <int NG, int NB = 32> constexpr int kWarpsOf = NB != 32 ? (NG == 1 ? 12 : 10) : NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
+template <int NG, int NB = 32> constexpr int kThreadsOf = kWarpsOf<NG, NB> * 32;
 // Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
 template <int NG>
 struct UnitState {
@@ -189,9 +192,58 @@ __device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
     }
 }
 
+// ---- blocks of 128 / 256 symbols (NB = 16 / 8 blocks per stream) ------------------------------------------------
+// The attention part of the kernel wants lane l to hold symbols 64 l .. 64 l + 63 of both streams. With larger blocks
+// there are fewer blocks than lanes, so the decode is laid out differently and its result re-dealt through a
+// per-warp tile in shared memory: lanes 0 .. NB-1 decode the K blocks while lanes 16 .. 16+NB-1 decode the V blocks
+// (at NB = 16 every lane is busy and a page costs as many decoder steps per lane as with 64-symbol blocks; at NB = 8
+// half the lanes idle), every four quads leave as one 16-byte store, and after a warp barrier each lane reads its
+// sixteen K quads and sixteen V quads back with 16-byte loads. A tile row is one lane's 64 symbols plus 16 bytes
+// of padding (row stride 80 bytes), which keeps both the stores and the loads off each other's banks; the V tile
+// sits 16 bytes further for the same reason.
+constexpr uint32_t kTileRow = 80u, kTileStream = 32u * kTileRow, kTileBytes = 2u * kTileStream + 32u;
+
+template <int NB, class Lane>
+__device__ __forceinline__ void stage_with(Lane &d, uint32_t block, uint8_t *tile) {
+    constexpr int kQuads = 512 / NB;   // per block
+#pragma unroll 2
+    for (int q = 0; q < kQuads; q += 4) {
+        const uint32_t a = d.quad(q), b = d.quad(q + 1), c = d.quad(q + 2), e = d.quad(q + 3);
+        const uint32_t at = block * kQuads + q;   // quad index in the stream: row = at / 16, column = at % 16
+        *reinterpret_cast<uint4 *>(tile + (at >> 4) * kTileRow + (at & 15u) * 4u) = make_uint4(a, b, c, e);
+    }
+}
+
+// One lane's share: block `block` of the part, whatever its coder.
+template <int NB>
+__device__ __forceinline__ void stage_blocks(const uint8_t *part, uint32_t part_bytes, uint32_t coder, uint32_t block,
+                                             const uint32_t *slot_table, const uint16_t *lut, uint8_t *tile) {
+    if (coder == CF_B200_CODER_RANS_SPLIT4) {
+        RansSplitLaneT<NB> d;
+        d.open(part, part_bytes, block, slot_table);
+        stage_with<NB>(d, block, tile);
+    } else if (coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
+        HuffSplitLaneT<NB> d;
+        d.open(part, part_bytes, block, lut);
+        stage_with<NB>(d, block, tile);
+    } else if (coder == CF_B200_CODER_RANS) {
+        RansLaneT<NB> d;
+        d.open(part, part_bytes, block, slot_table);
+        stage_with<NB>(d, block, tile);
+    } else if (coder == CF_B200_CODER_HUFFMAN) {
+        HuffLaneT<NB> d;
+        d.open(part, part_bytes, block, lut);
+        stage_with<NB>(d, block, tile);
+    } else {
+        FixedLaneT<NB> d;
+        d.open(part, part_bytes, block);
+        stage_with<NB>(d, block, tile);
+    }
+}
+
 // Shared memory of one warp: two record stages, the softmax scratch, two mbarriers and (NG = 2) the query rows.
 //   scratch: P rows fp16 high halves [4 NG][16] | low halves [4 NG][16] | 128 zero bytes | alpha[4 NG]
-template <int NG>
+template <int NG, int NB = 32>
 struct WarpLayout {
     static constexpr uint32_t kPBytes = 4 * NG * 16 * 2;
     static constexpr uint32_t kPLo = 2 * kStageBytes + kPBytes;
@@ -200,19 +252,22 @@ struct WarpLayout {
     static constexpr uint32_t kBars = kAlpha + 4 * NG * 4;
     static constexpr uint32_t kQRows = kBars + 32;
     static constexpr uint32_t kQRowWords = 36;
-    static constexpr uint32_t kBytes = (kQRows + (NG == 2 ? 16 * kQRowWords * 4 : 0) + 15u) / 16u * 16u;
-    static constexpr uint32_t kSmem = kTableBytes + kWarpsOf<NG> * kBytes;
+    static constexpr uint32_t kTile = (kQRows + (NG == 2 ? 16 * kQRowWords * 4 : 0) + 15u) / 16u * 16u;   // NB != 32 only
+    static constexpr uint32_t kBytes = kTile + (NB != 32 ? kTileBytes : 0u);
+    static constexpr uint32_t kSmem = kTableBytes + kWarpsOf<NG, NB> * kBytes;
 };
-static_assert(WarpLayout<1>::kSmem <= 232448 && WarpLayout<2>::kSmem <= 232448, "a CTA has 227 KB of shared memory");
+static_assert(WarpLayout<1>::kSmem <= 232448 && WarpLayout<2>::kSmem <= 232448 && WarpLayout<1, 16>::kSmem <= 232448 &&
+              WarpLayout<2, 16>::kSmem <= 232448, "a CTA has 227 KB of shared memory");
 
 // kSplitQ (with NG = 2): the queries are fp32. A pass serves four heads; their rows are split into binary16(q) and
 // binary16(q - binary16(q)), stored as the rows of group 0 and group 1, the two score fragments are added, and one
 // softmax / P V follows: the scores equal fp32-query scores to 2^-22 relative, at the cost of a second score mma.
-template <int NG, int kMode = kAttend, bool kSplitQ = false>
-__global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(AttentionParams p) {
+template <int NG, int kMode = kAttend, bool kSplitQ = false, int NB = 32>
+__global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(AttentionParams p) {
     constexpr bool kProbe = kMode != kAttend;
     static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
-    using L = WarpLayout<NG>;
+    static_assert(NB == 32 || NB == 16 || NB == 8, "blocks per stream");
+    using L = WarpLayout<NG, NB>;
     using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
     constexpr uint32_t kPassHeads = kSplitQ ? 4u : 4u * NG;
     constexpr int NS = kSplitQ ? 1 : NG;   // groups that go through softmax and P V
@@ -231,7 +286,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_mem + L::kBars);
     uint32_t *q_rows = reinterpret_cast<uint32_t *>(warp_mem + L::kQRows);     // NG == 2 only
 
-    load_tables(smem, p, tid, kThreadsOf<NG>);   // coding tables: once per CTA
+    load_tables(smem, p, tid, kThreadsOf<NG, NB>);   // coding tables: once per CTA
     reinterpret_cast<uint32_t *>(warp_mem + L::kZero)[lane] = 0u;   // the zero row inactive lanes read their fragments from
     if (lane == 0) {
         mbar_init(&bars[0], 1);
@@ -387,9 +442,15 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
                 const uint32_t k_coder = hv.y & 0xffu, v_coder = (hv.y >> 8) & 0xffu, token_count = hv.y >> 16;
                 const uint8_t *k_part = rec + 16;
                 const uint8_t *v_part = k_part + k_bytes;
-                const bool good = record_header_ok(hv, entry_cur, p.codebook_id) &&
-                                  __all_sync(0xffffffffu, part_offsets_ok(k_part, k_coder, k_bytes, lane) &&
-                                                              part_offsets_ok(v_part, v_coder, v_bytes, lane));
+                bool offsets_ok;
+                if constexpr (NB == 32) {
+                    offsets_ok = part_offsets_ok(k_part, k_coder, k_bytes, lane) && part_offsets_ok(v_part, v_coder, v_bytes, lane);
+                } else {   // lanes 0..NB-1 hold the K blocks, lanes 16..16+NB-1 the V blocks
+                    const bool mine = (lane & 15u) < static_cast<uint32_t>(NB);
+                    offsets_ok = !mine || (lane < 16u ? part_offsets_ok<NB>(k_part, k_coder, k_bytes, lane)
+                                                      : part_offsets_ok<NB>(v_part, v_coder, v_bytes, lane - 16u));
+                }
+                const bool good = record_header_ok(hv, entry_cur, p.codebook_id) && __all_sync(0xffffffffu, offsets_ok);
                 uint32_t dump_page = 0u;
                 if constexpr (kMode == kDump) dump_page = table_row[page_begin + i];
                 if (!good || dump_page >= p.dump_pages) {   // dump_pages is 1 outside the dump mode
@@ -404,7 +465,34 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
 #pragma unroll
                     for (int n = 0; n < NG; ++n) u.score[n][0] = u.score[n][1] = u.score[n][2] = u.score[n][3] = 0.0f;
 
-                    if (k_coder == CF_B200_CODER_RANS_SPLIT4 && v_coder == CF_B200_CODER_RANS_SPLIT4) {
+                    if constexpr (NB != 32) {
+                        uint8_t *tile = warp_mem + L::kTile;
+                        if ((lane & 15u) < static_cast<uint32_t>(NB)) {
+                            if (lane < 16u) stage_blocks<NB>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
+                            else stage_blocks<NB>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStream + 16u);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint4 kk = *reinterpret_cast<const uint4 *>(tile + lane * kTileRow + 16u * c);
+                            const uint4 vv = *reinterpret_cast<const uint4 *>(tile + kTileStream + 16u + lane * kTileRow + 16u * c);
+                            const uint32_t kq[4] = {kk.x, kk.y, kk.z, kk.w}, vq[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int q = 4 * c + j;
+                                if constexpr (kMode == kFold) {
+                                    u.vq[0] ^= kq[j] ^ vq[j];
+                                } else if constexpr (kMode == kDump) {
+                                    u.dump[q] = kq[j];
+                                    u.dump[512 + q] = vq[j];
+                                } else {
+                                    u.vq[q] = vq[j];
+                                    score_quad(u, qs, q, kq[j]);
+                                }
+                            }
+                        }
+                        if constexpr (kProbe) __syncwarp();   // the tile is rewritten for the next page
+                    } else if (k_coder == CF_B200_CODER_RANS_SPLIT4 && v_coder == CF_B200_CODER_RANS_SPLIT4) {
                         RansSplitLane k, v;
                         k.open(k_part, k_bytes, lane, k_slot);
                         v.open(v_part, v_bytes, lane, v_slot);
@@ -589,43 +677,52 @@ __global__ void __launch_bounds__(kThreadsOf<NG>, 1) lanes_attention_kernel(Atte
 }  // namespace
 
 bool lanes_kernel_supports(const AttentionParams &p) {
-    return p.head_dim == 128 && p.page_tokens == 16 && p.block_size == 64 && p.group >= 1 && p.group <= 16 &&
+    return p.head_dim == 128 && p.page_tokens == 16 && (p.block_size == 64 || p.block_size == 128 || p.block_size == 256) &&
+           p.group >= 1 && p.group <= 16 &&
            (p.query_type == CF_B200_F16 || p.query_type == CF_B200_F32);
 }
 
 // Query groups of up to four heads per kv head run the four-head kernel; larger groups run the eight-head one, which
 // decodes a page once for eight query heads (its query operands live in shared memory instead of registers). fp32
 // queries (the reference's own ABIs pass nothing else) run the split-query kernel, four heads per pass.
+namespace {
+
+template <int NG, int kMode, bool kSplitQ, int NB>
+cudaError_t launch_one(const AttentionParams &p, int sm_count, cudaStream_t stream) {
+    static std::atomic<uint64_t> configured{0};   // bit = device ordinal
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (device & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        e = cudaFuncSetAttribute(lanes_attention_kernel<NG, kMode, kSplitQ, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(WarpLayout<NG, NB>::kSmem));
+        if (e != cudaSuccess) return e;
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    lanes_attention_kernel<NG, kMode, kSplitQ, NB><<<sm_count, kThreadsOf<NG, NB>, WarpLayout<NG, NB>::kSmem, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+template <int NB>
+cudaError_t launch_for_blocks(const AttentionParams &p, int sm_count, cudaStream_t stream) {
+    if (p.decode_probe == 2u) return launch_one<1, kDump, false, NB>(p, sm_count, stream);
+    if (p.decode_probe) return launch_one<1, kFold, false, NB>(p, sm_count, stream);
+    if (p.query_type == CF_B200_F32) return launch_one<2, kAttend, true, NB>(p, sm_count, stream);
+    if (p.group <= 4) return launch_one<1, kAttend, false, NB>(p, sm_count, stream);
+    return launch_one<2, kAttend, false, NB>(p, sm_count, stream);
+}
+
+}  // namespace
+
 cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream) {
     static LauncherState table[64];
     cudaError_t e;
     LauncherState *state = launcher_state(table, &e);
     if (!state) return e;
-    const int sm_count = state->sm_count;
-    if (!state->configured) {
-        e = cudaFuncSetAttribute(lanes_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(WarpLayout<1>::kSmem));
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<1, kFold>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(WarpLayout<1>::kSmem));
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<1, kDump>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(WarpLayout<1>::kSmem));
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(WarpLayout<2>::kSmem));
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(lanes_attention_kernel<2, kAttend, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(WarpLayout<2>::kSmem));
-        if (e != cudaSuccess) return e;
-        state->configured = true;
-    }
-    if (p.decode_probe == 2u) lanes_attention_kernel<1, kDump><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
-    else if (p.decode_probe) lanes_attention_kernel<1, kFold><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
-    else if (p.query_type == CF_B200_F32) lanes_attention_kernel<2, kAttend, true><<<sm_count, kThreadsOf<2>, WarpLayout<2>::kSmem, stream>>>(p);
-    else if (p.group <= 4) lanes_attention_kernel<1><<<sm_count, kThreadsOf<1>, WarpLayout<1>::kSmem, stream>>>(p);
-    else lanes_attention_kernel<2><<<sm_count, kThreadsOf<2>, WarpLayout<2>::kSmem, stream>>>(p);
-    return cudaPeekAtLastError();
+    if (p.block_size == 128) return launch_for_blocks<16>(p, state->sm_count, stream);
+    if (p.block_size == 256) return launch_for_blocks<8>(p, state->sm_count, stream);
+    return launch_for_blocks<32>(p, state->sm_count, stream);
 }
 
 }  // namespace cfb

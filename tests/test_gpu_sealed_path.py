@@ -91,7 +91,7 @@ def test_gpu_decode_is_bit_exact(native, oracle, coder):
     assert layer.device_status() == 0
 
 
-def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None):
+def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None, block=64):
     """Every record of `sequences` (page ids in import order from 1): the dumped K and V symbols against the symbols
     the CPU quantiser produced and against what the restated reference decoders recover from the record's bytes."""
     pid, checked = 1, 0
@@ -100,7 +100,7 @@ def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None):
             if s in sequences:
                 for h, rec in enumerate(page):
                     want_k, want_v = host.symbols[s][p][h]
-                    back_k, back_v = oracle.open_record(rec, 128, 16, 64, kcb, vcb)
+                    back_k, back_v = oracle.open_record(rec, 128, 16, block, kcb, vcb)
                     assert np.array_equal(back_k, want_k) and np.array_equal(back_v, want_v)
                     assert np.array_equal(dump[pid, h, 0], want_k), ("K", s, p, h)
                     assert np.array_equal(dump[pid, h, 1], want_v), ("V", s, p, h)
@@ -127,6 +127,43 @@ def test_lane_decoders_yield_exactly_the_oracle_symbols(native, oracle, coder):
     dump = layer.dump_lane_decoders(q).cpu().numpy()
     assert layer.device_status() == 0
     assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}) == 2 * (3 + 1 + 3 + 10)
+
+
+@pytest.mark.parametrize("block", [128, 256])
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_larger_blocks_are_decoded_exactly_and_attend_like_the_oracle(native, oracle, coder, block):
+    """Blocks of 128 / 256 symbols (16 / 8 blocks per stream) run the lane-per-block kernel behind its staging step:
+    the symbols the lanes hold after the tile pass equal the oracle's, symbol for symbol (ragged last page and a
+    mixed-coder record included), and attention agrees with the oracle for fp16 queries in groups of four and eight
+    heads and for fp32 queries."""
+    import torch
+    rng = np.random.default_rng(31)
+    contexts, tails = [48, 16, 37, 160], [3, 0, 0, 9]
+    layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=16, hkv=2, d=128, t=16, block=block,
+                                                           coder=CODERS[coder], contexts=contexts, tails=tails,
+                                                           noisy_k_pages={(3, 1), (3, 7)})
+    if coder != "fixed8":
+        rec = host.records[3][1][0]
+        assert rec[4] == CODERS["fixed8"] and rec[5] == CODERS[coder]
+    q = rng.standard_normal((4, 16, 128)).astype(np.float16)
+    dump = layer.dump_lane_decoders(torch.from_numpy(q).cuda()).cpu().numpy()
+    assert layer.device_status() == 0
+    assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}, block=block) == 2 * (3 + 1 + 3 + 10)
+    want = _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q, 16, stride)
+    for qt in (torch.from_numpy(q).cuda(), torch.from_numpy(q.astype(np.float32)).cuda()):
+        got = layer.attention(qt, kernel=native.KERNEL_LANES, min_pages_per_unit=2).cpu().numpy()
+        assert layer.device_status() == 0
+        ok, err = attention_close(got, want)
+        assert ok, f"max abs error {err}"
+    # groups of four heads (the register-resident query operands) and the decode-only probe
+    layer4, host4, kcb4, vcb4, tk4, tv4, stride4 = _build(native, oracle, rng, hq=4, hkv=2, d=128, t=16, block=block,
+                                                          coder=CODERS[coder], contexts=[80, 33], tails=[0, 5])
+    q4 = rng.standard_normal((2, 4, 128)).astype(np.float16)
+    want4 = _oracle_attention(oracle, host4, kcb4, vcb4, [80, 33], [0, 5], tk4, tv4, q4, 4, stride4)
+    got4 = layer4.attention(torch.from_numpy(q4).cuda(), kernel=native.KERNEL_LANES).cpu().numpy()
+    assert layer4.device_status() == 0
+    ok, err = attention_close(got4, want4)
+    assert ok, f"max abs error {err}"
 
 
 @pytest.mark.parametrize("coder", list(CODERS))
