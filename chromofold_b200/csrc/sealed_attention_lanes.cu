@@ -41,8 +41,12 @@ using namespace lanes;
 #endif
 // Warps per CTA (one CTA per SM): the four-head kernel and the kernels whose query rows live in shared memory (they
 // need 2.3 KB more per warp) are sized separately.
-// The kernels for larger blocks (NB = 16 or 8 blocks per stream) keep a 5 KB symbol tile per warp and run fewer warps.
-template <int NG, int NB = 32> constexpr int kWarpsOf = NB != 32 ? (NG == 1 ? 12 : 10) : NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
+// The kernels for larger blocks (NB = 16 or 8 blocks per stream) keep a 5 KB symbol tile per warp instead of a second
+// record stage: a record is free for the next copy as soon as it has been decoded into the tile.
+#ifndef CFB_LANES_WARPS_BIG
+#define CFB_LANES_WARPS_BIG 16
+#endif
+template <int NG, int NB = 32> constexpr int kWarpsOf = NB != 32 ? (NG == 1 ? CFB_LANES_WARPS_BIG : 14) : NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
 template <int NG, int NB = 32> constexpr int kThreadsOf = kWarpsOf<NG, NB> * 32;
 // Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
 template <int NG>
@@ -246,7 +250,8 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *part, uint32_t part_
 template <int NG, int NB = 32>
 struct WarpLayout {
     static constexpr uint32_t kPBytes = 4 * NG * 16 * 2;
-    static constexpr uint32_t kPLo = 2 * kStageBytes + kPBytes;
+    static constexpr uint32_t kStages = NB == 32 ? 2 : 1;
+    static constexpr uint32_t kPLo = kStages * kStageBytes + kPBytes;
     static constexpr uint32_t kZero = kPLo + kPBytes;
     static constexpr uint32_t kAlpha = kZero + 128;
     static constexpr uint32_t kBars = kAlpha + 4 * NG * 4;
@@ -279,7 +284,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint8_t *warp_mem = smem + kTableBytes + warp * L::kBytes;
-    __half *p_rows = reinterpret_cast<__half *>(warp_mem + 2 * kStageBytes);   // [4 NG][16] fp16(p)
+    __half *p_rows = reinterpret_cast<__half *>(warp_mem + L::kStages * kStageBytes);   // [4 NG][16] fp16(p)
     __half *p_rows_lo = reinterpret_cast<__half *>(warp_mem + L::kPLo);        // [4 NG][16] fp16(p - fp16(p))
     const __half *zero_row = reinterpret_cast<const __half *>(warp_mem + L::kZero);
     float *alpha_s = reinterpret_cast<float *>(warp_mem + L::kAlpha);          // [4 NG]
@@ -420,11 +425,14 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
         bool alive = true;
 
         for (uint32_t i = 0; i < n_pages; ++i) {
-            const uint32_t st = i & 1u;
+            const uint32_t st = NB == 32 ? (i & 1u) : 0u;
             uint64_t entry_after = 0ull;
+            bool next_issued = NB == 32;
             if (i + 1 < n_pages) {
-                __syncwarp();  // every lane is done with the other stage (page i-1)
-                issue(st ^ 1u, entry_next);
+                if constexpr (NB == 32) {
+                    __syncwarp();  // every lane is done with the other stage (page i-1)
+                    issue(st ^ 1u, entry_next);
+                }
                 if (i + 2 < n_pages) entry_after = load_entry(page_begin + i + 2);
             }
             if (!entry_ok(entry_cur)) {
@@ -472,6 +480,8 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                             else stage_blocks<NB>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStream + 16u);
                         }
                         __syncwarp();
+                        if (i + 1 < n_pages) issue(0u, entry_next);   // the record is decoded: its stage takes the next one
+                        next_issued = true;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const uint4 kk = *reinterpret_cast<const uint4 *>(tile + lane * kTileRow + 16u * c);
@@ -618,13 +628,17 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                     }   // !kProbe
                 }
             }
+            if (!next_issued && i + 1 < n_pages) {   // single stage, page skipped: nobody reads the stage any more
+                __syncwarp();
+                issue(0u, entry_next);
+            }
             entry_cur = entry_next;
             entry_next = entry_after;
         }
         if (!alive) {
             // give the copies still in flight a bounded chance to land before this warp's buffers go away
             mbar_wait(&bars[0], phase_bits & 1u, p.wait_polls);
-            mbar_wait(&bars[1], (phase_bits >> 1) & 1u, p.wait_polls);
+            if constexpr (L::kStages == 2) mbar_wait(&bars[1], (phase_bits >> 1) & 1u, p.wait_polls);
             return;
         }
 
