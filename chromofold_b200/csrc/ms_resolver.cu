@@ -31,6 +31,7 @@ struct SharedPage {
 };
 struct LayerSeq {
     std::vector<PageRef> pages;
+    uint32_t pins = 0;   // unreleased snapshots that still hold this list as "its first n pages" (see Snapshot)
     uint32_t sealed_tokens = 0, tiles = 0;
     bool partial_last = false;
     uint32_t active_begin = 0, active_count = 0;
@@ -43,8 +44,13 @@ struct Sequence {
     uint64_t topology_generation = 0;
     std::vector<LayerSeq> layers;
 };
-struct Snapshot { int64_t sequence_id; uint32_t layer; std::vector<uint64_t> page_ids; };
-struct Pending { Snapshot snapshot; cudaEvent_t event = nullptr; };
+// What a batch item reads: the first page_count pages of a (sequence, layer) list at the time of the launch. Taking it
+// costs nothing per page: the list is pinned (LayerSeq::pins) and only when the sequence is about to DROP pages while a
+// snapshot is still out are the page ids written down and each page's in-flight count raised (materialise_pins), so
+// a decode step over long sequences does not walk tens of thousands of page objects on the host. A page list only
+// grows at its end between drops, which is what makes "the first n pages" a stable name.
+struct Snapshot { int64_t sequence_id; uint32_t layer; uint32_t page_count; bool lazy; std::vector<uint64_t> page_ids; };
+struct Pending { std::vector<Snapshot> snapshots; cudaEvent_t event = nullptr; };   // one event per batch
 
 // Reference int4 page (all kv heads): value = (nibble - 8) * scale[flat / block_size], flat = (token*Hkv + head)*D + d,
 // two nibbles per byte, low nibble first (src/cuda/device_kv_seal_attention.cu:106-118). Written as fp32 rows into
@@ -217,13 +223,49 @@ struct cf_ms_cuda_resolver {
     }
 
     void release_snapshot(const Snapshot &snap) {
-        for (uint64_t id : snap.page_ids) {
-            auto p = pages.find(id);
-            if (p == pages.end() || p->second.in_flight_refs == 0) throw std::runtime_error("snapshot reference underflow");
-            --p->second.in_flight_refs;
-            --counters.in_flight_page_references;
+        if (snap.lazy) {   // never written down: the list it pinned is still there (a drop would have materialised it)
+            auto q = sequences.find(snap.sequence_id);
+            if (q == sequences.end() || snap.layer >= q->second.layers.size() || q->second.layers[snap.layer].pins == 0)
+                throw std::runtime_error("snapshot reference underflow");
+            --q->second.layers[snap.layer].pins;
+            counters.in_flight_page_references -= snap.page_count;
+        } else {
+            for (uint64_t id : snap.page_ids) {
+                auto p = pages.find(id);
+                if (p == pages.end() || p->second.in_flight_refs == 0) throw std::runtime_error("snapshot reference underflow");
+                --p->second.in_flight_refs;
+                --counters.in_flight_page_references;
+            }
         }
         ++counters.snapshots_released;
+    }
+
+    // Before (sequence, layer) drops pages: every snapshot that still names its list lazily gets its page ids written
+    // down and its pages' in-flight counts raised, so that reclamation waits for the launches that read them.
+    // `building` = snapshots of a batch that is being assembled (not yet in `pending`).
+    void materialise_pins(Sequence &q, uint32_t layer, std::vector<Snapshot> *building = nullptr) {
+        LayerSeq &L = q.layers[layer];
+        if (L.pins == 0) return;
+        auto write_down = [&](Snapshot &snap) {
+            if (!snap.lazy || snap.sequence_id != q.id || snap.layer != layer) return;
+            snap.page_ids.reserve(snap.page_count);
+            for (uint32_t i = 0; i < snap.page_count && i < L.pages.size(); ++i) {
+                PageRef &ref = L.pages[i];
+                SharedPage &page = ref.page ? *ref.page : pages.at(ref.page_id);
+                ++page.in_flight_refs;
+                snap.page_ids.push_back(ref.page_id);
+            }
+            counters.in_flight_page_references -= snap.page_count - snap.page_ids.size();
+            snap.lazy = false;
+            --L.pins;
+        };
+        for (Pending &p : pending)
+            for (Snapshot &snap : p.snapshots) write_down(snap);
+        if (building)
+            for (Snapshot &snap : *building) write_down(snap);
+    }
+    void materialise_pins(Sequence &q) {
+        for (uint32_t layer = 0; layer < q.layers.size(); ++layer) materialise_pins(q, layer);
     }
 };
 
@@ -565,6 +607,7 @@ extern "C" int cf_b200_ms_truncate_async(cf_ms_cuda_resolver *r, int64_t id, uin
             if (token_count >= L.sealed_tokens) {
                 L.active_count = token_count - L.sealed_tokens;
             } else {
+                r->materialise_pins(q, layer);
                 L.active_count = 0;
                 while (!L.pages.empty() && L.sealed_tokens > token_count) {
                     const PageRef ref = L.pages.back();
@@ -609,6 +652,7 @@ extern "C" int cf_b200_ms_drop_prefix_async(cf_ms_cuda_resolver *r, int64_t id, 
         for (uint32_t layer = 0; layer < q.layers.size(); ++layer) {
             LayerSeq &L = q.layers[layer];
             if (L.pages.empty()) continue;
+            r->materialise_pins(q, layer);
             uint32_t dropped_tokens = 0, dropped_tiles = 0;
             size_t dropped_pages = 0;
             while (dropped_tokens < token_count) {
@@ -679,6 +723,7 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
         auto old = r->sequences.find(destination_id);
         if (old != r->sequences.end()) {  // the old destination is replaced: its pages lose one reference each
             old->second.dispatchable = false;
+            r->materialise_pins(old->second);
             for (auto &layer : old->second.layers)
                 for (const auto &ref : layer.pages) {
                     SharedPage &page = r->pages.at(ref.page_id);
@@ -694,6 +739,7 @@ extern "C" int cf_ms_cuda_copy_sequence_async(cf_ms_cuda_resolver *r, int64_t so
         candidate.layers = source.layers;
         for (uint32_t layer = 0; layer < r->config.layer_count; ++layer) {
             LayerSeq &L = candidate.layers[layer];
+            L.pins = 0;   // the snapshots out on the source pin the source's list, not the copy's
             for (const auto &ref : L.pages) {
                 ++r->pages.at(ref.page_id).logical_refs;
                 ++r->ref_increments;
@@ -779,18 +825,13 @@ extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_m
             total_rows += it.query.token_count;
         }
         if (total_rows > kMaxBatchTokens || item_count > 1024) throw std::runtime_error("batch is larger than the resolver's staging buffers");
+        snapshots.reserve(item_count);
         for (uint32_t i = 0; i < item_count; ++i) {
-            Snapshot snap{items[i].sequence_id, items[i].layer, {}};
-            const auto &refs = r->sequences.at(items[i].sequence_id).layers[items[i].layer].pages;
-            snap.page_ids.reserve(refs.size());
-            for (const auto &ref : refs) {
-                SharedPage &page = ref.page ? *ref.page : r->pages.at(ref.page_id);
-                ++page.in_flight_refs;
-                ++r->counters.in_flight_page_references;
-                snap.page_ids.push_back(ref.page_id);
-            }
+            LayerSeq &L = r->sequences.at(items[i].sequence_id).layers[items[i].layer];
+            snapshots.push_back(Snapshot{items[i].sequence_id, items[i].layer, static_cast<uint32_t>(L.pages.size()), true, {}});
+            ++L.pins;
+            r->counters.in_flight_page_references += L.pages.size();
             ++r->counters.snapshots_acquired;
-            snapshots.push_back(std::move(snap));
         }
         ++r->counters.server_batches_received;
         r->counters.tokens_per_batch_peak = std::max<uint64_t>(r->counters.tokens_per_batch_peak, item_count);
@@ -873,13 +914,18 @@ extern "C" int cf_ms_cuda_execute_batch_async(cf_ms_cuda_resolver *r, const cf_m
         }
         scatter_outputs_kernel<<<dim3(8, item_count), 256, 0, s>>>(r->item_io.ptr, r->o_dense.ptr, Hq, D);
         cuda_check(cudaGetLastError(), "output scatter launch");
-        for (auto &snap : snapshots) {
+        {   // one event for the batch: every snapshot of it is released when the batch's last kernel is done
             Pending p;
-            p.snapshot = std::move(snap);
             cuda_check(cudaEventCreateWithFlags(&p.event, cudaEventDisableTiming), "create snapshot release event");
-            cuda_check(cudaEventRecord(p.event, s), "record snapshot release event");
+            const cudaError_t recorded = cudaEventRecord(p.event, s);
+            if (recorded != cudaSuccess) {
+                cudaEventDestroy(p.event);
+                cuda_check(recorded, "record snapshot release event");
+            }
+            r->counters.snapshot_release_events += snapshots.size();
+            p.snapshots = std::move(snapshots);
+            snapshots.clear();
             r->pending.push_back(std::move(p));
-            ++r->counters.snapshot_release_events;
         }
         ++r->counters.compressed_batches_executed;
         r->error.clear();
@@ -908,6 +954,7 @@ extern "C" int cf_ms_cuda_sequence_remove_async(cf_ms_cuda_resolver *r, int64_t 
     if (!r) return -1;
     return locked(r, false, [&] {
         Sequence &q = find_sequence(r, id, "sequence is missing");
+        r->materialise_pins(q);
         for (auto &layer : q.layers)
             for (const auto &ref : layer.pages) {
                 SharedPage &page = r->pages.at(ref.page_id);
@@ -928,7 +975,7 @@ extern "C" int cf_ms_cuda_reclaim_async(cf_ms_cuda_resolver *r, void *stream) {
             const cudaError_t status = cudaEventQuery(it->event);
             if (status == cudaErrorNotReady) { ++it; continue; }
             cuda_check(status, "query snapshot release event");
-            r->release_snapshot(it->snapshot);
+            for (const Snapshot &snap : it->snapshots) r->release_snapshot(snap);
             cudaEventDestroy(it->event);
             it = r->pending.erase(it);
         }
