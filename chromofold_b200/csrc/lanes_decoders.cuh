@@ -152,15 +152,15 @@ __device__ __forceinline__ uint32_t merge_split_quad(uint32_t e0, uint32_t e1, u
 
 // Nibble-split rANS (CF_B200_CODER_RANS_SPLIT4): the low nibble of every symbol is stored raw in a lane-interleaved
 // plane, and the rANS stream codes PAIRS of high nibbles (pair symbol = hi(2k) << 4 | hi(2k + 1)), so a block of 64
-// symbols is 32 steps of the same recurrence. Part layout: u32 state0[NB] | u16 byte_off[NB] | u32 lo[2048/NB/8][NB] |
+// symbols is 32 steps of the same recurrence. Part layout: u32 state0[NB] | u16 byte_off[NB] | u32 lo[symbols/NB/8][NB] |
 // bytes; lo[j][l] holds the low nibbles of symbols 8j..8j+7 of block l: symbol 8j + i at bits 8i..8i+3 for i < 4,
 // symbol 8j + 4 + i at bits 8i+4..8i+7. The plane is 1024 bytes whatever the block size.
-template <int NB>
+template <int NB, int kSyms = 2048>
 struct RansSplitLaneT : RansLaneT<NB> {
     using Base = RansLaneT<NB>;
     using Base::x; using Base::pos; using Base::table; using Base::used; using Base::kHead;
     static constexpr bool kWholeQuads = true;   // callers ask for a quad at a time (the window is refilled inside)
-    static constexpr uint32_t kPlaneBytes = 1024u;
+    static constexpr uint32_t kPlaneBytes = kSyms / 2u;   // a nibble per symbol
     uint32_t lo;   // shared-memory byte address of lo[0][lane]
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint32_t *slot_table) {
         x = reinterpret_cast<const uint32_t *>(part)[lane];
@@ -228,13 +228,13 @@ struct HuffLaneT {
 };
 using HuffLane = HuffLaneT<32>;
 
-// Nibble-split Huffman (CF_B200_CODER_HUFFMAN_SPLIT4): u16 bit_off[NB] | u32 lo[2048/NB/8][NB] | words; one LUT hit = a pair.
-template <int NB>
+// Nibble-split Huffman (CF_B200_CODER_HUFFMAN_SPLIT4): u16 bit_off[NB] | u32 lo[symbols/NB/8][NB] | words; one LUT hit = a pair.
+template <int NB, int kSyms = 2048>
 struct HuffSplitLaneT : HuffLaneT<NB> {
     using Base = HuffLaneT<NB>;
     using Base::bit; using Base::words; using Base::table; using Base::used; using Base::kHead;
     static constexpr bool kWholeQuads = true;
-    static constexpr uint32_t kPlaneBytes = 1024u;
+    static constexpr uint32_t kPlaneBytes = kSyms / 2u;   // a nibble per symbol
     uint32_t lo;
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t part_bytes, uint32_t lane, const uint16_t *lut) {
         const uint32_t payload_bits = part_bytes > kHead + kPlaneBytes ? (part_bytes - kHead - kPlaneBytes) * 8u : 0u;
@@ -257,14 +257,14 @@ struct HuffSplitLaneT : HuffLaneT<NB> {
 };
 using HuffSplitLane = HuffSplitLaneT<32>;
 
-template <int NB>
+template <int NB, int kSyms = 2048>
 struct FixedLaneT {
     static constexpr bool kWholeQuads = true;  // a quad is one word: nothing to interleave
     static constexpr int kSymbolsPerReload = 4;
     const uint32_t *words;
-    // A fixed-width part is 2048 bytes at a 16-byte aligned offset of at most 16 + 2048 into the stage: always inside it.
+    // A fixed-width part is kSyms bytes at a 16-byte aligned offset of at most 16 + 2048 into the stage: always inside it.
     __device__ __forceinline__ void open(const uint8_t *part, uint32_t, uint32_t lane) {
-        words = reinterpret_cast<const uint32_t *>(part) + (512u / NB) * lane;
+        words = reinterpret_cast<const uint32_t *>(part) + (kSyms / 4u / NB) * lane;
     }
     // src/runtime/kv_gpu_fixture.cpp:110-116: symbol i sits in the i-th byte from the top of the word.
     __device__ __forceinline__ uint32_t quad(int) { return __byte_perm(*words++, 0u, 0x0123); }
@@ -302,18 +302,18 @@ __device__ __forceinline__ bool record_header_ok(const uint4 &hv, uint64_t dir_e
 // The block table of a staged part against the part's length: lane l checks the start of block l. The reference
 // validates its descriptors on the host before the launch (src/cuda/paged_kv_attention.cu:280-299); records here are
 // written by the sealer, by import or by unpack, so the check runs where the table is read.
-template <int NB = 32>
+template <int NB = 32, int kSyms = 2048>
 __device__ __forceinline__ bool part_offsets_ok(const uint8_t *part, uint32_t coder, uint32_t part_bytes, uint32_t lane) {
-    constexpr uint32_t kRansHead = RansLaneT<NB>::kHead, kHuffHead = HuffLaneT<NB>::kHead;
+    constexpr uint32_t kRansHead = RansLaneT<NB>::kHead, kHuffHead = HuffLaneT<NB>::kHead, kPlane = kSyms / 2u;
     if (coder == CF_B200_CODER_RANS)
         return part_bytes >= kRansHead && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead;
     if (coder == CF_B200_CODER_HUFFMAN)
         return part_bytes >= kHuffHead && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - kHuffHead) * 8u;
     if (coder == CF_B200_CODER_RANS_SPLIT4)
-        return part_bytes >= kRansHead + 1024u && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead - 1024u;
+        return part_bytes >= kRansHead + kPlane && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead - kPlane;
     if (coder == CF_B200_CODER_HUFFMAN_SPLIT4)
-        return part_bytes >= kHuffHead + 1024u && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - kHuffHead - 1024u) * 8u;
-    return part_bytes == 2048u;
+        return part_bytes >= kHuffHead + kPlane && reinterpret_cast<const uint16_t *>(part)[lane] <= (part_bytes - kHuffHead - kPlane) * 8u;
+    return part_bytes == static_cast<uint32_t>(kSyms);
 }
 
 }  // namespace lanes

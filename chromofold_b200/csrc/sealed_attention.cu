@@ -619,7 +619,7 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || probe ||
                            (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
-    if (use_lanes && p.block_size == 64 && p.decode_probe != 1u && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
+    if (use_lanes && p.block_size == 64 && p.head_dim == 128 && p.decode_probe != 1u && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static cfb::LauncherState table[64];
         cudaError_t e;
         const cfb::LauncherState *state = cfb::launcher_state(table, &e);

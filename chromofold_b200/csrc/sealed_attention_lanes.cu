@@ -49,11 +49,13 @@ using namespace lanes;
 template <int NG, int NB = 32> constexpr int kWarpsOf = NB != 32 ? (NG == 1 ? CFB_LANES_WARPS_BIG : 14) : NG == 1 ? CFB_LANES_WARPS : CFB_LANES_WARPS2;
 template <int NG, int NB = 32> constexpr int kThreadsOf = kWarpsOf<NG, NB> * 32;
 // Per-warp running state of one unit; NG = number of four-head query groups served by one decode pass.
-template <int NG>
+// kDim = head_dim: a lane holds kDim / 8 quads of each stream (K: kDim / 2 channels of one token; V: kDim / 32 channels,
+// every token).
+template <int NG, int kDim = 128>
 struct UnitState {
     float score[NG][4];      // S fragments of the current page
-    float acc[NG][4][4];     // O fragments: [group][channel of the lane's V block][fragment register]
-    uint32_t vq[16];         // V symbols of the current page, [channel*4 + token quad]
+    float acc[NG][kDim / 32][4];   // O fragments: [group][channel of the lane's V block][fragment register]
+    uint32_t vq[kDim / 8];   // V symbols of the current page, [channel*4 + token quad]
     float m0[NG], m1[NG], l0[NG], l1[NG];  // running max / partial sum of the lane's two heads of each group
     uint32_t *dump;          // kDump only: where this lane's quads of the current record go (K at +0, V at +512 words)
 };
@@ -68,14 +70,16 @@ constexpr int kAttend = 0, kFold = 1, kDump = 2;
 //   QSmem: the query rows of up to eight heads sit in the warp's shared memory as [head][half][64 channels] with a
 //   row stride of 36 words, which puts the eight rows one load touches into different banks; a lane reads two words
 //   of row (head g&3 of the group, half t&1), or of a zero row when the column is not its own.
-struct QRegs {
-    uint32_t bq[16][2];
+template <int kQuads>
+struct QRegsT {
+    uint32_t bq[kQuads][2];
     template <int GRP>
     __device__ __forceinline__ void get(int q, uint32_t &b0, uint32_t &b1) const {
         b0 = bq[q][0];
         b1 = bq[q][1];
     }
 };
+using QRegs = QRegsT<16>;
 struct QSmem {
     uint32_t addr, group_stride;  // byte address of the lane's row for group 0; distance to the row for group 1 (0 on the zero row)
     template <int GRP>
@@ -84,8 +88,8 @@ struct QSmem {
     }
 };
 
-template <int NG, class QSrc>
-__device__ __forceinline__ void score_quad(UnitState<NG> &u, const QSrc &qs, int q, uint32_t kq) {
+template <int NG, int kDim, class QSrc>
+__device__ __forceinline__ void score_quad(UnitState<NG, kDim> &u, const QSrc &qs, int q, uint32_t kq) {
     uint32_t lo, hi, b0, b1;
     quad_to_half2(kq, lo, hi);
     qs.template get<0>(q, b0, b1);
@@ -205,43 +209,49 @@ __device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
 // sixteen K quads and sixteen V quads back with 16-byte loads. A tile row is one lane's 64 symbols plus 16 bytes
 // of padding (row stride 80 bytes), which keeps both the stores and the loads off each other's banks; the V tile
 // sits 16 bytes further for the same reason.
-constexpr uint32_t kTileRow = 80u, kTileStream = 32u * kTileRow, kTileBytes = 2u * kTileStream + 32u;
+// The same staging serves head_dim 64 (streams of 1024 symbols, 16 blocks of 64): a lane's share is then 32 symbols
+// of each stream (K: half of one token's channels; V: two channels, every token) and a tile row 32 + 16 bytes.
+template <int kDim> constexpr uint32_t kTileRowOf = kDim / 2u + 16u;      // one lane's kDim / 2 symbols + padding
+template <int kDim> constexpr uint32_t kTileStreamOf = 32u * kTileRowOf<kDim>;
+constexpr uint32_t kTileBytes = 2u * kTileStreamOf<128> + 32u;
 
-template <int NB, class Lane>
+template <int NB, int kDim, class Lane>
 __device__ __forceinline__ void stage_with(Lane &d, uint32_t block, uint8_t *tile) {
-    constexpr int kQuads = 512 / NB;   // per block
+    constexpr int kQuads = 4 * kDim / NB;   // per block
+    constexpr uint32_t kRowQuads = kDim / 8;
 #pragma unroll 2
     for (int q = 0; q < kQuads; q += 4) {
         const uint32_t a = d.quad(q), b = d.quad(q + 1), c = d.quad(q + 2), e = d.quad(q + 3);
-        const uint32_t at = block * kQuads + q;   // quad index in the stream: row = at / 16, column = at % 16
-        *reinterpret_cast<uint4 *>(tile + (at >> 4) * kTileRow + (at & 15u) * 4u) = make_uint4(a, b, c, e);
+        const uint32_t at = block * kQuads + q;   // quad index in the stream: row = at / kRowQuads, column = at % kRowQuads
+        *reinterpret_cast<uint4 *>(tile + (at / kRowQuads) * kTileRowOf<kDim> + (at % kRowQuads) * 4u) = make_uint4(a, b, c, e);
     }
 }
 
 // One lane's share: block `block` of the part, whatever its coder.
-template <int NB>
+template <int NB, int kDim>
 __device__ __forceinline__ void stage_blocks(const uint8_t *part, uint32_t part_bytes, uint32_t coder, uint32_t block,
                                              const uint32_t *slot_table, const uint16_t *lut, uint8_t *tile) {
+    constexpr int kSyms = 16 * kDim;
     if (coder == CF_B200_CODER_RANS_SPLIT4) {
-        RansSplitLaneT<NB> d;
+        RansSplitLaneT<NB, kSyms> d;
         d.open(part, part_bytes, block, slot_table);
-        stage_with<NB>(d, block, tile);
+        stage_with<NB, kDim>(d, block, tile);
     } else if (coder == CF_B200_CODER_HUFFMAN_SPLIT4) {
-        HuffSplitLaneT<NB> d;
+        HuffSplitLaneT<NB, kSyms> d;
         d.open(part, part_bytes, block, lut);
-        stage_with<NB>(d, block, tile);
+        stage_with<NB, kDim>(d, block, tile);
     } else if (coder == CF_B200_CODER_RANS) {
         RansLaneT<NB> d;
         d.open(part, part_bytes, block, slot_table);
-        stage_with<NB>(d, block, tile);
+        stage_with<NB, kDim>(d, block, tile);
     } else if (coder == CF_B200_CODER_HUFFMAN) {
         HuffLaneT<NB> d;
         d.open(part, part_bytes, block, lut);
-        stage_with<NB>(d, block, tile);
+        stage_with<NB, kDim>(d, block, tile);
     } else {
-        FixedLaneT<NB> d;
+        FixedLaneT<NB, kSyms> d;
         d.open(part, part_bytes, block);
-        stage_with<NB>(d, block, tile);
+        stage_with<NB, kDim>(d, block, tile);
     }
 }
 
@@ -267,13 +277,16 @@ static_assert(WarpLayout<1>::kSmem <= 232448 && WarpLayout<2>::kSmem <= 232448 &
 // kSplitQ (with NG = 2): the queries are fp32. A pass serves four heads; their rows are split into binary16(q) and
 // binary16(q - binary16(q)), stored as the rows of group 0 and group 1, the two score fragments are added, and one
 // softmax / P V follows: the scores equal fp32-query scores to 2^-22 relative, at the cost of a second score mma.
-template <int NG, int kMode = kAttend, bool kSplitQ = false, int NB = 32>
+template <int NG, int kMode = kAttend, bool kSplitQ = false, int NB = 32, int kDim = 128>
 __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(AttentionParams p) {
     constexpr bool kProbe = kMode != kAttend;
     static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
     static_assert(NB == 32 || NB == 16 || NB == 8, "blocks per stream");
+    static_assert(kDim == 128 || (kDim == 64 && NB != 32), "head_dim 64 goes through the staging tile");
+    constexpr int kQ = kDim / 8, kVCh = kDim / 32, kSyms = 16 * kDim;   // quads per lane and stream; V channels per lane
+    constexpr uint32_t kRowWords = kDim / 4;   // words of half a query row (the channels one lane's K block covers)
     using L = WarpLayout<NG, NB>;
-    using QSrc = typename std::conditional<NG == 1, QRegs, QSmem>::type;
+    using QSrc = typename std::conditional<NG == 1, QRegsT<kQ>, QSmem>::type;
     constexpr uint32_t kPassHeads = kSplitQ ? 4u : 4u * NG;
     constexpr int NS = kSplitQ ? 1 : NG;   // groups that go through softmax and P V
     extern __shared__ __align__(128) uint8_t smem[];
@@ -345,10 +358,10 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
         if constexpr (NG == 1) {
             const bool live = q_col_mine && q_head_of_col < G;
             const __half *qrow = reinterpret_cast<const __half *>(p.queries) +
-                                 (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base + q_head_of_col) * 128u +
-                                 64u * (t & 1u);
+                                 (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base + q_head_of_col) * kDim +
+                                 (kDim / 2) * (t & 1u);
 #pragma unroll
-            for (int s = 0; s < 16; ++s) {
+            for (int s = 0; s < kQ; ++s) {
                 uint2 v = make_uint2(0u, 0u);
                 if (live) v = *reinterpret_cast<const uint2 *>(qrow + 4 * s);
                 qs.bq[s][0] = v.x;
@@ -356,42 +369,42 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
             }
         } else if constexpr (kSplitQ) {
             const float2 *qsrc = reinterpret_cast<const float2 *>(
-                reinterpret_cast<const float *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * 128u);
+                reinterpret_cast<const float *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * kDim);
             __syncwarp();  // the previous unit's readers are done
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {    // 4 heads x 64 channel pairs; row = head*2 + half, residues 8 rows further
-                const uint32_t i = lane + 32u * j, head = i >> 6;
+            for (int j = 0; j < kDim / 16; ++j) {    // 4 heads x kDim / 2 channel pairs; row = head*2 + half, residues 8 rows further
+                const uint32_t i = lane + 32u * j, head = i / (2u * kRowWords);
                 const float2 x = head < G ? qsrc[i] : make_float2(0.0f, 0.0f);
                 const __half2 hi = __floats2half2_rn(x.x, x.y);
                 const float2 back = __half22float2(hi);
                 const __half2 lo = __floats2half2_rn(x.x - back.x, x.y - back.y);
-                q_rows[(i >> 5) * L::kQRowWords + (i & 31u)] = *reinterpret_cast<const uint32_t *>(&hi);
-                q_rows[((i >> 5) + 8u) * L::kQRowWords + (i & 31u)] = *reinterpret_cast<const uint32_t *>(&lo);
+                q_rows[(i / kRowWords) * L::kQRowWords + i % kRowWords] = *reinterpret_cast<const uint32_t *>(&hi);
+                q_rows[(i / kRowWords + 8u) * L::kQRowWords + i % kRowWords] = *reinterpret_cast<const uint32_t *>(&lo);
             }
             __syncwarp();
             qs.addr = q_col_mine ? smem_addr(q_rows + (q_head_of_col * 2u + (t & 1u)) * L::kQRowWords) : smem_addr(zero_row);
             qs.group_stride = q_col_mine ? 8u * L::kQRowWords * 4u : 0u;
         } else {
             const uint32_t *qsrc = reinterpret_cast<const uint32_t *>(
-                reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * 128u);
+                reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * kDim);
             __syncwarp();  // the previous unit's readers are done
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {   // 8 heads x 64 words; row = head*2 + half
-                const uint32_t i = lane + 32u * j, head = i >> 6;
-                q_rows[(i >> 5) * L::kQRowWords + (i & 31u)] = head < G ? qsrc[i] : 0u;
+            for (int j = 0; j < kDim / 8; ++j) {   // 8 heads x kDim / 2 words; row = head*2 + half
+                const uint32_t i = lane + 32u * j, head = i / (2u * kRowWords);
+                q_rows[(i / kRowWords) * L::kQRowWords + i % kRowWords] = head < G ? qsrc[i] : 0u;
             }
             __syncwarp();
             qs.addr = q_col_mine ? smem_addr(q_rows + (q_head_of_col * 2u + (t & 1u)) * L::kQRowWords) : smem_addr(zero_row);
             qs.group_stride = q_col_mine ? 8u * L::kQRowWords * 4u : 0u;
         }
 
-        UnitState<NG> u;
+        UnitState<NG, kDim> u;
         if constexpr (kProbe) u.vq[0] = 0u;
         u.dump = nullptr;
 #pragma unroll
         for (int n = 0; n < NG; ++n) {
 #pragma unroll
-            for (int a = 0; a < 4; ++a)
+            for (int a = 0; a < kVCh; ++a)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) u.acc[n][a][b] = 0.0f;
             u.m0[n] = u.m1[n] = -CUDART_INF_F;
@@ -455,8 +468,8 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                     offsets_ok = part_offsets_ok(k_part, k_coder, k_bytes, lane) && part_offsets_ok(v_part, v_coder, v_bytes, lane);
                 } else {   // lanes 0..NB-1 hold the K blocks, lanes 16..16+NB-1 the V blocks
                     const bool mine = (lane & 15u) < static_cast<uint32_t>(NB);
-                    offsets_ok = !mine || (lane < 16u ? part_offsets_ok<NB>(k_part, k_coder, k_bytes, lane)
-                                                      : part_offsets_ok<NB>(v_part, v_coder, v_bytes, lane - 16u));
+                    offsets_ok = !mine || (lane < 16u ? part_offsets_ok<NB, kSyms>(k_part, k_coder, k_bytes, lane)
+                                                      : part_offsets_ok<NB, kSyms>(v_part, v_coder, v_bytes, lane - 16u));
                 }
                 const bool good = record_header_ok(hv, entry_cur, p.codebook_id) && __all_sync(0xffffffffu, offsets_ok);
                 uint32_t dump_page = 0u;
@@ -466,7 +479,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                 } else {
                     if constexpr (kMode == kDump)   // [page id][kv head][K stream | V stream], one byte per symbol
                         u.dump = reinterpret_cast<uint32_t *>(p.output) +
-                                 (static_cast<uint64_t>(dump_page) * p.kv_head_count + kv_head) * 1024u + 16u * lane;
+                                 (static_cast<uint64_t>(dump_page) * p.kv_head_count + kv_head) * (kSyms / 2) + kQ * lane;
                     const float k_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z & 0xffffu))) *
                                           (p.softmax_scale * kLog2e);
                     const float v_scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hv.z >> 16)));
@@ -476,16 +489,16 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                     if constexpr (NB != 32) {
                         uint8_t *tile = warp_mem + L::kTile;
                         if ((lane & 15u) < static_cast<uint32_t>(NB)) {
-                            if (lane < 16u) stage_blocks<NB>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
-                            else stage_blocks<NB>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStream + 16u);
+                            if (lane < 16u) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
+                            else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
                         }
                         __syncwarp();
                         if (i + 1 < n_pages) issue(0u, entry_next);   // the record is decoded: its stage takes the next one
                         next_issued = true;
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint4 kk = *reinterpret_cast<const uint4 *>(tile + lane * kTileRow + 16u * c);
-                            const uint4 vv = *reinterpret_cast<const uint4 *>(tile + kTileStream + 16u + lane * kTileRow + 16u * c);
+                        for (int c = 0; c < kQ / 4; ++c) {
+                            const uint4 kk = *reinterpret_cast<const uint4 *>(tile + lane * kTileRowOf<kDim> + 16u * c);
+                            const uint4 vv = *reinterpret_cast<const uint4 *>(tile + kTileStreamOf<kDim> + 16u + lane * kTileRowOf<kDim> + 16u * c);
                             const uint32_t kq[4] = {kk.x, kk.y, kk.z, kk.w}, vq[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -494,7 +507,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                                     u.vq[0] ^= kq[j] ^ vq[j];
                                 } else if constexpr (kMode == kDump) {
                                     u.dump[q] = kq[j];
-                                    u.dump[512 + q] = vq[j];
+                                    u.dump[kSyms / 4 + q] = vq[j];
                                 } else {
                                     u.vq[q] = vq[j];
                                     score_quad(u, qs, q, kq[j]);
@@ -587,7 +600,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                     for (int n = 0; n < NS; ++n) {
                         const float beta = alpha_s[4u * n + o_head] * v_ratio;
 #pragma unroll
-                        for (int dd = 0; dd < 4; ++dd)
+                        for (int dd = 0; dd < kVCh; ++dd)
 #pragma unroll
                             for (int c = 0; c < 4; ++c) u.acc[n][dd][c] *= beta;
                     }
@@ -614,7 +627,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 #pragma unroll
                     for (int tq = 0; tq < 4; ++tq) {   // token quads outside: consecutive mma feed different accumulators
 #pragma unroll
-                        for (int dd = 0; dd < 4; ++dd) {
+                        for (int dd = 0; dd < kVCh; ++dd) {
                             uint32_t lo, hi;
                             quad_to_half2(u.vq[dd * 4 + tq], lo, hi);   // converted once, used by both parts
 #pragma unroll
@@ -674,11 +687,11 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
             if (4u * n + o_head < G) {
                 float *dst = partial_ptr(p, chunk, out_head_base + 4u * n + o_head) + 2;
 #pragma unroll
-                for (int dd = 0; dd < 4; ++dd) {
+                for (int dd = 0; dd < kVCh; ++dd) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint32_t owner = 4u * (2u * t + (c & 1)) + (g >> 2) + 2u * (c >> 1);  // lane whose V block it is
-                        dst[4u * owner + dd] = u.acc[n][dd][c] * v_scale_prev;
+                        dst[kVCh * owner + dd] = u.acc[n][dd][c] * v_scale_prev;
                     }
                 }
             }
@@ -691,8 +704,10 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 }  // namespace
 
 bool lanes_kernel_supports(const AttentionParams &p) {
-    return p.head_dim == 128 && p.page_tokens == 16 && (p.block_size == 64 || p.block_size == 128 || p.block_size == 256) &&
-           p.group >= 1 && p.group <= 16 &&
+    const bool geometry = p.page_tokens == 16 &&
+                          ((p.head_dim == 128 && (p.block_size == 64 || p.block_size == 128 || p.block_size == 256)) ||
+                           (p.head_dim == 64 && (p.block_size == 64 || p.block_size == 128)));
+    return geometry && p.group >= 1 && p.group <= 16 &&
            (p.query_type == CF_B200_F16 || p.query_type == CF_B200_F32);
 }
 
@@ -701,7 +716,7 @@ bool lanes_kernel_supports(const AttentionParams &p) {
 // queries (the reference's own ABIs pass nothing else) run the split-query kernel, four heads per pass.
 namespace {
 
-template <int NG, int kMode, bool kSplitQ, int NB>
+template <int NG, int kMode, bool kSplitQ, int NB, int kDim>
 cudaError_t launch_one(const AttentionParams &p, int sm_count, cudaStream_t stream) {
     static std::atomic<uint64_t> configured{0};   // bit = device ordinal
     int device = 0;
@@ -709,22 +724,22 @@ cudaError_t launch_one(const AttentionParams &p, int sm_count, cudaStream_t stre
     if (e != cudaSuccess) return e;
     const uint64_t bit = 1ull << (device & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        e = cudaFuncSetAttribute(lanes_attention_kernel<NG, kMode, kSplitQ, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(lanes_attention_kernel<NG, kMode, kSplitQ, NB, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(WarpLayout<NG, NB>::kSmem));
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_release);
     }
-    lanes_attention_kernel<NG, kMode, kSplitQ, NB><<<sm_count, kThreadsOf<NG, NB>, WarpLayout<NG, NB>::kSmem, stream>>>(p);
+    lanes_attention_kernel<NG, kMode, kSplitQ, NB, kDim><<<sm_count, kThreadsOf<NG, NB>, WarpLayout<NG, NB>::kSmem, stream>>>(p);
     return cudaPeekAtLastError();
 }
 
-template <int NB>
+template <int NB, int kDim = 128>
 cudaError_t launch_for_blocks(const AttentionParams &p, int sm_count, cudaStream_t stream) {
-    if (p.decode_probe == 2u) return launch_one<1, kDump, false, NB>(p, sm_count, stream);
-    if (p.decode_probe) return launch_one<1, kFold, false, NB>(p, sm_count, stream);
-    if (p.query_type == CF_B200_F32) return launch_one<2, kAttend, true, NB>(p, sm_count, stream);
-    if (p.group <= 4) return launch_one<1, kAttend, false, NB>(p, sm_count, stream);
-    return launch_one<2, kAttend, false, NB>(p, sm_count, stream);
+    if (p.decode_probe == 2u) return launch_one<1, kDump, false, NB, kDim>(p, sm_count, stream);
+    if (p.decode_probe) return launch_one<1, kFold, false, NB, kDim>(p, sm_count, stream);
+    if (p.query_type == CF_B200_F32) return launch_one<2, kAttend, true, NB, kDim>(p, sm_count, stream);
+    if (p.group <= 4) return launch_one<1, kAttend, false, NB, kDim>(p, sm_count, stream);
+    return launch_one<2, kAttend, false, NB, kDim>(p, sm_count, stream);
 }
 
 }  // namespace
@@ -734,6 +749,10 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
     cudaError_t e;
     LauncherState *state = launcher_state(table, &e);
     if (!state) return e;
+    if (p.head_dim == 64) {   // 16 x 64 pages: 16 (or 8) blocks per stream, always staged
+        return p.block_size == 64 ? launch_for_blocks<16, 64>(p, state->sm_count, stream)
+                                  : launch_for_blocks<8, 64>(p, state->sm_count, stream);
+    }
     if (p.block_size == 128) return launch_for_blocks<16>(p, state->sm_count, stream);
     if (p.block_size == 256) return launch_for_blocks<8>(p, state->sm_count, stream);
     return launch_for_blocks<32>(p, state->sm_count, stream);

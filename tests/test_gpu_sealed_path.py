@@ -91,7 +91,7 @@ def test_gpu_decode_is_bit_exact(native, oracle, coder):
     assert layer.device_status() == 0
 
 
-def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None, block=64):
+def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None, block=64, d=128):
     """Every record of `sequences` (page ids in import order from 1): the dumped K and V symbols against the symbols
     the CPU quantiser produced and against what the restated reference decoders recover from the record's bytes."""
     pid, checked = 1, 0
@@ -100,7 +100,7 @@ def _expect_dump(dump, host, oracle, kcb, vcb, sequences, first_page_of=None, bl
             if s in sequences:
                 for h, rec in enumerate(page):
                     want_k, want_v = host.symbols[s][p][h]
-                    back_k, back_v = oracle.open_record(rec, 128, 16, block, kcb, vcb)
+                    back_k, back_v = oracle.open_record(rec, d, 16, block, kcb, vcb)
                     assert np.array_equal(back_k, want_k) and np.array_equal(back_v, want_v)
                     assert np.array_equal(dump[pid, h, 0], want_k), ("K", s, p, h)
                     assert np.array_equal(dump[pid, h, 1], want_v), ("V", s, p, h)
@@ -164,6 +164,32 @@ def test_larger_blocks_are_decoded_exactly_and_attend_like_the_oracle(native, or
     assert layer4.device_status() == 0
     ok, err = attention_close(got4, want4)
     assert ok, f"max abs error {err}"
+
+
+@pytest.mark.parametrize("block", [64, 128])
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_head_dim_64_pages_run_the_lane_kernel(native, oracle, coder, block):
+    """16 x 64 pages (streams of 1024 symbols: 16 or 8 blocks) go through the staging tile of the lane-per-block kernel
+    with half-size lane shares: symbols exact against the oracle, attention against the oracle for groups of four
+    and eight heads, fp16 and fp32 queries."""
+    import torch
+    rng = np.random.default_rng(41)
+    contexts, tails = [48, 16, 37, 160], [3, 0, 0, 9]
+    for hq in (16, 8):
+        layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=hq, hkv=2, d=64, t=16, block=block,
+                                                               coder=CODERS[coder], contexts=contexts, tails=tails,
+                                                               noisy_k_pages={(3, 1), (3, 7)})
+        q = rng.standard_normal((4, hq, 64)).astype(np.float16)
+        if hq == 16:
+            dump = layer.dump_lane_decoders(torch.from_numpy(q).cuda()).cpu().numpy()
+            assert layer.device_status() == 0
+            assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}, block=block, d=64) == 2 * (3 + 1 + 3 + 10)
+        want = _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q, hq, stride)
+        for qt in (torch.from_numpy(q).cuda(), torch.from_numpy(q.astype(np.float32)).cuda()):
+            got = layer.attention(qt, kernel=native.KERNEL_LANES, min_pages_per_unit=2).cpu().numpy()
+            assert layer.device_status() == 0
+            ok, err = attention_close(got, want)
+            assert ok, f"max abs error {err}"
 
 
 @pytest.mark.parametrize("coder", list(CODERS))
