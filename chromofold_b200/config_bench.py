@@ -337,20 +337,20 @@ def transfer(a, device):
 
 
 def head_dim_dial(a, device, check=None):
-    """16 x 64 pages (head_dim 64, the shape of the reference's own live runs) through the lane-per-block kernel's
-    staging path and, for comparison, through the any-geometry kernel: batch 32 x 8192, Laplace(b=12) codes."""
+    """16 x 96, 16 x 64 (the shape of the reference's own live runs) and 16 x 32 pages through the lane-per-block
+    kernel's staging path and, for comparison, through the any-geometry kernel: batch 32 x 8192, Laplace(b=12) codes."""
     contexts = np.full(32, 8192)
     results = []
     for coder in ("rans4", "huffman4", "rans", "huffman", "fixed8"):
-        for block in (64, 128):
-            layer, info = build_sealed_layer(contexts, coder=coder, seed=45, device=device, head_dim=64, block_size=block)
+        for dim, block in ((96, 64), (64, 64), (64, 128), (32, 64)):
+            layer, info = build_sealed_layer(contexts, coder=coder, seed=45, device=device, head_dim=dim, block_size=block)
             g = torch.Generator(device=device)
             g.manual_seed(46)
-            q = torch.randn((32, 32, 64), generator=g, device=device, dtype=torch.float32).half()
-            out = torch.zeros((32, 32, 64), dtype=torch.float32, device=device)
+            q = torch.randn((32, 32, dim), generator=g, device=device, dtype=torch.float32).half()
+            out = torch.zeros((32, 32, dim), dtype=torch.float32, device=device)
             ms = _time(lambda: layer.attention(q, out=out), a.steps, a.warmup)
             ms_generic = _time(lambda: layer.attention(q, out=out, kernel=N.KERNEL_GENERIC), 3, 1)
-            results.append(_checked({"head_dim": 64, "coder": coder, "block_size": block,
+            results.append(_checked({"head_dim": dim, "coder": coder, "block_size": block,
                                      "sealed_bytes_per_seq_token": round(info["bytes_per_seq_token"], 1),
                                      "ms_per_step": round(ms, 4), "seq_tokens_per_s": round(int(contexts.sum()) / ms * 1e3),
                                      "sealed_gbs": round(info["sealed_bytes"] / ms / 1e6, 1),
@@ -437,7 +437,7 @@ def main():
     ap.add_argument("--transfer", action="store_true", help="time the pack / unpack kernels of transfer images instead")
     ap.add_argument("--delta", action="store_true", help="time cf_delta_fetch_async instead")
     ap.add_argument("--seal", action="store_true", help="time cf_b200_seal_pages_async alone, every coder")
-    ap.add_argument("--head-dim-64", action="store_true", help="time attention over 16 x 64 pages")
+    ap.add_argument("--head-dims", action="store_true", help="time attention over 16 x 96, 16 x 64 and 16 x 32 pages")
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
@@ -464,7 +464,7 @@ def main():
         rows = delta_fetch(a, device)
     elif a.seal:
         rows = seal_rate(a, device)
-    elif a.head_dim_64:
+    elif a.head_dims:
         rows = head_dim_dial(a, device)
     elif a.transfer:
         rows = transfer(a, device)

@@ -209,9 +209,12 @@ __device__ __forceinline__ void decode_v_only(VLane &v, UnitState<NG> &u) {
 // sixteen K quads and sixteen V quads back with 16-byte loads. A tile row is one lane's 64 symbols plus 16 bytes
 // of padding (row stride 80 bytes), which keeps both the stores and the loads off each other's banks; the V tile
 // sits 16 bytes further for the same reason.
-// The same staging serves head_dim 64 (streams of 1024 symbols, 16 blocks of 64): a lane's share is then 32 symbols
-// of each stream (K: half of one token's channels; V: two channels, every token) and a tile row 32 + 16 bytes.
-template <int kDim> constexpr uint32_t kTileRowOf = kDim / 2u + 16u;      // one lane's kDim / 2 symbols + padding
+// The same staging serves head_dim 96, 64 and 32 (streams of 1536 / 1024 / 512 symbols): a lane's share is then
+// kDim / 2 symbols of each stream (K: half of one token's channels; V: kDim / 32 channels, every token). At head_dim
+// 96 with 64-symbol blocks there are 48 blocks for 32 lanes: every lane takes block `lane`, the first sixteen
+// lanes also block `lane + 32`.
+// one lane's kDim / 2 symbols + padding that keeps the row stride off multiples of 64 bytes
+template <int kDim> constexpr uint32_t kTileRowOf = kDim / 2u + ((kDim / 2u + 16u) % 64u == 0 ? 32u : 16u);
 template <int kDim> constexpr uint32_t kTileStreamOf = 32u * kTileRowOf<kDim>;
 constexpr uint32_t kTileBytes = 2u * kTileStreamOf<128> + 32u;
 
@@ -281,8 +284,8 @@ template <int NG, int kMode = kAttend, bool kSplitQ = false, int NB = 32, int kD
 __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(AttentionParams p) {
     constexpr bool kProbe = kMode != kAttend;
     static_assert(!kSplitQ || NG == 2, "split queries use the two-group query layout");
-    static_assert(NB == 32 || NB == 16 || NB == 8, "blocks per stream");
-    static_assert(kDim == 128 || (kDim == 64 && NB != 32), "head_dim 64 goes through the staging tile");
+    static_assert(NB == 32 || NB == 24 || NB == 16 || NB == 12 || NB == 8 || NB == 4, "blocks per stream");
+    static_assert(kDim == 128 || ((kDim == 96 || kDim == 64 || kDim == 32) && NB != 32), "other head_dims go through the staging tile");
     constexpr int kQ = kDim / 8, kVCh = kDim / 32, kSyms = 16 * kDim;   // quads per lane and stream; V channels per lane
     constexpr uint32_t kRowWords = kDim / 4;   // words of half a query row (the channels one lane's K block covers)
     using L = WarpLayout<NG, NB>;
@@ -466,10 +469,16 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                 bool offsets_ok;
                 if constexpr (NB == 32) {
                     offsets_ok = part_offsets_ok(k_part, k_coder, k_bytes, lane) && part_offsets_ok(v_part, v_coder, v_bytes, lane);
-                } else {   // lanes 0..NB-1 hold the K blocks, lanes 16..16+NB-1 the V blocks
+                } else if constexpr (NB <= 16) {   // lanes 0..NB-1 hold the K blocks, lanes 16..16+NB-1 the V blocks
                     const bool mine = (lane & 15u) < static_cast<uint32_t>(NB);
                     offsets_ok = !mine || (lane < 16u ? part_offsets_ok<NB, kSyms>(k_part, k_coder, k_bytes, lane)
                                                       : part_offsets_ok<NB, kSyms>(v_part, v_coder, v_bytes, lane - 16u));
+                } else {   // more blocks than lanes: block lane and block lane + 32 of the 2 NB (K blocks first)
+                    offsets_ok = true;
+#pragma unroll
+                    for (uint32_t gb = lane; gb < 2u * NB; gb += 32u)
+                        offsets_ok = offsets_ok && (gb < static_cast<uint32_t>(NB) ? part_offsets_ok<NB, kSyms>(k_part, k_coder, k_bytes, gb)
+                                                                                 : part_offsets_ok<NB, kSyms>(v_part, v_coder, v_bytes, gb - NB));
                 }
                 const bool good = record_header_ok(hv, entry_cur, p.codebook_id) && __all_sync(0xffffffffu, offsets_ok);
                 uint32_t dump_page = 0u;
@@ -488,9 +497,16 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 
                     if constexpr (NB != 32) {
                         uint8_t *tile = warp_mem + L::kTile;
-                        if ((lane & 15u) < static_cast<uint32_t>(NB)) {
-                            if (lane < 16u) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
-                            else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
+                        if constexpr (NB <= 16) {
+                            if ((lane & 15u) < static_cast<uint32_t>(NB)) {
+                                if (lane < 16u) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
+                                else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
+                            }
+                        } else {   // two rounds: 2 NB blocks dealt over the 32 lanes, K blocks first
+                            for (uint32_t gb = lane; gb < 2u * NB; gb += 32u) {
+                                if (gb < static_cast<uint32_t>(NB)) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, gb, k_slot, k_lut, tile);
+                                else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, gb - NB, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
+                            }
                         }
                         __syncwarp();
                         if (i + 1 < n_pages) issue(0u, entry_next);   // the record is decoded: its stage takes the next one
@@ -706,7 +722,8 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 bool lanes_kernel_supports(const AttentionParams &p) {
     const bool geometry = p.page_tokens == 16 &&
                           ((p.head_dim == 128 && (p.block_size == 64 || p.block_size == 128 || p.block_size == 256)) ||
-                           (p.head_dim == 64 && (p.block_size == 64 || p.block_size == 128)));
+                           ((p.head_dim == 96 || p.head_dim == 64) && (p.block_size == 64 || p.block_size == 128)) ||
+                           (p.head_dim == 32 && p.block_size == 64));
     return geometry && p.group >= 1 && p.group <= 16 &&
            (p.query_type == CF_B200_F16 || p.query_type == CF_B200_F32);
 }
@@ -753,6 +770,11 @@ cudaError_t launch_lanes_attention(const AttentionParams &p, cudaStream_t stream
         return p.block_size == 64 ? launch_for_blocks<16, 64>(p, state->sm_count, stream)
                                   : launch_for_blocks<8, 64>(p, state->sm_count, stream);
     }
+    if (p.head_dim == 96) {
+        return p.block_size == 64 ? launch_for_blocks<24, 96>(p, state->sm_count, stream)
+                                  : launch_for_blocks<12, 96>(p, state->sm_count, stream);
+    }
+    if (p.head_dim == 32) return launch_for_blocks<8, 32>(p, state->sm_count, stream);
     if (p.block_size == 128) return launch_for_blocks<16>(p, state->sm_count, stream);
     if (p.block_size == 256) return launch_for_blocks<8>(p, state->sm_count, stream);
     return launch_for_blocks<32>(p, state->sm_count, stream);

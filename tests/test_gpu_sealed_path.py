@@ -166,24 +166,26 @@ def test_larger_blocks_are_decoded_exactly_and_attend_like_the_oracle(native, or
     assert ok, f"max abs error {err}"
 
 
-@pytest.mark.parametrize("block", [64, 128])
+@pytest.mark.parametrize("geometry", [(64, 64), (64, 128), (96, 64), (96, 128), (32, 64)], ids=lambda g: f"d{g[0]}b{g[1]}")
 @pytest.mark.parametrize("coder", list(CODERS))
-def test_head_dim_64_pages_run_the_lane_kernel(native, oracle, coder, block):
-    """16 x 64 pages (streams of 1024 symbols: 16 or 8 blocks) go through the staging tile of the lane-per-block kernel
-    with half-size lane shares: symbols exact against the oracle, attention against the oracle for groups of four
-    and eight heads, fp16 and fp32 queries."""
+def test_smaller_head_dims_run_the_lane_kernel(native, oracle, coder, geometry):
+    """16 x 64, 16 x 96 and 16 x 32 pages go through the staging tile of the lane-per-block kernel with smaller lane
+    shares (at 16 x 96 with 64-symbol blocks the 48 blocks of a record are dealt over the 32 lanes in two rounds):
+    symbols exact against the oracle, attention against the oracle for groups of four and eight heads, fp16 and fp32
+    queries."""
     import torch
+    d, block = geometry
     rng = np.random.default_rng(41)
     contexts, tails = [48, 16, 37, 160], [3, 0, 0, 9]
     for hq in (16, 8):
-        layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=hq, hkv=2, d=64, t=16, block=block,
+        layer, host, kcb, vcb, tail_k, tail_v, stride = _build(native, oracle, rng, hq=hq, hkv=2, d=d, t=16, block=block,
                                                                coder=CODERS[coder], contexts=contexts, tails=tails,
                                                                noisy_k_pages={(3, 1), (3, 7)})
-        q = rng.standard_normal((4, hq, 64)).astype(np.float16)
+        q = rng.standard_normal((4, hq, d)).astype(np.float16)
         if hq == 16:
             dump = layer.dump_lane_decoders(torch.from_numpy(q).cuda()).cpu().numpy()
             assert layer.device_status() == 0
-            assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}, block=block, d=64) == 2 * (3 + 1 + 3 + 10)
+            assert _expect_dump(dump, host, oracle, kcb, vcb, {0, 1, 2, 3}, block=block, d=d) == 2 * (3 + 1 + 3 + 10)
         want = _oracle_attention(oracle, host, kcb, vcb, contexts, tails, tail_k, tail_v, q, hq, stride)
         for qt in (torch.from_numpy(q).cuda(), torch.from_numpy(q.astype(np.float32)).cuda()):
             got = layer.attention(qt, kernel=native.KERNEL_LANES, min_pages_per_unit=2).cpu().numpy()
