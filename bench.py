@@ -235,14 +235,18 @@ def oracle_check(layer, q, out, slots=None, rows=None):
 
 def other_configurations(a, device):
     """Configurations 3, 4 and 5 of the benchmark at their stated sizes on this GPU, each checked against the CPU oracle
-    on a sample of its sequences (configuration 4: all eight)."""
+    on a sample of its sequences (configuration 4: all eight); with them the block-size dial of configuration 3, the
+    other head dimensions the fast kernel serves, and the sealer's own rate."""
     from types import SimpleNamespace
     from chromofold_b200 import config_bench as cb
     args = SimpleNamespace(steps=max(a.steps // 5, 5), warmup=3, coder=a.coder, batch4=8, ctx4=131072, seqs5=256,
                            prefix5=16384, suffix5=512)
     extra = {"config3": cb.config3(args, device, check=oracle_check)}
+    extra["config3_block_sizes"] = cb.config3_blocks(args, device, check=oracle_check)   # 64 / 128 / 256 symbols per block
     extra["config4"] = cb.config4(args, device, 0, 1, check=oracle_check)
     extra["config5"] = cb.config5(args, device, check=oracle_check)
+    extra["head_dims"] = cb.head_dim_dial(args, device, check=oracle_check)   # 16 x 96 / 64 / 32 pages
+    extra["sealer"] = cb.seal_rate(args, device)
     rows = [r for rows in extra.values() for r in rows if "oracle_check" in r]
     extra["all_within_2e-3_rel_1e-3_abs"] = all(r["oracle_check"]["within_2e-3_rel_1e-3_abs"] for r in rows)
     return extra
