@@ -276,6 +276,38 @@ def test_gpu_sealer_is_byte_exact(native, oracle, coder):
             assert np.array_equal(got, want), (s, h)
 
 
+@pytest.mark.parametrize("coder", list(CODERS))
+def test_gpu_sealer_is_byte_exact_on_fp32_rows(native, oracle, coder):
+    """The stores behind the reference's ABIs hand the sealer fp32 rows (values that binary16 cannot hold): the records
+    must still equal the oracle's byte for byte, full pages and a page of eleven rows."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(29)
+    hkv, d, t = 2, 128, 16
+    hist = hist_for_coder(laplace_codes(rng, 1 << 16, 12.0).astype(np.int16) + 128, CODERS[coder])
+    kcb = oracle.codebook_from_hist(hist)
+    vcb = oracle.codebook_from_hist(hist)
+    layer = _layer(native, kv_heads=hkv, query_heads=4, coder=CODERS[coder], max_sequences=4)
+    layer.set_codebooks(hist, hist)
+    rows = [16, 16, 11, 16]
+    k = (rng.laplace(0.0, 12.0, (4, hkv, t, d)) * 0.0137).astype(np.float32)
+    v = (rng.laplace(0.0, 12.0, (4, hkv, t, d)) * 0.0071).astype(np.float32)
+    k[3] = rng.uniform(-1.0, 1.0, (hkv, t, d)).astype(np.float32)      # does not shrink: stored fixed-width
+    dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    ids = torch.arange(1, 5, dtype=torch.int32, device="cuda")
+    desc = layer._seal_desc(torch.arange(4, dtype=torch.int32, device="cuda"), ids,
+                            torch.as_tensor(rows, dtype=torch.int32, device="cuda"))
+    desc.tail_k, desc.tail_v, desc.tail_type = dk.data_ptr(), dv.data_ptr(), native.F32
+    assert native.lib().cf_b200_seal_pages_async(C.byref(desc), None) == 0
+    torch.cuda.synchronize()
+    assert layer.device_status() == 0
+    for s in range(4):
+        for h in range(hkv):
+            want = oracle.seal_record(k[s, h, :rows[s]], v[s, h, :rows[s]], rows[s], d, t, 64, CODERS[coder], 0, kcb, vcb)[0]
+            got = layer.record_bytes(s + 1, h)
+            assert got.size == want.size and np.array_equal(got, want), (s, h)
+
+
 def test_gpu_sealer_rejects_non_finite(native, oracle):
     import torch
     layer = _layer(native, max_sequences=2)
