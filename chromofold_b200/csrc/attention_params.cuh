@@ -55,6 +55,9 @@ __device__ __forceinline__ PlanHeader *plan_header(const AttentionParams &p) {
 __device__ __forceinline__ uint32_t *chunk_prefix(const AttentionParams &p) {
     return reinterpret_cast<uint32_t *>(p.workspace + p.layout.prefix_offset);
 }
+__device__ __forceinline__ ChunkInfo *chunk_info(const AttentionParams &p) {
+    return reinterpret_cast<ChunkInfo *>(p.workspace + p.layout.info_offset);
+}
 __device__ __forceinline__ float *partial_ptr(const AttentionParams &p, uint32_t chunk, uint32_t local_q_head) {
     return reinterpret_cast<float *>(p.workspace + p.layout.partials_offset) +
            (static_cast<uint64_t>(chunk) * (p.kv_head_span * p.group) + local_q_head) * p.layout.partial_stride_floats;

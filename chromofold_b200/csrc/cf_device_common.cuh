@@ -33,12 +33,21 @@ struct PlanHeader {
     uint32_t pad[7];
 };
 
+// What a (chunk, kv head) unit needs to start, written per chunk by the plan kernel so that the attention kernel's
+// warps read one 32-byte record instead of searching the chunk prefix and chasing four dependent loads.
+struct ChunkInfo {
+    uint32_t seq, slot, sealed, qpos;      // batch entry, its sequence slot, its sealed tokens, its query position
+    uint32_t page_begin, reserved[3];      // first page (index into the slot's page-table row) of the chunk
+};
+static_assert(sizeof(ChunkInfo) == 32, "one chunk record is two 16-byte loads");
+
 struct WorkspaceLayout {
     uint64_t prefix_offset;
     uint64_t shared_offset;          // 0 = no room was set aside for shared-prefix partials
     uint64_t partials_offset;
     uint64_t partial_stride_floats;  // per (chunk, local query head)
     uint64_t chunk_capacity;
+    uint64_t info_offset;            // ChunkInfo[chunk_capacity], behind the partials
 };
 
 __host__ __device__ inline WorkspaceLayout workspace_layout(uint32_t seq_count, uint32_t local_q_heads,
@@ -55,7 +64,9 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(uint32_t seq_count, 
                               w.partial_stride_floats * 4ull + 255ull) / 256ull * 256ull;
     }
     const uint64_t per_chunk = w.partial_stride_floats * 4ull * local_q_heads;
-    w.chunk_capacity = workspace_bytes > w.partials_offset ? (workspace_bytes - w.partials_offset) / per_chunk : 0;
+    w.chunk_capacity = workspace_bytes > w.partials_offset + 32ull
+                           ? (workspace_bytes - w.partials_offset - 32ull) / (per_chunk + sizeof(ChunkInfo)) : 0;
+    w.info_offset = (w.partials_offset + w.chunk_capacity * per_chunk + 31ull) / 32ull * 32ull;
     return w;
 }
 

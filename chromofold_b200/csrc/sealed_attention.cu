@@ -90,14 +90,34 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     uint32_t pages_per_unit = p.min_pages_per_unit;
     uint32_t overflow = 0;
     uint32_t local = 0;  // chunks of this thread's sequences at the current pages_per_unit
-    if (pages_per_unit == 0u) {   // the library's choice: by the number of pages this launch will read
-        for (uint32_t s = begin; s < end; ++s) local += visible_pages(p, s, nullptr, shared);
-        scan[tid] = local;
+    if (pages_per_unit == 0u) {
+        // The library's choice. Units are equal-sized and handed out dynamically to W resident warps, so a launch lasts
+        // about ceil(units / W) rounds of one unit each; a unit costs its pages plus a start-up worth about three
+        // quarters of a page. Warp w scores the candidate 4 + w pages per unit over all sequences; the cheapest that
+        // fits the workspace wins (ties: the larger unit, fewer partials to merge). A launch too small to give every
+        // warp a unit comes out at 4.
+        const uint32_t warp = tid >> 5, lane = tid & 31u, candidate = 4u + warp;
+        uint64_t units = 0;
+        for (uint32_t s = lane; s < p.seq_count; s += 32u) units += (visible_pages(p, s, nullptr, shared) + candidate - 1u) / candidate;
+        for (int o = 16; o > 0; o >>= 1) units += __shfl_xor_sync(0xffffffffu, units, o);
+        const uint32_t pass_heads = p.group <= 4u ? 4u : p.query_type == CF_B200_F32 ? 4u : 8u;
+        const uint64_t warps = 16ull * (p.sm_count ? p.sm_count : 148u);
+        const uint64_t rounds = (units * p.kv_head_span * ((p.group + pass_heads - 1u) / pass_heads) + warps - 1ull) / warps;
+        uint64_t cost = rounds * (4ull * candidate + 3ull);
+        if (units > p.layout.chunk_capacity || units == 0) cost = ~0ull;
+        if (lane == 0) reinterpret_cast<unsigned long long *>(scan)[warp] = cost;   // 32 x 8 bytes of the scan array
         __syncthreads();
         if (tid == 0) {
-            uint64_t total = 0;
-            for (uint32_t i = 0; i < kPlanThreads; ++i) total += scan[i];
-            s_total = default_pages_per_unit(total, p.kv_head_span);
+            uint32_t best = 16u;
+            unsigned long long best_cost = ~0ull;
+            for (uint32_t w = 0; w < kPlanThreads / 32; ++w) {
+                const unsigned long long c = reinterpret_cast<unsigned long long *>(scan)[w];
+                if (c <= best_cost && c != ~0ull) {
+                    best_cost = c;
+                    best = 4u + w;
+                }
+            }
+            s_total = best;
         }
         __syncthreads();
         pages_per_unit = s_total;
@@ -121,10 +141,42 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         if (attempt == 31 || pages_per_unit >= (1u << 30)) { overflow = 1; break; }
         pages_per_unit <<= 1;
     }
+    // Chunk prefix per sequence, and every chunk's start-up record (the attention kernel's warps read that record, not
+    // the prefix). Few sequences with many chunks each: a warp per sequence writes the records side by side; many
+    // sequences with few chunks: every thread writes those of its own sequences.
     uint32_t running = scan[tid] - local;
+    ChunkInfo *info = chunk_info(p);
+    const bool by_warp = !overflow && s_total >= 8ull * p.seq_count;
     for (uint32_t s = begin; s < end; ++s) {
         prefix[s] = overflow ? 0u : running;
-        running += (visible_pages(p, s, nullptr, shared) + pages_per_unit - 1u) / pages_per_unit;
+        uint32_t first_page;
+        const uint32_t chunks = (visible_pages(p, s, &first_page, shared) + pages_per_unit - 1u) / pages_per_unit;
+        if (!overflow && !by_warp && chunks) {
+            const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
+            const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
+            for (uint32_t k = 0; k < chunks; ++k) {
+                uint4 *dst = reinterpret_cast<uint4 *>(info + running + k);
+                dst[0] = make_uint4(s, slot, sealed, qpos);
+                dst[1] = make_uint4(first_page + k * pages_per_unit, 0u, 0u, 0u);
+            }
+        }
+        running += chunks;
+    }
+    if (by_warp) {
+        __syncthreads();   // prefix[] is complete
+        for (uint32_t s = tid >> 5; s < p.seq_count; s += kPlanThreads / 32) {
+            const uint32_t c0 = prefix[s], c1 = s + 1u < p.seq_count ? prefix[s + 1u] : s_total;
+            if (c1 == c0) continue;
+            uint32_t first_page;
+            visible_pages(p, s, &first_page, shared);
+            const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
+            const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
+            for (uint32_t c = c0 + (tid & 31u); c < c1; c += 32u) {
+                uint4 *dst = reinterpret_cast<uint4 *>(info + c);
+                dst[0] = make_uint4(s, slot, sealed, qpos);
+                dst[1] = make_uint4(first_page + (c - c0) * pages_per_unit, 0u, 0u, 0u);
+            }
+        }
     }
     if (tid == 0) {
         prefix[p.seq_count] = overflow ? 0u : s_total;
@@ -597,7 +649,7 @@ extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_seal
     const uint32_t ppu = d->min_pages_per_unit ? d->min_pages_per_unit : cfb::default_pages_per_unit(total_pages, span);
     const uint64_t chunks = total_pages / ppu + d->seq_count + 1;  // each sequence may round up once
     const cfb::WorkspaceLayout w = cfb::workspace_layout(d->seq_count, local_q, d->head_dim, 0, d->shared_prefix_pages != 0);
-    *out_bytes = w.partials_offset + chunks * w.partial_stride_floats * 4ull * local_q;
+    *out_bytes = w.partials_offset + chunks * (w.partial_stride_floats * 4ull * local_q + sizeof(cfb::ChunkInfo)) + 64ull;
     return CF_OK;
 }
 

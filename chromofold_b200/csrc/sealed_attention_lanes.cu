@@ -317,7 +317,6 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
     __syncthreads();
 
     PlanHeader *hdr = plan_header(p);
-    const uint32_t *prefix = chunk_prefix(p);
     const uint32_t subgroups = (p.group + kPassHeads - 1u) / kPassHeads;   // 4 NG query heads per pass
     const uint32_t unit_count = hdr->chunk_count * p.kv_head_span * subgroups;
     const uint32_t pages_per_unit = hdr->pages_per_unit;
@@ -344,15 +343,12 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
         const uint32_t G = min(kPassHeads, p.group - kPassHeads * sub);       // query heads served by this pass
         const uint32_t q_head_base = kv_head * p.group + kPassHeads * sub;    // first of them
         const uint32_t out_head_base = head_local * p.group + kPassHeads * sub;
-        const uint32_t seq = sequence_of_chunk(prefix, p.seq_count, chunk);
-        const uint32_t slot = slot_of(p, seq);
-        const uint32_t sealed = p.seq_sealed_tokens[slot];
-        const uint32_t tail = p.tail_tokens ? p.tail_tokens[slot] : 0u;
-        const uint32_t qpos = query_position(p, seq, sealed, tail);
+        // the chunk's start-up record, written by the plan kernel (which also took the shared pages off its front)
+        const uint4 *ci = reinterpret_cast<const uint4 *>(chunk_info(p) + chunk);
+        const uint4 ci0 = ci[0];
+        const uint32_t seq = ci0.x, slot = ci0.y, sealed = ci0.z, qpos = ci0.w, page_begin = ci[1].x;
         const uint32_t first_token = window_begin(qpos, p.causal_window);
         const uint32_t pages = min((sealed + 15u) / 16u, qpos / 16u + 1u);
-        const uint32_t first_page = min(max(first_token / 16u, hdr->shared_pages), pages);   // shared pages are not this kernel's
-        const uint32_t page_begin = first_page + (chunk - prefix[seq]) * pages_per_unit;
         const uint32_t page_end = min(page_begin + pages_per_unit, pages);
         const uint32_t n_pages = page_end > page_begin ? page_end - page_begin : 0u;
         const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot) * p.page_table_stride;
