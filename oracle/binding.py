@@ -15,7 +15,8 @@ CODER_FIXED8, CODER_HUFFMAN, CODER_RANS, CODER_RANS_SPLIT4, CODER_HUFFMAN_SPLIT4
 def build(with_ref=None):
     """Compile liboracle.so; also oracle/_ref when the reference tree is present (or with_ref=True)."""
     targets = ["all"]
-    ref_root = os.environ.get("CF_REFERENCE_ROOT", "/root/reference")
+    # the reference tree: CF_REFERENCE_ROOT, or a checkout named `reference` beside this repository
+    ref_root = os.environ.get("CF_REFERENCE_ROOT", os.path.abspath(os.path.join(HERE, "..", "..", "reference")))
     if with_ref is None:
         with_ref = os.path.isdir(os.path.join(ref_root, "src", "runtime"))
     if with_ref:

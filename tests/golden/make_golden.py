@@ -176,7 +176,7 @@ def delta_cluster():
     """A small reference/delta cluster frozen by the reference's own exporter (tools/export_delta.py, numpy only):
     base + sparse per-member overrides + the original sequences the fetch must reproduce."""
     import subprocess
-    ref_root = os.environ.get("CF_REFERENCE_ROOT", "/root/reference")
+    ref_root = os.environ.get("CF_REFERENCE_ROOT", os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference")))
     subprocess.run([sys.executable, os.path.join(ref_root, "tools", "export_delta.py"), os.path.join(HERE, "delta_cluster.cfdc"),
                     "--members", "12", "--base", "600", "--divergence", "0.02", "--suffix", "24", "--vocab", "50000",
                     "--seed", "7"], check=True)
