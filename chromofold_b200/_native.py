@@ -38,7 +38,7 @@ class SealedAttentionDesc(C.Structure):
         ("softmax_scale", _f32), ("causal_window", _u32),
         ("workspace", _vp), ("workspace_bytes", _u64), ("min_pages_per_unit", _u32), ("kernel", _u32),
         ("status", _vp), ("tail_type", _u32), ("tail_capacity", _u32), ("query_positions", _vp),
-        ("shared_prefix_pages", _u32), ("reserved0", _u32),
+        ("shared_prefix_pages", _u32), ("reserved0", _u32), ("row_map", _vp),
     ]
 
 
@@ -164,7 +164,7 @@ class MgShard(C.Structure):    # cf_b200_mg_shard
 
 class MgCounters(C.Structure):
     _fields_ = [("steps", _u64), ("attention_launches", _u64), ("peer_copies", _u64), ("peer_bytes", _u64),
-                ("refused_batches", _u64)]
+                ("refused_batches", _u64), ("direct_steps", _u64)]
 
 
 MG_BY_SEQUENCE, MG_BY_KV_HEAD = 1, 2

@@ -291,13 +291,15 @@ class SealedKvLayer:
     @_on_own_device
     def attention(self, queries, slots=None, out=None, *, softmax_scale=None, causal_window=0, kernel=N.KERNEL_AUTO,
                   kv_head_begin=0, kv_head_span=0, min_pages_per_unit=0, stages=N.STAGE_ALL, shared_prefix_pages=0,
-                  query_positions=None):
+                  query_positions=None, row_map=None):
         """Decode-step attention: queries [n, query_heads, head_dim] (float16 or float32) -> float32 output.
         shared_prefix_pages = P states that the first P pages of every listed sequence are the same pages (as after
         copy_sequence): they are then decoded once for all the sequences instead of once per sequence.
         query_positions (int32 device tensor [n]) gives every entry's query-token position instead of "right after
-        everything cached"; entries naming the same slot at different positions are multi-query (prefill) attention."""
-        n = queries.shape[0]
+        everything cached"; entries naming the same slot at different positions are multi-query (prefill) attention.
+        row_map (int32 device tensor [n], with `slots` and `out` given): entry i reads row row_map[i] of `queries` and
+        writes row row_map[i] of `out`, so a call can serve a subset of a larger batch in place."""
+        n = queries.shape[0] if row_map is None else int(row_map.numel())
         if out is None:
             out = torch.zeros((n, self.query_heads, self.head_dim), dtype=torch.float32, device=self.device)
         d = self._attention_desc(queries, out, n, slots)
@@ -309,6 +311,8 @@ class SealedKvLayer:
         d.shared_prefix_pages = shared_prefix_pages
         if query_positions is not None:
             d.query_positions = query_positions.data_ptr()
+        if row_map is not None:
+            d.row_map = row_map.data_ptr()
         N.check("sealed_attention", self.lib.cf_b200_sealed_attention_stages_async(C.byref(d), C.c_uint32(stages),
                                                                                       _stream_ptr()))
         return out

@@ -26,6 +26,7 @@ struct AttentionParams {
     const uint32_t *tail_tokens;
     uint32_t tail_type, tail_capacity;
     const uint32_t *query_positions;
+    const uint32_t *row_map;        // optional: batch entry -> row of queries / output
     // io
     const void *queries;
     void *output;
@@ -68,6 +69,10 @@ __device__ __forceinline__ float *shared_partial_ptr(const AttentionParams &p, u
            ((static_cast<uint64_t>(chunk) * p.seq_count + seq) * (p.kv_head_span * p.group) + local_q_head) *
                p.layout.partial_stride_floats;
 }
+// Row of the query and output tensors that batch entry `seq` stands for.
+__device__ __forceinline__ uint32_t row_of(const AttentionParams &p, uint32_t seq) {
+    return p.row_map ? p.row_map[seq] : seq;
+}
 __device__ __forceinline__ uint32_t slot_of(const AttentionParams &p, uint32_t seq) {
     return p.seq_slots ? p.seq_slots[seq] : seq;
 }
@@ -93,6 +98,7 @@ __device__ __forceinline__ uint32_t sequence_of_chunk(const uint32_t *prefix, ui
 #endif
 
 // Implemented in sealed_attention.cu
+cf_status sealed_attention_stages(const cf_b200_sealed_attention_desc *d, uint32_t stages, void *stream, bool output_on_peer);
 cudaError_t launch_plan(const AttentionParams &p, cudaStream_t stream);
 cudaError_t launch_combine(const AttentionParams &p, cudaStream_t stream);
 cudaError_t launch_generic_attention(const AttentionParams &p, cudaStream_t stream);

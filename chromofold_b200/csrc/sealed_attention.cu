@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
             for (uint32_t k = 0; k < chunks; ++k) {
                 uint4 *dst = reinterpret_cast<uint4 *>(info + running + k);
                 dst[0] = make_uint4(s, slot, sealed, qpos);
-                dst[1] = make_uint4(first_page + k * pages_per_unit, 0u, 0u, 0u);
+                dst[1] = make_uint4(first_page + k * pages_per_unit, row_of(p, s), 0u, 0u);
             }
         }
         running += chunks;
@@ -171,10 +171,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
             visible_pages(p, s, &first_page, shared);
             const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
             const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
+            const uint32_t row = row_of(p, s);
             for (uint32_t c = c0 + (tid & 31u); c < c1; c += 32u) {
                 uint4 *dst = reinterpret_cast<uint4 *>(info + c);
                 dst[0] = make_uint4(s, slot, sealed, qpos);
-                dst[1] = make_uint4(first_page + (c - c0) * pages_per_unit, 0u, 0u, 0u);
+                dst[1] = make_uint4(first_page + (c - c0) * pages_per_unit, row, 0u, 0u);
             }
         }
     }
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
         const uint32_t page_end = min(page_begin + pages_per_unit, first_page + vis);
 
         for (uint32_t i = tid; i < G * D; i += kGenericThreads) {
-            q[i] = load_query(p, seq, kv_head * G + i / D, i % D) * (p.softmax_scale * kLog2e);
+            q[i] = load_query(p, row_of(p, seq), kv_head * G + i / D, i % D) * (p.softmax_scale * kLog2e);
             acc[i] = 0.0f;
         }
         if (tid < G) {
@@ -402,12 +403,13 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
     const uint32_t first_token = window_begin(qpos, p.causal_window);
     const uint32_t *prefix = chunk_prefix(p);
     const uint32_t c0 = prefix[seq], c1 = prefix[seq + 1];
+    const uint32_t row = row_of(p, seq);   // of the query and output tensors
 
     // tail scores (binary16 rows, one warp per token)
     for (uint32_t t = warp; t < tail; t += kCombineThreads / 32) {
-        const uint64_t row = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * C + t) * D;
+        const uint64_t tail_row = ((static_cast<uint64_t>(slot) * p.kv_head_count + kv_head) * C + t) * D;
         float dot = 0.0f;
-        for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, seq, q_head, d) * load_tail(p.tail_k, p.tail_type, row + d);
+        for (uint32_t d = lane; d < D; d += 32) dot += load_query(p, row, q_head, d) * load_tail(p.tail_k, p.tail_type, tail_row + d);
         dot = warp_sum(dot);
         if (lane == 0)
             tail_scores[t] = (sealed + t >= first_token && sealed + t <= qpos) ? dot * p.softmax_scale * kLog2e : -CUDART_INF_F;
@@ -478,7 +480,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
     }
     if (tid < D) {
         const float out = l > 0.0f ? a / l : 0.0f;  // no visible token: zeros (paged_kv_attention.cu:170-173)
-        const uint64_t i = (static_cast<uint64_t>(seq) * p.query_head_count + q_head) * D + tid;
+        const uint64_t i = (static_cast<uint64_t>(row) * p.query_head_count + q_head) * D + tid;
         if (p.output_type == CF_B200_F16) reinterpret_cast<__half *>(p.output)[i] = __float2half_rn(out);
         else reinterpret_cast<float *>(p.output)[i] = out;
     }
@@ -548,6 +550,7 @@ bool fill_params(const cf_b200_sealed_attention_desc *d, AttentionParams *p) {
     p->tail_tokens = d->tail_tokens;
     p->tail_type = d->tail_type == CF_B200_F32 ? CF_B200_F32 : CF_B200_F16;
     p->query_positions = d->query_positions;
+    p->row_map = d->row_map;
     p->tail_capacity = d->tail_capacity ? d->tail_capacity : d->page_tokens;
     p->queries = d->queries;
     p->output = d->output;
@@ -655,11 +658,18 @@ extern "C" cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_seal
 
 extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_attention_desc *d, uint32_t stages,
                                                            void *stream) {
+    return cfb::sealed_attention_stages(d, stages, stream, false);
+}
+
+// output_on_peer: the one exception to "every pointer is the current device's" — the multi-GPU scheduler lets the
+// combine kernel store its output rows straight into the root GPU's tensor (plain coalesced stores over a peer mapping
+// the scheduler has enabled and checked). Everything that is READ stays local.
+cf_status cfb::sealed_attention_stages(const cf_b200_sealed_attention_desc *d, uint32_t stages, void *stream, bool output_on_peer) {
     const cf_status valid = cf_b200_sealed_attention_validate(d);
     if (valid != CF_OK) return valid;
     if (stages == 0 || stages > 7u) return CF_ERR_INVALID_ARGUMENT;
     if (!cfb::on_current_device(d->arena) || !cfb::on_current_device(d->workspace) || !cfb::on_current_device(d->queries) ||
-        !cfb::on_current_device(d->output))
+        !cfb::on_current_device(d->row_map) || (!output_on_peer && !cfb::on_current_device(d->output)))
         return CF_ERR_INVALID_ARGUMENT;   // memory of another GPU: the call must be made with that GPU current
     AttentionParams p;
     cfb::fill_params(d, &p);
@@ -671,7 +681,7 @@ extern "C" cf_status cf_b200_sealed_attention_stages_async(const cf_b200_sealed_
     const bool use_lanes = d->kernel == CF_B200_KERNEL_LANES || probe ||
                            (d->kernel == CF_B200_KERNEL_AUTO && lanes_ok);
     // the shared-prefix kernel works on rows of 128 = whole query groups and on pages every query token sees in full
-    if (use_lanes && p.block_size == 64 && p.head_dim == 128 && p.decode_probe != 1u && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
+    if (use_lanes && p.block_size == 64 && p.head_dim == 128 && d->row_map == nullptr && p.decode_probe != 1u && d->shared_prefix_pages && d->causal_window == 0 && 128u % p.group == 0) {
         static cfb::LauncherState table[64];
         cudaError_t e;
         const cfb::LauncherState *state = cfb::launcher_state(table, &e);

@@ -346,7 +346,8 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
         // the chunk's start-up record, written by the plan kernel (which also took the shared pages off its front)
         const uint4 *ci = reinterpret_cast<const uint4 *>(chunk_info(p) + chunk);
         const uint4 ci0 = ci[0];
-        const uint32_t seq = ci0.x, slot = ci0.y, sealed = ci0.z, qpos = ci0.w, page_begin = ci[1].x;
+        const uint4 ci1 = ci[1];
+        const uint32_t slot = ci0.y, sealed = ci0.z, qpos = ci0.w, page_begin = ci1.x, q_row = ci1.y;   // ci0.x = batch entry
         const uint32_t first_token = window_begin(qpos, p.causal_window);
         const uint32_t pages = min((sealed + 15u) / 16u, qpos / 16u + 1u);
         const uint32_t page_end = min(page_begin + pages_per_unit, pages);
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
         if constexpr (NG == 1) {
             const bool live = q_col_mine && q_head_of_col < G;
             const __half *qrow = reinterpret_cast<const __half *>(p.queries) +
-                                 (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base + q_head_of_col) * kDim +
+                                 (static_cast<uint64_t>(q_row) * p.query_head_count + q_head_base + q_head_of_col) * kDim +
                                  (kDim / 2) * (t & 1u);
 #pragma unroll
             for (int s = 0; s < kQ; ++s) {
@@ -368,7 +369,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
             }
         } else if constexpr (kSplitQ) {
             const float2 *qsrc = reinterpret_cast<const float2 *>(
-                reinterpret_cast<const float *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * kDim);
+                reinterpret_cast<const float *>(p.queries) + (static_cast<uint64_t>(q_row) * p.query_head_count + q_head_base) * kDim);
             __syncwarp();  // the previous unit's readers are done
 #pragma unroll
             for (int j = 0; j < kDim / 16; ++j) {    // 4 heads x kDim / 2 channel pairs; row = head*2 + half, residues 8 rows further
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
             qs.group_stride = q_col_mine ? 8u * L::kQRowWords * 4u : 0u;
         } else {
             const uint32_t *qsrc = reinterpret_cast<const uint32_t *>(
-                reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(seq) * p.query_head_count + q_head_base) * kDim);
+                reinterpret_cast<const __half *>(p.queries) + (static_cast<uint64_t>(q_row) * p.query_head_count + q_head_base) * kDim);
             __syncwarp();  // the previous unit's readers are done
 #pragma unroll
             for (int j = 0; j < kDim / 8; ++j) {   // 8 heads x kDim / 2 words; row = head*2 + half

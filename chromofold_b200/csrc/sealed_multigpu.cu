@@ -3,11 +3,13 @@
 // peer copies. No kernel here reads or writes another GPU's memory; the two row-permutation kernels run on the root
 // GPU over the root GPU's own buffers.
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
 #include <atomic>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -16,6 +18,7 @@
 #include <thread>
 #include <vector>
 
+#include "attention_params.cuh"
 #include "chromofold_b200/sealed_kv_multigpu.h"
 
 namespace {
@@ -49,6 +52,7 @@ struct StepJob {
     const void *root_queries = nullptr;
     void *root_output = nullptr;
     uint32_t first_row[CF_B200_MG_MAX_DEVICES] = {};   // by-sequence: where the device's rows start in device-major order
+    bool direct = false;   // this step's outputs are stored straight into root_output by every device
 };
 
 struct cf_b200_mg_scheduler {
@@ -75,6 +79,38 @@ struct cf_b200_mg_scheduler {
     uint32_t *d_perm = nullptr;        // root device
     uint32_t *h_perm = nullptr;        // pinned
     std::vector<uint32_t> last_perm;   // what d_perm holds
+    // Direct output (every device can store into the root's memory): a device keeps the whole batch's query rows
+    // (one peer copy per step) and the rows of its own entries as a row map; its combine kernel stores the output rows
+    // straight into the root's tensor. No staging, no permute kernels, no copies back.
+    bool direct = false;
+    std::vector<uint8_t *> q_full;             // per device: max_rows query rows (nullptr on the root)
+    std::vector<uint32_t *> d_rows, h_rows;    // per device: row map on the device / pinned copy of what it holds
+    std::vector<uint32_t> rows_held;           // per device: entries of the row map that are valid (0 = none uploaded)
+    const void *checked_output = nullptr;      // the last root_output whose mapping was checked, and the answer
+    bool checked_writable = false;
+
+    // Whether every other device may STORE to `ptr` (memory of the root): asked of the driver per device
+    // (CU_POINTER_ATTRIBUTE_ACCESS_FLAGS with that device current). Anything but a clear "read and write" — an
+    // allocation from a pool that was not opened to the peers, a driver that does not answer — keeps the copy path.
+    bool every_device_may_store(const void *ptr) {
+        if (ptr == checked_output) return checked_writable;
+        using QueryFn = CUresult (*)(void *, CUpointer_attribute, CUdeviceptr);
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        bool writable = cudaGetDriverEntryPoint("cuPointerGetAttribute", &entry, cudaEnableDefault, &found) == cudaSuccess &&
+                        found == cudaDriverEntryPointSuccess && entry != nullptr;
+        for (size_t d = 1; d < ordinals.size() && writable; ++d) {
+            unsigned long long flags = 0;
+            writable = cudaSetDevice(ordinals[d]) == cudaSuccess &&
+                       reinterpret_cast<QueryFn>(entry)(&flags, CU_POINTER_ATTRIBUTE_ACCESS_FLAGS,
+                                                        reinterpret_cast<CUdeviceptr>(ptr)) == CUDA_SUCCESS &&
+                       flags == CU_POINTER_ATTRIBUTE_ACCESS_FLAG_READWRITE;
+        }
+        cudaGetLastError();
+        checked_output = ptr;
+        checked_writable = writable;
+        return writable;
+    }
     cf_b200_mg_counters counters{};
     mutable std::mutex mutex;
     std::string error;
@@ -109,6 +145,12 @@ struct cf_b200_mg_scheduler {
             if (d < streams.size() && streams[d]) cudaStreamDestroy(streams[d]);
             if (d < done.size() && done[d]) cudaEventDestroy(done[d]);
         }
+        for (size_t d = 0; d < ordinals.size(); ++d) {
+            if (cudaSetDevice(ordinals[d]) != cudaSuccess) continue;
+            if (d < q_full.size() && q_full[d]) cudaFree(q_full[d]);
+            if (d < d_rows.size() && d_rows[d]) cudaFree(d_rows[d]);
+            if (d < h_rows.size() && h_rows[d]) cudaFreeHost(h_rows[d]);
+        }
         if (!ordinals.empty() && cudaSetDevice(ordinals[0]) == cudaSuccess) {
             if (ready) cudaEventDestroy(ready);
             if (staging_q) cudaFree(staging_q);
@@ -135,6 +177,38 @@ cf_status submit_device(cf_b200_mg_scheduler *s, uint32_t d) {
     };
     cudaError_t e;
     if ((e = cudaStreamWaitEvent(stream, s->ready, 0)) != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+    if (job.direct) {
+        cf_b200_sealed_attention_desc local = desc;
+        if (d != 0) {   // the batch's query rows, whole: reads stay local to this device
+            uint8_t *q = job.mode == CF_B200_MG_BY_SEQUENCE ? s->q_full[d] : static_cast<uint8_t *>(const_cast<void *>(desc.queries));
+            e = cudaMemcpyPeerAsync(q, s->ordinals[d], job.root_queries, s->ordinals[0], q_row * job.row_count, stream);
+            if (e != cudaSuccess) return cuda_fail(e, "query rows out");
+            local.queries = q;
+        } else {
+            local.queries = job.root_queries;
+        }
+        local.output = job.root_output;   // rows (or head columns) are stored where the caller wants them
+        if (job.mode == CF_B200_MG_BY_SEQUENCE && job.shards[d].rows) {
+            const uint32_t *rows = job.shards[d].rows;
+            bool changed = s->rows_held[d] != desc.seq_count;
+            for (uint32_t i = 0; !changed && i < desc.seq_count; ++i) changed = s->h_rows[d][i] != rows[i];
+            if (changed) {   // a new placement: a few hundred bytes, and the pinned copy must not change under a copy in flight
+                if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return cuda_fail(e, "row map upload");
+                std::memcpy(s->h_rows[d], rows, sizeof(uint32_t) * desc.seq_count);
+                e = cudaMemcpyAsync(s->d_rows[d], s->h_rows[d], sizeof(uint32_t) * desc.seq_count, cudaMemcpyHostToDevice, stream);
+                if (e != cudaSuccess) return cuda_fail(e, "row map upload");
+                s->rows_held[d] = desc.seq_count;
+            }
+            local.row_map = s->d_rows[d];
+        }
+        const cf_status launched = cfb::sealed_attention_stages(&local, CF_B200_STAGE_PLAN | CF_B200_STAGE_ATTENTION | CF_B200_STAGE_COMBINE, stream, d != 0);
+        if (launched != CF_OK) {
+            error = "attention launch failed on a device";
+            return launched;
+        }
+        if ((e = cudaEventRecord(s->done[d], stream)) != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+        return CF_OK;
+    }
     if (job.mode == CF_B200_MG_BY_SEQUENCE) {
         const uint32_t at = job.first_row[d];
         e = cudaMemcpyPeerAsync(const_cast<void *>(desc.queries), s->ordinals[d], s->staging_q + q_row * at, s->ordinals[0],
@@ -228,19 +302,35 @@ extern "C" cf_b200_mg_scheduler *cf_b200_mg_create(const cf_b200_mg_config *c) {
     s->done.assign(c->device_count, nullptr);
     s->failed.assign(c->device_count, 0);
     DeviceGuard guard;
-    bool ok = true;
+    bool ok = true, every_device_maps_the_root = true;
     for (uint32_t d = 0; d < c->device_count && ok; ++d) {
         ok = cudaSetDevice(s->ordinals[d]) == cudaSuccess &&
              cudaStreamCreateWithFlags(&s->streams[d], cudaStreamNonBlocking) == cudaSuccess &&
              cudaEventCreateWithFlags(&s->done[d], cudaEventDisableTiming) == cudaSuccess;
         if (ok && d > 0) {   // a direct path between the root and this device, both ways, where the box has one
             int can = 0;
+            bool mapped = false;
             if (cudaDeviceCanAccessPeer(&can, s->ordinals[d], s->ordinals[0]) == cudaSuccess && can) {
                 const cudaError_t e = cudaDeviceEnablePeerAccess(s->ordinals[0], 0);
                 if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) ok = false;
+                mapped = ok;
                 cudaGetLastError();
             }
+            if (!mapped) every_device_maps_the_root = false;
         }
+    }
+    // direct output needs every device to have the root's memory mapped; CHROMOFOLD_B200_MG_COPIES=1 keeps the copy path
+    const char *copies = std::getenv("CHROMOFOLD_B200_MG_COPIES");
+    s->direct = ok && every_device_maps_the_root && !(copies && copies[0] == '1');
+    s->q_full.assign(c->device_count, nullptr);
+    s->d_rows.assign(c->device_count, nullptr);
+    s->h_rows.assign(c->device_count, nullptr);
+    s->rows_held.assign(c->device_count, 0u);
+    for (uint32_t d = 0; d < c->device_count && ok && s->direct; ++d) {
+        ok = cudaSetDevice(s->ordinals[d]) == cudaSuccess &&
+             (d == 0 || cudaMalloc(&s->q_full[d], s->query_row_bytes() * c->max_rows) == cudaSuccess) &&
+             cudaMalloc(&s->d_rows[d], sizeof(uint32_t) * c->max_rows) == cudaSuccess &&
+             cudaMallocHost(&s->h_rows[d], sizeof(uint32_t) * c->max_rows) == cudaSuccess;
     }
     if (ok) ok = cudaSetDevice(s->ordinals[0]) == cudaSuccess;
     for (uint32_t d = 1; d < c->device_count && ok; ++d) {
@@ -392,6 +482,7 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
     DeviceGuard guard;
     cudaStream_t root_stream = static_cast<cudaStream_t>(root_stream_ptr);
     const size_t q_row = s->query_row_bytes(), o_row = s->output_row_bytes();
+    const bool direct = s->direct && s->every_device_may_store(root_output);
     cudaError_t e = cudaSetDevice(s->ordinals[0]);
     if (e != cudaSuccess) return s->cuda_fail(e, "cudaSetDevice");
     StepJob &job = s->job;
@@ -400,9 +491,10 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
     job.row_count = row_count;
     job.root_queries = root_queries;
     job.root_output = root_output;
+    job.direct = direct;
     const uint32_t q_units = static_cast<uint32_t>(q_row / 16u), o_units = static_cast<uint32_t>(o_row / 16u);
 
-    if (mode == CF_B200_MG_BY_SEQUENCE) {
+    if (mode == CF_B200_MG_BY_SEQUENCE && !direct) {
         // query rows into device-major order on the root (one kernel), one copy per device out, one per device back,
         // output rows back into batch order (one kernel)
         uint32_t at = 0;
@@ -425,7 +517,7 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
         const uint32_t blocks = std::min<uint32_t>(1024u, (listed * q_units + 255u) / 256u);
         permute_rows_kernel<true><<<blocks, 256, 0, root_stream>>>(static_cast<const uint4 *>(root_queries),
                                                                    reinterpret_cast<uint4 *>(s->staging_q), s->d_perm, listed, q_units);
-    } else {
+    } else if (mode == CF_B200_MG_BY_KV_HEAD) {
         for (uint32_t d = 0; d < devices; ++d)
             if (shards[d].desc.seq_count && (shards[d].rows || shards[d].desc.seq_count != row_count))
                 return s->fail(CF_ERR_INVALID_ARGUMENT, "kv-head sharding serves every row on every device");
@@ -446,21 +538,26 @@ extern "C" cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *s, const cf_
         if (d != 0) {
             const cf_b200_sealed_attention_desc &desc = shards[d].desc;
             const uint32_t span = desc.kv_head_span ? desc.kv_head_span : desc.kv_head_count - desc.kv_head_begin;
-            s->counters.peer_copies += 2u;
-            s->counters.peer_bytes += mode == CF_B200_MG_BY_SEQUENCE
+            s->counters.peer_copies += direct ? 1u : 2u;   // direct: the outputs cross as stores of the combine kernel
+            s->counters.peer_bytes += direct ? q_row * row_count + (mode == CF_B200_MG_BY_SEQUENCE
+                                                      ? o_row * desc.seq_count
+                                                      : static_cast<size_t>(span) * (desc.query_head_count / desc.kv_head_count) *
+                                                            desc.head_dim * 4u * row_count)
+                                      : mode == CF_B200_MG_BY_SEQUENCE
                                           ? (q_row + o_row) * desc.seq_count
                                           : q_row * row_count + static_cast<size_t>(span) * (desc.query_head_count / desc.kv_head_count) *
                                                                     desc.head_dim * 4u * row_count;
         }
         if ((e = cudaStreamWaitEvent(root_stream, s->done[d], 0)) != cudaSuccess) return s->cuda_fail(e, "cudaStreamWaitEvent");
     }
-    if (mode == CF_B200_MG_BY_SEQUENCE) {
+    if (mode == CF_B200_MG_BY_SEQUENCE && !direct) {
         const uint32_t oblocks = std::min<uint32_t>(1024u, (listed * o_units + 255u) / 256u);
         permute_rows_kernel<false><<<oblocks, 256, 0, root_stream>>>(reinterpret_cast<const uint4 *>(s->staging_out),
                                                                      static_cast<uint4 *>(root_output), s->d_perm, listed, o_units);
         if ((e = cudaPeekAtLastError()) != cudaSuccess) return s->cuda_fail(e, "row permutation");
     }
     ++s->counters.steps;
+    if (direct) ++s->counters.direct_steps;
     s->error.clear();
     return CF_OK;
 }

@@ -80,14 +80,21 @@ typedef struct cf_b200_mg_shard {
  * device's memory (query_type / float). On root_stream (a stream of the root device) the call is ordered like a
  * kernel launch: it starts after the work queued there before, and work queued there afterwards sees the gathered
  * output. Per device: query rows are copied over, cf_b200_sealed_attention_async runs on the device's own stream,
- * the output rows (or columns) are copied back. Returns CF_ERR_UNSUPPORTED when a listed device is marked failed. */
+ * the output rows (or columns) are copied back. Returns CF_ERR_UNSUPPORTED when a listed device is marked failed.
+ *
+ * Direct output: where every GPU has the root's memory mapped (peer access, enabled at creation) and the driver
+ * confirms, per root_output, that every GPU may store to it, a GPU keeps a copy of the batch's query rows (one peer
+ * copy per step), gets the rows of its entries as a row map (cf_b200_sealed_attention_desc.row_map) and its combine
+ * kernel stores the output rows straight into root_output: no staging, no row permutation, no copies back. All loads
+ * stay local to the GPU that issues them. CHROMOFOLD_B200_MG_COPIES=1 in the environment keeps the copy path. */
 cf_status cf_b200_mg_execute_async(cf_b200_mg_scheduler *scheduler, const cf_b200_mg_shard *shards, uint32_t shard_count,
                                    const void *root_queries, void *root_output, uint32_t row_count, uint32_t mode,
                                    void *root_stream);
 
-/* Launch counters since creation: steps, per-device attention launches, peer copies issued and their bytes. */
+/* Launch counters since creation: steps, per-device attention launches, peer copies issued, bytes that crossed between
+ * GPUs, refused batches, and the steps whose outputs were stored directly into the root's tensor (below). */
 typedef struct cf_b200_mg_counters {
-    uint64_t steps, attention_launches, peer_copies, peer_bytes, refused_batches;
+    uint64_t steps, attention_launches, peer_copies, peer_bytes, refused_batches, direct_steps;
 } cf_b200_mg_counters;
 cf_status cf_b200_mg_get_counters(const cf_b200_mg_scheduler *scheduler, cf_b200_mg_counters *out);
 

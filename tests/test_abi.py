@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported(native):
 def test_struct_sizes_match_the_headers(native):
     # computed by hand from the header layouts; a mismatch means the ctypes mirror drifted
     assert C.sizeof(native.CodebookTables) == 4096 * 4 + 256 * 2 + 256 * 2 + 4096 * 2 + 256 * 4 + 256 * 8
-    assert C.sizeof(native.SealedAttentionDesc) == 216
+    assert C.sizeof(native.SealedAttentionDesc) == 224
     assert C.sizeof(native.SealDesc) == 160
     assert C.sizeof(native.DenseAttentionDesc) == 120
 

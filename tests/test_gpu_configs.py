@@ -334,3 +334,29 @@ def test_decode_probe_folds_exactly_the_symbols_of_every_page(native, oracle, co
             want = (np.bitwise_xor.reduce(np.ascontiguousarray(ks[:, head]).view("<u4").ravel()) ^
                     np.bitwise_xor.reduce(np.ascontiguousarray(vs[:, head]).view("<u4").ravel()))
             assert int(partials[seq, head * 4, 0]) == int(want), (seq, head)
+
+
+@pytest.mark.parametrize("kernel", ["lanes", "generic"])
+def test_row_map_serves_a_subset_of_a_batch_in_place(native, kernel):
+    """cf_b200_sealed_attention_desc.row_map: two calls, each over half of the batch's sequences with the rows of the
+    shared query / output tensors they stand for, give exactly what one call over the whole batch gives (and leave the
+    other half's rows alone). Tails included, so the combine kernel's query reads are covered too."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    contexts = np.array([16 * 40, 16 * 3, 16 * 77, 16 * 12, 16 * 150, 16 * 1])
+    layer, _ = build_sealed_layer(contexts, query_heads=8, kv_heads=2, coder="rans4", seed=61)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(62)
+    tails = torch.randn((6, 2, 16, 128), generator=g, device="cuda", dtype=torch.float32).half()
+    layer.fill_tails(list(range(6)), tails, tails.flip(0).contiguous(), 7)
+    q = torch.randn((6, 8, 128), generator=g, device="cuda", dtype=torch.float32).half()
+    k = native.KERNEL_LANES if kernel == "lanes" else native.KERNEL_GENERIC
+    want = layer.attention(q, kernel=k, min_pages_per_unit=4)
+    out = torch.full((6, 8, 128), 7.0, dtype=torch.float32, device="cuda")
+    first, second = [4, 0, 3], [5, 2, 1]
+    layer.attention(q, slots=first, out=out, kernel=k, min_pages_per_unit=4,
+                    row_map=torch.as_tensor(first, dtype=torch.int32, device="cuda"))
+    assert torch.equal(out[first], want[first]) and bool((out[second] == 7.0).all())
+    layer.attention(q, slots=second, out=out, kernel=k, min_pages_per_unit=4,
+                    row_map=torch.as_tensor(second, dtype=torch.int32, device="cuda"))
+    assert torch.equal(out, want) and layer.device_status() == 0

@@ -51,9 +51,21 @@ def test_sequences_sharded_over_the_devices_of_one_process(native, oracle, coder
             lay.import_records(local, recs)
         layers.append(lay)
         local_slots.append(list(range(len(mine))))
+    # the copy path first (staging, row permutation, copies back), then the default, which stores the output rows
+    # straight into the root's tensor wherever the GPUs have the root's memory mapped
+    import os
+    os.environ["CHROMOFOLD_B200_MG_COPIES"] = "1"
+    try:
+        copying = MultiGpuScheduler(layers, max_rows=16)
+    finally:
+        del os.environ["CHROMOFOLD_B200_MG_COPIES"]
+    out = torch.zeros((11, 32, 128), dtype=torch.float32, device="cuda:0")
+    copying.attention_by_sequence(q, out, assignment, local_slots, min_pages_per_unit=16)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want) and copying.counters()["direct_steps"] == 0
+    copying.close()
     sched = MultiGpuScheduler(layers, max_rows=16)
     assert sched.plan_sequences(contexts) == assignment
-    out = torch.zeros((11, 32, 128), dtype=torch.float32, device="cuda:0")
     for _ in range(2):    # the second step reuses the cached row order
         out.zero_()
         sched.attention_by_sequence(q, out, assignment, local_slots, min_pages_per_unit=16)
@@ -61,6 +73,7 @@ def test_sequences_sharded_over_the_devices_of_one_process(native, oracle, coder
         assert np.array_equal(out.cpu().numpy(), want)
     c = sched.counters()
     assert c["steps"] == 2 and c["attention_launches"] == 2 * sum(1 for a in assignment if a)
+    assert c["direct_steps"] in (0, 2) and (world > 1 or c["direct_steps"] == 2)
     assert all(lay.device_status() == 0 for lay in layers)
     # a device marked failed: the batch that names it is refused, the planner routes around it
     if world > 1:
