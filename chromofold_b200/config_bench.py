@@ -80,9 +80,12 @@ def config3_blocks(a, device, check=None):
     the p sweep."""
     contexts = np.full(32, 8192)
     results = []
+    only = getattr(a, "cell", "")   # "coder:block" runs that one cell at p = 0.1 (for profiler captures)
     for p in (0.1, 0.4):
         for coder in ("rans", "huffman", "rans4", "huffman4"):
             for block in (64, 128, 256):
+                if only and (only != f"{coder}:{block}" or p != 0.1):
+                    continue
                 layer, info = build_sealed_layer(contexts, coder=coder, dist=("geometric", p), seed=40, device=device,
                                                  block_size=block)
                 q = _queries(32, 32, 41, device)
@@ -341,8 +344,11 @@ def head_dim_dial(a, device, check=None):
     kernel's staging path and, for comparison, through the any-geometry kernel: batch 32 x 8192, Laplace(b=12) codes."""
     contexts = np.full(32, 8192)
     results = []
+    only = getattr(a, "cell", "")   # "coder:head_dim:block" runs that one cell (for profiler captures)
     for coder in ("rans4", "huffman4", "rans", "huffman", "fixed8"):
         for dim, block in ((96, 64), (64, 64), (64, 128), (32, 64)):
+            if only and only != f"{coder}:{dim}:{block}":
+                continue
             layer, info = build_sealed_layer(contexts, coder=coder, seed=45, device=device, head_dim=dim, block_size=block)
             g = torch.Generator(device=device)
             g.manual_seed(46)
@@ -442,6 +448,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--coder", default="rans", choices=["rans", "huffman", "fixed8", "rans4", "huffman4"], help="configurations 4 and 5")
     ap.add_argument("--blocks", action="store_true", help="configuration 3: the block-size dial instead of the p sweep")
+    ap.add_argument("--cell", default="", help="with --blocks: coder:block, with --head-dims: coder:head_dim:block — run that one cell")
     ap.add_argument("--one-process", type=int, default=0, metavar="N",
                     help="configuration 4 on N GPUs driven by this one process through the C-ABI batch scheduler")
     ap.add_argument("--batch4", type=int, default=8)

@@ -494,16 +494,18 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 
                     if constexpr (NB != 32) {
                         uint8_t *tile = warp_mem + L::kTile;
+                        // One call site for both streams: the lanes that decode V blocks differ from those that decode K
+                        // blocks only in the pointers they pass, so the warp runs the decoder once, not once per stream.
+                        auto stage_one = [&](bool is_v, uint32_t block) {
+                            stage_blocks<NB, kDim>(is_v ? v_part : k_part, is_v ? v_bytes : k_bytes, is_v ? v_coder : k_coder, block,
+                                                   is_v ? v_slot : k_slot, is_v ? v_lut : k_lut,
+                                                   tile + (is_v ? kTileStreamOf<kDim> + 16u : 0u));
+                        };
                         if constexpr (NB <= 16) {
-                            if ((lane & 15u) < static_cast<uint32_t>(NB)) {
-                                if (lane < 16u) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, lane, k_slot, k_lut, tile);
-                                else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, lane - 16u, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
-                            }
+                            if ((lane & 15u) < static_cast<uint32_t>(NB)) stage_one(lane >= 16u, lane & 15u);
                         } else {   // two rounds: 2 NB blocks dealt over the 32 lanes, K blocks first
-                            for (uint32_t gb = lane; gb < 2u * NB; gb += 32u) {
-                                if (gb < static_cast<uint32_t>(NB)) stage_blocks<NB, kDim>(k_part, k_bytes, k_coder, gb, k_slot, k_lut, tile);
-                                else stage_blocks<NB, kDim>(v_part, v_bytes, v_coder, gb - NB, v_slot, v_lut, tile + kTileStreamOf<kDim> + 16u);
-                            }
+                            for (uint32_t gb = lane; gb < 2u * NB; gb += 32u)
+                                stage_one(gb >= static_cast<uint32_t>(NB), gb >= static_cast<uint32_t>(NB) ? gb - NB : gb);
                         }
                         __syncwarp();
                         if (i + 1 < n_pages) issue(0u, entry_next);   // the record is decoded: its stage takes the next one
