@@ -69,6 +69,17 @@ __device__ __forceinline__ uint32_t quantise_symbol(float x, float scale) {
     return static_cast<uint32_t>(q + kZero);
 }
 
+// The same symbol without the IEEE division on the common path. With r = RN(1 / scale), y = RN(x * r) differs from
+// q = RN(x / scale) by at most 1.5 * 2^-23 * |q|, which is below 2^-15 wherever the clamp does not decide anyway; so when
+// y is further than 2^-14 from every half-integer, rint(y) = rint(q), and only the few values closer than that take
+// the division. (Beyond +-129 both round far outside the clamp; an overflowing product is +-inf on both paths.)
+__device__ __forceinline__ uint32_t quantise_symbol_rcp(float x, float scale, float rcp) {
+    const float y = x * rcp, n = rintf(y);
+    if (fabsf(fabsf(y - n) - 0.5f) < 6.103515625e-05f) return quantise_symbol(x, scale);
+    const int q = max(-128, min(127, __float2int_rn(n)));
+    return static_cast<uint32_t>(q + kZero);
+}
+
 // Block-wide absmax and non-finite flag over `count` binary16 values.
 __device__ __forceinline__ float tile_value(const void *base, uint32_t type, uint64_t i) {
     return type == CF_B200_F32 ? static_cast<const float *>(base)[i] : __half2float(static_cast<const __half *>(base)[i]);
@@ -529,14 +540,15 @@ __global__ void __launch_bounds__(kSealThreads, CFB_SEAL_CTAS) seal_pages_fast_k
     }
     const uint16_t k_bits = scale_bits_from_absmax(__uint_as_float(km)), v_bits = scale_bits_from_absmax(__uint_as_float(vm));
     const float k_scale = __half2float(__ushort_as_half(k_bits)), v_scale = __half2float(__ushort_as_half(v_bits));
+    const float k_rcp = __frcp_rn(k_scale), v_rcp = __frcp_rn(v_scale);
     uint32_t kw[4], vw[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t a = 0u, b = 0u;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            a |= (k_live ? quantise_symbol(kf[4 * i + j], k_scale) : static_cast<uint32_t>(kZero)) << (8 * j);
-            b |= (static_cast<uint32_t>(4 * i + j) < rows ? quantise_symbol(vf[4 * i + j], v_scale) : static_cast<uint32_t>(kZero)) << (8 * j);
+            a |= (k_live ? quantise_symbol_rcp(kf[4 * i + j], k_scale, k_rcp) : static_cast<uint32_t>(kZero)) << (8 * j);
+            b |= (static_cast<uint32_t>(4 * i + j) < rows ? quantise_symbol_rcp(vf[4 * i + j], v_scale, v_rcp) : static_cast<uint32_t>(kZero)) << (8 * j);
         }
         kw[i] = a, vw[i] = b;
     }

@@ -293,6 +293,13 @@ def test_gpu_sealer_is_byte_exact_on_fp32_rows(native, oracle, coder):
     k = (rng.laplace(0.0, 12.0, (4, hkv, t, d)) * 0.0137).astype(np.float32)
     v = (rng.laplace(0.0, 12.0, (4, hkv, t, d)) * 0.0071).astype(np.float32)
     k[3] = rng.uniform(-1.0, 1.0, (hkv, t, d)).astype(np.float32)      # does not shrink: stored fixed-width
+    # values a hair's breadth from the rounding boundaries of the quantiser, x = scale * (n + 1/2) * (1 + j 2^-24): the
+    # sealer's multiply-by-reciprocal path must hand exactly these to the division (the oracle divides every value)
+    scale = np.float32(np.float16(0.0123))
+    n_half = rng.integers(-127, 127, (hkv, t, d)).astype(np.float64) + 0.5
+    jitter = 1.0 + rng.integers(-12, 13, (hkv, t, d)).astype(np.float64) * 2.0 ** -24
+    v[1] = (np.float64(scale) * n_half * jitter).astype(np.float32)
+    v[1, :, 0, 0] = np.float32(127.0) * scale                          # pins the stream's absmax, hence the scale
     dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
     ids = torch.arange(1, 5, dtype=torch.int32, device="cuda")
     desc = layer._seal_desc(torch.arange(4, dtype=torch.int32, device="cuda"), ids,
