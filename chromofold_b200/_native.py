@@ -149,7 +149,7 @@ EXPORTS = {
         "cf_llama_kv_options_validate", "cf_llama_kv_create", "cf_llama_kv_destroy", "cf_llama_kv_append",
         "cf_llama_kv_attention", "cf_llama_kv_attention_host", "cf_llama_kv_flush", "cf_llama_kv_seq_rm",
         "cf_llama_kv_seq_cp", "cf_llama_kv_seq_shift", "cf_llama_kv_clear", "cf_llama_kv_get_stats",
-        "cf_llama_kv_last_error", "cf_b200_llama_kv_reference_page",
+        "cf_llama_kv_last_error", "cf_b200_llama_kv_reference_page", "cf_b200_llama_kv_reserved_bytes",
     ],
 }
 

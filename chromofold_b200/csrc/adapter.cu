@@ -226,6 +226,19 @@ struct cf_llama_kv_adapter {
             kivi_descs.back()->ensure(64, s);
         }
         kivi_host_descs.assign(opt.layer_count, {});
+        if (const char *reserve = std::getenv("CHROMOFOLD_B200_RESERVE_TOKENS")) {   // page memory and descriptors up front
+            const unsigned long long tokens = std::strtoull(reserve, nullptr, 10);
+            const size_t pages = static_cast<size_t>((tokens + opt.page_size - 1) / opt.page_size);   // per layer and kv head
+            const size_t page_bytes = (kivi_layout(opt.page_size, opt.head_dim, kivi_bits).total + 255u) / 256u * 256u;
+            const size_t per_chunk = kKiviChunk / page_bytes;
+            const size_t chunks = per_chunk ? (pages * opt.layer_count * opt.kv_head_count + per_chunk - 1) / per_chunk : 0;
+            for (size_t i = kivi_chunks.size(); i < chunks; ++i) {
+                uint8_t *fresh = nullptr;
+                cuda_check(cudaMalloc(reinterpret_cast<void **>(&fresh), kKiviChunk), "cudaMalloc");
+                kivi_chunks.push_back(fresh);
+            }
+            for (uint32_t l = 0; l < opt.layer_count; ++l) kivi_descs[l]->ensure(std::max<size_t>(64, pages * opt.kv_head_count), s);
+        }
         cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
     }
     void kivi_reset() {
@@ -767,6 +780,10 @@ extern "C" const char *cf_llama_kv_last_error(const cf_llama_kv_adapter *adapter
 // Additive: the device descriptor of a page of reference-exact mode (the reference's cf_kv_device_page: fixed-width words,
 // K per-channel and V per-token fp32 scales), so that a test or a tool can read back exactly what was stored.
 // page_index counts the pages of `layer` in the order they were sealed, over all kv heads. Returns -1 in format-v1 mode.
+extern "C" uint64_t cf_b200_llama_kv_reserved_bytes(const cf_llama_kv_adapter *adapter) {
+    return adapter ? static_cast<uint64_t>(adapter->kivi_chunks.size()) * cf_llama_kv_adapter::kKiviChunk : 0;
+}
+
 extern "C" int cf_b200_llama_kv_reference_page(const cf_llama_kv_adapter *adapter, uint32_t layer, uint32_t page_index,
                                                cf_kv_device_page *out_page) {
     if (adapter == nullptr || out_page == nullptr || !adapter->kivi || layer >= adapter->kivi_host_descs.size() ||

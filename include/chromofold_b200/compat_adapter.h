@@ -87,6 +87,11 @@ const char *cf_llama_kv_last_error(const cf_llama_kv_adapter *adapter);         
  * the order they were sealed over all kv heads; -1 in format-v1 mode or out of range. */
 int cf_b200_llama_kv_reference_page(const cf_llama_kv_adapter *adapter, uint32_t layer, uint32_t page_index,
                                     cf_kv_device_page *out_page);
+/* Additive: bytes of page memory the adapter holds on the device (reference-exact mode). The reference's options have no
+ * context limit, so page memory grows in 32 MB chunks as tokens arrive; CHROMOFOLD_B200_RESERVE_TOKENS=<tokens per
+ * sequence position, i.e. context length> in the environment makes cf_llama_kv_create take the chunks and the
+ * descriptor arrays for that many tokens of every layer and kv head up front, so that no append allocates. */
+uint64_t cf_b200_llama_kv_reserved_bytes(const cf_llama_kv_adapter *adapter);
 
 #ifdef __cplusplus
 }

@@ -426,3 +426,38 @@ def test_flat_fused_and_dense_attention(native, oracle, shape):
     assert call(nq_=seq + 1) == 1 and call(window_=0) == 1 and call(block_=0) == 1 and call(scale_=float("nan")) == 1
     assert call(head_=(None,) + head[1:]) == 1
     assert call(dim_=129) == 2 and call(window_=513) == 2
+
+
+def test_adapter_reserves_its_page_memory_up_front_when_asked(native, monkeypatch):
+    """CHROMOFOLD_B200_RESERVE_TOKENS: the adapter takes its page chunks and descriptor arrays at create; appending that
+    many tokens then allocates nothing more (the reserved byte count does not move). Without it page memory starts
+    empty and grows with the first sealed page."""
+    lib = native.lib()
+    lib.cf_llama_kv_create.restype = C.c_void_p
+    lib.cf_b200_llama_kv_reserved_bytes.restype = C.c_uint64
+    monkeypatch.delenv("CHROMOFOLD_B200_CODER", raising=False)
+    hq, hkv, page, layers, d, tokens = 8, 2, 32, 3, 128, 8192
+    o = LlamaKvOptions()
+    o.struct_size, o.backend = C.sizeof(o), 1
+    o.layer_count, o.kv_head_count, o.query_head_count, o.head_dim, o.page_size, o.gqa_group_size = layers, hkv, hq, d, page, hq // hkv
+    o.kv_bits = 8
+    plain = C.c_void_p(lib.cf_llama_kv_create(C.byref(o)))
+    assert plain.value and lib.cf_b200_llama_kv_reserved_bytes(plain) == 0
+    lib.cf_llama_kv_destroy(plain)
+    monkeypatch.setenv("CHROMOFOLD_B200_RESERVE_TOKENS", str(tokens))
+    a = C.c_void_p(lib.cf_llama_kv_create(C.byref(o)))
+    assert a.value
+    reserved = lib.cf_b200_llama_kv_reserved_bytes(a)
+    # int8 page of 32 x 128: 2 x 4096 B of words + scales + offsets, rounded to 256 B; 256 pages per layer and head
+    assert reserved >= layers * hkv * (tokens // page) * 2 * 4096
+    rng = np.random.default_rng(77)
+    rows = rng.standard_normal((512, d)).astype(np.float32)
+    p = lambda x: np.ascontiguousarray(x).ctypes.data_as(C.c_void_p)
+    for begin in range(0, tokens, 512):
+        for layer in range(layers):
+            for h in range(hkv):
+                assert lib.cf_llama_kv_append(a, layer, h, begin, p(rows), p(rows), 512, None) == 0
+    st = LlamaKvStats()
+    assert lib.cf_llama_kv_get_stats(a, C.byref(st)) == 0 and st.sealed_pages == layers * hkv * (tokens // page)
+    assert lib.cf_b200_llama_kv_reserved_bytes(a) == reserved
+    lib.cf_llama_kv_destroy(a)
