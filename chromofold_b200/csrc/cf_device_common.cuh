@@ -93,9 +93,9 @@ inline LauncherState *launcher_state(LauncherState (&table)[64], cudaError_t *er
     return state;
 }
 
-// Pages per (chunk, kv head) unit when the caller leaves the choice to the library: 16, or fewer (down to 4) when the
-// batch is so small that units of 16 pages would not give every resident warp of the attention kernel (148 SMs x 16
-// warps) about four units to balance over.
+// The unit size the WORKSPACE is sized for when the caller leaves the choice to the library: 16 pages, or fewer (down
+// to 4) when the batch is so small that units of 16 pages would not give every resident warp of the attention kernel
+// (148 SMs x 16 warps) about four units. (The plan kernel makes the actual choice, among the sizes that fit.)
 __host__ __device__ inline uint32_t default_pages_per_unit(uint64_t total_pages, uint32_t kv_head_span) {
     const uint64_t slots = 4ull * 148ull * 16ull;
     const uint64_t wanted = (total_pages * kv_head_span + slots - 1ull) / slots;

@@ -95,8 +95,9 @@ typedef struct cf_b200_sealed_attention_desc {
 
     void *workspace;                     /* split-KV partials; see cf_b200_sealed_attention_workspace_bytes */
     uint64_t workspace_bytes;
-    uint32_t min_pages_per_unit;         /* pages per split-KV unit; 0 = the library chooses: 16, or down to 4 for batches
-                                            too small to fill the GPU with units of 16 */
+    uint32_t min_pages_per_unit;         /* pages per split-KV unit; 0 = the library chooses (4 to 35) on the device, from the
+                                            pages the launch will read: the size whose rounds over the GPU's resident
+                                            warps cost least, among those whose partials fit the workspace */
     uint32_t kernel;                     /* CF_B200_KERNEL_* */
     uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
     uint32_t tail_type;                  /* CF_B200_F16 (0 means F16 too) or CF_B200_F32: element type of the tails */
@@ -158,7 +159,8 @@ cf_status cf_b200_test_wait_expiry(uint32_t skip_copy_page_id, uint32_t wait_pol
 cf_status cf_b200_sealed_attention_validate(const cf_b200_sealed_attention_desc *desc);
 
 /* Workspace needed so that a batch with at most total_pages sealed pages (summed over sequences) never
- * has to grow its units beyond min_pages_per_unit. A smaller workspace is legal: units grow to fit. */
+ * has to grow its units beyond min_pages_per_unit (or, with 0, beyond 16 pages, 4 for small batches). A smaller
+ * workspace is legal: units grow to fit. */
 cf_status cf_b200_sealed_attention_workspace_bytes(const cf_b200_sealed_attention_desc *desc,
                                                    uint64_t total_pages, uint64_t *out_bytes);
 
