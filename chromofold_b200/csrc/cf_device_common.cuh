@@ -184,9 +184,15 @@ __device__ __forceinline__ void fixed8_decode_block(const uint32_t *words, uint3
     }
 }
 
-// Start offset of block `b` against the part's length: false = the record's block table is corrupt.
+// Start offset of block `b` against the part's length, and (rANS) its start state against [2^23, 2^31), the range every
+// state the sealer leaves lies in: false = the record's block table is corrupt.
 __device__ __forceinline__ bool part_block_start_ok(const uint8_t *part, uint32_t part_bytes, uint32_t coder, uint32_t nblocks,
                                                     uint32_t b, uint32_t symbols) {
+    if (coder == CF_B200_CODER_RANS || coder == CF_B200_CODER_RANS_SPLIT4) {
+        if (part_bytes < align_up_u32(6u * nblocks, 4u)) return false;
+        const uint32_t state0 = reinterpret_cast<const uint32_t *>(part)[b];
+        if (state0 < kRansL || state0 >= (kRansL << 8)) return false;
+    }
     if (coder == CF_B200_CODER_RANS) {
         const uint32_t head = align_up_u32(6u * nblocks, 4u);
         return part_bytes >= head && reinterpret_cast<const uint16_t *>(part + 4u * nblocks)[b] <= part_bytes - head;

@@ -110,13 +110,13 @@ struct RansLaneT {
     __device__ __forceinline__ void reload() {
         pos += used >> 3;
         used = 0;
-        const uint32_t base = pos & ~3u, sel = imad(pos & 3u, 0x1111u, 0x0123u);
+        const uint32_t base = pos & ~3u, align = imad(pos & 3u, 0x1111u, 0x0123u);
         uint32_t w0, w1, w2;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(base));
         asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(base));
         asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(w2) : "r"(base));
-        whi = __byte_perm(w0, w1, sel);
-        wlo = __byte_perm(w1, w2, sel);
+        whi = __byte_perm(w0, w1, align);
+        wlo = __byte_perm(w1, w2, align);
     }
     // src/cuda/rans.cu:20-23: x = freq * (x >> 12) + (x & 4095) - cum, then bytes are shifted in while x < 2^23.
     // The shared-memory table holds e = sym | (slot - cum) << 8 | freq << 20, so e >> 8 = (slot - cum) + freq * 4096
@@ -305,6 +305,12 @@ __device__ __forceinline__ bool record_header_ok(const uint4 &hv, uint64_t dir_e
 template <int NB = 32, int kSyms = 2048>
 __device__ __forceinline__ bool part_offsets_ok(const uint8_t *part, uint32_t coder, uint32_t part_bytes, uint32_t lane) {
     constexpr uint32_t kRansHead = RansLaneT<NB>::kHead, kHuffHead = HuffLaneT<NB>::kHead, kPlane = kSyms / 2u;
+    // A rANS block's start state must lie in [2^23, 2^31), as every state the sealer leaves does: the lane decoders
+    // rely on it (a state in range stays in range, and then a step takes at most two bytes).
+    if (coder == CF_B200_CODER_RANS || coder == CF_B200_CODER_RANS_SPLIT4) {
+        const uint32_t state0 = reinterpret_cast<const uint32_t *>(part)[lane];
+        if (part_bytes < kRansHead || state0 < CF_B200_RANS_L || state0 >= (CF_B200_RANS_L << 8)) return false;
+    }
     if (coder == CF_B200_CODER_RANS)
         return part_bytes >= kRansHead && reinterpret_cast<const uint16_t *>(part + 4 * NB)[lane] <= part_bytes - kRansHead;
     if (coder == CF_B200_CODER_HUFFMAN)
