@@ -86,19 +86,26 @@ struct cf_b200_mg_scheduler {
     std::vector<uint8_t *> q_full;             // per device: max_rows query rows (nullptr on the root)
     std::vector<uint32_t *> d_rows, h_rows;    // per device: row map on the device / pinned copy of what it holds
     std::vector<uint32_t> rows_held;           // per device: entries of the row map that are valid (0 = none uploaded)
-    const void *checked_output = nullptr;      // the last root_output whose mapping was checked, and the answer
-    bool checked_writable = false;
+    void *access_query = nullptr;              // cuPointerGetAttribute, looked up once
+    bool access_query_looked_up = false;
 
     // Whether every other device may STORE to `ptr` (memory of the root): asked of the driver per device
     // (CU_POINTER_ATTRIBUTE_ACCESS_FLAGS with that device current). Anything but a clear "read and write" — an
     // allocation from a pool that was not opened to the peers, a driver that does not answer — keeps the copy path.
+    // Asked on every call (a few microseconds of host time): an address can come back from the allocator as a
+    // different kind of memory.
     bool every_device_may_store(const void *ptr) {
-        if (ptr == checked_output) return checked_writable;
         using QueryFn = CUresult (*)(void *, CUpointer_attribute, CUdeviceptr);
-        void *entry = nullptr;
-        cudaDriverEntryPointQueryResult found;
-        bool writable = cudaGetDriverEntryPoint("cuPointerGetAttribute", &entry, cudaEnableDefault, &found) == cudaSuccess &&
-                        found == cudaDriverEntryPointSuccess && entry != nullptr;
+        if (!access_query_looked_up) {
+            cudaDriverEntryPointQueryResult found;
+            void *entry = nullptr;
+            if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &entry, cudaEnableDefault, &found) == cudaSuccess &&
+                found == cudaDriverEntryPointSuccess)
+                access_query = entry;
+            access_query_looked_up = true;
+        }
+        void *entry = access_query;
+        bool writable = entry != nullptr;
         for (size_t d = 1; d < ordinals.size() && writable; ++d) {
             unsigned long long flags = 0;
             writable = cudaSetDevice(ordinals[d]) == cudaSuccess &&
@@ -107,8 +114,6 @@ struct cf_b200_mg_scheduler {
                        flags == CU_POINTER_ATTRIBUTE_ACCESS_FLAG_READWRITE;
         }
         cudaGetLastError();
-        checked_output = ptr;
-        checked_writable = writable;
         return writable;
     }
     cf_b200_mg_counters counters{};
