@@ -16,6 +16,7 @@ KERNEL_AUTO, KERNEL_GENERIC, KERNEL_LANES, KERNEL_DECODE_PROBE, KERNEL_DECODE_DU
 STATIC_WORKSPACE_BYTES = 8 << 20
 STAGE_PLAN, STAGE_ATTENTION, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 7
 DEVSTAT_BAD_RECORD, DEVSTAT_WAIT_EXPIRED, DEVSTAT_WORKSPACE, DEVSTAT_NONFINITE, DEVSTAT_ARENA_FULL = 1, 2, 4, 8, 16
+DEVSTAT_TAIL_FULL = 0x80
 
 _u32, _u64, _vp, _f32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_float
 
@@ -54,6 +55,15 @@ class SealDesc(C.Structure):
     ]
 
 
+class AppendDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", _u32), ("abi_version", _u32),
+        ("kv_head_count", _u32), ("head_dim", _u32), ("tail_capacity", _u32), ("tail_type", _u32),
+        ("tail_k", _vp), ("tail_v", _vp), ("tail_tokens", _vp), ("slots", _vp), ("k_rows", _vp), ("v_rows", _vp),
+        ("row_type", _u32), ("row_count", _u32), ("status", _vp),
+    ]
+
+
 class DenseAttentionDesc(C.Structure):
     _fields_ = [
         ("struct_size", _u32), ("abi_version", _u32),
@@ -70,7 +80,7 @@ EXPORTS = {
     "sealed_kv.h": [
         "cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
         "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async", "cf_b200_codebook_build",
-        "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
+        "cf_b200_seal_validate", "cf_b200_seal_pages_async", "cf_b200_append_rows_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
         "cf_b200_dense_attention_async", "cf_b200_build_info", "cf_b200_sealed_attention_static_async",
         "cf_b200_sealed_attention_static_error", "cf_b200_shared_prefix_launches", "cf_b200_test_wait_expiry",
     ],
@@ -241,7 +251,7 @@ def lib():
         for name in ("cf_b200_sealed_attention_validate", "cf_b200_sealed_attention_workspace_bytes",
                      "cf_b200_sealed_attention_async", "cf_b200_sealed_attention_stages_async",
                      "cf_b200_codebook_build", "cf_b200_seal_validate",
-                     "cf_b200_seal_pages_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
+                     "cf_b200_seal_pages_async", "cf_b200_append_rows_async", "cf_b200_histogram_async", "cf_b200_decode_pages_async",
                      "cf_b200_dense_attention_async", "cf_b200_sealed_attention_static_async"):
             getattr(_lib, name).restype = C.c_int
         _lib.cf_b200_sealed_attention_static_error.restype = C.c_char_p

@@ -747,6 +747,53 @@ extern "C" cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *d, void *
     return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
 }
 
+namespace cfb {
+namespace {
+
+// One block per row: the K and V rows of a token go to position tail_tokens[slot] of the slot's tails.
+__global__ void __launch_bounds__(128) append_rows_kernel(cf_b200_append_desc d) {
+    const uint32_t row = blockIdx.x, slot = d.slots[row];
+    const uint32_t at = d.tail_tokens[slot];
+    if (at >= d.tail_capacity) {
+        if (threadIdx.x == 0 && d.status) atomicOr(d.status, CF_B200_DEVSTAT_TAIL_FULL);
+        return;
+    }
+    const uint32_t values = d.kv_head_count * d.head_dim;
+    for (uint32_t i = threadIdx.x; i < values; i += blockDim.x) {
+        const uint32_t head = i / d.head_dim, dim = i % d.head_dim;
+        const uint64_t src = static_cast<uint64_t>(row) * values + i;
+        const uint64_t dst = ((static_cast<uint64_t>(slot) * d.kv_head_count + head) * d.tail_capacity + at) * d.head_dim + dim;
+        const float k = tile_value(d.k_rows, d.row_type, src), v = tile_value(d.v_rows, d.row_type, src);
+        if (d.tail_type == CF_B200_F32) {
+            static_cast<float *>(d.tail_k)[dst] = k;
+            static_cast<float *>(d.tail_v)[dst] = v;
+        } else {
+            static_cast<__half *>(d.tail_k)[dst] = __float2half_rn(k);
+            static_cast<__half *>(d.tail_v)[dst] = __float2half_rn(v);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) d.tail_tokens[slot] = at + 1u;
+}
+
+}  // namespace
+}  // namespace cfb
+
+extern "C" cf_status cf_b200_append_rows_async(const cf_b200_append_desc *d, void *stream) {
+    if (d == nullptr || d->struct_size != sizeof(cf_b200_append_desc) || d->abi_version != CF_B200_ABI_VERSION ||
+        d->kv_head_count == 0 || d->head_dim == 0 || d->tail_capacity == 0 || d->tail_k == nullptr || d->tail_v == nullptr ||
+        d->tail_tokens == nullptr || (d->row_count != 0 && (d->slots == nullptr || d->k_rows == nullptr || d->v_rows == nullptr)) ||
+        (d->row_type != CF_B200_F16 && d->row_type != CF_B200_F32))
+        return CF_ERR_INVALID_ARGUMENT;
+    if (d->row_count == 0) return CF_OK;
+    if (!cfb::on_current_device(d->tail_k) || !cfb::on_current_device(d->k_rows) || !cfb::on_current_device(d->tail_tokens))
+        return CF_ERR_INVALID_ARGUMENT;   // memory of another GPU: the call must be made with that GPU current
+    cf_b200_append_desc local = *d;
+    local.tail_type = d->tail_type == CF_B200_F32 ? CF_B200_F32 : CF_B200_F16;
+    cfb::append_rows_kernel<<<d->row_count, 128, 0, static_cast<cudaStream_t>(stream)>>>(local);
+    return cudaPeekAtLastError() == cudaSuccess ? CF_OK : CF_ERR_CUDA;
+}
+
 extern "C" cf_status cf_b200_histogram_async(const cf_b200_seal_desc *d, unsigned long long *hist_k,
                                              unsigned long long *hist_v, void *stream) {
     const cf_status s = cfb::validate_common(d);

@@ -145,6 +145,7 @@ typedef struct cf_b200_sealed_attention_desc {
 #define CF_B200_DEVSTAT_NONFINITE 0x8u       /* the sealer met NaN or Inf; the page was not published */
 #define CF_B200_DEVSTAT_ARENA_FULL 0x10u     /* the sealer found no room in the arena */
 #define CF_B200_DEVSTAT_PREFIX_MISMATCH 0x20u /* shared_prefix_pages was set but the page-table rows differ */
+#define CF_B200_DEVSTAT_TAIL_FULL 0x80u      /* an append found its slot's unsealed tail full; the row was not stored */
 #define CF_B200_SHARED_CHUNKS_MAX 16u        /* a shared prefix is cut into at most this many chunks */
 
 /* Test hook for the bounded waits of the attention kernels: from the next launch on, the record of page id
@@ -244,6 +245,31 @@ typedef struct cf_b200_seal_desc {
 
 cf_status cf_b200_seal_validate(const cf_b200_seal_desc *desc);
 cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *desc, void *stream);
+
+/* Raw launch: append one token to the unsealed tails of the listed slots (the reference's append step,
+ * src/cuda/device_kv_dataplane.cu:150-190, as one launch for a whole decode batch). Row i
+ * (k_rows / v_rows: [row_count][kv_head_count][head_dim] of row_type, device memory) is stored at position
+ * tail_tokens[slots[i]] of that slot's tails ([slot][kv_head_count][tail_capacity][head_dim] of tail_type) and the
+ * count is raised by one. A slot may be listed once per call. A full tail (count == tail_capacity) takes nothing and
+ * raises CF_B200_DEVSTAT_TAIL_FULL: seal first (cf_b200_seal_pages_async), then the caller resets the count. */
+typedef struct cf_b200_append_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t kv_head_count;
+    uint32_t head_dim;
+    uint32_t tail_capacity;
+    uint32_t tail_type;       /* CF_B200_F16 (0 too) or CF_B200_F32 */
+    void *tail_k;
+    void *tail_v;
+    uint32_t *tail_tokens;    /* [slot] */
+    const uint32_t *slots;    /* [row_count], distinct */
+    const void *k_rows;
+    const void *v_rows;
+    uint32_t row_type;        /* CF_B200_F16 or CF_B200_F32 */
+    uint32_t row_count;
+    uint32_t *status;         /* optional */
+} cf_b200_append_desc;
+cf_status cf_b200_append_rows_async(const cf_b200_append_desc *desc, void *stream);
 
 /* Symbol histograms of quantised K and V streams of the same tails (for codebook calibration).
  * hist_k / hist_v: device uint64[256], accumulated into (not cleared). */

@@ -594,3 +594,33 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(native, ora
     layer.status.zero_()
     again = layer.attention(q, **kw).cpu().numpy()
     assert layer.device_status() == 0 and np.array_equal(again, good)
+
+
+def test_append_rows_entry_point_fills_the_tails_and_reports_a_full_one(native):
+    """cf_b200_append_rows_async: one launch stores a token's K and V rows (binary16 or fp32 rows) at each listed slot's
+    tail position and raises the count; a slot whose tail is full takes nothing and raises CF_B200_DEVSTAT_TAIL_FULL."""
+    import torch
+    layer = _layer(native, kv_heads=2, query_heads=4, max_sequences=4)
+    rng = np.random.default_rng(71)
+    want_k = np.zeros((4, 2, 16, 128), np.float16)
+    want_v = np.zeros_like(want_k)
+    counts = [0, 0, 0, 0]
+    for step in range(16):
+        slots = [0, 2, 3] if step % 2 == 0 else [2, 1]
+        dtype = np.float16 if step % 3 else np.float32
+        k = rng.standard_normal((len(slots), 2, 128)).astype(dtype)
+        v = rng.standard_normal((len(slots), 2, 128)).astype(dtype)
+        layer.append(slots, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+        for i, s in enumerate(slots):
+            want_k[s, :, counts[s]] = k[i].astype(np.float16)
+            want_v[s, :, counts[s]] = v[i].astype(np.float16)
+            counts[s] += 1
+    assert layer.tail_tokens.cpu().tolist() == counts == [8, 8, 16, 8] and layer.device_status() == 0
+    assert np.array_equal(layer.tail_k.cpu().numpy(), want_k) and np.array_equal(layer.tail_v.cpu().numpy(), want_v)
+    with pytest.raises(ValueError):                 # the host mirror refuses before the device is asked
+        layer.append([2], torch.zeros((1, 2, 128), dtype=torch.float16, device="cuda"), torch.zeros((1, 2, 128), dtype=torch.float16, device="cuda"))
+    layer.h_tail[2] = 0                             # ask the device anyway: nothing is stored, the status bit is raised
+    layer.append([2], torch.ones((1, 2, 128), dtype=torch.float16, device="cuda"), torch.ones((1, 2, 128), dtype=torch.float16, device="cuda"))
+    torch.cuda.synchronize()
+    assert layer.device_status() == native.DEVSTAT_TAIL_FULL
+    assert layer.tail_tokens.cpu().tolist() == counts and np.array_equal(layer.tail_k.cpu().numpy(), want_k)
