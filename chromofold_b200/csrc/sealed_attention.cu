@@ -382,7 +382,10 @@ __global__ void __launch_bounds__(kGenericThreads) generic_attention_kernel(Atte
 // ---------------------------------------------------------------------------------------------------------------
 // Combine: merge the chunk partials of one (sequence, query head) with the unsealed tail and write the output.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kCombineThreads = 256;
+#ifndef CFB_COMBINE_THREADS
+#define CFB_COMBINE_THREADS 128   // = the largest head_dim: thread d owns output channel d; more threads only wait
+#endif
+constexpr int kCombineThreads = CFB_COMBINE_THREADS;
 constexpr int kCombineWarps = kCombineThreads / 32;
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParams p) {
