@@ -190,6 +190,12 @@ def sealed_decode_attention(arena, dir_offset, page_table, seq_tokens, queries_f
     dir_offset = np.ascontiguousarray(dir_offset, np.uint64)
     page_table = np.ascontiguousarray(page_table, np.uint32)
     seq_tokens = np.ascontiguousarray(seq_tokens, np.uint32)
+    queries_f16 = np.asarray(queries_f16)
+    if queries_f16.dtype != np.float16 and queries_f16.dtype != np.uint16:   # fp32 queries: the oracle's rows are binary16
+        narrowed = queries_f16.astype(np.float16)
+        if not np.array_equal(narrowed.astype(queries_f16.dtype), queries_f16):
+            raise ValueError("the oracle takes binary16 queries; these values do not survive the narrowing")
+        queries_f16 = narrowed
     q = np.ascontiguousarray(queries_f16).view(np.uint16)
     s = seq_tokens.size
     out = np.zeros((s, hq, head_dim), np.float32)
