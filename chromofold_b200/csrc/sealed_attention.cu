@@ -20,6 +20,7 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kPlanThreads = 1024;
+constexpr uint32_t kPlanCache = 2048;   // batch entries whose page ranges the plan kernel keeps in shared memory
 constexpr int kGenericThreads = 128;
 constexpr uint32_t kGenericMaxGroup = 16;
 
@@ -53,7 +54,10 @@ __global__ void __launch_bounds__(256) verify_prefix_kernel(AttentionParams p) {
 
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     __shared__ uint32_t scan[kPlanThreads];
+    __shared__ uint32_t warp_totals[kPlanThreads / 32];
+    __shared__ uint32_t s_visible[kPlanCache], s_first[kPlanCache];
     __shared__ uint32_t s_total;
+    static_assert(kPlanThreads == 1024, "the block scan below is 32 warps of 32 lanes");
     const uint32_t tid = threadIdx.x;
     const uint32_t per_thread = (p.seq_count + kPlanThreads - 1) / kPlanThreads;
     const uint32_t begin = min(tid * per_thread, p.seq_count);
@@ -87,6 +91,23 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         shared_chunks = (shared + shared_per_chunk - 1u) / shared_per_chunk;
     }
 
+    // The visible page range of every batch entry is needed by each pass below; it costs a chain of dependent loads
+    // (slot, sealed tokens, tail tokens, query position), so batches of up to kPlanCache entries keep it in shared memory.
+    const bool cached = p.seq_count <= kPlanCache;
+    if (cached) {
+        for (uint32_t s = tid; s < p.seq_count; s += kPlanThreads) {
+            uint32_t first_page;
+            s_visible[s] = visible_pages(p, s, &first_page, shared);
+            s_first[s] = first_page;
+        }
+        __syncthreads();
+    }
+    auto visible_of = [&](uint32_t s, uint32_t *first_page) {
+        if (!cached) return visible_pages(p, s, first_page, shared);
+        if (first_page) *first_page = s_first[s];
+        return s_visible[s];
+    };
+
     uint32_t pages_per_unit = p.min_pages_per_unit;
     uint32_t overflow = 0;
     uint32_t local = 0;  // chunks of this thread's sequences at the current pages_per_unit
@@ -98,7 +119,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         // warp a unit comes out at 4.
         const uint32_t warp = tid >> 5, lane = tid & 31u, candidate = 4u + warp;
         uint64_t units = 0;
-        for (uint32_t s = lane; s < p.seq_count; s += 32u) units += (visible_pages(p, s, nullptr, shared) + candidate - 1u) / candidate;
+        for (uint32_t s = lane; s < p.seq_count; s += 32u) units += (visible_of(s, nullptr) + candidate - 1u) / candidate;
         for (int o = 16; o > 0; o >>= 1) units += __shfl_xor_sync(0xffffffffu, units, o);
         const uint32_t pass_heads = p.group <= 4u ? 4u : p.query_type == CF_B200_F32 ? 4u : 8u;
         const uint64_t warps = 16ull * (p.sm_count ? p.sm_count : 148u);
@@ -125,17 +146,29 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     }
     for (int attempt = 0; attempt < 32; ++attempt) {
         local = 0;
-        for (uint32_t s = begin; s < end; ++s) local += (visible_pages(p, s, nullptr, shared) + pages_per_unit - 1u) / pages_per_unit;
-        __syncthreads();
-        scan[tid] = local;
-        __syncthreads();
-        for (uint32_t off = 1; off < kPlanThreads; off <<= 1) {  // inclusive scan
-            const uint32_t add = tid >= off ? scan[tid - off] : 0u;
-            __syncthreads();
-            scan[tid] += add;
-            __syncthreads();
+        for (uint32_t s = begin; s < end; ++s) local += (visible_of(s, nullptr) + pages_per_unit - 1u) / pages_per_unit;
+        // inclusive scan over the block: inside each warp with shuffles, then over the 32 warp totals
+        uint32_t incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((tid & 31u) >= static_cast<uint32_t>(o)) incl += up;
         }
-        if (tid == kPlanThreads - 1) s_total = scan[tid];
+        __syncthreads();                          // the previous use of warp_totals is over
+        if ((tid & 31u) == 31u) warp_totals[tid >> 5] = incl;
+        __syncthreads();
+        if (tid < 32u) {
+            uint32_t v = warp_totals[tid];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, v, o);
+                if (tid >= static_cast<uint32_t>(o)) v += up;
+            }
+            warp_totals[tid] = v;
+            if (tid == 31u) s_total = v;
+        }
+        __syncthreads();
+        scan[tid] = incl + ((tid >> 5) ? warp_totals[(tid >> 5) - 1u] : 0u);
         __syncthreads();
         if (s_total <= p.layout.chunk_capacity) break;
         if (attempt == 31 || pages_per_unit >= (1u << 30)) { overflow = 1; break; }
@@ -150,7 +183,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
     for (uint32_t s = begin; s < end; ++s) {
         prefix[s] = overflow ? 0u : running;
         uint32_t first_page;
-        const uint32_t chunks = (visible_pages(p, s, &first_page, shared) + pages_per_unit - 1u) / pages_per_unit;
+        const uint32_t chunks = (visible_of(s, &first_page) + pages_per_unit - 1u) / pages_per_unit;
         if (!overflow && !by_warp && chunks) {
             const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
             const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
@@ -168,7 +201,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
             const uint32_t c0 = prefix[s], c1 = s + 1u < p.seq_count ? prefix[s + 1u] : s_total;
             if (c1 == c0) continue;
             uint32_t first_page;
-            visible_pages(p, s, &first_page, shared);
+            visible_of(s, &first_page);
             const uint32_t slot = slot_of(p, s), sealed = p.seq_sealed_tokens[slot];
             const uint32_t qpos = query_position(p, s, sealed, p.tail_tokens ? p.tail_tokens[slot] : 0u);
             const uint32_t row = row_of(p, s);
