@@ -360,3 +360,22 @@ def test_row_map_serves_a_subset_of_a_batch_in_place(native, kernel):
     layer.attention(q, slots=second, out=out, kernel=k, min_pages_per_unit=4,
                     row_map=torch.as_tensor(second, dtype=torch.int32, device="cuda"))
     assert torch.equal(out, want) and layer.device_status() == 0
+
+
+def test_a_batch_of_three_thousand_short_sequences(native):
+    """More batch entries than the plan kernel keeps in shared memory (2048) and fewer chunks than eight per entry: the
+    plan kernel's uncached, thread-per-sequence paths. Lanes kernel against the any-geometry kernel and the oracle."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    contexts = np.array([16 * (1 + i % 5) for i in range(3000)])
+    layer, _ = build_sealed_layer(contexts, query_heads=8, kv_heads=2, coder="rans4", seed=81)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(82)
+    q = torch.randn((3000, 8, 128), generator=g, device="cuda", dtype=torch.float32).half()
+    fast = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    slow = layer.attention(q, kernel=native.KERNEL_GENERIC).cpu().numpy()
+    assert layer.device_status() == 0
+    ok, err = attention_close(fast, slow, rel=1e-3, abs_=5e-4)
+    assert ok, err
+    ok, err = attention_close(fast, oracle_from_layer(layer, q.cpu().numpy()))
+    assert ok, err
