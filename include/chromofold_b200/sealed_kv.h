@@ -119,8 +119,9 @@ typedef struct cf_b200_sealed_attention_desc {
     uint32_t reserved0;
     /* Optional [seq_count], device memory: batch entry i reads row row_map[i] of `queries` and writes row row_map[i] of
      * `output` instead of row i. A call can then serve a subset of a larger batch in place — the multi-GPU scheduler
-     * (sealed_kv_multigpu.h) gives every GPU the rows of its own sequences this way. NULL = entry i is row i. The
-     * shared-prefix hint is not used together with a row map. */
+     * (sealed_kv_multigpu.h) gives every GPU the rows of its own sequences this way. NULL = entry i is row i. The rows
+     * of one call must be distinct (two entries writing one output row would race). The shared-prefix hint is not
+     * used together with a row map. */
     const uint32_t *row_map;
 } cf_b200_sealed_attention_desc;
 
