@@ -104,3 +104,22 @@ def test_codebook_tables_match_oracle(native, oracle):
             nxt = xs + (e[:, 1] & np.uint64(0x1FFF)) + q * ((e[:, 1] >> np.uint64(13)) & np.uint64(0xFFF))
             ff, cc = np.tile(f, 3), np.tile(cum, 3)
             assert np.array_equal(nxt, ((xs // ff) << np.uint64(12)) + xs % ff + cc)
+
+
+def test_every_c_header_compiles_as_c11():
+    """The boundary is a C ABI: every header under include/chromofold_b200 (the C++ convenience class apart) must be
+    usable from plain C, as the reference requires of its own runtime headers (.github/workflows/m9-runtime.yml:34-48)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        import pytest
+        pytest.skip("no C compiler here")
+    include = os.path.join(ROOT, "include")
+    for h in sorted(os.listdir(os.path.join(include, "chromofold_b200"))):
+        if not h.endswith(".h"):
+            continue
+        done = subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-I" + include, "-x", "c", "-"],
+                              input=f'#include "chromofold_b200/{h}"\nint main(void) {{ return 0; }}\n', text=True,
+                              capture_output=True)
+        assert done.returncode == 0, f"{h}: {done.stderr[:400]}"
