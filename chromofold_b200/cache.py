@@ -103,7 +103,7 @@ class SealedKvLayer:
         key = slots.tobytes()     # the device copy of a slot list is kept: a decode loop appends to the same slots every step
         if getattr(self, "_append_key", None) != key:
             self._append_key, self._append_slots = key, torch.as_tensor(slots.astype(np.int32), device=self.device)
-        if k.dtype not in (torch.float16, torch.float32):
+        if k.dtype not in (torch.float16, torch.float32, torch.bfloat16):
             k, v = k.float(), v.float()
         k, v = k.contiguous(), v.to(k.dtype).contiguous()
         d = N.AppendDesc()
@@ -111,7 +111,7 @@ class SealedKvLayer:
         d.kv_head_count, d.head_dim, d.tail_capacity, d.tail_type = self.kv_heads, self.head_dim, self.page_tokens, N.F16
         d.tail_k, d.tail_v, d.tail_tokens = self.tail_k.data_ptr(), self.tail_v.data_ptr(), self.tail_tokens.data_ptr()
         d.slots, d.k_rows, d.v_rows = self._append_slots.data_ptr(), k.data_ptr(), v.data_ptr()
-        d.row_type = N.F16 if k.dtype == torch.float16 else N.F32
+        d.row_type = {torch.float16: N.F16, torch.bfloat16: N.BF16, torch.float32: N.F32}[k.dtype]
         d.row_count, d.status = slots.size, self.status.data_ptr()
         N.check("append_rows", self.lib.cf_b200_append_rows_async(C.byref(d), _stream_ptr()))
         self.h_tail[slots] += 1

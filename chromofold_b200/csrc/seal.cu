@@ -8,6 +8,8 @@
 // cf_device_common.cuh, takes room in the arena with one atomic add, writes the record and only then the directory
 // entry, so a reader never sees a half-written page and the host is not involved.
 
+#include <cuda_bf16.h>
+
 #include <type_traits>
 
 #include "cf_device_common.cuh"
@@ -763,7 +765,14 @@ __global__ void __launch_bounds__(128) append_rows_kernel(cf_b200_append_desc d)
         const uint32_t head = i / d.head_dim, dim = i % d.head_dim;
         const uint64_t src = static_cast<uint64_t>(row) * values + i;
         const uint64_t dst = ((static_cast<uint64_t>(slot) * d.kv_head_count + head) * d.tail_capacity + at) * d.head_dim + dim;
-        const float k = tile_value(d.k_rows, d.row_type, src), v = tile_value(d.v_rows, d.row_type, src);
+        float k, v;
+        if (d.row_type == CF_B200_BF16) {
+            k = __bfloat162float(static_cast<const __nv_bfloat16 *>(d.k_rows)[src]);
+            v = __bfloat162float(static_cast<const __nv_bfloat16 *>(d.v_rows)[src]);
+        } else {
+            k = tile_value(d.k_rows, d.row_type, src);
+            v = tile_value(d.v_rows, d.row_type, src);
+        }
         if (d.tail_type == CF_B200_F32) {
             static_cast<float *>(d.tail_k)[dst] = k;
             static_cast<float *>(d.tail_v)[dst] = v;
@@ -783,7 +792,7 @@ extern "C" cf_status cf_b200_append_rows_async(const cf_b200_append_desc *d, voi
     if (d == nullptr || d->struct_size != sizeof(cf_b200_append_desc) || d->abi_version != CF_B200_ABI_VERSION ||
         d->kv_head_count == 0 || d->head_dim == 0 || d->tail_capacity == 0 || d->tail_k == nullptr || d->tail_v == nullptr ||
         d->tail_tokens == nullptr || (d->row_count != 0 && (d->slots == nullptr || d->k_rows == nullptr || d->v_rows == nullptr)) ||
-        (d->row_type != CF_B200_F16 && d->row_type != CF_B200_F32))
+        (d->row_type != CF_B200_F16 && d->row_type != CF_B200_F32 && d->row_type != CF_B200_BF16))
         return CF_ERR_INVALID_ARGUMENT;
     if (d->row_count == 0) return CF_OK;
     if (!cfb::on_current_device(d->tail_k) || !cfb::on_current_device(d->k_rows) || !cfb::on_current_device(d->tail_tokens))

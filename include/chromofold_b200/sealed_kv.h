@@ -249,7 +249,8 @@ cf_status cf_b200_seal_pages_async(const cf_b200_seal_desc *desc, void *stream);
 
 /* Raw launch: append one token to the unsealed tails of the listed slots (the reference's append step,
  * src/cuda/device_kv_dataplane.cu:150-190, as one launch for a whole decode batch). Row i
- * (k_rows / v_rows: [row_count][kv_head_count][head_dim] of row_type, device memory) is stored at position
+ * (k_rows / v_rows: [row_count][kv_head_count][head_dim] of row_type — the element types a model's KV rows come in,
+ * cf_device_tensor_view: fp16, bf16, fp32 — device memory) is stored at position
  * tail_tokens[slots[i]] of that slot's tails ([slot][kv_head_count][tail_capacity][head_dim] of tail_type) and the
  * count is raised by one. A slot may be listed once per call. A full tail (count == tail_capacity) takes nothing and
  * raises CF_B200_DEVSTAT_TAIL_FULL: seal first (cf_b200_seal_pages_async), then the caller resets the count. */
@@ -266,7 +267,7 @@ typedef struct cf_b200_append_desc {
     const uint32_t *slots;    /* [row_count], distinct */
     const void *k_rows;
     const void *v_rows;
-    uint32_t row_type;        /* CF_B200_F16 or CF_B200_F32 */
+    uint32_t row_type;        /* CF_B200_F16, CF_B200_BF16 or CF_B200_F32 */
     uint32_t row_count;
     uint32_t *status;         /* optional */
 } cf_b200_append_desc;

@@ -610,7 +610,11 @@ def test_append_rows_entry_point_fills_the_tails_and_reports_a_full_one(native):
         dtype = np.float16 if step % 3 else np.float32
         k = rng.standard_normal((len(slots), 2, 128)).astype(dtype)
         v = rng.standard_normal((len(slots), 2, 128)).astype(dtype)
-        layer.append(slots, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+        dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+        if step % 5 == 4:            # bfloat16 rows: the values the tail must hold are the bf16-rounded ones
+            dk, dv = dk.to(torch.bfloat16), dv.to(torch.bfloat16)
+            k, v = dk.float().cpu().numpy(), dv.float().cpu().numpy()
+        layer.append(slots, dk, dv)
         for i, s in enumerate(slots):
             want_k[s, :, counts[s]] = k[i].astype(np.float16)
             want_v[s, :, counts[s]] = v[i].astype(np.float16)
