@@ -18,7 +18,7 @@ __host__ __device__ inline uint32_t align_up_u32(uint32_t v, uint32_t a) { retur
 // Split-KV workspace. One chunk = `pages_per_unit` consecutive pages of one sequence; one unit = (chunk, kv head).
 //   [0, 64)                       PlanHeader
 //   [64, 64 + 4*(seq_count+1))    chunk_prefix: number of chunks before each sequence
-//   [shared_offset, ...)          shared-prefix partials, per (shared chunk, sequence, local query head), when asked for
+//   [shared_offset, ...)          shared-prefix partials, per (cell, sequence, local query head), when asked for (SharedSplit)
 //   [partials_offset, ...)        per chunk and local query head: float m, float l, float acc[head_dim]
 struct PlanHeader {
     uint32_t chunk_count;
@@ -27,11 +27,36 @@ struct PlanHeader {
     uint32_t chunk_capacity;
     uint32_t overflow;
     uint32_t shared_pages;            // pages at the head of every sequence that the shared-prefix kernel handles (0 = none)
-    uint32_t shared_chunks;           // the shared prefix is cut into this many chunks of
-    uint32_t shared_pages_per_chunk;  // this many pages
-    uint32_t reserved_shared;         // unused (the shared-prefix kernel splits its units statically)
+    uint32_t shared_ctas;             // CTAs of the shared-prefix kernel that take a share of it (0 = none), and
+    uint32_t shared_rounds;           // rounds of eight pages that the shared pages make for one (kv head, row tile)
+    uint32_t reserved_shared;         // unused
     uint32_t pad[7];
 };
+
+// How the shared-prefix kernel's work is cut. The rounds of all (kv head, row tile) pairs form one line, head-tile major:
+// round x belongs to head-tile x / rounds. CTA b of `ctas` takes the rounds [first_round(b), first_round(b + 1)): every CTA
+// gets the same number of rounds to within one, whatever the number of head-tiles. A CTA's stretch inside one head-tile is
+// a unit; it leaves one partial per row, in cell (b - cta_of(the head-tile's first round)) of the row's shared partials.
+// The plan kernel picks `ctas` so that no head-tile meets more than CF_B200_SHARED_CHUNKS_MAX CTAs.
+struct SharedSplit {
+    uint32_t rounds, head_tiles, ctas;
+    __host__ __device__ uint64_t total() const { return static_cast<uint64_t>(rounds) * head_tiles; }
+    __host__ __device__ uint64_t first_round(uint32_t b) const { return total() * b / ctas; }
+    // the CTA whose stretch holds round x: the last b with first_round(b) <= x
+    __host__ __device__ uint32_t cta_of(uint64_t x) const {
+        return static_cast<uint32_t>(((x + 1ull) * ctas + total() - 1ull) / total()) - 1u;
+    }
+};
+// Number of CTAs for the split: all `sm_count` of them where that keeps a head-tile within `cells` CTAs, else a multiple
+// of the head-tiles (stretches then start and end on head-tile boundaries, `cells` or `cells - 1` CTAs per head-tile).
+__host__ __device__ inline uint32_t shared_split_ctas(uint32_t rounds, uint32_t head_tiles, uint32_t sm_count, uint32_t cells) {
+    const uint64_t total = static_cast<uint64_t>(rounds) * head_tiles;
+    if (total == 0 || sm_count == 0) return 0;
+    if (static_cast<uint64_t>(cells) * head_tiles <= sm_count) return head_tiles * (rounds < cells ? rounds : cells);
+    const uint32_t ctas = total < sm_count ? static_cast<uint32_t>(total) : sm_count;
+    if ((ctas + head_tiles - 1u) / head_tiles + 1u <= cells) return ctas;
+    return head_tiles * (cells - 1u);
+}
 
 // What a (chunk, kv head) unit needs to start, written per chunk by the plan kernel so that the attention kernel's
 // warps read one 32-byte record instead of searching the chunk prefix and chasing four dependent loads.

@@ -81,14 +81,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
             if (tid == 0) raise_status(p, CF_B200_DEVSTAT_PREFIX_MISMATCH);
         }
     }
-    uint32_t shared_chunks = 0, shared_per_chunk = 0;
-    if (shared) {
+    uint32_t shared_ctas = 0, shared_rounds = 0;
+    if (shared) {   // an even split of the prefix's rounds over the CTAs of the shared-prefix kernel (SharedSplit)
         const uint32_t row_tiles = (p.seq_count * p.group + 127u) / 128u;
-        // about six equal units per SM (CTA b takes units b, b + grid, ...), so that the last wave is short
-        const uint32_t wanted = (6u * p.sm_count + p.kv_head_span * row_tiles - 1u) / (p.kv_head_span * row_tiles);
-        shared_chunks = min(max(wanted, 1u), min(CF_B200_SHARED_CHUNKS_MAX, (shared + 15u) / 16u));
-        shared_per_chunk = ((shared + shared_chunks - 1u) / shared_chunks + 7u) / 8u * 8u;   // whole rounds of eight pages
-        shared_chunks = (shared + shared_per_chunk - 1u) / shared_per_chunk;
+        shared_rounds = (shared + 7u) / 8u;
+        shared_ctas = shared_split_ctas(shared_rounds, p.kv_head_span * row_tiles, p.sm_count, CF_B200_SHARED_CHUNKS_MAX);
     }
 
     // The visible page range of every batch entry is needed by each pass below; it costs a chain of dependent loads
@@ -220,8 +217,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         hdr->chunk_capacity = static_cast<uint32_t>(min(p.layout.chunk_capacity, static_cast<uint64_t>(0xffffffffu)));
         hdr->overflow = overflow;
         hdr->shared_pages = overflow ? 0u : shared;
-        hdr->shared_chunks = overflow ? 0u : shared_chunks;
-        hdr->shared_pages_per_chunk = shared_per_chunk;
+        hdr->shared_ctas = overflow ? 0u : shared_ctas;
+        hdr->shared_rounds = shared_rounds;
         if (overflow) raise_status(p, CF_B200_DEVSTAT_WORKSPACE);
     }
 }
@@ -470,8 +467,16 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(AttentionParam
             for (int j = 0; j < 4; ++j) wa[j] = wa[j] * so + pa[j] * sn;
             wm = nm;
         }
-        const uint32_t shared_chunks = plan_header(p)->shared_chunks;
-        for (uint32_t c = warp; c < shared_chunks; c += kCombineWarps) {   // the shared prefix's chunks, same rule
+        // the shared prefix's partials, same rule: one per CTA of the shared-prefix kernel that met the row's head-tile
+        const PlanHeader *hdr = plan_header(p);
+        uint32_t cells = 0;
+        if (hdr->shared_pages != 0u && hdr->shared_ctas != 0u) {
+            const uint32_t row_tiles = (p.seq_count * G + 127u) / 128u;
+            const SharedSplit split = {hdr->shared_rounds, p.kv_head_span * row_tiles, hdr->shared_ctas};
+            const uint64_t first = static_cast<uint64_t>((local_q / G) * row_tiles + (seq * G + local_q % G) / 128u) * split.rounds;
+            cells = min(split.cta_of(first + split.rounds - 1u) - split.cta_of(first) + 1u, CF_B200_SHARED_CHUNKS_MAX);
+        }
+        for (uint32_t c = warp; c < cells; c += kCombineWarps) {
             const float *part = shared_partial_ptr(p, c, seq, local_q);
             const float pm = part[0], pl = part[1];
             float pa[4];

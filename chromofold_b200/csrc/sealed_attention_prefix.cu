@@ -6,8 +6,9 @@
 // The per-sequence kernel would decode such a page once per sequence. Here a page is decoded once per tile of 128
 // query rows (rows = sequence x query head of the kv head's group) and contracted with all those rows at once.
 //
-// One CTA of 20 warps per SM works on units = (prefix chunk, kv head, row tile): CTA b takes units b, b + grid, ...
-// (equal-sized, so a static split balances), in rounds of 8 pages = 128 tokens. The warps are specialised:
+// One CTA of 20 warps per SM. The work is cut evenly (SharedSplit): the rounds (8 pages = 128 tokens) of every
+// (kv head, row tile) pair form one line and each CTA takes an equal stretch of it; the part of a stretch inside one
+// pair is a unit, which ends in one partial per row. The warps are specialised:
 //   decoder warps 0..11  the page slots of the CTA's units form one sequence; warp w takes slots w, w + 12, ... It
 //                        receives the record by one bulk async copy (mbarrier, bounded wait), decodes it with the
 //                        lane-per-block decoders INTO REGISTERS (32 packed quads per lane), starts the copy of its next
@@ -233,25 +234,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// What both groups derive from a unit number.
+// What both groups derive from a unit number: unit j of CTA b is the CTA's stretch of rounds inside the j-th head-tile it
+// meets (SharedSplit). `valid` is false past the CTA's last unit.
 struct UnitShape {
-    uint32_t tile_index, head_local, chunk, kv_head, page_begin, page_end;
+    uint32_t tile_index, head_local, chunk, kv_head, page_begin, page_end, valid;
 };
-__device__ __forceinline__ UnitShape unit_shape(const AttentionParams &p, uint32_t unit, uint32_t row_tiles, uint32_t per_chunk,
-                                                uint32_t shared_pages) {
-    UnitShape u;
-    u.tile_index = unit % row_tiles;
-    u.head_local = (unit / row_tiles) % p.kv_head_span;
-    u.chunk = unit / (row_tiles * p.kv_head_span);
+__device__ __forceinline__ UnitShape unit_shape(const AttentionParams &p, const SharedSplit &split, uint32_t cta, uint32_t unit,
+                                                uint32_t row_tiles, uint32_t shared_pages) {
+    UnitShape u = {};
+    const uint64_t lo = split.first_round(cta), hi = split.first_round(cta + 1u);
+    const uint64_t head_tile = lo / split.rounds + unit, base = head_tile * split.rounds;
+    u.valid = lo < hi && base < hi;
+    if (!u.valid) return u;
+    const uint32_t r0 = static_cast<uint32_t>((lo > base ? lo : base) - base);
+    const uint32_t r1 = static_cast<uint32_t>((hi < base + split.rounds ? hi : base + split.rounds) - base);
+    u.tile_index = static_cast<uint32_t>(head_tile % row_tiles);
+    u.head_local = static_cast<uint32_t>(head_tile / row_tiles);
+    u.chunk = cta - split.cta_of(base);
     u.kv_head = p.kv_head_begin + u.head_local;
-    u.page_begin = u.chunk * per_chunk;
-    u.page_end = min(u.page_begin + per_chunk, shared_pages);
+    u.page_begin = 8u * r0;
+    u.page_end = min(8u * r1, shared_pages);
     return u;
 }
 
 // ---- decoder group: warps 0..11 -----------------------------------------------------------------------------------
-// The CTA's units are blockIdx.x, blockIdx.x + gridDim.x, ... Their page slots (pages of a unit padded to whole rounds of
-// eight) form one sequence; decoder warp w takes slots w, w + 12, w + 24, ... A slot is decoded into registers first;
+// The page slots of the CTA's units (pages of a unit padded to whole rounds of eight) form one sequence; decoder warp w takes slots w, w + 12, w + 24, ... A slot is decoded into registers first;
 // only then does the warp wait for the tile pair of the slot's round, so that decoding never waits for the tensor core.
 struct SlotCursor {
     uint32_t unit, valid, first_slot, first_round, slots;   // of the unit that holds the slot
@@ -259,7 +266,7 @@ struct SlotCursor {
 };
 
 __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t warp, uint32_t lane,
-                                             uint32_t row_tiles, uint32_t unit_count) {
+                                             uint32_t row_tiles, const SharedSplit &split) {
     const uint32_t *k_slot = reinterpret_cast<const uint32_t *>(smem);
     const uint32_t *v_slot = k_slot + 4096;
     const uint16_t *k_lut = reinterpret_cast<const uint16_t *>(v_slot + 4096);
@@ -268,21 +275,19 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
     uint64_t *bar = bars + warp, *bar_full = bars + kBarFull, *bar_free = bars + kBarFree;
     uint32_t *round_desc = reinterpret_cast<uint32_t *>(smem + kOffRound);
-    const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
+    const uint32_t shared_pages = hdr->shared_pages;
     const uint32_t *table_row = p.page_table + static_cast<uint64_t>(slot_of(p, 0)) * p.page_table_stride;
 
     auto load_unit = [&](SlotCursor &c) {
-        c.valid = c.unit < unit_count;
-        if (c.valid) {
-            c.u = unit_shape(p, c.unit, row_tiles, per_chunk, shared_pages);
-            c.slots = (c.u.page_end - c.u.page_begin + 7u) / 8u * 8u;
-        }
+        c.u = unit_shape(p, split, blockIdx.x, c.unit, row_tiles, shared_pages);
+        c.valid = c.u.valid;
+        if (c.valid) c.slots = (c.u.page_end - c.u.page_begin + 7u) / 8u * 8u;
     };
     auto seek = [&](SlotCursor &c, uint32_t n) {   // the unit that holds slot n (n only grows)
         while (c.valid && n >= c.first_slot + c.slots) {
             c.first_slot += c.slots;
             c.first_round += c.slots / 8u;
-            c.unit += gridDim.x;
+            c.unit += 1u;
             load_unit(c);
         }
     };
@@ -318,7 +323,7 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
     };
 
     SlotCursor cur;
-    cur.unit = blockIdx.x;
+    cur.unit = 0;
     cur.first_slot = 0;
     cur.first_round = 0;
     cur.slots = 0;
@@ -452,12 +457,12 @@ __device__ __forceinline__ void decoder_role(const AttentionParams &p, uint8_t *
 // sum of two products, which equals the fp32-query product to 2^-22 relative.
 template <bool kSplitQ>
 __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *smem, PlanHeader *hdr, uint32_t tmem, uint32_t warp,
-                                             uint32_t lane, uint32_t row_tiles) {
+                                             uint32_t lane, uint32_t row_tiles, const SharedSplit &split) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
     uint64_t *bar_full = bars + kBarFull, *bar_free = bars + kBarFree, *bar_s = bars + kBarS, *bar_o = bars + kBarO;
     const uint32_t *round_desc = reinterpret_cast<const uint32_t *>(smem + kOffRound);
     float *row_max = reinterpret_cast<float *>(smem + kOffRowMax);
-    const uint32_t shared_pages = hdr->shared_pages, per_chunk = hdr->shared_pages_per_chunk;
+    const uint32_t shared_pages = hdr->shared_pages;
     const uint32_t G = p.group, rows_total = p.seq_count * G;
     // Thread (warp w, lane) owns row 32 (w & 3) + lane — its warp's quarter of the tensor-memory lanes — and the 64 score
     // columns (4 pages) of half (w - 12) >> 2; the two threads of a row meet through row_max[].
@@ -498,7 +503,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
         if (unit == kStopUnit) break;
 
         if (flags & kFirstRound) {   // Q rows of the unit: global memory -> tensor memory (binary16 pairs, 64 columns)
-            u = unit_shape(p, unit, row_tiles, per_chunk, shared_pages);
+            u = unit_shape(p, split, blockIdx.x, unit, row_tiles, shared_pages);
             m_run = -CUDART_INF_F;
             l_run = 0.0f;
             v_unit = 0.0f;
@@ -714,7 +719,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
     uint32_t *misc = reinterpret_cast<uint32_t *>(smem + kOffMisc);
 
     PlanHeader *hdr = plan_header(p);
-    if (hdr->shared_pages == 0 || hdr->shared_chunks == 0) return;   // uniform: nothing shared, or the plan refused the hint
+    // uniform: nothing shared, the plan refused the hint, or the split leaves this CTA without a share
+    if (hdr->shared_pages == 0 || blockIdx.x >= hdr->shared_ctas) return;
 
     load_tables(smem, p, tid, kTcThreads);
     if (tid == 0) {
@@ -736,14 +742,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefix_attention_kernel(Attenti
 
     const uint32_t rows_total = p.seq_count * p.group;
     const uint32_t row_tiles = (rows_total + 127u) / 128u;
-    const uint32_t unit_count = hdr->shared_chunks * p.kv_head_span * row_tiles;
+    const SharedSplit split = {hdr->shared_rounds, p.kv_head_span * row_tiles, hdr->shared_ctas};
 
     if (warp < kDecodeWarps) {   // whole warpgroups on either side: the register split is per warpgroup
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDecoderRegs));
-        decoder_role(p, smem, hdr, warp, lane, row_tiles, unit_count);
+        decoder_role(p, smem, hdr, warp, lane, row_tiles, split);
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        softmax_role<kSplitQ>(p, smem, hdr, tmem, warp, lane, row_tiles);
+        softmax_role<kSplitQ>(p, smem, hdr, tmem, warp, lane, row_tiles, split);
     }
 
     tc_fence_before();

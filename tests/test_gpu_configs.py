@@ -211,7 +211,8 @@ def test_shared_prefix_with_several_units_per_cta(native, oracle, coder):
 
 def test_shared_prefix_under_kv_head_sharding_and_fp32_queries(native, oracle):
     """The hint combined with the other launch options: a kv-head shard (each rank of a head-sharded deployment passes
-    kv_head_begin / kv_head_span) writes exactly its heads' columns of the unsharded result; fp32 queries give the
+    kv_head_begin / kv_head_span) writes its heads' columns of the unsharded result (to fp32 rounding: how the prefix is
+    cut over the CTAs depends on the number of heads, and with it the order the partials merge in); fp32 queries give the
     fp16-query result within tolerance whichever kernel serves them."""
     import torch
     from chromofold_b200.workloads import build_sealed_layer
@@ -237,7 +238,7 @@ def test_shared_prefix_under_kv_head_sharding_and_fp32_queries(native, oracle):
         layer.attention(q, out=out, kernel=native.KERNEL_LANES, shared_prefix_pages=pages, kv_head_begin=begin, kv_head_span=span)
         got = out.cpu().numpy()
         lo, hi = begin * group, (begin + span) * group
-        assert np.array_equal(got[:, lo:hi], full[:, lo:hi])                  # same units, same arithmetic
+        assert np.allclose(got[:, lo:hi], full[:, lo:hi], rtol=1e-5, atol=2e-6)
         assert np.all(got[:, :lo] == 7.0) and np.all(got[:, hi:] == 7.0)      # other heads' columns untouched
     f32 = layer.attention(q.float(), shared_prefix_pages=pages).cpu().numpy()
     ok, err = attention_close(f32, full)
