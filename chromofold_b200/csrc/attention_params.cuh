@@ -63,7 +63,7 @@ __device__ __forceinline__ float *partial_ptr(const AttentionParams &p, uint32_t
     return reinterpret_cast<float *>(p.workspace + p.layout.partials_offset) +
            (static_cast<uint64_t>(chunk) * (p.kv_head_span * p.group) + local_q_head) * p.layout.partial_stride_floats;
 }
-// Shared-prefix partial of (shared chunk, batch entry, local query head).
+// Shared-prefix partial of (cell, batch entry, local query head); cells as SharedSplit numbers them.
 __device__ __forceinline__ float *shared_partial_ptr(const AttentionParams &p, uint32_t chunk, uint32_t seq, uint32_t local_q_head) {
     return reinterpret_cast<float *>(p.workspace + p.layout.shared_offset) +
            ((static_cast<uint64_t>(chunk) * p.seq_count + seq) * (p.kv_head_span * p.group) + local_q_head) *

@@ -147,7 +147,7 @@ typedef struct cf_b200_sealed_attention_desc {
 #define CF_B200_DEVSTAT_ARENA_FULL 0x10u     /* the sealer found no room in the arena */
 #define CF_B200_DEVSTAT_PREFIX_MISMATCH 0x20u /* shared_prefix_pages was set but the page-table rows differ */
 #define CF_B200_DEVSTAT_TAIL_FULL 0x80u      /* an append found its slot's unsealed tail full; the row was not stored */
-#define CF_B200_SHARED_CHUNKS_MAX 16u        /* a shared prefix is cut into at most this many chunks */
+#define CF_B200_SHARED_CHUNKS_MAX 16u        /* a batch entry's shared-prefix result comes in at most this many partials */
 
 /* Test hook for the bounded waits of the attention kernels: from the next launch on, the record of page id
  * skip_copy_page_id is armed on its barrier but never fetched, and every wait gives up after wait_polls polls (each
