@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(AttentionParams p) {
         const uint32_t row_tiles = (p.seq_count * p.group + 127u) / 128u;
         shared_rounds = (shared + 7u) / 8u;
         shared_ctas = shared_split_ctas(shared_rounds, p.kv_head_span * row_tiles, p.sm_count, CF_B200_SHARED_CHUNKS_MAX);
+        if (shared_ctas == 0u) shared = 0;   // no CTA to take it: the pages stay with the per-sequence chunks
     }
 
     // The visible page range of every batch entry is needed by each pass below; it costs a chain of dependent loads

@@ -35,7 +35,8 @@
 // queries only: the row is split into binary16(q) and its rounding residue, S = Q K^T + Q residue K^T) (binary16 pairs per
 // column, row = lane). B tiles use the no-swizzle K-major canonical layout: 8 rows x 16 bytes core matrices, element
 // (row r, 16-byte chunk c) at (r % 8) * 16 + (r / 8) * 2048 + c * 128 bytes.
-// The page's V scale relative to the unit's first page rides on P, O is kept in units of that first scale.
+// The page's V scale relative to the largest one met so far in the unit rides on P (never above 1, so the binary16
+// weights cannot overflow); O is kept in units of that scale and rescaled when a larger one arrives.
 // Every mbarrier wait is bounded. A warp whose wait ran out raises CF_B200_DEVSTAT_WAIT_EXPIRED and skips all later
 // waits and work; a decoder warp still arrives for each of its slots, a softmax warp still takes part in its group's
 // barriers, which OR-reduce the failure so that the whole group leaves its loop at the same point; the CTA then frees
@@ -485,7 +486,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
     };
     UnitShape u = {};
     float m_run = -CUDART_INF_F, l_run = 0.0f;   // the row's running maximum; this thread's half of its running sum
-    float v_unit = 0.0f;                          // V scale of the unit's first present page: the unit of O
+    float v_unit = 0.0f;                          // largest V scale met so far in the unit: the unit of O
     bool o_started = false;
 
     for (uint32_t it = 0;; ++it) {
@@ -568,9 +569,10 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             }
             umma_commit(bar_s);
         }
-        if (v_unit == 0.0f)
-            for (uint32_t pg = 0; pg < kRoundPages; ++pg)
-                if (v_unit == 0.0f && __float_as_uint(meta[4 * pg + 2]) != 0u) v_unit = meta[4 * pg + 1];
+        float round_scale = 0.0f;   // largest V scale among the round's present pages
+#pragma unroll
+        for (uint32_t pg = 0; pg < kRoundPages; ++pg)
+            if (__float_as_uint(meta[4 * pg + 2]) != 0u) round_scale = fmaxf(round_scale, meta[4 * pg + 1]);
         if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_s, s_phase & 1u, p.wait_polls))) {
             failed = true;
             if (lane == 0) raise_status(p, CF_B200_DEVSTAT_WAIT_EXPIRED);
@@ -615,15 +617,23 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             const float z = m_new == -CUDART_INF_F ? 0.0f : m_new;
             const float alpha = fast_exp2(m_run - z);   // m_run = -inf gives 0
             m_run = m_new;
-            // O in tensor memory follows the new maximum (this thread's 64 channels); skipped when no row of the warp moved
-            if (o_started && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+            // The unit of O is the largest V scale met so far in the unit, so that a page's scale relative to it (which
+            // rides on the binary16 weights) never exceeds 1; when a round brings a larger one, O changes unit with it.
+            float o_scale = alpha;
+            if (round_scale > v_unit) {
+                o_scale *= v_unit / round_scale;   // v_unit = 0: nothing accumulated yet
+                v_unit = round_scale;
+            }
+            // O in tensor memory follows the new maximum and unit (this thread's 64 channels); skipped when no row of the
+            // warp moved
+            if (o_started && !__all_sync(0xffffffffu, o_scale == 1.0f)) {
 #pragma unroll 1
                 for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
                     uint32_t o_raw[32];
                     tmem_load32(tmem_row + kColO + 64u * half + c0, o_raw);
                     tmem_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * alpha);
+                    for (int j = 0; j < 32; ++j) o_raw[j] = __float_as_uint(__uint_as_float(o_raw[j]) * o_scale);
                     tmem_store32(tmem_row + kColO + 64u * half + c0, o_raw);
                 }
             }

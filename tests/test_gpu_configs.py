@@ -380,3 +380,32 @@ def test_a_batch_of_three_thousand_short_sequences(native):
     assert ok, err
     ok, err = attention_close(fast, oracle_from_layer(layer, q.cpu().numpy()))
     assert ok, err
+
+
+def test_shared_prefix_whose_first_page_has_a_tiny_v_scale(native, oracle):
+    """The shared-prefix kernel keeps O in units of a V scale and lets each page's scale ride on its binary16 weights.
+    A unit whose first page holds almost-zero V rows (scale 2^-24) followed by ordinary pages (scale ~ 0.02) must not
+    push those weights past the binary16 range: the result has to equal the per-sequence path's."""
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    n, pages = 8, 24
+    layer, info = build_sealed_layer(np.array([0] * n), coder="rans4", seed=120, extra_pages_per_sequence=pages + 2,
+                                     reserve_pages=2 * n)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(121)
+    for t in range(16 * pages):
+        k = (torch.randn((1, 8, 128), generator=g, device="cuda") * 0.7).float()
+        v = (torch.randn((1, 8, 128), generator=g, device="cuda") * (1e-7 if t < 16 else 0.7)).float()
+        layer.append([0], k, v)
+        layer.seal_full_pages()
+    for s in range(1, n):
+        layer.copy_sequence(0, s)
+    q = _q(n, 32, 122)
+    plain = layer.attention(q, kernel=native.KERNEL_LANES).cpu().numpy()
+    shared = layer.attention(q, kernel=native.KERNEL_LANES, shared_prefix_pages=pages).cpu().numpy()
+    assert layer.device_status() == 0
+    assert np.all(np.isfinite(shared))
+    ok, err = attention_close(shared, plain)
+    assert ok, err
+    ok, err = attention_close(shared, oracle_from_layer(layer, q.cpu().numpy()))
+    assert ok, err
