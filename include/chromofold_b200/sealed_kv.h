@@ -88,7 +88,10 @@ typedef struct cf_b200_sealed_attention_desc {
 
     const void *queries;                 /* [seq_count][query_head_count][head_dim] */
     void *output;                        /* same shape */
-    uint32_t query_type;                 /* CF_B200_F16 or CF_B200_F32 */
+    uint32_t query_type;                 /* CF_B200_F16 or CF_B200_F32. At head_dim 128 / 96 / 64 / 32 an fp32 row is
+                                          * contracted as binary16(q) + binary16(q - binary16(q)) (scores equal to the
+                                          * fp32 product to 2^-22 relative), which holds finite |q| up to 65504; larger
+                                          * components give NaN there. Other geometries compute in fp32 throughout. */
     uint32_t output_type;                /* CF_B200_F16 or CF_B200_F32 */
     float softmax_scale;
     uint32_t causal_window;              /* 0 = all history */
