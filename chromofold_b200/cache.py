@@ -74,6 +74,7 @@ class SealedKvLayer:
         self.h_tail = np.zeros(max_sequences, np.int64)
         self.next_page_id = 1  # page id 0 stays unpublished so a zeroed table entry is detectable
         self.host_tables = (N.CodebookTables(), N.CodebookTables())
+        self._codebooks_set = False
 
     # -- codebooks ---------------------------------------------------------------------------------
     @_on_own_device
@@ -82,6 +83,13 @@ class SealedKvLayer:
             h = np.ascontiguousarray(hist, np.uint64)
             N.check("codebook_build", self.lib.cf_b200_codebook_build(h.ctypes.data_as(C.c_void_p), C.byref(host)))
             dev.copy_(torch.frombuffer(bytearray(bytes(host)), dtype=torch.uint8))
+        self._codebooks_set = True
+
+    def _need_codebooks(self):
+        """An entropy coder codes against the layer's tables; all-zero tables would give records that decode to
+        something else than what was sealed."""
+        if self.coder != N.CODER_FIXED8 and not self._codebooks_set:
+            raise RuntimeError("set_codebooks() must be called before pages are sealed with an entropy coder")
 
     @_on_own_device
     def histograms(self, slots=None):
@@ -145,6 +153,7 @@ class SealedKvLayer:
         d_ids = torch.as_tensor(ids, device=self.device)
         d_rows = torch.as_tensor(rows, device=self.device)
         d = self._seal_desc(d_slots, d_ids, d_rows)
+        self._need_codebooks()
         N.check("seal_pages", self.lib.cf_b200_seal_pages_async(C.byref(d), _stream_ptr()))
         self.h_page_table[full, page_index] = ids
         self.page_table[d_slots.long(), torch.as_tensor(page_index, device=self.device)] = d_ids
@@ -177,6 +186,7 @@ class SealedKvLayer:
         d_ids = torch.as_tensor(ids, device=self.device)
         d = self._seal_desc(d_tiles, d_ids, None)
         d.tail_k, d.tail_v = k_tiles.data_ptr(), v_tiles.data_ptr()
+        self._need_codebooks()
         N.check("seal_pages", self.lib.cf_b200_seal_pages_async(C.byref(d), _stream_ptr()))
         self.h_page_table[slots, page_index] = ids
         self.page_table[torch.as_tensor(slots, device=self.device), torch.as_tensor(page_index, device=self.device)] = d_ids

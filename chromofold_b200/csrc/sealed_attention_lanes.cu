@@ -63,6 +63,8 @@ struct UnitState {
 // What the kernel does with the symbols: attention; or (measurement) fold them into a checksum; or (test) store
 // every quad the lane decoders yield to global memory, so that they can be compared symbol for symbol.
 constexpr int kAttend = 0, kFold = 1, kDump = 2;
+// The softmax weights go to the tensor cores as binary16 (value + rounding residue) scaled by this power of two.
+constexpr float kWeightScale = 32768.0f;
 
 // Where a lane finds its B fragments of S = K * Q^T (column n = parity*4 + head; zero where the lane's slice of the
 // contraction belongs to the other token of the pair).
@@ -597,12 +599,15 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
                         u.m1[n] = n1;
                         // P goes to the tensor cores as fp16; the rounding residue is fed as a second operand so that
                         // P V is accurate to fp32 level whatever the magnitude of V
+                        // The weights (at most 1) are scaled by 2^15 on the way, O by 2^-15 at the unit's end, both exact:
+                        // binary16 then resolves weights down to 2^-40 of the row maximum instead of 2^-25.
                         const uint32_t h0 = 4u * n + my_head0;
-                        const __half p0h = __float2half_rn(p0), p1h = __float2half_rn(p1);
+                        const float w0 = p0 * kWeightScale, w1 = p1 * kWeightScale;
+                        const __half p0h = __float2half_rn(w0), p1h = __float2half_rn(w1);
                         p_rows[h0 * 16u + my_token] = p0h;
                         p_rows[(h0 + 1u) * 16u + my_token] = p1h;
-                        p_rows_lo[h0 * 16u + my_token] = __float2half_rn(p0 - __half2float(p0h));
-                        p_rows_lo[(h0 + 1u) * 16u + my_token] = __float2half_rn(p1 - __half2float(p1h));
+                        p_rows_lo[h0 * 16u + my_token] = __float2half_rn(w0 - __half2float(p0h));
+                        p_rows_lo[(h0 + 1u) * 16u + my_token] = __float2half_rn(w1 - __half2float(p1h));
                         if (g == 0 && t < 2) {
                             alpha_s[h0] = a0;
                             alpha_s[h0 + 1u] = a1;
@@ -706,7 +711,7 @@ __global__ void __launch_bounds__(kThreadsOf<NG, NB>, 1) lanes_attention_kernel(
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint32_t owner = 4u * (2u * t + (c & 1)) + (g >> 2) + 2u * (c >> 1);  // lane whose V block it is
-                        dst[kVCh * owner + dd] = u.acc[n][dd][c] * v_scale_prev;
+                        dst[kVCh * owner + dd] = u.acc[n][dd][c] * (v_scale_prev * (1.0f / kWeightScale));
                     }
                 }
             }

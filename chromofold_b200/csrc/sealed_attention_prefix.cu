@@ -68,6 +68,7 @@ static_assert(kTcSmem <= 232448, "the shared-prefix kernel must fit the 227 KB o
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColP = 320, kColPResidue = 384, kColQResidue = 448;
 constexpr uint32_t kStopUnit = 0xffffffffu;
+constexpr float kWeightScale = 32768.0f;   // power of two the binary16 weights are scaled by (O sheds it at a unit's end)
 constexpr uint32_t kFirstRound = 1u, kLastRound = 2u;   // round flags
 constexpr uint32_t kSoftmaxBarrier = 1;   // named barrier (0 is __syncthreads)
 // Register split (setmaxnreg). A CTA can only redistribute the registers it was launched with: kLaunchRegs per thread,
@@ -645,7 +646,9 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
                 const uint32_t pg = 4u * half + q;
                 const uint32_t count = __float_as_uint(meta[4 * pg + 2]);
                 const float ks = meta[4 * pg];
-                const float ratio = count ? __fdividef(meta[4 * pg + 1], v_unit) : 0.0f;
+                // the weights (at most 1) also carry 2^15, exactly, which O sheds at the unit's end: binary16 then resolves
+                // weights down to 2^-40 of the row maximum instead of 2^-25
+                const float ratio = count ? __fdividef(meta[4 * pg + 1], v_unit) * kWeightScale : 0.0f;
                 uint32_t hi[8], lo[8];
 #pragma unroll
                 for (int j = 0; j < 16; j += 2) {
@@ -694,6 +697,7 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
             const uint32_t row = u.tile_index * 128u + row_in_tile;
             const bool live = row < rows_total;   // whole warps go on: the tensor-memory loads are warp-wide
             float *dst = live ? shared_partial_ptr(p, u.chunk, row / G, u.head_local * G + row % G) : nullptr;
+            const float o_unit = v_unit * (1.0f / kWeightScale);
             if (live && half == 0) {
                 dst[0] = m_run;
                 dst[1] = row_max[row_in_tile] + row_max[128u + row_in_tile];
@@ -708,9 +712,9 @@ __device__ __forceinline__ void softmax_role(const AttentionParams &p, uint8_t *
                     for (int t = 0; t < 8; ++t) {   // columns t, t + 8, t + 16, t + 24 of the 32 are 4 consecutive channels
                         float *out = dst + 2 + 64u * half + c0 + 4 * t;
                         *reinterpret_cast<float2 *>(out) =
-                            make_float2(__uint_as_float(o_raw[t]) * v_unit, __uint_as_float(o_raw[t + 8]) * v_unit);
+                            make_float2(__uint_as_float(o_raw[t]) * o_unit, __uint_as_float(o_raw[t + 8]) * o_unit);
                         *reinterpret_cast<float2 *>(out + 2) =
-                            make_float2(__uint_as_float(o_raw[t + 16]) * v_unit, __uint_as_float(o_raw[t + 24]) * v_unit);
+                            make_float2(__uint_as_float(o_raw[t + 16]) * o_unit, __uint_as_float(o_raw[t + 24]) * o_unit);
                     }
                 }
             }

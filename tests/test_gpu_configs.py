@@ -391,6 +391,7 @@ def test_shared_prefix_whose_first_page_has_a_tiny_v_scale(native, oracle):
     n, pages = 8, 24
     layer, info = build_sealed_layer(np.array([0] * n), coder="rans4", seed=120, extra_pages_per_sequence=pages + 2,
                                      reserve_pages=2 * n)
+    layer.set_codebooks(np.ones(256, np.uint64), np.ones(256, np.uint64))   # nothing was sealed yet to calibrate on
     g = torch.Generator(device="cuda")
     g.manual_seed(121)
     for t in range(16 * pages):

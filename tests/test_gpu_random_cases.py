@@ -1,0 +1,112 @@
+"""Randomised cases of the decode-attention path: geometry, coder, batch shape, context lengths (empty and ragged ones
+included), shared prefixes, kv-head shards, unit sizes, causal windows, fp32 queries and query positions are drawn from
+a seed, K and V rows with magnitudes that change from token to token by orders of magnitude, and the lane-per-block
+kernels (with the shared-prefix kernel where the case has a prefix) are compared with the CPU oracle or, where the
+oracle has no such option, with the any-geometry kernel, which computes in fp32 throughout."""
+import numpy as np
+import pytest
+
+from helpers import oracle_from_layer
+
+pytestmark = pytest.mark.gpu
+
+GEOMETRIES = [(128, 64), (128, 64), (128, 128), (128, 256), (64, 64), (96, 64), (32, 64), (64, 128)]   # head_dim, block
+HEADS = [(32, 8), (16, 8), (8, 8), (64, 8), (8, 2)]
+CODERS = ["rans4", "huffman4", "rans", "huffman", "fixed8"]
+
+
+def _close(actual, expected):
+    """|a - e| <= 2e-4 * (largest |e| of the row + 0.5 % of the largest |e| of the case): far inside the 2e-3 bar, and
+    scaled to the data because the V rows span six orders of magnitude. The second term is there for rows whose exact
+    value is nearly zero next to the values the row is averaged from (a dominant token whose V quantised to zero):
+    the kernels resolve softmax weights down to 2^-40 of the row maximum, the fp32 checkers further."""
+    a, e = np.asarray(actual, np.float64), np.asarray(expected, np.float64)
+    scale = np.abs(e).max(axis=-1, keepdims=True) + 5e-3 * np.abs(e).max() + 1e-30
+    err = np.abs(a - e) / scale
+    return bool(np.all(np.isfinite(a)) and err.max() <= 2e-4), float(err.max())
+
+
+def _case(native, seed):
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    rng = np.random.default_rng(seed)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    n = int(rng.integers(1, 13))
+    head_dim, block = GEOMETRIES[int(rng.integers(0, len(GEOMETRIES)))]
+    hq, hkv = HEADS[int(rng.integers(0, len(HEADS)))]
+    coder = CODERS[int(rng.integers(0, len(CODERS)))]
+    group = hq // hkv
+    prefix_pages = int(rng.integers(1, 12)) if (head_dim == 128 and block == 64 and 128 % group == 0 and rng.random() < 0.5) else 0
+    contexts = rng.integers(0, 300, n)
+    if rng.random() < 0.3:
+        contexts[int(rng.integers(0, n))] = 0
+    pages = int(contexts.max()) // 16 + prefix_pages + 3
+    layer, _ = build_sealed_layer(np.array([0] * n), query_heads=hq, kv_heads=hkv, head_dim=head_dim, block_size=block,
+                                  coder=coder, seed=seed, extra_pages_per_sequence=pages, reserve_pages=n * pages + 8)
+    hist = np.rint(1e6 * np.exp(-np.abs(np.arange(256) - 128) / float(rng.uniform(2, 40)))).astype(np.uint64) + 1
+    layer.set_codebooks(hist, hist)
+    wild = rng.random() < 0.6
+
+    def rows(count):
+        k = torch.randn((count, hkv, head_dim), generator=g, device="cuda")
+        v = torch.randn((count, hkv, head_dim), generator=g, device="cuda")
+        if wild:   # a new magnitude for every token
+            k = k * float(10.0 ** rng.uniform(-2, 0.7))
+            v = v * float(10.0 ** rng.uniform(-4, 2))
+        return k.float(), v.float()
+
+    for _ in range(16 * prefix_pages):       # the shared prefix: sealed on slot 0, then referenced by every other slot
+        layer.append([0], *rows(1))
+        layer.seal_full_pages()
+    for s in range(1, n):
+        if prefix_pages:
+            layer.copy_sequence(0, s)
+    for t in range(int(contexts.max())):
+        slots = [s for s in range(n) if contexts[s] > t]
+        layer.append(slots, *rows(len(slots)))
+        layer.seal_full_pages()
+
+    q = (torch.randn((n, hq, head_dim), generator=g, device="cuda") * float(10.0 ** rng.uniform(-1, 0.5))).half()
+    options = {}
+    if prefix_pages and rng.random() < 0.8:
+        options["shared_prefix_pages"] = prefix_pages
+    if rng.random() < 0.3:
+        span = int(rng.integers(1, hkv + 1))
+        options["kv_head_begin"], options["kv_head_span"] = int(rng.integers(0, hkv - span + 1)), span
+    if rng.random() < 0.3:
+        options["min_pages_per_unit"] = int(rng.integers(1, 9))
+    if rng.random() < 0.25 and "shared_prefix_pages" not in options:
+        options["causal_window"] = int(rng.integers(1, 200))
+    positions = None
+    if rng.random() < 0.25:   # query tokens somewhere inside what is cached (behind the shared prefix, if claimed)
+        cached = (layer.h_sealed[:n] + layer.h_tail[:n]).astype(np.int64)
+        low = 16 * prefix_pages if "shared_prefix_pages" in options else 0
+        positions = torch.from_numpy(np.array([int(rng.integers(low, max(c, low) + 1)) for c in cached], np.int32)).cuda()
+        options["query_positions"] = positions
+    queries = q.float() if rng.random() < 0.3 else q
+
+    out = torch.full((n, hq, head_dim), 7.0, dtype=torch.float32, device="cuda")
+    layer.attention(queries, out=out, kernel=native.KERNEL_LANES, **options)
+    assert layer.device_status() == 0
+    got = out.cpu().numpy()
+    if positions is None:
+        want = oracle_from_layer(layer, q.cpu().numpy(), causal_window=options.get("causal_window", 0))
+    else:
+        plain = {k: v for k, v in options.items() if k in ("causal_window", "query_positions")}
+        want = layer.attention(q, kernel=native.KERNEL_GENERIC, **plain).cpu().numpy()
+        assert layer.device_status() == 0
+    lo = options.get("kv_head_begin", 0) * group
+    hi = lo + options.get("kv_head_span", hkv) * group
+    ok, err = _close(got[:, lo:hi], want[:, lo:hi])
+    what = dict(seed=seed, n=n, head_dim=head_dim, block=block, heads=(hq, hkv), coder=coder, prefix_pages=prefix_pages,
+                wild=wild, options={k: v for k, v in options.items() if k != "query_positions"},
+                positions=None if positions is None else positions.cpu().tolist(), contexts=contexts.tolist())
+    assert ok, (err, what)
+    assert np.all(got[:, :lo] == 7.0) and np.all(got[:, hi:] == 7.0), what    # the other heads' columns are not touched
+
+
+@pytest.mark.parametrize("first", range(0, 96, 8))
+def test_random_cases_against_the_fp32_checkers(native, oracle, first):
+    for seed in range(first, first + 8):
+        _case(native, 1000 + seed)
