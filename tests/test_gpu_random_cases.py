@@ -110,3 +110,74 @@ def _case(native, seed):
 def test_random_cases_against_the_fp32_checkers(native, oracle, first):
     for seed in range(first, first + 8):
         _case(native, 1000 + seed)
+
+
+SEAL_GEOMETRIES = [(128, 64), (128, 64), (128, 128), (128, 256), (64, 64), (96, 64), (32, 64), (64, 128), (96, 128)]
+
+
+def _rows_of_some_kind(rng, shape):
+    """K or V rows [kv head][token][channel] of one of eight kinds, at a magnitude between 1e-9 and 1e5."""
+    kind = int(rng.integers(0, 8))
+    mag = float(10.0 ** rng.uniform(-9, 5))
+    if kind == 0:
+        x = rng.laplace(0, 1, shape) * mag
+    elif kind == 1:
+        x = rng.normal(0, 1, shape) * mag
+    elif kind == 2:
+        x = rng.uniform(-1, 1, shape) * mag
+    elif kind == 3:   # a few outliers over a quiet floor
+        x = rng.normal(0, 1, shape) * mag * 1e-3
+        x.reshape(-1)[rng.integers(0, x.size, 5)] = rng.choice([-1, 1], 5) * mag
+    elif kind == 4:
+        x = np.zeros(shape)
+    elif kind == 5:
+        x = np.full(shape, mag) * rng.choice([-1, 1])
+    elif kind == 6:   # on and around the quantiser's rounding boundaries
+        scale = np.float32(np.float16(mag / 127)) if 0 < mag / 127 < 6e4 else np.float32(1.0)
+        x = np.float64(scale) * (rng.integers(-127, 127, shape) + 0.5) * (1.0 + rng.integers(-3, 4, shape) * 2.0 ** -24)
+        x.reshape(-1)[0] = 127.0 * float(scale)
+    else:             # a magnitude per token
+        x = rng.normal(0, 1, shape) * (10.0 ** rng.uniform(-6, 2, (shape[0], shape[1], 1)))
+    return x.astype(np.float32)
+
+
+@pytest.mark.parametrize("first", range(0, 120, 20))
+def test_random_sealer_cases_are_byte_exact(native, oracle, first):
+    """The GPU sealer (both kernels: compile-time geometry and any geometry) against the oracle's records, byte for byte:
+    random geometry, coder, codebook, rows per page, fp32 or binary16 rows of the kinds above."""
+    import ctypes as C
+    import torch
+    from chromofold_b200.cache import SealedKvLayer
+    from helpers import hist_for_coder, laplace_codes
+    for seed in range(2000 + first, 2000 + first + 20):
+        rng = np.random.default_rng(seed)
+        d, block = SEAL_GEOMETRIES[int(rng.integers(0, len(SEAL_GEOMETRIES)))]
+        coder = int(rng.integers(0, 5))
+        hkv, t, n = 2, 16, 4
+        hist = hist_for_coder(laplace_codes(rng, 1 << 15, float(rng.uniform(1.5, 40))).astype(np.int16) + 128, coder)
+        kcb, vcb = oracle.codebook_from_hist(hist), oracle.codebook_from_hist(hist[::-1].copy())
+        layer = SealedKvLayer(kv_heads=hkv, query_heads=4, head_dim=d, page_tokens=t, block_size=block, coder=coder,
+                              max_sequences=n, max_pages_per_sequence=4, max_pages=64, arena_bytes=2 << 20)
+        layer.set_codebooks(hist, hist[::-1].copy())
+        rows = [int(rng.integers(1, 17)) if rng.random() < 0.4 else 16 for _ in range(n)]
+        k = np.stack([_rows_of_some_kind(rng, (hkv, t, d)) for _ in range(n)])
+        v = np.stack([_rows_of_some_kind(rng, (hkv, t, d)) for _ in range(n)])
+        half = rng.random() < 0.4
+        if half:
+            k = np.clip(k, -6e4, 6e4).astype(np.float16).astype(np.float32)
+            v = np.clip(v, -6e4, 6e4).astype(np.float16).astype(np.float32)
+            dk, dv = torch.from_numpy(k.astype(np.float16)).cuda(), torch.from_numpy(v.astype(np.float16)).cuda()
+        else:
+            dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+        desc = layer._seal_desc(torch.arange(n, dtype=torch.int32, device="cuda"),
+                                torch.arange(1, n + 1, dtype=torch.int32, device="cuda"),
+                                torch.as_tensor(rows, dtype=torch.int32, device="cuda"))
+        desc.tail_k, desc.tail_v, desc.tail_type = dk.data_ptr(), dv.data_ptr(), native.F16 if half else native.F32
+        assert native.lib().cf_b200_seal_pages_async(C.byref(desc), None) == 0
+        torch.cuda.synchronize()
+        assert layer.device_status() == 0
+        for s in range(n):
+            for h in range(hkv):
+                want = oracle.seal_record(k[s, h, :rows[s]], v[s, h, :rows[s]], rows[s], d, t, block, coder, 0, kcb, vcb)[0]
+                got = layer.record_bytes(s + 1, h)
+                assert got.size == want.size and np.array_equal(got, want), (seed, d, block, coder, rows, half, s, h)
