@@ -181,3 +181,100 @@ def test_random_sealer_cases_are_byte_exact(native, oracle, first):
                 want = oracle.seal_record(k[s, h, :rows[s]], v[s, h, :rows[s]], rows[s], d, t, block, coder, 0, kcb, vcb)[0]
                 got = layer.record_bytes(s + 1, h)
                 assert got.size == want.size and np.array_equal(got, want), (seed, d, block, coder, rows, half, s, h)
+
+
+@pytest.mark.parametrize("first", range(0, 60, 20))
+def test_random_reference_descriptor_cases(native, oracle, first):
+    """cf_kv_paged_attention_async on random descriptors of the reference's own fixed-width pages (its fixture encoder
+    makes them): heads, head_dim (48 and 80 too), 4 or 8 bits, ragged page sizes, no page at all, fp32 tail, several
+    query rows, causal window, per-token magnitudes. The answer must match fp64 softmax over the dequantised rows, and
+    the reference's kernel (compiled from its sources) must return the same status on the same descriptor."""
+    import ctypes as C
+    import torch
+    from compat_types import DevicePage, PagedAttentionDesc
+    from test_gpu_compat import _dev, _softmax_attention
+    ref_cpu, ref_cuda = oracle.ref_cpu(), oracle.ref_cuda()
+    if ref_cpu is None or ref_cuda is None:
+        pytest.skip("needs oracle/_ref (the reference's fixture encoder and kernels)")
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    for seed in range(first, first + 20):
+        rng = np.random.default_rng(seed)
+        hq, hkv = [(14, 2), (8, 8), (4, 2), (6, 2), (32, 8), (16, 2), (1, 1), (64, 8)][int(rng.integers(0, 8))]
+        d = [32, 64, 96, 128, 128, 48, 80][int(rng.integers(0, 7))]
+        bits = [4, 8][int(rng.integers(0, 2))]
+        full = int(rng.choice([16, 32, 64]))
+        sizes = [full if rng.random() < 0.7 else int(rng.integers(1, full + 1)) for _ in range(int(rng.integers(0, 9)))]
+        wild = rng.random() < 0.5
+        pages, keep, begin = [], [], 0
+        dense_k = np.zeros((hkv, sum(sizes), d), np.float32)
+        dense_v = np.zeros_like(dense_k)
+        for tokens in sizes:
+            for h in range(hkv):
+                n = tokens * d
+                k = rng.standard_normal(n).astype(np.float32)
+                v = rng.standard_normal(n).astype(np.float32)
+                if wild:
+                    k = (k.reshape(tokens, d) * (10.0 ** rng.uniform(-2, 0.7, (tokens, 1)))).astype(np.float32).reshape(-1)
+                    v = (v.reshape(tokens, d) * (10.0 ** rng.uniform(-4, 2, (tokens, 1)))).astype(np.float32).reshape(-1)
+                words, blocks = (n * bits + 31) // 32, (n + 63) // 64
+                kw, vw = np.zeros(words + 1, np.uint32), np.zeros(words + 1, np.uint32)
+                ko, vo = np.zeros(blocks, np.int32), np.zeros(blocks, np.int32)
+                lut = np.zeros(1 << bits, np.int32)
+                ks, vs = np.zeros(d, np.float32), np.zeros(tokens, np.float32)
+                dk, dv = np.zeros(n, np.float32), np.zeros(n, np.float32)
+                assert ref_cpu.ref_fixture_encode(ptr(k), ptr(v), C.c_uint32(begin), C.c_uint32(tokens), C.c_uint32(d),
+                                                  C.c_uint32(h), C.c_uint32(64), C.c_uint32(bits), ptr(kw), ptr(ko), ptr(vw),
+                                                  ptr(vo), ptr(lut), ptr(ks), ptr(vs), ptr(dk), ptr(dv), None) == 0
+                dense_k[h, begin:begin + tokens] = dk.reshape(tokens, d)
+                dense_v[h, begin:begin + tokens] = dv.reshape(tokens, d)
+                held = [_dev(x) for x in (kw, ko, lut, ks, vw, vo, lut, vs)]
+                keep.append(held)
+                pg = DevicePage()
+                (pg.k_words, pg.k_block_offsets, pg.k_lut, pg.k_scales, pg.v_words, pg.v_block_offsets, pg.v_lut,
+                 pg.v_scales) = [x.data_ptr() for x in held]
+                pg.token_begin, pg.token_count, pg.head_dim, pg.block_size = begin, tokens, d, 64
+                pg.k_max_code_length = pg.v_max_code_length = bits
+                pg.zero_point, pg.kv_head, pg.fixed_code_length = 1 << (bits - 1), h, bits
+                pages.append(pg)
+            begin += tokens
+        sealed = sum(sizes)
+        tail = int(rng.integers(0, 12))
+        if sealed + tail == 0:
+            tail = 1
+        nq = int(rng.integers(1, min(5, sealed + tail) + 1))
+        window = int(rng.integers(1, sealed + tail + 5)) if rng.random() < 0.5 else 0
+        tk = rng.standard_normal((max(tail, 1), hkv, d)).astype(np.float32)[:tail]
+        tv = rng.standard_normal((max(tail, 1), hkv, d)).astype(np.float32)[:tail]
+        q = (rng.standard_normal((nq, hq, d)) * 10.0 ** rng.uniform(-1, 0.5)).astype(np.float32)
+        desc = PagedAttentionDesc()
+        desc.struct_size, desc.abi_version = C.sizeof(desc), 0
+        if pages:
+            d_pages = _dev(np.frombuffer(bytes((DevicePage * len(pages))(*pages)), np.uint8).copy())
+            desc.pages = d_pages.data_ptr()
+        desc.page_count = len(pages)
+        desc.kv_head_count, desc.query_head_count, desc.gqa_group_size = hkv, hq, hq // hkv
+        if tail:
+            d_tk, d_tv = _dev(tk), _dev(tv)
+            desc.active_k, desc.active_v = d_tk.data_ptr(), d_tv.data_ptr()
+        desc.active_token_begin, desc.active_token_count = sealed, tail
+        d_q = _dev(q)
+        desc.queries, desc.query_token_begin, desc.query_count = d_q.data_ptr(), sealed + tail - nq, nq
+        desc.head_dim, desc.causal_window, desc.softmax_scale = d, window, 1.0 / np.sqrt(d)
+        k_all = np.concatenate([dense_k, tk.transpose(1, 0, 2)], axis=1)
+        v_all = np.concatenate([dense_v, tv.transpose(1, 0, 2)], axis=1)
+        pos = [sealed + tail - nq + i for i in range(nq)]
+        want = _softmax_attention(k_all, v_all, q, pos, [max(0, p + 1 - window) if window else 0 for p in pos],
+                                  1.0 / np.sqrt(d), hq // hkv)
+        answers = []
+        for lib in (native.lib(), ref_cuda):
+            out = torch.full((nq, hq, d), 3.0, dtype=torch.float32, device="cuda")
+            desc.output = out.data_ptr()
+            checked = lib.cf_kv_validate_paged_attention_desc(C.byref(desc))
+            status = lib.cf_kv_paged_attention_async(C.byref(desc), None)
+            torch.cuda.synchronize()
+            answers.append((checked, status, out.cpu().numpy()))
+        what = dict(seed=seed, heads=(hq, hkv), d=d, bits=bits, sizes=sizes, tail=tail, nq=nq, window=window, wild=wild)
+        assert answers[0][:2] == answers[1][:2], what
+        if answers[0][1] == 0:
+            got = answers[0][2]
+            assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-4 * (np.abs(want).max() + 1e-30), what
