@@ -278,3 +278,171 @@ def test_random_reference_descriptor_cases(native, oracle, first):
         if answers[0][1] == 0:
             got = answers[0][2]
             assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-4 * (np.abs(want).max() + 1e-30), what
+
+
+# ---- the multi-sequence cache ABI under random operations -------------------------------------------------------------
+# A Python model holds, per sequence, the logical position of its first row and the rows of every layer; every operation
+# the model allows must succeed, and attention must match the model's rows (sealed pages quantised as the sealer does).
+def _multisequence_run(native, oracle, seed, steps):
+    import ctypes as C
+    import torch
+    from compat_types import MsBatchItem, MultisequenceConfig, MultisequenceCounters
+    from test_gpu_ms_resolver import _expected
+    from test_gpu_mscache import _view
+    INF, END = 1 << 40, 1 << 30   # removal takes 64-bit positions, copy and shift 32-bit ones
+    rng = np.random.default_rng(seed)
+    LAYERS = int(rng.integers(1, 3)); HKV = int(rng.choice([1, 2, 4])); G = int(rng.choice([1, 2, 4])); HQ = HKV * G
+    D = int(rng.choice([128, 128, 64])); PAGE = 16
+    lib = native.lib()
+    lib.cf_multisequence_create.restype = C.c_void_p
+    lib.cf_multisequence_last_error.restype = C.c_char_p
+    lib.cf_sequence_speculation_begin.restype = C.c_uint64
+    c = C.c_void_p(lib.cf_multisequence_create(C.byref(MultisequenceConfig(LAYERS, HKV, HQ, D, PAGE, G, 0, 1))))
+    assert c.value
+    err = lambda: lib.cf_multisequence_last_error(c)
+    i64 = C.c_int64
+    seqs = {}   # id -> dict(base=int, rows=[per layer [k, v]])
+    next_id = 1
+    log = []
+    def item(seq, layer, q, out, position):
+        it = MsBatchItem()
+        it.sequence_id, it.layer = seq, layer
+        it.query = _view(q, q.shape[0])
+        it.output, it.output_type = out.data_ptr(), 3
+        es = out.element_size()
+        it.output_token_stride_bytes, it.output_head_stride_bytes, it.output_element_stride_bytes = out.stride(0) * es, out.stride(1) * es, es
+        it.query_token_begin, it.softmax_scale, it.causal_window = position, 1.0 / np.sqrt(D), 0
+        return it
+    def append(seq, tokens):
+        s = seqs[seq]
+        dtype = [torch.float16, torch.float32, torch.bfloat16][int(rng.integers(0, 3))]
+        for layer in range(LAYERS):
+            k = torch.from_numpy(rng.standard_normal((tokens, HKV, D)).astype(np.float32) * 0.8).to(dtype).cuda()
+            v = torch.from_numpy(rng.standard_normal((tokens, HKV, D)).astype(np.float32) * 0.8).to(dtype).cuda()
+            begin = s["base"] + s["rows"][layer][0].shape[0]
+            rc = lib.cf_sequence_append_async(c, i64(seq), layer, begin, C.byref(_view(k, tokens)), C.byref(_view(v, tokens)), None)
+            assert rc == 0, ("append", seq, layer, tokens, begin, err(), log[-6:])
+            s["rows"][layer] = [np.concatenate([s["rows"][layer][0], k.float().cpu().numpy()]), np.concatenate([s["rows"][layer][1], v.float().cpu().numpy()])]
+    def count(seq): return seqs[seq]["rows"][0][0].shape[0]
+    def attend(pairs):
+        qs, outs, items = [], [], (MsBatchItem * len(pairs))()
+        for i, (seq, layer) in enumerate(pairs):
+            q = torch.from_numpy(rng.standard_normal((1, HQ, D)).astype(np.float32)).cuda()
+            out = torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda")
+            items[i] = item(seq, layer, q, out, seqs[seq]["base"] + count(seq) - 1)
+            qs.append(q); outs.append(out)
+        rc = lib.cf_multisequence_attention_async(c, items, len(pairs), None)
+        assert rc == 0, ("attend", pairs, err(), log[-6:])
+        torch.cuda.synchronize()
+        for (seq, layer), q, out in zip(pairs, qs, outs):
+            k, v = seqs[seq]["rows"][layer]
+            sealed = k.shape[0] // PAGE * PAGE
+            want = _expected(oracle, k, v, sealed, 16, q.cpu().numpy(), [k.shape[0] - 1], 1.0 / np.sqrt(D), G)
+            got = out.cpu().numpy()
+            assert np.allclose(got, want, rtol=2e-3, atol=1e-3), ("attention differs", seq, layer, float(np.abs(got - want).max()), log[-8:])
+    for step in range(steps):
+        ops = ["create", "append", "append", "append", "attend", "attend", "copy", "remove_suffix", "remove", "shift", "speculate", "reclaim"]
+        op = ops[int(rng.integers(0, len(ops)))]
+        live = [s for s in seqs]
+        nonempty = [s for s in live if count(s) > 0]
+        if op == "create" or not live:
+            if len(live) >= 6: continue
+            assert lib.cf_sequence_create(c, i64(next_id)) == 0, err()
+            seqs[next_id] = dict(base=0, rows=[[np.zeros((0, HKV, D), np.float32)] * 2 for _ in range(LAYERS)])
+            log.append(("create", next_id)); next_id += 1
+        elif op == "append":
+            seq = live[int(rng.integers(0, len(live)))]
+            if count(seq) > 200: continue
+            room = PAGE - count(seq) % PAGE
+            for _ in range(int(rng.integers(1, 4))):
+                room = PAGE - count(seq) % PAGE
+                tokens = int(rng.integers(1, room + 1)) if rng.random() < 0.6 else room
+                log.append(("append", seq, tokens)); append(seq, tokens)
+        elif op == "attend" and nonempty:
+            pairs = [(nonempty[int(rng.integers(0, len(nonempty)))], int(rng.integers(0, LAYERS))) for _ in range(int(rng.integers(1, 6)))]
+            if rng.random() < 0.5: pairs = [(s, pairs[0][1]) for s, _ in pairs]   # one layer for the whole batch
+            log.append(("attend", pairs)); attend(pairs)
+        elif op == "copy" and nonempty and len(live) < 6:
+            src = nonempty[int(rng.integers(0, len(nonempty)))]
+            s = seqs[src]; n = count(src); sealed = n // PAGE * PAGE
+            kind = int(rng.integers(0, 4))
+            if kind == 0: b, e = 0, END
+            elif kind == 1: b, e = 0, s["base"] + int(rng.integers(0, sealed + 1))
+            elif kind == 2: b, e = s["base"] + int(rng.integers(0, sealed + 1)), END
+            else:
+                x, y = sorted(int(v) for v in rng.integers(0, sealed + 1, 2)); b, e = s["base"] + x, s["base"] + y
+            # model: pages wholly inside [b, e), active rows only when e reaches the end
+            first = max(0, -(-(b - s["base"]) // PAGE))                 # first page index wholly at or after b
+            last = min(sealed, (min(e, s["base"] + n) - s["base"]) // PAGE * PAGE) // PAGE   # one past the last whole page before e
+            lo_row = first * PAGE
+            hi_row = n if e >= s["base"] + n else last * PAGE
+            if hi_row <= lo_row: continue
+            rc = lib.cf_sequence_copy_async(c, i64(src), i64(next_id), C.c_uint32(b), C.c_uint32(e), None)
+            log.append(("copy", src, next_id, b, e, "rows", lo_row, hi_row, "base", s["base"], "n", n))
+            assert rc == 0, ("copy", err(), log[-6:])
+            seqs[next_id] = dict(base=s["base"] + lo_row, rows=[[a[lo_row:hi_row].copy() for a in s["rows"][layer]] for layer in range(LAYERS)])
+            next_id += 1
+        elif op == "remove_suffix" and nonempty:
+            seq = nonempty[int(rng.integers(0, len(nonempty)))]
+            s = seqs[seq]; n = count(seq); sealed = n // PAGE * PAGE
+            if sealed == 0: continue
+            cut = int(rng.integers(1, sealed // PAGE + 1)) * PAGE   # keep at least one page
+            rc = lib.cf_sequence_remove_async(c, i64(seq), i64(s["base"] + cut), i64(INF), None)
+            log.append(("remove_suffix", seq, s["base"] + cut))
+            assert rc == 0, ("remove suffix", err(), log[-6:])
+            s["rows"] = [[a[:cut] for a in s["rows"][layer]] for layer in range(LAYERS)]
+        elif op == "remove" and len(live) > 1:
+            seq = live[int(rng.integers(0, len(live)))]
+            assert lib.cf_sequence_remove_async(c, i64(seq), i64(-1), i64(-1), None) == 0, err()
+            log.append(("remove", seq)); del seqs[seq]
+        elif op == "shift" and nonempty:
+            seq = nonempty[int(rng.integers(0, len(nonempty)))]
+            s = seqs[seq]
+            delta = int(rng.integers(-s["base"], 40)) if s["base"] else int(rng.integers(0, 40))
+            rc = lib.cf_sequence_shift_async(c, i64(seq), C.c_uint32(0), C.c_uint32(END), C.c_int32(delta), None)
+            log.append(("shift", seq, delta, "base", s["base"]))
+            assert rc == 0, ("shift", err(), log[-6:])
+            s["base"] += delta
+        elif op == "speculate" and nonempty:
+            seq = nonempty[int(rng.integers(0, len(nonempty)))]
+            room = PAGE - count(seq) % PAGE
+            if room < 3: continue
+            k = int(rng.integers(1, room))   # does not fill the page
+            spec = lib.cf_sequence_speculation_begin(c, i64(seq))
+            before = [[a.copy() for a in seqs[seq]["rows"][layer]] for layer in range(LAYERS)]
+            n0 = count(seq)
+            append(seq, k)
+            if rng.random() < 0.5:
+                keep = int(rng.integers(0, k + 1))
+                rc = lib.cf_sequence_speculation_commit(c, i64(seq), C.c_uint64(spec), keep, None)
+                log.append(("spec commit", seq, k, keep))
+                assert rc == 0, ("commit", err(), log[-6:])
+                seqs[seq]["rows"] = [[a[:n0 + keep] for a in seqs[seq]["rows"][layer]] for layer in range(LAYERS)]
+            else:
+                rc = lib.cf_sequence_speculation_rollback(c, i64(seq), C.c_uint64(spec), None)
+                log.append(("spec rollback", seq, k))
+                assert rc == 0, ("rollback", err(), log[-6:])
+                seqs[seq]["rows"] = before
+        elif op == "reclaim":
+            torch.cuda.synchronize()
+            assert lib.cf_multisequence_reclaim_async(c, None) == 0 and lib.cf_multisequence_audit(c) == 0, (err(), log[-6:])
+            log.append(("reclaim",))
+    k = MultisequenceCounters()
+    lib.cf_multisequence_get_counters(c, C.byref(k))
+    assert k.invariant_failures == 0, log[-6:]
+    for seq in list(seqs):
+        assert lib.cf_sequence_remove_async(c, i64(seq), i64(-1), i64(-1), None) == 0
+    torch.cuda.synchronize()
+    assert lib.cf_multisequence_reclaim_async(c, None) == 0 and lib.cf_multisequence_audit(c) == 0
+    lib.cf_multisequence_get_counters(c, C.byref(k))
+    assert k.active_sequences == 0 and k.pages_pending_reclamation == 0 and k.invariant_failures == 0, (k.active_sequences, k.pages_pending_reclamation)
+    lib.cf_multisequence_destroy(c, None)
+    return len(log)
+
+
+@pytest.mark.parametrize("first", range(0, 24, 8))
+def test_random_operations_on_the_multisequence_cache(native, oracle, first):
+    """cf_sequence_create / append (fp16, bf16, fp32 rows) / copy over ranges / suffix and whole removal / shift /
+    speculation commit and rollback / reclaim with audit / batched attention, in random order on up to six sequences."""
+    for seed in range(3000 + first, 3000 + first + 8):
+        assert _multisequence_run(native, oracle, seed, 100) > 0
