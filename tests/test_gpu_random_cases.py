@@ -324,22 +324,27 @@ def _multisequence_run(native, oracle, seed, steps):
             assert rc == 0, ("append", seq, layer, tokens, begin, err(), log[-6:])
             s["rows"][layer] = [np.concatenate([s["rows"][layer][0], k.float().cpu().numpy()]), np.concatenate([s["rows"][layer][1], v.float().cpu().numpy()])]
     def count(seq): return seqs[seq]["rows"][0][0].shape[0]
-    def attend(pairs):
-        qs, outs, items = [], [], (MsBatchItem * len(pairs))()
+    pending = []   # attention batches launched and not yet checked: (pairs, queries, outputs, rows captured at launch)
+    def attend(pairs, defer=False):
+        qs, outs, items, rows = [], [], (MsBatchItem * len(pairs))(), []
         for i, (seq, layer) in enumerate(pairs):
             q = torch.from_numpy(rng.standard_normal((1, HQ, D)).astype(np.float32)).cuda()
             out = torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda")
             items[i] = item(seq, layer, q, out, seqs[seq]["base"] + count(seq) - 1)
-            qs.append(q); outs.append(out)
+            qs.append(q); outs.append(out); rows.append(tuple(seqs[seq]["rows"][layer]))
         rc = lib.cf_multisequence_attention_async(c, items, len(pairs), None)
         assert rc == 0, ("attend", pairs, err(), log[-6:])
+        pending.append((pairs, qs, outs, rows, list(log[-8:])))
+        if not defer: settle()
+    def settle():
         torch.cuda.synchronize()
-        for (seq, layer), q, out in zip(pairs, qs, outs):
-            k, v = seqs[seq]["rows"][layer]
-            sealed = k.shape[0] // PAGE * PAGE
-            want = _expected(oracle, k, v, sealed, 16, q.cpu().numpy(), [k.shape[0] - 1], 1.0 / np.sqrt(D), G)
-            got = out.cpu().numpy()
-            assert np.allclose(got, want, rtol=2e-3, atol=1e-3), ("attention differs", seq, layer, float(np.abs(got - want).max()), log[-8:])
+        for pairs, qs, outs, rows, at in pending:
+            for (seq, layer), q, out, (k, v) in zip(pairs, qs, outs, rows):
+                sealed = k.shape[0] // PAGE * PAGE
+                want = _expected(oracle, k, v, sealed, 16, q.cpu().numpy(), [k.shape[0] - 1], 1.0 / np.sqrt(D), G)
+                got = out.cpu().numpy()
+                assert np.allclose(got, want, rtol=2e-3, atol=1e-3), ("attention differs", seq, layer, float(np.abs(got - want).max()), at, log[-8:])
+        pending.clear()
     for step in range(steps):
         ops = ["create", "append", "append", "append", "attend", "attend", "copy", "remove_suffix", "remove", "shift", "speculate", "reclaim"]
         op = ops[int(rng.integers(0, len(ops)))]
@@ -361,7 +366,8 @@ def _multisequence_run(native, oracle, seed, steps):
         elif op == "attend" and nonempty:
             pairs = [(nonempty[int(rng.integers(0, len(nonempty)))], int(rng.integers(0, LAYERS))) for _ in range(int(rng.integers(1, 6)))]
             if rng.random() < 0.5: pairs = [(s, pairs[0][1]) for s, _ in pairs]   # one layer for the whole batch
-            log.append(("attend", pairs)); attend(pairs)
+            defer = rng.random() < 0.6
+            log.append(("attend", pairs, "deferred" if defer else "")); attend(pairs, defer)
         elif op == "copy" and nonempty and len(live) < 6:
             src = nonempty[int(rng.integers(0, len(nonempty)))]
             s = seqs[src]; n = count(src); sealed = n // PAGE * PAGE
@@ -424,9 +430,11 @@ def _multisequence_run(native, oracle, seed, steps):
                 assert rc == 0, ("rollback", err(), log[-6:])
                 seqs[seq]["rows"] = before
         elif op == "reclaim":
-            torch.cuda.synchronize()
+            if rng.random() < 0.5: torch.cuda.synchronize()
             assert lib.cf_multisequence_reclaim_async(c, None) == 0 and lib.cf_multisequence_audit(c) == 0, (err(), log[-6:])
             log.append(("reclaim",))
+        if len(pending) >= 3 or (pending and rng.random() < 0.3): settle()
+    settle()
     k = MultisequenceCounters()
     lib.cf_multisequence_get_counters(c, C.byref(k))
     assert k.invariant_failures == 0, log[-6:]
@@ -443,6 +451,8 @@ def _multisequence_run(native, oracle, seed, steps):
 @pytest.mark.parametrize("first", range(0, 24, 8))
 def test_random_operations_on_the_multisequence_cache(native, oracle, first):
     """cf_sequence_create / append (fp16, bf16, fp32 rows) / copy over ranges / suffix and whole removal / shift /
-    speculation commit and rollback / reclaim with audit / batched attention, in random order on up to six sequences."""
+    speculation commit and rollback / reclaim with audit / batched attention, in random order on up to six sequences.
+    More than half of the attention batches are checked only after the operations that follow them (removals, reclaim,
+    new pages that may take freed arena slots), against the rows the sequences had when the batch was launched."""
     for seed in range(3000 + first, 3000 + first + 8):
         assert _multisequence_run(native, oracle, seed, 100) > 0
