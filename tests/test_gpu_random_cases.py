@@ -456,3 +456,103 @@ def test_random_operations_on_the_multisequence_cache(native, oracle, first):
     new pages that may take freed arena slots), against the rows the sequences had when the batch was launched."""
     for seed in range(3000 + first, 3000 + first + 8):
         assert _multisequence_run(native, oracle, seed, 100) > 0
+
+
+# ---- the llama.cpp KV adapter ABI: pages in the reference's own format -------------------------------------------------
+def _adapter_rows(rng, shape):
+    """Rows [kv head][token][channel]: plain normal, one magnitude, a magnitude per token, per channel, zero channels and
+    zero tokens, or many rounding ties."""
+    kind = int(rng.integers(0, 6))
+    x = rng.standard_normal(shape)
+    if kind == 1: x *= 10.0 ** rng.uniform(-6, 4)
+    elif kind == 2: x *= 10.0 ** rng.uniform(-5, 3, (shape[0], shape[1], 1))      # per token
+    elif kind == 3: x *= 10.0 ** rng.uniform(-5, 3, (shape[0], 1, shape[2]))      # per channel
+    elif kind == 4: x[:, :, rng.integers(0, shape[2], 3)] = 0.0; x[:, rng.integers(0, shape[1], 2), :] = 0.0
+    elif kind == 5: x = np.rint(x * 3) * 0.5   # many ties
+    return x.astype(np.float32)
+
+
+def _adapter_case(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import DevicePage, LlamaKvOptions, LlamaKvStats
+    from test_gpu_compat import _dev, _read_device, _softmax_attention
+    rng = np.random.default_rng(seed)
+    ref = oracle.ref_cpu(); lib = native.lib()
+    lib.cf_llama_kv_create.restype = C.c_void_p; lib.cf_llama_kv_last_error.restype = C.c_char_p
+    hq, hkv = [(14, 2), (8, 8), (4, 2), (32, 8), (16, 2), (1, 1)][int(rng.integers(0, 6))]
+    head_dim = int(rng.choice([32, 64, 96, 128, 128, 48, 80, 16]))
+    page = int(rng.choice([16, 32, 64])); bits = int(rng.choice([4, 8])); layers = int(rng.integers(1, 3))
+    tokens = int(rng.integers(1, 4 * page + 10))
+    o = LlamaKvOptions()
+    o.struct_size, o.backend = C.sizeof(o), 1
+    o.layer_count, o.kv_head_count, o.query_head_count, o.head_dim, o.page_size, o.gqa_group_size = layers, hkv, hq, head_dim, page, hq // hkv
+    o.kv_bits = bits if bits == 8 else int(rng.choice([0, 4, 5]))
+    a = C.c_void_p(lib.cf_llama_kv_create(C.byref(o)))
+    what = dict(seed=seed, heads=(hq, hkv), d=head_dim, page=page, bits=bits, layers=layers, tokens=tokens)
+    if not a.value: return ("create refused",), what
+    k = np.stack([_adapter_rows(rng, (hkv, tokens, head_dim)) for _ in range(layers)]); v = np.stack([_adapter_rows(rng, (hkv, tokens, head_dim)) for _ in range(layers)])
+    p = lambda x: np.ascontiguousarray(x).ctypes.data_as(C.c_void_p)
+    cuts = sorted(set([0, tokens] + [int(x) for x in rng.integers(0, tokens + 1, int(rng.integers(0, 4)))]))
+    for layer in range(layers):
+        for b, e in zip(cuts[:-1], cuts[1:]):
+            for h in range(hkv):
+                rc = lib.cf_llama_kv_append(a, layer, h, b, p(k[layer, h, b:e]), p(v[layer, h, b:e]), e - b, None)
+                if rc != 0: return ("append", rc, lib.cf_llama_kv_last_error(a)), what
+    full = tokens // page
+    st = LlamaKvStats()
+    assert lib.cf_llama_kv_get_stats(a, C.byref(st)) == 0
+    if st.sealed_pages != layers * hkv * full or st.active_tokens != layers * hkv * (tokens - full * page):
+        return ("stats", st.sealed_pages, st.active_tokens), what
+    deq_k, deq_v = k.copy(), v.copy()
+    n = page * head_dim; words, nb = (n * bits + 31) // 32, (n + 63) // 64
+    for layer in range(layers):
+        for index in range(hkv * full):
+            pg = DevicePage()
+            if lib.cf_b200_llama_kv_reference_page(a, layer, index, C.byref(pg)) != 0: return ("page lookup", layer, index), what
+            h, begin = pg.kv_head, pg.token_begin
+            kw, vw = np.zeros(words + 1, np.uint32), np.zeros(words + 1, np.uint32)
+            ko, vo = np.zeros(nb, np.int32), np.zeros(nb, np.int32)
+            lut = np.zeros(1 << bits, np.int32)
+            ks, vs = np.zeros(head_dim, np.float32), np.zeros(page, np.float32)
+            dk, dv = np.zeros(n, np.float32), np.zeros(n, np.float32)
+            rk, rv = k[layer, h, begin:begin + page].ravel(), v[layer, h, begin:begin + page].ravel()
+            assert ref.ref_fixture_encode(p(rk), p(rv), C.c_uint32(begin), C.c_uint32(page), C.c_uint32(head_dim), C.c_uint32(h),
+                                          C.c_uint32(64), C.c_uint32(bits), p(kw), p(ko), p(vw), p(vo), p(lut), p(ks), p(vs), p(dk), p(dv), None) == 0
+            checks = [("k words", _read_device(pg.k_words, words, np.uint32), kw[:words]), ("v words", _read_device(pg.v_words, words, np.uint32), vw[:words]),
+                      ("k scales", _read_device(pg.k_scales, head_dim, np.float32).view(np.uint32), ks.view(np.uint32)),
+                      ("v scales", _read_device(pg.v_scales, page, np.float32).view(np.uint32), vs.view(np.uint32)),
+                      ("k offsets", _read_device(pg.k_block_offsets, nb, np.int32), ko)]
+            for name, got, want in checks:
+                if not np.array_equal(got, want):
+                    i = int(np.argmax(got != want)); return (name, layer, index, i, int(got[i]), int(want[i])), what
+            deq_k[layer, h, begin:begin + page] = dk.reshape(page, head_dim); deq_v[layer, h, begin:begin + page] = dv.reshape(page, head_dim)
+    nq = int(rng.integers(1, min(4, tokens) + 1)); window = int(rng.integers(1, tokens + 4)) if rng.random() < 0.5 else 0
+    q = rng.standard_normal((nq, hq, head_dim)).astype(np.float32)
+    pos = [tokens - nq + i for i in range(nq)]
+    d_q = _dev(q)
+    for layer in range(layers):
+        out = torch.zeros((nq, hq, head_dim), dtype=torch.float32, device="cuda")
+        rc = lib.cf_llama_kv_attention(a, layer, C.c_void_p(d_q.data_ptr()), C.c_void_p(out.data_ptr()), nq, hq, hq // hkv,
+                                       tokens - nq, C.c_float(1.0 / np.sqrt(head_dim)), window, None)
+        if rc != 0: return ("attention rc", rc, lib.cf_llama_kv_last_error(a)), what
+        torch.cuda.synchronize()
+        want = _softmax_attention(deq_k[layer], deq_v[layer], q, pos, [max(0, x + 1 - window) if window else 0 for x in pos], 1.0 / np.sqrt(head_dim), hq // hkv)
+        got = out.cpu().numpy()
+        e = np.abs(got - want).max() / (np.abs(want).max() + 1e-30)
+        if not np.isfinite(got).all() or e > 2e-4: return ("attention", layer, float(e)), what
+    lib.cf_llama_kv_destroy(a)
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 60, 20))
+def test_random_adapter_cases_store_the_references_own_pages(native, oracle, first, monkeypatch):
+    """cf_llama_kv_* with the default page format on random shapes (heads, head_dim 16..128, page 16 / 32 / 64, int4 or
+    int8, append chunking): every sealed page equals the reference encoder's (oracle/_ref) bit for bit — words, fp32
+    scales, block offsets — and attention matches fp64 softmax over the reference's dequantised rows."""
+    if oracle.ref_cpu() is None:
+        pytest.skip("the reference's encoder was not built (oracle/_ref)")
+    monkeypatch.delenv("CHROMOFOLD_B200_CODER", raising=False)
+    for seed in range(4000 + first, 4000 + first + 20):
+        bad, what = _adapter_case(native, oracle, seed)
+        assert bad is None, (bad, what)
