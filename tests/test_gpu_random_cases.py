@@ -556,3 +556,88 @@ def test_random_adapter_cases_store_the_references_own_pages(native, oracle, fir
     for seed in range(4000 + first, 4000 + first + 20):
         bad, what = _adapter_case(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the flat-stream entry points of the reference's first ABI ----------------------------------------------------------
+def _flat_rans_case(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from helpers import hist_of, laplace_codes
+    from test_gpu_compat import _dev, _softmax_attention
+    rng = np.random.default_rng(seed)
+    block = int(rng.choice([64, 64, 64, 32, 100, 128, 256, 1024, 1, 7]))
+    n = int(rng.choice([1, 63, 64, 65, 4096, 4097, 64 * 64, 64 * 64 + 1, 64 * 65, int(rng.integers(1, 300000))]))
+    b = float(10.0 ** rng.uniform(-1.5, 1.8))
+    sym = (laplace_codes(rng, n, b).astype(np.int16) + 128).astype(np.uint8)
+    if rng.random() < 0.2: sym[:] = sym[0]
+    hist = hist_of(sym) if rng.random() < 0.7 else hist_of((laplace_codes(rng, 4096, 20.0).astype(np.int16) + 128).astype(np.uint8)) + 1
+    cb = oracle.codebook_from_hist(hist)
+    data, off, st = oracle.rans_encode(sym, block, cb)
+    args = [_dev(np.concatenate([data, np.zeros(8, np.uint8)])), _dev(off), _dev(st), _dev(cb.np("slot2sym")), _dev(cb.np("freq")), _dev(cb.np("cum"))]
+    outs = []
+    for lib in (native.lib(), oracle.ref_cuda()):
+        out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+        rc = lib.cf_rans_decode_async(*[C.c_void_p(t.data_ptr()) for t in args], C.c_int(block), C.c_int(n), C.c_void_p(out.data_ptr()), None)
+        torch.cuda.synchronize()
+        outs.append((rc, out.cpu().numpy()))
+    what = dict(kind="rans", seed=seed, block=block, n=n, b=b)
+    if outs[0][0] != outs[1][0]: return ("rc", outs[0][0], outs[1][0]), what
+    if outs[0][0] == 0 and not np.array_equal(outs[0][1], sym.astype(np.int32)): return ("symbols", int(np.argmax(outs[0][1] != sym)),), what
+    if outs[0][0] == 0 and not np.array_equal(outs[0][1], outs[1][1]): return ("vs reference",), what
+    return None, what
+
+
+def _flat_fused_case(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from helpers import hist_of, laplace_codes
+    from test_gpu_compat import _dev, _softmax_attention
+    rng = np.random.default_rng(seed)
+    seq = int(rng.integers(1, 400)); dim = int(rng.choice([16, 32, 40, 64, 80, 97, 128])); nq = int(rng.integers(1, seq + 1))
+    nq = min(nq, 64); window = int(rng.integers(1, 513)); block = int(rng.choice([16, 32, 64, 100, 128]))
+    ksym = (laplace_codes(rng, seq * dim, float(rng.uniform(1, 30))).astype(np.int16) + 128).astype(np.uint8)
+    vsym = (laplace_codes(rng, seq * dim, float(rng.uniform(1, 30))).astype(np.int16) + 128).astype(np.uint8)
+    kcb, vcb = oracle.codebook_from_hist(hist_of(ksym)), oracle.codebook_from_hist(hist_of(vsym))
+    kw, kb = oracle.huff_encode(ksym, block, kcb); vw, vb = oracle.huff_encode(vsym, block, vcb)
+    kscale = (rng.uniform(0.005, 0.02, dim) * 10.0 ** rng.uniform(-1, 1)).astype(np.float32)
+    vscale = (rng.uniform(0.005, 0.02, seq) * 10.0 ** rng.uniform(-3, 2, seq)).astype(np.float32)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    sscale = 1.0 / np.sqrt(dim)
+    kd = (ksym.astype(np.float32).reshape(seq, dim) - 128.0) * kscale[None, :]
+    vd = (vsym.astype(np.float32).reshape(seq, dim) - 128.0) * vscale[:, None]
+    positions = np.arange(nq); firsts = np.maximum(0, positions - window + 1)
+    expect = _softmax_attention(kd[None], vd[None], q[:, None, :], positions, firsts, sscale, 1)[:, 0]
+    pad = np.zeros(2, np.uint32)
+    dev = [_dev(np.concatenate([kw, pad])), _dev(kb), _dev(kcb.np("lut")), _dev(np.concatenate([vw, pad])), _dev(vb), _dev(vcb.np("lut")), _dev(kscale), _dev(vscale), _dev(q)]
+    p = [C.c_void_p(t.data_ptr()) for t in dev]
+    res = []
+    what = dict(kind="fused", seed=seed, seq=seq, dim=dim, nq=nq, window=window, block=block)
+    for lib in (native.lib(), oracle.ref_cuda()):
+        fused = torch.zeros((nq, dim), dtype=torch.float32, device="cuda"); dense = torch.zeros_like(fused)
+        kdd = torch.zeros((seq, dim), dtype=torch.float32, device="cuda"); vdd = torch.zeros_like(kdd)
+        tail = (C.c_int(seq), C.c_int(dim), C.c_int(nq), C.c_int(window), C.c_int(block), C.c_int(128), C.c_float(sscale), None)
+        head = (p[0], p[1], p[2], C.c_int(12), p[3], p[4], p[5], C.c_int(12), p[6], p[7], p[8])
+        rc1 = lib.cf_kv_attn_fused_async(*head, C.c_void_p(fused.data_ptr()), *tail)
+        rc2 = lib.cf_kv_attn_dense_async(*head, C.c_void_p(kdd.data_ptr()), C.c_void_p(vdd.data_ptr()), C.c_void_p(dense.data_ptr()), *tail)
+        torch.cuda.synchronize()
+        res.append((rc1, rc2, fused.cpu().numpy(), dense.cpu().numpy(), kdd.cpu().numpy(), vdd.cpu().numpy()))
+    if res[0][:2] != res[1][:2]: return ("rc", res[0][:2], res[1][:2]), what
+    if res[0][0] != 0: return None, what
+    if not np.array_equal(res[0][2], res[0][3]): return ("fused != dense",), what
+    if not (np.array_equal(res[0][4], kd) and np.array_equal(res[0][5], vd)): return ("dequantised rows",), what
+    scale = np.abs(expect).max() + 1e-30
+    if np.abs(res[0][2] - expect).max() / scale > 2e-4: return ("vs fp64", float(np.abs(res[0][2] - expect).max() / scale), "ref", float(np.abs(res[1][2] - expect).max() / scale)), what
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_random_flat_stream_cases(native, oracle, first):
+    """cf_rans_decode_async and cf_kv_attn_fused_async / cf_kv_attn_dense_async on random sizes, block sizes (1 and 7
+    included), codebooks that were not made from the stream, constant streams and per-token V scales over five orders:
+    symbols exact, fused == dense bit for bit, the same status and the same symbols as the reference's kernels."""
+    if oracle.ref_cuda() is None:
+        pytest.skip("needs the reference's kernels (oracle/_ref)")
+    for seed in range(5000 + first, 5000 + first + 20):
+        for case in (_flat_rans_case, _flat_fused_case):
+            bad, what = case(native, oracle, seed)
+            assert bad is None, (bad, what)
