@@ -641,3 +641,56 @@ def test_random_flat_stream_cases(native, oracle, first):
         for case in (_flat_rans_case, _flat_fused_case):
             bad, what = case(native, oracle, seed)
             assert bad is None, (bad, what)
+
+
+# ---- the shared-prefix kernel at larger batch sizes ---------------------------------------------------------------------
+def _prefix_case(native, seed):
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    rng = np.random.default_rng(seed)
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    n = int(rng.choice([1, 2, 7, 31, 32, 33, 64, 100, 129, 257, int(rng.integers(1, 300))]))
+    hq, hkv = [(32, 8), (16, 8), (8, 8), (64, 8), (8, 2), (4, 1), (16, 1), (2, 2)][int(rng.integers(0, 8))]
+    group = hq // hkv
+    coder = ["rans4", "huffman4", "rans", "huffman", "fixed8"][int(rng.integers(0, 5))]
+    pp = int(rng.choice([1, 2, 7, 8, 9, 16, 17, 40, int(rng.integers(1, 60))]))
+    private = int(rng.integers(0, 40))
+    layer, info = build_sealed_layer(np.array([16 * pp] + [0] * (n - 1)), query_heads=hq, kv_heads=hkv, coder=coder, seed=seed,
+                                     extra_pages_per_sequence=private // 16 + 3, reserve_pages=n * (private // 16 + 2) + 8)
+    for s in range(1, n): layer.copy_sequence(0, s)
+    slots = list(range(n))
+    ragged = rng.random() < 0.5
+    for t in range(private):
+        sl = [s for s in slots if (not ragged) or (s * 7 + 3) % (private + 1) > t] or [0]
+        k = (torch.randn((len(sl), hkv, 128), generator=g, device="cuda") * 0.7).half()
+        v = (torch.randn((len(sl), hkv, 128), generator=g, device="cuda") * 0.7).half()
+        layer.append(sl, k, v); layer.seal_full_pages()
+    q = (torch.randn((n, hq, 128), generator=g, device="cuda")).half()
+    kw = {}
+    if rng.random() < 0.4:
+        span = int(rng.integers(1, hkv + 1)); kw["kv_head_begin"], kw["kv_head_span"] = int(rng.integers(0, hkv - span + 1)), span
+    qq = q.float() if rng.random() < 0.3 else q
+    claim = pp if rng.random() < 0.7 else int(rng.integers(1, pp + 1))
+    a = torch.full((n, hq, 128), 7.0, dtype=torch.float32, device="cuda"); b = torch.full((n, hq, 128), 7.0, dtype=torch.float32, device="cuda")
+    before = native.lib().cf_b200_shared_prefix_launches()
+    layer.attention(qq, out=a, kernel=native.KERNEL_LANES, shared_prefix_pages=claim, **kw)
+    used = native.lib().cf_b200_shared_prefix_launches() - before
+    st = layer.device_status()
+    layer.attention(qq, out=b, kernel=native.KERNEL_LANES, **kw)
+    A, B = a.cpu().numpy().astype(np.float64), b.cpu().numpy().astype(np.float64)
+    err = np.abs(A - B).max() / (np.abs(B).max() + 1e-30)
+    what = dict(seed=seed, n=n, heads=(hq, hkv), coder=coder, prefix_pages=pp, claim=claim, private=private, ragged=ragged, kw=kw, used=int(used))
+    if st != 0 or not np.isfinite(A).all() or err > 2e-5: return (st, float(err)), what
+    if 128 % group == 0 and used != 1: return ("prefix kernel not used",), what
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_random_shared_prefix_cases(native, first):
+    """The shared-prefix kernel on batches of 1 to 300 sequences (one to several row tiles, the last one partly filled),
+    1 to 60 shared pages (whole and ragged rounds), heads from 2 x 2 to 64 x 8, private tails of equal or ragged
+    length, kv-head shards, fp32 queries, partial claims: equal to the per-sequence path to 2e-5 of the output's
+    scale, and the kernel did run."""
+    for seed in range(6000 + first, 6000 + first + 20):
+        bad, what = _prefix_case(native, seed)
+        assert bad is None, (bad, what)
