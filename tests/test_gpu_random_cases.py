@@ -694,3 +694,58 @@ def test_random_shared_prefix_cases(native, first):
     for seed in range(6000 + first, 6000 + first + 20):
         bad, what = _prefix_case(native, seed)
         assert bad is None, (bad, what)
+
+
+# ---- longer contexts, larger query groups ---------------------------------------------------------------------------
+def _long_case(native, seed):
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    rng = np.random.default_rng(seed)
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    n = int(rng.integers(1, 9))
+    D, block = [(128, 64), (128, 64), (128, 128), (128, 256), (64, 64), (96, 64), (32, 64), (64, 128), (96, 128)][int(rng.integers(0, 9))]
+    hq, hkv = [(32, 8), (64, 8), (8, 8), (128, 8), (16, 2), (12, 4), (40, 8)][int(rng.integers(0, 7))]
+    coder = ["rans4", "huffman4", "rans", "huffman", "fixed8"][int(rng.integers(0, 5))]
+    ctx = (rng.integers(0, 400, n) * 16)
+    if rng.random() < 0.3: ctx[int(rng.integers(0, n))] = 0
+    dist = ("laplace", float(rng.uniform(2, 30))) if rng.random() < 0.7 else ("geometric", float(rng.uniform(0.05, 0.7)))
+    layer, info = build_sealed_layer(ctx, query_heads=hq, kv_heads=hkv, head_dim=D, block_size=block, coder=coder, dist=dist, seed=seed,
+                                     extra_pages_per_sequence=3, reserve_pages=2 * n)
+    if ctx.sum() == 0: layer.set_codebooks(np.ones(256, np.uint64), np.ones(256, np.uint64))
+    tail = int(rng.integers(0, 16))
+    for t in range(tail):
+        sl = [s for s in range(n) if (s + t) % 3 != 0 or t < 2]
+        k = (torch.randn((len(sl), hkv, D), generator=g, device="cuda") * 0.3).half(); v = (torch.randn((len(sl), hkv, D), generator=g, device="cuda") * 0.3).half()
+        layer.append(sl, k, v)
+    q = (torch.randn((n, hq, D), generator=g, device="cuda") * float(10.0 ** rng.uniform(-0.5, 0.5))).half()
+    kw = {}
+    if rng.random() < 0.4: kw["min_pages_per_unit"] = int(rng.choice([1, 2, 3, 5, 8, 16, 33, 64, 200]))
+    if rng.random() < 0.3: kw["causal_window"] = int(rng.integers(1, 3000))
+    if rng.random() < 0.3:
+        span = int(rng.integers(1, hkv + 1)); kw["kv_head_begin"], kw["kv_head_span"] = int(rng.integers(0, hkv - span + 1)), span
+    qq = q.float() if rng.random() < 0.3 else q
+    out = torch.full((n, hq, D), 7.0, dtype=torch.float32, device="cuda")
+    layer.attention(qq, out=out, kernel=native.KERNEL_LANES, **kw)
+    st = layer.device_status()
+    got = out.cpu().numpy()
+    want = oracle_from_layer(layer, q.cpu().numpy(), causal_window=kw.get("causal_window", 0))
+    group = hq // hkv
+    lo = kw.get("kv_head_begin", 0) * group; hi = lo + kw.get("kv_head_span", hkv) * group
+    a, e = got[:, lo:hi].astype(np.float64), want[:, lo:hi].astype(np.float64)
+    err = np.abs(a - e).max() / (np.abs(e).max() + 1e-30)
+    what = dict(seed=seed, n=n, D=D, block=block, heads=(hq, hkv), coder=coder, ctx=ctx.tolist(), tail=tail, kw=kw, dist=dist)
+    untouched = np.all(got[:, :lo] == 7.0) and np.all(got[:, hi:] == 7.0)
+    if st != 0 or not np.isfinite(a).all() or err > 1e-4 or not untouched: return (st, float(err), bool(untouched)), what
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_random_long_context_cases(native, oracle, first):
+    """Contexts of up to 6400 tokens (many chunks per sequence), groups of 1 to 16 query heads per kv head, every fast
+    geometry and coder, Laplace and geometric codes, ragged tails, units from 1 page to whole sequences, windows, kv-head
+    shards, fp32 queries, against the oracle. The bar is 1e-4 of the output's scale: the fp32 accumulation of the
+    tensor cores drifts by about 1e-7 per page of a unit, which shows when a caller asks for units of hundreds of pages
+    (2e-5 at 300); the library's own choice keeps units below 36 pages."""
+    for seed in range(7000 + first, 7000 + first + 20):
+        bad, what = _long_case(native, seed)
+        assert bad is None, (bad, what)
