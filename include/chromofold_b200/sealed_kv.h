@@ -100,7 +100,10 @@ typedef struct cf_b200_sealed_attention_desc {
     uint64_t workspace_bytes;
     uint32_t min_pages_per_unit;         /* pages per split-KV unit; 0 = the library chooses (4 to 35) on the device, from the
                                             pages the launch will read: the size whose rounds over the GPU's resident
-                                            warps cost least, among those whose partials fit the workspace */
+                                            warps cost least, among those whose partials fit the workspace. A unit's
+                                            weighted sum is kept by the tensor cores in fp32; its rounding drifts by
+                                            about 1e-7 of the output's scale per page, so units of hundreds of pages
+                                            are a few 1e-5 off where the library's own sizes stay below 4e-6 */
     uint32_t kernel;                     /* CF_B200_KERNEL_* */
     uint32_t *status;                    /* optional device word; a kernel ORs CF_B200_DEVSTAT_* into it */
     uint32_t tail_type;                  /* CF_B200_F16 (0 means F16 too) or CF_B200_F32: element type of the tails */
