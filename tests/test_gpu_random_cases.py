@@ -749,3 +749,60 @@ def test_random_long_context_cases(native, oracle, first):
     for seed in range(7000 + first, 7000 + first + 20):
         bad, what = _long_case(native, seed)
         assert bad is None, (bad, what)
+
+
+# ---- transfer images ----------------------------------------------------------------------------------------------
+def _transfer_case(native, seed):
+    import torch
+    from chromofold_b200.workloads import build_sealed_layer
+    rng = np.random.default_rng(seed)
+    D, block = [(128, 64), (128, 128), (128, 256), (64, 64), (96, 64), (32, 64)][int(rng.integers(0, 6))]
+    hq, hkv = [(32, 8), (8, 2), (4, 4), (16, 1)][int(rng.integers(0, 4))]
+    coder = ["rans4", "huffman4", "rans", "huffman", "fixed8"][int(rng.integers(0, 5))]
+    pages = int(rng.integers(1, 80)); other = int(rng.integers(0, 5)) * 16
+    src, _ = build_sealed_layer(np.array([16 * pages, other]), query_heads=hq, kv_heads=hkv, head_dim=D, block_size=block, coder=coder, seed=seed,
+                                dist=("laplace", float(rng.uniform(2, 40))))
+    image = src.export_pages(0)
+    what = dict(seed=seed, D=D, block=block, heads=(hq, hkv), coder=coder, pages=pages)
+    if src.device_status() != 0: return ("export status", src.device_status()), what
+    def fresh(seed2):
+        pre = int(rng.integers(0, 4)) * 16
+        dst, _ = build_sealed_layer(np.array([0, pre]), query_heads=hq, kv_heads=hkv, head_dim=D, block_size=block, coder=coder, seed=seed2,
+                                    extra_pages_per_sequence=pages + 4, reserve_pages=pages + 8)
+        dst.k_tables.copy_(src.k_tables); dst.v_tables.copy_(src.v_tables); dst.host_tables = src.host_tables; dst.codebook_id = src.codebook_id
+        dst._codebooks_set = True
+        return dst
+    dst = fresh(seed + 1)
+    if dst.import_pages(0, image) != pages or dst.device_status() != 0: return ("import", dst.device_status()), what
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    q = torch.randn((1, hq, D), generator=g, device="cuda").half()
+    a = src.attention(q, slots=[0]).cpu().numpy(); b = dst.attention(q, slots=[0]).cpu().numpy()
+    if not np.array_equal(a, b): return ("attention differs", float(np.abs(a - b).max())), what
+    for h in range(hkv):
+        for pg in (0, pages - 1):
+            if not np.array_equal(src.record_bytes(int(src.h_page_table[0, pg]), h), dst.record_bytes(int(dst.h_page_table[0, pg]), h)): return ("record differs", pg, h), what
+    # tampering: flip one to three bits somewhere in the payload
+    header = native.TransferHeader.from_buffer_copy(image[:64])
+    man_bytes = 16 * pages * hkv
+    man = np.frombuffer(image[64:64 + man_bytes], dtype=[("off", "<u4"), ("len", "<u4"), ("sum", "<u8")])
+    for trial in range(3):
+        bad = bytearray(image)
+        e = man[int(rng.integers(0, man.size))]
+        for _ in range(int(rng.integers(1, 4))):
+            at = 64 + man_bytes + 16 * int(e["off"]) + int(rng.integers(0, 16 * int(e["len"])))
+            bad[at] ^= 1 << int(rng.integers(0, 8))
+        if bytes(bad) == image: continue
+        d2 = fresh(seed + 2 + trial)
+        d2.import_pages(0, bytes(bad))
+        if not (d2.device_status() & native.DEVSTAT_CHECKSUM): return ("tampering not caught", trial), what
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 30, 15))
+def test_random_transfer_images(native, first):
+    """Transfer images of 1 to 79 pages in every fast geometry and coder: the importing store holds the same record bytes
+    and answers attention bit for bit like the exporting one; one to three flipped payload bits are always caught by the
+    per-record checksum."""
+    for seed in range(8000 + first, 8000 + first + 15):
+        bad, what = _transfer_case(native, seed)
+        assert bad is None, (bad, what)
