@@ -470,8 +470,8 @@ int guarded(cf_llama_kv_adapter *adapter, Operation &&operation) {  // chromofol
 }
 
 uint32_t choose_tile_tokens(uint32_t page_size, uint32_t head_dim) {
-    // 16-token records at head_dim 128 are the geometry of the lane-per-block attention kernel
-    if (head_dim == 128 && page_size % 16 == 0) return 16;
+    // 16-token records at head_dim 128, 96, 64 and 32 are the geometries of the lane-per-block attention kernels
+    if ((head_dim == 128 || head_dim == 96 || head_dim == 64 || head_dim == 32) && page_size % 16 == 0) return 16;
     const uint32_t limit = CF_B200_MAX_STREAM_SYMBOLS / head_dim;
     for (uint32_t t = std::min(page_size, limit); t >= 1; --t)
         if (page_size % t == 0) return t;

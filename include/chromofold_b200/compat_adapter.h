@@ -18,8 +18,8 @@
  * reference's numbers. With CHROMOFOLD_B200_CODER = rans | huffman | fixed8 | rans4 | huffman4 in the environment the pages
  * are instead quantised to int8 with one fp16 scale per stream and entropy coded (format v1, sealed_page_format.h):
  * physically a page of page_size tokens is then page_size / T records of T tokens with T * head_dim <= 4096 (T = 16 at
- * head_dim 128, the record geometry of the lane-per-block attention kernel, which takes the fp32 queries of this ABI as
- * binary16 + residue rows). Statistics are reported in the reference's units in both modes. */
+ * head_dim 128, 96, 64 and 32 with pages of a multiple of 16 tokens: the record geometry of the lane-per-block
+ * attention kernels, which take the fp32 queries of this ABI as binary16 + residue rows). Statistics are reported in the reference's units in both modes. */
 #ifndef CHROMOFOLD_B200_COMPAT_ADAPTER_H
 #define CHROMOFOLD_B200_COMPAT_ADAPTER_H
 

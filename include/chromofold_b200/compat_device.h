@@ -8,7 +8,8 @@
  * generation unchanged and the layer in CF_SEAL_ACTIVE_FULL (src/cuda/device_kv_seal_attention.cu:328-333).
  * Different: pages are int8 + entropy-coded format-v1 records sealed in ONE launch (the reference: int4 nibbles,
  * six launches); a page of page_size tokens is stored as page_size / T records of T tokens (T * head_dim <= 4096;
- * T = 16 at head_dim 128, where the lane-per-block attention kernel serves these calls, fp32 queries included);
+ * T = 16 at head_dim 128, 96, 64 and 32 with pages of a multiple of 16 tokens, where the lane-per-block attention
+ * kernels serve these calls, fp32 queries included);
  * cf_device_kv_seal_full_pages_async and cf_device_kv_attention_async work (the reference ships them as fail-closed
  * stubs, src/cuda/device_kv_dataplane.cu:208-224). cf_device_page_descriptor is declared for layout compatibility;
  * this engine keeps its pages in its own arena and hands out no descriptors. */

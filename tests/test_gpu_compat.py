@@ -226,9 +226,9 @@ def test_adapter_round_trip(native, oracle, head_dim, coder, monkeypatch):
     assert st.appended_tokens == layers * hkv * tokens and st.sealed_pages == layers * hkv * 2
     assert st.sealed_tokens == layers * hkv * 64 and st.active_tokens == layers * hkv * 6
     assert 0 < st.compressed_bytes < layers * hkv * 64 * head_dim * 2 * 2      # smaller than fp16
-    # expected: tiles of T tokens quantised per stream: T = 32 while 32 * head_dim <= 4096, but 16 at head_dim 128
-    # (the record geometry of the lane-per-block kernel)
-    tile = 16 if head_dim == 128 else 32
+    # expected: tiles of T tokens quantised per stream: T = 16 at these head_dims (the record geometry of the
+    # lane-per-block kernels), else the largest divisor of the page with T * head_dim <= 4096
+    tile = 16
     deq_k, deq_v = k.copy(), v.copy()
     for layer in range(layers):
         for h in range(hkv):

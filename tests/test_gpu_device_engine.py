@@ -170,7 +170,7 @@ def test_dataplane_append_seal_attention(native, oracle, dtype):
     assert lib.cf_device_kv_attention_async(p, 0, C.c_void_p(dq.data_ptr()), C.c_void_p(out.data_ptr()), nq, tokens - nq,
                                             C.c_float(scale), 0, None) == 0, lib.cf_device_kv_last_error(p)
     torch.cuda.synchronize()
-    want = _expected(oracle, k, v, 2 * page, 32, q, [tokens - 2, tokens - 1], 0, scale, hq // hkv)
+    want = _expected(oracle, k, v, 2 * page, 16, q, [tokens - 2, tokens - 1], 0, scale, hq // hkv)
     assert np.abs(out.cpu().numpy() - want).max() <= 2e-4
     assert lib.cf_device_kv_clear_async(p, None) == 0
     # a layer may start anywhere (src/cuda/device_kv_dataplane.cu:160-168): the same rows appended from position 1000 on

@@ -129,7 +129,7 @@ def test_resolver_publish_share_batch_reclaim(native, oracle):
         if (seq, layer) in tails:
             hk = np.concatenate([hk, tails[(seq, layer)][0]])
             hv = np.concatenate([hv, tails[(seq, layer)][1]])
-        want = _expected(oracle, hk, hv, sealed, 64, q, pos, scale, hq // hkv)
+        want = _expected(oracle, hk, hv, sealed, 16, q, pos, scale, hq // hkv)
         got = od[:, :, :d].float().cpu().numpy()
         assert np.abs(got - want).max() <= (2e-3 if half_out else 2e-4), (seq, layer)
     lib.cf_ms_cuda_get_counters(r, C.byref(n))

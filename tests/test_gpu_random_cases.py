@@ -806,3 +806,76 @@ def test_random_transfer_images(native, first):
     for seed in range(8000 + first, 8000 + first + 15):
         bad, what = _transfer_case(native, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the device dataplane ABI -----------------------------------------------------------------------------------------
+def _record_tokens(page, d):
+    """Tokens per record the stores behind the reference's device ABIs choose (engine_common.cuh)."""
+    if d in (128, 96, 64, 32) and page % 16 == 0: return 16
+    limit = 4096 // d
+    for t in range(min(page, limit), 0, -1):
+        if page % t == 0: return t
+    return 1
+
+
+def _dataplane_case(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import DeviceKvConfig, DeviceKvCounters, TensorView
+    from test_gpu_device_engine import _expected
+    rng = np.random.default_rng(seed)
+    lib = native.lib(); lib.cf_device_kv_create.restype = C.c_void_p; lib.cf_device_kv_last_error.restype = C.c_char_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4, 8])); group = int(rng.choice([1, 2, 4, 7])); hq = hkv * group
+    d = int(rng.choice([32, 64, 96, 128, 128, 48, 80])); page = int(rng.choice([16, 32, 64, 24]))
+    p = C.c_void_p(lib.cf_device_kv_create(C.byref(DeviceKvConfig(layers, hkv, hq, d, page, group, 0))))
+    what = dict(seed=seed, layers=layers, heads=(hq, hkv), d=d, page=page)
+    if not p.value: return ("create refused",), what
+    dtype = ["f16", "bf16", "f32"][int(rng.integers(0, 3))]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dtype]; code = {"f16": 1, "bf16": 2, "f32": 3}[dtype]; width = 2 if dtype != "f32" else 4
+    tokens = int(rng.integers(1, 5 * page)); base = int(rng.choice([0, 0, 1000, 17]))
+    pad = int(rng.choice([0, 8]))
+    what.update(dtype=dtype, tokens=tokens, base=base)
+    ks, vs = [], []
+    for layer in range(layers):
+        k_src = torch.from_numpy((rng.standard_normal((tokens, hkv, d + pad)) * 10.0 ** rng.uniform(-2, 1)).astype(np.float32)).cuda().to(tdt)
+        v_src = torch.from_numpy((rng.standard_normal((tokens, hkv, d + pad)) * 10.0 ** rng.uniform(-3, 2)).astype(np.float32)).cuda().to(tdt)
+        ks.append(k_src); vs.append(v_src)
+        def view(t, begin, count): return TensorView(t[begin:].data_ptr(), code, count, hkv, d, hkv * (d + pad) * width, (d + pad) * width, width, 0)
+        at = 0
+        while at < tokens:
+            room = page - at % page
+            count = min(tokens - at, int(rng.integers(1, room + 1)))
+            rc = lib.cf_device_kv_append_async(p, layer, base + at, C.byref(view(k_src, at, count)), C.byref(view(v_src, at, count)), None)
+            if rc != 0: return ("append", at, count, lib.cf_device_kv_last_error(p)), what
+            at += count
+            if at % page == 0 or rng.random() < 0.2:
+                if lib.cf_device_kv_seal_full_pages_async(p, None) != 0: return ("seal", lib.cf_device_kv_last_error(p)), what
+    sealed = tokens // page * page
+    nq = int(rng.integers(1, min(4, tokens) + 1)); window = int(rng.integers(1, tokens + 3)) if rng.random() < 0.4 else 0
+    scale = 1.0 / np.sqrt(d)
+    q = rng.standard_normal((nq, hq, d)).astype(np.float32); dq = torch.from_numpy(q).cuda()
+    for layer in range(layers):
+        out = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda")
+        rc = lib.cf_device_kv_attention_async(p, layer, C.c_void_p(dq.data_ptr()), C.c_void_p(out.data_ptr()), nq, base + tokens - nq, C.c_float(scale), window, None)
+        if rc != 0: return ("attention rc", lib.cf_device_kv_last_error(p)), what
+        torch.cuda.synchronize()
+        k = ks[layer][:, :, :d].float().cpu().numpy(); v = vs[layer][:, :, :d].float().cpu().numpy()
+        want = _expected(oracle, k, v, sealed, _record_tokens(page, d), q, [tokens - nq + i for i in range(nq)], window, scale, group)
+        got = out.cpu().numpy()
+        e = np.abs(got - want).max() / (np.abs(want).max() + 1e-30)
+        if not np.isfinite(got).all() or e > 2e-4: return ("attention", layer, float(e)), what
+    n = DeviceKvCounters(); lib.cf_device_kv_get_counters(p, C.byref(n))
+    if n.dense_fallback_launches != 0: return ("dense fallback",), what
+    lib.cf_device_kv_destroy(p, None)
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_random_dataplane_cases(native, oracle, first):
+    """cf_device_kv_* on random shapes (1-2 layers, 1-8 kv heads, groups of 1-7, head_dim 32..128 with 48 and 80, pages of
+    16 / 24 / 32 / 64 tokens), fp16 / bf16 / fp32 strided rows appended in random pieces from position 0, 17 or 1000,
+    sealing as pages fill, one to four query rows with or without a window: fp64 softmax over the engine's quantisation
+    of the sealed rows, at the reference's 2e-4."""
+    for seed in range(9000 + first, 9000 + first + 20):
+        bad, what = _dataplane_case(native, oracle, seed)
+        assert bad is None, (bad, what)
