@@ -984,3 +984,111 @@ def test_random_batches_through_the_decode_runtime(native, first):
     for seed in range(9500 + first, 9500 + first + 15):
         bad, what = _runtime_case(native, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the device sequence resolver ABI under random operations ----------------------------------------------------------
+def _resolver_run(native, oracle, seed, steps):
+    import ctypes as C
+    import torch
+    from compat_types import MsBatchItem, MsConfig, MsCounters, MsPublication, PageDescriptor, TensorView
+    from test_gpu_ms_resolver import _expected, _int4_page
+    rng = np.random.default_rng(seed)
+    lib = native.lib(); lib.cf_ms_cuda_create.restype = C.c_void_p; lib.cf_ms_cuda_last_error.restype = C.c_char_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4])); group = int(rng.choice([1, 2, 4])); hq = hkv * group
+    d = int(rng.choice([64, 128, 32, 96])); page = int(rng.choice([16, 32, 64])); block = int(rng.choice([16, 32, 64]))
+    r = C.c_void_p(lib.cf_ms_cuda_create(C.byref(MsConfig(layers, hkv, hq, d, page, group, 0))))
+    assert r.value
+    err = lambda: lib.cf_ms_cuda_last_error(r)
+    tile = _record_tokens(page, d)
+    keep = []
+    seqs = {}   # id -> per layer dict(k, v sealed rows; closed (short last page); tk, tv tail rows)
+    next_id = 1; log = []; scale = 1.0 / np.sqrt(d)
+    def new_layer(): return dict(k=np.zeros((0, hkv, d), np.float32), v=np.zeros((0, hkv, d), np.float32), closed=False, tk=np.zeros((0, hkv, d), np.float32), tv=np.zeros((0, hkv, d), np.float32))
+    def total(L): return L["k"].shape[0] + L["tk"].shape[0]
+    for step in range(steps):
+        op = ["create", "publish", "publish", "publish", "stage", "stage", "copy", "execute", "execute", "remove", "reclaim"][int(rng.integers(0, 11))]
+        live = list(seqs)
+        if op == "create" or not live:
+            if len(live) >= 5: continue
+            assert lib.cf_ms_cuda_sequence_create(r, C.c_int64(next_id)) == 0, err()
+            seqs[next_id] = [new_layer() for _ in range(layers)]; log.append(("create", next_id)); next_id += 1
+        elif op == "publish":
+            s = live[int(rng.integers(0, len(live)))]; layer = int(rng.integers(0, layers)); L = seqs[s][layer]
+            if L["closed"] or L["tk"].shape[0] or L["k"].shape[0] > 400: continue
+            tokens = page if rng.random() < 0.8 else int(rng.integers(1, page + 1))
+            if (tokens * hkv * d) % block: tokens = page
+            (kp, ks, kd), (vp, vs, vd) = _int4_page(rng, tokens, hkv, d, block)
+            t = [torch.from_numpy(x).cuda() for x in (kp, vp, ks, vs)]; keep.append(t)
+            pub = MsPublication(); pub.sequence_id, pub.layer = s, layer
+            pub.descriptor = PageDescriptor(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(), L["k"].shape[0], tokens, hkv, d,
+                                            block, ks.size, kp.size, vp.size, kp.size + vp.size + 8 * ks.size, 1)
+            pub.resident_bytes, pub.seal_generation = kp.size + vp.size + 8 * ks.size, 1
+            rc = lib.cf_ms_cuda_publish_page_async(r, C.byref(pub), None)
+            log.append(("publish", s, layer, tokens))
+            assert rc == 0, ("publish", err(), log[-6:])
+            L["k"] = np.concatenate([L["k"], kd]); L["v"] = np.concatenate([L["v"], vd]); L["closed"] = tokens < page
+        elif op == "stage":
+            s = live[int(rng.integers(0, len(live)))]; layer = int(rng.integers(0, layers)); L = seqs[s][layer]
+            count = int(rng.integers(1, page))
+            tk = rng.standard_normal((count, hkv, d)).astype(np.float32); tv = rng.standard_normal((count, hkv, d)).astype(np.float32)
+            dk, dv = torch.from_numpy(tk).cuda(), torch.from_numpy(tv).cuda(); keep.append((dk, dv))
+            rc = lib.cf_ms_cuda_stage_active_async(r, C.c_int64(s), layer, L["k"].shape[0], C.c_void_p(dk.data_ptr()), C.c_void_p(dv.data_ptr()), count, None)
+            log.append(("stage", s, layer, count))
+            assert rc == 0, ("stage", err(), log[-6:])
+            L["tk"], L["tv"] = tk, tv
+        elif op == "copy" and len(live) < 5:
+            src = live[int(rng.integers(0, len(live)))]
+            rc = lib.cf_ms_cuda_copy_sequence_async(r, C.c_int64(src), C.c_int64(next_id), None)
+            log.append(("copy", src, next_id)); assert rc == 0, ("copy", err(), log[-6:])
+            seqs[next_id] = [dict(k=L["k"].copy(), v=L["v"].copy(), closed=L["closed"], tk=L["tk"].copy(), tv=L["tv"].copy()) for L in seqs[src]]
+            next_id += 1
+        elif op == "execute":
+            cand = [(s, layer) for s in live for layer in range(layers) if total(seqs[s][layer]) > 0]
+            if not cand: continue
+            n = int(rng.integers(1, min(5, len(cand)) + 1))
+            picks = [cand[i] for i in rng.choice(len(cand), n, replace=False)]
+            items = (MsBatchItem * n)(); checks = []
+            for i, (s, layer) in enumerate(picks):
+                L = seqs[s][layer]; tot = total(L)
+                nq = int(rng.integers(1, min(3, tot) + 1)); begin = tot - nq
+                q = rng.standard_normal((nq, hq, d)).astype(np.float32)
+                qd = torch.from_numpy(q).cuda(); od = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda"); keep.append((qd, od))
+                items[i].sequence_id, items[i].layer = s, layer
+                items[i].query = TensorView(qd.data_ptr(), 3, nq, hq, d, hq * d * 4, d * 4, 4, 0)
+                items[i].output, items[i].output_type = od.data_ptr(), 3
+                items[i].output_token_stride_bytes, items[i].output_head_stride_bytes, items[i].output_element_stride_bytes = hq * d * 4, d * 4, 4
+                items[i].query_token_begin, items[i].softmax_scale, items[i].causal_window = begin, scale, 0
+                checks.append((s, layer, q, [begin + j for j in range(nq)], od))
+            rc = lib.cf_ms_cuda_execute_batch_async(r, items, n, None)
+            log.append(("execute", picks)); assert rc == 0, ("execute", err(), log[-6:])
+            torch.cuda.synchronize()
+            for s, layer, q, pos, od in checks:
+                L = seqs[s][layer]
+                hk = np.concatenate([L["k"], L["tk"]]); hv = np.concatenate([L["v"], L["tv"]])
+                want = _expected(oracle, hk, hv, L["k"].shape[0], tile, q, pos, scale, group)
+                got = od.cpu().numpy()
+                assert np.abs(got - want).max() <= 2e-4 * max(1.0, np.abs(want).max()), ("attention", s, layer, float(np.abs(got - want).max()), log[-6:])
+        elif op == "remove" and len(live) > 1:
+            s = live[int(rng.integers(0, len(live)))]
+            assert lib.cf_ms_cuda_sequence_remove_async(r, C.c_int64(s), None) == 0, err()
+            log.append(("remove", s)); del seqs[s]
+        elif op == "reclaim":
+            assert lib.cf_ms_cuda_reclaim_async(r, None) == 0 and lib.cf_ms_cuda_audit(r) == 0, (err(), log[-6:])
+            log.append(("reclaim",))
+    for s in list(seqs): assert lib.cf_ms_cuda_sequence_remove_async(r, C.c_int64(s), None) == 0
+    torch.cuda.synchronize()
+    assert lib.cf_ms_cuda_reclaim_async(r, None) == 0 and lib.cf_ms_cuda_audit(r) == 0
+    n = MsCounters(); lib.cf_ms_cuda_get_counters(r, C.byref(n))
+    assert n.in_flight_page_references == 0 and n.pending_reclamation_bytes == 0 and n.dense_fallback_launches == 0, (n.in_flight_page_references, n.pending_reclamation_bytes)
+    lib.cf_ms_cuda_destroy(r, None)
+    return len(log)
+
+
+@pytest.mark.parametrize("first", range(0, 12, 6))
+def test_random_operations_on_the_sequence_resolver(native, oracle, first):
+    """cf_ms_cuda_*: sequences created, int4 pages published (transcoded on the GPU; a short page closes its layer),
+    tails staged, sequences copied and removed, batches of decode and short prefill items executed, reclaim with audit,
+    in random order; attention against fp64 softmax over the model's rows with the sealed ones requantised as the
+    store does."""
+    for seed in range(9800 + first, 9800 + first + 6):
+        assert _resolver_run(native, oracle, seed, 70) > 0
