@@ -130,3 +130,63 @@ def test_memory_of_another_gpu_is_refused_before_any_launch(native):
         assert native.lib().cf_b200_sealed_attention_async(C.byref(desc), stream) == native.CF_OK
         torch.cuda.synchronize()
     assert layer.device_status() == 0
+
+
+def _scheduler_run(native, seed):
+    import os
+    import torch
+    from chromofold_b200.scheduler import MultiGpuScheduler
+    from chromofold_b200.workloads import build_sealed_layer
+    rng = np.random.default_rng(seed)
+    world = min(torch.cuda.device_count(), 4)
+    n = int(rng.integers(1, 24))
+    hq, hkv = [(32, 8), (64, 8), (8, 8)][int(rng.integers(0, 3))]
+    coder = ["rans4", "huffman4", "rans", "fixed8"][int(rng.integers(0, 4))]
+    contexts = rng.integers(1, 60, n) * 16
+    whole, _ = build_sealed_layer(contexts, query_heads=hq, kv_heads=hkv, coder=coder, seed=seed, device="cuda:0")
+    where = rng.integers(0, world, n)           # an arbitrary placement, not the planner's
+    layers, slot_of = [], {}
+    for d in range(world):
+        mine = [s for s in range(n) if where[s] == d]
+        lay, _ = build_sealed_layer(np.array([0] * max(len(mine), 1)), query_heads=hq, kv_heads=hkv, coder=coder, seed=seed + 1 + d, device=f"cuda:{d}",
+                                    extra_pages_per_sequence=int(contexts.max()) // 16 + 2, reserve_pages=int(contexts.sum()) // 16 + 8)
+        lay.k_tables.copy_(whole.k_tables.to(lay.device)); lay.v_tables.copy_(whole.v_tables.to(lay.device)); lay.host_tables = whole.host_tables
+        for local, seq in enumerate(mine):
+            pages = int(contexts[seq]) // 16
+            recs = [[whole.record_bytes(int(whole.h_page_table[seq, p]), h) for h in range(hkv)] for p in range(pages)]
+            lay.import_records(local, recs); slot_of[seq] = (d, local)
+        layers.append(lay)
+    copies = rng.random() < 0.3
+    if copies: os.environ["CHROMOFOLD_B200_MG_COPIES"] = "1"
+    try: sched = MultiGpuScheduler(layers, max_rows=32)
+    finally: os.environ.pop("CHROMOFOLD_B200_MG_COPIES", None)
+    g = torch.Generator(device="cuda:0"); g.manual_seed(seed)
+    for step in range(int(rng.integers(2, 6))):
+        m = int(rng.integers(1, n + 1))
+        subset = [int(x) for x in rng.choice(n, m, replace=False)]          # row i of the batch is sequence subset[i]
+        if step and rng.random() < 0.4: subset = prev                        # the same placement again (cached row order)
+        prev = subset; m = len(subset)
+        q = torch.randn((m, hq, 128), generator=g, device="cuda:0", dtype=torch.float32).half()
+        want = whole.attention(q, slots=subset, min_pages_per_unit=16).cpu().numpy()
+        assignment = [[i for i, s in enumerate(subset) if slot_of[s][0] == d] for d in range(world)]
+        local_slots = [[slot_of[subset[i]][1] for i in assignment[d]] for d in range(world)]
+        out = torch.full((m, hq, 128), 5.0, dtype=torch.float32, device="cuda:0")
+        sched.attention_by_sequence(q, out, assignment, local_slots, min_pages_per_unit=16)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        if not np.array_equal(got, want):
+            return ("step", step, float(np.abs(got - want).max()), dict(seed=seed, n=n, m=m, heads=(hq, hkv), coder=coder, copies=copies, world=world))
+    ok = all(l.device_status() == 0 for l in layers)
+    sched.close()
+    return None if ok else ("status",)
+
+
+@pytest.mark.parametrize("first", range(0, 12, 6))
+def test_random_placements_and_changing_batches(native, first):
+    """Sequences placed on the devices at random (not by the planner), then several steps through ONE scheduler whose
+    batches change from step to step — a random subset of the sequences in a random row order, or the same batch again
+    (the cached row order) — on the direct-store path or the copy path: every step equals the answer of one store
+    holding everything, bit for bit."""
+    for seed in range(500 + first, 500 + first + 6):
+        bad = _scheduler_run(native, seed)
+        assert bad is None, bad
