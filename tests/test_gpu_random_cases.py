@@ -328,9 +328,10 @@ def _multisequence_run(native, oracle, seed, steps):
     def attend(pairs, defer=False):
         qs, outs, items, rows = [], [], (MsBatchItem * len(pairs))(), []
         for i, (seq, layer) in enumerate(pairs):
-            q = torch.from_numpy(rng.standard_normal((1, HQ, D)).astype(np.float32)).cuda()
-            out = torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda")
-            items[i] = item(seq, layer, q, out, seqs[seq]["base"] + count(seq) - 1)
+            nq = int(rng.integers(1, min(4, count(seq)) + 1)) if rng.random() < 0.3 else 1   # a short prefill item now and then
+            q = torch.from_numpy(rng.standard_normal((nq, HQ, D)).astype(np.float32)).cuda()
+            out = torch.zeros((nq, HQ, D), dtype=torch.float32, device="cuda")
+            items[i] = item(seq, layer, q, out, seqs[seq]["base"] + count(seq) - nq)
             qs.append(q); outs.append(out); rows.append(tuple(seqs[seq]["rows"][layer]))
         rc = lib.cf_multisequence_attention_async(c, items, len(pairs), None)
         assert rc == 0, ("attend", pairs, err(), log[-6:])
@@ -341,7 +342,8 @@ def _multisequence_run(native, oracle, seed, steps):
         for pairs, qs, outs, rows, at in pending:
             for (seq, layer), q, out, (k, v) in zip(pairs, qs, outs, rows):
                 sealed = k.shape[0] // PAGE * PAGE
-                want = _expected(oracle, k, v, sealed, 16, q.cpu().numpy(), [k.shape[0] - 1], 1.0 / np.sqrt(D), G)
+                nq = q.shape[0]
+                want = _expected(oracle, k, v, sealed, 16, q.cpu().numpy(), list(range(k.shape[0] - nq, k.shape[0])), 1.0 / np.sqrt(D), G)
                 got = out.cpu().numpy()
                 assert np.allclose(got, want, rtol=2e-3, atol=1e-3), ("attention differs", seq, layer, float(np.abs(got - want).max()), at, log[-8:])
         pending.clear()
@@ -366,6 +368,7 @@ def _multisequence_run(native, oracle, seed, steps):
         elif op == "attend" and nonempty:
             pairs = [(nonempty[int(rng.integers(0, len(nonempty)))], int(rng.integers(0, LAYERS))) for _ in range(int(rng.integers(1, 6)))]
             if rng.random() < 0.5: pairs = [(s, pairs[0][1]) for s, _ in pairs]   # one layer for the whole batch
+            pairs = list(dict.fromkeys(pairs)) if rng.random() < 0.5 else pairs
             defer = rng.random() < 0.6
             log.append(("attend", pairs, "deferred" if defer else "")); attend(pairs, defer)
         elif op == "copy" and nonempty and len(live) < 6:
@@ -451,7 +454,8 @@ def _multisequence_run(native, oracle, seed, steps):
 @pytest.mark.parametrize("first", range(0, 24, 8))
 def test_random_operations_on_the_multisequence_cache(native, oracle, first):
     """cf_sequence_create / append (fp16, bf16, fp32 rows) / copy over ranges / suffix and whole removal / shift /
-    speculation commit and rollback / reclaim with audit / batched attention, in random order on up to six sequences.
+    speculation commit and rollback / reclaim with audit / batched attention (decode items and short prefill items), in
+    random order on up to six sequences.
     More than half of the attention batches are checked only after the operations that follow them (removals, reclaim,
     new pages that may take freed arena slots), against the rows the sequences had when the batch was launched."""
     for seed in range(3000 + first, 3000 + first + 8):
