@@ -1096,3 +1096,77 @@ def test_random_operations_on_the_sequence_resolver(native, oracle, first):
     store does."""
     for seed in range(9800 + first, 9800 + first + 6):
         assert _resolver_run(native, oracle, seed, 70) > 0
+
+
+# ---- the seal engine ABI ----------------------------------------------------------------------------------------------
+def _seal_engine_case(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import DeviceSealConfig, DeviceSealCounters, TensorView
+    from test_gpu_device_engine import _expected
+    rng = np.random.default_rng(seed)
+    lib = native.lib(); lib.cf_device_seal_create.restype = C.c_void_p; lib.cf_device_seal_last_error.restype = C.c_char_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4, 8])); group = int(rng.choice([1, 2, 4, 7])); hq = hkv * group
+    d = int(rng.choice([32, 64, 96, 128, 128, 80])); page = int(rng.choice([16, 32, 64]))
+    e = C.c_void_p(lib.cf_device_seal_create(C.byref(DeviceSealConfig(layers, hkv, hq, d, page, group, 64, 0))))
+    what = dict(seed=seed, layers=layers, heads=(hq, hkv), d=d, page=page)
+    if not e.value: return ("create refused",), what
+    err = lambda: lib.cf_device_seal_last_error(e)
+    state, n = C.c_uint32(0), DeviceSealCounters()
+    tile = _record_tokens(page, d)
+    for layer in range(layers):
+        pages = int(rng.integers(0, 6)); tail = int(rng.integers(0, page))
+        if pages + tail == 0: tail = 1
+        tokens = pages * page + tail
+        k = (rng.standard_normal((tokens, hkv, d)) * 10.0 ** rng.uniform(-2, 1)).astype(np.float32); v = (rng.standard_normal((tokens, hkv, d)) * 10.0 ** rng.uniform(-3, 2)).astype(np.float32)
+        dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+        def stage(begin, count, src_k=None): return lib.cf_device_seal_stage_active_page(e, layer, begin, C.c_void_p((src_k if src_k is not None else dk)[begin:].data_ptr()), C.c_void_p(dv[begin:].data_ptr()), count, None)
+        for pg in range(pages):
+            b = pg * page
+            if rng.random() < 0.3:   # a partial stage first, then the whole page
+                part = int(rng.integers(1, page))
+                if stage(b, part) != 0: return ("partial stage", err()), what
+                if lib.cf_device_seal_full_page_async(e, layer, None) != -1: return ("sealed a page that is not full",), what
+            if rng.random() < 0.2:   # a NaN page is refused and stays staged
+                bad = dk.clone(); bad[b + int(rng.integers(0, page)), int(rng.integers(0, hkv)), int(rng.integers(0, d))] = float("nan")
+                if stage(b, page, bad) != 0: return ("stage nan", err()), what
+                if lib.cf_device_seal_full_page_async(e, layer, None) != -1 or b"NaN" not in err(): return ("nan page not refused", err()), what
+            if stage(b, page) != 0: return ("stage", err()), what
+            lib.cf_device_seal_get_counters(e, C.byref(n)); before = (n.seal_successes, n.page_table_generation, n.descriptor_publications)
+            for _ in range(int(rng.integers(0, 3))):
+                fault = int(rng.choice([1, 2, 3, 4, 5, 6, 7, 9, 10]))
+                lib.cf_device_seal_set_fault(e, fault)
+                if lib.cf_device_seal_full_page_async(e, layer, None) != -1: return ("fault ignored", fault), what
+                lib.cf_device_seal_get_state(e, layer, C.byref(state)); lib.cf_device_seal_get_counters(e, C.byref(n))
+                if state.value != 1 or (n.seal_successes, n.page_table_generation, n.descriptor_publications) != before: return ("fault left traces", fault), what
+            lib.cf_device_seal_set_fault(e, 0)
+            if lib.cf_device_seal_full_page_async(e, layer, None) != 0: return ("seal", err()), what
+        if tail and stage(pages * page, tail) != 0: return ("tail stage", err()), what
+        for _ in range(2):
+            nq = int(rng.integers(1, min(4, tokens) + 1)); window = int(rng.integers(1, tokens + 3)) if rng.random() < 0.4 else 0
+            scale = 1.0 / np.sqrt(d)
+            q = rng.standard_normal((nq, hq, d)).astype(np.float32); qf = torch.from_numpy(q).cuda()
+            view = TensorView(qf.data_ptr(), 3, nq, hq, d, hq * d * 4, d * 4, 4, 0)
+            out = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda")
+            pos0 = int(rng.integers(nq - 1, tokens)) - (nq - 1)
+            pos = [pos0 + i for i in range(nq)]
+            rc = lib.cf_device_seal_attention_async(e, layer, C.byref(view), C.c_void_p(out.data_ptr()), 3, C.c_uint64(hq * d * 4), C.c_uint64(d * 4), C.c_uint64(4), pos[0], C.c_float(scale), window, None)
+            if rc != 0: return ("attention rc", err(), pos, tokens), what
+            torch.cuda.synchronize()
+            want = _expected(oracle, k, v, pages * page, tile, q, pos, window, scale, group)
+            got = out.cpu().numpy()
+            er = np.abs(got - want).max() / (np.abs(want).max() + 1e-30)
+            if not np.isfinite(got).all() or er > 2e-4: return ("attention", layer, float(er), pos, tokens, window), what
+    lib.cf_device_seal_destroy(e, None)
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 30, 15))
+def test_random_seal_engine_cases(native, oracle, first):
+    """cf_device_seal_*: pages staged (sometimes partly first, sometimes with a NaN first, which must be refused and
+    leave the page staged), sealed after zero to two injected faults at random fault points (each must abort without
+    a trace in the counters or the state), a partial tail, and query rows at random positions with or without a
+    window, against fp64 softmax over the engine's quantisation."""
+    for seed in range(9900 + first, 9900 + first + 15):
+        bad, what = _seal_engine_case(native, oracle, seed)
+        assert bad is None, (bad, what)
