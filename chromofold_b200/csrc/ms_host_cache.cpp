@@ -222,13 +222,33 @@ extern "C" int cf_sequence_remove_async(cf_multisequence_cache *c, int64_t id, i
             maybe_audit(c);
             return;
         }
+        // src/multisequence_cache.cpp:314-347. A sealed page the range covers goes, one it cuts is an error (an empty range
+        // strictly inside a page cuts it); an active tail the range covers goes, one it enters and leaves by its end is
+        // cut there, any other overlap is an error (an empty range strictly inside the tail too); a range that meets
+        // nothing cached succeeds. Every successful range removal counts as a removal. Narrower here: what goes must be
+        // a suffix of the sequence.
         const int64_t base = find(c, id).base;   // positions are logical; the store counts from the sequence's first held token
-        position_begin = std::max<int64_t>(position_begin - base, 0);
-        position_end = position_end < 0 ? position_end : std::max<int64_t>(position_end - base, 0);
-        const uint32_t total = total_tokens(c, id);
-        if (position_begin >= total) return;   // nothing cached there
-        if (position_end < total) throw Unsupported("only a suffix of a sequence can be removed");
-        if (cf_b200_ms_truncate_async(c->device, id, static_cast<uint32_t>(position_begin), stream) != 0)
+        const int64_t lo = std::max<int64_t>(position_begin, 0) - base, hi = position_end - base;   // may be negative
+        const int64_t page = c->config.page_size, total = total_tokens(c, id), sealed = sealed_tokens(c, id);
+        int64_t keep = total;   // tokens that stay
+        bool page_kept_after_removed = false;
+        for (int64_t p0 = 0; p0 < sealed; p0 += page) {
+            const int64_t p1 = std::min(p0 + page, sealed);
+            if (hi <= p0 || lo >= p1) {
+                if (keep < total) page_kept_after_removed = true;
+                continue;
+            }
+            if (lo > p0 || hi < p1) throw Unsupported("removal inside immutable page is not supported");
+            keep = std::min(keep, p0);
+        }
+        if (total > sealed) {   // the active tail [sealed, total)
+            if (lo <= sealed && hi >= total) keep = std::min(keep, sealed);
+            else if (lo >= sealed && lo < total && hi >= total) keep = std::min(keep, lo);
+            else if (hi > sealed && lo < total) throw Unsupported("non-suffix active-tail removal is not supported");
+            else if (keep < total) page_kept_after_removed = true;   // pages went, the tail after them stays
+        }
+        if (page_kept_after_removed) throw Unsupported("only a suffix of a sequence can be removed");
+        if (keep < total && cf_b200_ms_truncate_async(c->device, id, static_cast<uint32_t>(keep), stream) != 0)
             throw Unsupported(cf_ms_cuda_last_error(c->device));
         ++c->counters.sequences_removed;
         maybe_audit(c);
@@ -247,13 +267,17 @@ extern "C" int cf_sequence_shift_async(cf_multisequence_cache *c, int64_t id, ui
         const uint32_t page = c->config.page_size, total = total_tokens(c, id), sealed = sealed_tokens(c, id);
         const uint64_t lo = position_begin > q.base ? position_begin - q.base : 0u;
         const uint64_t hi = position_end > q.base ? std::min<uint64_t>(position_end - q.base, total) : 0u;
-        const bool cuts_a_page = (lo < sealed && lo % page != 0) || (hi < sealed && hi % page != 0) ||
-                                 (lo > sealed && lo < total) || (hi > sealed && hi < total);
+        // a sealed page the range cuts is an error; an active tail the range cuts simply does not move (:372-377)
+        const bool cuts_a_page = (lo < sealed && lo % page != 0) || (hi < sealed && hi % page != 0);
         if (lo < hi && cuts_a_page) throw Unsupported("context shift must align with immutable page boundaries");
-        const bool everything = lo == 0 && hi >= total, nothing = lo >= hi;
+        const uint64_t first_page = std::min<uint64_t>((lo + page - 1) / page, sealed / page);
+        const uint64_t pages_moved = lo < hi ? std::min<uint64_t>(hi, sealed) / page - std::min(first_page, std::min<uint64_t>(hi, sealed) / page) : 0u;
+        const bool has_tail = total > sealed, tail_moves = has_tail && lo < hi && lo <= sealed && hi >= total;
+        const bool nothing = pages_moved == 0 && !tail_moves;
+        const bool everything = total > 0 && pages_moved == sealed / page && (tail_moves || !has_tail);
         if (!nothing && !everything && delta != 0)
             throw Unsupported("a shift of part of a sequence would leave a gap in its stored tokens");
-        if (everything && total > 0) {
+        if (everything) {
             if (static_cast<int64_t>(q.base) + delta < 0) throw std::runtime_error("context shift produces negative token position");
             q.base = static_cast<uint32_t>(static_cast<int64_t>(q.base) + delta);
         }
@@ -269,6 +293,9 @@ extern "C" int cf_sequence_append_async(cf_multisequence_cache *c, int64_t id, u
         return -1;
     return guarded(c, [&] {
         SequenceState &q = find(c, id);
+        // a sequence that holds nothing adopts the position of its first rows (src/multisequence_cache.cpp:423: an empty
+        // active page takes the caller's token_begin); the layers of one sequence share that first position here
+        if (total_tokens(c, id) == 0) q.base = token_begin;
         if (token_begin < q.base) throw std::runtime_error("non-contiguous sequence append");
         device_check(c, cf_b200_ms_append_active_async(c->device, id, layer, token_begin - q.base, keys, values, stream));
         uint32_t sealed = 0, active = 0;
@@ -328,7 +355,8 @@ extern "C" int cf_sequence_speculation_commit(cf_multisequence_cache *c, int64_t
         if (it == c->sequences.end() || !it->second.speculation.active || it->second.speculation.id != speculation_id)
             throw std::runtime_error("invalid speculative transaction");
         const uint32_t baseline = it->second.speculation.baseline_tokens;
-        if (accepted_tokens > total_tokens(c, id) - std::min(baseline, total_tokens(c, id)))
+        if (total_tokens(c, id) < baseline) throw std::runtime_error("active tail predates speculative baseline");
+        if (accepted_tokens > total_tokens(c, id) - baseline)
             throw std::runtime_error("accepted token count exceeds provisional tail");
         device_check(c, cf_b200_ms_truncate_async(c->device, id, baseline + accepted_tokens, stream));
         it->second.speculation = {};

@@ -15,9 +15,17 @@
  * it, shared by reference, and the active tail if it lies wholly inside; a range that starts after token 0 gives a
  * sequence whose first held token keeps its old position. Shift (:357-380): a range that cuts a sealed page is an
  * error; a range that covers the whole sequence moves it (positions are not stored in sealed pages, so only the
- * sequence's offset changes); a range that covers nothing, or a delta of 0, does nothing.
+ * sequence's offset changes); a range that covers nothing, or a delta of 0, does nothing; an active tail that the
+ * range cuts stays where it is without an error, as in the reference. A sequence that holds nothing takes the position
+ * of the first rows appended to it (:423). A removal range that covers nothing cached succeeds, and every successful
+ * range removal counts in sequences_removed (:345). A commit is refused when the tail has become shorter than it was
+ * at speculation_begin (:497). The calls that can be compared with the reference's own cache (no sealed pages: its
+ * cache never seals) return the same status for the same sequence of operations; tests/test_gpu_random_cases.py
+ * runs both side by side.
  * Narrower than the reference: a non-zero shift of only part of a sequence (which would leave a gap inside it) and the
- * removal of a range that is not a suffix are refused and counted in unsupported_operations. */
+ * removal of a range that is not a suffix are refused and counted in unsupported_operations; the layers of one
+ * sequence start at the same position; a rollback never lengthens a tail (the reference sets every layer to the
+ * baseline count even when rows were removed in between). */
 #ifndef CHROMOFOLD_B200_COMPAT_MSCACHE_H
 #define CHROMOFOLD_B200_COMPAT_MSCACHE_H
 

@@ -58,6 +58,13 @@ def ref_cuda():
     return C.CDLL(path) if os.path.exists(path) else None
 
 
+def ref_mscache():
+    """The reference's host sequence cache (src/multisequence_cache.cpp) with the tensor-view validator it calls
+    (None when not built)."""
+    path = os.path.join(HERE, "_ref", "libcfref_mscache.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
 def _p(a, t=None):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 

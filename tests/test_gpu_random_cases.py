@@ -1170,3 +1170,132 @@ def test_random_seal_engine_cases(native, oracle, first):
     for seed in range(9900 + first, 9900 + first + 15):
         bad, what = _seal_engine_case(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the host sequence cache against the reference's own ---------------------------------------------------------------
+def _cache_prototypes(lib):
+    import ctypes as C
+    lib.cf_multisequence_create.restype = C.c_void_p
+    lib.cf_multisequence_last_error.restype = C.c_char_p
+    lib.cf_sequence_speculation_begin.restype = C.c_uint64
+
+
+def _cache_side_by_side(native, oracle, seed, steps):
+    """The same random calls on this library's cache and on the reference's, compiled from its source; returns the first
+    difference in a status (with the calls before it) or in the final counters, or None."""
+    import ctypes as C
+    import torch
+    from compat_types import MultisequenceConfig, MultisequenceCounters, MULTISEQUENCE_COUNTER_NAMES
+    from test_gpu_mscache import _view
+    rng = np.random.default_rng(seed)
+    mine, ref = native.lib(), oracle.ref_mscache()
+    _cache_prototypes(mine); _cache_prototypes(ref)
+    LAYERS = int(rng.integers(1, 3)); HKV = int(rng.choice([1, 2])); G = int(rng.choice([1, 4])); HQ = HKV * G; D = 128; PAGE = int(rng.choice([16, 32]))
+    cfg = MultisequenceConfig(LAYERS, HKV, HQ, D, PAGE, G, 0, 1)
+    a, b = C.c_void_p(mine.cf_multisequence_create(C.byref(cfg))), C.c_void_p(ref.cf_multisequence_create(C.byref(cfg)))
+    assert a.value and b.value
+    i64 = C.c_int64
+    count = {}; begin = {}   # model of the active rows per sequence (the same in every layer)
+    specs = {}               # sequence -> (id mine, id ref, baseline)
+    log = []
+    rows = torch.zeros((PAGE, HKV, D), dtype=torch.float16, device="cuda")
+    def both(name, *args):
+        ra, rb = getattr(mine, name)(a, *args), getattr(ref, name)(b, *args)
+        return ra, rb
+    for step in range(steps):
+        ids = list(count) or [1]
+        pick = lambda: int(ids[int(rng.integers(0, len(ids)))]) if rng.random() < 0.9 else int(rng.integers(1, 9))
+        op = ["create", "append", "append", "append", "copy", "remove", "remove_range", "shift", "spec_begin", "spec_end", "reclaim"][int(rng.integers(0, 11))]
+        if op == "create":
+            s = int(rng.integers(1, 9)); ra, rb = both("cf_sequence_create", i64(s)); log.append((op, s, ra, rb))
+            if ra == 0 and rb == 0 and s not in count: count[s] = 0; begin[s] = 0
+        elif op == "append":
+            s = pick(); n = int(rng.integers(1, PAGE + 2)); c = count.get(s, 0)
+            if c + n == PAGE: n += 1            # an exactly full page: this library seals it, the reference's cache never does
+            n = min(n, PAGE)
+            if c + n == PAGE: continue
+            where = begin.get(s, 0) + c if (c or rng.random() < 0.7) else int(rng.integers(0, 100))
+            if rng.random() < 0.1: where += int(rng.integers(1, 5))      # a gap
+            res = []
+            for layer in range(LAYERS):
+                kv = _view(rows, n)
+                res.append((mine.cf_sequence_append_async(a, i64(s), layer, where, C.byref(kv), C.byref(kv), None),
+                            ref.cf_sequence_append_async(b, i64(s), layer, where, C.byref(kv), C.byref(kv), None)))
+            log.append((op, s, n, where, res))
+            if any(x != y for x, y in res): return ("append", [l for l in log if len(l) > 1 and l[1] == s][-12:], "PAGE", PAGE)
+            if res[0][0] == 0 and s in count:
+                if c == 0: begin[s] = where
+                count[s] = c + n
+        elif op == "copy":
+            s, t = pick(), int(rng.integers(1, 9))
+            kind = int(rng.integers(0, 3))
+            lo, hi = (0, 1 << 30) if kind == 0 else tuple(sorted(int(x) for x in rng.integers(0, 120, 2)))
+            ra, rb = both("cf_sequence_copy_async", i64(s), i64(t), C.c_uint32(lo), C.c_uint32(hi), None); log.append((op, s, t, lo, hi, ra, rb))
+            if ra != rb: return ("copy", log[-5:])
+            if ra == 0:
+                c, bg = count.get(s, 0), begin.get(s, 0)
+                inside = c and bg >= lo and bg + c <= hi
+                count[t] = c if inside else 0; begin[t] = bg if inside else 0
+                specs.pop(t, None)
+        elif op == "remove":
+            s = pick(); ra, rb = both("cf_sequence_remove_async", i64(s), i64(-1), i64(-1), None); log.append((op, s, ra, rb))
+            if ra != rb: return ("remove", log[-5:])
+            if ra == 0: count.pop(s, None); begin.pop(s, None); specs.pop(s, None)
+        elif op == "remove_range":
+            s = pick(); c, bg = count.get(s, 0), begin.get(s, 0)
+            if s in specs: continue     # the reference's rollback would then lengthen the tail again
+            lo = bg + int(rng.integers(-2, c + 3)); hi = lo + int(rng.integers(0, c + 4)) if rng.random() < 0.5 else 1 << 40
+            ra, rb = both("cf_sequence_remove_async", i64(s), i64(lo), i64(hi), None); log.append((op, s, lo, hi, "active", bg, c, ra, rb))
+            if ra != rb: return ("remove_range", log[-5:])
+            if ra == 0 and s in count:
+                l2 = max(lo, 0)
+                if l2 <= bg and hi >= bg + c: count[s] = 0
+                elif bg <= l2 < bg + c and hi >= bg + c: count[s] = l2 - bg
+        elif op == "shift":
+            s = pick(); c, bg = count.get(s, 0), begin.get(s, 0)
+            lo, hi = (0, 1 << 30) if rng.random() < 0.6 else tuple(sorted(int(x) for x in rng.integers(0, 120, 2)))
+            delta = int(rng.integers(-40, 40))
+            ra, rb = both("cf_sequence_shift_async", i64(s), C.c_uint32(lo), C.c_uint32(hi), C.c_int32(delta), None); log.append((op, s, lo, hi, delta, "active", bg, c, ra, rb))
+            if ra != rb: return ("shift", log[-5:])
+            if ra == 0 and s in count and c and bg >= lo and bg + c <= hi: begin[s] = bg + delta
+        elif op == "spec_begin":
+            s = pick(); ia, ib = mine.cf_sequence_speculation_begin(a, i64(s)), ref.cf_sequence_speculation_begin(b, i64(s)); log.append((op, s, ia, ib))
+            if (ia == 0) != (ib == 0): return ("spec_begin", log[-5:])
+            if ia: specs[s] = (ia, ib, count.get(s, 0))
+        elif op == "spec_end" and specs:
+            s = list(specs)[int(rng.integers(0, len(specs)))]; ia, ib, base = specs[s]
+            if rng.random() < 0.15: ia, ib = ia + 7, ib + 7      # a wrong id
+            if rng.random() < 0.5:
+                keep = int(rng.integers(0, max(count.get(s, 0) - base, 0) + 2))
+                ra, rb = mine.cf_sequence_speculation_commit(a, i64(s), C.c_uint64(ia), keep, None), ref.cf_sequence_speculation_commit(b, i64(s), C.c_uint64(ib), keep, None)
+                log.append(("commit", s, keep, "count", count.get(s), "base", base, ra, rb))
+                if ra != rb: return ("commit", log[-5:])
+                if ra == 0: count[s] = base + keep; specs.pop(s)
+            else:
+                ra, rb = mine.cf_sequence_speculation_rollback(a, i64(s), C.c_uint64(ia), None), ref.cf_sequence_speculation_rollback(b, i64(s), C.c_uint64(ib), None)
+                log.append(("rollback", s, "count", count.get(s), "base", base, ra, rb))
+                if ra != rb: return ("rollback", log[-5:])
+                if ra == 0: count[s] = base; specs.pop(s)
+        elif op == "reclaim":
+            ra, rb = both("cf_multisequence_reclaim_async", None); ra2, rb2 = mine.cf_multisequence_audit(a), ref.cf_multisequence_audit(b)
+            if (ra, ra2) != (rb, rb2): return ("reclaim/audit", ra, rb, ra2, rb2, log[-5:])
+    ka, kb = MultisequenceCounters(), MultisequenceCounters()
+    mine.cf_multisequence_get_counters(a, C.byref(ka)); ref.cf_multisequence_get_counters(b, C.byref(kb))
+    diff = {n: (int(getattr(ka, n)), int(getattr(kb, n))) for n in MULTISEQUENCE_COUNTER_NAMES if getattr(ka, n) != getattr(kb, n)}
+    mine.cf_multisequence_destroy(a, None); ref.cf_multisequence_destroy(b, None)
+    return ("counters", diff) if diff else None
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_sequence_cache_calls_answer_like_the_references_own_cache(native, oracle, first):
+    """cf_sequence_create / append / copy / remove (whole and ranges) / shift / speculation begin, commit, rollback /
+    reclaim / audit with valid and invalid arguments (unknown ids, gaps, ranges that cut the tail, empty ranges, wrong
+    speculation ids), the same calls on the reference's own host cache (src/multisequence_cache.cpp compiled into
+    oracle/_ref): every call returns the same status and the counter blocks are equal at the end. The runs stay where
+    the two can be compared: the reference's cache never seals a page, so no tail is filled exactly, and no rows are
+    removed while a speculation is open (its rollback would then lengthen the tail again)."""
+    if oracle.ref_mscache() is None:
+        pytest.skip("needs the reference's host cache (oracle/_ref)")
+    for seed in range(first, first + 20):
+        bad = _cache_side_by_side(native, oracle, seed, 120)
+        assert bad is None, (seed, bad)
