@@ -8,7 +8,9 @@
  * Different, on purpose:
  *   - nibbles are read as offset-binary (value = nibble - 8), which is what the reference's seal engine writes
  *     (src/cuda/device_kv_seal_attention.cu:102,118); the reference's own batch kernel reads them as two's
- *     complement (src/cuda/production_attention.cu:39-44) and so disagrees with the pages it is given;
+ *     complement (src/cuda/production_attention.cu:39-44) and so disagrees with the pages it is given (given the same
+ *     values re-encoded as two's-complement nibbles, its kernel and this library agree to 2e-5:
+ *     tests/test_gpu_random_cases.py runs the two side by side);
  *   - visibility is the rule of the rest of the path, first <= token <= query position with
  *     first = max(0, position + 1 - window) (src/runtime/kv_reference.cpp:205-207), not
  *     `token + window < query_token_begin` (production_attention.cu:84);

@@ -65,6 +65,14 @@ def ref_mscache():
     return C.CDLL(path) if os.path.exists(path) else None
 
 
+def ref_device():
+    """The reference's own decode runtime, seal engine, sequence resolver and dataplane (src/cuda/production_attention.cu,
+    device_kv_seal_attention.cu, multisequence_cuda_resolver.cu, device_kv_dataplane.cu), compiled for sm_100a (None when
+    not built)."""
+    path = os.path.join(HERE, "_ref", "libcfref_device.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
 def _p(a, t=None):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 

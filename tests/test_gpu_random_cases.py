@@ -1299,3 +1299,139 @@ def test_sequence_cache_calls_answer_like_the_references_own_cache(native, oracl
     for seed in range(first, first + 20):
         bad = _cache_side_by_side(native, oracle, seed, 120)
         assert bad is None, (seed, bad)
+
+
+# ---- the decode runtime beside the reference's own --------------------------------------------------------------------
+def _runtime_int4_page_pair(rng, tokens, token_begin, keep, HKV, D, BLOCK, wild):
+    """One page twice: nibbles as the reference's seal engine writes them (value + 8, device_kv_seal_attention.cu:101) and
+    the same values as two's-complement nibbles, which is how the reference's decode kernel reads a nibble
+    (production_attention.cu:39-44)."""
+    import torch
+    from compat_types import PageDescriptor
+    desc, desc2, dense = PageDescriptor(), PageDescriptor(), []
+    for name in ("key", "value"):
+        x = rng.standard_normal((tokens, HKV, D)).astype(np.float32)
+        if wild: x *= (10.0 ** rng.uniform(-3, 2, (tokens, 1, 1))).astype(np.float32)
+        blocks = x.reshape(-1, BLOCK)
+        scale = (np.abs(blocks).max(axis=1) / 7.0).astype(np.float32)
+        scale[scale == 0] = 1.0
+        q = np.clip(np.rint(blocks / scale[:, None]), -7, 7).astype(np.int32)
+        dense.append((q.astype(np.float32) * scale[:, None]).reshape(tokens, HKV, D))
+        nib = (q + 8).astype(np.uint8).reshape(-1)
+        payload = (nib[0::2] | (nib[1::2] << 4)).astype(np.uint8)
+        twos = (q & 0xF).astype(np.uint8).reshape(-1)                    # the same values as two's-complement nibbles
+        payload2 = (twos[0::2] | (twos[1::2] << 4)).astype(np.uint8)
+        p, s, p2 = torch.from_numpy(payload).cuda(), torch.from_numpy(scale).cuda(), torch.from_numpy(payload2).cuda()
+        keep += [p, s, p2]
+        setattr(desc, name + "_payload", p.data_ptr()); setattr(desc, name + "_scales", s.data_ptr()); setattr(desc, name + "_payload_bytes", payload.size)
+        setattr(desc2, name + "_payload", p2.data_ptr()); setattr(desc2, name + "_scales", s.data_ptr()); setattr(desc2, name + "_payload_bytes", payload.size)
+    for x in (desc, desc2):
+        x.token_begin, x.token_count, x.kv_head_count, x.head_dim = token_begin, tokens, HKV, D
+        x.block_size, x.blocks_per_page = BLOCK, tokens * HKV * D // BLOCK
+    return (desc, desc2), dense[0], dense[1]
+
+
+def _runtime_side_by_side(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import AttentionBatchItem, AttentionCounters, AttentionRuntimeConfig, PageDescriptor, TensorView
+    rng = np.random.default_rng(seed)
+    lib = native.lib(); lib.cf_attention_runtime_create.restype = C.c_void_p; lib.cf_attention_last_error.restype = C.c_char_p
+    ref = oracle.ref_device(); ref.cf_attention_runtime_create.restype = C.c_void_p
+    HKV = int(rng.choice([1, 2, 4, 8])); G = int(rng.choice([1, 2, 4, 7])); HQ = HKV * G
+    D = int(rng.choice([32, 64, 96, 128, 80])); BLOCK = int(rng.choice([16, 32, 64])); PAGE = int(rng.choice([16, 32, 64]))
+    if D % BLOCK and BLOCK % D: BLOCK = 16
+    mode = 1; layers = int(rng.integers(1, 4))
+    cfg = AttentionRuntimeConfig()
+    cfg.layer_count, cfg.query_head_count, cfg.kv_head_count, cfg.head_dim = layers, HQ, HKV, D
+    cfg.page_size, cfg.block_size, cfg.gqa_group_size, cfg.mode = PAGE, BLOCK, G, mode
+    rt = C.c_void_p(lib.cf_attention_runtime_create(C.byref(cfg)))
+    what = dict(seed=seed, heads=(HQ, HKV), D=D, BLOCK=BLOCK, PAGE=PAGE, mode=mode, layers=layers)
+    if not rt.value: return ("create refused",), what
+    n = int(rng.integers(1, 7)); wild = rng.random() < 0.4
+    keep, items, expected, outputs = [], (AttentionBatchItem * n)(), [], []
+    ref_pages = []
+    scale = 1.0 / np.sqrt(D)
+    cases = []
+    for i in range(n):
+        pages = int(rng.integers(0, 11)); tail = int(rng.integers(0, PAGE))
+        if pages + tail == 0: tail = 1
+        window = 0
+        qdt = [torch.float32, torch.float16, torch.bfloat16][int(rng.integers(0, 3))]; odt = [torch.float32, torch.float16][int(rng.integers(0, 2))]
+        cases.append((pages, tail, window, str(qdt), str(odt)))
+        descs = (PageDescriptor * max(pages, 1))(); descs2 = (PageDescriptor * max(pages, 1))(); ks, vs = [], []
+        for pg in range(pages):
+            (descs[pg], descs2[pg]), k, v = _runtime_int4_page_pair(rng, PAGE, pg * PAGE, keep, HKV, D, BLOCK, wild); ks.append(k); vs.append(v)
+        tk = rng.standard_normal((tail, HKV, D)).astype(np.float32); tv = rng.standard_normal((tail, HKV, D)).astype(np.float32)
+        ks.append(tk); vs.append(tv)
+        k_all, v_all = np.concatenate(ks), np.concatenate(vs)
+        qpos = pages * PAGE + tail - 1
+        q = torch.from_numpy(rng.standard_normal((HQ, D)).astype(np.float32)).to(qdt).cuda()
+        out = torch.zeros((HQ, D), dtype=odt, device="cuda")
+        d_desc = torch.from_numpy(np.frombuffer(bytes(descs), dtype=np.uint8).copy()).cuda()
+        d_desc2 = torch.from_numpy(np.frombuffer(bytes(descs2), dtype=np.uint8).copy()).cuda(); keep.append(d_desc2); ref_pages.append(d_desc2.data_ptr() if pages else None)
+        d_tk, d_tv = torch.from_numpy(np.ascontiguousarray(tk)).cuda(), torch.from_numpy(np.ascontiguousarray(tv)).cuda()
+        keep += [q, out, d_desc, d_tk, d_tv]
+        it = items[i]
+        it.sequence_id, it.layer = 100 + i, int(rng.integers(0, layers))
+        esz = q.element_size()
+        it.query = TensorView(q.data_ptr(), {torch.float16: 1, torch.bfloat16: 2, torch.float32: 3}[qdt], 1, HQ, D, HQ * D * esz, D * esz, esz, 0)
+        it.output, it.output_type = out.data_ptr(), {torch.float16: 1, torch.float32: 3}[odt]
+        osz = out.element_size()
+        it.output_token_stride_bytes, it.output_head_stride_bytes, it.output_element_stride_bytes = HQ * D * osz, D * osz, osz
+        it.query_token_begin, it.softmax_scale, it.causal_window = qpos, scale, window
+        it.sealed_pages, it.sealed_page_count = (d_desc.data_ptr() if pages else None), pages
+        it.active_keys, it.active_values = (d_tk.data_ptr() if tail else None), (d_tv.data_ptr() if tail else None)
+        it.active_token_begin, it.active_token_count = pages * PAGE, tail
+        first = 0 if window == 0 else max(0, qpos + 1 - window)
+        qf = q.float().cpu().numpy(); exp = np.zeros((HQ, D))
+        for h in range(HQ):
+            kv = h // G
+            s = (k_all[first:qpos + 1, kv].astype(np.float64) @ qf[h].astype(np.float64)) * scale
+            w = np.exp(s - s.max()); exp[h] = (w[:, None] * v_all[first:qpos + 1, kv]).sum(0) / w.sum()
+        expected.append(exp); outputs.append(out)
+    what["cases"] = cases; what["wild"] = wild
+    rc = lib.cf_attention_execute_async(rt, items, n, None)
+    if rc != 0: return ("execute", lib.cf_attention_last_error(rt)), what
+    torch.cuda.synchronize()
+    mine_out = [o.float().cpu().numpy().copy() for o in outputs]
+    for o in outputs: o.zero_()
+    rt2 = C.c_void_p(ref.cf_attention_runtime_create(C.byref(cfg)))
+    if not rt2.value: return ("reference create refused",), what
+    if D % BLOCK: return None, what      # the reference's kernel indexes scales per head; only whole blocks per head compare
+    items2 = (AttentionBatchItem * n)()
+    for i in range(n):
+        C.memmove(C.byref(items2[i]), C.byref(items[i]), C.sizeof(AttentionBatchItem)); items2[i].sealed_pages = ref_pages[i]
+    rc2 = ref.cf_attention_execute_async(rt2, items2, n, None)
+    torch.cuda.synchronize()
+    if rc2 != 0: return ("reference execute", rc2), what
+    for i, (a, o) in enumerate(zip(mine_out, outputs)):
+        r = o.float().cpu().numpy()
+        tol = 2e-3 if o.dtype == torch.float16 else 2e-5
+        e = np.abs(a - r).max() / (np.abs(r).max() + 1e-30)
+        if e > tol: return ("differs from the reference kernel", i, float(e)), what
+    ref.cf_attention_runtime_destroy(rt2, None)
+    for o, a in zip(outputs, mine_out): o.copy_(torch.from_numpy(a).to(o.dtype))
+    for i, (out, exp) in enumerate(zip(outputs, expected)):
+        got = out.float().cpu().numpy()
+        tol = 2e-3 if out.dtype == torch.float16 else 2e-4
+        e = np.abs(got - exp).max() / (np.abs(exp).max() + 1e-30)
+        if not np.isfinite(got).all() or e > tol: return ("item", i, float(e)), what
+    c = AttentionCounters(); lib.cf_attention_get_counters(rt, C.byref(c))
+    if c.cuda_errors != 0: return ("cuda errors",), what
+    lib.cf_attention_runtime_destroy(rt, None)
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 30, 15))
+def test_decode_runtime_beside_the_references_own_kernel(native, oracle, first):
+    """cf_attention_execute_async here and in the reference (src/cuda/production_attention.cu compiled into oracle/_ref) on
+    the same random batches, no window, query at the last token. The reference's kernel reads a nibble as two's
+    complement while its seal engine writes value + 8; it is therefore given the same values re-encoded, and the two
+    libraries must then agree to 2e-5 of the output's scale (2e-3 for fp16 outputs). This library reads the pages the
+    way the seal engine writes them."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's decode runtime (oracle/_ref)")
+    for seed in range(9600 + first, 9600 + first + 15):
+        bad, what = _runtime_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
