@@ -30,12 +30,13 @@ struct LayerHost {
     uint32_t state = CF_SEAL_ACTIVE_FILLING;
     uint64_t generation = 0;
     bool calibrated = false;
+    uint32_t descriptor_capacity = 0;              // pages the reference's descriptor table would hold (0, 4, 8, 16, ...)
     std::vector<uint32_t> page_ids;                // tile index -> page id
     uint32_t dev_sealed = 0xffffffffu, dev_tail = 0xffffffffu;
 };
 
 // What a seal reports back to the ABI front that called it.
-struct SealReport { uint64_t values = 0, bytes_written = 0; bool nonfinite = false; };
+struct SealReport { uint64_t values = 0, bytes_written = 0; bool nonfinite = false, table_grew = false; };
 
 struct Core {
     static constexpr uint32_t kMaxQueries = 4096;
@@ -157,13 +158,10 @@ SealReport core_seal_page(Core &c, uint32_t layer, cudaStream_t s, Inject inject
     const uint32_t first_tile = L.sealed_tokens / c.tile;
     L.state = CF_SEAL_VALIDATING;
     inject(CF_SEAL_FAULT_FINITE_VALIDATION);
-    L.state = CF_SEAL_QUANTIZING;
-    inject(CF_SEAL_FAULT_SCALE_ALLOC);
     // room: arena by the worst-case record size, directory by page count, page table by tile index
     c.arena.ensure((c.sealed_records + static_cast<uint64_t>(n) * c.cfg.kv_heads) * c.max_record_bytes() + 4096, s);
     c.page_dir.ensure(static_cast<size_t>(c.next_page_id + n + 1) * c.cfg.kv_heads, s);
     if (first_tile + n > c.stride) {
-        inject(CF_SEAL_FAULT_PAGE_TABLE_GROW);
         uint32_t wider = c.stride;
         while (first_tile + n > wider) wider *= 2;
         Buffer<uint32_t> fresh;
@@ -212,12 +210,10 @@ SealReport core_seal_page(Core &c, uint32_t layer, cudaStream_t s, Inject inject
     cuda_check(cudaMemcpyAsync(&cursor_before, c.cursor.ptr, sizeof cursor_before, cudaMemcpyDeviceToHost, s), "read cursor");
     c.sealed_records += static_cast<uint64_t>(n) * c.cfg.kv_heads;  // arena room is budgeted per launch, kept or not
     if (cf_b200_seal_pages_async(&d, s) != CF_OK) throw std::runtime_error("seal launch rejected");
-    inject(CF_SEAL_FAULT_QUANTIZE_LAUNCH);
-    L.state = CF_SEAL_PACKING;
-    inject(CF_SEAL_FAULT_PAYLOAD_ALLOC);
-    inject(CF_SEAL_FAULT_PACK_LAUNCH);
-    // the reference learns about NaN / Inf through a synchronisation at this point (device_kv_seal_attention.cu:265);
-    // so does this front: the device status word and the arena cursor come back together
+    // The reference learns about NaN / Inf through a synchronisation right after its finite scan, before any later
+    // fault point (device_kv_seal_attention.cu:262-268); so does this front: the device status word and the arena cursor
+    // of the one fused launch come back together, and a page that is not finite is refused whatever fault is armed
+    // beyond FINITE_VALIDATION.
     uint32_t status = 0;
     unsigned long long cursor_after = 0;
     cuda_check(cudaMemcpyAsync(&status, c.status.ptr, 4, cudaMemcpyDeviceToHost, s), "read status");
@@ -234,9 +230,25 @@ SealReport core_seal_page(Core &c, uint32_t layer, cudaStream_t s, Inject inject
         report.nonfinite = (status & CF_B200_DEVSTAT_NONFINITE) != 0;
         throw std::runtime_error(report.nonfinite ? "active page contains NaN or Inf" : "arena is full");
     }
-    try {
+    try {   // the later fault points, in the reference's order (:270-312)
+        L.state = CF_SEAL_QUANTIZING;
+        inject(CF_SEAL_FAULT_SCALE_ALLOC);
+        inject(CF_SEAL_FAULT_QUANTIZE_LAUNCH);
+        L.state = CF_SEAL_PACKING;
+        inject(CF_SEAL_FAULT_PAYLOAD_ALLOC);
+        inject(CF_SEAL_FAULT_PACK_LAUNCH);
         inject(CF_SEAL_FAULT_DESCRIPTOR_VALIDATE);
         L.state = CF_SEAL_PUBLISHING;
+        // PAGE_TABLE_GROW fires where the reference's descriptor table would grow: at a layer's 1st, 5th, 9th, 17th ...
+        // page (capacity 0 -> 4 -> 8 -> 16 ..., :300-307); a growth that happened stays even if a later point aborts
+        const uint32_t needed = L.sealed_tokens / c.cfg.page_size + 1u;
+        if (needed > L.descriptor_capacity) {
+            inject(CF_SEAL_FAULT_PAGE_TABLE_GROW);
+            uint32_t next = std::max<uint32_t>(4u, L.descriptor_capacity ? L.descriptor_capacity * 2u : 4u);
+            while (next < needed) next *= 2u;
+            L.descriptor_capacity = next;
+            report.table_grew = true;
+        }
         inject(CF_SEAL_FAULT_ACTIVE_REPLACEMENT);
         inject(CF_SEAL_FAULT_DESCRIPTOR_PUBLISH);
     } catch (...) {
@@ -525,7 +537,11 @@ extern "C" int cf_device_seal_stage_active_page(cf_device_seal_engine *e, uint32
         kv.data = k;
         vv.data = v;
         LayerHost &L = e->core.layers[layer];
-        if (token_begin != L.sealed_tokens)  // sealed tiles carry no position of their own: history is 0 .. sealed
+        // The reference stages a page at any position (:233-241). Sealed tiles carry no position of their own here, so a
+        // layer's history is contiguous from the position of its first page: a layer without sealed pages takes any
+        // position, one with sealed pages only the next one.
+        if (L.sealed_tokens == 0) L.base = token_begin;
+        else if (token_begin != L.base + L.sealed_tokens)
             throw std::runtime_error("active page must continue the sealed history of the layer");
         core_copy_rows(e->core, layer, kv, vv, 0, static_cast<cudaStream_t>(stream));
         L.active_begin = token_begin;
@@ -552,25 +568,19 @@ extern "C" int cf_device_seal_full_page_async(cf_device_seal_engine *e, uint32_t
         return -1;
     }
     try {
-        bool reached_quantise = false, reached_pack = false;
+        // One launch does what the reference splits over finite_scan, quantize and pack launches; the counters are booked
+        // where the reference books them, so an attempt that a later fault point aborts still counts the work it passed
+        // (device_kv_seal_attention.cu:262, 275, 284, 298).
+        const uint64_t values = 2ull * e->core.page_values();
         const SealReport r = core_seal_page(e->core, layer, static_cast<cudaStream_t>(stream), [&](uint32_t point) {
-            if (point == CF_SEAL_FAULT_QUANTIZE_LAUNCH) reached_quantise = true;
-            if (point == CF_SEAL_FAULT_PACK_LAUNCH) reached_pack = true;
-            if (e->fault == point) {
-                if (reached_quantise) { n.finite_validation_launches++; n.quantization_launches++; }
-                if (reached_pack) n.packing_launches++;
-                throw std::runtime_error("injected transactional seal failure");
-            }
+            if (point == CF_SEAL_FAULT_FINITE_VALIDATION) { n.finite_validation_launches++; n.values_scanned += values; }
+            if (point == CF_SEAL_FAULT_QUANTIZE_LAUNCH) { n.quantization_launches++; n.values_quantized += values; }
+            if (point == CF_SEAL_FAULT_PACK_LAUNCH) { n.packing_launches++; n.symbols_packed += values; }
+            if (point == CF_SEAL_FAULT_DESCRIPTOR_VALIDATE) n.descriptor_validations++;
+            if (e->fault == point) throw std::runtime_error("injected transactional seal failure");
         });
-        // one launch does what the reference splits over finite_scan, quantize and pack launches
-        n.finite_validation_launches++;
-        n.values_scanned += r.values;
-        n.quantization_launches++;
-        n.values_quantized += r.values;
-        n.packing_launches++;
-        n.symbols_packed += r.values;
+        if (r.table_grew) n.page_table_reallocations++;
         n.payload_bytes_written += r.bytes_written;
-        n.descriptor_validations++;
         n.descriptor_publications++;
         n.page_table_generation = L.generation;
         n.seal_successes++;
@@ -624,7 +634,9 @@ extern "C" int cf_device_seal_attention_async(cf_device_seal_engine *e, uint32_t
             c.o_dense.ensure(count, s);
             out = c.o_dense.ptr;
         }
-        core_attention(c, layer, q, q_type, out, query->token_count, query_begin, softmax_scale, window, s);
+        const uint32_t first_position = c.layers[layer].base;
+        if (query_begin < first_position) throw std::runtime_error("query position lies before the layer's first token");
+        core_attention(c, layer, q, q_type, out, query->token_count, query_begin - first_position, softmax_scale, window, s);
         if (!out_dense) {
             dense_to_view_kernel<<<blocks, threads, 0, s>>>(out, output, output_type, query->token_count, query->head_count,
                                                             query->head_dim, ots, ohs, oes);

@@ -5,7 +5,13 @@
  * Kept from the reference: opaque handles, int 0 / -1 returns with a last_error string owned by the handle, exceptions
  * never cross the boundary, handles are created without touching CUDA (device memory is taken on first use), the ten
  * host-side fault points and the seal state machine: a failed seal leaves the active page intact, the page table
- * generation unchanged and the layer in CF_SEAL_ACTIVE_FULL (src/cuda/device_kv_seal_attention.cu:328-333).
+ * generation unchanged and the layer in CF_SEAL_ACTIVE_FULL (src/cuda/device_kv_seal_attention.cu:328-333). The fault
+ * points fire in the reference's order: a page with NaN / Inf is refused ahead of every point after FINITE_VALIDATION,
+ * PAGE_TABLE_GROW fires at a layer's 1st, 5th, 9th, 17th ... page (where the reference's descriptor table grows), an
+ * armed fault stays armed, and an aborted attempt books the scan / quantise / pack work it got past, as the reference
+ * does. tests/test_gpu_random_cases.py runs this engine beside the reference's own (compiled from its source): same
+ * status for every call, same state after it, equal counters. A layer without sealed pages is staged at any
+ * position; with sealed pages only at the next one (the reference takes any, and would publish pages with gaps).
  * Different: pages are int8 + entropy-coded format-v1 records sealed in ONE launch (the reference: int4 nibbles,
  * six launches); a page of page_size tokens is stored as page_size / T records of T tokens (T * head_dim <= 4096;
  * T = 16 at head_dim 128, 96, 64 and 32 with pages of a multiple of 16 tokens, where the lane-per-block attention

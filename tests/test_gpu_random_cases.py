@@ -1435,3 +1435,79 @@ def test_decode_runtime_beside_the_references_own_kernel(native, oracle, first):
     for seed in range(9600 + first, 9600 + first + 15):
         bad, what = _runtime_side_by_side(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the seal engine beside the reference's own -----------------------------------------------------------------------
+SEAL_COUNTERS_COMPARED = ("seal_attempts", "seal_successes", "seal_failures", "invalid_pages_rejected", "values_quantized", "descriptor_publications",
+        "page_table_generation", "compressed_attention_launches", "sealed_pages_consumed", "cuda_errors")
+
+
+def _seal_engine_side_by_side(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import DeviceSealConfig, DeviceSealCounters
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_device()]
+    for l in libs: l.cf_device_seal_create.restype = C.c_void_p; l.cf_device_seal_last_error.restype = C.c_char_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4])); group = int(rng.choice([1, 2, 4])); hq = hkv * group
+    d = int(rng.choice([64, 128])); page = int(rng.choice([16, 32, 64])); block = int(rng.choice([32, 64]))
+    cfg = DeviceSealConfig(layers, hkv, hq, d, page, group, block, 0)
+    es = [C.c_void_p(l.cf_device_seal_create(C.byref(cfg))) for l in libs]
+    what = dict(seed=seed, layers=layers, heads=(hq, hkv), d=d, page=page, block=block)
+    if not es[0].value or not es[1].value: return ("create", bool(es[0].value), bool(es[1].value)), what
+    log = []
+    def both(name, *args):
+        r = tuple(getattr(l, name)(e, *args) for l, e in zip(libs, es)); log.append((name, r)); return r
+    def states(layer):
+        out = []
+        for l, e in zip(libs, es):
+            st = C.c_uint32(99); l.cf_device_seal_get_state(e, layer, C.byref(st)); out.append(st.value)
+        return tuple(out)
+    sealed = [0] * layers
+    base = {}
+    rows = {}
+    for step in range(int(rng.integers(10, 40))):
+        layer = int(rng.integers(0, layers + 1))    # one past the last: an invalid layer
+        op = ["stage", "stage", "seal", "seal", "fault", "attend", "stage_bad", "clear"][int(rng.integers(0, 8))]
+        if op in ("stage", "stage_bad"):
+            count = page if rng.random() < 0.6 else int(rng.integers(0, page + 2))
+            have = sealed[min(layer, layers - 1)]
+            begin = base.get(min(layer, layers - 1), 0) + have if (op == "stage" or have or rng.random() < 0.5) else int(rng.integers(0, 200))
+            if not have: base[min(layer, layers - 1)] = begin
+            k = rng.standard_normal((max(count, 1), hkv, d)).astype(np.float32); v = rng.standard_normal((max(count, 1), hkv, d)).astype(np.float32)
+            if rng.random() < 0.1: k[int(rng.integers(0, max(count, 1))), 0, 0] = np.nan
+            dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(); rows[step] = (dk, dv)
+            r = both("cf_device_seal_stage_active_page", layer, begin, C.c_void_p(dk.data_ptr()), C.c_void_p(dv.data_ptr()), count, None)
+            log[-1] = log[-1] + (("layer", layer, "begin", begin, "count", count, "sealed", sealed),)
+        elif op == "seal":
+            r = both("cf_device_seal_full_page_async", layer, None)
+            if r == (0, 0) and layer < layers: sealed[layer] += page
+        elif op == "fault":
+            fv = int(rng.integers(0, 12)); r = both("cf_device_seal_set_fault", fv); log[-1] = log[-1] + (fv,)
+        elif op == "clear":
+            if rng.random() < 0.7: continue
+            r = both("cf_device_seal_clear_async", None); sealed = [0] * layers; base = {}
+        else:
+            continue
+        torch.cuda.synchronize()
+        if r[0] != r[1]: return ("status", log[-6:]), what
+        if layer < layers and states(layer)[0] != states(layer)[1]: return ("state", states(layer), log[-6:]), what
+    ka, kb = DeviceSealCounters(), DeviceSealCounters()
+    libs[0].cf_device_seal_get_counters(es[0], C.byref(ka)); libs[1].cf_device_seal_get_counters(es[1], C.byref(kb))
+    diff = {n: (int(getattr(ka, n)), int(getattr(kb, n))) for n in SEAL_COUNTERS_COMPARED if getattr(ka, n) != getattr(kb, n)}
+    for l, e in zip(libs, es): l.cf_device_seal_destroy(e, None)
+    return (("counters", diff, log[-4:]), what) if diff else (None, what)
+
+
+@pytest.mark.parametrize("first", range(0, 40, 20))
+def test_seal_engine_answers_like_the_references_own(native, oracle, first):
+    """cf_device_seal_* here and in the reference (src/cuda/device_kv_seal_attention.cu compiled into oracle/_ref): random
+    stage / seal / set_fault / clear calls, valid and invalid (layers that do not exist, zero or too many rows, NaN
+    pages, every fault point, faults left armed). Every call returns the same status, the layer is in the same state
+    after it, and ten counters that mean the same in both are equal at the end. Staging stays where the two can be
+    compared: a layer that has sealed pages is staged at its next position (this library's history is contiguous)."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's seal engine (oracle/_ref)")
+    for seed in range(first, first + 20):
+        bad, what = _seal_engine_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
