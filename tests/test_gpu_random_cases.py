@@ -1511,3 +1511,132 @@ def test_seal_engine_answers_like_the_references_own(native, oracle, first):
     for seed in range(first, first + 20):
         bad, what = _seal_engine_side_by_side(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the sequence resolver beside the reference's own -----------------------------------------------------------------
+def _resolver_counters_compared():
+    from compat_types import MsCounters
+    return [n for n, _ in MsCounters._fields_ if n not in ("descriptor_table_rebuilds", "sequence_attention_launches", "descriptor_tables_built")]
+
+
+def _resolver_side_by_side(native, oracle, seed, steps):
+    import ctypes as C
+    import torch
+    from compat_types import MsBatchItem, MsConfig, MsCounters, MsPublication, PageDescriptor, TensorView
+    from test_gpu_ms_resolver import _int4_page
+    NAMES = _resolver_counters_compared()
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_device()]
+    for l in libs: l.cf_ms_cuda_create.restype = C.c_void_p; l.cf_ms_cuda_last_error.restype = C.c_char_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4])); group = int(rng.choice([1, 2, 4])); hq = hkv * group
+    d = int(rng.choice([64, 128])); page = int(rng.choice([16, 32, 64])); block = int(rng.choice([16, 32, 64]))
+    cfg = MsConfig(layers, hkv, hq, d, page, group, 0)
+    rs = [C.c_void_p(l.cf_ms_cuda_create(C.byref(cfg))) for l in libs]
+    what = dict(seed=seed, layers=layers, heads=(hq, hkv), d=d, page=page, block=block)
+    if not rs[0].value or not rs[1].value: return ("create", bool(rs[0].value), bool(rs[1].value)), what
+    keep = []; log = []
+    def both(name, *args):
+        r = tuple(getattr(l, name)(x, *args) for l, x in zip(libs, rs)); log.append((name, r)); return r
+    seqs = {}   # id -> per layer dict(sealed tokens, closed, tail rows, dense rows k / v, cancelled flag at sequence level)
+    cancelled = set(); next_id = 1; scale = 1.0 / np.sqrt(d)
+    def new_layer(): return dict(k=np.zeros((0, hkv, d), np.float32), v=np.zeros((0, hkv, d), np.float32), closed=False, tk=np.zeros((0, hkv, d), np.float32), tv=np.zeros((0, hkv, d), np.float32))
+    for step in range(steps):
+        live = list(seqs)
+        def pick():     # a live sequence, or now and then an id that may not exist; never a cancelled one, whose history the
+            while True:  # model no longer follows (this library would refuse a page that does not continue it)
+                s = int(live[int(rng.integers(0, len(live)))]) if live and rng.random() < 0.9 else int(rng.integers(1, 12))
+                if s not in cancelled: return s
+        op = ["create", "publish", "publish", "publish", "stage", "stage", "copy", "execute", "execute", "remove", "reclaim", "cancel", "audit"][int(rng.integers(0, 13))]
+        if op == "create":
+            s = int(rng.integers(1, 12))
+            if s in cancelled: continue
+            r = both("cf_ms_cuda_sequence_create", C.c_int64(s)); log[-1] += (s,)
+            if r == (0, 0): seqs[s] = [new_layer() for _ in range(layers)]
+        elif op == "publish":
+            s = pick(); layer = int(rng.integers(0, layers + 1)); L = seqs[s][layer] if s in seqs and layer < layers else None
+            if L is not None and (L["closed"] or L["tk"].shape[0] or L["k"].shape[0] > 300): continue
+            tokens = page if rng.random() < 0.8 else int(rng.integers(1, page + 1))
+            if (tokens * hkv * d) % block: tokens = page
+            (kp, ks, kd), (vp, vs, vd) = _int4_page(rng, tokens, hkv, d, block)
+            t = [torch.from_numpy(x).cuda() for x in (kp, vp, ks, vs)]; keep.append(t)
+            pub = MsPublication(); pub.sequence_id, pub.layer = s, layer
+            begin = L["k"].shape[0] if L is not None else 0
+            pub.descriptor = PageDescriptor(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(), begin, tokens, hkv, d, block, ks.size, kp.size, vp.size, kp.size + vp.size + 8 * ks.size, 1)
+            if rng.random() < 0.05: pub.descriptor.key_scales = None
+            pub.resident_bytes, pub.seal_generation = kp.size + vp.size + 8 * ks.size, 1
+            r = both("cf_ms_cuda_publish_page_async", C.byref(pub), None); log[-1] += (s, layer, tokens)
+            if r == (0, 0) and L is not None:
+                L["k"] = np.concatenate([L["k"], kd]); L["v"] = np.concatenate([L["v"], vd]); L["closed"] = tokens < page
+        elif op == "stage":
+            s = pick(); layer = int(rng.integers(0, layers + 1)); L = seqs[s][layer] if s in seqs and layer < layers else None
+            count = int(rng.integers(0, page + 2))
+            tk = rng.standard_normal((max(count, 1), hkv, d)).astype(np.float32); tv = rng.standard_normal((max(count, 1), hkv, d)).astype(np.float32)
+            dk, dv = torch.from_numpy(tk).cuda(), torch.from_numpy(tv).cuda(); keep.append((dk, dv))
+            begin = L["k"].shape[0] if L is not None else 0
+            r = both("cf_ms_cuda_stage_active_async", C.c_int64(s), layer, begin, C.c_void_p(dk.data_ptr()), C.c_void_p(dv.data_ptr()), count, None); log[-1] += (s, layer, count)
+            if r == (0, 0) and L is not None: L["tk"], L["tv"] = tk[:count], tv[:count]
+        elif op == "copy":
+            src = pick(); dst = next_id + 100; next_id += 1
+            r = both("cf_ms_cuda_copy_sequence_async", C.c_int64(src), C.c_int64(dst), None); log[-1] += (src, dst)
+            if r == (0, 0) and src in seqs: seqs[dst] = [dict(k=L["k"].copy(), v=L["v"].copy(), closed=L["closed"], tk=L["tk"].copy(), tv=L["tv"].copy()) for L in seqs[src]]
+        elif op == "execute":
+            cand = [(s, layer) for s in live for layer in range(layers) if seqs[s][layer]["k"].shape[0] + seqs[s][layer]["tk"].shape[0] > 0]
+            if not cand: continue
+            n = int(rng.integers(1, min(4, len(cand)) + 1)); picks = [cand[i] for i in rng.choice(len(cand), n, replace=False)]
+            if rng.random() < 0.1: picks[0] = (int(rng.integers(20, 30)), 0)      # an unknown sequence
+            outs = []
+            for lib, x in zip(libs, rs):
+                rng2 = np.random.default_rng(seed * 1000 + step)
+                items = (MsBatchItem * n)(); ods = []
+                for i, (s, layer) in enumerate(picks):
+                    L = seqs[s][layer] if s in seqs else None
+                    tot = (L["k"].shape[0] + L["tk"].shape[0]) if L is not None else 1
+                    nq = int(rng2.integers(1, min(3, tot) + 1)); begin = tot - nq
+                    q = rng2.standard_normal((nq, hq, d)).astype(np.float32)
+                    qd = torch.from_numpy(q).cuda(); od = torch.zeros((nq, hq, d), dtype=torch.float32, device="cuda"); keep.append((qd, od)); ods.append(od)
+                    items[i].sequence_id, items[i].layer = s, layer
+                    items[i].query = TensorView(qd.data_ptr(), 3, nq, hq, d, hq * d * 4, d * 4, 4, 0)
+                    items[i].output, items[i].output_type = od.data_ptr(), 3
+                    items[i].output_token_stride_bytes, items[i].output_head_stride_bytes, items[i].output_element_stride_bytes = hq * d * 4, d * 4, 4
+                    items[i].query_token_begin, items[i].softmax_scale, items[i].causal_window = begin, scale, 0
+                rc = lib.cf_ms_cuda_execute_batch_async(x, items, n, None); torch.cuda.synchronize()
+                outs.append((rc, [o.cpu().numpy() for o in ods]))
+            log.append(("execute", (outs[0][0], outs[1][0]), picks))
+            if outs[0][0] != outs[1][0]: return ("status", log[-6:]), what
+            if outs[0][0] == 0:
+                for a, b in zip(outs[0][1], outs[1][1]):
+                    e = np.abs(a - b).max() / (np.abs(b).max() + 1e-30)
+                    if not np.isfinite(a).all() or e > 5e-2: return ("attention", float(e), log[-3:]), what
+            continue
+        elif op == "remove":
+            s = pick(); r = both("cf_ms_cuda_sequence_remove_async", C.c_int64(s), None); log[-1] += (s,)
+            if r == (0, 0): seqs.pop(s, None)
+        elif op == "cancel":
+            if rng.random() < 0.7: continue
+            s = pick(); r = both("cf_ms_cuda_cancel_sequence_async", C.c_int64(s), None); log[-1] += (s,)
+            if r == (0, 0): seqs.pop(s, None); cancelled.add(s)      # not dispatchable any more: leave it alone
+        elif op == "reclaim":
+            torch.cuda.synchronize(); r = both("cf_ms_cuda_reclaim_async", None)
+        else:
+            r = both("cf_ms_cuda_audit")
+        if r[0] != r[1]: return ("status", log[-6:], libs[0].cf_ms_cuda_last_error(rs[0]), libs[1].cf_ms_cuda_last_error(rs[1])), what
+    ka, kb = MsCounters(), MsCounters()
+    libs[0].cf_ms_cuda_get_counters(rs[0], C.byref(ka)); libs[1].cf_ms_cuda_get_counters(rs[1], C.byref(kb))
+    diff = {n: (int(getattr(ka, n)), int(getattr(kb, n))) for n in NAMES if getattr(ka, n) != getattr(kb, n)}
+    for l, x in zip(libs, rs): l.cf_ms_cuda_destroy(x, None)
+    return (("counters", diff), what) if diff else (None, what)
+
+
+@pytest.mark.parametrize("first", range(0, 20, 10))
+def test_sequence_resolver_answers_like_the_references_own(native, oracle, first):
+    """cf_ms_cuda_* here and in the reference (src/cuda/multisequence_cuda_resolver.cu compiled into oracle/_ref): random
+    create / publish / stage / copy / execute / remove / cancel / reclaim / audit calls, valid and invalid (unknown
+    sequences, layers that do not exist, incomplete descriptors, zero or too many rows). Every call returns the same
+    status; every counter but the three that describe the reference's descriptor tables and its launch per item is
+    equal at the end; attention agrees to 5 % of the output's scale (the reference reads the int4 pages as they are,
+    this library its int8 transcoding of them). Pages are published in order, which is what this library takes."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's resolver (oracle/_ref)")
+    for seed in range(first, first + 10):
+        bad, what = _resolver_side_by_side(native, oracle, seed, 70)
+        assert bad is None, (bad, what)
