@@ -1640,3 +1640,117 @@ def test_sequence_resolver_answers_like_the_references_own(native, oracle, first
     for seed in range(first, first + 10):
         bad, what = _resolver_side_by_side(native, oracle, seed, 70)
         assert bad is None, (bad, what)
+
+
+# ---- the llama-server runtime beside the reference's own --------------------------------------------------------------
+def _server_side_by_side(native, oracle, seed, steps):
+    import ctypes as C
+    import torch
+    from compat_types import LlamaServerBatch, LlamaServerConfig, LlamaServerStats, MsBatchItem, TensorView
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_device()]
+    for l in libs: l.cf_llama_server_runtime_create.restype = C.c_void_p; l.cf_llama_server_last_error.restype = C.c_char_p
+    LAYERS = int(rng.integers(1, 3)); HKV = int(rng.choice([1, 2])); G = int(rng.choice([1, 4])); HQ = HKV * G; D = int(rng.choice([64, 128])); PAGE = int(rng.choice([16, 32]))
+    cfg = LlamaServerConfig(LAYERS, HQ, HKV, D, PAGE, 64, 4096, G, 0, 1, None, b"76f46ad2", b"0" * 64)
+    rs = [C.c_void_p(l.cf_llama_server_runtime_create(C.byref(cfg))) for l in libs]
+    what = dict(seed=seed, layers=LAYERS, heads=(HQ, HKV), d=D, page=PAGE)
+    if not rs[0].value or not rs[1].value: return ("create", bool(rs[0].value), bool(rs[1].value)), what
+    i64 = C.c_int64; log = []; keep = []
+    def both(name, *args):
+        r = tuple(getattr(l, name)(x, *args) for l, x in zip(libs, rs)); log.append((name, r) + tuple(a.value if hasattr(a, "value") else a for a in args[:3])); return r
+    rows = {}     # (sequence, layer) -> (k, v) staged rows
+    live = set(); cancelled = set(); shut = False; scale = 1.0 / np.sqrt(D)
+    for step in range(steps):
+        ids = sorted(live) or [1]
+        pick = lambda: int(ids[int(rng.integers(0, len(ids)))]) if rng.random() < 0.9 else int(rng.integers(1, 9))
+        op = ["slot", "slot", "append", "append", "append", "execute", "execute", "copy", "reset", "cancel", "remove_range", "shift", "shutdown"][int(rng.integers(0, 13))]
+        if op == "slot":
+            s = int(rng.integers(1, 9)); r = both("cf_llama_server_slot_create", i64(s))
+            if r == (0, 0): live.add(s)
+        elif op == "append":
+            s = pick(); layer = int(rng.integers(0, LAYERS + 1)); n = int(rng.integers(0, PAGE + 1))
+            if n == PAGE: n -= 1          # a full page is sealed here and stays staged in the reference
+            if (s, layer) in rows or s in cancelled: continue     # the reference restages, this library appends: one append per layer
+            k = rng.standard_normal((max(n, 1), HKV, D)).astype(np.float32); v = rng.standard_normal((max(n, 1), HKV, D)).astype(np.float32)
+            dk, dv = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(); keep.append((dk, dv))
+            r = both("cf_llama_server_append_layer_async", i64(s), layer, 0, C.c_void_p(dk.data_ptr()), C.c_void_p(dv.data_ptr()), n, None)
+            if r == (0, 0): rows[(s, layer)] = (k[:n], v[:n])
+        elif op == "execute":
+            cand = [key for key in rows if key[0] in live and key[0] not in cancelled]
+            if not cand and rng.random() < 0.8: continue
+            picks = [cand[i] for i in rng.choice(len(cand), int(rng.integers(1, min(3, len(cand)) + 1)), replace=False)] if cand else [(int(rng.integers(1, 9)), 0)]
+            if rng.random() < 0.1: picks.append((int(rng.integers(20, 30)), 0))
+            outs = []
+            for lib, x in zip(libs, rs):
+                rng2 = np.random.default_rng(seed * 977 + step)
+                items = (MsBatchItem * len(picks))(); ods = []
+                for i, (s, layer) in enumerate(picks):
+                    tot = rows[(s, layer)][0].shape[0] if (s, layer) in rows else 1
+                    q = rng2.standard_normal((1, HQ, D)).astype(np.float32); qd = torch.from_numpy(q).cuda(); od = torch.zeros((1, HQ, D), dtype=torch.float32, device="cuda"); keep.append((qd, od)); ods.append(od)
+                    items[i].sequence_id, items[i].layer = s, layer
+                    items[i].query = TensorView(qd.data_ptr(), 3, 1, HQ, D, HQ * D * 4, D * 4, 4, 0)
+                    items[i].output, items[i].output_type = od.data_ptr(), 3
+                    items[i].output_token_stride_bytes, items[i].output_head_stride_bytes, items[i].output_element_stride_bytes = HQ * D * 4, D * 4, 4
+                    items[i].query_token_begin, items[i].softmax_scale, items[i].causal_window = tot - 1, scale, 0
+                batch = LlamaServerBatch(None, 0, C.cast(items, C.c_void_p), len(picks))
+                rc = lib.cf_llama_server_execute_batch_async(x, C.byref(batch), None); torch.cuda.synchronize()
+                outs.append((rc, [o.cpu().numpy() for o in ods]))
+            log.append(("execute", (outs[0][0], outs[1][0]), picks))
+            if outs[0][0] != outs[1][0]: return ("status", log[-6:], libs[0].cf_llama_server_last_error(rs[0]), libs[1].cf_llama_server_last_error(rs[1])), what
+            if outs[0][0] == 0:
+                for a, b in zip(outs[0][1], outs[1][1]):
+                    e = np.abs(a - b).max() / (np.abs(b).max() + 1e-30)
+                    if not np.isfinite(a).all() or e > 2e-5: return ("attention", float(e), log[-3:]), what     # only unsealed fp32 rows here: the same numbers
+            continue
+        elif op == "copy":
+            s = pick(); t = int(rng.integers(30, 60))
+            r = both("cf_llama_server_sequence_copy_async", i64(s), i64(t), C.c_uint32(0), C.c_uint32(1 << 30), None)
+            if r == (0, 0):
+                live.add(t)
+                for layer in range(LAYERS):
+                    if (s, layer) in rows: rows[(t, layer)] = rows[(s, layer)]
+                if s in cancelled: cancelled.add(t) if False else None
+        elif op == "reset":
+            s = pick(); r = both("cf_llama_server_slot_reset_async", i64(s), None)
+            if r == (0, 0):
+                live.discard(s); cancelled.discard(s)
+                for layer in range(LAYERS): rows.pop((s, layer), None)
+        elif op == "cancel":
+            if rng.random() < 0.6: continue
+            s = pick(); r = both("cf_llama_server_cancel_async", i64(s), None)
+            if r == (0, 0): cancelled.add(s)
+        elif op == "remove_range":
+            s = pick()
+            if any((s, layer) in rows for layer in range(LAYERS)): continue    # host bookkeeping only in the reference: rows stay staged there
+            lo = int(rng.integers(0, 40)); r = both("cf_llama_server_sequence_remove_async", i64(s), i64(lo), i64(lo + int(rng.integers(0, 40))), None)
+        elif op == "shift":
+            s = pick()
+            if any((s, layer) in rows for layer in range(LAYERS)): continue
+            r = both("cf_llama_server_sequence_shift_async", i64(s), C.c_uint32(0), C.c_uint32(1 << 30), C.c_int32(int(rng.integers(0, 30))), None)
+        else:
+            if rng.random() < 0.85: continue
+            r = both("cf_llama_server_shutdown_async", None); shut = True; live.clear(); rows.clear()
+        if r[0] != r[1]: return ("status", log[-6:], libs[0].cf_llama_server_last_error(rs[0]), libs[1].cf_llama_server_last_error(rs[1])), what
+    if not shut:
+        r = both("cf_llama_server_shutdown_async", None)
+        if r[0] != r[1]: return ("shutdown", r), what
+    sa, sb = LlamaServerStats(), LlamaServerStats()
+    libs[0].cf_llama_server_get_stats(rs[0], C.byref(sa)); libs[1].cf_llama_server_get_stats(rs[1], C.byref(sb))
+    diff = {n: (int(getattr(sa, n)), int(getattr(sb, n))) for n, _ in LlamaServerStats._fields_ if getattr(sa, n) != getattr(sb, n)}
+    for l, x in zip(libs, rs): l.cf_llama_server_runtime_destroy(x, None)
+    return (("stats", diff), what) if diff else (None, what)
+
+
+@pytest.mark.parametrize("first", range(0, 16, 8))
+def test_llama_server_runtime_answers_like_the_references_own(native, oracle, first):
+    """cf_llama_server_* here and in the reference (src/llama_server_runtime.cpp over its host cache and resolver, compiled
+    into oracle/_ref): slots created, reset and cancelled, layers appended, sequences copied, ranges removed and shifted,
+    batches executed (unknown sequences too), shutdown. Same status for every call, equal statistics, and the same
+    attention to 2e-5 (the rows stay unsealed fp32 in both). The runs stay where the two mean the same: one append of
+    less than a page per layer (the reference restages a tail where this library appends to it and seals full pages),
+    ranges removed or shifted only on sequences without rows (host bookkeeping only in the reference)."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's llama-server runtime (oracle/_ref)")
+    for seed in range(first, first + 8):
+        bad, what = _server_side_by_side(native, oracle, seed, 60)
+        assert bad is None, (bad, what)
