@@ -1754,3 +1754,65 @@ def test_llama_server_runtime_answers_like_the_references_own(native, oracle, fi
     for seed in range(first, first + 8):
         bad, what = _server_side_by_side(native, oracle, seed, 60)
         assert bad is None, (bad, what)
+
+
+# ---- the tensor-view validator and the dataplane's appends beside the reference's own ---------------------------------
+def _random_tensor_views(rng, n):
+    """Tensor views with every field drawn from a few values, most of them invalid one way or another."""
+    from compat_types import TensorView
+    out = []
+    for _ in range(n):
+        t = int(rng.choice([0, 1, 2, 3, 4, 7])); tok = int(rng.choice([0, 1, 5, 64])); h = int(rng.choice([0, 1, 2, 8])); d = int(rng.choice([0, 1, 64, 128, 129]))
+        es = int(rng.choice([0, 1, 2, 4, 8])); hs = int(rng.choice([0, es * d, es * d + 16, 3])); ts = int(rng.choice([0, hs * h, hs * h + 32, 5]))
+        data = int(rng.choice([0, 0x7f0000001000, 0x7f0000001001, 0x7f0000001002, 0x7f0000001004]))
+        out.append(TensorView(data, t, tok, h, d, ts, hs, es, int(rng.choice([0, 0, 1]))))
+    return out
+
+
+def _dataplane_side_by_side(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import DeviceKvConfig, TensorView
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_device()]
+    for v in _random_tensor_views(rng, 400):
+        a, b = libs[0].cf_device_tensor_validate(C.byref(v)), libs[1].cf_device_tensor_validate(C.byref(v))
+        if a != b: return ("validate", a, b, [getattr(v, n) for n, _ in TensorView._fields_]), seed
+    for l in libs: l.cf_device_kv_create.restype = C.c_void_p
+    layers = int(rng.integers(1, 3)); hkv = int(rng.choice([1, 2, 4])); group = int(rng.choice([1, 4])); hq = hkv * group; d = int(rng.choice([64, 128])); page = int(rng.choice([16, 32]))
+    cfg = DeviceKvConfig(layers, hkv, hq, d, page, group, 0)
+    ps = [C.c_void_p(l.cf_device_kv_create(C.byref(cfg))) for l in libs]
+    if bool(ps[0].value) != bool(ps[1].value): return ("create",), seed
+    rows = torch.zeros((page, hkv, d), dtype=torch.float32, device="cuda")
+    count = [0] * layers; begin = [0] * layers; log = []
+    for step in range(40):
+        layer = int(rng.integers(0, layers + 1)); L = min(layer, layers - 1)
+        n = int(rng.integers(0, page + 2)); c = count[L]
+        if c + n == page: n += 1       # an exactly full page: the reference's seal is a stub that fails, this library seals
+        n = min(n, page)
+        if c + n == page: continue
+        where = begin[L] + c if (c or rng.random() < 0.6) else int(rng.integers(0, 90))
+        if rng.random() < 0.1: where += int(rng.integers(1, 4))
+        hv = hkv if rng.random() < 0.9 else hkv + 1
+        view = TensorView(rows.data_ptr(), 3, n, hv, d, hv * d * 4, d * 4, 4, 0)
+        r = tuple(l.cf_device_kv_append_async(p, layer, where, C.byref(view), C.byref(view), None) for l, p in zip(libs, ps))
+        log.append((layer, where, n, hv, "count", c, r))
+        if r[0] != r[1]: return ("append", log[-5:]), seed
+        if r == (0, 0) and layer < layers:
+            if c == 0: begin[L] = where
+            count[L] = c + n
+    for l, p in zip(libs, ps): l.cf_device_kv_destroy(p, None)
+    return None, seed
+
+
+@pytest.mark.parametrize("first", range(0, 20, 10))
+def test_tensor_validator_and_dataplane_appends_answer_like_the_references_own(native, oracle, first):
+    """cf_device_tensor_validate on 400 random views per run and cf_device_kv_append_async on random appends (layers that
+    do not exist, gaps, page-boundary crossings, wrong head counts, a first append anywhere), here and in the reference
+    (src/cuda/device_kv_dataplane.cu in oracle/_ref): the same answer for every call. No page is filled exactly: the
+    reference's seal is a stub that fails, this library seals."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's dataplane (oracle/_ref)")
+    for seed in range(first, first + 10):
+        bad, what = _dataplane_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
