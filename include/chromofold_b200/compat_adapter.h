@@ -19,7 +19,11 @@
  * are instead quantised to int8 with one fp16 scale per stream and entropy coded (format v1, sealed_page_format.h):
  * physically a page of page_size tokens is then page_size / T records of T tokens with T * head_dim <= 4096 (T = 16 at
  * head_dim 128, 96, 64 and 32 with pages of a multiple of 16 tokens: the record geometry of the lane-per-block
- * attention kernels, which take the fp32 queries of this ABI as binary16 + residue rows). Statistics are reported in the reference's units in both modes. */
+ * attention kernels, which take the fp32 queries of this ABI as binary16 + residue rows). Statistics are reported in the
+ * reference's units in both modes.
+ * tests/test_gpu_random_cases.py runs this adapter beside the reference's own, end to end (compiled from its sources):
+ * same status for every call, equal statistics, attention equal to 2e-4. Narrower in one point: rows appended right
+ * after a page was sealed must start at the next position (the reference takes any position there). */
 #ifndef CHROMOFOLD_B200_COMPAT_ADAPTER_H
 #define CHROMOFOLD_B200_COMPAT_ADAPTER_H
 

@@ -73,6 +73,14 @@ def ref_device():
     return C.CDLL(path) if os.path.exists(path) else None
 
 
+def ref_adapter():
+    """The reference's llama KV adapter with everything under it (integrations/llama.cpp/chromofold_kv_adapter.cpp,
+    src/runtime/compressed_kv_cache.cu, its quantiser and its paged-attention kernel), compiled for sm_100a (None when not
+    built)."""
+    path = os.path.join(HERE, "_ref", "libcfref_adapter.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
 def _p(a, t=None):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 

@@ -1816,3 +1816,97 @@ def test_tensor_validator_and_dataplane_appends_answer_like_the_references_own(n
     for seed in range(first, first + 10):
         bad, what = _dataplane_side_by_side(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the llama KV adapter beside the reference's own, end to end -------------------------------------------------------
+def _adapter_side_by_side(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import LlamaKvOptions, LlamaKvStats
+    from test_gpu_compat import _dev
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_adapter()]
+    for l in libs: l.cf_llama_kv_create.restype = C.c_void_p; l.cf_llama_kv_last_error.restype = C.c_char_p
+    hq, hkv = [(14, 2), (8, 8), (4, 2), (32, 8), (16, 2), (1, 1)][int(rng.integers(0, 6))]
+    head_dim = int(rng.choice([32, 64, 96, 128, 128])); page = int(rng.choice([16, 32, 64])); layers = int(rng.integers(1, 3))
+    o = LlamaKvOptions(); o.struct_size, o.backend = C.sizeof(o), 1
+    o.layer_count, o.kv_head_count, o.query_head_count, o.head_dim, o.page_size, o.gqa_group_size = layers, hkv, hq, head_dim, page, hq // hkv
+    o.kv_bits = int(rng.choice([0, 4, 8, 8]))
+    if rng.random() < 0.1: o.gqa_group_size += 1
+    what = dict(seed=seed, heads=(hq, hkv), d=head_dim, page=page, layers=layers, bits=int(o.kv_bits))
+    v = tuple(l.cf_llama_kv_options_validate(C.byref(o)) for l in libs)
+    if v[0] != v[1]: return ("validate", v), what
+    hs = [C.c_void_p(l.cf_llama_kv_create(C.byref(o))) for l in libs]
+    if bool(hs[0].value) != bool(hs[1].value): return ("create", bool(hs[0].value), bool(hs[1].value)), what
+    if not hs[0].value: return None, what
+    log = []
+    def both(name, *args):
+        r = tuple(getattr(l, name)(h, *args) for l, h in zip(libs, hs)); log.append((name, r)); return r
+    p = lambda x: np.ascontiguousarray(x).ctypes.data_as(C.c_void_p)
+    tokens = int(rng.integers(1, 4 * page + 10))
+    k = rng.standard_normal((layers, hkv, tokens, head_dim)).astype(np.float32) * float(10.0 ** rng.uniform(-2, 1))
+    vv = rng.standard_normal((layers, hkv, tokens, head_dim)).astype(np.float32) * float(10.0 ** rng.uniform(-3, 2))
+    cuts = sorted(set([0, tokens] + [int(x) for x in rng.integers(0, tokens + 1, int(rng.integers(0, 4)))]))
+    for layer in range(layers):
+        for b, e in zip(cuts[:-1], cuts[1:]):
+            for h in range(hkv):
+                begin = b if (rng.random() < 0.95 or b % page == 0) else b + 3       # now and then a gap inside a page: both must refuse
+                r = both("cf_llama_kv_append", layer, h, begin, p(k[layer, h, b:e]), p(vv[layer, h, b:e]), e - b, None); log[-1] += (layer, h, begin, e - b)
+                if r[0] != r[1]: return ("append", log[-4:], libs[0].cf_llama_kv_last_error(hs[0]), libs[1].cf_llama_kv_last_error(hs[1])), what
+                if r[0] != 0:    # the gap was refused: append the piece where it belongs
+                    r = both("cf_llama_kv_append", layer, h, b, p(k[layer, h, b:e]), p(vv[layer, h, b:e]), e - b, None)
+                    if r[0] != r[1]: return ("append after refusal", r), what
+                    if r[0] != 0:      # both refuse alike (a head that took rows at the wrong place keeps them): end of this run
+                        for l, h in zip(libs, hs): l.cf_llama_kv_destroy(h)
+                        return None, what
+    def stats():
+        out = []
+        for l, h in zip(libs, hs):
+            st = LlamaKvStats(); rc = l.cf_llama_kv_get_stats(h, C.byref(st)); out.append((rc,) + tuple(int(getattr(st, n)) for n in ("appended_tokens", "sealed_tokens", "sealed_pages", "active_tokens")))
+        return out
+    s = stats()
+    if s[0] != s[1]: return ("stats", s), what
+    for rounds in range(2):
+        nq = int(rng.integers(1, min(4, tokens) + 1)); window = int(rng.integers(1, tokens + 4)) if rng.random() < 0.5 else 0
+        q = rng.standard_normal((nq, hq, head_dim)).astype(np.float32); d_q = _dev(q)
+        layer = int(rng.integers(0, layers + 1)); outs = []
+        for l, h in zip(libs, hs):
+            out = torch.zeros((nq, hq, head_dim), dtype=torch.float32, device="cuda")
+            rc = l.cf_llama_kv_attention(h, layer, C.c_void_p(d_q.data_ptr()), C.c_void_p(out.data_ptr()), nq, hq, hq // hkv, tokens - nq, C.c_float(1.0 / np.sqrt(head_dim)), window, None)
+            torch.cuda.synchronize(); host = np.zeros((nq, hq, head_dim), np.float32)
+            rc2 = l.cf_llama_kv_attention_host(h, layer, p(q), p(host), nq, hq, hq // hkv, tokens - nq, C.c_float(1.0 / np.sqrt(head_dim)), window, None)
+            outs.append((rc, rc2, out.cpu().numpy(), host))
+        if (outs[0][0], outs[0][1]) != (outs[1][0], outs[1][1]): return ("attention status", outs[0][:2], outs[1][:2], layer, libs[1].cf_llama_kv_last_error(hs[1]), dict(nq=nq, window=window, tokens=tokens, cuts=cuts)), what
+        if outs[0][0] == 0:
+            for j in (2, 3):
+                e = np.abs(outs[0][j] - outs[1][j]).max() / (np.abs(outs[1][j]).max() + 1e-30)
+                if not np.isfinite(outs[0][j]).all() or e > 2e-4: return ("attention", j, float(e)), what
+        if rounds == 0 and rng.random() < 0.5:
+            r = both("cf_llama_kv_flush", None)
+            if r[0] != r[1]: return ("flush", r), what
+            s = stats()
+            if s[0] != s[1]: return ("stats after flush", s), what
+    for name, args in (("cf_llama_kv_seq_cp", (0, 1)), ("cf_llama_kv_seq_cp", (0, 0)), ("cf_llama_kv_seq_shift", (0, 0)), ("cf_llama_kv_seq_shift", (0, 1)), ("cf_llama_kv_seq_rm", (1,)), ("cf_llama_kv_seq_rm", (0,))):
+        if rng.random() < 0.5: continue
+        r = both(name, *args)
+        if r[0] != r[1]: return (name, args, r), what
+    s = stats()
+    if s[0] != s[1]: return ("stats at the end", s), what
+    for l, h in zip(libs, hs): l.cf_llama_kv_destroy(h)
+    return None, what
+
+
+@pytest.mark.parametrize("first", range(0, 24, 12))
+def test_llama_kv_adapter_answers_like_the_references_own(native, oracle, first, monkeypatch):
+    """cf_llama_kv_* here and in the reference, end to end (its adapter over its CompressedKvCache, quantiser and
+    paged-attention kernel, compiled into oracle/_ref): options (valid or not), appends in random pieces with a gap now
+    and then, statistics, device and host attention on one to three query rows with or without a window (layers that do
+    not exist too), flush, the sequence calls. Same status for every call, equal statistics, outputs equal to 2e-4 of
+    their scale. Gaps are tried inside a page only: at a page boundary the reference takes any position for the next
+    rows, this library only the next one."""
+    if oracle.ref_adapter() is None:
+        pytest.skip("needs the reference's adapter (oracle/_ref)")
+    monkeypatch.delenv("CHROMOFOLD_B200_CODER", raising=False)
+    for seed in range(first, first + 12):
+        bad, what = _adapter_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
