@@ -1910,3 +1910,103 @@ def test_llama_kv_adapter_answers_like_the_references_own(native, oracle, first,
     for seed in range(first, first + 12):
         bad, what = _adapter_side_by_side(native, oracle, seed)
         assert bad is None, (bad, what)
+
+
+# ---- the multi-GPU admission runtime and the delta fetch beside the reference's own -----------------------------------
+def _multigpu_runtime_side_by_side(native, oracle, seed):
+    import ctypes as C
+    import torch
+    from compat_types import MultigpuCounters, MultigpuDeviceConfig, MultigpuPageView, MultigpuRuntimeConfig, MultigpuShard
+    rng = np.random.default_rng(seed)
+    libs = [native.lib(), oracle.ref_device()]
+    for l in libs: l.cf_multigpu_cuda_create.restype = C.c_void_p; l.cf_multigpu_cuda_last_error.restype = C.c_char_p
+    ndev = int(rng.integers(1, 5))
+    ords = [int(x) for x in rng.choice(6, ndev, replace=rng.random() < 0.1)]
+    if rng.random() < 0.8 and 0 not in ords: ords[0] = 0
+    devs = (MultigpuDeviceConfig * ndev)(*[MultigpuDeviceConfig(o if rng.random() < 0.95 else -1, int(rng.choice([0, 1 << 30])) if rng.random() < 0.1 else 1 << 30, 0) for o in ords])
+    cfg = MultigpuRuntimeConfig(C.cast(devs, C.c_void_p), ndev, int(rng.integers(1, 4)), int(rng.integers(1, 5)), int(rng.integers(0, 2)), int(rng.integers(0, 2)), int(rng.integers(0, 3)))
+    hs = [C.c_void_p(l.cf_multigpu_cuda_create(C.byref(cfg))) for l in libs]
+    what = dict(seed=seed, ords=ords, tp=cfg.tensor_parallel_size, layers=cfg.layer_count)
+    if bool(hs[0].value) != bool(hs[1].value): return ("create", bool(hs[0].value), bool(hs[1].value)), what
+    if not hs[0].value: return None, what
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda"); ptr = buf.data_ptr()
+    log = []
+    for step in range(int(rng.integers(3, 20))):
+        op = ["execute", "execute", "execute", "migrate", "inject", "shutdown"][int(rng.integers(0, 6))]
+        if op == "execute":
+            n = int(rng.integers(1, 4)); shards = (MultigpuShard * n)(); keep = []
+            for i in range(n):
+                npages = int(rng.integers(0, 4)) if rng.random() < 0.15 else int(rng.integers(1, 4))
+                dim = int(rng.choice([64, 128]))
+                pages = (MultigpuPageView * max(npages, 1))()
+                for j in range(npages):
+                    pages[j] = MultigpuPageView(ptr if rng.random() < 0.95 else None, ptr, ptr, ptr, 1024, 1024, int(rng.choice([4, 4, 4, 8, 1, 0, 9])), int(rng.choice([4, 4, 8, 2])),
+                                                int(rng.choice([16, 16, 0])), 2, dim if rng.random() < 0.95 else dim + 1, 32, 0, 1)
+                keep.append(pages)
+                shards[i] = MultigpuShard(int(rng.integers(1, 9)), int(rng.integers(0, cfg.layer_count + 1)) if rng.random() < 0.2 else 0, 0, int(rng.integers(0, 3)) if rng.random() < 0.1 else 4,
+                                          0 if rng.random() < 0.9 else int(rng.choice([7, -1])), ptr if rng.random() < 0.95 else None, ptr, 3, 3, dim, npages, C.cast(pages, C.c_void_p))
+            r = tuple(l.cf_multigpu_cuda_execute_async(h, shards, n, None) for l, h in zip(libs, hs))
+        elif op == "migrate":
+            pages = (MultigpuPageView * 2)(); src = int(rng.choice([0, 1])); dst = int(rng.choice([0, 1, 2]))
+            for j in range(2): pages[j] = MultigpuPageView(ptr, ptr if rng.random() < 0.9 else None, ptr, ptr, 64, 64, 4, 4, 16, 2, 64, 32, src if rng.random() < 0.9 else 5, 1)
+            count = int(rng.integers(0, 3))
+            r = tuple(l.cf_multigpu_cuda_migrate_sequence_async(h, C.c_uint64(3), src, dst, pages, count, None) for l, h in zip(libs, hs))
+        elif op == "inject":
+            if rng.random() < 0.7: continue
+            o = int(rng.choice(ords + [9])); r = tuple(l.cf_multigpu_cuda_inject_device_failure(h, o) for l, h in zip(libs, hs))
+        else:
+            if rng.random() < 0.8: continue
+            r = tuple(l.cf_multigpu_cuda_shutdown(h) for l, h in zip(libs, hs))
+        log.append((op, r))
+        if r[0] != r[1]: return ("status", log[-5:], libs[0].cf_multigpu_cuda_last_error(hs[0]), libs[1].cf_multigpu_cuda_last_error(hs[1])), what
+    ka, kb = MultigpuCounters(), MultigpuCounters()
+    libs[0].cf_multigpu_cuda_get_counters(hs[0], C.byref(ka)); libs[1].cf_multigpu_cuda_get_counters(hs[1], C.byref(kb))
+    diff = {n: (int(getattr(ka, n)), int(getattr(kb, n))) for n, _ in MultigpuCounters._fields_ if getattr(ka, n) != getattr(kb, n)}
+    for l, h in zip(libs, hs): l.cf_multigpu_cuda_destroy(h)
+    return (("counters", diff, log[-4:]), what) if diff else (None, what)
+
+
+def _delta_fetch_side_by_side(native, oracle, seed):
+    """A random reference/delta cluster (sorted override positions per member, some past the base's end) and random
+    queries, through cf_delta_fetch_async here and in the reference (src/cuda/delta_apply.cu): the same tokens."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(seed)
+    nbase, members = int(rng.integers(1, 5000)), int(rng.integers(1, 200))
+    base = rng.integers(0, 50000, nbase).astype(np.int32)
+    lens = rng.integers(0, min(nbase, 60) + 1, members).astype(np.int32)
+    if rng.random() < 0.3:
+        lens[:] = 0
+    starts = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+    dpos = np.concatenate([np.sort(rng.choice(nbase + 50, int(n), replace=False)) for n in lens] + [np.zeros(1)]).astype(np.int32)
+    dval = rng.integers(0, 50000, dpos.size).astype(np.int32)
+    count = int(rng.integers(1, 20000))
+    leaf = rng.integers(0, members, count).astype(np.int32)
+    pos = rng.integers(0, nbase + 100, count).astype(np.int32)
+    dev = [torch.from_numpy(x).cuda() for x in (base, dpos, dval, starts, lens, leaf, pos)]
+    outs = []
+    for lib in (native.lib(), oracle.ref_device()):
+        lib.cf_delta_fetch_async.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 7 + [C.c_size_t, C.c_void_p]
+        out = torch.full((count,), -7, dtype=torch.int32, device="cuda")
+        rc = lib.cf_delta_fetch_async(dev[0].data_ptr(), nbase, dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr(), dev[4].data_ptr(),
+                                      dev[5].data_ptr(), dev[6].data_ptr(), out.data_ptr(), count, None)
+        torch.cuda.synchronize()
+        outs.append((rc, out.cpu().numpy()))
+    if outs[0][0] != outs[1][0] or not np.array_equal(outs[0][1], outs[1][1]):
+        return ("delta fetch", outs[0][0], outs[1][0], int((outs[0][1] != outs[1][1]).sum())), dict(seed=seed, nbase=nbase, members=members)
+    return None, None
+
+
+@pytest.mark.parametrize("first", range(0, 60, 30))
+def test_multigpu_runtime_and_delta_fetch_answer_like_the_references_own(native, oracle, first):
+    """cf_multigpu_cuda_* (create with valid and invalid device lists, execute with valid and invalid shards and pages,
+    migrate, injected device failures, shutdown; local pages on device 0, so that neither side needs a second GPU) and
+    cf_delta_fetch_async, here and in the reference (oracle/_ref): same status for every call, equal counters, the same
+    fetched tokens."""
+    if oracle.ref_device() is None:
+        pytest.skip("needs the reference's sources compiled (oracle/_ref)")
+    for seed in range(first, first + 30):
+        bad, what = _multigpu_runtime_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
+        bad, what = _delta_fetch_side_by_side(native, oracle, seed)
+        assert bad is None, (bad, what)
