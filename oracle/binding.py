@@ -21,6 +21,9 @@ def build(with_ref=None):
         with_ref = os.path.isdir(os.path.join(ref_root, "src", "runtime"))
     if with_ref:
         targets.append("ref")
+        # the reference's own test programs, linked against this repository's library (which must be built already)
+        if os.path.exists(os.path.join(HERE, "..", "chromofold_b200", "libchromofold_b200.so")):
+            targets.append("reftests")
     subprocess.run(["make", "-C", HERE, f"REF={ref_root}"] + targets, check=True, capture_output=True)
 
 
@@ -79,6 +82,14 @@ def ref_adapter():
     built)."""
     path = os.path.join(HERE, "_ref", "libcfref_adapter.so")
     return C.CDLL(path) if os.path.exists(path) else None
+
+
+def reference_test_programs():
+    """{name: path} of the reference's own test programs built against this repository's library (oracle/_ref/reftests)."""
+    folder = os.path.join(HERE, "_ref", "reftests")
+    if not os.path.isdir(folder):
+        return {}
+    return {name: os.path.join(folder, name) for name in sorted(os.listdir(folder)) if os.access(os.path.join(folder, name), os.X_OK)}
 
 
 def _p(a, t=None):
