@@ -23,7 +23,7 @@ def build(with_ref=None):
         targets.append("ref")
         # the reference's own test programs, linked against this repository's library (which must be built already)
         if os.path.exists(os.path.join(HERE, "..", "chromofold_b200", "libchromofold_b200.so")):
-            targets.append("reftests")
+            targets += ["reftests", "benchmarks"]
     subprocess.run(["make", "-C", HERE, f"REF={ref_root}"] + targets, check=True, capture_output=True)
 
 
