@@ -96,3 +96,103 @@ def test_dense_backend_states_count_like_the_references_own(native, oracle):
         assert bytes(counters[0]) == bytes(counters[1])
         for l, s in zip(libs, states):
             l.cf_llama_graph_destroy(s)
+
+
+def _random_page(rng, fake):
+    """A page view that is valid about half the time: every field goes wrong with a few per cent probability."""
+    from compat_types import PageView
+    p = PageView()
+    odd = lambda good, bad: int(rng.choice(good)) if rng.random() < 0.96 else int(rng.choice(bad))
+    tokens, dim = odd([1, 4, 16, 64], [0, 4096]), odd([8, 64, 128], [0, 129, 256])
+    p.struct_size = odd([C.sizeof(PageView)], [0, 4, 300])
+    p.abi_version, p.flags = odd([0], [1, 9]), odd([1, 3], [0, 2])   # bit 0: sealed
+    p.layer, p.kv_head = int(rng.integers(0, 4)), int(rng.integers(0, 4))
+    p.token_begin = odd([0, 4, 100], [0xFFFFFFFE, 0xFFFFFFFF])
+    p.token_count, p.head_dim = tokens, dim
+    p.block_size, p.zero_point = odd([1, 32, 64], [0]), int(rng.choice([8, 128]))
+    values = tokens * dim
+    blocks = (values + max(p.block_size, 1) - 1) // max(p.block_size, 1)
+    ptr = lambda: fake if rng.random() < 0.98 else None
+    big = lambda n: n if rng.random() < 0.97 else int(rng.choice([0, 1, 0x7FFFFFFFFFFFFFFF]))
+    p.k_words, p.k_word_count = ptr(), big(max(values // 8, 1))
+    p.v_words, p.v_word_count = ptr(), big(max(values // 8, 1))
+    p.k_block_offsets, p.k_block_count = ptr(), big(blocks if rng.random() < 0.97 else max(blocks - 1, 0))
+    p.v_block_offsets, p.v_block_count = ptr(), big(blocks)
+    p.k_lut, p.k_lut_count, p.v_lut, p.v_lut_count = ptr(), big(16), ptr(), big(16)
+    p.k_scales, p.k_scale_count = ptr(), big(dim if rng.random() < 0.97 else dim + 1)
+    p.v_scales, p.v_scale_count = ptr(), big(tokens if rng.random() < 0.97 else tokens + 1)
+    return p
+
+
+def test_host_runtime_answers_like_the_references_own(native, oracle):
+    """cf_kv_validate_page / cf_kv_page_resident_bytes / cf_kv_validate_layout / cf_kv_cache_memory_stats on random
+    page views and layouts, and the online-softmax state (init, accumulate, merge, finalize) on random scores with -inf
+    and equal maxima among them: the same status and the same bytes as the reference's src/runtime/kv_runtime.cpp
+    (oracle/_ref)."""
+    from compat_types import CacheLayout, MemoryStats, PageView, SoftmaxState
+    ref = oracle.ref_cpu()
+    if ref is None:
+        pytest.skip("needs the reference's sources compiled (oracle/_ref)")
+    mine = native.lib()
+    rng = np.random.default_rng(79)
+    fake = 0x7f0000002000
+    for _ in range(3000):
+        p = _random_page(rng, fake)
+        assert mine.cf_kv_validate_page(C.byref(p)) == ref.cf_kv_validate_page(C.byref(p)), [getattr(p, n) for n, _ in PageView._fields_]
+        a, b = C.c_uint64(7), C.c_uint64(7)
+        ra, rb = mine.cf_kv_page_resident_bytes(C.byref(p), C.byref(a)), ref.cf_kv_page_resident_bytes(C.byref(p), C.byref(b))
+        assert (ra, a.value if ra == 0 else 0) == (rb, b.value if rb == 0 else 0), [getattr(p, n) for n, _ in PageView._fields_]
+    for _ in range(1500):
+        count = int(rng.integers(0, 5))
+        pages = (PageView * max(count, 1))()
+        begin = 0
+        for i in range(count):   # mostly a well-formed run of pages, sometimes not
+            q = _random_page(rng, fake) if rng.random() < 0.15 else _random_page(np.random.default_rng(1), fake)
+            if rng.random() < 0.85:
+                q.struct_size, q.abi_version, q.flags, q.token_count, q.head_dim, q.block_size = C.sizeof(PageView), 0, 1, 4, 8, 32
+                q.token_begin = begin if rng.random() < 0.9 else begin + 1
+                q.layer, q.kv_head = 0, 0
+                for name, n in (("k_word", 4), ("v_word", 4), ("k_block", 1), ("v_block", 1), ("k_lut", 16), ("v_lut", 16), ("k_scale", 8), ("v_scale", 4)):
+                    setattr(q, name + "s" if not name.endswith("lut") else name, fake)
+                    setattr(q, name + "_count", n)
+                q.k_block_offsets = q.v_block_offsets = fake
+                begin += 4
+            pages[i] = q
+        lay = CacheLayout()
+        lay.struct_size = C.sizeof(CacheLayout) if rng.random() < 0.9 else 8
+        lay.abi_version = int(rng.choice([0, 0, 0, 3]))
+        lay.layer_count, lay.kv_head_count, lay.head_dim = int(rng.choice([0, 1, 2])), int(rng.choice([0, 1, 2])), int(rng.choice([0, 8, 8, 16]))
+        lay.page_capacity_tokens = int(rng.choice([0, 4, 4, 8]))
+        lay.active_token_begin = begin if rng.random() < 0.8 else int(rng.integers(0, 40))
+        lay.active_token_count, lay.active_element_bytes = int(rng.choice([0, 2, 4, 5])), int(rng.choice([0, 2, 4, 4, 3]))
+        lay.pages, lay.page_count = (pages if rng.random() < 0.95 else None), count
+        lay.active_k_bytes = lay.active_v_bytes = int(lay.active_token_count) * 8 * int(lay.active_element_bytes) if rng.random() < 0.85 else 7
+        assert mine.cf_kv_validate_layout(C.byref(lay)) == ref.cf_kv_validate_layout(C.byref(lay))
+        sa, sb = MemoryStats(), MemoryStats()
+        ra, rb = mine.cf_kv_cache_memory_stats(C.byref(lay), C.byref(sa)), ref.cf_kv_cache_memory_stats(C.byref(lay), C.byref(sb))
+        assert ra == rb and (ra != 0 or bytes(sa) == bytes(sb))
+    for _ in range(300):
+        dim = int(rng.choice([1, 3, 64, 128]))
+        outs = []
+        seeds = int(rng.integers(0, 1 << 30))
+        for lib in (mine, ref):
+            r = np.random.default_rng(seeds)
+            states, buffers, log = [], [], []
+            for s in range(2):
+                buf = (C.c_double * dim)()
+                st = SoftmaxState()
+                log.append(lib.cf_online_softmax_init(C.byref(st), buf, dim if r.random() < 0.95 else 0))
+                states.append(st)
+                buffers.append(buf)
+                for _ in range(int(r.integers(0, 12))):
+                    score = float(r.choice([r.normal(0, 5), r.normal(0, 5), -np.inf, 3.0, 3.0, np.nan, np.inf]))
+                    value = r.standard_normal(dim).astype(np.float32)
+                    log.append(lib.cf_online_softmax_accumulate(C.byref(st), C.c_double(score), value.ctypes.data_as(C.c_void_p)))
+            log.append(lib.cf_online_softmax_merge(C.byref(states[0]), C.byref(states[1])))
+            out = np.full(dim, 9.0, np.float32)
+            log.append(lib.cf_online_softmax_finalize(C.byref(states[0]), out.ctypes.data_as(C.c_void_p)))
+            outs.append((log, out.tobytes(), states[0].max_score, states[0].exp_sum, states[0].initialized))
+        assert outs[0][0] == outs[1][0]
+        assert outs[0][1] == outs[1][1]
+        same = lambda x, y: x == y or (x != x and y != y)
+        assert same(outs[0][2], outs[1][2]) and same(outs[0][3], outs[1][3]) and outs[0][4] == outs[1][4]
