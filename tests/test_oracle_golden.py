@@ -132,3 +132,49 @@ def test_oracle_against_live_reference_sources(oracle):
     assert rc == 1
     rc, _ = oracle.dense_attention(k, v, 100, q[:1], 5, 0, 0.125)
     assert rc == 1
+
+
+def test_oracle_against_live_reference_sources_on_random_inputs(oracle):
+    """The same, swept: the oracle's dense attention beside reference::paged_attention on random shapes, windows and query
+    positions (positions with no visible token included: both must refuse), and the oracle's block-Huffman decoder
+    beside the reference's cf_bh_decode_at, bit position by bit position, on random streams."""
+    ref = oracle.ref_cpu()
+    if ref is None:
+        pytest.skip("oracle/_ref not built here")
+    from helpers import hist_of, laplace_codes
+    rng = np.random.default_rng(177)
+    for _ in range(150):
+        hkv = int(rng.choice([1, 2, 4]))
+        hq = hkv * int(rng.choice([1, 3, 4, 7]))
+        d = int(rng.choice([8, 32, 64, 128]))
+        tokens, begin = int(rng.integers(1, 80)), int(rng.choice([0, 0, 5, 100]))
+        nq = int(rng.integers(1, 4))
+        k = (rng.standard_normal((hkv, tokens, d)) * 10.0 ** rng.uniform(-2, 1)).astype(np.float32)
+        v = (rng.standard_normal((hkv, tokens, d)) * 10.0 ** rng.uniform(-3, 2)).astype(np.float32)
+        q = rng.standard_normal((nq, hq, d)).astype(np.float32)
+        qpos = int(rng.integers(0, begin + tokens + 10))
+        window = int(rng.choice([0, 0, 1, 7, 1000]))
+        scale = float(rng.choice([0.125, 1.0 / np.sqrt(d)]))
+        want = np.zeros((nq, hq, d), np.float32)
+        rc_ref = ref.ref_paged_attention_dense(_p(k), _p(v), C.c_uint32(begin), C.c_uint32(tokens), _p(q), C.c_uint32(nq),
+                                               C.c_uint32(hq), C.c_uint32(hkv), C.c_uint32(d), C.c_uint32(qpos),
+                                               C.c_uint32(window), C.c_float(scale), _p(want))
+        rc, got = oracle.dense_attention(k, v, begin, q, qpos, window, scale)
+        assert rc == rc_ref, (rc, rc_ref, begin, tokens, qpos, window, nq)
+        if rc == 0:
+            assert near(got, want), (begin, tokens, qpos, window)
+    for _ in range(60):
+        n, block = int(rng.integers(1, 3000)), int(rng.choice([16, 64, 100, 1024]))
+        sym = (laplace_codes(rng, n, float(10.0 ** rng.uniform(-0.5, 1.6))).astype(np.int16) + 128).astype(np.uint8)
+        cb = oracle.codebook_from_hist(hist_of(sym) if rng.random() < 0.7 else hist_of(sym) + 1)
+        words, off = oracle.huff_encode(sym, block, cb)
+        assert np.array_equal(oracle.huff_decode(words, off, cb, block, n), sym)
+        padded = np.concatenate([words, np.zeros(2, np.uint32)])
+        lut = cb.np("lut").astype(np.int32)
+        # the reference's decoder walks a block from its bit offset: entry = symbol | length << 8 (block_huffman_device.cuh)
+        for b in rng.choice(off.size, min(off.size, 6), replace=False):
+            pos = int(off[b])
+            for i in range(int(b) * block, min((int(b) + 1) * block, n)):
+                entry = ref.ref_bh_decode_at(_p(padded), _p(lut), C.c_int(12), C.c_int(pos))
+                assert (entry & 0xFF) == int(sym[i]), (n, block, int(b), i)
+                pos += entry >> 8
