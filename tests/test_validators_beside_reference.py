@@ -196,3 +196,57 @@ def test_host_runtime_answers_like_the_references_own(native, oracle):
         assert outs[0][1] == outs[1][1]
         same = lambda x, y: x == y or (x != x and y != y)
         assert same(outs[0][2], outs[1][2]) and same(outs[0][3], outs[1][3]) and outs[0][4] == outs[1][4]
+
+
+def test_dense_runtime_bridge_behaves_like_the_references_own(native, oracle, tmp_path):
+    """cf_llama_runtime_* on the dense backend (no adapter, no GPU): random record / append / error calls give the same
+    status and the same last_error text, the snapshots are equal byte for byte, and the evidence files written by
+    cf_llama_runtime_write_json are the same JSON documents."""
+    import json
+    from compat_types import LlamaRuntimeSnapshot, LlamaTensorView
+    ref = oracle.ref_adapter()
+    if ref is None:
+        pytest.skip("needs the reference's sources compiled (oracle/_ref)")
+    libs = [native.lib(), ref]
+    for l in libs:
+        l.cf_llama_runtime_create.restype = C.c_void_p
+        l.cf_llama_runtime_last_error.restype = C.c_char_p
+    rng = np.random.default_rng(80)
+    rows = np.zeros((1, 2, 64), np.float32)
+    view = LlamaTensorView(rows.ctypes.data, 2 * 64 * 4, 64 * 4, 4, 1, 2, 64, 0)
+    for run in range(40):
+        o = LlamaRuntimeOptions()
+        o.struct_size = C.sizeof(o)
+        o.kv.struct_size, o.kv.backend = C.sizeof(o.kv), 0          # dense
+        o.kv.layer_count, o.kv.kv_head_count, o.kv.query_head_count = 2, 2, 8
+        o.kv.head_dim, o.kv.page_size, o.kv.gqa_group_size, o.kv.kv_bits = 64, 32, 4, 8
+        o.causal_window, o.require_cuda, o.allow_dense_fallback, o.emit_stats = int(rng.choice([0, 512])), 0, 1, int(rng.integers(0, 2))
+        hs = [C.c_void_p(l.cf_llama_runtime_create(C.byref(o))) for l in libs]
+        assert bool(hs[0].value) == bool(hs[1].value)
+        if not hs[0].value:
+            continue
+        for _ in range(int(rng.integers(1, 15))):
+            op = int(rng.integers(0, 4))
+            if op == 0:
+                r = [l.cf_llama_runtime_record_dense_fallback(h) for l, h in zip(libs, hs)]
+            elif op == 1:
+                a, b = int(rng.integers(0, 1 << 20)), int(rng.integers(0, 1 << 10))
+                r = [l.cf_llama_runtime_record_compressed_launch(h, C.c_uint64(a), C.c_uint64(b)) for l, h in zip(libs, hs)]
+            elif op == 2:
+                r = [l.cf_llama_runtime_append(h, 0, 0, C.byref(view), C.byref(view), None) for l, h in zip(libs, hs)]
+            else:
+                r = [l.cf_llama_runtime_record_cuda_error(h) for l, h in zip(libs, hs)]
+            assert r[0] == r[1]
+            assert libs[0].cf_llama_runtime_last_error(hs[0]) == libs[1].cf_llama_runtime_last_error(hs[1])
+        snaps = [LlamaRuntimeSnapshot(), LlamaRuntimeSnapshot()]
+        for l, h, s in zip(libs, hs, snaps):
+            assert l.cf_llama_runtime_snapshot_get(h, C.byref(s)) == 0
+        assert bytes(snaps[0]) == bytes(snaps[1])
+        docs = []
+        for i, (l, h) in enumerate(zip(libs, hs)):
+            path = str(tmp_path / f"evidence_{run}_{i}.json").encode()
+            assert l.cf_llama_runtime_write_json(h, path) == 0
+            docs.append(json.load(open(path)))
+        assert docs[0] == docs[1]
+        for l, h in zip(libs, hs):
+            l.cf_llama_runtime_destroy(h)
