@@ -94,6 +94,9 @@ const char *cf_multisequence_last_error(const cf_multisequence_cache *cache);   
 /* ---- include/chromofold/llama_server_runtime.h ---------------------------------------------------------- */
 typedef struct cf_llama_server_runtime cf_llama_server_runtime;
 
+/* The reference's header uses `#pragma once`, so there is no guard macro to test for it: a translation unit that has
+ * already included it defines CHROMOFOLD_LLAMA_SERVER_RUNTIME_TYPES before this header. */
+#ifndef CHROMOFOLD_LLAMA_SERVER_RUNTIME_TYPES
 typedef struct cf_llama_server_config { /* :16-30 */
     uint32_t layer_count, query_head_count, kv_head_count, head_dim, page_size, block_size, context_window;
     uint32_t gqa_group_size, cuda_device, strict_mode;
@@ -118,6 +121,7 @@ typedef struct cf_llama_server_stats { /* :46-56 */
     uint64_t http_requests, interleaved_batches, slot_reuses, cancelled_requests, context_shifts, speculative_rollbacks;
     uint64_t dense_nodes_scheduled, shutdown_audits, shutdown_failures;
 } cf_llama_server_stats;
+#endif
 
 cf_llama_server_runtime *cf_llama_server_runtime_create(const cf_llama_server_config *config);              /* :58 */
 void cf_llama_server_runtime_destroy(cf_llama_server_runtime *runtime, void *stream);                        /* :59 */

@@ -15,6 +15,9 @@
 extern "C" {
 #endif
 
+/* The reference's header uses `#pragma once`: a translation unit that has already included it defines
+ * CHROMOFOLD_MULTIGPU_CUDA_RUNTIME_TYPES before this header. */
+#ifndef CHROMOFOLD_MULTIGPU_CUDA_RUNTIME_TYPES
 typedef enum cf_multigpu_transport { CF_MULTIGPU_TRANSPORT_P2P = 1, CF_MULTIGPU_TRANSPORT_HOST_STAGED = 2 } cf_multigpu_transport;
 typedef enum cf_multigpu_collective {
     CF_MULTIGPU_COLLECTIVE_NONE = 0, CF_MULTIGPU_COLLECTIVE_NCCL_ALL_REDUCE = 1, CF_MULTIGPU_COLLECTIVE_HOST_REDUCE = 2,
@@ -55,6 +58,7 @@ typedef struct cf_multigpu_counters { /* :68-88 */
     uint64_t device_failures_detected, fail_closed_rejections, cross_device_contamination, dense_fallback_launches;
     uint64_t cuda_errors, transfer_errors, page_refs_at_shutdown, snapshot_refs_at_shutdown;
 } cf_multigpu_counters;
+#endif
 
 typedef struct cf_multigpu_cuda_runtime cf_multigpu_cuda_runtime;
 

@@ -30,6 +30,9 @@
 extern "C" {
 #endif
 
+/* The reference's header uses `#pragma once`: a translation unit that has already included it defines
+ * CHROMOFOLD_PRODUCTION_ATTENTION_TYPES before this header. */
+#ifndef CHROMOFOLD_PRODUCTION_ATTENTION_TYPES
 typedef enum cf_attention_kernel_mode { CF_ATTENTION_REFERENCE = 0, CF_ATTENTION_OPTIMIZED = 1 } cf_attention_kernel_mode;
 
 typedef struct cf_attention_tuning { /* production_attention.h:16-24; accepted, not needed by this implementation */
@@ -68,6 +71,7 @@ typedef struct cf_attention_counters { /* :60-86 */
     uint64_t scale_bytes_read, allocation_count, pool_hits, pool_misses, peak_reserved_bytes, peak_live_bytes;
     uint64_t numerical_failures, cross_sequence_contamination, dense_fallback_launches, cuda_errors;
 } cf_attention_counters;
+#endif
 
 typedef struct cf_attention_runtime cf_attention_runtime;
 
