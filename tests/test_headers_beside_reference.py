@@ -45,6 +45,17 @@ def test_prototypes_are_the_references_own(tmp_path):
     assert done.returncode == 0, done.stderr[-3000:]
 
 
+def test_prototypes_of_the_second_library_are_the_references_own(tmp_path):
+    """compat_llama_ms_bridge.h (the llama-server bridges, a library of their own) beside the reference's bridge headers."""
+    _need_reference()
+    src = tmp_path / "bridges.cpp"
+    src.write_text('#include "multisequence/llama_server_multisequence_bridge.h"\n'
+                   '#include "multisequence/llama_server_cuda_resolver_bridge.h"\n'
+                   '#include "chromofold_b200/compat_llama_ms_bridge.h"\nint main() { return 0; }\n')
+    done = subprocess.run(["g++", "-fsyntax-only", "-Wall"] + _flags() + [str(src)], capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-3000:]
+
+
 def _structs():
     """(struct name, member names) of every struct with a body in this library's compat headers."""
     found = []
