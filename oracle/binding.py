@@ -68,6 +68,13 @@ def ref_mscache():
     return C.CDLL(path) if os.path.exists(path) else None
 
 
+def ref_msbridge():
+    """The reference's llama-server multisequence bridge (integrations/llama.cpp/multisequence/
+    llama_server_multisequence_bridge.cpp over its host cache; None when not built)."""
+    path = os.path.join(HERE, "_ref", "libcfref_msbridge.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
 def ref_device():
     """The reference's own decode runtime, seal engine, sequence resolver and dataplane (src/cuda/production_attention.cu,
     device_kv_seal_attention.cu, multisequence_cuda_resolver.cu, device_kv_dataplane.cu), compiled for sm_100a (None when

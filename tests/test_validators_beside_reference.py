@@ -286,3 +286,25 @@ def test_hand_written_host_contract_cases_hold_for_the_reference_itself(native, 
     stand_in = types.SimpleNamespace(**{k: getattr(native, k) for k in dir(native) if not k.startswith("__")})
     stand_in.lib = lambda: reference
     getattr(test_compat_host, name)(stand_in)
+
+
+@pytest.mark.parametrize("name", [
+    "test_graph_contract_validation", "test_dense_graph_state_counts_and_never_owns_a_runtime",
+    "test_runtime_bridge_options_and_dense_runtime", "test_forwarding_bridges_refuse_bad_options_without_a_gpu"])
+def test_hand_written_bridge_cases_hold_for_the_reference_itself(native, oracle, name, tmp_path):
+    """The same for the CPU cases of tests/test_compat_bridges.py: the llama.cpp-side bridges of the reference
+    (integrations/llama.cpp/*.cpp, compiled into oracle/_ref) must pass the very tests written for this library's."""
+    import inspect
+    import types
+    import test_compat_bridges
+    if any(lib is None for lib in (oracle.ref_device(), oracle.ref_adapter(), oracle.ref_msbridge())):
+        pytest.skip("needs the reference's sources compiled (oracle/_ref)")
+    reference = _ReferenceLibraries(oracle)
+    stand_in = types.SimpleNamespace(**{k: getattr(native, k) for k in dir(native) if not k.startswith("__")})
+    stand_in.lib = lambda: reference
+    stand_in.ms_bridge_lib = oracle.ref_msbridge
+    function = getattr(test_compat_bridges, name)
+    if "tmp_path" in inspect.signature(function).parameters:
+        function(stand_in, tmp_path)
+    else:
+        function(stand_in)
